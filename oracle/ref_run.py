@@ -1,0 +1,96 @@
+"""Child-process runner for the UNMODIFIED reference build on its ``paras:0`` host engine.
+
+TEST INFRASTRUCTURE ONLY (checker and CPU-baseline timer); never on the product path.
+
+    python oracle/ref_run.py jobs.pt results.pt
+
+``jobs.pt`` is a ``torch.save``'d list of dicts ``{"op": name, "args": {...}, "repeat": n}``;
+``results.pt`` receives a list of ``{"out": tensor | tuple, "seconds": best wall time,
+"threads": host threads the reference engine used}``.  Ops go through exactly the public
+entry points a user of the reference calls (F.scaled_dot_product_attention,
+torch.ops.aten.rms_norm, torch.ops.paras.*, torch.ops.torch_paras.swiglu).
+"""
+import os
+import sys
+import time
+
+import torch
+import torch.nn.functional as F
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+import ref_loader  # noqa: E402
+
+DEV = "paras:0"
+
+
+def _dev(t):
+    return t.to(DEV) if torch.is_tensor(t) else t
+
+
+def _cpu(o):
+    if torch.is_tensor(o):
+        return o.cpu()
+    if isinstance(o, (tuple, list)):
+        return tuple(_cpu(x) for x in o)
+    return o
+
+
+def run_op(op, a):
+    if op == "sdpa":
+        q, k, v = _dev(a["q"]), _dev(a["k"]), _dev(a["v"])
+        mask = _dev(a.get("attn_mask"))
+        kw = {}
+        if a.get("scale") is not None:
+            kw["scale"] = a["scale"]
+        if a.get("enable_gqa"):
+            kw["enable_gqa"] = True
+        return lambda: F.scaled_dot_product_attention(
+            q, k, v, attn_mask=mask, is_causal=bool(a.get("is_causal", False)), **kw)
+    if op == "rms_norm_aten":
+        x, w = _dev(a["x"]), _dev(a.get("weight"))
+        return lambda: torch.ops.aten.rms_norm(x, list(a["normalized_shape"]), w, a.get("eps"))
+    if op == "rms_norm_paras":
+        x, w = _dev(a["x"]), _dev(a["weight"])
+        return lambda: torch.ops.paras.rms_norm(x, w, float(a["eps"]))
+    if op == "rms_norm_paras_backward":
+        g, x, w, r = _dev(a["grad_out"]), _dev(a["x"]), _dev(a["weight"]), _dev(a["rstd"])
+        return lambda: torch.ops.paras.rms_norm_backward(g, x, w, r)
+    if op == "swiglu_paras":
+        g, u = _dev(a["gate"]), _dev(a["up"])
+        return lambda: torch.ops.paras.swiglu(g, u)
+    if op == "swiglu_paras_backward":
+        d, g, u = _dev(a["grad_out"]), _dev(a["gate"]), _dev(a["up"])
+        return lambda: torch.ops.paras.swiglu_backward(d, g, u)
+    if op == "swiglu_composite":
+        x, g = _dev(a["x"]), _dev(a["gate"])
+        return lambda: torch.ops.torch_paras.swiglu(x, g)
+    if op == "rotate_half":
+        x = _dev(a["x"])
+        return lambda: torch.ops.paras.rotate_half(x)
+    if op == "rotate_half_backward":
+        x = _dev(a["grad_out"])
+        return lambda: torch.ops.paras.rotate_half_backward(x)
+    raise ValueError(f"unknown op {op}")
+
+
+def main():
+    jobs_path, out_path = sys.argv[1], sys.argv[2]
+    mod = ref_loader.load()
+    jobs = torch.load(jobs_path)
+    results = []
+    for job in jobs:
+        fn = run_op(job["op"], job["args"])
+        best, out = None, None
+        for _ in range(max(1, int(job.get("repeat", 1)))):
+            t0 = time.perf_counter()
+            out = fn()
+            mod.synchronize_all()
+            dt = time.perf_counter() - t0
+            best = dt if best is None else min(best, dt)
+        results.append({"out": _cpu(out) if job.get("keep_out", True) else None,
+                        "seconds": best, "threads": torch.get_num_threads()})
+    torch.save(results, out_path)
+
+
+if __name__ == "__main__":
+    main()
