@@ -1,0 +1,133 @@
+// Shared helpers of libparas_b200: status codes, thread-local error text, device/stream
+// resolution and small device-side conversion utilities.  No torch, no C++ exceptions
+// across the ABI.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+
+#include "paras_b200.h"
+
+namespace pb {
+
+// Records a message for paras_b200_last_error() of this thread and returns `code`.
+int fail(int code, const char* fmt, ...);
+void set_last_kernel(const char* name);
+
+// Per-GPU state owned by runtime.cu.
+struct Gpu {
+    int ordinal = -1;
+    cudaStream_t stream = nullptr;     // the library's non-blocking stream
+    cudaStream_t copy_stream = nullptr;
+    cudaMemPool_t pool = nullptr;
+    int sm_count = 0;
+    int cc_major = 0, cc_minor = 0;
+    size_t smem_optin = 0;
+    char name[256] = {0};
+    // Status word in mapped pinned host memory: kernels whose bounded waits run out
+    // write a non-zero code here instead of trapping or spinning.
+    int* status_host = nullptr;
+    int* status_dev = nullptr;
+};
+
+// Returns PARAS_E_TIMEOUT (and clears the word) when a kernel on `g` reported that one of
+// its bounded waits gave up; PARAS_OK otherwise.
+int check_status_word(Gpu* g);
+
+// Makes `gpu` current on the calling thread and returns its state; nullptr (and an error
+// message) when the ordinal is bad or there is no device.
+Gpu* use_gpu(int gpu, int* status);
+
+inline cudaStream_t pick_stream(Gpu* g, void* stream) {
+    return stream ? static_cast<cudaStream_t>(stream) : g->stream;
+}
+
+#define PB_CUDA(call)                                                                    \
+    do {                                                                                 \
+        cudaError_t e_ = (call);                                                         \
+        if (e_ != cudaSuccess)                                                           \
+            return ::pb::fail(PARAS_E_CUDA, "paras_b200: %s: %s", #call,                  \
+                              cudaGetErrorString(e_));                                   \
+    } while (0)
+
+#define PB_LAUNCH_CHECK(what)                                                            \
+    do {                                                                                 \
+        cudaError_t e_ = cudaGetLastError();                                             \
+        if (e_ != cudaSuccess)                                                           \
+            return ::pb::fail(PARAS_E_CUDA, "paras_b200: launch of %s failed: %s", what, \
+                              cudaGetErrorString(e_));                                   \
+    } while (0)
+
+inline size_t dtype_size(int dt) { return dt == PARAS_F32 ? 4 : 2; }
+
+// ---- device-side scalar conversions -------------------------------------------------
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) {
+    return __bfloat162float(v);
+}
+template <> __device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) {
+    return __float2bfloat16_rn(v);
+}
+template <> __device__ __forceinline__ __half from_f32<__half>(float v) {
+    return __float2half_rn(v);
+}
+
+// Rounds an fp32 value to T and back: the reference's "result cast to the tensor dtype".
+template <typename T> __device__ __forceinline__ float round_to(float v) {
+    return to_f32<T>(from_f32<T>(v));
+}
+
+// 16-byte vector of T.
+template <typename T> struct Vec16 {
+    static constexpr int N = 16 / sizeof(T);
+    T v[N];
+};
+
+template <typename T>
+__device__ __forceinline__ Vec16<T> ld16(const T* p) {
+    Vec16<T> r;
+    *reinterpret_cast<uint4*>(&r) = *reinterpret_cast<const uint4*>(p);
+    return r;
+}
+template <typename T>
+__device__ __forceinline__ Vec16<T> ld16_stream(const T* p) {
+    Vec16<T> r;
+    *reinterpret_cast<uint4*>(&r) = __ldcs(reinterpret_cast<const uint4*>(p));
+    return r;
+}
+template <typename T>
+__device__ __forceinline__ void st16(T* p, const Vec16<T>& r) {
+    *reinterpret_cast<uint4*>(p) = *reinterpret_cast<const uint4*>(&r);
+}
+template <typename T>
+__device__ __forceinline__ void st16_stream(T* p, const Vec16<T>& r) {
+    __stcs(reinterpret_cast<uint4*>(p), *reinterpret_cast<const uint4*>(&r));
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ double warp_sum(double v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+}  // namespace pb

@@ -1,0 +1,344 @@
+// Memory-bound elementwise kernels: SwiGLU forward/backward, rotate_half, strided
+// copy-with-cast and fill.
+//
+// SwiGLU replaces the reference's paras::swiglu lambda (csrc/ops/fused_ops.cpp:162-194,
+// one generic grid-stride thread per element with per-element div/mod index math, double
+// arithmetic) and the torch_paras::swiglu composite (csrc/ops/rms_swiglu_ops.cpp:83-86:
+// silu.out then mul.out, two passes over HBM) with ONE pass: 128-bit streaming loads of
+// gate and up, fp32 math, 128-bit streaming store.  Algorithmic traffic 3*n*sizeof(T).
+#include "common.cuh"
+
+namespace pb {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kUnroll = 4;
+
+template <typename T> __device__ __forceinline__ float silu_f32(float g) {
+    if constexpr (sizeof(T) == 4) {
+        return g / (1.0f + expf(-g));
+    } else {
+        return __fdividef(g, 1.0f + __expf(-g));
+    }
+}
+
+template <typename T, int MODE>
+__device__ __forceinline__ T swiglu_one(T g, T u) {
+    const float gf = to_f32<T>(g);
+    const float uf = to_f32<T>(u);
+    float s = silu_f32<T>(gf);
+    if constexpr (MODE == PARAS_ROUND_PER_OP) s = round_to<T>(s);
+    return from_f32<T>(s * uf);
+}
+
+template <typename T, int MODE>
+__global__ void __launch_bounds__(kThreads)
+swiglu_fwd_vec_kernel(const T* __restrict__ gate, const T* __restrict__ up, T* __restrict__ out,
+                      int64_t nvec) {
+    constexpr int N = Vec16<T>::N;
+    const int64_t stride = int64_t(gridDim.x) * kThreads * kUnroll;
+    for (int64_t base = int64_t(blockIdx.x) * kThreads * kUnroll + threadIdx.x; base < nvec;
+         base += stride) {
+        Vec16<T> g[kUnroll], u[kUnroll];
+#pragma unroll
+        for (int k = 0; k < kUnroll; ++k) {
+            const int64_t i = base + int64_t(k) * kThreads;
+            if (i < nvec) {
+                g[k] = ld16_stream(gate + i * N);
+                u[k] = ld16_stream(up + i * N);
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < kUnroll; ++k) {
+            const int64_t i = base + int64_t(k) * kThreads;
+            if (i < nvec) {
+                Vec16<T> o;
+#pragma unroll
+                for (int e = 0; e < N; ++e) o.v[e] = swiglu_one<T, MODE>(g[k].v[e], u[k].v[e]);
+                st16_stream(out + i * N, o);
+            }
+        }
+    }
+}
+
+template <typename T, int MODE>
+__global__ void __launch_bounds__(kThreads)
+swiglu_fwd_scalar_kernel(const T* __restrict__ gate, const T* __restrict__ up,
+                         T* __restrict__ out, int64_t begin, int64_t n) {
+    for (int64_t i = begin + int64_t(blockIdx.x) * kThreads + threadIdx.x; i < n;
+         i += int64_t(gridDim.x) * kThreads)
+        out[i] = swiglu_one<T, MODE>(gate[i], up[i]);
+}
+
+// dgate = dy*u*s*(1+g*(1-s)), dup = dy*g*s with s = sigmoid(g)  (fused_ops.cpp:196-229)
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+swiglu_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ gate, const T* __restrict__ up,
+                  T* __restrict__ dgate, T* __restrict__ dup, int64_t n) {
+    for (int64_t i = int64_t(blockIdx.x) * kThreads + threadIdx.x; i < n;
+         i += int64_t(gridDim.x) * kThreads) {
+        const float d = to_f32<T>(dy[i]), g = to_f32<T>(gate[i]), u = to_f32<T>(up[i]);
+        const float s = 1.0f / (1.0f + expf(-g));
+        dup[i] = from_f32<T>(d * g * s);
+        dgate[i] = from_f32<T>(d * u * (s * (1.0f + g * (1.0f - s))));
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+rotate_half_kernel(const T* __restrict__ x, T* __restrict__ out, int64_t n, int64_t D,
+                   int backward) {
+    const int64_t half = D / 2;
+    for (int64_t i = int64_t(blockIdx.x) * kThreads + threadIdx.x; i < n;
+         i += int64_t(gridDim.x) * kThreads) {
+        const int64_t col = i % D;
+        const bool lo = col < half;
+        const T v = x[lo ? i + half : i - half];
+        const bool neg = backward ? !lo : lo;
+        out[i] = neg ? from_f32<T>(-to_f32<T>(v)) : v;
+    }
+}
+
+// ---- strided copy with conversion ----------------------------------------------------
+struct CopySpec {
+    int ndim;
+    int64_t sizes[8];
+    int64_t sstr[8];
+    int64_t dstr[8];
+};
+
+struct Wide {
+    double d;
+    long long i;
+    bool is_int;
+};
+
+__device__ __forceinline__ Wide load_wide(const void* p, int code, int64_t off) {
+    Wide w{0.0, 0, false};
+    switch (code) {
+        case PARAS_SC_F32: w.d = static_cast<const float*>(p)[off]; break;
+        case PARAS_SC_BF16: w.d = __bfloat162float(static_cast<const __nv_bfloat16*>(p)[off]); break;
+        case PARAS_SC_F16: w.d = __half2float(static_cast<const __half*>(p)[off]); break;
+        case PARAS_SC_F64: w.d = static_cast<const double*>(p)[off]; break;
+        case PARAS_SC_I64: w.i = static_cast<const long long*>(p)[off]; w.is_int = true; break;
+        case PARAS_SC_I32: w.i = static_cast<const int*>(p)[off]; w.is_int = true; break;
+        case PARAS_SC_I16: w.i = static_cast<const short*>(p)[off]; w.is_int = true; break;
+        case PARAS_SC_I8: w.i = static_cast<const signed char*>(p)[off]; w.is_int = true; break;
+        case PARAS_SC_U8: w.i = static_cast<const unsigned char*>(p)[off]; w.is_int = true; break;
+        case PARAS_SC_BOOL: w.i = static_cast<const unsigned char*>(p)[off] ? 1 : 0; w.is_int = true; break;
+    }
+    return w;
+}
+
+__device__ __forceinline__ void store_wide(void* p, int code, int64_t off, const Wide& w) {
+    const double d = w.is_int ? double(w.i) : w.d;
+    const long long i = w.is_int ? w.i : (long long)(w.d);
+    switch (code) {
+        case PARAS_SC_F32: static_cast<float*>(p)[off] = w.is_int ? float(w.i) : float(w.d); break;
+        case PARAS_SC_BF16: static_cast<__nv_bfloat16*>(p)[off] = __float2bfloat16_rn(float(d)); break;
+        case PARAS_SC_F16: static_cast<__half*>(p)[off] = __float2half_rn(float(d)); break;
+        case PARAS_SC_F64: static_cast<double*>(p)[off] = d; break;
+        case PARAS_SC_I64: static_cast<long long*>(p)[off] = i; break;
+        case PARAS_SC_I32: static_cast<int*>(p)[off] = int(i); break;
+        case PARAS_SC_I16: static_cast<short*>(p)[off] = short(i); break;
+        case PARAS_SC_I8: static_cast<signed char*>(p)[off] = (signed char)(i); break;
+        case PARAS_SC_U8: static_cast<unsigned char*>(p)[off] = (unsigned char)(i); break;
+        case PARAS_SC_BOOL:
+            static_cast<unsigned char*>(p)[off] = (w.is_int ? (w.i != 0) : (w.d != 0.0)) ? 1 : 0;
+            break;
+    }
+}
+
+__global__ void __launch_bounds__(kThreads)
+strided_copy_kernel(void* dst, int dcode, const void* src, int scode, CopySpec sp, int64_t n) {
+    for (int64_t i = int64_t(blockIdx.x) * kThreads + threadIdx.x; i < n;
+         i += int64_t(gridDim.x) * kThreads) {
+        int64_t rem = i, so = 0, dof = 0;
+#pragma unroll 1
+        for (int d = sp.ndim - 1; d >= 0; --d) {
+            const int64_t q = rem / sp.sizes[d];
+            const int64_t r = rem - q * sp.sizes[d];
+            so += r * sp.sstr[d];
+            dof += r * sp.dstr[d];
+            rem = q;
+        }
+        store_wide(dst, dcode, dof, load_wide(src, scode, so));
+    }
+}
+
+__global__ void __launch_bounds__(kThreads)
+fill_kernel(void* dst, int code, double value, int64_t n) {
+    Wide w{value, (long long)value, false};
+    for (int64_t i = int64_t(blockIdx.x) * kThreads + threadIdx.x; i < n;
+         i += int64_t(gridDim.x) * kThreads)
+        store_wide(dst, code, i, w);
+}
+
+int grid_for(const Gpu* g, int64_t work_items, int per_block, int waves = 8) {
+    int64_t blocks = (work_items + per_block - 1) / per_block;
+    const int64_t cap = int64_t(g->sm_count > 0 ? g->sm_count : 148) * waves;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    return int(blocks);
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+template <typename T, int MODE>
+int launch_swiglu(Gpu* g, const void* gate, const void* up, void* out, int64_t n,
+                  cudaStream_t s) {
+    constexpr int N = Vec16<T>::N;
+    const T* pg = static_cast<const T*>(gate);
+    const T* pu = static_cast<const T*>(up);
+    T* po = static_cast<T*>(out);
+    int64_t done = 0;
+    if (aligned16(gate) && aligned16(up) && aligned16(out) && n >= N) {
+        const int64_t nvec = n / N;
+        // One CTA-iteration moves kThreads*kUnroll vectors; the grid is a multiple of the
+        // SM count so every SM streams the same share.
+        const int blocks = grid_for(g, nvec, kThreads * kUnroll, 16);
+        swiglu_fwd_vec_kernel<T, MODE><<<blocks, kThreads, 0, s>>>(pg, pu, po, nvec);
+        PB_LAUNCH_CHECK("swiglu_fwd_vec_kernel");
+        done = nvec * N;
+    }
+    if (done < n) {
+        const int blocks = grid_for(g, n - done, kThreads);
+        swiglu_fwd_scalar_kernel<T, MODE><<<blocks, kThreads, 0, s>>>(pg, pu, po, done, n);
+        PB_LAUNCH_CHECK("swiglu_fwd_scalar_kernel");
+    }
+    return PARAS_OK;
+}
+
+}  // namespace
+}  // namespace pb
+
+using pb::fail;
+using pb::Gpu;
+
+extern "C" {
+
+int paras_b200_swiglu_fwd(int gpu, const void* gate, const void* up, void* out, int64_t n,
+                          int dtype, int mode, void* stream) {
+    if (n < 0) return fail(PARAS_E_INVALID, "paras swiglu: negative element count");
+    if (dtype != PARAS_F32 && dtype != PARAS_BF16 && dtype != PARAS_F16)
+        return fail(PARAS_E_UNSUPPORTED, "paras swiglu: unsupported dtype %d", dtype);
+    if (mode != PARAS_ROUND_ONCE && mode != PARAS_ROUND_PER_OP)
+        return fail(PARAS_E_INVALID, "paras swiglu: bad rounding mode %d", mode);
+    int st;
+    Gpu* g = pb::use_gpu(gpu, &st);
+    if (!g) return st;
+    if (n == 0) return PARAS_OK;
+    if (!gate || !up || !out) return fail(PARAS_E_INVALID, "paras swiglu: null pointer");
+    cudaStream_t s = pb::pick_stream(g, stream);
+#define PB_SWIGLU(T)                                                               \
+    (mode == PARAS_ROUND_ONCE ? pb::launch_swiglu<T, PARAS_ROUND_ONCE>(g, gate, up, out, n, s) \
+                              : pb::launch_swiglu<T, PARAS_ROUND_PER_OP>(g, gate, up, out, n, s))
+    switch (dtype) {
+        case PARAS_F32: return PB_SWIGLU(float);
+        case PARAS_BF16: return PB_SWIGLU(__nv_bfloat16);
+        default: return PB_SWIGLU(__half);
+    }
+#undef PB_SWIGLU
+}
+
+int paras_b200_swiglu_bwd(int gpu, const void* grad_out, const void* gate, const void* up,
+                          void* grad_gate, void* grad_up, int64_t n, int dtype, void* stream) {
+    if (n < 0) return fail(PARAS_E_INVALID, "paras swiglu_backward: negative element count");
+    if (dtype != PARAS_F32 && dtype != PARAS_BF16 && dtype != PARAS_F16)
+        return fail(PARAS_E_UNSUPPORTED, "paras swiglu_backward: unsupported dtype %d", dtype);
+    int st;
+    Gpu* g = pb::use_gpu(gpu, &st);
+    if (!g) return st;
+    if (n == 0) return PARAS_OK;
+    if (!grad_out || !gate || !up || !grad_gate || !grad_up)
+        return fail(PARAS_E_INVALID, "paras swiglu_backward: null pointer");
+    cudaStream_t s = pb::pick_stream(g, stream);
+    const int blocks = pb::grid_for(g, n, pb::kThreads);
+#define PB_BWD(T)                                                                        \
+    pb::swiglu_bwd_kernel<T><<<blocks, pb::kThreads, 0, s>>>(                             \
+        static_cast<const T*>(grad_out), static_cast<const T*>(gate),                    \
+        static_cast<const T*>(up), static_cast<T*>(grad_gate), static_cast<T*>(grad_up), n)
+    switch (dtype) {
+        case PARAS_F32: PB_BWD(float); break;
+        case PARAS_BF16: PB_BWD(__nv_bfloat16); break;
+        default: PB_BWD(__half); break;
+    }
+#undef PB_BWD
+    PB_LAUNCH_CHECK("swiglu_bwd_kernel");
+    return PARAS_OK;
+}
+
+int paras_b200_rotate_half(int gpu, const void* x, void* out, int64_t rows, int64_t D, int dtype,
+                           int backward, void* stream) {
+    if (rows < 0 || D < 0) return fail(PARAS_E_INVALID, "paras rotate_half: negative size");
+    if (D % 2) return fail(PARAS_E_INVALID, "paras rotate_half: last dimension must be even");
+    if (dtype != PARAS_F32 && dtype != PARAS_BF16 && dtype != PARAS_F16)
+        return fail(PARAS_E_UNSUPPORTED, "paras rotate_half: unsupported dtype %d", dtype);
+    int st;
+    Gpu* g = pb::use_gpu(gpu, &st);
+    if (!g) return st;
+    const int64_t n = rows * D;
+    if (n == 0) return PARAS_OK;
+    if (!x || !out) return fail(PARAS_E_INVALID, "paras rotate_half: null pointer");
+    cudaStream_t s = pb::pick_stream(g, stream);
+    const int blocks = pb::grid_for(g, n, pb::kThreads);
+#define PB_ROT(T)                                                                   \
+    pb::rotate_half_kernel<T><<<blocks, pb::kThreads, 0, s>>>(                       \
+        static_cast<const T*>(x), static_cast<T*>(out), n, D, backward)
+    switch (dtype) {
+        case PARAS_F32: PB_ROT(float); break;
+        case PARAS_BF16: PB_ROT(__nv_bfloat16); break;
+        default: PB_ROT(__half); break;
+    }
+#undef PB_ROT
+    PB_LAUNCH_CHECK("rotate_half_kernel");
+    return PARAS_OK;
+}
+
+int paras_b200_strided_copy(int gpu, void* dst, int dst_code, const int64_t* dst_strides,
+                            const void* src, int src_code, const int64_t* src_strides,
+                            const int64_t* sizes, int ndim, void* stream) {
+    if (ndim < 0 || ndim > 8)
+        return fail(PARAS_E_UNSUPPORTED, "paras copy: rank %d exceeds kernel limit 8", ndim);
+    if (dst_code < 0 || dst_code > PARAS_SC_BOOL || src_code < 0 || src_code > PARAS_SC_BOOL)
+        return fail(PARAS_E_UNSUPPORTED, "paras copy: unsupported element type");
+    if (ndim > 0 && (!sizes || !dst_strides || !src_strides))
+        return fail(PARAS_E_INVALID, "paras copy: null shape");
+    int st;
+    Gpu* g = pb::use_gpu(gpu, &st);
+    if (!g) return st;
+    pb::CopySpec sp{};
+    sp.ndim = ndim;
+    int64_t n = 1;
+    for (int d = 0; d < ndim; ++d) {
+        if (sizes[d] < 0) return fail(PARAS_E_INVALID, "paras copy: negative size");
+        sp.sizes[d] = sizes[d];
+        sp.sstr[d] = src_strides[d];
+        sp.dstr[d] = dst_strides[d];
+        n *= sizes[d];
+    }
+    if (n == 0) return PARAS_OK;
+    if (!dst || !src) return fail(PARAS_E_INVALID, "paras copy: null pointer");
+    const int blocks = pb::grid_for(g, n, pb::kThreads, 16);
+    pb::strided_copy_kernel<<<blocks, pb::kThreads, 0, pb::pick_stream(g, stream)>>>(
+        dst, dst_code, src, src_code, sp, n);
+    PB_LAUNCH_CHECK("strided_copy_kernel");
+    return PARAS_OK;
+}
+
+int paras_b200_fill(int gpu, void* dst, int code, double value, int64_t n, void* stream) {
+    if (n < 0) return fail(PARAS_E_INVALID, "paras fill: negative element count");
+    if (code < 0 || code > PARAS_SC_BOOL)
+        return fail(PARAS_E_UNSUPPORTED, "paras fill: unsupported element type");
+    int st;
+    Gpu* g = pb::use_gpu(gpu, &st);
+    if (!g) return st;
+    if (n == 0) return PARAS_OK;
+    if (!dst) return fail(PARAS_E_INVALID, "paras fill: null pointer");
+    const int blocks = pb::grid_for(g, n, pb::kThreads);
+    pb::fill_kernel<<<blocks, pb::kThreads, 0, pb::pick_stream(g, stream)>>>(dst, code, value, n);
+    PB_LAUNCH_CHECK("fill_kernel");
+    return PARAS_OK;
+}
+
+}  // extern "C"

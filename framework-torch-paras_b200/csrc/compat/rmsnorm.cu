@@ -1,0 +1,336 @@
+// RMSNorm forward/backward for sm_100a.
+//
+// Replaces (a) the reference's fused paras::rms_norm lambda (csrc/ops/fused_ops.cpp:43-88:
+// ONE THREAD per row, serial over H, double math, uncoalesced) and (b) the aten::rms_norm
+// composite (csrc/ops/rms_swiglu_ops.cpp:43-75: pow, mean, add, rsqrt, mul, mul = six
+// full passes over HBM, each rounding to the tensor dtype).
+//
+// Forward kernel: one WARP per row, the whole row held in registers, so HBM sees exactly
+// one 128-bit coalesced read and one 128-bit write per element (algorithmic traffic
+// 2*rows*H*sizeof(T) + H*sizeof(T)); sum of squares via warp shuffles, accumulated in
+// double so that 16-bit results reproduce the reference's double arithmetic.  Rows too
+// long for registers take a CTA-per-row two-pass kernel whose second read hits L2.
+//
+// MODE PARAS_ROUND_ONCE   : y = T((x * rstd) * w), rstd = 1/sqrt(sum(x^2)/H + eps)
+// MODE PARAS_ROUND_PER_OP : emulates the composite's per-op rounding (pointwise_ops.cpp:
+//                           33-52 unary, 62-85 binary, 246-249 mean = sum then *1/N).
+#include "common.cuh"
+
+namespace pb {
+namespace {
+
+constexpr int kWarpsPerBlock = 4;
+
+template <typename T> struct RowMath {
+    // value of x*x as the reference's pow(2) leaves it, plus its contribution to the sum
+    template <int MODE> static __device__ __forceinline__ float sq(float x) {
+        if constexpr (MODE == PARAS_ROUND_PER_OP) return round_to<T>(x * x);
+        return x * x;
+    }
+};
+
+// Per-row scalar pipeline shared by both kernels.  `ss` is the (double) sum of squares.
+template <typename T, int MODE>
+__device__ __forceinline__ void row_scalars(double ss, int64_t H, double eps, float* inv_f,
+                                            double* inv_d) {
+    if constexpr (MODE == PARAS_ROUND_ONCE) {
+        const double r = 1.0 / sqrt(ss / double(H) + eps);
+        *inv_d = r;
+        *inv_f = float(r);
+    } else {
+        // sum -> T, *1/N -> T, +eps(T) -> T, rsqrt -> T ; each via double -> float -> T
+        float s = round_to<T>(float(ss));
+        s = round_to<T>(float(double(s) * (1.0 / double(H))));
+        s = round_to<T>(float(double(s) + eps));
+        s = round_to<T>(float(1.0 / sqrt(double(s))));
+        *inv_f = s;
+        *inv_d = double(s);
+    }
+}
+
+template <typename T, int MODE>
+__device__ __forceinline__ T finish(T xv, float inv_f, double inv_d, bool has_w, T wv) {
+    if constexpr (MODE == PARAS_ROUND_ONCE) {
+        if constexpr (sizeof(T) == 4) {
+            double y = double(xv) * inv_d;
+            if (has_w) y *= double(wv);
+            return float(y);
+        } else {
+            float y = to_f32<T>(xv) * inv_f;
+            if (has_w) y *= to_f32<T>(wv);
+            return from_f32<T>(y);
+        }
+    } else {
+        float y = round_to<T>(to_f32<T>(xv) * inv_f);
+        if (has_w) y = round_to<T>(y * to_f32<T>(wv));
+        return from_f32<T>(y);
+    }
+}
+
+// KV = 16-byte vectors per lane (row held in registers).  nvec = H / N vectors per row.
+template <typename T, int MODE, int KV>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+rmsnorm_fwd_warp_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__ y,
+                        float* __restrict__ rstd, int64_t rows, int64_t H, int nvec, double eps) {
+    constexpr int N = Vec16<T>::N;
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = int64_t(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5);
+    const int64_t nwarps = int64_t(gridDim.x) * kWarpsPerBlock;
+    for (int64_t row = warp; row < rows; row += nwarps) {
+        const T* xr = x + row * H;
+        Vec16<T> v[KV];
+#pragma unroll
+        for (int k = 0; k < KV; ++k) {
+            const int i = lane + 32 * k;
+            if (i < nvec) v[k] = ld16_stream(xr + int64_t(i) * N);
+        }
+        double acc = 0.0;
+#pragma unroll
+        for (int k = 0; k < KV; ++k) {
+            const int i = lane + 32 * k;
+            if (i < nvec) {
+                if constexpr (sizeof(T) == 4) {
+#pragma unroll
+                    for (int e = 0; e < N; ++e) {
+                        const float f = v[k].v[e];
+                        acc += (MODE == PARAS_ROUND_ONCE) ? double(f) * double(f) : double(f * f);
+                    }
+                } else {
+                    float part = 0.f;
+#pragma unroll
+                    for (int e = 0; e < N; ++e)
+                        part += RowMath<T>::template sq<MODE>(to_f32<T>(v[k].v[e]));
+                    acc += double(part);
+                }
+            }
+        }
+        acc = warp_sum(acc);
+        float inv_f;
+        double inv_d;
+        row_scalars<T, MODE>(acc, H, eps, &inv_f, &inv_d);
+        if (rstd && lane == 0) rstd[row] = inv_f;
+        T* yr = y + row * H;
+#pragma unroll
+        for (int k = 0; k < KV; ++k) {
+            const int i = lane + 32 * k;
+            if (i < nvec) {
+                Vec16<T> wv;
+                if (w) wv = ld16(w + int64_t(i) * N);
+                Vec16<T> o;
+#pragma unroll
+                for (int e = 0; e < N; ++e)
+                    o.v[e] = finish<T, MODE>(v[k].v[e], inv_f, inv_d, w != nullptr,
+                                             w ? wv.v[e] : v[k].v[e]);
+                st16_stream(yr + int64_t(i) * N, o);
+            }
+        }
+    }
+}
+
+// Any H, any alignment: one CTA per row, two passes (the second read is an L2 hit).
+template <typename T, int MODE>
+__global__ void __launch_bounds__(256)
+rmsnorm_fwd_block_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__ y,
+                         float* __restrict__ rstd, int64_t rows, int64_t H, double eps) {
+    __shared__ double red[8];
+    __shared__ double total;
+    for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+        const T* xr = x + row * H;
+        double acc = 0.0;
+        for (int64_t j = threadIdx.x; j < H; j += blockDim.x) {
+            const float f = to_f32<T>(xr[j]);
+            if constexpr (sizeof(T) == 4 && MODE == PARAS_ROUND_ONCE)
+                acc += double(f) * double(f);
+            else
+                acc += double(RowMath<T>::template sq<MODE>(f));
+        }
+        acc = warp_sum(acc);
+        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            double t = 0.0;
+            for (int i = 0; i < int(blockDim.x >> 5); ++i) t += red[i];
+            total = t;
+        }
+        __syncthreads();
+        float inv_f;
+        double inv_d;
+        row_scalars<T, MODE>(total, H, eps, &inv_f, &inv_d);
+        if (rstd && threadIdx.x == 0) rstd[row] = inv_f;
+        T* yr = y + row * H;
+        for (int64_t j = threadIdx.x; j < H; j += blockDim.x)
+            yr[j] = finish<T, MODE>(xr[j], inv_f, inv_d, w != nullptr, w ? w[j] : xr[j]);
+        __syncthreads();
+    }
+}
+
+// grad_x (fused_ops.cpp:111-135): one warp per row.
+template <typename T>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+rmsnorm_bwd_dx_kernel(const T* __restrict__ go, const T* __restrict__ x, const T* __restrict__ w,
+                      const float* __restrict__ rstd, T* __restrict__ gx, int64_t rows, int64_t H) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = int64_t(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5);
+    const int64_t nwarps = int64_t(gridDim.x) * kWarpsPerBlock;
+    for (int64_t row = warp; row < rows; row += nwarps) {
+        const T* gr = go + row * H;
+        const T* xr = x + row * H;
+        double dot = 0.0;
+        for (int64_t j = lane; j < H; j += 32)
+            dot += double(to_f32<T>(gr[j])) * double(to_f32<T>(w[j])) * double(to_f32<T>(xr[j]));
+        dot = warp_sum(dot);
+        const double rr = double(rstd[row]);
+        const double coef = rr * rr * rr / double(H);
+        T* out = gx + row * H;
+        for (int64_t j = lane; j < H; j += 32) {
+            const double gj = to_f32<T>(gr[j]), wj = to_f32<T>(w[j]), xj = to_f32<T>(xr[j]);
+            out[j] = from_f32<T>(float(gj * wj * rr - coef * xj * dot));
+        }
+    }
+}
+
+// grad_weight[j] = sum_r go[r,j]*x[r,j]*rstd[r] (fused_ops.cpp:137-155): a 32x32 thread
+// tile per 32 columns, rows strided over the tile's second dimension.
+template <typename T>
+__global__ void __launch_bounds__(1024)
+rmsnorm_bwd_dw_kernel(const T* __restrict__ go, const T* __restrict__ x,
+                      const float* __restrict__ rstd, T* __restrict__ gw, int64_t rows, int64_t H) {
+    __shared__ double part[32][33];
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const int64_t col = int64_t(blockIdx.x) * 32 + tx;
+    double acc = 0.0;
+    if (col < H)
+        for (int64_t r = ty; r < rows; r += 32)
+            acc += double(to_f32<T>(go[r * H + col])) * double(to_f32<T>(x[r * H + col])) *
+                   double(rstd[r]);
+    part[ty][tx] = acc;
+    __syncthreads();
+    if (ty == 0 && col < H) {
+        double t = 0.0;
+        for (int i = 0; i < 32; ++i) t += part[i][tx];
+        gw[col] = from_f32<T>(float(t));
+    }
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+double round_scalar_to(double v, int dtype) {
+    // what wrapping a scalar into a 0-dim tensor of the output dtype does (double->float->T)
+    float f = float(v);
+    if (dtype == PARAS_BF16) return double(__bfloat162float(__float2bfloat16_rn(f)));
+    if (dtype == PARAS_F16) return double(__half2float(__float2half_rn(f)));
+    return double(f);
+}
+
+template <typename T, int MODE>
+int launch_fwd(Gpu* g, const void* x, const void* w, void* y, float* rstd, int64_t rows,
+               int64_t H, double eps, cudaStream_t s) {
+    constexpr int N = Vec16<T>::N;
+    const T* px = static_cast<const T*>(x);
+    const T* pw = static_cast<const T*>(w);
+    T* py = static_cast<T*>(y);
+    const bool vec_ok = (H % N == 0) && aligned16(x) && aligned16(y) && (!w || aligned16(w));
+    const int64_t nvec = H / N;
+    const int sms = g->sm_count > 0 ? g->sm_count : 148;
+    if (vec_ok && nvec <= 32 * 16) {
+        int64_t blocks = (rows + kWarpsPerBlock - 1) / kWarpsPerBlock;
+        const int64_t cap = int64_t(sms) * 16;
+        if (blocks > cap) blocks = cap;
+        const int kv = int((nvec + 31) / 32);
+#define PB_RMS_LAUNCH(KV)                                                                   \
+    rmsnorm_fwd_warp_kernel<T, MODE, KV><<<int(blocks), kWarpsPerBlock * 32, 0, s>>>(        \
+        px, pw, py, rstd, rows, H, int(nvec), eps)
+        if (kv <= 1) PB_RMS_LAUNCH(1);
+        else if (kv <= 2) PB_RMS_LAUNCH(2);
+        else if (kv <= 4) PB_RMS_LAUNCH(4);
+        else if (kv <= 8) PB_RMS_LAUNCH(8);
+        else PB_RMS_LAUNCH(16);
+#undef PB_RMS_LAUNCH
+        PB_LAUNCH_CHECK("rmsnorm_fwd_warp_kernel");
+        return PARAS_OK;
+    }
+    int64_t blocks = rows;
+    const int64_t cap = int64_t(sms) * 8;
+    if (blocks > cap) blocks = cap;
+    rmsnorm_fwd_block_kernel<T, MODE><<<int(blocks), 256, 0, s>>>(px, pw, py, rstd, rows, H, eps);
+    PB_LAUNCH_CHECK("rmsnorm_fwd_block_kernel");
+    return PARAS_OK;
+}
+
+}  // namespace
+}  // namespace pb
+
+using pb::fail;
+using pb::Gpu;
+
+extern "C" {
+
+int paras_b200_rmsnorm_fwd(int gpu, const void* x, const void* weight, void* y, float* rstd,
+                           int64_t rows, int64_t H, double eps, int dtype, int mode,
+                           void* stream) {
+    if (rows < 0 || H < 0) return fail(PARAS_E_INVALID, "paras rms_norm: negative size");
+    if (dtype != PARAS_F32 && dtype != PARAS_BF16 && dtype != PARAS_F16)
+        return fail(PARAS_E_UNSUPPORTED, "paras rms_norm: unsupported dtype %d", dtype);
+    if (mode != PARAS_ROUND_ONCE && mode != PARAS_ROUND_PER_OP)
+        return fail(PARAS_E_INVALID, "paras rms_norm: bad rounding mode %d", mode);
+    int st;
+    Gpu* g = pb::use_gpu(gpu, &st);
+    if (!g) return st;
+    if (rows == 0 || H == 0) return PARAS_OK;
+    if (!x || !y) return fail(PARAS_E_INVALID, "paras rms_norm: null pointer");
+    cudaStream_t s = pb::pick_stream(g, stream);
+    const double eps_used = mode == PARAS_ROUND_PER_OP ? pb::round_scalar_to(eps, dtype) : eps;
+#define PB_RMS(T)                                                                            \
+    (mode == PARAS_ROUND_ONCE                                                                \
+         ? pb::launch_fwd<T, PARAS_ROUND_ONCE>(g, x, weight, y, rstd, rows, H, eps_used, s)  \
+         : pb::launch_fwd<T, PARAS_ROUND_PER_OP>(g, x, weight, y, rstd, rows, H, eps_used, s))
+    switch (dtype) {
+        case PARAS_F32: return PB_RMS(float);
+        case PARAS_BF16: return PB_RMS(__nv_bfloat16);
+        default: return PB_RMS(__half);
+    }
+#undef PB_RMS
+}
+
+int paras_b200_rmsnorm_bwd(int gpu, const void* grad_out, const void* x, const void* weight,
+                           const float* rstd, void* grad_x, void* grad_weight, int64_t rows,
+                           int64_t H, int dtype, void* stream) {
+    if (rows < 0 || H < 0) return fail(PARAS_E_INVALID, "paras rms_norm_backward: negative size");
+    if (dtype != PARAS_F32 && dtype != PARAS_BF16 && dtype != PARAS_F16)
+        return fail(PARAS_E_UNSUPPORTED, "paras rms_norm_backward: unsupported dtype %d", dtype);
+    int st;
+    Gpu* g = pb::use_gpu(gpu, &st);
+    if (!g) return st;
+    if (H == 0) return PARAS_OK;
+    if (!grad_weight) return fail(PARAS_E_INVALID, "paras rms_norm_backward: null pointer");
+    cudaStream_t s = pb::pick_stream(g, stream);
+    if (rows == 0) {
+        PB_CUDA(cudaMemsetAsync(grad_weight, 0, size_t(H) * pb::dtype_size(dtype), s));
+        return PARAS_OK;
+    }
+    if (!grad_out || !x || !weight || !rstd || !grad_x)
+        return fail(PARAS_E_INVALID, "paras rms_norm_backward: null pointer");
+    const int sms = g->sm_count > 0 ? g->sm_count : 148;
+    int64_t blocks = (rows + pb::kWarpsPerBlock - 1) / pb::kWarpsPerBlock;
+    if (blocks > int64_t(sms) * 16) blocks = int64_t(sms) * 16;
+    const int dwblocks = int((H + 31) / 32);
+#define PB_BWD(T)                                                                             \
+    do {                                                                                      \
+        pb::rmsnorm_bwd_dx_kernel<T><<<int(blocks), pb::kWarpsPerBlock * 32, 0, s>>>(          \
+            static_cast<const T*>(grad_out), static_cast<const T*>(x),                        \
+            static_cast<const T*>(weight), rstd, static_cast<T*>(grad_x), rows, H);           \
+        pb::rmsnorm_bwd_dw_kernel<T><<<dwblocks, 1024, 0, s>>>(                               \
+            static_cast<const T*>(grad_out), static_cast<const T*>(x), rstd,                  \
+            static_cast<T*>(grad_weight), rows, H);                                           \
+    } while (0)
+    switch (dtype) {
+        case PARAS_F32: PB_BWD(float); break;
+        case PARAS_BF16: PB_BWD(__nv_bfloat16); break;
+        default: PB_BWD(__half); break;
+    }
+#undef PB_BWD
+    PB_LAUNCH_CHECK("rmsnorm_bwd kernels");
+    return PARAS_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,52 @@
+// Internal interfaces shared by the SDPA kernels and their dispatcher.
+#pragma once
+
+#include "common.cuh"
+
+namespace pb {
+
+// Split-KV partial results: o_part[split][row][D] (unnormalised, relative to m),
+// ml_part[split][row] = {running max of scaled scores, running sum of exp}.
+// row = (b*Hq + h)*Lq + qi.
+struct SplitWorkspace {
+    float* o_part = nullptr;
+    float2* ml_part = nullptr;
+    int splits = 1;
+};
+
+inline size_t split_workspace_bytes(int64_t rows, int D, int splits) {
+    if (splits <= 1) return 0;
+    // o_part then ml_part; both 16-byte aligned as long as the base is
+    return size_t(splits) * size_t(rows) * (size_t(D) * sizeof(float) + sizeof(float2));
+}
+
+inline SplitWorkspace carve_workspace(void* base, int64_t rows, int D, int splits) {
+    SplitWorkspace w;
+    w.splits = splits;
+    if (splits > 1) {
+        w.o_part = static_cast<float*>(base);
+        w.ml_part = reinterpret_cast<float2*>(w.o_part + size_t(splits) * rows * D);
+    }
+    return w;
+}
+
+// Generic CUDA-core flash kernel: any dtype, D <= 256, masks, any strides.
+int sdpa_simt_launch(Gpu* g, const paras_sdpa_args& a, float scale, const SplitWorkspace& ws,
+                     cudaStream_t s);
+int sdpa_simt_pick_splits(const Gpu* g, const paras_sdpa_args& a);
+
+// Merges split-KV partials into out (and lse).
+int sdpa_combine_launch(Gpu* g, const paras_sdpa_args& a, const SplitWorkspace& ws,
+                        cudaStream_t s);
+
+// tcgen05/TMEM/TMA kernel: bf16/f16, D == 128, no mask tensor.
+bool sdpa_tc_supported(const Gpu* g, const paras_sdpa_args& a, const char** why);
+int sdpa_tc_launch(Gpu* g, const paras_sdpa_args& a, float scale, cudaStream_t s);
+
+// Tensor-core split-KV decode kernel: 16-bit, D == 128, short Lq, no mask tensor.
+bool sdpa_decode_supported(const Gpu* g, const paras_sdpa_args& a, const char** why);
+int sdpa_decode_pick_splits(const Gpu* g, const paras_sdpa_args& a);
+int sdpa_decode_launch(Gpu* g, const paras_sdpa_args& a, float scale, const SplitWorkspace& ws,
+                       cudaStream_t s);
+
+}  // namespace pb

@@ -1,0 +1,461 @@
+// Flash attention forward for sm_100a: tcgen05 tensor cores, TMEM accumulators, TMA-fed
+// K/V ring, warp-specialised roles.  16-bit tensors, head dim 128, causal (top-left
+// aligned, csrc/ops/attention_ops.cpp:103-116) or full attention, GQA by indexing the
+// shared kv head (never materialising the repeat_interleave of attention_ops.cpp:83-93).
+//
+// One CTA owns 256 consecutive query rows of one (batch, head) as two 128-row tiles that
+// ping-pong: while the tensor core runs tile 0's MMAs, tile 1's softmax runs on the CUDA
+// cores, and vice versa.
+//
+//   warps 0-3   softmax of query tile 0: one thread per row (TMEM lane = row)
+//   warps 4-7   softmax of query tile 1
+//   warp  8     allocates TMEM, then one lane issues every tcgen05.mma
+//   warp  9     one lane issues every TMA load
+//
+// TMEM (512 columns x 128 lanes, fp32): S0 @0, S1 @128, O0 @256, O1 @384.  The 16-bit
+// probabilities P_t overwrite the first 64 columns of S_t and feed the P*V MMA straight
+// from TMEM.  Shared memory: Q 2x32 KB, K/V ring 4x32 KB, all 128-byte swizzled as TMA
+// writes them.
+//
+// Per kv tile j and query tile t:  S_t = Q_t K_j^T  (8 MMAs, K=16 each)
+//                                  P_t = exp2(S_t*c - m_t*c), row sums l_t, running max m_t
+//                                  O_t += P_t V_j     (8 MMAs)
+// O_t is rescaled in TMEM only when a row's max grew by more than 2^8 (the stale max is
+// used consistently for P and l, so the final O/l is exact).
+//
+// Every wait is bounded (tc_prims.cuh); a wait that runs out raises the CTA's abort flag,
+// all roles fall through to the common exit, TMEM is freed and the GPU's status word is set.
+#include <cmath>
+#include <mutex>
+
+#include "sdpa_common.cuh"
+#include "tc_prims.cuh"
+
+namespace pb {
+namespace {
+
+using namespace tc;
+
+constexpr int BM = 128;            // query rows per tile (MMA M)
+constexpr int BN = 128;            // keys per tile (MMA N of QK^T, K of PV)
+constexpr int HD = 128;            // head dim
+constexpr int kTilesPerCta = 2;
+constexpr int kStages = 4;         // K/V ring slots
+constexpr int kChunkBytes = 64 * 2 * 128;    // 64 elements x 128 rows
+constexpr int kTileBytes = 2 * kChunkBytes;  // 128 x 128 x 2 B
+constexpr int kSoftmaxWarps = 8;
+constexpr int kMmaWarp = 8;
+constexpr int kLoadWarp = 9;
+constexpr int kThreads = 320;
+constexpr int kTmemCols = 512;
+constexpr int kColS = 0, kColO = 256;  // + 128 * tile
+constexpr float kRescaleThreshold = 8.0f;    // log2 units
+
+constexpr int kSmemQ = 0;
+constexpr int kSmemKV = kTilesPerCta * kTileBytes;
+constexpr int kSmemBars = kSmemKV + kStages * kTileBytes;
+// barrier indices
+constexpr int kBarQFull = 0;                      // [2]
+constexpr int kBarKVFull = 2;                     // [kStages]
+constexpr int kBarKVEmpty = kBarKVFull + kStages; // [kStages]
+constexpr int kBarSFull = kBarKVEmpty + kStages;  // [2]
+constexpr int kBarPFull = kBarSFull + 2;          // [2]
+constexpr int kBarOFull = kBarPFull + 2;          // [2]
+constexpr int kNumBars = kBarOFull + 2;
+constexpr int kSmemMisc = kSmemBars + kNumBars * 8;   // tmem base word, abort flag
+constexpr int kSmemTotal = kSmemMisc + 16;
+constexpr int kSmemLaunch = kSmemTotal + 1024;        // slack to align the base to 1024 B
+
+struct TcParams {
+    void* out;
+    float* lse;
+    int B, Hq, Hkv, Lq, Lk;
+    int64_t os[3];
+    int causal;
+    float scale;
+    float scale_log2;
+    int* status;
+};
+
+__device__ __forceinline__ int kv_tiles_for(const TcParams& p, int start) {
+    if (start >= p.Lq) return 0;
+    int last = p.Lk;
+    if (p.causal) last = min(last, min(p.Lq, start + BM));  // keys 0..row
+    return (last + BN - 1) / BN;
+}
+
+template <bool BF16>
+__global__ void __launch_bounds__(kThreads, 1)
+sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+               const __grid_constant__ CUtensorMap map_v, const TcParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    auto bar = [&](int i) { return smem_base + kSmemBars + 8u * i; };
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + kSmemMisc);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + kSmemMisc + 4);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int qblk = int(gridDim.x) - 1 - int(blockIdx.x);  // longest (latest) rows first
+    const int h = blockIdx.y, b = blockIdx.z;
+    const int hk = h / (p.Hq / p.Hkv);
+    const int q0 = qblk * (kTilesPerCta * BM);
+    int start[2], ntile[2];
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+        start[t] = q0 + t * BM;
+        ntile[t] = kv_tiles_for(p, start[t]);
+    }
+    const int n = max(ntile[0], ntile[1]);
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < kNumBars; ++i) {
+            const bool pfull = (i >= kBarPFull && i < kBarPFull + 2);
+            mbar_init(bar(i), pfull ? 4u : 1u);
+        }
+        *abort_flag = 0;
+        mbar_fence_init();
+        fence_proxy_async_smem();
+    }
+    if (warp == kMmaWarp) {
+        tmem_alloc(smem_base + kSmemMisc, kTmemCols);
+        tmem_relinquish();
+    }
+    if (warp == kLoadWarp && lane == 0) {
+        tma_prefetch_desc(&map_q);
+        tma_prefetch_desc(&map_k);
+        tma_prefetch_desc(&map_v);
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == kLoadWarp) {
+        // ------------------------------ TMA producer ------------------------------
+        if (lane == 0) {
+#pragma unroll
+            for (int t = 0; t < 2; ++t) {
+                if (ntile[t] > 0) {
+                    mbar_arrive_expect_tx(bar(kBarQFull + t), kTileBytes);
+                    const uint32_t dst = smem_base + kSmemQ + t * kTileBytes;
+                    tma_load_4d(dst, &map_q, bar(kBarQFull + t), 0, start[t], h, b);
+                    tma_load_4d(dst + kChunkBytes, &map_q, bar(kBarQFull + t), 64, start[t], h, b);
+                }
+            }
+            bool ok = true;
+            for (int item = 0; ok && item < 2 * n; ++item) {  // K0 V0 K1 V1 ...
+                const int slot = item % kStages;
+                const uint32_t ph = (item / kStages) & 1;
+                ok = mbar_wait(bar(kBarKVEmpty + slot), ph ^ 1u, abort_flag);
+                if (!ok) break;
+                const int j = item >> 1;
+                const CUtensorMap* map = (item & 1) ? &map_v : &map_k;
+                mbar_arrive_expect_tx(bar(kBarKVFull + slot), kTileBytes);
+                const uint32_t dst = smem_base + kSmemKV + slot * kTileBytes;
+                tma_load_4d(dst, map, bar(kBarKVFull + slot), 0, j * BN, hk, b);
+                tma_load_4d(dst + kChunkBytes, map, bar(kBarKVFull + slot), 64, j * BN, hk, b);
+            }
+        }
+    } else if (warp == kMmaWarp) {
+        // ------------------------------ MMA issuer --------------------------------
+        if (lane == 0) {
+            constexpr uint32_t idesc_qk = instr_desc_f16(BF16 ? 1 : 0, BM, BN, false, false);
+            constexpr uint32_t idesc_pv = instr_desc_f16(BF16 ? 1 : 0, BM, HD, false, true);
+            auto issue_qk = [&](int t, int slot) {
+                const uint32_t qa = smem_base + kSmemQ + t * kTileBytes;
+                const uint32_t ka = smem_base + kSmemKV + slot * kTileBytes;
+#pragma unroll
+                for (int c = 0; c < 2; ++c)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const uint32_t off = c * kChunkBytes + i * 32;  // 16 elements = 32 B
+                        mma_ss(tmem + kColS + t * 128, smem_desc_sw128(qa + off, 16, 1024),
+                               smem_desc_sw128(ka + off, 16, 1024), idesc_qk, (c | i) ? 1u : 0u);
+                    }
+            };
+            auto issue_pv = [&](int t, int slot, bool acc) {
+                const uint32_t va = smem_base + kSmemKV + slot * kTileBytes;
+#pragma unroll
+                for (int ks = 0; ks < BN / 16; ++ks) {
+                    // 16 keys = 16 rows of 128 B inside each 64-wide half of the head dim
+                    mma_ts(tmem + kColO + t * 128, tmem + kColS + t * 128 + ks * 8,
+                           smem_desc_sw128(va + ks * 16 * 128, kChunkBytes, 1024), idesc_pv,
+                           (acc || ks) ? 1u : 0u);
+                }
+            };
+            bool ok = n > 0;
+            if (ok) ok = mbar_wait(bar(kBarKVFull + 0), 0, abort_flag);  // K0
+#pragma unroll
+            for (int t = 0; t < 2; ++t) {
+                if (ok && ntile[t] > 0) {
+                    ok = mbar_wait(bar(kBarQFull + t), 0, abort_flag);
+                    if (ok) {
+                        tc_fence_after_sync();
+                        issue_qk(t, 0);
+                        tc_commit(bar(kBarSFull + t));
+                    }
+                }
+            }
+            if (ok) tc_commit(bar(kBarKVEmpty + 0));
+            for (int j = 0; ok && j < n; ++j) {
+                const int item_v = 2 * j + 1, item_k = 2 * j + 2;
+                const int slot_v = item_v % kStages, slot_k = item_k % kStages;
+                ok = mbar_wait(bar(kBarKVFull + slot_v), (item_v / kStages) & 1, abort_flag);
+                if (ok && j + 1 < n)
+                    ok = mbar_wait(bar(kBarKVFull + slot_k), (item_k / kStages) & 1, abort_flag);
+                if (!ok) break;
+#pragma unroll
+                for (int t = 0; t < 2; ++t) {
+                    if (ok && j < ntile[t]) {
+                        ok = mbar_wait(bar(kBarPFull + t), j & 1, abort_flag);
+                        if (!ok) break;
+                        tc_fence_after_sync();
+                        issue_pv(t, slot_v, j > 0);
+                        if (j + 1 < ntile[t]) {
+                            issue_qk(t, slot_k);
+                            tc_commit(bar(kBarSFull + t));
+                        } else {
+                            tc_commit(bar(kBarOFull + t));
+                        }
+                    }
+                }
+                if (!ok) break;
+                tc_commit(bar(kBarKVEmpty + slot_v));
+                if (j + 1 < n) tc_commit(bar(kBarKVEmpty + slot_k));
+            }
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------ softmax + epilogue --------------------------
+        const int t = warp >> 2;
+        const int wq = warp & 3;
+        const uint32_t lane_base = uint32_t(wq * 32) << 16;
+        const uint32_t s_addr = tmem + lane_base + kColS + t * 128;
+        const uint32_t o_addr = tmem + lane_base + kColO + t * 128;
+        const int row_q = start[t] + wq * 32 + lane;
+        const float c2 = p.scale_log2;
+        float m = -INFINITY, l = 0.f;
+        bool ok = true;
+        for (int j = 0; j < ntile[t]; ++j) {
+            ok = mbar_wait(bar(kBarSFull + t), j & 1, abort_flag);
+            if (!ok) break;
+            tc_fence_after_sync();
+            uint32_t s[BN];
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+                tmem_ld32(s_addr + 32 * c, reinterpret_cast<uint32_t(&)[32]>(s[32 * c]));
+            tmem_wait_ld();
+#pragma unroll
+            for (int c = 0; c < 4; ++c) tmem_ld_fence32(reinterpret_cast<uint32_t(&)[32]>(s[32 * c]));
+
+            const int col0 = j * BN;
+            const bool need_mask = (p.causal && col0 + BN - 1 > start[t]) || (col0 + BN > p.Lk);
+            if (need_mask) {
+                const int limit = (p.causal ? min(row_q, p.Lk - 1) : p.Lk - 1) - col0;
+#pragma unroll
+                for (int i = 0; i < BN; ++i)
+                    if (i > limit) s[i] = 0xff800000u;  // -inf
+            }
+            float mx = __uint_as_float(s[0]);
+#pragma unroll
+            for (int i = 1; i < BN; ++i) mx = fmaxf(mx, __uint_as_float(s[i]));
+
+            float alpha = 1.f;
+            bool grew = false;
+            if (j == 0) {
+                m = mx;
+            } else {
+                const float m_new = fmaxf(m, mx);
+                if ((m_new - m) * c2 > kRescaleThreshold) {
+                    alpha = ex2_approx((m - m_new) * c2);
+                    l *= alpha;
+                    m = m_new;
+                    grew = true;
+                }
+            }
+            if (j > 0 && __any_sync(0xffffffffu, grew)) {
+                // PV_t(j-1) has completed (S_t(j) was committed after it) and PV_t(j) waits
+                // for this tile's P barrier, so O_t is quiescent here.
+#pragma unroll 1
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t o[32];
+                    tmem_ld32(o_addr + 32 * c, o);
+                    tmem_wait_ld();
+                    tmem_ld_fence32(o);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                    tmem_st32(o_addr + 32 * c, o);
+                }
+            }
+            const float neg_m = -m * c2;
+            float lsum0 = 0.f, lsum1 = 0.f;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                uint32_t pk[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const int e = 32 * c + 2 * i;
+                    const float p0 = ex2_approx(fmaf(__uint_as_float(s[e]), c2, neg_m));
+                    const float p1 = ex2_approx(fmaf(__uint_as_float(s[e + 1]), c2, neg_m));
+                    lsum0 += p0;
+                    lsum1 += p1;
+                    pk[i] = pack16<BF16>(p0, p1);
+                }
+                tmem_st16(s_addr + 16 * c, pk);  // P_t over the first 64 columns of S_t
+            }
+            l += lsum0 + lsum1;
+            tmem_wait_st();
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(kBarPFull + t));
+        }
+        if (ok && ntile[t] > 0) ok = mbar_wait(bar(kBarOFull + t), 0, abort_flag);
+        if (ok && ntile[t] > 0) {
+            tc_fence_after_sync();
+            const float inv = 1.0f / l;
+            const bool live = row_q < p.Lq;
+            uint16_t* orow = static_cast<uint16_t*>(p.out) + int64_t(b) * p.os[0] +
+                             int64_t(h) * p.os[1] + int64_t(live ? row_q : 0) * p.os[2];
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                uint32_t o[32];
+                tmem_ld32(o_addr + 32 * c, o);
+                tmem_wait_ld();
+                tmem_ld_fence32(o);
+                if (live) {
+#pragma unroll
+                    for (int v = 0; v < 4; ++v) {
+                        uint4 w;
+                        w.x = pack16<BF16>(__uint_as_float(o[8 * v + 0]) * inv, __uint_as_float(o[8 * v + 1]) * inv);
+                        w.y = pack16<BF16>(__uint_as_float(o[8 * v + 2]) * inv, __uint_as_float(o[8 * v + 3]) * inv);
+                        w.z = pack16<BF16>(__uint_as_float(o[8 * v + 4]) * inv, __uint_as_float(o[8 * v + 5]) * inv);
+                        w.w = pack16<BF16>(__uint_as_float(o[8 * v + 6]) * inv, __uint_as_float(o[8 * v + 7]) * inv);
+                        *reinterpret_cast<uint4*>(orow + 32 * c + 8 * v) = w;
+                    }
+                }
+            }
+            if (p.lse && live)
+                p.lse[(int64_t(b) * p.Hq + h) * p.Lq + row_q] = m * p.scale + logf(l);
+        }
+    }
+
+    // ------------------------------ common exit ------------------------------------
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == kMmaWarp) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem, kTmemCols);
+    }
+    if (threadIdx.x == 0 && *abort_flag) {
+        *p.status = 1;
+        __threadfence_system();
+    }
+}
+
+// ---- host side -------------------------------------------------------------------------
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                              CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                              CUtensorMapFloatOOBfill);
+
+EncodeFn encode_fn() {
+    static EncodeFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) ==
+                cudaSuccess && qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeFn>(sym);
+        else
+            cudaGetLastError();
+    });
+    return fn;
+}
+
+// [B, H, L, 128] tensor with element strides st = {B, H, L}; box = 64 x 128 rows, 128-byte
+// swizzle, out-of-range rows read as zero.
+int make_map(CUtensorMap* map, const void* base, int dtype, int B, int H, int L,
+             const int64_t* st) {
+    EncodeFn fn = encode_fn();
+    if (!fn) return fail(PARAS_E_CUDA, "paras sdpa: cuTensorMapEncodeTiled is unavailable");
+    const cuuint64_t dims[4] = {cuuint64_t(HD), cuuint64_t(L), cuuint64_t(H), cuuint64_t(B)};
+    // a stride of a size-1 dim is never used for addressing; keep it a legal multiple of 16
+    const int64_t sl = L > 1 ? st[2] : HD;
+    const int64_t sh = H > 1 ? st[1] : sl * L;
+    const int64_t sb = B > 1 ? st[0] : sh * H;
+    const cuuint64_t strides[3] = {cuuint64_t(sl) * 2, cuuint64_t(sh) * 2, cuuint64_t(sb) * 2};
+    const cuuint32_t box[4] = {64, cuuint32_t(BN), 1, 1};
+    const cuuint32_t estr[4] = {1, 1, 1, 1};
+    const CUresult r = fn(map, dtype == PARAS_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                  : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                          4, const_cast<void*>(base), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail(PARAS_E_CUDA, "paras sdpa: cuTensorMapEncodeTiled failed with code %d", int(r));
+    return PARAS_OK;
+}
+
+bool strides_ok(const void* base, const int64_t* st, int B, int H, int L) {
+    if (reinterpret_cast<uintptr_t>(base) & 15u) return false;
+    if (L > 1 && (st[2] < HD || (st[2] * 2) % 16)) return false;
+    if (H > 1 && (st[1] <= 0 || (st[1] * 2) % 16)) return false;
+    if (B > 1 && (st[0] <= 0 || (st[0] * 2) % 16)) return false;
+    return true;
+}
+
+}  // namespace
+
+bool sdpa_tc_supported(const Gpu* g, const paras_sdpa_args& a, const char** why) {
+    *why = "";
+    if (g->cc_major != 10) { *why = "GPU is not compute capability 10.x"; return false; }
+    if (a.dtype != PARAS_BF16 && a.dtype != PARAS_F16) { *why = "dtype is not 16-bit"; return false; }
+    if (a.D != HD) { *why = "head dim is not 128"; return false; }
+    if (a.mask) { *why = "explicit attn_mask"; return false; }
+    if (a.Lq < 1 || a.Lk < 1) { *why = "empty sequence"; return false; }
+    if (!(a.scale > 0.0) || !std::isfinite(a.scale)) { *why = "scale is not positive"; return false; }
+    if (a.Hq > 65535 || a.B > 65535) { *why = "batch or heads exceed the grid limit"; return false; }
+    if (g->smem_optin < size_t(kSmemLaunch)) { *why = "not enough shared memory"; return false; }
+    if (!strides_ok(a.q, a.q_strides, a.B, a.Hq, a.Lq) || !strides_ok(a.k, a.k_strides, a.B, a.Hkv, a.Lk) ||
+        !strides_ok(a.v, a.v_strides, a.B, a.Hkv, a.Lk) || !strides_ok(a.out, a.o_strides, a.B, a.Hq, a.Lq)) {
+        *why = "pointers or strides are not 16-byte aligned";
+        return false;
+    }
+    return true;
+}
+
+int sdpa_tc_launch(Gpu* g, const paras_sdpa_args& a, float scale, cudaStream_t s) {
+    int st = check_status_word(g);
+    if (st != PARAS_OK) return st;
+    CUtensorMap mq, mk, mv;
+    if ((st = make_map(&mq, a.q, a.dtype, a.B, a.Hq, a.Lq, a.q_strides)) != PARAS_OK) return st;
+    if ((st = make_map(&mk, a.k, a.dtype, a.B, a.Hkv, a.Lk, a.k_strides)) != PARAS_OK) return st;
+    if ((st = make_map(&mv, a.v, a.dtype, a.B, a.Hkv, a.Lk, a.v_strides)) != PARAS_OK) return st;
+    TcParams p{};
+    p.out = a.out;
+    p.lse = a.lse;
+    p.B = a.B; p.Hq = a.Hq; p.Hkv = a.Hkv; p.Lq = a.Lq; p.Lk = a.Lk;
+    for (int i = 0; i < 3; ++i) p.os[i] = a.o_strides[i];
+    p.causal = a.causal;
+    p.scale = scale;
+    p.scale_log2 = scale * 1.4426950408889634f;
+    p.status = g->status_dev;
+    dim3 grid((a.Lq + kTilesPerCta * BM - 1) / (kTilesPerCta * BM), a.Hq, a.B);
+    static std::once_flag attr_once[2];
+    if (a.dtype == PARAS_BF16) {
+        PB_CUDA(cudaFuncSetAttribute(sdpa_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     kSmemLaunch));
+        sdpa_tc_kernel<true><<<grid, kThreads, kSmemLaunch, s>>>(mq, mk, mv, p);
+    } else {
+        PB_CUDA(cudaFuncSetAttribute(sdpa_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     kSmemLaunch));
+        sdpa_tc_kernel<false><<<grid, kThreads, kSmemLaunch, s>>>(mq, mk, mv, p);
+    }
+    (void)attr_once;
+    PB_LAUNCH_CHECK("sdpa_tc_kernel");
+    return PARAS_OK;
+}
+
+}  // namespace pb

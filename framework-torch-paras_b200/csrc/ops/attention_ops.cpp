@@ -1,0 +1,149 @@
+// scaled_dot_product_attention on `paras:N`: one fused flash-attention launch through the
+// C ABI instead of the reference's composition.
+//
+// Reference being replaced: sdpa_math, csrc/ops/attention_ops.cpp:71-136, registered as
+// aten::_scaled_dot_product_attention_math (140-142) -- repeat_interleave + matmul + mul +
+// ones/tril/logical_not/masked_fill + softmax + matmul, each a full pass over a
+// [B,H,Lq,Lk] score tensor.  Same argument checks and error behaviour (RuntimeError):
+// rank >= 3, is_causal excludes attn_mask, query heads must be a multiple of kv heads with
+// enable_gqa, default scale 1/sqrt(E), causal mask top-left aligned.
+//
+// Both the math op and the top-level aten::scaled_dot_product_attention are registered for
+// PrivateUse1 (the reference suggests the second at attention_ops.cpp:144-150); the
+// top-level registration keeps PyTorch from pre-converting a bool mask into an additive one.
+// Dropout is not part of the fused path and raises.
+#include <torch/library.h>
+
+#include <cmath>
+#include <cstdlib>
+
+#include "core/device_runtime.h"
+
+namespace paras {
+namespace {
+
+using at::Tensor;
+
+// (..., H, L, E) -> [B, H, L, E] with a unit stride on E; 3-D inputs are (B, L, E) with one head.
+Tensor as_bhle(const Tensor& t) {
+    Tensor r = t;
+    if (r.dim() == 3) r = r.unsqueeze(1);
+    else if (r.dim() > 4) r = r.reshape({-1, r.size(-3), r.size(-2), r.size(-1)});
+    if (r.size(-1) > 1 && r.stride(-1) != 1) r = r.contiguous();
+    return r;
+}
+
+bool ref_scale_rounding() {
+    static const bool on = [] {
+        const char* e = std::getenv("PARAS_SDPA_TRUE_SCALE");
+        return !(e && std::atoi(e) != 0);
+    }();
+    return on;
+}
+
+Tensor sdpa_forward(const Tensor& query, const Tensor& key, const Tensor& value,
+                    const std::optional<Tensor>& attn_mask, double dropout_p, bool is_causal,
+                    std::optional<double> scale, bool enable_gqa) {
+    TORCH_CHECK(query.dim() >= 3 && key.dim() >= 3 && value.dim() >= 3,
+                "paras sdpa: query/key/value must be at least 3-D (..., seq, head_dim)");
+    const bool has_mask = attn_mask.has_value() && attn_mask->defined();
+    TORCH_CHECK(!(is_causal && has_mask),
+                "paras sdpa: is_causal and attn_mask are mutually exclusive");
+    TORCH_CHECK(dropout_p == 0.0,
+                "paras sdpa: dropout_p > 0 is not supported by the fused B200 attention kernel");
+    TORCH_CHECK(query.scalar_type() == key.scalar_type() && query.scalar_type() == value.scalar_type(),
+                "paras sdpa: query, key and value must have the same dtype");
+    const int dt = dtype_code(query.scalar_type());
+    TORCH_CHECK(dt >= 0, "paras sdpa: unsupported dtype ", query.scalar_type(),
+                " (float32, bfloat16 and float16 are supported)");
+    TORCH_CHECK(key.device() == query.device() && value.device() == query.device(),
+                "paras sdpa: query, key and value must be on the same device");
+    Runtime& rt = Runtime::get();
+    const int gpu = rt.gpu_of(query);
+
+    Tensor q = as_bhle(query), k = as_bhle(key), v = as_bhle(value);
+    const int64_t B = q.size(0), Hq = q.size(1), Lq = q.size(2), E = q.size(3);
+    const int64_t Hkv = k.size(1), Lk = k.size(2);
+    TORCH_CHECK(k.size(0) == B && v.size(0) == B, "paras sdpa: batch dimensions of query, key and value differ");
+    TORCH_CHECK(k.size(3) == E, "paras sdpa: query and key head_dim differ");
+    TORCH_CHECK(v.size(1) == Hkv && v.size(2) == Lk, "paras sdpa: key and value shapes differ");
+    TORCH_CHECK(v.size(3) == E, "paras sdpa: value head_dim must equal query head_dim in the fused kernel");
+    if (Hkv != Hq) {
+        TORCH_CHECK(enable_gqa, "paras sdpa: key/value have ", Hkv, " heads but query has ", Hq,
+                    "; pass enable_gqa=True for grouped-query attention");
+        TORCH_CHECK(Hkv > 0 && Hq % Hkv == 0,
+                    "paras sdpa: query heads must be a multiple of key/value heads for enable_gqa");
+    }
+    c10::DeviceGuard guard(query.device());
+    Tensor out = at::empty({B, Hq, Lq, E}, q.options());
+
+    paras_sdpa_args a{};
+    a.q = q.data_ptr();
+    a.k = k.data_ptr();
+    a.v = v.data_ptr();
+    a.out = out.data_ptr();
+    a.dtype = dt;
+    a.B = int32_t(B); a.Hq = int32_t(Hq); a.Hkv = int32_t(Hkv);
+    a.Lq = int32_t(Lq); a.Lk = int32_t(Lk); a.D = int32_t(E);
+    for (int i = 0; i < 3; ++i) {
+        a.q_strides[i] = q.stride(i);
+        a.k_strides[i] = k.stride(i);
+        a.v_strides[i] = v.stride(i);
+        a.o_strides[i] = out.stride(i);
+    }
+    Tensor mask;  // keeps a converted mask alive until the launch is queued
+    if (has_mask) {
+        mask = *attn_mask;
+        TORCH_CHECK(mask.device() == query.device(), "paras sdpa: attn_mask must be on the query's device");
+        if (mask.scalar_type() == c10::kBool) a.mask_kind = 1;
+        else if (mask.scalar_type() == query.scalar_type()) a.mask_kind = 2;
+        else if (mask.scalar_type() == c10::kFloat) a.mask_kind = 3;
+        else { mask = mask.to(query.scalar_type()); a.mask_kind = 2; }
+        while (mask.dim() < 4) mask = mask.unsqueeze(0);
+        if (mask.dim() > 4) mask = mask.reshape({-1, mask.size(-3), mask.size(-2), mask.size(-1)});
+        mask = mask.expand({B, Hq, Lq, Lk});
+        a.mask = mask.data_ptr();
+        for (int i = 0; i < 4; ++i) a.mask_strides[i] = mask.stride(i);
+    }
+    a.causal = is_causal ? 1 : 0;
+    a.scale = scale.has_value() ? *scale : 1.0 / std::sqrt(double(E));
+    a.flags = ref_scale_rounding() ? PARAS_SDPA_REF_SCALE : 0;
+    a.gpu = gpu;
+    a.stream = nullptr;
+    PARAS_ABI(paras_b200_sdpa_fwd(&a));
+
+    if (query.dim() == 3) return out.squeeze(1);
+    if (query.dim() > 4) {
+        std::vector<int64_t> shape(query.sizes().begin(), query.sizes().end());
+        return out.reshape(shape);
+    }
+    return out;
+}
+
+// aten::_scaled_dot_product_attention_math: the second result (attention weights) is what
+// a flash kernel never forms; an empty tensor is returned in its place.
+std::tuple<Tensor, Tensor> sdpa_math(const Tensor& query, const Tensor& key, const Tensor& value,
+                                     const std::optional<Tensor>& attn_mask, double dropout_p,
+                                     bool is_causal, const std::optional<Tensor>& dropout_mask,
+                                     std::optional<double> scale, bool enable_gqa) {
+    PARAS_TRACE_OP("_scaled_dot_product_attention_math");
+    TORCH_CHECK(!(dropout_mask.has_value() && dropout_mask->defined()),
+                "paras sdpa: dropout_mask is not supported by the fused B200 attention kernel");
+    Tensor out = sdpa_forward(query, key, value, attn_mask, dropout_p, is_causal, scale, enable_gqa);
+    return {out, at::empty({0}, query.options())};
+}
+
+Tensor sdpa(const Tensor& query, const Tensor& key, const Tensor& value,
+            const std::optional<Tensor>& attn_mask, double dropout_p, bool is_causal,
+            std::optional<double> scale, bool enable_gqa) {
+    PARAS_TRACE_OP("scaled_dot_product_attention");
+    return sdpa_forward(query, key, value, attn_mask, dropout_p, is_causal, scale, enable_gqa);
+}
+
+}  // namespace
+}  // namespace paras
+
+TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
+    m.impl("aten::_scaled_dot_product_attention_math", &paras::sdpa_math);
+    m.impl("aten::scaled_dot_product_attention", &paras::sdpa);
+}

@@ -1,0 +1,223 @@
+"""ctypes bindings of the C ABI in ``include/paras_b200.h`` (``libparas_b200.so``).
+
+This is the same boundary the operator layer (``_C.so``) calls; it is exposed to Python so
+that tests, benchmarks and other runtimes can drive the kernels on raw device pointers --
+for example on ``torch.cuda`` tensors -- without the ``paras`` device in between.
+Every wrapper raises ``RuntimeError`` with the library's message on a non-zero status.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import torch
+
+_LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "libparas_b200.so")
+
+F32, BF16, F16 = 0, 1, 2
+ROUND_ONCE, ROUND_PER_OP = 0, 1
+SDPA_REF_SCALE, SDPA_FORCE_SIMT, SDPA_FORCE_TENSOR = 1, 2, 4
+
+_DT = {torch.float32: F32, torch.bfloat16: BF16, torch.float16: F16}
+
+EXPORTS = [
+    "paras_b200_abi_version", "paras_b200_backend_name", "paras_b200_last_error",
+    "paras_b200_device_count", "paras_b200_device_name", "paras_b200_device_sm_count",
+    "paras_b200_stream", "paras_b200_synchronize", "paras_b200_malloc_async",
+    "paras_b200_free_async", "paras_b200_pool_stats", "paras_b200_pool_trim",
+    "paras_b200_memcpy_h2d", "paras_b200_memcpy_d2h", "paras_b200_memcpy_d2d",
+    "paras_b200_memcpy_peer", "paras_b200_memset", "paras_b200_host_alloc", "paras_b200_host_free",
+    "paras_b200_strided_copy", "paras_b200_fill", "paras_b200_sdpa_fwd",
+    "paras_b200_sdpa_workspace_bytes", "paras_b200_sdpa_last_kernel", "paras_b200_rmsnorm_fwd",
+    "paras_b200_rmsnorm_bwd", "paras_b200_swiglu_fwd", "paras_b200_swiglu_bwd",
+    "paras_b200_rotate_half",
+]
+
+
+class SdpaArgs(C.Structure):
+    _fields_ = [
+        ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("out", C.c_void_p),
+        ("lse", C.c_void_p), ("mask", C.c_void_p), ("mask_kind", C.c_int32), ("dtype", C.c_int32),
+        ("B", C.c_int32), ("Hq", C.c_int32), ("Hkv", C.c_int32), ("Lq", C.c_int32),
+        ("Lk", C.c_int32), ("D", C.c_int32),
+        ("q_strides", C.c_int64 * 3), ("k_strides", C.c_int64 * 3), ("v_strides", C.c_int64 * 3),
+        ("o_strides", C.c_int64 * 3), ("mask_strides", C.c_int64 * 4),
+        ("causal", C.c_int32), ("flags", C.c_int32), ("scale", C.c_double),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+        ("gpu", C.c_int32), ("reserved", C.c_int32), ("stream", C.c_void_p),
+    ]
+
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        if not os.path.exists(_LIB_PATH):
+            raise RuntimeError(f"{_LIB_PATH} is missing: build it with framework-torch-paras_b200/build.py")
+        L = C.CDLL(_LIB_PATH)
+        L.paras_b200_last_error.restype = C.c_char_p
+        L.paras_b200_backend_name.restype = C.c_char_p
+        L.paras_b200_sdpa_last_kernel.restype = C.c_char_p
+        L.paras_b200_sdpa_fwd.argtypes = [C.POINTER(SdpaArgs)]
+        L.paras_b200_sdpa_workspace_bytes.argtypes = [C.POINTER(SdpaArgs), C.POINTER(C.c_size_t)]
+        L.paras_b200_rmsnorm_fwd.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                             C.c_int64, C.c_int64, C.c_double, C.c_int, C.c_int, C.c_void_p]
+        L.paras_b200_rmsnorm_bwd.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                             C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int, C.c_void_p]
+        L.paras_b200_swiglu_fwd.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64,
+                                            C.c_int, C.c_int, C.c_void_p]
+        L.paras_b200_swiglu_bwd.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                            C.c_void_p, C.c_int64, C.c_int, C.c_void_p]
+        L.paras_b200_rotate_half.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64,
+                                             C.c_int, C.c_int, C.c_void_p]
+        L.paras_b200_memcpy_h2d.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p, C.c_int]
+        L.paras_b200_memcpy_d2h.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]
+        L.paras_b200_malloc_async.argtypes = [C.c_int, C.c_size_t, C.c_void_p, C.POINTER(C.c_void_p)]
+        L.paras_b200_free_async.argtypes = [C.c_int, C.c_void_p, C.c_void_p]
+        L.paras_b200_synchronize.argtypes = [C.c_int]
+        L.paras_b200_stream.argtypes = [C.c_int, C.POINTER(C.c_void_p)]
+        L.paras_b200_host_alloc.argtypes = [C.c_size_t, C.POINTER(C.c_void_p)]
+        L.paras_b200_host_free.argtypes = [C.c_void_p]
+        _lib = L
+    return _lib
+
+
+def check(status: int) -> None:
+    if status != 0:
+        raise RuntimeError(lib().paras_b200_last_error().decode())
+
+
+def dtype_code(t: torch.Tensor) -> int:
+    try:
+        return _DT[t.dtype]
+    except KeyError:
+        raise RuntimeError(f"paras: unsupported dtype {t.dtype}") from None
+
+
+def _stream_of(t: torch.Tensor, stream) -> int:
+    if stream is not None:
+        return int(stream)
+    if t.is_cuda:
+        return int(torch.cuda.current_stream(t.device).cuda_stream)
+    return 0
+
+
+def _gpu_of(t: torch.Tensor) -> int:
+    if not t.is_cuda:
+        raise RuntimeError("paras abi: expected a CUDA tensor (raw device memory)")
+    return t.device.index if t.device.index is not None else torch.cuda.current_device()
+
+
+def sdpa_args(q, k, v, out, *, causal=False, scale=None, mask=None, lse=None, flags=0,
+              workspace=None, stream=None) -> SdpaArgs:
+    """Fills a ``paras_sdpa_args`` from [B,H,L,D] tensors (any B/H/L strides, unit D stride)."""
+    for t in (q, k, v, out):
+        if t.dim() != 4 or (t.size(-1) > 1 and t.stride(-1) != 1):
+            raise RuntimeError("paras abi: expected [B,H,L,D] tensors with a contiguous last dim")
+    a = SdpaArgs()
+    a.q, a.k, a.v, a.out = q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr()
+    a.lse = lse.data_ptr() if lse is not None else None
+    a.dtype = dtype_code(q)
+    a.B, a.Hq, a.Lq, a.D = q.shape
+    a.Hkv, a.Lk = k.shape[1], k.shape[2]
+    for i in range(3):
+        a.q_strides[i], a.k_strides[i] = q.stride(i), k.stride(i)
+        a.v_strides[i], a.o_strides[i] = v.stride(i), out.stride(i)
+    if mask is not None:
+        m = mask
+        while m.dim() < 4:
+            m = m.unsqueeze(0)
+        m = m.expand(q.shape[0], q.shape[1], q.shape[2], k.shape[2])
+        a.mask = m.data_ptr()
+        a.mask_kind = 1 if m.dtype == torch.bool else (2 if m.dtype == q.dtype else 3)
+        if a.mask_kind == 3 and m.dtype != torch.float32:
+            raise RuntimeError("paras abi: additive mask must have the tensors' dtype or float32")
+        for i in range(4):
+            a.mask_strides[i] = m.stride(i)
+        a._keep = m
+    a.causal = 1 if causal else 0
+    a.flags = flags
+    a.scale = float(scale) if scale is not None else 1.0 / (q.shape[-1] ** 0.5)
+    if workspace is not None:
+        a.workspace, a.workspace_bytes = workspace.data_ptr(), workspace.numel() * workspace.element_size()
+    a.gpu = _gpu_of(q)
+    a.stream = _stream_of(q, stream)
+    return a
+
+
+def sdpa_fwd(q, k, v, *, causal=False, scale=None, mask=None, return_lse=False, flags=0,
+             out=None, workspace=None, stream=None):
+    """softmax(q k^T * scale [+mask]) v through ``paras_b200_sdpa_fwd``."""
+    if out is None:
+        out = torch.empty(q.shape, dtype=q.dtype, device=q.device)
+    lse = torch.empty(q.shape[:3], dtype=torch.float32, device=q.device) if return_lse else None
+    a = sdpa_args(q, k, v, out, causal=causal, scale=scale, mask=mask, lse=lse, flags=flags,
+                  workspace=workspace, stream=stream)
+    check(lib().paras_b200_sdpa_fwd(C.byref(a)))
+    return (out, lse) if return_lse else out
+
+
+def sdpa_workspace_bytes(q, k, v, *, causal=False, flags=0) -> int:
+    out = torch.empty(0, dtype=q.dtype, device=q.device)
+    a = sdpa_args(q, k, v, q, causal=causal, flags=flags)
+    n = C.c_size_t(0)
+    del out
+    check(lib().paras_b200_sdpa_workspace_bytes(C.byref(a), C.byref(n)))
+    return int(n.value)
+
+
+def sdpa_last_kernel() -> str:
+    return lib().paras_b200_sdpa_last_kernel().decode()
+
+
+def rmsnorm_fwd(x, weight, eps=1e-6, *, mode=ROUND_ONCE, return_rstd=False, out=None, stream=None):
+    h = x.shape[-1]
+    rows = x.numel() // h if h else 0
+    assert x.is_contiguous() and (weight is None or weight.is_contiguous())
+    if out is None:
+        out = torch.empty_like(x)
+    rstd = torch.empty(rows, dtype=torch.float32, device=x.device) if return_rstd else None
+    check(lib().paras_b200_rmsnorm_fwd(
+        _gpu_of(x), x.data_ptr(), weight.data_ptr() if weight is not None else None, out.data_ptr(),
+        rstd.data_ptr() if rstd is not None and rows else None, rows, h, float(eps), dtype_code(x),
+        mode, _stream_of(x, stream)))
+    return (out, rstd) if return_rstd else out
+
+
+def rmsnorm_bwd(grad_out, x, weight, rstd, *, stream=None):
+    h = x.shape[-1]
+    rows = x.numel() // h if h else 0
+    gx = torch.empty_like(x)
+    gw = torch.empty_like(weight)
+    check(lib().paras_b200_rmsnorm_bwd(
+        _gpu_of(x), grad_out.data_ptr(), x.data_ptr(), weight.data_ptr(), rstd.data_ptr(),
+        gx.data_ptr(), gw.data_ptr(), rows, h, dtype_code(x), _stream_of(x, stream)))
+    return gx, gw
+
+
+def swiglu_fwd(gate, up, *, mode=ROUND_ONCE, out=None, stream=None):
+    assert gate.is_contiguous() and up.is_contiguous() and gate.shape == up.shape
+    if out is None:
+        out = torch.empty_like(gate)
+    check(lib().paras_b200_swiglu_fwd(_gpu_of(gate), gate.data_ptr(), up.data_ptr(), out.data_ptr(),
+                                      gate.numel(), dtype_code(gate), mode, _stream_of(gate, stream)))
+    return out
+
+
+def swiglu_bwd(grad_out, gate, up, *, stream=None):
+    gg, gu = torch.empty_like(gate), torch.empty_like(up)
+    check(lib().paras_b200_swiglu_bwd(_gpu_of(gate), grad_out.data_ptr(), gate.data_ptr(), up.data_ptr(),
+                                      gg.data_ptr(), gu.data_ptr(), gate.numel(), dtype_code(gate),
+                                      _stream_of(gate, stream)))
+    return gg, gu
+
+
+def rotate_half(x, *, backward=False, stream=None):
+    assert x.is_contiguous()
+    d = x.shape[-1]
+    out = torch.empty_like(x)
+    check(lib().paras_b200_rotate_half(_gpu_of(x), x.data_ptr(), out.data_ptr(), x.numel() // d if d else 0,
+                                       d, dtype_code(x), 1 if backward else 0, _stream_of(x, stream)))
+    return out

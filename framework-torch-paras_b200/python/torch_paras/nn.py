@@ -1,0 +1,62 @@
+"""Differentiable wrappers over the fused ``paras::`` operators.
+
+Same public functions as the reference's python/torch_paras/nn.py:36-89 (``rms_norm``,
+``swiglu``, ``rotate_half``): a custom-op namespace has no autograd formula of its own, so
+each forward/backward pair is tied together with a ``torch.autograd.Function``.
+"""
+import torch
+
+from . import _C  # noqa: F401  (loads the operator registrations)
+
+__all__ = ["rms_norm", "swiglu", "rotate_half"]
+
+
+class _RMSNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, eps):
+        out, rstd = torch.ops.paras.rms_norm(x, weight, eps)
+        ctx.save_for_backward(x, weight, rstd)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad):
+        x, weight, rstd = ctx.saved_tensors
+        gx, gw = torch.ops.paras.rms_norm_backward(grad.contiguous(), x, weight, rstd)
+        return gx, gw, None
+
+
+class _SwiGLU(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, gate, up):
+        ctx.save_for_backward(gate, up)
+        return torch.ops.paras.swiglu(gate, up)
+
+    @staticmethod
+    def backward(ctx, grad):
+        gate, up = ctx.saved_tensors
+        return torch.ops.paras.swiglu_backward(grad.contiguous(), gate, up)
+
+
+class _RotateHalf(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x):
+        return torch.ops.paras.rotate_half(x)
+
+    @staticmethod
+    def backward(ctx, grad):
+        return torch.ops.paras.rotate_half_backward(grad.contiguous())
+
+
+def rms_norm(input: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
+    """RMSNorm over the last dimension of ``input`` in one kernel."""
+    return _RMSNorm.apply(input, weight, eps)
+
+
+def swiglu(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """``silu(gate) * up`` in one kernel."""
+    return _SwiGLU.apply(gate, up)
+
+
+def rotate_half(x: torch.Tensor) -> torch.Tensor:
+    """RoPE helper ``cat(-x2, x1, dim=-1)`` with ``x1, x2 = x.chunk(2, dim=-1)``."""
+    return _RotateHalf.apply(x)

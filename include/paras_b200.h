@@ -1,0 +1,197 @@
+/*
+ * paras_b200.h -- C ABI of the B200 (sm_100a) hot-path library `libparas_b200.so`.
+ *
+ * This is the lower boundary that replaces the reference's compat layer for the
+ * transformer hot path.  In the reference that boundary is a C++ template over a device
+ * lambda compiled by the ParaS compiler (csrc/compat/paras_compat.h:143-202,
+ * `compat::Queue::{alloc,dealloc,copy,memset,synchronize,parallel_for<F>}`); here it is a
+ * plain C ABI over hand-written CUDA kernels: `extern "C"`, plain pointers and sizes,
+ * `int` status codes, no C++ or torch type in any signature.
+ *
+ * Conventions
+ *   - Every function returns 0 on success and a negative PARAS_E_* code on failure and
+ *     never throws; `paras_b200_last_error()` returns the calling thread's last message.
+ *     (The reference throws std::runtime_error("ptsycl: ...") from compat::fail,
+ *     csrc/compat/paras_compat.cpp:35-37; the operator layer above this ABI turns a
+ *     non-zero status back into an exception.)
+ *   - `gpu` is a CUDA ordinal 0..count-1.  (The `paras:N` device index of the operator
+ *     layer is gpu+1; index 0 is the host engine, csrc/compat/paras_compat.cpp:87-135.)
+ *   - `stream` is a `cudaStream_t` passed as `void*`; NULL means the library's own
+ *     non-blocking stream of that GPU (the reference creates one per GPU,
+ *     csrc/compat/paras_compat.cpp:230-254).
+ *   - All device pointers must belong to `gpu`.  Kernels only borrow pointers; outputs
+ *     are allocated by the caller.
+ *   - There is no CPU fallback: without a usable GPU every compute entry point fails
+ *     with PARAS_E_NODEVICE.
+ */
+#ifndef PARAS_B200_H_
+#define PARAS_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define PARAS_B200_ABI_VERSION 1
+
+enum {
+    PARAS_OK = 0,
+    PARAS_E_INVALID = -1,     /* bad argument (null pointer, bad shape, misalignment)  */
+    PARAS_E_UNSUPPORTED = -2, /* valid request this build has no kernel for            */
+    PARAS_E_CUDA = -3,        /* a CUDA runtime/driver call failed                      */
+    PARAS_E_NODEVICE = -4,    /* no usable GPU                                          */
+    PARAS_E_NOMEM = -5,       /* device or pinned allocation failed                     */
+    PARAS_E_TIMEOUT = -6      /* a bounded device-side wait ran out (status word set)   */
+};
+
+typedef enum { PARAS_F32 = 0, PARAS_BF16 = 1, PARAS_F16 = 2 } paras_dtype;
+
+/* ---- runtime: replaces compat::enumerate_devices / Queue (paras_compat.h:74-218) ---- */
+
+int paras_b200_abi_version(void);
+/* compat::backend_name() (paras_compat.h:221) */
+const char* paras_b200_backend_name(void);
+const char* paras_b200_last_error(void);
+/* Number of CUDA GPUs (0 when there is none; never an error).  enumerate_devices,
+ * csrc/compat/paras_compat.cpp:87-135. */
+int paras_b200_device_count(void);
+int paras_b200_device_name(int gpu, char* buf, size_t buflen);
+int paras_b200_device_sm_count(int gpu, int* sms);
+/* The library's stream of `gpu` (Queue::init, paras_compat.cpp:230-254). */
+int paras_b200_stream(int gpu, void** stream);
+/* Queue::synchronize (paras_compat.cpp:354-364): waits for the library stream. */
+int paras_b200_synchronize(int gpu);
+
+/* Stream-ordered device memory (replaces Queue::alloc = cudaMallocManaged,
+ * paras_compat.cpp:270-307, and core/allocator.cpp's MemoryPool): cudaMallocAsync /
+ * cudaFreeAsync on a per-GPU pool with a high release threshold. */
+int paras_b200_malloc_async(int gpu, size_t bytes, void* stream, void** ptr);
+int paras_b200_free_async(int gpu, void* ptr, void* stream);
+/* Bytes handed out and bytes reserved by the pool (MemoryPool::allocated_bytes /
+ * cached_bytes, core/allocator.h:43-44). */
+int paras_b200_pool_stats(int gpu, uint64_t* used_bytes, uint64_t* reserved_bytes);
+/* MemoryPool::clear (core/allocator.cpp): returns cached memory to the driver. */
+int paras_b200_pool_trim(int gpu);
+
+/* Queue::copy / Queue::memset (paras_compat.cpp:326-352).  Host<->device copies of
+ * pageable memory go through the library's pinned staging buffers; `blocking` != 0
+ * returns only when the bytes have landed (device->host always blocks). */
+int paras_b200_memcpy_h2d(int gpu, void* dst, const void* src, size_t bytes, void* stream,
+                          int blocking);
+int paras_b200_memcpy_d2h(int gpu, void* dst, const void* src, size_t bytes, void* stream);
+int paras_b200_memcpy_d2d(int gpu, void* dst, const void* src, size_t bytes, void* stream);
+int paras_b200_memcpy_peer(int dst_gpu, void* dst, int src_gpu, const void* src, size_t bytes);
+int paras_b200_memset(int gpu, void* dst, int value, size_t bytes, void* stream);
+/* Pinned host memory for callers that stage their own transfers. */
+int paras_b200_host_alloc(size_t bytes, void** ptr);
+int paras_b200_host_free(void* ptr);
+
+/* Strided copy with element conversion between f32/bf16/f16/f64/i64/i32/i16/i8/u8/bool
+ * (the device<->device branch of _copy_from, csrc/ops/tensor_ops.cpp:252-330, and
+ * launch_strided_store, core/kernels.h).  `code` values are PARAS_SC_*; sizes/strides in
+ * elements, ndim <= 8. */
+enum { PARAS_SC_F32 = 0, PARAS_SC_BF16 = 1, PARAS_SC_F16 = 2, PARAS_SC_F64 = 3, PARAS_SC_I64 = 4,
+       PARAS_SC_I32 = 5, PARAS_SC_I16 = 6, PARAS_SC_I8 = 7, PARAS_SC_U8 = 8, PARAS_SC_BOOL = 9 };
+int paras_b200_strided_copy(int gpu, void* dst, int dst_code, const int64_t* dst_strides,
+                            const void* src, int src_code, const int64_t* src_strides,
+                            const int64_t* sizes, int ndim, void* stream);
+/* fill_.Scalar (tensor_ops.cpp): contiguous fill of n elements with a value given as double. */
+int paras_b200_fill(int gpu, void* dst, int code, double value, int64_t n, void* stream);
+
+/* ---- scaled dot product attention forward ----
+ * Replaces sdpa_math (csrc/ops/attention_ops.cpp:71-136) together with everything it
+ * composes: repeat_interleave (tensor_ops.cpp:687-729), bmm.out (vision_ops.cpp:398-406),
+ * mul.out (pointwise_ops.cpp:280-284), ones/tril/masked_fill (creation_ops.cpp:45-51,
+ * indexing_ops.cpp:533-596, scatter_ops.cpp:43-71) and _softmax (pointwise_ops.cpp:926-981).
+ *
+ * q   [B, Hq,  Lq, D]   k, v [B, Hkv, Lk, D]   out [B, Hq, Lq, D]; the last dim is
+ * contiguous, the other three have element strides *_strides[3] = {B, H, L}.
+ * Hq must be a multiple of Hkv (GQA; query head h reads kv head h / (Hq/Hkv), which is
+ * what repeat_interleave produces).  `causal` uses the reference's TOP-LEFT alignment:
+ * query i attends keys 0..i whatever Lk-Lq is (attention_ops.cpp:103-116).
+ * `mask` (optional, exclusive with causal) is [B, Hq, Lq, Lk] with element strides
+ * mask_strides[4] (0 = broadcast); kind 1 = bool (true = attend), 2 = additive in `dtype`,
+ * 3 = additive f32 (attention_ops.cpp:117-126).
+ * `lse` (optional) receives log-sum-exp of the scaled scores, f32 [B, Hq, Lq].
+ * `flags`: PARAS_SDPA_REF_SCALE rounds `scale` to `dtype` first, as the reference's
+ * scalar wrapping does (pointwise_ops.cpp:54-59).
+ * `workspace` (optional): device scratch for split-KV partial results; when NULL and the
+ * chosen kernel needs scratch, it is taken from the GPU's pool and freed stream-ordered.
+ * Query it with paras_b200_sdpa_workspace_bytes().
+ */
+enum { PARAS_SDPA_REF_SCALE = 1, PARAS_SDPA_FORCE_SIMT = 2, PARAS_SDPA_FORCE_TENSOR = 4 };
+
+typedef struct paras_sdpa_args {
+    const void* q;
+    const void* k;
+    const void* v;
+    void* out;
+    float* lse;
+    const void* mask;
+    int32_t mask_kind;
+    int32_t dtype; /* paras_dtype */
+    int32_t B, Hq, Hkv, Lq, Lk, D;
+    int64_t q_strides[3];
+    int64_t k_strides[3];
+    int64_t v_strides[3];
+    int64_t o_strides[3];
+    int64_t mask_strides[4];
+    int32_t causal;
+    int32_t flags;
+    double scale;
+    void* workspace;
+    size_t workspace_bytes;
+    int32_t gpu;
+    int32_t reserved;
+    void* stream;
+} paras_sdpa_args;
+
+int paras_b200_sdpa_fwd(const paras_sdpa_args* args);
+int paras_b200_sdpa_workspace_bytes(const paras_sdpa_args* args, size_t* bytes);
+/* Name of the kernel the last successful paras_b200_sdpa_fwd call of this thread used
+ * ("tcgen05", "simt", "decode_mma", ...); for tests and logs. */
+const char* paras_b200_sdpa_last_kernel(void);
+
+/* ---- RMSNorm ----
+ * mode PARAS_ROUND_ONCE  = paras::rms_norm (csrc/ops/fused_ops.cpp:43-88): wide
+ *      accumulation, one rounding of the result; `rstd` (optional, f32[rows]) receives
+ *      1/sqrt(mean(x^2)+eps).
+ * mode PARAS_ROUND_PER_OP = aten::rms_norm on the reference (csrc/ops/rms_swiglu_ops.cpp:
+ *      43-75): emulates its rounding to `dtype` after pow, sum, *1/N, +eps, rsqrt, *inv and
+ *      *weight (pointwise_ops.cpp:33-85,246-249), so 16-bit results match it.
+ * x, y: [rows, H] contiguous rows with a row stride of H; weight: [H] or NULL.
+ */
+enum { PARAS_ROUND_ONCE = 0, PARAS_ROUND_PER_OP = 1 };
+int paras_b200_rmsnorm_fwd(int gpu, const void* x, const void* weight, void* y, float* rstd,
+                           int64_t rows, int64_t H, double eps, int dtype, int mode,
+                           void* stream);
+/* paras::rms_norm_backward (csrc/ops/fused_ops.cpp:90-157). grad_weight has `dtype`. */
+int paras_b200_rmsnorm_bwd(int gpu, const void* grad_out, const void* x, const void* weight,
+                           const float* rstd, void* grad_x, void* grad_weight, int64_t rows,
+                           int64_t H, int dtype, void* stream);
+
+/* ---- SwiGLU ----
+ * mode PARAS_ROUND_ONCE  = paras::swiglu(gate, up) (csrc/ops/fused_ops.cpp:162-194):
+ *      out = gate/(1+exp(-gate)) * up, one rounding.
+ * mode PARAS_ROUND_PER_OP = torch_paras::swiglu(x, gate) = x * silu(gate)
+ *      (csrc/ops/rms_swiglu_ops.cpp:83-86): silu is rounded to `dtype` before the multiply.
+ *      Pass x as `up`.
+ * Contiguous, n elements.
+ */
+int paras_b200_swiglu_fwd(int gpu, const void* gate, const void* up, void* out, int64_t n,
+                          int dtype, int mode, void* stream);
+/* paras::swiglu_backward (csrc/ops/fused_ops.cpp:196-229). */
+int paras_b200_swiglu_bwd(int gpu, const void* grad_out, const void* gate, const void* up,
+                          void* grad_gate, void* grad_up, int64_t n, int dtype, void* stream);
+
+/* paras::rotate_half / rotate_half_backward (csrc/ops/fused_ops.cpp:234-302): rows of D
+ * contiguous elements, out = cat(-x2, x1) (forward) or cat(g2, -g1) (backward). */
+int paras_b200_rotate_half(int gpu, const void* x, void* out, int64_t rows, int64_t D, int dtype,
+                           int backward, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PARAS_B200_H_ */

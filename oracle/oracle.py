@@ -71,9 +71,15 @@ def softmax_lastdim(x: Tensor) -> Tensor:
 
 
 def matmul_ref(a: Tensor, b: Tensor) -> Tensor:
-    """The reference hands both operands to libtorch's CPU ``at::bmm`` and copies the
-    result back (vision_ops.cpp:398-406); the result has the operands' dtype."""
-    return torch.matmul(a, b)
+    """Upstream ``at::matmul`` folds the leading dims and calls ``bmm.out``; the reference's
+    bmm_out makes CONTIGUOUS host copies of both operands and runs libtorch's CPU ``at::bmm``
+    on them (vision_ops.cpp:34-36,398-406).  The result has the operands' dtype."""
+    if a.dim() < 3 or b.dim() < 3 or a.shape[:-2] != b.shape[:-2]:
+        return torch.matmul(a, b)
+    lead = a.shape[:-2]
+    a3 = a.reshape(-1, a.size(-2), a.size(-1)).contiguous()
+    b3 = b.reshape(-1, b.size(-2), b.size(-1)).contiguous()
+    return torch.bmm(a3, b3).reshape(*lead, a.size(-2), b.size(-1))
 
 
 # ----------------------------------------------------------------------------------
