@@ -1,0 +1,400 @@
+#!/usr/bin/env python
+"""Benchmark of the transformer hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--quick]
+
+Headline (the JSON line's metric/value): causal bf16 scaled-dot-product attention forward
+on the Llama-style configuration  B=8 Hq=Hkv=32 S=2048 D=128  in TFLOP/s, algorithmic
+FLOPs = 4*B*H*Lq*Lk*D/2 (causal).  One step = one attention forward over one batch that is
+already resident in HBM; K steps are timed with CUDA events on the launching stream, after W
+warm-up steps, between barrier + synchronize on both sides, max over ranks.  q,k,v,out are
+537 MB per step, larger than the 126 MB L2, so no explicit L2 flush is needed.
+
+Beside it, in "extra": RMSNorm [16384,4096] and SwiGLU [32768,14336] in HBM GB/s, the GQA
+long-sequence attention (B=4 Hq=64 Hkv=8 S=8192) in TFLOP/s and the decode step
+(B=64 q_len=1 kv_len=32768 Hq=32 Hkv=8) in HBM GB/s, each with its roofline fraction.
+
+"e2e" is the same attention through the public operator on the `paras` device with HOST
+buffers: pinned host q,k,v -> paras:N, F.scaled_dot_product_attention, result -> host, all
+inside the timed region.
+
+N > 1 (one process per GPU under torchrun): every rank runs the same per-GPU workload on its
+own batch shard (weak scaling, no collective on the forward path); value = total FLOPs of all
+ranks / max-over-ranks time.
+
+`--impl reference` times the reference's own CPU implementation (its paras:0 host engine,
+built into oracle/_ref by oracle/Makefile; the oracle restatement if that build is absent) on
+a bounded sample of the same workload, with all the host threads torch gives it.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for _p in (os.path.join(ROOT, "framework-torch-paras_b200", "python"), ROOT):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+import torch  # noqa: E402
+
+WORKLOAD = "config2: bf16 causal SDPA B=8 Hq=Hkv=32 S=2048 D=128 (Llama-style)"
+C2 = dict(B=8, Hq=32, Hkv=32, S=2048, D=128)
+# bounded CPU sample of config 2: one batch element, 16 of its 32 heads, full sequence
+CPU_SAMPLE = dict(B=1, H=16, S=2048, D=128)
+
+
+def sdpa_flops(B, Hq, Lq, Lk, D, causal):
+    f = 4.0 * B * Hq * Lq * Lk * D
+    return f / 2 if causal else f
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"],
+                "bf16_tflops_sustained": p.get("bf16_tflops_sustained"), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0,
+            "source": "fallback"}
+
+
+class ClockSampler:
+    """Polls NVML for SM clock and throttle reasons while a timed region runs."""
+
+    def __init__(self, index: int, period_s: float = 0.002):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        self.period = period_s
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:  # noqa: BLE001
+            self.nv = None
+
+    _NAMES = {0x2: "applications_clocks_setting", 0x4: "sw_power_cap", 0x8: "hw_slowdown",
+              0x10: "sync_boost", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown",
+              0x80: "hw_power_brake_slowdown", 0x100: "display_clock_setting"}
+
+    def _poll(self):
+        nv = self.nv
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                try:
+                    r = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                except Exception:  # noqa: BLE001
+                    r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for bit, name in self._NAMES.items():
+                    if r & bit:
+                        self.reasons.add(name)
+            except Exception:  # noqa: BLE001
+                pass
+            time.sleep(self.period)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self._thread = threading.Thread(target=self._poll, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": 0}
+        return {"sm_mhz": statistics.median(self.samples), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+def dist_env():
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    return rank, world, local
+
+
+# --------------------------------------------------------------------------------------
+# reference arm: the reference's CPU implementation on the host cores
+# --------------------------------------------------------------------------------------
+def cpu_sample_inputs():
+    g = torch.Generator().manual_seed(1001)
+    s = CPU_SAMPLE
+    mk = lambda: torch.randn(s["B"], s["H"], s["S"], s["D"], generator=g).bfloat16()  # noqa: E731
+    return mk(), mk(), mk()
+
+
+def time_cpu_reference(repeat: int, warmup: int):
+    """Returns (seconds per pass list, kind, threads).  kind = "reference" when the unmodified
+    reference build is present, else "port" (the oracle restatement)."""
+    q, k, v = cpu_sample_inputs()
+    ref_so = os.path.join(ROOT, "oracle", "_ref", "_C.so")
+    if os.path.exists(ref_so):
+        jobs = [{"op": "sdpa", "args": {"q": q, "k": k, "v": v, "is_causal": True},
+                 "repeat": 1, "keep_out": False} for _ in range(warmup + repeat)]
+        with tempfile.TemporaryDirectory() as td:
+            torch.save(jobs, os.path.join(td, "j.pt"))
+            subprocess.check_call([sys.executable, os.path.join(ROOT, "oracle", "ref_run.py"),
+                                   os.path.join(td, "j.pt"), os.path.join(td, "r.pt")])
+            res = torch.load(os.path.join(td, "r.pt"))
+        return [r["seconds"] for r in res[warmup:]], "reference", res[0]["threads"]
+    from oracle import oracle as O
+    times = []
+    for i in range(warmup + repeat):
+        t0 = time.perf_counter()
+        O.sdpa(q, k, v, is_causal=True)
+        if i >= warmup:
+            times.append(time.perf_counter() - t0)
+    return times, "port", torch.get_num_threads()
+
+
+def sample_desc():
+    s = CPU_SAMPLE
+    return (f"B={s['B']} H={s['H']} S={s['S']} D={s['D']} causal bf16 = "
+            f"{s['B'] * s['H']}/{C2['B'] * C2['Hq']} of the workload's (batch, head) units")
+
+
+def run_reference_arm(args):
+    rank, world, _ = dist_env()
+    if rank != 0:
+        return
+    times, kind, threads = time_cpu_reference(args.steps, args.warmup)
+    s = CPU_SAMPLE
+    fl = sdpa_flops(s["B"], s["H"], s["S"], s["S"], s["D"], True)
+    total = sum(times)
+    val = fl * len(times) / total / 1e12
+    line = {
+        "impl": "reference", "metric": "sdpa_fwd_tflops", "value": val, "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": 1e3 * total / len(times), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "step": "bounded CPU sample: " + sample_desc()},
+        "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": threads, "kind": kind,
+                         "sample": sample_desc()},
+        "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------------------
+# our arm
+# --------------------------------------------------------------------------------------
+def timed_loop(fn, steps, warmup, barrier):
+    """fn() launches one step on torch's current stream.  Returns total milliseconds for
+    `steps` steps, measured with CUDA events on that stream."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    barrier()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        fn()
+    stop.record()
+    torch.cuda.synchronize()
+    barrier()
+    return start.elapsed_time(stop)
+
+
+def run_ours(args):
+    rank, world, local = dist_env()
+    if world != args.gpus and world > 1:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no GPU visible; the hot path has no CPU fallback")
+    torch.cuda.set_device(local)
+    import torch.nn.functional as F
+    import torch_paras
+    from torch_paras import abi
+
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+
+    def max_over_ranks(ms: float) -> float:
+        if dist is None:
+            return ms
+        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    dev = torch.device("cuda", local)
+    peaks = measured_peaks()
+    steps, warmup = args.steps, max(args.warmup, 3)
+
+    def gen(shape, seed, mean=0.0, std=1.0):
+        g = torch.Generator(device=dev).manual_seed(seed * 1000 + rank)
+        return (mean + std * torch.randn(shape, generator=g, device=dev)).bfloat16()
+
+    # ---------------- headline: config 2 attention ----------------
+    c = C2
+    q = gen((c["B"], c["Hq"], c["S"], c["D"]), 1)
+    k = gen((c["B"], c["Hkv"], c["S"], c["D"]), 2)
+    v = gen((c["B"], c["Hkv"], c["S"], c["D"]), 3)
+    out = torch.empty_like(q)
+    flops = sdpa_flops(c["B"], c["Hq"], c["S"], c["S"], c["D"], True)
+
+    def step():
+        abi.sdpa_fwd(q, k, v, causal=True, out=out, flags=abi.SDPA_REF_SCALE)
+
+    step()
+    kernel_name = abi.sdpa_last_kernel()
+    with ClockSampler(local) as clk:
+        ms = max_over_ranks(timed_loop(step, steps, warmup, barrier))
+    ms_step = ms / steps
+    tflops = world * flops / (ms_step * 1e-3) / 1e12
+    per_gpu_tflops = tflops / world
+    roofline = {"bound": "tensor", "kernel": f"sdpa_tc_kernel ({kernel_name})",
+                "achieved": per_gpu_tflops, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                "frac": per_gpu_tflops / peaks["bf16_tflops"], "peak_source": peaks["source"] + " (burst)",
+                "frac_of_nominal_2250": per_gpu_tflops / 2250.0, "traffic": None}
+
+    extra = {}
+    if not args.quick:
+        esteps = max(5, min(steps, 20))
+
+        # RMSNorm, config 2 shape: bytes = 2*rows*H*2 + H*2
+        x = gen((16384, 4096), 4)
+        w = gen((4096,), 5, mean=1.0, std=0.1)
+        y = torch.empty_like(x)
+        rstd = None
+        t = max_over_ranks(timed_loop(lambda: abi.rmsnorm_fwd(x, w, 1e-6, out=y), esteps, warmup, barrier)) / esteps
+        nbytes = 2 * x.numel() * 2 + w.numel() * 2
+        gbs = nbytes / (t * 1e-3) / 1e9
+        extra["rmsnorm_fused_16384x4096"] = {"ms": t, "gbs": gbs, "frac_of_hbm_peak": gbs / peaks["hbm_gbs"],
+                                             "bytes": nbytes}
+        t = max_over_ranks(timed_loop(lambda: abi.rmsnorm_fwd(x, w, 1e-6, out=y, mode=abi.ROUND_PER_OP),
+                                      esteps, warmup, barrier)) / esteps
+        gbs = nbytes / (t * 1e-3) / 1e9
+        extra["rmsnorm_aten_16384x4096"] = {"ms": t, "gbs": gbs, "frac_of_hbm_peak": gbs / peaks["hbm_gbs"],
+                                            "bytes": nbytes}
+        del x, y, rstd
+
+        # SwiGLU, config 3 shape: bytes = 3*n*2
+        gate, up = gen((32768, 14336), 6), gen((32768, 14336), 7)
+        so = torch.empty_like(gate)
+        t = max_over_ranks(timed_loop(lambda: abi.swiglu_fwd(gate, up, out=so), esteps, warmup, barrier)) / esteps
+        nbytes = 3 * gate.numel() * 2
+        gbs = nbytes / (t * 1e-3) / 1e9
+        extra["swiglu_32768x14336"] = {"ms": t, "gbs": gbs, "frac_of_hbm_peak": gbs / peaks["hbm_gbs"],
+                                       "bytes": nbytes}
+        del gate, up, so
+
+        # config 3 attention: B=4 Hq=64 Hkv=8 S=8192
+        q3, k3, v3 = gen((4, 64, 8192, 128), 8), gen((4, 8, 8192, 128), 9), gen((4, 8, 8192, 128), 10)
+        o3 = torch.empty_like(q3)
+        s3 = max(3, esteps // 4)
+        t = max_over_ranks(timed_loop(lambda: abi.sdpa_fwd(q3, k3, v3, causal=True, out=o3), s3, 3, barrier)) / s3
+        f3 = sdpa_flops(4, 64, 8192, 8192, 128, True)
+        tf = f3 / (t * 1e-3) / 1e12
+        extra["sdpa_gqa_B4_Hq64_Hkv8_S8192"] = {"ms": t, "tflops": tf, "frac_of_bf16_peak": tf / peaks["bf16_tflops"],
+                                                 "kernel": abi.sdpa_last_kernel()}
+        del q3, k3, v3, o3
+
+        # config 4 decode: bytes = K + V (once per kv head) + q + o
+        qd, kd, vd = gen((64, 32, 1, 128), 11), gen((64, 8, 32768, 128), 12), gen((64, 8, 32768, 128), 13)
+        od = torch.empty_like(qd)
+        ws_bytes = abi.sdpa_workspace_bytes(qd, kd, vd)
+        ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=dev)
+        t = max_over_ranks(timed_loop(lambda: abi.sdpa_fwd(qd, kd, vd, out=od, workspace=ws if ws_bytes else None),
+                                      s3, 3, barrier)) / s3
+        nbytes = (kd.numel() + vd.numel() + qd.numel() + od.numel()) * 2
+        gbs = nbytes / (t * 1e-3) / 1e9
+        extra["sdpa_decode_B64_kv32768"] = {"ms": t, "gbs": gbs, "frac_of_hbm_peak": gbs / peaks["hbm_gbs"],
+                                            "bytes": nbytes, "kernel": abi.sdpa_last_kernel()}
+        del qd, kd, vd, od, ws
+        torch.cuda.empty_cache()
+
+    # ---------------- e2e: public operator on the paras device, host buffers ----------------
+    pdev = f"paras:{local + 1}"
+    hq, hk, hv = (t_.cpu().pin_memory() for t_ in (q, k, v))
+    h2d = (hq.numel() + hk.numel() + hv.numel()) * 2
+    d2h = hq.numel() * 2
+
+    def e2e_step():
+        dq = hq.to(pdev, non_blocking=True)
+        dk = hk.to(pdev, non_blocking=True)
+        dv = hv.to(pdev, non_blocking=True)
+        return F.scaled_dot_product_attention(dq, dk, dv, is_causal=True).cpu()
+
+    e2e_steps = max(2, min(steps, 5))
+    for _ in range(2):
+        e2e_step()
+    torch_paras.synchronize(local + 1)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_step()
+    torch_paras.synchronize(local + 1)
+    e2e_s = (time.perf_counter() - t0) / e2e_steps
+    e2e_s = max_over_ranks(e2e_s * 1e3) * 1e-3
+    e2e = {"value": world * flops / e2e_s / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_s * 1e3,
+           "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+           "api": "F.scaled_dot_product_attention on paras device, pinned host q/k/v in, host result out"}
+
+    cpu_baseline = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        times, kind, threads = time_cpu_reference(args.cpu_repeat, 1)
+        s = CPU_SAMPLE
+        fl = sdpa_flops(s["B"], s["H"], s["S"], s["S"], s["D"], True)
+        cpu_baseline = {"value": fl * len(times) / sum(times) / 1e12, "unit": "TFLOP/s", "cores": threads,
+                        "kind": kind, "sample": sample_desc(), "seconds_per_pass": sum(times) / len(times)}
+
+    if rank == 0:
+        line = {
+            "metric": "sdpa_fwd_tflops", "value": tflops, "unit": "TFLOP/s", "n_gpus": world,
+            "steps": steps, "warmup": warmup, "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "per_gpu_batch": c["B"], "global_batch": c["B"] * world,
+                       "l2": "inputs (537 MB per step) larger than the 126 MB L2; no flush",
+                       "sharding": "batch shards, one per rank, no collective on the forward path"},
+            "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e,
+            "gpu_launches": steps, "clocks": clk.summary(), "extra": extra,
+        }
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--quick", action="store_true", help="headline + e2e only")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cpu-repeat", type=int, default=3)
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

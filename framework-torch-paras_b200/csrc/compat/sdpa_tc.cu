@@ -66,6 +66,10 @@ constexpr int kSmemMisc = kSmemBars + kNumBars * 8;   // tmem base word, abort f
 constexpr int kSmemTotal = kSmemMisc + 16;
 constexpr int kSmemLaunch = kSmemTotal + 1024;        // slack to align the base to 1024 B
 
+// Set by any CTA whose bounded wait ran out; later CTAs of the same (already failed) launch
+// see it and leave at once, so a broken launch costs one wave of timeouts, not one per CTA.
+__device__ int g_abort_latch = 0;
+
 struct TcParams {
     void* out;
     float* lse;
@@ -107,6 +111,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         ntile[t] = kv_tiles_for(p, start[t]);
     }
     const int n = max(ntile[0], ntile[1]);
+    if (*reinterpret_cast<volatile int*>(&g_abort_latch)) return;  // uniform: before any barrier or TMEM use
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < kNumBars; ++i) {
@@ -348,6 +353,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         tmem_dealloc(tmem, kTmemCols);
     }
     if (threadIdx.x == 0 && *abort_flag) {
+        g_abort_latch = 1;
         *p.status = 1;
         __threadfence_system();
     }
@@ -428,7 +434,12 @@ bool sdpa_tc_supported(const Gpu* g, const paras_sdpa_args& a, const char** why)
 
 int sdpa_tc_launch(Gpu* g, const paras_sdpa_args& a, float scale, cudaStream_t s) {
     int st = check_status_word(g);
-    if (st != PARAS_OK) return st;
+    if (st != PARAS_OK) {
+        // report the earlier failure once and re-arm the kernel
+        const int zero = 0;
+        cudaMemcpyToSymbol(g_abort_latch, &zero, sizeof(int));
+        return st;
+    }
     CUtensorMap mq, mk, mv;
     if ((st = make_map(&mq, a.q, a.dtype, a.B, a.Hq, a.Lq, a.q_strides)) != PARAS_OK) return st;
     if ((st = make_map(&mk, a.k, a.dtype, a.B, a.Hkv, a.Lk, a.k_strides)) != PARAS_OK) return st;
@@ -443,7 +454,6 @@ int sdpa_tc_launch(Gpu* g, const paras_sdpa_args& a, float scale, cudaStream_t s
     p.scale_log2 = scale * 1.4426950408889634f;
     p.status = g->status_dev;
     dim3 grid((a.Lq + kTilesPerCta * BM - 1) / (kTilesPerCta * BM), a.Hq, a.B);
-    static std::once_flag attr_once[2];
     if (a.dtype == PARAS_BF16) {
         PB_CUDA(cudaFuncSetAttribute(sdpa_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      kSmemLaunch));
@@ -453,7 +463,6 @@ int sdpa_tc_launch(Gpu* g, const paras_sdpa_args& a, float scale, cudaStream_t s
                                      kSmemLaunch));
         sdpa_tc_kernel<false><<<grid, kThreads, kSmemLaunch, s>>>(mq, mk, mv, p);
     }
-    (void)attr_once;
     PB_LAUNCH_CHECK("sdpa_tc_kernel");
     return PARAS_OK;
 }

@@ -51,7 +51,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // Bounded wait: gives up after `limit_ns` of wall time, or as soon as another thread of
 // the CTA has raised `*abort_flag` (a shared-memory word).  Returns false when it gave up;
 // the caller then stops issuing work and leaves through the kernel's common exit.
-constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s: orders of magnitude above any real wait
+constexpr uint64_t kWaitLimitNs = 200000000ull;  // 0.2 s: orders of magnitude above any real wait
 
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
                                           volatile int* abort_flag) {

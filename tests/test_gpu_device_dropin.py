@@ -1,0 +1,243 @@
+"""Drop-in behaviour behind the `paras` device: the same calls a user of the reference makes
+(F.scaled_dot_product_attention, torch.ops.aten.rms_norm, torch.ops.torch_paras.swiglu,
+torch_paras.nn.*) on device paras:1, compared with CPU PyTorch at the reference's own
+tolerance (atol = rtol = 1e-4, dtype and shape must match).  The cases follow the
+reference's tests/test_attention_norm_ops.py and tests/test_fused_ops.py one for one."""
+import math
+import threading
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+from oracle import oracle as O
+
+import torch_paras
+from torch_paras import nn as paras_nn
+
+pytestmark = pytest.mark.gpu
+DEV = "paras:1"
+
+
+def assert_close(actual, expected, msg=""):
+    actual, expected = actual.cpu(), expected.cpu()
+    assert actual.dtype == expected.dtype, f"{msg}: dtype {actual.dtype} vs {expected.dtype}"
+    assert actual.shape == expected.shape, f"{msg}: shape {tuple(actual.shape)} vs {tuple(expected.shape)}"
+    if actual.dtype.is_floating_point:
+        assert torch.allclose(actual, expected, atol=1e-4, rtol=1e-4, equal_nan=True), msg
+    else:
+        assert torch.equal(actual, expected), msg
+
+
+@pytest.fixture(autouse=True)
+def _seed():
+    torch.manual_seed(0)
+
+
+def _qkv(B=2, H=4, Lq=8, Lk=8, E=16):
+    q, k, v = torch.randn(B, H, Lq, E), torch.randn(B, H, Lk, E), torch.randn(B, H, Lk, E)
+    return q, k, v, q.to(DEV), k.to(DEV), v.to(DEV)
+
+
+def test_device_bring_up():
+    assert torch_paras.gpu_count() >= 1
+    assert torch_paras.device_count() == torch_paras.gpu_count() + 1
+    assert torch_paras.is_gpu_device(1)
+    assert "B200" in torch_paras.device_name(1) or torch_paras.device_name(1)
+    x = torch.randn(64, 64)
+    y = x.to(DEV)
+    assert y.device.type == "paras" and y.device.index == 1 and y.is_paras
+    assert torch.equal(y.cpu(), x)
+    assert torch_paras.memory_allocated(1) >= x.numel() * 4
+    torch_paras.synchronize()
+    torch_paras.synchronize(1)
+
+
+def test_sdpa_basic():
+    q, k, v, dq, dk, dv = _qkv()
+    assert_close(F.scaled_dot_product_attention(dq, dk, dv), F.scaled_dot_product_attention(q, k, v))
+
+
+def test_sdpa_explicit_scale():
+    q, k, v, dq, dk, dv = _qkv(E=16)
+    s = 1.0 / math.sqrt(32)
+    assert_close(F.scaled_dot_product_attention(dq, dk, dv, scale=s),
+                 F.scaled_dot_product_attention(q, k, v, scale=s))
+
+
+def test_sdpa_causal():
+    q, k, v, dq, dk, dv = _qkv()
+    assert_close(F.scaled_dot_product_attention(dq, dk, dv, is_causal=True),
+                 F.scaled_dot_product_attention(q, k, v, is_causal=True))
+
+
+def test_sdpa_causal_unequal_lengths():
+    q, k, v, dq, dk, dv = _qkv(Lq=4, Lk=8)
+    assert_close(F.scaled_dot_product_attention(dq, dk, dv, is_causal=True),
+                 F.scaled_dot_product_attention(q, k, v, is_causal=True))
+
+
+def test_sdpa_bool_mask():
+    q, k, v, dq, dk, dv = _qkv()
+    mask = torch.rand(2, 4, 8, 8) > 0.3
+    assert_close(F.scaled_dot_product_attention(dq, dk, dv, attn_mask=mask.to(DEV)),
+                 F.scaled_dot_product_attention(q, k, v, attn_mask=mask))
+
+
+def test_sdpa_additive_mask():
+    q, k, v, dq, dk, dv = _qkv()
+    bias = torch.randn(2, 4, 8, 8) * 0.1
+    assert_close(F.scaled_dot_product_attention(dq, dk, dv, attn_mask=bias.to(DEV)),
+                 F.scaled_dot_product_attention(q, k, v, attn_mask=bias))
+
+
+def test_sdpa_gqa_through_math_op():
+    q, k, v = torch.randn(2, 4, 8, 16), torch.randn(2, 2, 8, 16), torch.randn(2, 2, 8, 16)
+    ref, _ = torch.ops.aten._scaled_dot_product_attention_math(
+        q, k, v, None, 0.0, False, None, scale=None, enable_gqa=True)
+    out, _ = torch.ops.aten._scaled_dot_product_attention_math(
+        q.to(DEV), k.to(DEV), v.to(DEV), None, 0.0, False, None, scale=None, enable_gqa=True)
+    assert_close(out, ref)
+
+
+def test_sdpa_mismatched_gqa_heads_raises():
+    q, k = torch.randn(1, 5, 4, 8).to(DEV), torch.randn(1, 2, 4, 8).to(DEV)
+    with pytest.raises(RuntimeError):
+        torch.ops.aten._scaled_dot_product_attention_math(q, k, k, None, 0.0, False, None,
+                                                          scale=None, enable_gqa=True)
+
+
+def test_sdpa_bf16_llama_shape_hits_the_tensor_core_kernel():
+    g = torch.Generator().manual_seed(1001)
+    q = torch.randn(1, 8, 512, 128, generator=g).bfloat16()
+    k = torch.randn(1, 2, 512, 128, generator=g).bfloat16()
+    v = torch.randn(1, 2, 512, 128, generator=g).bfloat16()
+    out = F.scaled_dot_product_attention(q.to(DEV), k.to(DEV), v.to(DEV), is_causal=True, enable_gqa=True)
+    assert torch_paras._C.sdpa_last_kernel() == "tcgen05"
+    want = O.sdpa(q, k, v, is_causal=True, enable_gqa=True)
+    assert out.dtype == torch.bfloat16 and out.shape == want.shape
+    assert (out.cpu().double() - want.double()).abs().max().item() <= 2e-2
+    # 3-D input (batch, seq, dim) and a [B, L, H, D] -> transpose(1, 2) view
+    q3 = torch.randn(4, 70, 64, generator=g)
+    assert_close(F.scaled_dot_product_attention(q3.to(DEV), q3.to(DEV), q3.to(DEV)),
+                 F.scaled_dot_product_attention(q3, q3, q3))
+    qt = torch.randn(2, 33, 4, 32, generator=g)
+    assert_close(F.scaled_dot_product_attention(*(qt.to(DEV).transpose(1, 2),) * 3, is_causal=True),
+                 F.scaled_dot_product_attention(*(qt.transpose(1, 2),) * 3, is_causal=True))
+
+
+def test_sdpa_dropout_is_refused_not_emulated():
+    q = torch.randn(1, 2, 8, 16).to(DEV)
+    with pytest.raises(RuntimeError, match="dropout"):
+        F.scaled_dot_product_attention(q, q, q, dropout_p=0.1)
+
+
+def test_rms_norm_no_weight():
+    x = torch.randn(4, 6, 32)
+    assert_close(torch.ops.aten.rms_norm(x.to(DEV), [32], None, None),
+                 x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + 1e-6))
+
+
+def test_rms_norm_with_weight():
+    x, w = torch.randn(4, 6, 32), torch.randn(32)
+    assert_close(torch.ops.aten.rms_norm(x.to(DEV), [32], w.to(DEV), 1e-5),
+                 torch.ops.aten.rms_norm(x, [32], w, 1e-5))
+    assert_close(F.rms_norm(x.to(DEV), (32,), w.to(DEV), 1e-5), F.rms_norm(x, (32,), w, 1e-5))
+
+
+def test_rms_norm_multi_dim_normalized_shape():
+    x = torch.randn(3, 4, 5)
+    assert_close(torch.ops.aten.rms_norm(x.to(DEV), [4, 5], None, 1e-6),
+                 torch.ops.aten.rms_norm(x, [4, 5], None, 1e-6))
+
+
+def test_rms_norm_shape_mismatch_raises():
+    x, w = torch.randn(4, 6, 32).to(DEV), torch.randn(16).to(DEV)
+    with pytest.raises(RuntimeError):
+        torch.ops.aten.rms_norm(x, [32], w, None)
+
+
+def test_swiglu_composite_and_manual():
+    x, gate = torch.randn(4, 32), torch.randn(4, 32)
+    assert_close(torch.ops.torch_paras.swiglu(x.to(DEV), gate.to(DEV)), torch.ops.torch_paras.swiglu(x, gate))
+    assert_close(torch.ops.torch_paras.swiglu(x.to(DEV), gate.to(DEV)), x * F.silu(gate))
+    # broadcasting, as the composite allows
+    assert_close(torch.ops.torch_paras.swiglu(x.to(DEV), gate[:1].to(DEV)), x * F.silu(gate[:1]))
+
+
+def test_fused_rms_norm_forward_backward():
+    x, w = torch.randn(4, 8, requires_grad=True), torch.randn(8, requires_grad=True)
+    ref = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + 1e-6) * w
+    ref.sum().backward()
+    xd = x.detach().to(DEV).requires_grad_()
+    wd = w.detach().to(DEV).requires_grad_()
+    out = paras_nn.rms_norm(xd, wd, 1e-6)
+    assert_close(out.detach(), ref.detach())
+    out.sum().backward()
+    assert_close(xd.grad, x.grad)
+    assert_close(wd.grad, w.grad)
+
+
+def test_fused_swiglu_forward_backward():
+    gate, up = torch.randn(4, 8, requires_grad=True), torch.randn(4, 8, requires_grad=True)
+    ref = F.silu(gate) * up
+    ref.sum().backward()
+    gd = gate.detach().to(DEV).requires_grad_()
+    ud = up.detach().to(DEV).requires_grad_()
+    out = paras_nn.swiglu(gd, ud)
+    assert_close(out.detach(), ref.detach())
+    out.sum().backward()
+    assert_close(gd.grad, gate.grad)
+    assert_close(ud.grad, up.grad)
+
+
+def test_rotate_half_forward_backward():
+    x = torch.randn(4, 8, requires_grad=True)
+    x1, x2 = x.chunk(2, dim=-1)
+    ref = torch.cat((-x2, x1), dim=-1)
+    ref.sum().backward()
+    xd = x.detach().to(DEV).requires_grad_()
+    out = paras_nn.rotate_half(xd)
+    assert_close(out.detach(), ref.detach())
+    out.sum().backward()
+    assert_close(xd.grad, x.grad)
+
+
+def test_copy_cases():
+    a, src = torch.randn(4, 5), torch.randn(4, 5)
+    assert_close(a.to(DEV).clone().copy_(src.to(DEV)), a.clone().copy_(src))
+    with pytest.raises(RuntimeError):
+        a.to(DEV).clone().copy_(torch.randn(5).to(DEV))          # broadcasting copy is refused
+    h = torch.randn(4, 5).half()
+    assert_close(a.to(DEV).clone().copy_(h.to(DEV)), a.clone().copy_(h))   # dtype cast on device
+    d = torch.randn(4, 5).to(DEV)
+    d.copy_(src)
+    assert_close(d, src)
+    t = torch.randn(6, 7)
+    assert_close(t.to(DEV).t().contiguous(), t.t().contiguous())            # strided device copy
+    assert_close(t.to(DEV)[1:5, ::2], t[1:5, ::2])
+    big = torch.randn(3000, 3000)                                            # several staging chunks
+    assert_close(big.to(DEV), big)
+    assert torch.zeros(5, device=DEV).cpu().abs().sum().item() == 0
+    assert torch.full((3,), 7.0, device=DEV).cpu().tolist() == [7.0, 7.0, 7.0]
+    one = torch.tensor([1.5, -2.25, 3.0])
+    assert one.to(DEV)[1].item() == -2.25                                     # _local_scalar_dense
+
+
+def test_concurrent_dispatch_from_python_threads():
+    x = torch.randn(256, 512)
+    want = F.silu(x) * x
+    errs = []
+
+    def work():
+        try:
+            for _ in range(20):
+                d = x.to(DEV)
+                assert torch.allclose(torch.ops.paras.swiglu(d, d).cpu(), want, atol=1e-4, rtol=1e-4)
+        except Exception as e:  # noqa: BLE001
+            errs.append(e)
+
+    ts = [threading.Thread(target=work) for _ in range(4)]
+    [t.start() for t in ts]
+    [t.join() for t in ts]
+    assert not errs, errs[0]

@@ -1,0 +1,111 @@
+"""Parity at the full sizes of the benchmark configurations, where the oracle cannot run
+whole: oracle comparison on slices (attention is independent per batch and query head;
+RMSNorm and SwiGLU per row) plus size-independent properties of the operators."""
+import pytest
+import torch
+
+from oracle import oracle as O
+
+import torch_paras  # noqa: F401
+from torch_paras import abi
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def gen(shape, seed, dtype=torch.bfloat16, mean=0.0, std=1.0):
+    g = torch.Generator(device=DEV).manual_seed(seed)
+    t = torch.randn(shape, generator=g, device=DEV, dtype=torch.float32)
+    return (mean + std * t).to(dtype)
+
+
+def test_config2_llama_causal_sdpa_full_size():
+    # bf16 B=8 Hq=Hkv=32 S=2048 D=128
+    q, k, v = gen((8, 32, 2048, 128), 1), gen((8, 32, 2048, 128), 2), gen((8, 32, 2048, 128), 3)
+    out = abi.sdpa_fwd(q, k, v, causal=True, flags=abi.SDPA_REF_SCALE)
+    assert abi.sdpa_last_kernel() == "tcgen05"
+    # oracle on two (batch, head) slices
+    for b, h in ((0, 0), (7, 31)):
+        want = O.sdpa(q[b:b + 1, h:h + 1].cpu(), k[b:b + 1, h:h + 1].cpu(), v[b:b + 1, h:h + 1].cpu(),
+                      is_causal=True)
+        err = (out[b:b + 1, h:h + 1].cpu().double() - want.double()).abs().max().item()
+        assert err <= 2e-2, f"slice ({b},{h}): max-abs {err}"
+    # causality: changing keys/values from position p on leaves rows < p bit-identical
+    p = 1111
+    k2, v2 = k.clone(), v.clone()
+    k2[:, :, p:] = gen((8, 32, 2048 - p, 128), 4)
+    v2[:, :, p:] = gen((8, 32, 2048 - p, 128), 5)
+    out2 = abi.sdpa_fwd(q, k2, v2, causal=True, flags=abi.SDPA_REF_SCALE)
+    assert torch.equal(out[:, :, :p], out2[:, :, :p])
+    assert not torch.equal(out[:, :, p:], out2[:, :, p:])
+    # rows of softmax sum to one: V = 1 gives exactly-representable ones
+    ones = torch.ones_like(v)
+    o1 = abi.sdpa_fwd(q, k, ones, causal=True)
+    assert (o1.float() - 1.0).abs().max().item() <= 1e-2
+    # first query row attends only key 0: output row 0 equals v[0]
+    assert torch.equal(out[:, :, 0], v[:, :, 0])
+
+
+def test_config3_gqa_causal_sdpa_long_sequence_slice():
+    # bf16 Hq=64 Hkv=8 S=8192 D=128; one batch element (the config's B=4 repeats it)
+    q, k, v = gen((1, 64, 8192, 128), 6), gen((1, 8, 8192, 128), 7), gen((1, 8, 8192, 128), 8)
+    out = abi.sdpa_fwd(q, k, v, causal=True, flags=abi.SDPA_REF_SCALE)
+    assert abi.sdpa_last_kernel() == "tcgen05"
+    # GQA: query head 13 must read kv head 13 // 8 = 1 -- check against the oracle on rows 0..1023
+    h = 13
+    want = O.sdpa(q[:, h:h + 1, :1024].cpu(), k[:, 1:2, :1024].cpu(), v[:, 1:2, :1024].cpu(), is_causal=True)
+    err = (out[:, h:h + 1, :1024].cpu().double() - want.double()).abs().max().item()
+    assert err <= 2e-2
+    # agreement with the independent CUDA-core kernel on the last rows of one head
+    sl = slice(8192 - 64, 8192)
+    ref = abi.sdpa_fwd(q[:, 63:64, sl].contiguous(), k[:, 7:8], v[:, 7:8], causal=False,
+                       flags=abi.SDPA_FORCE_SIMT | abi.SDPA_REF_SCALE,
+                       mask=torch.ones(64, 8192, dtype=torch.bool, device=DEV).tril(8192 - 64))
+    assert (out[:, 63:64, sl].float() - ref.float()).abs().max().item() <= 2e-2
+
+
+def test_config4_decode_step_full_size_slice():
+    # bf16 B=64 q_len=1 kv_len=32768 Hq=32 Hkv=8 D=128, non-causal; 8 of the 64 batch rows
+    q, k, v = gen((8, 32, 1, 128), 9), gen((8, 8, 32768, 128), 10), gen((8, 8, 32768, 128), 11)
+    out = abi.sdpa_fwd(q, k, v, flags=abi.SDPA_REF_SCALE)
+    want = O.sdpa(q[:1].cpu(), k[:1].cpu(), v[:1].cpu(), enable_gqa=True)
+    assert (out[:1].cpu().double() - want.double()).abs().max().item() <= 2e-2
+    # permuting the cache positions must not change a non-causal result (up to summation order)
+    perm = torch.randperm(32768, device=DEV)
+    out_p = abi.sdpa_fwd(q, k[:, :, perm].contiguous(), v[:, :, perm].contiguous(), flags=abi.SDPA_REF_SCALE)
+    assert (out.float() - out_p.float()).abs().max().item() <= 1e-2
+
+
+def test_config2_rmsnorm_full_size():
+    x = gen((16384, 4096), 12)
+    w = gen((4096,), 13, mean=1.0, std=0.1)
+    y, rstd = abi.rmsnorm_fwd(x, w, 1e-6, return_rstd=True)
+    yc = abi.rmsnorm_fwd(x, w, 1e-6, mode=abi.ROUND_PER_OP)
+    for rows in (slice(0, 64), slice(16384 - 64, 16384)):
+        yo, ro = O.rms_norm_fused(x[rows].cpu(), w.cpu(), 1e-6)
+        assert (y[rows].cpu().double() - yo.double()).abs().max().item() <= 2e-2
+        assert (y[rows].cpu() == yo).float().mean().item() > 0.999
+        assert torch.allclose(rstd[rows].cpu(), ro, rtol=1e-5, atol=1e-6)
+        yco = O.rms_norm_composite(x[rows].cpu(), [4096], w.cpu(), 1e-6)
+        assert (yc[rows].cpu().double() - yco.double()).abs().max().item() <= 2e-2
+    # every normalised row has unit RMS once the weight is divided out
+    rms = (y.float() / w.float()).pow(2).mean(-1).sqrt()
+    assert (rms - 1.0).abs().max().item() < 1e-2
+    # power-of-two scaling of x leaves the output unchanged up to eps
+    y2 = abi.rmsnorm_fwd(x * 4, w, 1e-6)
+    assert (y.float() - y2.float()).abs().max().item() <= 2e-2
+
+
+def test_config3_swiglu_full_size():
+    gate, up = gen((32768, 14336), 14), gen((32768, 14336), 15)
+    out = abi.swiglu_fwd(gate, up)
+    for rows in (slice(0, 16), slice(32768 - 16, 32768)):
+        want = O.swiglu_fused(gate[rows].cpu(), up[rows].cpu())
+        assert (out[rows].cpu().double() - want.double()).abs().max().item() <= 2e-2
+        assert (out[rows].cpu() == want).float().mean().item() > 0.999
+    # linear in `up` for power-of-two factors, odd in neither; checksum of checksums
+    out2 = abi.swiglu_fwd(gate, up * 2)
+    assert torch.equal(out2, out * 2)
+    comp = abi.swiglu_fwd(gate, up, mode=abi.ROUND_PER_OP)
+    want = O.swiglu_composite(up[:16].cpu(), gate[:16].cpu())
+    assert (comp[:16].cpu().double() - want.double()).abs().max().item() <= 2e-2

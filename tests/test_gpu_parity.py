@@ -1,0 +1,239 @@
+"""GPU parity tests proper: the CUDA kernels, called through the C ABI (ctypes on
+libparas_b200.so with raw device pointers), against the CPU oracle and the committed golden
+vectors of the reference build.
+
+Tolerances (stated by the task): fp32 max-abs 1e-4 (checked as the reference's own
+atol = rtol = 1e-4); bf16 / fp16 max-abs 2e-2 with fp32 accumulation.
+"""
+import math
+
+import pytest
+import torch
+
+from conftest import golden_names, load_golden
+from oracle import oracle as O
+
+import torch_paras  # noqa: F401
+from torch_paras import abi
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def tol_check(got, want, name=""):
+    got = got.detach().cpu()
+    assert got.dtype == want.dtype, f"{name}: dtype {got.dtype} vs {want.dtype}"
+    assert got.shape == want.shape, f"{name}: shape {tuple(got.shape)} vs {tuple(want.shape)}"
+    if want.dtype == torch.float32:
+        ok = torch.allclose(got, want, atol=1e-4, rtol=1e-4, equal_nan=True)
+        err = (got.double() - want.double()).abs().max().item() if got.numel() else 0.0
+        assert ok, f"{name}: fp32 mismatch, max-abs {err:.3e}"
+    else:
+        g, w = got.double(), want.double()
+        assert torch.equal(torch.isnan(g), torch.isnan(w)), f"{name}: NaN pattern differs"
+        err = (g - w).nan_to_num(0.0).abs().max().item() if got.numel() else 0.0
+        assert err <= 2e-2, f"{name}: 16-bit mismatch, max-abs {err:.3e} > 2e-2"
+
+
+def run_cuda(op, a, **kw):
+    c = lambda t: t.to(DEV) if torch.is_tensor(t) else t  # noqa: E731
+    if op == "sdpa":
+        q, k, v = c(a["q"]), c(a["k"]), c(a["v"])
+        return abi.sdpa_fwd(q, k, v, causal=bool(a.get("is_causal", False)), scale=a.get("scale"),
+                            mask=c(a.get("attn_mask")), flags=abi.SDPA_REF_SCALE | kw.get("flags", 0))
+    if op == "rms_norm_aten":
+        x = c(a["x"])
+        n = 1
+        for s in a["normalized_shape"]:
+            n *= s
+        w = c(a["weight"]).reshape(n) if a.get("weight") is not None else None
+        eps = 1e-6 if a.get("eps") is None else a["eps"]
+        return abi.rmsnorm_fwd(x.reshape(-1, n), w, eps, mode=abi.ROUND_PER_OP).reshape(x.shape)
+    if op == "rms_norm_paras":
+        return abi.rmsnorm_fwd(c(a["x"]), c(a["weight"]), a["eps"], return_rstd=True)
+    if op == "rms_norm_paras_backward":
+        return abi.rmsnorm_bwd(c(a["grad_out"]), c(a["x"]), c(a["weight"]), c(a["rstd"]))
+    if op == "swiglu_paras":
+        return abi.swiglu_fwd(c(a["gate"]), c(a["up"]))
+    if op == "swiglu_paras_backward":
+        return abi.swiglu_bwd(c(a["grad_out"]), c(a["gate"]), c(a["up"]))
+    if op == "swiglu_composite":
+        return abi.swiglu_fwd(c(a["gate"]), c(a["x"]), mode=abi.ROUND_PER_OP)
+    if op == "rotate_half":
+        return abi.rotate_half(c(a["x"]))
+    if op == "rotate_half_backward":
+        return abi.rotate_half(c(a["grad_out"]), backward=True)
+    raise AssertionError(op)
+
+
+def as_tuple(x):
+    return x if isinstance(x, tuple) else (x,)
+
+
+@pytest.mark.parametrize("name", golden_names())
+def test_against_reference_golden_vectors(name):
+    g = load_golden(name)
+    got = as_tuple(run_cuda(g["op"], g["args"]))
+    want = as_tuple(g["out"])
+    for i, (a, b) in enumerate(zip(got, want)):
+        tol_check(a, b, f"{name}[{i}]")
+
+
+def _qkv(B, Hq, Hkv, Lq, Lk, D, dtype, seed):
+    g = torch.Generator().manual_seed(seed)
+    q = torch.randn(B, Hq, Lq, D, generator=g).to(dtype)
+    k = torch.randn(B, Hkv, Lk, D, generator=g).to(dtype)
+    v = torch.randn(B, Hkv, Lk, D, generator=g).to(dtype)
+    return q, k, v
+
+
+SDPA_CASES = [
+    # B, Hq, Hkv, Lq,  Lk,  D,  causal
+    (1, 2, 2, 256, 256, 128, True),     # exactly one CTA of two query tiles
+    (2, 4, 4, 512, 512, 128, True),
+    (1, 8, 2, 640, 640, 128, True),     # GQA 4:1, odd number of query tiles
+    (1, 4, 1, 300, 300, 128, True),     # ragged: not a multiple of any tile
+    (1, 2, 2, 384, 384, 128, False),    # full attention
+    (1, 2, 2, 200, 456, 128, False),    # Lq != Lk, ragged
+    (1, 2, 2, 130, 400, 128, True),     # causal with Lk > Lq: top-left alignment
+    (1, 2, 2, 400, 130, 128, True),     # causal with Lk < Lq
+    (2, 8, 2, 1, 700, 128, False),      # decode step, GQA
+    (1, 4, 4, 7, 260, 128, False),      # a few query rows
+    (1, 2, 2, 129, 129, 64, True),      # D = 64
+    (1, 3, 1, 50, 77, 32, False),       # small D, GQA 3:1
+]
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("case", SDPA_CASES)
+def test_sdpa_against_oracle(case, dtype):
+    B, Hq, Hkv, Lq, Lk, D, causal = case
+    q, k, v = _qkv(B, Hq, Hkv, Lq, Lk, D, dtype, seed=hash(case) % 10000)
+    want = O.sdpa(q, k, v, is_causal=causal, enable_gqa=Hq != Hkv)
+    got = abi.sdpa_fwd(q.to(DEV), k.to(DEV), v.to(DEV), causal=causal, flags=abi.SDPA_REF_SCALE)
+    tol_check(got, want, f"sdpa {case} {dtype} [{abi.sdpa_last_kernel()}]")
+
+
+def test_tensor_core_kernel_is_the_one_that_runs():
+    q, k, v = _qkv(1, 2, 2, 512, 512, 128, torch.bfloat16, 5)
+    abi.sdpa_fwd(q.to(DEV), k.to(DEV), v.to(DEV), causal=True)
+    assert abi.sdpa_last_kernel() == "tcgen05"
+    q32 = q.float()
+    abi.sdpa_fwd(q32.to(DEV), k.float().to(DEV), v.float().to(DEV), causal=True)
+    assert abi.sdpa_last_kernel().startswith("simt")
+
+
+def test_sdpa_simt_and_tensor_kernels_agree():
+    q, k, v = _qkv(1, 4, 2, 700, 700, 128, torch.bfloat16, 11)
+    qd, kd, vd = q.to(DEV), k.to(DEV), v.to(DEV)
+    a = abi.sdpa_fwd(qd, kd, vd, causal=True)
+    b = abi.sdpa_fwd(qd, kd, vd, causal=True, flags=abi.SDPA_FORCE_SIMT)
+    assert (a.float() - b.float()).abs().max().item() <= 2e-2
+
+
+def test_sdpa_strided_inputs_and_lse():
+    # [B, L, H, D] storage viewed as [B, H, L, D]: what a fused QKV projection produces
+    g = torch.Generator().manual_seed(3)
+    qs = torch.randn(2, 300, 4, 128, generator=g).bfloat16()
+    ks = torch.randn(2, 300, 4, 128, generator=g).bfloat16()
+    vs = torch.randn(2, 300, 4, 128, generator=g).bfloat16()
+    q, k, v = (t.transpose(1, 2) for t in (qs, ks, vs))
+    want = O.sdpa(q, k, v, is_causal=True)
+    got, lse = abi.sdpa_fwd(qs.to(DEV).transpose(1, 2), ks.to(DEV).transpose(1, 2),
+                            vs.to(DEV).transpose(1, 2), causal=True, return_lse=True,
+                            flags=abi.SDPA_REF_SCALE)
+    tol_check(got, want, "strided sdpa")
+    sc = float(torch.tensor(1 / math.sqrt(128)).bfloat16())
+    s = (q.float() @ k.float().transpose(-1, -2)) * sc
+    s = s.masked_fill(~torch.ones(300, 300, dtype=torch.bool).tril(), float("-inf"))
+    assert torch.allclose(lse.cpu(), torch.logsumexp(s, -1), atol=2e-3, rtol=2e-3)
+
+
+def test_sdpa_empty_and_degenerate_shapes():
+    z = torch.empty(1, 2, 0, 128, dtype=torch.bfloat16, device=DEV)
+    kv = torch.randn(1, 2, 16, 128, device=DEV).bfloat16()
+    assert abi.sdpa_fwd(z, kv, kv).shape == (1, 2, 0, 128)
+    q = torch.randn(1, 2, 4, 128, device=DEV).bfloat16()
+    no_keys = torch.empty(1, 2, 0, 128, dtype=torch.bfloat16, device=DEV)
+    out = abi.sdpa_fwd(q, no_keys, no_keys)          # softmax over nothing, times nothing = 0
+    assert torch.equal(out.cpu(), torch.zeros(1, 2, 4, 128, dtype=torch.bfloat16))
+    # a row whose keys are all masked out is NaN in the reference too
+    mask = torch.ones(1, 1, 4, 16, dtype=torch.bool)
+    mask[0, 0, 2] = False
+    want = O.sdpa(q.cpu(), kv.cpu(), kv.cpu(), attn_mask=mask)
+    got = abi.sdpa_fwd(q, kv, kv, mask=mask.to(DEV), flags=abi.SDPA_REF_SCALE)
+    tol_check(got, want, "fully masked row")
+    with pytest.raises(RuntimeError, match="mutually exclusive"):
+        abi.sdpa_fwd(q, kv, kv, causal=True, mask=mask.to(DEV))
+    with pytest.raises(RuntimeError, match="multiple of key/value heads"):
+        abi.sdpa_fwd(torch.randn(1, 5, 4, 8, device=DEV), torch.randn(1, 2, 4, 8, device=DEV),
+                     torch.randn(1, 2, 4, 8, device=DEV))
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32, torch.float16])
+@pytest.mark.parametrize("shape", [(64, 4096), (33, 1024), (7, 100), (3, 8200), (5, 24), (0, 16), (130, 256)])
+def test_rmsnorm_both_entry_points_against_oracle(shape, dtype):
+    g = torch.Generator().manual_seed(shape[0] * 131 + shape[1])
+    x = torch.randn(*shape, generator=g).to(dtype)
+    w = (1 + 0.1 * torch.randn(shape[1], generator=g)).to(dtype)
+    y, rstd = abi.rmsnorm_fwd(x.to(DEV), w.to(DEV), 1e-6, return_rstd=True)
+    yo, ro = O.rms_norm_fused(x, w, 1e-6)
+    tol_check(y, yo, "paras::rms_norm")
+    assert torch.allclose(rstd.cpu(), ro, atol=1e-6, rtol=1e-5)
+    if dtype != torch.float32 and shape[0]:
+        frac = (y.cpu() == yo).float().mean().item()
+        assert frac > 0.999, f"fused RMSNorm only {frac:.4f} bit-exact"
+    yc = abi.rmsnorm_fwd(x.to(DEV), w.to(DEV), 1e-6, mode=abi.ROUND_PER_OP)
+    tol_check(yc, O.rms_norm_composite(x, [shape[1]], w, 1e-6), "aten::rms_norm")
+    yn = abi.rmsnorm_fwd(x.to(DEV), None, 1e-5, mode=abi.ROUND_PER_OP)
+    tol_check(yn, O.rms_norm_composite(x, [shape[1]], None, 1e-5), "aten::rms_norm no weight")
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32, torch.float16])
+@pytest.mark.parametrize("n", [(128, 14336), (17, 77), (1, 1), (0, 4), (3, 1000003)])
+def test_swiglu_both_entry_points_against_oracle(n, dtype):
+    g = torch.Generator().manual_seed(n[0] + n[1])
+    gate = torch.randn(*n, generator=g).to(dtype)
+    up = torch.randn(*n, generator=g).to(dtype)
+    tol_check(abi.swiglu_fwd(gate.to(DEV), up.to(DEV)), O.swiglu_fused(gate, up), "paras::swiglu")
+    tol_check(abi.swiglu_fwd(gate.to(DEV), up.to(DEV), mode=abi.ROUND_PER_OP),
+              O.swiglu_composite(up, gate), "torch_paras::swiglu")
+    if dtype == torch.bfloat16 and gate.numel():
+        frac = (abi.swiglu_fwd(gate.to(DEV), up.to(DEV)).cpu() == O.swiglu_fused(gate, up)).float().mean().item()
+        assert frac > 0.999
+
+
+def test_swiglu_unaligned_pointers_take_the_scalar_path():
+    g = torch.Generator().manual_seed(4)
+    gate = torch.randn(4099, generator=g).bfloat16()
+    up = torch.randn(4099, generator=g).bfloat16()
+    gd, ud = gate.to(DEV)[1:], up.to(DEV)[1:]          # 2-byte offset: not 16-byte aligned
+    out = torch.empty_like(gd)
+    abi.swiglu_fwd(gd, ud, out=out)
+    tol_check(out, O.swiglu_fused(gate[1:], up[1:]), "unaligned swiglu")
+
+
+def test_backward_ops_and_rotate_half_against_oracle():
+    g = torch.Generator().manual_seed(8)
+    for dtype in (torch.float32, torch.bfloat16):
+        x = torch.randn(37, 200, generator=g).to(dtype)
+        w = (1 + 0.1 * torch.randn(200, generator=g)).to(dtype)
+        go = torch.randn(37, 200, generator=g).to(dtype)
+        _, rstd = O.rms_norm_fused(x, w, 1e-6)
+        gx, gw = abi.rmsnorm_bwd(go.to(DEV), x.to(DEV), w.to(DEV), rstd.to(DEV))
+        gxo, gwo = O.rms_norm_fused_backward(go, x, w, rstd)
+        tol_check(gx, gxo, "rms_norm_backward dx")
+        if dtype == torch.float32:
+            tol_check(gw, gwo, "rms_norm_backward dw")
+        else:
+            assert (gw.cpu().double() - gwo.double()).abs().max().item() <= 2e-2 * max(1.0, gwo.abs().max().item())
+        gate = torch.randn(19, 33, generator=g).to(dtype)
+        up = torch.randn(19, 33, generator=g).to(dtype)
+        d = torch.randn(19, 33, generator=g).to(dtype)
+        gg, gu = abi.swiglu_bwd(d.to(DEV), gate.to(DEV), up.to(DEV))
+        ggo, guo = O.swiglu_fused_backward(d, gate, up)
+        tol_check(gg, ggo, "swiglu_backward dgate")
+        tol_check(gu, guo, "swiglu_backward dup")
+        r = torch.randn(5, 64, generator=g).to(dtype)
+        assert torch.equal(abi.rotate_half(r.to(DEV)).cpu(), O.rotate_half(r))
+        assert torch.equal(abi.rotate_half(r.to(DEV), backward=True).cpu(), O.rotate_half_backward(r))
