@@ -436,6 +436,11 @@ int paras_b200_host_alloc(size_t bytes, void** ptr) {
     return PARAS_OK;
 }
 
+int paras_b200_host_is_pinned(const void* ptr) {
+    if (!ptr || paras_b200_device_count() == 0) return 0;
+    return pb::host_ptr_is_pinned(ptr) ? 1 : 0;
+}
+
 int paras_b200_host_free(void* ptr) {
     if (!ptr) return PARAS_OK;
     PB_CUDA(cudaFreeHost(ptr));

@@ -113,10 +113,38 @@ struct GuardImpl final : public c10::impl::DeviceGuardImplInterface {
 GuardImpl g_guard;
 c10::impl::DeviceGuardImplRegistrar g_guard_registrar(kDevice, &g_guard);
 
+// Page-locked host memory (`tensor.pin_memory()`, `torch.empty(..., pin_memory=True)`): the
+// source/destination of direct DMA transfers; pageable tensors go through the library's
+// own pinned staging ring instead.
+void delete_pinned(void* ptr) {
+    if (ptr) paras_b200_host_free(ptr);
+}
+
+class PinnedAllocator final : public c10::Allocator {
+public:
+    c10::DataPtr allocate(size_t nbytes) override {
+        void* p = nullptr;
+        if (nbytes) PARAS_ABI(paras_b200_host_alloc(nbytes, &p));
+        return c10::DataPtr(p, p, &delete_pinned, c10::Device(c10::kCPU));
+    }
+    c10::DeleterFnPtr raw_deleter() const override { return &delete_pinned; }
+    void copy_data(void* dest, const void* src, std::size_t count) const override {
+        std::memcpy(dest, src, count);
+    }
+};
+
+PinnedAllocator g_pinned_allocator;
+
 struct Hooks final : public at::PrivateUse1HooksInterface {
+    bool isBuilt() const override { return true; }
+    bool isAvailable() const override { return Runtime::get().device_count() > 0; }
     bool hasPrimaryContext(c10::DeviceIndex index) const override {
         return index >= 0 && index < Runtime::get().device_count();
     }
+    bool isPinnedPtr(const void* data) const override {
+        return paras_b200_host_is_pinned(data) != 0;
+    }
+    c10::Allocator* getPinnedMemoryAllocator() const override { return &g_pinned_allocator; }
 };
 
 struct HooksRegistrar {

@@ -27,6 +27,7 @@ EXPORTS = [
     "paras_b200_free_async", "paras_b200_pool_stats", "paras_b200_pool_trim",
     "paras_b200_memcpy_h2d", "paras_b200_memcpy_d2h", "paras_b200_memcpy_d2d",
     "paras_b200_memcpy_peer", "paras_b200_memset", "paras_b200_host_alloc", "paras_b200_host_free",
+    "paras_b200_host_is_pinned",
     "paras_b200_strided_copy", "paras_b200_fill", "paras_b200_sdpa_fwd",
     "paras_b200_sdpa_workspace_bytes", "paras_b200_sdpa_last_kernel", "paras_b200_rmsnorm_fwd",
     "paras_b200_rmsnorm_bwd", "paras_b200_swiglu_fwd", "paras_b200_swiglu_bwd",
@@ -80,6 +81,7 @@ def lib() -> C.CDLL:
         L.paras_b200_stream.argtypes = [C.c_int, C.POINTER(C.c_void_p)]
         L.paras_b200_host_alloc.argtypes = [C.c_size_t, C.POINTER(C.c_void_p)]
         L.paras_b200_host_free.argtypes = [C.c_void_p]
+        L.paras_b200_host_is_pinned.argtypes = [C.c_void_p]
         _lib = L
     return _lib
 
@@ -96,11 +98,16 @@ def dtype_code(t: torch.Tensor) -> int:
         raise RuntimeError(f"paras: unsupported dtype {t.dtype}") from None
 
 
+_LEGACY_DEFAULT_STREAM = 1  # cudaStreamLegacy: a NULL stream argument means "the library's own"
+
+
 def _stream_of(t: torch.Tensor, stream) -> int:
+    """The stream the launch goes to: torch's current stream of the tensor's device, so that
+    the kernel is ordered with the torch work that produced its inputs and reads its outputs."""
     if stream is not None:
         return int(stream)
     if t.is_cuda:
-        return int(torch.cuda.current_stream(t.device).cuda_stream)
+        return int(torch.cuda.current_stream(t.device).cuda_stream) or _LEGACY_DEFAULT_STREAM
     return 0
 
 
@@ -160,10 +167,8 @@ def sdpa_fwd(q, k, v, *, causal=False, scale=None, mask=None, return_lse=False, 
 
 
 def sdpa_workspace_bytes(q, k, v, *, causal=False, flags=0) -> int:
-    out = torch.empty(0, dtype=q.dtype, device=q.device)
     a = sdpa_args(q, k, v, q, causal=causal, flags=flags)
     n = C.c_size_t(0)
-    del out
     check(lib().paras_b200_sdpa_workspace_bytes(C.byref(a), C.byref(n)))
     return int(n.value)
 

@@ -87,6 +87,8 @@ int paras_b200_memset(int gpu, void* dst, int value, size_t bytes, void* stream)
 /* Pinned host memory for callers that stage their own transfers. */
 int paras_b200_host_alloc(size_t bytes, void** ptr);
 int paras_b200_host_free(void* ptr);
+/* 1 when `ptr` points into pinned (page-locked) host memory known to CUDA, else 0. */
+int paras_b200_host_is_pinned(const void* ptr);
 
 /* Strided copy with element conversion between f32/bf16/f16/f64/i64/i32/i16/i8/u8/bool
  * (the device<->device branch of _copy_from, csrc/ops/tensor_ops.cpp:252-330, and
