@@ -12,6 +12,7 @@
 // D with q broadcast from shared memory), the chunk's max/sum are warp reductions, and
 // the P*V update gives lane l the output dims l, l+32, ... so V rows are read coalesced.
 #include <cfloat>
+#include <mutex>
 
 #include "sdpa_common.cuh"
 
@@ -255,3 +256,109 @@ int sdpa_combine_launch(Gpu* g, const paras_sdpa_args& a, const SplitWorkspace& 
 }
 
 }  // namespace pb
+
+// ---------------------------------------------------------------------------------------
+// paras_b200_sdpa_fwd_static_scratch: the split-KV CUDA-core kernel above, with its partial
+// results kept in a fixed array inside this library instead of allocated memory.
+//
+// Some callers cannot allocate device memory at the moment they need attention: a serving
+// process whose own memory manager claimed the whole GPU at start-up (a cudaMalloc from
+// inside a request then fails or stalls behind an implicit synchronisation), or a decode loop
+// with a latency budget that has no room for an allocator call.  For them this entry point
+// allocates nothing -- no cudaMalloc/cudaFree, no pool, no stream or event creation: the
+// scratch is the file-scope device array below (held by every GPU that loads the library,
+// until the process exits), the launch goes to the caller's stream.
+//
+// The array's name is only a host-side handle; its device address is looked up once per
+// GPU, with that GPU current, by cudaGetSymbolAddress, and that pointer is what the kernel
+// gets.  The look-up happens inside the first call on each GPU, so make that first call
+// outside any stream capture.  All calls share the one array and it keeps whatever the last
+// call left: the kernel overwrites every partial it later reads, so nothing needs clearing,
+// but two calls that overlap on the GPU (different streams) race on it.
+namespace pb {
+namespace {
+
+constexpr size_t kStaticScratchBytes = size_t(4) << 20;  // 4 MiB
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+constexpr int kMaxGpus = 64;
+std::mutex g_scratch_mu;
+void* g_scratch_ptr[kMaxGpus] = {nullptr};
+
+int static_scratch_for(int gpu, void** out) {
+    std::lock_guard<std::mutex> lk(g_scratch_mu);
+    if (!g_scratch_ptr[gpu]) {
+        void* p = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);  // `gpu` is current
+        if (e != cudaSuccess || !p)
+            return fail(PARAS_E_CUDA, "paras sdpa: cudaGetSymbolAddress for the static scratch failed: %s",
+                        cudaGetErrorString(e));
+        g_scratch_ptr[gpu] = p;
+    }
+    *out = g_scratch_ptr[gpu];
+    return PARAS_OK;
+}
+
+}  // namespace
+}  // namespace pb
+
+extern "C" int paras_b200_sdpa_static_scratch_bytes(void) { return int(pb::kStaticScratchBytes); }
+
+extern "C" int paras_b200_sdpa_fwd_static_scratch(const paras_sdpa_args* a) {
+    using pb::fail;
+    if (!a) return fail(PARAS_E_INVALID, "paras sdpa: null argument block");
+    if (a->dtype != PARAS_F32 && a->dtype != PARAS_BF16 && a->dtype != PARAS_F16)
+        return fail(PARAS_E_UNSUPPORTED, "paras sdpa: unsupported dtype %d", a->dtype);
+    if (a->B < 0 || a->Hq < 0 || a->Hkv < 0 || a->Lq < 0 || a->Lk < 0 || a->D < 0)
+        return fail(PARAS_E_INVALID, "paras sdpa: negative dimension");
+    if (a->Hkv == 0 ? a->Hq != 0 : (a->Hq % a->Hkv) != 0)
+        return fail(PARAS_E_INVALID,
+                    "paras sdpa: query heads must be a multiple of key/value heads for enable_gqa");
+    if (a->causal && a->mask)
+        return fail(PARAS_E_INVALID, "paras sdpa: is_causal and attn_mask are mutually exclusive");
+    if (a->mask && (a->mask_kind < 1 || a->mask_kind > 3))
+        return fail(PARAS_E_INVALID, "paras sdpa: bad mask kind %d", a->mask_kind);
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || count == 0) {
+        cudaGetLastError();
+        return fail(PARAS_E_NODEVICE, "paras_b200: no CUDA GPU is visible; this build has no CPU fallback");
+    }
+    if (a->gpu < 0 || a->gpu >= count || a->gpu >= pb::kMaxGpus)
+        return fail(PARAS_E_INVALID, "paras_b200: gpu ordinal %d out of range [0,%d)", a->gpu, count);
+    PB_CUDA(cudaSetDevice(a->gpu));
+    if (int64_t(a->B) * a->Hq * a->Lq * a->D == 0) return PARAS_OK;
+    if (!a->q || !a->out || (a->Lk > 0 && (!a->k || !a->v)))
+        return fail(PARAS_E_INVALID, "paras sdpa: null pointer");
+
+    pb::Gpu g{};  // a plain descriptor: nothing is created or allocated for it
+    g.ordinal = a->gpu;
+    PB_CUDA(cudaDeviceGetAttribute(&g.sm_count, cudaDevAttrMultiProcessorCount, a->gpu));
+    const int splits = pb::sdpa_simt_pick_splits(&g, *a);
+    const int64_t rows = int64_t(a->B) * a->Hq * a->Lq;
+    const size_t need = pb::split_workspace_bytes(rows, a->D, splits);
+    if (need > pb::kStaticScratchBytes)
+        return fail(PARAS_E_INVALID,
+                    "paras sdpa: this problem needs %zu bytes of split-KV scratch but the static "
+                    "scratch holds %zu; use paras_b200_sdpa_fwd with a workspace instead",
+                    need, pb::kStaticScratchBytes);
+    void* scratch = nullptr;
+    if (need) {
+        const int st = pb::static_scratch_for(a->gpu, &scratch);
+        if (st != PARAS_OK) return st;
+    }
+    double sc = a->scale;
+    if (a->flags & PARAS_SDPA_REF_SCALE) {
+        float f = float(sc);
+        if (a->dtype == PARAS_BF16) f = __bfloat162float(__float2bfloat16_rn(f));
+        else if (a->dtype == PARAS_F16) f = __half2float(__float2half_rn(f));
+        sc = f;
+    }
+    // a NULL stream cannot mean "the library's own stream" here (creating one would be an
+    // allocation): it means the legacy default stream
+    cudaStream_t s = a->stream ? static_cast<cudaStream_t>(a->stream) : cudaStreamLegacy;
+    const pb::SplitWorkspace ws = pb::carve_workspace(scratch, rows, a->D, splits);
+    const int st = pb::sdpa_simt_launch(&g, *a, float(sc), ws, s);
+    if (st == PARAS_OK) pb::set_last_kernel(splits > 1 ? "simt_splitkv_static" : "simt");
+    return st;
+}
+

@@ -30,6 +30,7 @@ EXPORTS = [
     "paras_b200_host_is_pinned",
     "paras_b200_strided_copy", "paras_b200_fill", "paras_b200_sdpa_fwd",
     "paras_b200_sdpa_workspace_bytes", "paras_b200_sdpa_last_kernel", "paras_b200_rmsnorm_fwd",
+    "paras_b200_sdpa_fwd_static_scratch", "paras_b200_sdpa_static_scratch_bytes",
     "paras_b200_rmsnorm_bwd", "paras_b200_swiglu_fwd", "paras_b200_swiglu_bwd",
     "paras_b200_rotate_half",
 ]
@@ -63,6 +64,7 @@ def lib() -> C.CDLL:
         L.paras_b200_sdpa_last_kernel.restype = C.c_char_p
         L.paras_b200_sdpa_fwd.argtypes = [C.POINTER(SdpaArgs)]
         L.paras_b200_sdpa_workspace_bytes.argtypes = [C.POINTER(SdpaArgs), C.POINTER(C.c_size_t)]
+        L.paras_b200_sdpa_fwd_static_scratch.argtypes = [C.POINTER(SdpaArgs)]
         L.paras_b200_rmsnorm_fwd.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                              C.c_int64, C.c_int64, C.c_double, C.c_int, C.c_int, C.c_void_p]
         L.paras_b200_rmsnorm_bwd.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
@@ -164,6 +166,19 @@ def sdpa_fwd(q, k, v, *, causal=False, scale=None, mask=None, return_lse=False, 
                   workspace=workspace, stream=stream)
     check(lib().paras_b200_sdpa_fwd(C.byref(a)))
     return (out, lse) if return_lse else out
+
+
+def sdpa_fwd_static_scratch(q, k, v, *, causal=False, scale=None, mask=None, flags=0, out=None,
+                            stream=None):
+    """Attention through ``paras_b200_sdpa_fwd_static_scratch``: for callers that must not
+    allocate device memory while they run (the split-KV scratch is a fixed array inside the
+    library).  ``out`` should be passed in by such a caller; it is only created here when
+    omitted."""
+    if out is None:
+        out = torch.empty(q.shape, dtype=q.dtype, device=q.device)
+    a = sdpa_args(q, k, v, out, causal=causal, scale=scale, mask=mask, flags=flags, stream=stream)
+    check(lib().paras_b200_sdpa_fwd_static_scratch(C.byref(a)))
+    return out
 
 
 def sdpa_workspace_bytes(q, k, v, *, causal=False, flags=0) -> int:

@@ -156,6 +156,19 @@ int paras_b200_sdpa_workspace_bytes(const paras_sdpa_args* args, size_t* bytes);
  * ("tcgen05", "simt", "decode_mma", ...); for tests and logs. */
 const char* paras_b200_sdpa_last_kernel(void);
 
+/* No counterpart in the reference.  The same attention, for callers that cannot allocate
+ * device memory when they call -- for example a server whose memory manager claimed the whole
+ * GPU at start-up, or a latency-bound decode loop: this entry point calls no cudaMalloc /
+ * cudaFree and creates no pool, stream or event.  It always runs the CUDA-core (split-KV)
+ * kernel; the split-KV partial results live in a fixed device array inside the library
+ * (paras_b200_sdpa_static_scratch_bytes() = 4 MiB, resident on every GPU that loaded the
+ * library until the process exits).  A problem whose partials do not fit is rejected with
+ * PARAS_E_INVALID.  `workspace` is ignored; a NULL `stream` means the legacy default stream.
+ * The first call on each GPU looks up the array's device address; make that call outside
+ * any stream capture.  All calls share the array: calls that overlap on the GPU race. */
+int paras_b200_sdpa_fwd_static_scratch(const paras_sdpa_args* args);
+int paras_b200_sdpa_static_scratch_bytes(void);
+
 /* ---- RMSNorm ----
  * mode PARAS_ROUND_ONCE  = paras::rms_norm (csrc/ops/fused_ops.cpp:43-88): wide
  *      accumulation, one rounding of the result; `rstd` (optional, f32[rows]) receives
