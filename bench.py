@@ -273,60 +273,72 @@ def run_ours(args):
                 "frac_of_nominal_2250": per_gpu_tflops / 2250.0, "traffic": None}
 
     extra = {}
-    if not args.quick:
-        esteps = max(5, min(steps, 20))
+    only = args.only
+    esteps = max(5, min(steps, 20))
+    s3 = max(3, esteps // 4)
 
+    def want(name):
+        return only == name or (only is None and not args.quick)
+
+    def loop_ms(fn, n, w=warmup):
+        return max_over_ranks(timed_loop(fn, n, w, barrier)) / n
+
+    if want("rmsnorm"):
         # RMSNorm, config 2 shape: bytes = 2*rows*H*2 + H*2
         x = gen((16384, 4096), 4)
         w = gen((4096,), 5, mean=1.0, std=0.1)
         y = torch.empty_like(x)
-        rstd = None
-        t = max_over_ranks(timed_loop(lambda: abi.rmsnorm_fwd(x, w, 1e-6, out=y), esteps, warmup, barrier)) / esteps
         nbytes = 2 * x.numel() * 2 + w.numel() * 2
-        gbs = nbytes / (t * 1e-3) / 1e9
-        extra["rmsnorm_fused_16384x4096"] = {"ms": t, "gbs": gbs, "frac_of_hbm_peak": gbs / peaks["hbm_gbs"],
-                                             "bytes": nbytes}
-        t = max_over_ranks(timed_loop(lambda: abi.rmsnorm_fwd(x, w, 1e-6, out=y, mode=abi.ROUND_PER_OP),
-                                      esteps, warmup, barrier)) / esteps
-        gbs = nbytes / (t * 1e-3) / 1e9
-        extra["rmsnorm_aten_16384x4096"] = {"ms": t, "gbs": gbs, "frac_of_hbm_peak": gbs / peaks["hbm_gbs"],
-                                            "bytes": nbytes}
-        del x, y, rstd
+        for key, mode in (("rmsnorm_fused_16384x4096", abi.ROUND_ONCE), ("rmsnorm_aten_16384x4096", abi.ROUND_PER_OP)):
+            t = loop_ms(lambda: abi.rmsnorm_fwd(x, w, 1e-6, out=y, mode=mode), esteps)
+            gbs = nbytes / (t * 1e-3) / 1e9
+            extra[key] = {"ms": t, "gbs": gbs, "frac_of_hbm_peak": gbs / peaks["hbm_gbs"], "bytes": nbytes}
+        del x, y
 
+    if want("swiglu"):
         # SwiGLU, config 3 shape: bytes = 3*n*2
         gate, up = gen((32768, 14336), 6), gen((32768, 14336), 7)
         so = torch.empty_like(gate)
-        t = max_over_ranks(timed_loop(lambda: abi.swiglu_fwd(gate, up, out=so), esteps, warmup, barrier)) / esteps
+        t = loop_ms(lambda: abi.swiglu_fwd(gate, up, out=so), esteps)
         nbytes = 3 * gate.numel() * 2
         gbs = nbytes / (t * 1e-3) / 1e9
         extra["swiglu_32768x14336"] = {"ms": t, "gbs": gbs, "frac_of_hbm_peak": gbs / peaks["hbm_gbs"],
                                        "bytes": nbytes}
         del gate, up, so
 
+    if want("gqa"):
         # config 3 attention: B=4 Hq=64 Hkv=8 S=8192
         q3, k3, v3 = gen((4, 64, 8192, 128), 8), gen((4, 8, 8192, 128), 9), gen((4, 8, 8192, 128), 10)
         o3 = torch.empty_like(q3)
-        s3 = max(3, esteps // 4)
-        t = max_over_ranks(timed_loop(lambda: abi.sdpa_fwd(q3, k3, v3, causal=True, out=o3), s3, 3, barrier)) / s3
+        t = loop_ms(lambda: abi.sdpa_fwd(q3, k3, v3, causal=True, out=o3), s3, 3)
         f3 = sdpa_flops(4, 64, 8192, 8192, 128, True)
         tf = f3 / (t * 1e-3) / 1e12
         extra["sdpa_gqa_B4_Hq64_Hkv8_S8192"] = {"ms": t, "tflops": tf, "frac_of_bf16_peak": tf / peaks["bf16_tflops"],
                                                  "kernel": abi.sdpa_last_kernel()}
         del q3, k3, v3, o3
 
+    if want("decode"):
         # config 4 decode: bytes = K + V (once per kv head) + q + o
         qd, kd, vd = gen((64, 32, 1, 128), 11), gen((64, 8, 32768, 128), 12), gen((64, 8, 32768, 128), 13)
         od = torch.empty_like(qd)
         ws_bytes = abi.sdpa_workspace_bytes(qd, kd, vd)
         ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=dev)
-        t = max_over_ranks(timed_loop(lambda: abi.sdpa_fwd(qd, kd, vd, out=od, workspace=ws if ws_bytes else None),
-                                      s3, 3, barrier)) / s3
+        t = loop_ms(lambda: abi.sdpa_fwd(qd, kd, vd, out=od, workspace=ws if ws_bytes else None), s3, 3)
         nbytes = (kd.numel() + vd.numel() + qd.numel() + od.numel()) * 2
         gbs = nbytes / (t * 1e-3) / 1e9
         extra["sdpa_decode_B64_kv32768"] = {"ms": t, "gbs": gbs, "frac_of_hbm_peak": gbs / peaks["hbm_gbs"],
                                             "bytes": nbytes, "kernel": abi.sdpa_last_kernel()}
         del qd, kd, vd, od, ws
-        torch.cuda.empty_cache()
+    torch.cuda.empty_cache()
+
+    if only:
+        if rank == 0:
+            print(json.dumps({"only": only, "n_gpus": world, "headline_sdpa_tflops": tflops, "extra": extra}),
+                  flush=True)
+        if dist is not None:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
 
     # ---------------- e2e: public operator on the paras device, host buffers ----------------
     pdev = f"paras:{local + 1}"
@@ -387,6 +399,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--quick", action="store_true", help="headline + e2e only")
+    ap.add_argument("--only", choices=["rmsnorm", "swiglu", "gqa", "decode"],
+                    help="after the headline loop run just this extra workload and print it (for profiling)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-repeat", type=int, default=3)
     args = ap.parse_args()

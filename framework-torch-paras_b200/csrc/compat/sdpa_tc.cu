@@ -55,13 +55,15 @@ constexpr int kSmemQ = 0;
 constexpr int kSmemKV = kTilesPerCta * kTileBytes;
 constexpr int kSmemBars = kSmemKV + kStages * kTileBytes;
 // barrier indices
-constexpr int kBarQFull = 0;                      // [2]
-constexpr int kBarKVFull = 2;                     // [kStages]
-constexpr int kBarKVEmpty = kBarKVFull + kStages; // [kStages]
-constexpr int kBarSFull = kBarKVEmpty + kStages;  // [2]
-constexpr int kBarPFull = kBarSFull + 2;          // [2]
-constexpr int kBarOFull = kBarPFull + 2;          // [2]
-constexpr int kNumBars = kBarOFull + 2;
+constexpr int kBarQFull = 0;                       // [2]  TMA -> MMA: Q tile landed
+constexpr int kBarQEmpty = 2;                      // [2]  MMA -> TMA: last QK^T of the item is done
+constexpr int kBarKVFull = 4;                      // [kStages]
+constexpr int kBarKVEmpty = kBarKVFull + kStages;  // [kStages]
+constexpr int kBarSFull = kBarKVEmpty + kStages;   // [2]  MMA -> softmax: S_t ready
+constexpr int kBarPFull = kBarSFull + 2;           // [2]  softmax -> MMA: P_t written, O_t rescaled
+constexpr int kBarOFull = kBarPFull + 2;           // [2]  MMA -> softmax: last PV of the item is done
+constexpr int kBarOEmpty = kBarOFull + 2;          // [2]  softmax -> MMA: O_t has been read out
+constexpr int kNumBars = kBarOEmpty + 2;
 constexpr int kSmemMisc = kSmemBars + kNumBars * 8;   // tmem base word, abort flag
 constexpr int kSmemTotal = kSmemMisc + 16;
 constexpr int kSmemLaunch = kSmemTotal + 1024;        // slack to align the base to 1024 B
@@ -79,6 +81,17 @@ struct TcParams {
     float scale;
     float scale_log2;
     int* status;
+    int nq;      // 256-row query blocks per (batch, head)
+    int npair;   // ceil(nq / 2)
+    int units;   // B * Hq * npair
+};
+
+// One work item = one 256-row query block of one (batch, head).
+struct Item {
+    int b, h, hk;
+    int start[2];  // first query row of each 128-row tile
+    int ntile[2];  // kv tiles each query tile visits (0 = tile is past the end of the sequence)
+    int n;         // max of the two
 };
 
 __device__ __forceinline__ int kv_tiles_for(const TcParams& p, int start) {
@@ -86,6 +99,32 @@ __device__ __forceinline__ int kv_tiles_for(const TcParams& p, int start) {
     int last = p.Lk;
     if (p.causal) last = min(last, min(p.Lq, start + BM));  // keys 0..row
     return (last + BN - 1) / BN;
+}
+
+// Static persistent schedule.  A unit pairs the query blocks (nq-1-pair) and (pair) of one
+// head: under a causal mask their kv-tile counts add up to the same total for every pair,
+// so handing out units round-robin keeps the CTAs balanced without an atomic work queue,
+// and the query blocks of one head (and the heads of one GQA group, which are adjacent
+// units) run at the same time, so their K/V tiles are L2 hits.
+// `seq` counts items of this CTA: unit = blockIdx.x + (seq/2)*gridDim.x, half = seq & 1.
+__device__ __forceinline__ bool get_item(const TcParams& p, int seq, Item* it) {
+    const int unit = int(blockIdx.x) + (seq >> 1) * int(gridDim.x);
+    if (unit >= p.units) return false;
+    const int hb = unit / p.npair;
+    const int pair = unit - hb * p.npair;
+    const int hi = p.nq - 1 - pair;
+    const int qblk = (seq & 1) ? pair : hi;
+    it->b = hb / p.Hq;
+    it->h = hb - it->b * p.Hq;
+    it->hk = it->h / (p.Hq / p.Hkv);
+    const bool dup = (seq & 1) && pair == hi;  // odd block count: the middle block has no partner
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+        it->start[t] = qblk * (kTilesPerCta * BM) + t * BM;
+        it->ntile[t] = dup ? 0 : kv_tiles_for(p, it->start[t]);
+    }
+    it->n = max(it->ntile[0], it->ntile[1]);
+    return true;
 }
 
 template <bool BF16>
@@ -100,23 +139,12 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + kSmemMisc + 4);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int qblk = int(gridDim.x) - 1 - int(blockIdx.x);  // longest (latest) rows first
-    const int h = blockIdx.y, b = blockIdx.z;
-    const int hk = h / (p.Hq / p.Hkv);
-    const int q0 = qblk * (kTilesPerCta * BM);
-    int start[2], ntile[2];
-#pragma unroll
-    for (int t = 0; t < 2; ++t) {
-        start[t] = q0 + t * BM;
-        ntile[t] = kv_tiles_for(p, start[t]);
-    }
-    const int n = max(ntile[0], ntile[1]);
     if (*reinterpret_cast<volatile int*>(&g_abort_latch)) return;  // uniform: before any barrier or TMEM use
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < kNumBars; ++i) {
-            const bool pfull = (i >= kBarPFull && i < kBarPFull + 2);
-            mbar_init(bar(i), pfull ? 4u : 1u);
+            const bool four = (i >= kBarPFull && i < kBarPFull + 2) || (i >= kBarOEmpty && i < kBarOEmpty + 2);
+            mbar_init(bar(i), four ? 4u : 1u);  // one arrival per softmax warp, else one commit / TMA
         }
         *abort_flag = 0;
         mbar_fence_init();
@@ -139,27 +167,36 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     if (warp == kLoadWarp) {
         // ------------------------------ TMA producer ------------------------------
         if (lane == 0) {
-#pragma unroll
-            for (int t = 0; t < 2; ++t) {
-                if (ntile[t] > 0) {
-                    mbar_arrive_expect_tx(bar(kBarQFull + t), kTileBytes);
-                    const uint32_t dst = smem_base + kSmemQ + t * kTileBytes;
-                    tma_load_4d(dst, &map_q, bar(kBarQFull + t), 0, start[t], h, b);
-                    tma_load_4d(dst + kChunkBytes, &map_q, bar(kBarQFull + t), 64, start[t], h, b);
-                }
-            }
             bool ok = true;
-            for (int item = 0; ok && item < 2 * n; ++item) {  // K0 V0 K1 V1 ...
-                const int slot = item % kStages;
-                const uint32_t ph = (item / kStages) & 1;
-                ok = mbar_wait(bar(kBarKVEmpty + slot), ph ^ 1u, abort_flag);
-                if (!ok) break;
-                const int j = item >> 1;
-                const CUtensorMap* map = (item & 1) ? &map_v : &map_k;
-                mbar_arrive_expect_tx(bar(kBarKVFull + slot), kTileBytes);
-                const uint32_t dst = smem_base + kSmemKV + slot * kTileBytes;
-                tma_load_4d(dst, map, bar(kBarKVFull + slot), 0, j * BN, hk, b);
-                tma_load_4d(dst + kChunkBytes, map, bar(kBarKVFull + slot), 64, j * BN, hk, b);
+            int ring = 0;              // K/V tiles loaded so far: K0 V0 K1 V1 ... across items
+            uint32_t qcnt[2] = {0, 0};  // items that used query tile t
+            Item it;
+            for (int seq = 0; ok && get_item(p, seq, &it); ++seq) {
+#pragma unroll
+                for (int t = 0; t < 2; ++t) {
+                    if (ok && it.ntile[t] > 0) {
+                        // the previous item's last QK^T on this Q buffer has completed
+                        ok = mbar_wait(bar(kBarQEmpty + t), (qcnt[t] & 1u) ^ 1u, abort_flag);
+                        if (!ok) break;
+                        ++qcnt[t];
+                        mbar_arrive_expect_tx(bar(kBarQFull + t), kTileBytes);
+                        const uint32_t dst = smem_base + kSmemQ + t * kTileBytes;
+                        tma_load_4d(dst, &map_q, bar(kBarQFull + t), 0, it.start[t], it.h, it.b);
+                        tma_load_4d(dst + kChunkBytes, &map_q, bar(kBarQFull + t), 64, it.start[t], it.h, it.b);
+                    }
+                }
+                for (int x = 0; ok && x < 2 * it.n; ++x, ++ring) {
+                    const int slot = ring % kStages;
+                    const uint32_t ph = (ring / kStages) & 1;
+                    ok = mbar_wait(bar(kBarKVEmpty + slot), ph ^ 1u, abort_flag);
+                    if (!ok) break;
+                    const int j = x >> 1;
+                    const CUtensorMap* map = (x & 1) ? &map_v : &map_k;
+                    mbar_arrive_expect_tx(bar(kBarKVFull + slot), kTileBytes);
+                    const uint32_t dst = smem_base + kSmemKV + slot * kTileBytes;
+                    tma_load_4d(dst, map, bar(kBarKVFull + slot), 0, j * BN, it.hk, it.b);
+                    tma_load_4d(dst + kChunkBytes, map, bar(kBarKVFull + slot), 64, j * BN, it.hk, it.b);
+                }
             }
         }
     } else if (warp == kMmaWarp) {
@@ -189,45 +226,65 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                            (acc || ks) ? 1u : 0u);
                 }
             };
-            bool ok = n > 0;
-            if (ok) ok = mbar_wait(bar(kBarKVFull + 0), 0, abort_flag);  // K0
-#pragma unroll
-            for (int t = 0; t < 2; ++t) {
-                if (ok && ntile[t] > 0) {
-                    ok = mbar_wait(bar(kBarQFull + t), 0, abort_flag);
-                    if (ok) {
-                        tc_fence_after_sync();
-                        issue_qk(t, 0);
-                        tc_commit(bar(kBarSFull + t));
-                    }
-                }
-            }
-            if (ok) tc_commit(bar(kBarKVEmpty + 0));
-            for (int j = 0; ok && j < n; ++j) {
-                const int item_v = 2 * j + 1, item_k = 2 * j + 2;
-                const int slot_v = item_v % kStages, slot_k = item_k % kStages;
-                ok = mbar_wait(bar(kBarKVFull + slot_v), (item_v / kStages) & 1, abort_flag);
-                if (ok && j + 1 < n)
-                    ok = mbar_wait(bar(kBarKVFull + slot_k), (item_k / kStages) & 1, abort_flag);
-                if (!ok) break;
+            bool ok = true;
+            int ring = 0;               // ring index of the current item's K0
+            uint32_t qcnt[2] = {0, 0};   // items that used tile t (Q / O barriers)
+            uint32_t pcnt[2] = {0, 0};   // softmax iterations of tile t so far (P barrier)
+            Item it;
+            for (int seq = 0; ok && get_item(p, seq, &it); ++seq) {
+                if (it.n == 0) continue;
+                ok = mbar_wait(bar(kBarKVFull + ring % kStages), (ring / kStages) & 1, abort_flag);  // K0
 #pragma unroll
                 for (int t = 0; t < 2; ++t) {
-                    if (ok && j < ntile[t]) {
-                        ok = mbar_wait(bar(kBarPFull + t), j & 1, abort_flag);
-                        if (!ok) break;
-                        tc_fence_after_sync();
-                        issue_pv(t, slot_v, j > 0);
-                        if (j + 1 < ntile[t]) {
-                            issue_qk(t, slot_k);
+                    if (ok && it.ntile[t] > 0) {
+                        ok = mbar_wait(bar(kBarQFull + t), qcnt[t] & 1u, abort_flag);
+                        if (ok) {
+                            tc_fence_after_sync();
+                            issue_qk(t, ring % kStages);
                             tc_commit(bar(kBarSFull + t));
-                        } else {
-                            tc_commit(bar(kBarOFull + t));
+                            if (it.ntile[t] == 1) tc_commit(bar(kBarQEmpty + t));
                         }
                     }
                 }
                 if (!ok) break;
-                tc_commit(bar(kBarKVEmpty + slot_v));
-                if (j + 1 < n) tc_commit(bar(kBarKVEmpty + slot_k));
+                tc_commit(bar(kBarKVEmpty + ring % kStages));
+                for (int j = 0; ok && j < it.n; ++j) {
+                    const int item_v = ring + 2 * j + 1, item_k = ring + 2 * j + 2;
+                    const int slot_v = item_v % kStages, slot_k = item_k % kStages;
+                    ok = mbar_wait(bar(kBarKVFull + slot_v), (item_v / kStages) & 1, abort_flag);
+                    if (ok && j + 1 < it.n)
+                        ok = mbar_wait(bar(kBarKVFull + slot_k), (item_k / kStages) & 1, abort_flag);
+                    if (!ok) break;
+#pragma unroll
+                    for (int t = 0; t < 2; ++t) {
+                        if (ok && j < it.ntile[t]) {
+                            ok = mbar_wait(bar(kBarPFull + t), pcnt[t] & 1u, abort_flag);
+                            if (!ok) break;
+                            ++pcnt[t];
+                            if (j == 0) {
+                                // the first PV overwrites O_t: the previous item's epilogue has read it
+                                ok = mbar_wait(bar(kBarOEmpty + t), (qcnt[t] & 1u) ^ 1u, abort_flag);
+                                if (!ok) break;
+                            }
+                            tc_fence_after_sync();
+                            issue_pv(t, slot_v, j > 0);
+                            if (j + 1 < it.ntile[t]) {
+                                issue_qk(t, slot_k);
+                                tc_commit(bar(kBarSFull + t));
+                                if (j + 2 == it.ntile[t]) tc_commit(bar(kBarQEmpty + t));
+                            } else {
+                                tc_commit(bar(kBarOFull + t));
+                            }
+                        }
+                    }
+                    if (!ok) break;
+                    tc_commit(bar(kBarKVEmpty + slot_v));
+                    if (j + 1 < it.n) tc_commit(bar(kBarKVEmpty + slot_k));
+                }
+#pragma unroll
+                for (int t = 0; t < 2; ++t)
+                    if (it.ntile[t] > 0) ++qcnt[t];
+                ring += 2 * it.n;
             }
         }
         __syncwarp();
@@ -238,96 +295,118 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         const uint32_t lane_base = uint32_t(wq * 32) << 16;
         const uint32_t s_addr = tmem + lane_base + kColS + t * 128;
         const uint32_t o_addr = tmem + lane_base + kColO + t * 128;
-        const int row_q = start[t] + wq * 32 + lane;
         const float c2 = p.scale_log2;
-        float m = -INFINITY, l = 0.f;
         bool ok = true;
-        for (int j = 0; j < ntile[t]; ++j) {
-            ok = mbar_wait(bar(kBarSFull + t), j & 1, abort_flag);
-            if (!ok) break;
-            tc_fence_after_sync();
-            uint32_t s[BN];
+        uint32_t scnt = 0;  // S tiles consumed so far
+        uint32_t ocnt = 0;  // items finished so far
+        Item it;
+        for (int seq = 0; ok && get_item(p, seq, &it); ++seq) {
+            const int nt = it.ntile[t];
+            if (nt == 0) continue;
+            const int row_q = it.start[t] + wq * 32 + lane;
+            float m = -INFINITY, l = 0.f;
+            for (int j = 0; j < nt; ++j) {
+                ok = mbar_wait(bar(kBarSFull + t), scnt & 1u, abort_flag);
+                if (!ok) break;
+                ++scnt;
+                tc_fence_after_sync();
+                uint32_t s[BN];
 #pragma unroll
-            for (int c = 0; c < 4; ++c)
-                tmem_ld32(s_addr + 32 * c, reinterpret_cast<uint32_t(&)[32]>(s[32 * c]));
-            tmem_wait_ld();
+                for (int c = 0; c < 4; ++c)
+                    tmem_ld32(s_addr + 32 * c, reinterpret_cast<uint32_t(&)[32]>(s[32 * c]));
+                tmem_wait_ld();
 #pragma unroll
-            for (int c = 0; c < 4; ++c) tmem_ld_fence32(reinterpret_cast<uint32_t(&)[32]>(s[32 * c]));
+                for (int c = 0; c < 4; ++c) tmem_ld_fence32(reinterpret_cast<uint32_t(&)[32]>(s[32 * c]));
 
-            const int col0 = j * BN;
-            const bool need_mask = (p.causal && col0 + BN - 1 > start[t]) || (col0 + BN > p.Lk);
-            if (need_mask) {
-                const int limit = (p.causal ? min(row_q, p.Lk - 1) : p.Lk - 1) - col0;
+                const int col0 = j * BN;
+                const bool need_mask = (p.causal && col0 + BN - 1 > it.start[t]) || (col0 + BN > p.Lk);
+                if (need_mask) {
+                    const int limit = (p.causal ? min(row_q, p.Lk - 1) : p.Lk - 1) - col0;
 #pragma unroll
-                for (int i = 0; i < BN; ++i)
-                    if (i > limit) s[i] = 0xff800000u;  // -inf
-            }
-            float mx = __uint_as_float(s[0]);
-#pragma unroll
-            for (int i = 1; i < BN; ++i) mx = fmaxf(mx, __uint_as_float(s[i]));
-
-            float alpha = 1.f;
-            bool grew = false;
-            if (j == 0) {
-                m = mx;
-            } else {
-                const float m_new = fmaxf(m, mx);
-                if ((m_new - m) * c2 > kRescaleThreshold) {
-                    alpha = ex2_approx((m - m_new) * c2);
-                    l *= alpha;
-                    m = m_new;
-                    grew = true;
+                    for (int i = 0; i < BN; ++i)
+                        if (i > limit) s[i] = 0xff800000u;  // -inf
                 }
-            }
-            if (j > 0 && __any_sync(0xffffffffu, grew)) {
-                // PV_t(j-1) has completed (S_t(j) was committed after it) and PV_t(j) waits
-                // for this tile's P barrier, so O_t is quiescent here.
+                float mx0 = __uint_as_float(s[0]), mx1 = __uint_as_float(s[1]);
+                float mx2 = __uint_as_float(s[2]), mx3 = __uint_as_float(s[3]);
+#pragma unroll
+                for (int i = 4; i < BN; i += 4) {
+                    mx0 = fmaxf(mx0, __uint_as_float(s[i]));
+                    mx1 = fmaxf(mx1, __uint_as_float(s[i + 1]));
+                    mx2 = fmaxf(mx2, __uint_as_float(s[i + 2]));
+                    mx3 = fmaxf(mx3, __uint_as_float(s[i + 3]));
+                }
+                const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+
+                float alpha = 1.f;
+                bool grew = false;
+                if (j == 0) {
+                    m = mx;
+                } else {
+                    const float m_new = fmaxf(m, mx);
+                    if ((m_new - m) * c2 > kRescaleThreshold) {
+                        alpha = ex2_approx((m - m_new) * c2);
+                        l *= alpha;
+                        m = m_new;
+                        grew = true;
+                    }
+                }
+                if (j > 0 && __any_sync(0xffffffffu, grew)) {
+                    // PV_t(j-1) has completed (S_t(j) was committed after it) and PV_t(j) waits
+                    // for this tile's P barrier, so O_t is quiescent here.
 #pragma unroll 1
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t o[32];
+                        tmem_ld32(o_addr + 32 * c, o);
+                        tmem_wait_ld();
+                        tmem_ld_fence32(o);
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                        tmem_st32(o_addr + 32 * c, o);
+                    }
+                }
+                const float neg_m = -m * c2;
+                float lsum0 = 0.f, lsum1 = 0.f;
+#pragma unroll
                 for (int c = 0; c < 4; ++c) {
-                    uint32_t o[32];
-                    tmem_ld32(o_addr + 32 * c, o);
-                    tmem_wait_ld();
-                    tmem_ld_fence32(o);
+                    uint32_t pk[16];
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                    tmem_st32(o_addr + 32 * c, o);
+                    for (int i = 0; i < 16; ++i) {
+                        const int e = 32 * c + 2 * i;
+                        const float p0 = ex2_approx(fmaf(__uint_as_float(s[e]), c2, neg_m));
+                        const float p1 = ex2_approx(fmaf(__uint_as_float(s[e + 1]), c2, neg_m));
+                        lsum0 += p0;
+                        lsum1 += p1;
+                        pk[i] = pack16<BF16>(p0, p1);
+                    }
+                    tmem_st16(s_addr + 16 * c, pk);  // P_t over the first 64 columns of S_t
                 }
+                l += lsum0 + lsum1;
+                tmem_wait_st();
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar(kBarPFull + t));
             }
-            const float neg_m = -m * c2;
-            float lsum0 = 0.f, lsum1 = 0.f;
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                uint32_t pk[16];
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const int e = 32 * c + 2 * i;
-                    const float p0 = ex2_approx(fmaf(__uint_as_float(s[e]), c2, neg_m));
-                    const float p1 = ex2_approx(fmaf(__uint_as_float(s[e + 1]), c2, neg_m));
-                    lsum0 += p0;
-                    lsum1 += p1;
-                    pk[i] = pack16<BF16>(p0, p1);
-                }
-                tmem_st16(s_addr + 16 * c, pk);  // P_t over the first 64 columns of S_t
-            }
-            l += lsum0 + lsum1;
-            tmem_wait_st();
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar(kBarPFull + t));
-        }
-        if (ok && ntile[t] > 0) ok = mbar_wait(bar(kBarOFull + t), 0, abort_flag);
-        if (ok && ntile[t] > 0) {
+            if (!ok) break;
+            ok = mbar_wait(bar(kBarOFull + t), ocnt & 1u, abort_flag);
+            if (!ok) break;
+            ++ocnt;
             tc_fence_after_sync();
             const float inv = 1.0f / l;
             const bool live = row_q < p.Lq;
-            uint16_t* orow = static_cast<uint16_t*>(p.out) + int64_t(b) * p.os[0] +
-                             int64_t(h) * p.os[1] + int64_t(live ? row_q : 0) * p.os[2];
+            uint16_t* orow = static_cast<uint16_t*>(p.out) + int64_t(it.b) * p.os[0] +
+                             int64_t(it.h) * p.os[1] + int64_t(live ? row_q : 0) * p.os[2];
 #pragma unroll 1
             for (int c = 0; c < 4; ++c) {
                 uint32_t o[32];
                 tmem_ld32(o_addr + 32 * c, o);
                 tmem_wait_ld();
                 tmem_ld_fence32(o);
+                if (c == 3) {
+                    // O_t is in registers: the next item's first PV may overwrite it
+                    tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar(kBarOEmpty + t));
+                }
                 if (live) {
 #pragma unroll
                     for (int v = 0; v < 4; ++v) {
@@ -341,7 +420,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                 }
             }
             if (p.lse && live)
-                p.lse[(int64_t(b) * p.Hq + h) * p.Lq + row_q] = m * p.scale + logf(l);
+                p.lse[(int64_t(it.b) * p.Hq + it.h) * p.Lq + row_q] = m * p.scale + logf(l);
         }
     }
 
@@ -453,7 +532,13 @@ int sdpa_tc_launch(Gpu* g, const paras_sdpa_args& a, float scale, cudaStream_t s
     p.scale = scale;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.status = g->status_dev;
-    dim3 grid((a.Lq + kTilesPerCta * BM - 1) / (kTilesPerCta * BM), a.Hq, a.B);
+    p.nq = (a.Lq + kTilesPerCta * BM - 1) / (kTilesPerCta * BM);
+    p.npair = (p.nq + 1) / 2;
+    const int64_t units = int64_t(a.B) * a.Hq * p.npair;
+    if (units > INT32_MAX) return fail(PARAS_E_UNSUPPORTED, "paras sdpa: too many work units");
+    p.units = int(units);
+    const int sms = g->sm_count > 0 ? g->sm_count : 148;
+    dim3 grid(unsigned(units < sms ? units : sms));  // persistent: one CTA per SM
     if (a.dtype == PARAS_BF16) {
         PB_CUDA(cudaFuncSetAttribute(sdpa_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      kSmemLaunch));
