@@ -69,7 +69,7 @@ __device__ __forceinline__ T finish(T xv, float inv_f, double inv_d, bool has_w,
 
 // KV = 16-byte vectors per lane (row held in registers).  nvec = H / N vectors per row.
 template <typename T, int MODE, int KV>
-__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+__global__ void __launch_bounds__(kWarpsPerBlock * 32, KV >= 16 ? 5 : 8)
 rmsnorm_fwd_warp_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__ y,
                         float* __restrict__ rstd, int64_t rows, int64_t H, int nvec, double eps) {
     constexpr int N = Vec16<T>::N;
@@ -103,6 +103,14 @@ rmsnorm_fwd_warp_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __r
                     acc += double(part);
                 }
             }
+        }
+        // Keep the row in its packed form across the reduction: without this fence the
+        // compiler keeps the fp32 copies of all elements live as well (twice the registers,
+        // a third of the occupancy).
+#pragma unroll
+        for (int k = 0; k < KV; ++k) {
+            uint4& u = *reinterpret_cast<uint4*>(&v[k]);
+            asm volatile("" : "+r"(u.x), "+r"(u.y), "+r"(u.z), "+r"(u.w));
         }
         acc = warp_sum(acc);
         float inv_f;
@@ -233,8 +241,10 @@ int launch_fwd(Gpu* g, const void* x, const void* w, void* y, float* rstd, int64
     const int64_t nvec = H / N;
     const int sms = g->sm_count > 0 ? g->sm_count : 148;
     if (vec_ok && nvec <= 32 * 16) {
+        // One row per warp and as many small CTAs as there are row groups: the block scheduler
+        // balances them, and every resident warp keeps a whole row (up to 8 KB) in flight.
         int64_t blocks = (rows + kWarpsPerBlock - 1) / kWarpsPerBlock;
-        const int64_t cap = int64_t(sms) * 16;
+        const int64_t cap = int64_t(1) << 30;
         if (blocks > cap) blocks = cap;
         const int kv = int((nvec + 31) / 32);
 #define PB_RMS_LAUNCH(KV)                                                                   \

@@ -114,6 +114,50 @@ def test_sdpa_against_oracle(case, dtype):
     tol_check(got, want, f"sdpa {case} {dtype} [{abi.sdpa_last_kernel()}]")
 
 
+DECODE_CASES = [
+    # B, Hq, Hkv, Lq, Lk, causal
+    (2, 8, 2, 1, 4096, False),      # group of 4, one query position
+    (1, 16, 1, 1, 5000, False),     # 16 query heads on one kv head; cache not a multiple of the tile
+    (3, 8, 4, 2, 1031, False),      # two query positions x group of 2
+    (1, 8, 2, 4, 777, True),        # causal, top-left aligned: position i sees keys 0..i only
+    (1, 4, 4, 3, 9000, False),      # no sharing (group 1), three positions, several key ranges
+    (1, 2, 1, 1, 40000, False),     # long cache, few units: many key ranges per kv head
+]
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("case", DECODE_CASES)
+def test_decode_kernel_against_oracle(case, dtype):
+    B, Hq, Hkv, Lq, Lk, causal = case
+    q, k, v = _qkv(B, Hq, Hkv, Lq, Lk, 128, dtype, seed=Lk)
+    want = O.sdpa(q, k, v, is_causal=causal, enable_gqa=Hq != Hkv)
+    got, lse = abi.sdpa_fwd(q.to(DEV), k.to(DEV), v.to(DEV), causal=causal, flags=abi.SDPA_REF_SCALE,
+                            return_lse=True)
+    assert abi.sdpa_last_kernel() == "decode_mma"
+    tol_check(got, want, f"decode {case} {dtype}")
+    ref = abi.sdpa_fwd(q.to(DEV), k.to(DEV), v.to(DEV), causal=causal, return_lse=True,
+                       flags=abi.SDPA_REF_SCALE | abi.SDPA_FORCE_SIMT)
+    assert torch.allclose(lse, ref[1], atol=2e-3, rtol=2e-3)
+
+
+def test_decode_kernel_strided_cache_and_workspace():
+    # K/V cache stored [B, L, Hkv, D] (token-major, as a paged cache would hand it over)
+    g = torch.Generator().manual_seed(77)
+    ks = torch.randn(2, 3000, 2, 128, generator=g).bfloat16()
+    vs = torch.randn(2, 3000, 2, 128, generator=g).bfloat16()
+    q = torch.randn(2, 8, 1, 128, generator=g).bfloat16()
+    want = O.sdpa(q, ks.transpose(1, 2), vs.transpose(1, 2), enable_gqa=True)
+    kd, vd, qd = ks.to(DEV).transpose(1, 2), vs.to(DEV).transpose(1, 2), q.to(DEV)
+    need = abi.sdpa_workspace_bytes(qd, kd, vd)
+    ws = torch.empty(max(need, 16), dtype=torch.uint8, device=DEV)
+    got = abi.sdpa_fwd(qd, kd, vd, flags=abi.SDPA_REF_SCALE, workspace=ws)
+    assert abi.sdpa_last_kernel() == "decode_mma"
+    tol_check(got, want, "strided decode")
+    if need:
+        with pytest.raises(RuntimeError, match="smaller than"):
+            abi.sdpa_fwd(qd, kd, vd, workspace=ws[:16])
+
+
 def test_tensor_core_kernel_is_the_one_that_runs():
     q, k, v = _qkv(1, 2, 2, 512, 512, 128, torch.bfloat16, 5)
     abi.sdpa_fwd(q.to(DEV), k.to(DEV), v.to(DEV), causal=True)
