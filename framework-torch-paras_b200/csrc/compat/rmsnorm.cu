@@ -67,6 +67,22 @@ __device__ __forceinline__ T finish(T xv, float inv_f, double inv_d, bool has_w,
     }
 }
 
+// Packed 16-bit arithmetic for the per-op-rounding mode: a bf16x2 / f16x2 multiply rounds
+// its exact product once to the 16-bit type, which is precisely what "compute, then cast
+// to the tensor dtype" means for a product of two 16-bit values -- at half an instruction
+// per element instead of a convert/multiply/convert chain.
+template <typename T> struct Packed;
+template <> struct Packed<__nv_bfloat16> {
+    using T2 = __nv_bfloat162;
+    static __device__ __forceinline__ T2 dup(float v) { return __float2bfloat162_rn(v); }
+    static __device__ __forceinline__ float2 unpack(T2 v) { return __bfloat1622float2(v); }
+};
+template <> struct Packed<__half> {
+    using T2 = __half2;
+    static __device__ __forceinline__ T2 dup(float v) { return __float2half2_rn(v); }
+    static __device__ __forceinline__ float2 unpack(T2 v) { return __half22float2(v); }
+};
+
 // KV = 16-byte vectors per lane (row held in registers).  nvec = H / N vectors per row.
 template <typename T, int MODE, int KV>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32, KV >= 16 ? 5 : 8)
@@ -95,6 +111,16 @@ rmsnorm_fwd_warp_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __r
                         const float f = v[k].v[e];
                         acc += (MODE == PARAS_ROUND_ONCE) ? double(f) * double(f) : double(f * f);
                     }
+                } else if constexpr (MODE == PARAS_ROUND_PER_OP) {
+                    using T2 = typename Packed<T>::T2;
+                    const T2* x2 = reinterpret_cast<const T2*>(&v[k]);
+                    float part = 0.f;
+#pragma unroll
+                    for (int e = 0; e < N / 2; ++e) {
+                        const float2 f = Packed<T>::unpack(__hmul2(x2[e], x2[e]));  // pow(2), rounded
+                        part += f.x + f.y;
+                    }
+                    acc += double(part);
                 } else {
                     float part = 0.f;
 #pragma unroll
@@ -125,10 +151,24 @@ rmsnorm_fwd_warp_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __r
                 Vec16<T> wv;
                 if (w) wv = ld16(w + int64_t(i) * N);
                 Vec16<T> o;
+                if constexpr (sizeof(T) == 2 && MODE == PARAS_ROUND_PER_OP) {
+                    using T2 = typename Packed<T>::T2;
+                    const T2 inv2 = Packed<T>::dup(inv_f);  // inv_f is already a value of T
+                    const T2* x2 = reinterpret_cast<const T2*>(&v[k]);
+                    const T2* w2 = reinterpret_cast<const T2*>(&wv);
+                    T2* o2 = reinterpret_cast<T2*>(&o);
 #pragma unroll
-                for (int e = 0; e < N; ++e)
-                    o.v[e] = finish<T, MODE>(v[k].v[e], inv_f, inv_d, w != nullptr,
-                                             w ? wv.v[e] : v[k].v[e]);
+                    for (int e = 0; e < N / 2; ++e) {
+                        T2 t = __hmul2(x2[e], inv2);       // x * inv, rounded
+                        if (w) t = __hmul2(t, w2[e]);      // * weight, rounded
+                        o2[e] = t;
+                    }
+                } else {
+#pragma unroll
+                    for (int e = 0; e < N; ++e)
+                        o.v[e] = finish<T, MODE>(v[k].v[e], inv_f, inv_d, w != nullptr,
+                                                 w ? wv.v[e] : v[k].v[e]);
+                }
                 st16_stream(yr + int64_t(i) * N, o);
             }
         }
