@@ -12,7 +12,9 @@ import os
 
 import torch
 
-_LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "libparas_b200.so")
+# PARAS_B200_LIB points the bindings at another build of the library (e.g. a tuning variant).
+_LIB_PATH = os.environ.get("PARAS_B200_LIB") or os.path.join(
+    os.path.dirname(os.path.abspath(__file__)), "libparas_b200.so")
 
 F32, BF16, F16 = 0, 1, 2
 ROUND_ONCE, ROUND_PER_OP = 0, 1
