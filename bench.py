@@ -375,6 +375,16 @@ def run_ours(args):
         cpu_baseline = {"value": fl * len(times) / sum(times) / 1e12, "unit": "TFLOP/s", "cores": threads,
                         "kind": kind, "sample": sample_desc(), "seconds_per_pass": sum(times) / len(times)}
 
+    gathered = None
+    if dist is not None:
+        # Optional re-assembly of the sharded outputs (outside every timed region): one head of
+        # every rank's output, all-gathered over NCCL.
+        from torch_paras import sharding
+        piece = out[:, :1].contiguous()
+        full = sharding.gather_shards(piece, [piece.shape[0]] * world, dim=0)
+        torch.cuda.synchronize()
+        gathered = list(full.shape)
+
     if rank == 0:
         line = {
             "metric": "sdpa_fwd_tflops", "value": tflops, "unit": "TFLOP/s", "n_gpus": world,
@@ -382,7 +392,8 @@ def run_ours(args):
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": WORKLOAD, "per_gpu_batch": c["B"], "global_batch": c["B"] * world,
                        "l2": "inputs (537 MB per step) larger than the 126 MB L2; no flush",
-                       "sharding": "batch shards, one per rank, no collective on the forward path"},
+                       "sharding": "batch shards, one per rank, no collective on the forward path",
+                       "gathered_output_shape": gathered},
             "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e,
             "gpu_launches": steps, "clocks": clk.summary(), "extra": extra,
         }

@@ -1,0 +1,84 @@
+"""Sharding of the hot path over the GPUs of one box: one process per GPU, no collective on
+the forward path.
+
+Attention is independent per (batch, kv-head group), RMSNorm and SwiGLU per row, so each
+rank takes a contiguous block of units and runs the single-GPU kernels on it.  The only
+exchange the path ever needs is the optional re-assembly of the outputs, an all-gather
+(NCCL over NVLink on GPUs; gloo on CPU for the tests).  The reference has no multi-device
+logic beyond host-bounced copies (csrc/ops/tensor_ops.cpp:313-322); this module is new.
+"""
+from __future__ import annotations
+
+from typing import List, Sequence, Tuple
+
+import torch
+
+
+def shard_bounds(n_units: int, rank: int, world: int) -> Tuple[int, int]:
+    """Contiguous, balanced block of `n_units` for `rank`: the first n % world ranks get one more."""
+    if world < 1 or not 0 <= rank < world:
+        raise ValueError(f"bad rank {rank} for world size {world}")
+    base, extra = divmod(n_units, world)
+    start = rank * base + min(rank, extra)
+    return start, start + base + (1 if rank < extra else 0)
+
+
+def attention_shard(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, rank: int, world: int):
+    """Views of this rank's share of [B, Hq, L, D] / [B, Hkv, L, D] tensors and a description of
+    the share.  Splits along the batch when there are at least `world` batches, otherwise along
+    the kv heads (query heads follow their kv head, so GQA sharing stays inside one GPU)."""
+    B, Hq, Hkv = q.shape[0], q.shape[1], k.shape[1]
+    if Hkv == 0 or Hq % Hkv:
+        raise ValueError("query heads must be a multiple of key/value heads")
+    group = Hq // Hkv
+    if B >= world:
+        lo, hi = shard_bounds(B, rank, world)
+        return q[lo:hi], k[lo:hi], v[lo:hi], ("batch", lo, hi)
+    lo, hi = shard_bounds(Hkv, rank, world)
+    return (q[:, lo * group:hi * group], k[:, lo:hi], v[:, lo:hi], ("kv_head", lo, hi))
+
+
+def rows_shard(x: torch.Tensor, rank: int, world: int):
+    """This rank's block of rows of a [rows, H] (or [..., H]) tensor, split on dim 0."""
+    lo, hi = shard_bounds(x.shape[0], rank, world)
+    return x[lo:hi], (lo, hi)
+
+
+def as_cuda(t: torch.Tensor) -> torch.Tensor:
+    """A torch.cuda tensor aliasing the memory of a contiguous `paras:N` tensor (N >= 1), so
+    that torch.distributed's NCCL backend can send it.  The caller must synchronise the paras
+    device before the CUDA side reads the data."""
+    if t.device.type != "paras" or (t.device.index or 0) < 1:
+        raise ValueError("as_cuda expects a tensor on paras:1..N")
+    if not t.is_contiguous():
+        raise ValueError("as_cuda expects a contiguous tensor")
+    nbytes = t.numel() * t.element_size()
+
+    class _Mem:
+        __cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (t.data_ptr(), False),
+                                    "version": 2}
+
+    raw = torch.as_tensor(_Mem(), device=torch.device("cuda", t.device.index - 1))
+    out = raw.view(t.dtype).view(t.shape)
+    out._paras_owner = t  # keep the paras storage alive as long as the alias
+    return out
+
+
+def gather_shards(local: torch.Tensor, sizes: Sequence[int], dim: int = 0, group=None) -> torch.Tensor:
+    """All-gathers per-rank blocks whose extent along `dim` is `sizes[rank]` and concatenates them.
+    Works on CPU tensors (gloo) and CUDA tensors (NCCL); for `paras` tensors pass `as_cuda(t)`."""
+    import torch.distributed as dist
+    world = dist.get_world_size(group)
+    if len(sizes) != world:
+        raise ValueError("sizes must have one entry per rank")
+    moved = local.movedim(dim, 0).contiguous()
+    biggest = max(sizes)
+    padded = moved
+    if moved.shape[0] != biggest:
+        pad = torch.zeros((biggest - moved.shape[0],) + tuple(moved.shape[1:]), dtype=moved.dtype,
+                          device=moved.device)
+        padded = torch.cat([moved, pad], 0)
+    bufs: List[torch.Tensor] = [torch.empty_like(padded) for _ in range(world)]
+    dist.all_gather(bufs, padded, group=group)
+    out = torch.cat([b[:n] for b, n in zip(bufs, sizes)], 0)
+    return out.movedim(0, dim)

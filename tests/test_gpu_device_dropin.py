@@ -224,6 +224,19 @@ def test_copy_cases():
     assert one.to(DEV)[1].item() == -2.25                                     # _local_scalar_dense
 
 
+def test_paras_memory_viewed_as_cuda_tensor():
+    from torch_paras import sharding
+    x = torch.randn(33, 65).bfloat16()
+    d = x.to(DEV)
+    torch_paras.synchronize(1)
+    c = sharding.as_cuda(d)
+    assert c.device.type == "cuda" and c.dtype == torch.bfloat16 and c.shape == d.shape
+    assert torch.equal(c.cpu(), x)
+    c.mul_(2)                       # same memory: the paras tensor sees the change
+    torch.cuda.synchronize()
+    assert torch.equal(d.cpu(), x * 2)
+
+
 def test_concurrent_dispatch_from_python_threads():
     x = torch.randn(256, 512)
     want = F.silu(x) * x
