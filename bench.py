@@ -228,11 +228,16 @@ def run_ours(args):
     if world > 1:
         import torch.distributed as dist
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        # no device_id: with the `paras` backend registered torch reports it as the accelerator
+        dist.init_process_group("nccl")
 
     def barrier():
+        # an all-reduce of one CUDA scalar: dist.barrier() would pick the registered `paras`
+        # accelerator, which NCCL does not serve
         if dist is not None:
-            dist.barrier()
+            tok = torch.zeros(1, device=torch.device("cuda", local))
+            dist.all_reduce(tok)
+            torch.cuda.synchronize()
 
     def max_over_ranks(ms: float) -> float:
         if dist is None:
@@ -336,7 +341,7 @@ def run_ours(args):
             print(json.dumps({"only": only, "n_gpus": world, "headline_sdpa_tflops": tflops, "extra": extra}),
                   flush=True)
         if dist is not None:
-            dist.barrier()
+            barrier()
             dist.destroy_process_group()
         return
 
@@ -399,7 +404,7 @@ def run_ours(args):
         }
         print(json.dumps(line), flush=True)
     if dist is not None:
-        dist.barrier()
+        barrier()
         dist.destroy_process_group()
 
 

@@ -13,6 +13,7 @@
 #include <torch/version.h>
 
 #include <cstring>
+#include <map>
 #include <mutex>
 #include <vector>
 
@@ -113,21 +114,83 @@ struct GuardImpl final : public c10::impl::DeviceGuardImplInterface {
 GuardImpl g_guard;
 c10::impl::DeviceGuardImplRegistrar g_guard_registrar(kDevice, &g_guard);
 
-// Page-locked host memory (`tensor.pin_memory()`, `torch.empty(..., pin_memory=True)`): the
-// source/destination of direct DMA transfers; pageable tensors go through the library's
-// own pinned staging ring instead.
-void delete_pinned(void* ptr) {
-    if (ptr) paras_b200_host_free(ptr);
+// Page-locked host memory (`tensor.pin_memory()`, `torch.empty(..., pin_memory=True)`, and the
+// destination of every device->host `.cpu()` copy): the source/destination of direct DMA
+// transfers.  Pinning pages costs tens of milliseconds per 100 MB, so freed blocks are kept
+// in size classes and handed out again; `empty_cache()` returns them to the system.
+class PinnedCache {
+public:
+    void* take(size_t nbytes, size_t* rounded) {
+        const size_t cls = round_up(nbytes);
+        *rounded = cls;
+        {
+            std::lock_guard<std::mutex> lk(mu_);
+            auto it = free_.find(cls);
+            if (it != free_.end() && !it->second.empty()) {
+                void* p = it->second.back();
+                it->second.pop_back();
+                cached_ -= cls;
+                return p;
+            }
+        }
+        void* p = nullptr;
+        PARAS_ABI(paras_b200_host_alloc(cls, &p));
+        return p;
+    }
+    void give(void* p, size_t cls) {
+        std::lock_guard<std::mutex> lk(mu_);
+        free_[cls].push_back(p);
+        cached_ += cls;
+    }
+    void clear() {
+        std::lock_guard<std::mutex> lk(mu_);
+        for (auto& kv : free_)
+            for (void* p : kv.second) paras_b200_host_free(p);
+        free_.clear();
+        cached_ = 0;
+    }
+    static PinnedCache& get() {
+        static PinnedCache* c = new PinnedCache();  // leaked on purpose: tensors may outlive statics
+        return *c;
+    }
+
+private:
+    static size_t round_up(size_t n) {
+        if (n <= 4096) return 4096;
+        if (n <= (size_t(1) << 20)) {  // powers of two up to 1 MiB
+            size_t c = 4096;
+            while (c < n) c <<= 1;
+            return c;
+        }
+        const size_t mb = size_t(2) << 20;  // then multiples of 2 MiB
+        return (n + mb - 1) / mb * mb;
+    }
+    std::mutex mu_;
+    std::map<size_t, std::vector<void*>> free_;
+    size_t cached_ = 0;
+};
+
+struct PinnedRecord {
+    void* ptr;
+    size_t cls;
+};
+
+void delete_pinned(void* ctx) {
+    auto* rec = static_cast<PinnedRecord*>(ctx);
+    if (!rec) return;
+    PinnedCache::get().give(rec->ptr, rec->cls);
+    delete rec;
 }
 
 class PinnedAllocator final : public c10::Allocator {
 public:
     c10::DataPtr allocate(size_t nbytes) override {
-        void* p = nullptr;
-        if (nbytes) PARAS_ABI(paras_b200_host_alloc(nbytes, &p));
-        return c10::DataPtr(p, p, &delete_pinned, c10::Device(c10::kCPU));
+        if (nbytes == 0) return c10::DataPtr(nullptr, nullptr, &delete_pinned, c10::Device(c10::kCPU));
+        size_t cls = 0;
+        void* p = PinnedCache::get().take(nbytes, &cls);
+        return c10::DataPtr(p, new PinnedRecord{p, cls}, &delete_pinned, c10::Device(c10::kCPU));
     }
-    c10::DeleterFnPtr raw_deleter() const override { return &delete_pinned; }
+    c10::DeleterFnPtr raw_deleter() const override { return nullptr; }
     void copy_data(void* dest, const void* src, std::size_t count) const override {
         std::memcpy(dest, src, count);
     }
@@ -211,6 +274,7 @@ void Runtime::synchronize_all() {
 
 void Runtime::empty_cache_all() {
     for (int i = 0; i < gpu_count_; ++i) PARAS_ABI(paras_b200_pool_trim(i));
+    PinnedCache::get().clear();
 }
 
 uint64_t Runtime::allocated_bytes(int index) {

@@ -212,6 +212,30 @@ Tensor copy_from(const Tensor& self, const Tensor& dst, bool non_blocking) {
     return dst;
 }
 
+// aten::_to_copy for a paras source (`.cpu()`, `.to(dtype)`, `.to("paras:2")`).  A host
+// destination is allocated page-locked (from the cached pinned allocator), so the
+// device->host transfer is one direct DMA at PCIe speed instead of a staged copy into
+// pageable memory.
+Tensor to_copy(const Tensor& self, std::optional<c10::ScalarType> dtype,
+               std::optional<c10::Layout> layout, std::optional<c10::Device> device,
+               std::optional<bool> pin_memory, bool non_blocking,
+               std::optional<c10::MemoryFormat> /*memory_format*/) {
+    PARAS_TRACE_OP("_to_copy");
+    TORCH_CHECK(!layout || *layout == c10::kStrided, "paras backend supports only strided layout");
+    const c10::Device target = device.value_or(self.device());
+    const c10::ScalarType st = dtype.value_or(self.scalar_type());
+    Tensor dst;
+    if (target.is_cpu()) {
+        const bool pinned = pin_memory.value_or(on_gpu(self));
+        dst = at::empty(self.sizes(), at::TensorOptions().dtype(st).device(c10::kCPU).pinned_memory(pinned));
+    } else {
+        dst = at::empty(self.sizes(), self.options().dtype(st).device(target));
+    }
+    if (is_paras(dst) || is_paras(self)) copy_from(self, dst, non_blocking);
+    else dst.copy_(self, non_blocking);
+    return dst;
+}
+
 Tensor copy_from_and_resize(const Tensor& self, const Tensor& dst) {
     PARAS_TRACE_OP("_copy_from_and_resize");
     if (dst.sizes() != self.sizes()) dst.resize_(self.sizes());
@@ -332,6 +356,7 @@ TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
     m.impl("aten::as_strided", &paras::as_strided);
     m.impl("aten::_copy_from", &paras::copy_from);
     m.impl("aten::_copy_from_and_resize", &paras::copy_from_and_resize);
+    m.impl("aten::_to_copy", &paras::to_copy);
     m.impl("aten::fill_.Scalar", &paras::fill_scalar);
     m.impl("aten::zero_", &paras::zero_);
     m.impl("aten::_local_scalar_dense", &paras::local_scalar_dense);
