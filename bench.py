@@ -302,12 +302,13 @@ def run_ours(args):
 
     if want("swiglu"):
         # SwiGLU, config 3 shape: bytes = 3*n*2
-        gate, up = gen((32768, 14336), 6), gen((32768, 14336), 7)
+        srows = 8192 if args.small else 32768
+        gate, up = gen((srows, 14336), 6), gen((srows, 14336), 7)
         so = torch.empty_like(gate)
         t = loop_ms(lambda: abi.swiglu_fwd(gate, up, out=so), esteps)
         nbytes = 3 * gate.numel() * 2
         gbs = nbytes / (t * 1e-3) / 1e9
-        extra["swiglu_32768x14336"] = {"ms": t, "gbs": gbs, "frac_of_hbm_peak": gbs / peaks["hbm_gbs"],
+        extra[f"swiglu_{srows}x14336"] = {"ms": t, "gbs": gbs, "frac_of_hbm_peak": gbs / peaks["hbm_gbs"],
                                        "bytes": nbytes}
         del gate, up, so
 
@@ -324,14 +325,15 @@ def run_ours(args):
 
     if want("decode"):
         # config 4 decode: bytes = K + V (once per kv head) + q + o
-        qd, kd, vd = gen((64, 32, 1, 128), 11), gen((64, 8, 32768, 128), 12), gen((64, 8, 32768, 128), 13)
+        db = 8 if args.small else 64
+        qd, kd, vd = gen((db, 32, 1, 128), 11), gen((db, 8, 32768, 128), 12), gen((db, 8, 32768, 128), 13)
         od = torch.empty_like(qd)
         ws_bytes = abi.sdpa_workspace_bytes(qd, kd, vd)
         ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=dev)
         t = loop_ms(lambda: abi.sdpa_fwd(qd, kd, vd, out=od, workspace=ws if ws_bytes else None), s3, 3)
         nbytes = (kd.numel() + vd.numel() + qd.numel() + od.numel()) * 2
         gbs = nbytes / (t * 1e-3) / 1e9
-        extra["sdpa_decode_B64_kv32768"] = {"ms": t, "gbs": gbs, "frac_of_hbm_peak": gbs / peaks["hbm_gbs"],
+        extra[f"sdpa_decode_B{db}_kv32768"] = {"ms": t, "gbs": gbs, "frac_of_hbm_peak": gbs / peaks["hbm_gbs"],
                                             "bytes": nbytes, "kernel": abi.sdpa_last_kernel()}
         del qd, kd, vd, od, ws
     torch.cuda.empty_cache()
@@ -415,6 +417,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--quick", action="store_true", help="headline + e2e only")
+    ap.add_argument("--small", action="store_true",
+                    help="shrink the extra workloads (SwiGLU 8192 rows, decode batch 8) so that a profiler "
+                         "capture holds about 1 GB on the device; rates stay per-byte comparable")
     ap.add_argument("--only", choices=["rmsnorm", "swiglu", "gqa", "decode"],
                     help="after the headline loop run just this extra workload and print it (for profiling)")
     ap.add_argument("--no-cpu-baseline", action="store_true")

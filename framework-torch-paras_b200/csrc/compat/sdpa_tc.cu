@@ -24,7 +24,9 @@
 // used consistently for P and l, so the final O/l is exact).
 //
 // Every wait is bounded (tc_prims.cuh); a wait that runs out raises the CTA's abort flag,
-// all roles fall through to the common exit, TMEM is freed and the GPU's status word is set.
+// all roles fall through to the common exit, TMEM is freed and the GPU's status word is set to
+// a mask of the waits that were pending (bits: 0-1 Q buffer free, 2 ring slot free, 3 K/V
+// landed, 4-5 Q landed, 6-7 P ready, 8-9 O read out, 10-11 S ready, 16-17 last PV done).
 #include <cmath>
 #include <mutex>
 
@@ -176,7 +178,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                 for (int t = 0; t < 2; ++t) {
                     if (ok && it.ntile[t] > 0) {
                         // the previous item's last QK^T on this Q buffer has completed
-                        ok = mbar_wait(bar(kBarQEmpty + t), (qcnt[t] & 1u) ^ 1u, abort_flag);
+                        ok = mbar_wait(bar(kBarQEmpty + t), (qcnt[t] & 1u) ^ 1u, abort_flag, 0 + t);
                         if (!ok) break;
                         ++qcnt[t];
                         mbar_arrive_expect_tx(bar(kBarQFull + t), kTileBytes);
@@ -188,7 +190,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                 for (int x = 0; ok && x < 2 * it.n; ++x, ++ring) {
                     const int slot = ring % kStages;
                     const uint32_t ph = (ring / kStages) & 1;
-                    ok = mbar_wait(bar(kBarKVEmpty + slot), ph ^ 1u, abort_flag);
+                    ok = mbar_wait(bar(kBarKVEmpty + slot), ph ^ 1u, abort_flag, 2);
                     if (!ok) break;
                     const int j = x >> 1;
                     const CUtensorMap* map = (x & 1) ? &map_v : &map_k;
@@ -233,11 +235,11 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             Item it;
             for (int seq = 0; ok && get_item(p, seq, &it); ++seq) {
                 if (it.n == 0) continue;
-                ok = mbar_wait(bar(kBarKVFull + ring % kStages), (ring / kStages) & 1, abort_flag);  // K0
+                ok = mbar_wait(bar(kBarKVFull + ring % kStages), (ring / kStages) & 1, abort_flag, 3);  // K0
 #pragma unroll
                 for (int t = 0; t < 2; ++t) {
                     if (ok && it.ntile[t] > 0) {
-                        ok = mbar_wait(bar(kBarQFull + t), qcnt[t] & 1u, abort_flag);
+                        ok = mbar_wait(bar(kBarQFull + t), qcnt[t] & 1u, abort_flag, 4 + t);
                         if (ok) {
                             tc_fence_after_sync();
                             issue_qk(t, ring % kStages);
@@ -251,19 +253,19 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                 for (int j = 0; ok && j < it.n; ++j) {
                     const int item_v = ring + 2 * j + 1, item_k = ring + 2 * j + 2;
                     const int slot_v = item_v % kStages, slot_k = item_k % kStages;
-                    ok = mbar_wait(bar(kBarKVFull + slot_v), (item_v / kStages) & 1, abort_flag);
+                    ok = mbar_wait(bar(kBarKVFull + slot_v), (item_v / kStages) & 1, abort_flag, 3);
                     if (ok && j + 1 < it.n)
-                        ok = mbar_wait(bar(kBarKVFull + slot_k), (item_k / kStages) & 1, abort_flag);
+                        ok = mbar_wait(bar(kBarKVFull + slot_k), (item_k / kStages) & 1, abort_flag, 3);
                     if (!ok) break;
 #pragma unroll
                     for (int t = 0; t < 2; ++t) {
                         if (ok && j < it.ntile[t]) {
-                            ok = mbar_wait(bar(kBarPFull + t), pcnt[t] & 1u, abort_flag);
+                            ok = mbar_wait(bar(kBarPFull + t), pcnt[t] & 1u, abort_flag, 6 + t);
                             if (!ok) break;
                             ++pcnt[t];
                             if (j == 0) {
                                 // the first PV overwrites O_t: the previous item's epilogue has read it
-                                ok = mbar_wait(bar(kBarOEmpty + t), (qcnt[t] & 1u) ^ 1u, abort_flag);
+                                ok = mbar_wait(bar(kBarOEmpty + t), (qcnt[t] & 1u) ^ 1u, abort_flag, 8 + t);
                                 if (!ok) break;
                             }
                             tc_fence_after_sync();
@@ -306,7 +308,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             const int row_q = it.start[t] + wq * 32 + lane;
             float m = -INFINITY, l = 0.f;
             for (int j = 0; j < nt; ++j) {
-                ok = mbar_wait(bar(kBarSFull + t), scnt & 1u, abort_flag);
+                ok = mbar_wait(bar(kBarSFull + t), scnt & 1u, abort_flag, 10 + t);
                 if (!ok) break;
                 ++scnt;
                 tc_fence_after_sync();
@@ -387,7 +389,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                 if (lane == 0) mbar_arrive(bar(kBarPFull + t));
             }
             if (!ok) break;
-            ok = mbar_wait(bar(kBarOFull + t), ocnt & 1u, abort_flag);
+            ok = mbar_wait(bar(kBarOFull + t), ocnt & 1u, abort_flag, 16 + t);
             if (!ok) break;
             ++ocnt;
             tc_fence_after_sync();
@@ -433,7 +435,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     }
     if (threadIdx.x == 0 && *abort_flag) {
         g_abort_latch = 1;
-        *p.status = 1;
+        *p.status = *abort_flag;  // 0x40000000 | one bit per wait that was still pending
         __threadfence_system();
     }
 }

@@ -49,14 +49,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 }
 
 // Bounded wait: gives up after `limit_ns` of wall time, or as soon as another thread of
-// the CTA has raised `*abort_flag` (a shared-memory word).  Returns false when it gave up;
+// the CTA has raised `*abort_flag` (a shared-memory word, set to the caller's `tag`).  Returns false when it gave up;
 // the caller then stops issuing work and leaves through the kernel's common exit.
 constexpr uint64_t kWaitLimitNs = 200000000ull;  // 0.2 s: orders of magnitude above any real wait
 
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
-                                          volatile int* abort_flag) {
+                                          volatile int* abort_flag, int tag = 0) {
     // Plain polling first (each try_wait already blocks for a hardware time slice); the
     // clock and the abort flag are only consulted once a wait has become unusually long.
+    // `tag` (0..30) names the wait: every wait that was still pending when the CTA gave up
+    // sets bit `tag` of the abort word, which ends up in the GPU's status word.
 #pragma unroll 1
     for (int i = 0; i < 2048; ++i)
         if (mbar_try_wait(bar, parity)) return true;
@@ -64,9 +66,8 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
     uint32_t polls = 0;
     while (!mbar_try_wait(bar, parity)) {
         if ((++polls & 0xffu) == 0) {
-            if (*abort_flag) return false;
-            if (global_timer_ns() - t0 > kWaitLimitNs) {
-                *abort_flag = 1;
+            if (*abort_flag || global_timer_ns() - t0 > kWaitLimitNs) {
+                atomicOr(const_cast<int*>(abort_flag), int(0x40000000u | (1u << tag)));
                 return false;
             }
         }
