@@ -275,7 +275,12 @@ def run_ours(args):
     roofline = {"bound": "tensor", "kernel": f"sdpa_tc_kernel ({kernel_name})",
                 "achieved": per_gpu_tflops, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                 "frac": per_gpu_tflops / peaks["bf16_tflops"], "peak_source": peaks["source"] + " (burst)",
-                "frac_of_nominal_2250": per_gpu_tflops / 2250.0, "traffic": None}
+                "frac_of_nominal_2250": per_gpu_tflops / 2250.0,
+                # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this workload from the
+                # committed ncu capture (profiles/sdpa_tc_kernel_config2_causal_bf16.md); algorithmic
+                # q+k+v+o = 536.9 MB
+                "traffic": 513.9e6, "traffic_unit": "bytes per launch (ncu)",
+                "algorithmic_bytes": 4 * c["B"] * c["Hq"] * c["S"] * c["D"] * 2}
 
     extra = {}
     only = args.only
