@@ -328,16 +328,13 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                     for (int i = 0; i < BN; ++i)
                         if (i > limit) s[i] = 0xff800000u;  // -inf
                 }
-                float mx0 = __uint_as_float(s[0]), mx1 = __uint_as_float(s[1]);
-                float mx2 = __uint_as_float(s[2]), mx3 = __uint_as_float(s[3]);
+                float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
-                for (int i = 4; i < BN; i += 4) {
-                    mx0 = fmaxf(mx0, __uint_as_float(s[i]));
-                    mx1 = fmaxf(mx1, __uint_as_float(s[i + 1]));
-                    mx2 = fmaxf(mx2, __uint_as_float(s[i + 2]));
-                    mx3 = fmaxf(mx3, __uint_as_float(s[i + 3]));
+                for (int i = 0; i < BN; i += 4) {
+                    mx0 = fmax3(mx0, __uint_as_float(s[i]), __uint_as_float(s[i + 1]));
+                    mx1 = fmax3(mx1, __uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]));
                 }
-                const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+                const float mx = fmaxf(mx0, mx1);
 
                 float alpha = 1.f;
                 bool grew = false;
@@ -366,23 +363,25 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                         tmem_st32(o_addr + 32 * c, o);
                     }
                 }
+                // two columns per instruction on the FMA pipe (fp32x2 FMA / ADD)
                 const float neg_m = -m * c2;
-                float lsum0 = 0.f, lsum1 = 0.f;
+                const float2 c22 = make_float2(c2, c2), nm2 = make_float2(neg_m, neg_m);
+                float2 ls0 = make_float2(0.f, 0.f), ls1 = make_float2(0.f, 0.f);
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
                     uint32_t pk[16];
 #pragma unroll
                     for (int i = 0; i < 16; ++i) {
                         const int e = 32 * c + 2 * i;
-                        const float p0 = ex2_approx(fmaf(__uint_as_float(s[e]), c2, neg_m));
-                        const float p1 = ex2_approx(fmaf(__uint_as_float(s[e + 1]), c2, neg_m));
-                        lsum0 += p0;
-                        lsum1 += p1;
+                        const float2 x = ffma2(make_float2(__uint_as_float(s[e]), __uint_as_float(s[e + 1])), c22, nm2);
+                        const float p0 = ex2_approx(x.x), p1 = ex2_approx(x.y);
+                        if (i & 1) ls1 = fadd2(ls1, make_float2(p0, p1));
+                        else ls0 = fadd2(ls0, make_float2(p0, p1));
                         pk[i] = pack16<BF16>(p0, p1);
                     }
                     tmem_st16(s_addr + 16 * c, pk);  // P_t over the first 64 columns of S_t
                 }
-                l += lsum0 + lsum1;
+                l += (ls0.x + ls0.y) + (ls1.x + ls1.y);
                 tmem_wait_st();
                 tc_fence_before_sync();
                 __syncwarp();
