@@ -341,6 +341,39 @@ def run_ours(args):
         extra[f"sdpa_decode_B{db}_kv32768"] = {"ms": t, "gbs": gbs, "frac_of_hbm_peak": gbs / peaks["hbm_gbs"],
                                             "bytes": nbytes, "kernel": abi.sdpa_last_kernel()}
         del qd, kd, vd, od, ws
+    if want("block"):
+        # config 5, one GPU's share (B=64 over 8 GPUs -> 8 batch elements here): RMSNorm -> causal GQA
+        # attention -> RMSNorm -> SwiGLU, hidden 4096 (Hq=32, Hkv=8, D=128), S=4096, FFN width 14336.
+        # q/k/v and gate/up stand for the projections' outputs (the GEMMs are outside the path).
+        Bp = 2 if args.small else 8
+        rows = Bp * 4096
+        xh = gen((rows, 4096), 14)
+        wn = gen((4096,), 15, mean=1.0, std=0.1)
+        qb, kb, vb = gen((Bp, 32, 4096, 128), 16), gen((Bp, 8, 4096, 128), 17), gen((Bp, 8, 4096, 128), 18)
+        gb, ub = gen((rows, 14336), 19), gen((rows, 14336), 20)
+        y1, ob, y2, sb = torch.empty_like(xh), torch.empty_like(qb), torch.empty_like(xh), torch.empty_like(gb)
+
+        def block():
+            abi.rmsnorm_fwd(xh, wn, 1e-6, out=y1, mode=abi.ROUND_PER_OP)
+            abi.sdpa_fwd(qb, kb, vb, causal=True, out=ob, flags=abi.SDPA_REF_SCALE)
+            abi.rmsnorm_fwd(ob.view(rows, 4096), wn, 1e-6, out=y2, mode=abi.ROUND_PER_OP)
+            abi.swiglu_fwd(gb, ub, out=sb)
+
+        stages = {
+            "rmsnorm": lambda: abi.rmsnorm_fwd(xh, wn, 1e-6, out=y1, mode=abi.ROUND_PER_OP),
+            "sdpa": lambda: abi.sdpa_fwd(qb, kb, vb, causal=True, out=ob, flags=abi.SDPA_REF_SCALE),
+            "swiglu": lambda: abi.swiglu_fwd(gb, ub, out=sb),
+        }
+        res = {"per_gpu_batch": Bp, "ms_total": loop_ms(block, s3, 3)}
+        for name, fn in stages.items():
+            res["ms_" + name] = loop_ms(fn, s3, 3)
+        fl = sdpa_flops(Bp, 32, 4096, 4096, 128, True)
+        res["sdpa_tflops"] = fl / (res["ms_sdpa"] * 1e-3) / 1e12
+        res["rmsnorm_gbs"] = (2 * rows * 4096 * 2 + 8192) / (res["ms_rmsnorm"] * 1e-3) / 1e9
+        res["swiglu_gbs"] = 3 * rows * 14336 * 2 / (res["ms_swiglu"] * 1e-3) / 1e9
+        res["global_batch_all_ranks"] = Bp * world
+        extra["config5_decoder_block_share"] = res
+        del xh, qb, kb, vb, gb, ub, y1, ob, y2, sb
     torch.cuda.empty_cache()
 
     if only:
@@ -425,7 +458,7 @@ def main():
     ap.add_argument("--small", action="store_true",
                     help="shrink the extra workloads (SwiGLU 8192 rows, decode batch 8) so that a profiler "
                          "capture holds about 1 GB on the device; rates stay per-byte comparable")
-    ap.add_argument("--only", choices=["rmsnorm", "swiglu", "gqa", "decode"],
+    ap.add_argument("--only", choices=["rmsnorm", "swiglu", "gqa", "decode", "block"],
                     help="after the headline loop run just this extra workload and print it (for profiling)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-repeat", type=int, default=3)

@@ -53,19 +53,45 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // the caller then stops issuing work and leaves through the kernel's common exit.
 constexpr uint64_t kWaitLimitNs = 200000000ull;  // 0.2 s: orders of magnitude above any real wait
 
+template <int SLEEP_NS = 0>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
                                           volatile int* abort_flag, int tag = 0) {
     // Plain polling first (each try_wait already blocks for a hardware time slice); the
     // clock and the abort flag are only consulted once a wait has become unusually long.
     // `tag` (0..30) names the wait: every wait that was still pending when the CTA gave up
     // sets bit `tag` of the abort word, which ends up in the GPU's status word.
+    // SLEEP_NS > 0 yields the scheduler between polls: a spinning warp takes issue slots from
+    // the warps that share its scheduler and are doing the work it is waiting for.
 #pragma unroll 1
-    for (int i = 0; i < 2048; ++i)
+    for (int i = 0; i < 2048; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
+        if constexpr (SLEEP_NS > 0) __nanosleep(SLEEP_NS);
+    }
     const uint64_t t0 = global_timer_ns();
     uint32_t polls = 0;
     while (!mbar_try_wait(bar, parity)) {
+        if constexpr (SLEEP_NS > 0) __nanosleep(SLEEP_NS);
         if ((++polls & 0xffu) == 0) {
+            if (*abort_flag || global_timer_ns() - t0 > kWaitLimitNs) {
+                atomicOr(const_cast<int*>(abort_flag), int(0x40000000u | (1u << tag)));
+                return false;
+            }
+        }
+    }
+    return true;
+}
+
+// Same bounded wait for roles that are off the critical path and wait for a long time (an
+// epilogue waiting for a whole work item): sleeps between polls so that it does not take
+// issue slots from the warps sharing its scheduler.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity,
+                                                  volatile int* abort_flag, int tag = 0) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = global_timer_ns();
+    uint32_t polls = 0;
+    while (!mbar_try_wait(bar, parity)) {
+        __nanosleep(256);
+        if ((++polls & 0x3fu) == 0) {
             if (*abort_flag || global_timer_ns() - t0 > kWaitLimitNs) {
                 atomicOr(const_cast<int*>(abort_flag), int(0x40000000u | (1u << tag)));
                 return false;

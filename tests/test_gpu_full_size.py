@@ -113,3 +113,30 @@ def test_config3_swiglu_full_size():
     comp = abi.swiglu_fwd(gate, up, mode=abi.ROUND_PER_OP)
     want = O.swiglu_composite(up[:16].cpu(), gate[:16].cpu())
     assert (comp[:16].cpu().double() - want.double()).abs().max().item() <= 2e-2
+
+
+def test_config5_decoder_block_share_of_one_gpu():
+    # config 5 shards B=64 over 8 GPUs by batch; one batch element of a GPU's share is checked here:
+    # RMSNorm [S, 4096] -> causal GQA attention (Hq=32, Hkv=8, S=4096, D=128) -> RMSNorm -> SwiGLU [S, 14336]
+    S = 4096
+    x = gen((S, 4096), 30)
+    w = gen((4096,), 31, mean=1.0, std=0.1)
+    y1 = abi.rmsnorm_fwd(x, w, 1e-6, mode=abi.ROUND_PER_OP)
+    q, k, v = gen((1, 32, S, 128), 32), gen((1, 8, S, 128), 33), gen((1, 8, S, 128), 34)
+    att = abi.sdpa_fwd(q, k, v, causal=True, flags=abi.SDPA_REF_SCALE)
+    assert abi.sdpa_last_kernel() == "tcgen05"
+    y2 = abi.rmsnorm_fwd(att.transpose(1, 2).reshape(S, 4096).contiguous(), w, 1e-6, mode=abi.ROUND_PER_OP)
+    gate, up = gen((S, 14336), 35), gen((S, 14336), 36)
+    act = abi.swiglu_fwd(gate, up)
+    rows = slice(S - 32, S)
+    want1 = O.rms_norm_composite(x[rows].cpu(), [4096], w.cpu(), 1e-6)
+    assert (y1[rows].cpu().double() - want1.double()).abs().max().item() <= 2e-2
+    # attention: query heads 0-3 share kv head 0; oracle on the first 1024 positions
+    want_a = O.sdpa(q[:, :4, :1024].cpu(), k[:, :1, :1024].cpu(), v[:, :1, :1024].cpu(), is_causal=True, enable_gqa=True)
+    err = (att[:, :4, :1024].cpu().double() - want_a.double()).abs().max().item()
+    assert err <= 2e-2, f"attention slice max-abs {err}"
+    a2 = att.transpose(1, 2).reshape(S, 4096)[rows].contiguous()
+    want2 = O.rms_norm_composite(a2.cpu(), [4096], w.cpu(), 1e-6)
+    assert (y2[rows].cpu().double() - want2.double()).abs().max().item() <= 2e-2
+    want3 = O.swiglu_fused(gate[rows].cpu(), up[rows].cpu())
+    assert (act[rows].cpu().double() - want3.double()).abs().max().item() <= 2e-2
