@@ -15,7 +15,9 @@
 // TMEM (512 columns x 128 lanes, fp32): S0 @0, S1 @128, O0 @256, O1 @384.  The 16-bit
 // probabilities P_t overwrite the first 64 columns of S_t and feed the P*V MMA straight
 // from TMEM.  Shared memory: Q 2x32 KB, K/V ring 4x32 KB, all 128-byte swizzled as TMA
-// writes them.
+// writes them, and 8x4 KB (one per softmax warp) through which finished O rows leave as
+// TMA stores: a lane owns a row, so direct global stores would be 32 cache lines per
+// instruction and hold up the load/store path the TMEM traffic shares.
 //
 // Per kv tile j and query tile t:  S_t = Q_t K_j^T  (8 MMAs, K=16 each)
 //                                  P_t = exp2(S_t*c - m_t*c), row sums l_t, running max m_t
@@ -55,7 +57,9 @@ constexpr float kRescaleThreshold = 8.0f;    // log2 units
 
 constexpr int kSmemQ = 0;
 constexpr int kSmemKV = kTilesPerCta * kTileBytes;
-constexpr int kSmemBars = kSmemKV + kStages * kTileBytes;
+constexpr int kSmemO = kSmemKV + kStages * kTileBytes;   // per softmax warp: 32 rows x 128 B staging for the O store
+constexpr int kOStageBytes = 32 * 128;
+constexpr int kSmemBars = kSmemO + kSoftmaxWarps * kOStageBytes;
 // barrier indices
 constexpr int kBarQFull = 0;                       // [2]  TMA -> MMA: Q tile landed
 constexpr int kBarQEmpty = 2;                      // [2]  MMA -> TMA: last QK^T of the item is done
@@ -132,7 +136,8 @@ __device__ __forceinline__ bool get_item(const TcParams& p, int seq, Item* it) {
 template <bool BF16>
 __global__ void __launch_bounds__(kThreads, 1)
 sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-               const __grid_constant__ CUtensorMap map_v, const TcParams p) {
+               const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o,
+               const TcParams p) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -160,6 +165,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         tma_prefetch_desc(&map_q);
         tma_prefetch_desc(&map_k);
         tma_prefetch_desc(&map_v);
+        tma_prefetch_desc(&map_o);
     }
     tc_fence_before_sync();
     __syncthreads();
@@ -297,6 +303,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         const uint32_t lane_base = uint32_t(wq * 32) << 16;
         const uint32_t s_addr = tmem + lane_base + kColS + t * 128;
         const uint32_t o_addr = tmem + lane_base + kColO + t * 128;
+        const uint32_t o_stage = smem_base + kSmemO + warp * kOStageBytes;
         const float c2 = p.scale_log2;
         bool ok = true;
         uint32_t scnt = 0;  // S tiles consumed so far
@@ -394,8 +401,11 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             tc_fence_after_sync();
             const float inv = 1.0f / l;
             const bool live = row_q < p.Lq;
-            uint16_t* orow = static_cast<uint16_t*>(p.out) + int64_t(it.b) * p.os[0] +
-                             int64_t(it.h) * p.os[1] + int64_t(live ? row_q : 0) * p.os[2];
+            // O leaves through shared memory and a TMA store: a lane owns a row, so direct global
+            // stores would touch 32 cache lines per instruction.  Two halves of 64 columns share
+            // the warp's 4 KB staging buffer (128-byte swizzle: 16-byte chunk c of row r sits at
+            // chunk c ^ (r & 7)); rows past the end of the sequence are clipped by the tensor map.
+            const int row_w = it.start[t] + wq * 32;
 #pragma unroll 1
             for (int c = 0; c < 4; ++c) {
                 uint32_t o[32];
@@ -408,21 +418,32 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                     __syncwarp();
                     if (lane == 0) mbar_arrive(bar(kBarOEmpty + t));
                 }
-                if (live) {
+                if ((c & 1) == 0) {
+                    if (lane == 0) tma_store_wait_read();  // the previous store has read the buffer
+                    __syncwarp();
+                }
 #pragma unroll
-                    for (int v = 0; v < 4; ++v) {
-                        uint4 w;
-                        w.x = pack16<BF16>(__uint_as_float(o[8 * v + 0]) * inv, __uint_as_float(o[8 * v + 1]) * inv);
-                        w.y = pack16<BF16>(__uint_as_float(o[8 * v + 2]) * inv, __uint_as_float(o[8 * v + 3]) * inv);
-                        w.z = pack16<BF16>(__uint_as_float(o[8 * v + 4]) * inv, __uint_as_float(o[8 * v + 5]) * inv);
-                        w.w = pack16<BF16>(__uint_as_float(o[8 * v + 6]) * inv, __uint_as_float(o[8 * v + 7]) * inv);
-                        *reinterpret_cast<uint4*>(orow + 32 * c + 8 * v) = w;
+                for (int v = 0; v < 4; ++v) {
+                    uint4 w;
+                    w.x = pack16<BF16>(__uint_as_float(o[8 * v + 0]) * inv, __uint_as_float(o[8 * v + 1]) * inv);
+                    w.y = pack16<BF16>(__uint_as_float(o[8 * v + 2]) * inv, __uint_as_float(o[8 * v + 3]) * inv);
+                    w.z = pack16<BF16>(__uint_as_float(o[8 * v + 4]) * inv, __uint_as_float(o[8 * v + 5]) * inv);
+                    w.w = pack16<BF16>(__uint_as_float(o[8 * v + 6]) * inv, __uint_as_float(o[8 * v + 7]) * inv);
+                    st_shared_v4(o_stage + lane * 128 + (((4 * (c & 1) + v) ^ (lane & 7)) << 4), w);
+                }
+                if (c & 1) {
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0 && row_w < p.Lq) {
+                        tma_store_4d(&map_o, o_stage, 64 * (c >> 1), row_w, it.h, it.b);
+                        tma_store_commit();
                     }
                 }
             }
             if (p.lse && live)
                 p.lse[(int64_t(it.b) * p.Hq + it.h) * p.Lq + row_q] = m * p.scale + logf(l);
         }
+        if (lane == 0) tma_store_wait_read();  // shared memory stays valid until the last store has read it
     }
 
     // ------------------------------ common exit ------------------------------------
@@ -463,7 +484,7 @@ EncodeFn encode_fn() {
 // [B, H, L, 128] tensor with element strides st = {B, H, L}; box = 64 x 128 rows, 128-byte
 // swizzle, out-of-range rows read as zero.
 int make_map(CUtensorMap* map, const void* base, int dtype, int B, int H, int L,
-             const int64_t* st) {
+             const int64_t* st, int box_rows = BN) {
     EncodeFn fn = encode_fn();
     if (!fn) return fail(PARAS_E_CUDA, "paras sdpa: cuTensorMapEncodeTiled is unavailable");
     const cuuint64_t dims[4] = {cuuint64_t(HD), cuuint64_t(L), cuuint64_t(H), cuuint64_t(B)};
@@ -472,7 +493,7 @@ int make_map(CUtensorMap* map, const void* base, int dtype, int B, int H, int L,
     const int64_t sh = H > 1 ? st[1] : sl * L;
     const int64_t sb = B > 1 ? st[0] : sh * H;
     const cuuint64_t strides[3] = {cuuint64_t(sl) * 2, cuuint64_t(sh) * 2, cuuint64_t(sb) * 2};
-    const cuuint32_t box[4] = {64, cuuint32_t(BN), 1, 1};
+    const cuuint32_t box[4] = {64, cuuint32_t(box_rows), 1, 1};
     const cuuint32_t estr[4] = {1, 1, 1, 1};
     const CUresult r = fn(map, dtype == PARAS_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
                                                   : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
@@ -520,10 +541,11 @@ int sdpa_tc_launch(Gpu* g, const paras_sdpa_args& a, float scale, cudaStream_t s
         cudaMemcpyToSymbol(g_abort_latch, &zero, sizeof(int));
         return st;
     }
-    CUtensorMap mq, mk, mv;
+    CUtensorMap mq, mk, mv, mo;
     if ((st = make_map(&mq, a.q, a.dtype, a.B, a.Hq, a.Lq, a.q_strides)) != PARAS_OK) return st;
     if ((st = make_map(&mk, a.k, a.dtype, a.B, a.Hkv, a.Lk, a.k_strides)) != PARAS_OK) return st;
     if ((st = make_map(&mv, a.v, a.dtype, a.B, a.Hkv, a.Lk, a.v_strides)) != PARAS_OK) return st;
+    if ((st = make_map(&mo, a.out, a.dtype, a.B, a.Hq, a.Lq, a.o_strides, 32)) != PARAS_OK) return st;
     TcParams p{};
     p.out = a.out;
     p.lse = a.lse;
@@ -543,11 +565,11 @@ int sdpa_tc_launch(Gpu* g, const paras_sdpa_args& a, float scale, cudaStream_t s
     if (a.dtype == PARAS_BF16) {
         PB_CUDA(cudaFuncSetAttribute(sdpa_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      kSmemLaunch));
-        sdpa_tc_kernel<true><<<grid, kThreads, kSmemLaunch, s>>>(mq, mk, mv, p);
+        sdpa_tc_kernel<true><<<grid, kThreads, kSmemLaunch, s>>>(mq, mk, mv, mo, p);
     } else {
         PB_CUDA(cudaFuncSetAttribute(sdpa_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      kSmemLaunch));
-        sdpa_tc_kernel<false><<<grid, kThreads, kSmemLaunch, s>>>(mq, mk, mv, p);
+        sdpa_tc_kernel<false><<<grid, kThreads, kSmemLaunch, s>>>(mq, mk, mv, mo, p);
     }
     PB_LAUNCH_CHECK("sdpa_tc_kernel");
     return PARAS_OK;
