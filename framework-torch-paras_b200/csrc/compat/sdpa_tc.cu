@@ -11,13 +11,20 @@
 //   warps 4-7   softmax of query tile 1
 //   warp  8     allocates TMEM, then one lane issues every tcgen05.mma
 //   warp  9     one lane issues every TMA load
+//   warps 10-11 idle: they complete the third warpgroup, so that setmaxnreg can move their
+//               registers (and most of warps 8-9's) to the softmax warps, which hold a whole
+//               128-column S row per thread
 //
 // TMEM (512 columns x 128 lanes, fp32): S0 @0, S1 @128, O0 @256, O1 @384.  The 16-bit
 // probabilities P_t overwrite the first 64 columns of S_t and feed the P*V MMA straight
-// from TMEM.  Shared memory: Q 2x32 KB, K/V ring 4x32 KB, all 128-byte swizzled as TMA
-// writes them, and 8x4 KB (one per softmax warp) through which finished O rows leave as
-// TMA stores: a lane owns a row, so direct global stores would be 32 cache lines per
-// instruction and hold up the load/store path the TMEM traffic shares.
+// from TMEM.  Shared memory, all 128-byte swizzled as TMA writes it: Q 2x32 KB; a K/V ring
+// of 2x64 KB whose slots hold the pair (V_j, K_j+1) that one step of the MMA loop consumes
+// -- the single issuing thread is the busiest resource of the CTA (an mbarrier wait costs it
+// about 200 cycles even when the barrier has long completed), so it gets one full wait and
+// one release commit per step instead of one per tile; and 8x4 KB (one per softmax warp)
+// through which finished O rows leave as TMA stores: a lane owns a row, so direct global
+// stores would be 32 cache lines per instruction and hold up the load/store path the TMEM
+// traffic shares.
 //
 // Per kv tile j and query tile t:  S_t = Q_t K_j^T  (8 MMAs, K=16 each)
 //                                  P_t = exp2(S_t*c - m_t*c), row sums l_t, running max m_t
@@ -28,7 +35,7 @@
 // Every wait is bounded (tc_prims.cuh); a wait that runs out raises the CTA's abort flag,
 // all roles fall through to the common exit, TMEM is freed and the GPU's status word is set to
 // a mask of the waits that were pending (bits: 0-1 Q buffer free, 2 ring slot free, 3 K/V
-// landed, 4-5 Q landed, 6-7 P ready, 8-9 O read out, 10-11 S ready, 16-17 last PV done).
+// landed, 4-5 Q landed, 6-7 P ready, 10-11 S ready, 16-17 last PV done).
 #include <cmath>
 #include <mutex>
 
@@ -44,20 +51,26 @@ constexpr int BM = 128;            // query rows per tile (MMA M)
 constexpr int BN = 128;            // keys per tile (MMA N of QK^T, K of PV)
 constexpr int HD = 128;            // head dim
 constexpr int kTilesPerCta = 2;
-constexpr int kStages = 4;         // K/V ring slots
+constexpr int kStages = 2;         // K/V ring slots; a slot holds the pair (V_j, K_j+1) that one step consumes
 constexpr int kChunkBytes = 64 * 2 * 128;    // 64 elements x 128 rows
 constexpr int kTileBytes = 2 * kChunkBytes;  // 128 x 128 x 2 B
 constexpr int kSoftmaxWarps = 8;
 constexpr int kMmaWarp = 8;
 constexpr int kLoadWarp = 9;
-constexpr int kThreads = 320;
+constexpr int kThreads = 384;       // warps 10-11 only complete the third warpgroup (setmaxnreg works on warpgroups)
+// Registers per thread after setmaxnreg.  A scheduler hosts two softmax warps and one of warps
+// 8-11: 2*200 + 96 = 496 of its 512 registers per lane.  setmaxnreg.inc waits (without a bound)
+// until the registers it asks for are free, so the sum must stay below the file's size with
+// room to spare: a split that fitted exactly never got past the instruction.
+constexpr int kRegsSoftmax = 200, kRegsIssue = 96;
 constexpr int kTmemCols = 512;
 constexpr int kColS = 0, kColO = 256;  // + 128 * tile
 constexpr float kRescaleThreshold = 8.0f;    // log2 units
 
 constexpr int kSmemQ = 0;
 constexpr int kSmemKV = kTilesPerCta * kTileBytes;
-constexpr int kSmemO = kSmemKV + kStages * kTileBytes;   // per softmax warp: 32 rows x 128 B staging for the O store
+constexpr int kPairBytes = 2 * kTileBytes;   // V tile, then K tile
+constexpr int kSmemO = kSmemKV + kStages * kPairBytes;   // per softmax warp: 32 rows x 128 B staging for the O store
 constexpr int kOStageBytes = 32 * 128;
 constexpr int kSmemBars = kSmemO + kSoftmaxWarps * kOStageBytes;
 // barrier indices
@@ -68,8 +81,7 @@ constexpr int kBarKVEmpty = kBarKVFull + kStages;  // [kStages]
 constexpr int kBarSFull = kBarKVEmpty + kStages;   // [2]  MMA -> softmax: S_t ready
 constexpr int kBarPFull = kBarSFull + 2;           // [2]  softmax -> MMA: P_t written, O_t rescaled
 constexpr int kBarOFull = kBarPFull + 2;           // [2]  MMA -> softmax: last PV of the item is done
-constexpr int kBarOEmpty = kBarOFull + 2;          // [2]  softmax -> MMA: O_t has been read out
-constexpr int kNumBars = kBarOEmpty + 2;
+constexpr int kNumBars = kBarOFull + 2;
 constexpr int kSmemMisc = kSmemBars + kNumBars * 8;   // tmem base word, abort flag
 constexpr int kSmemTotal = kSmemMisc + 16;
 constexpr int kSmemLaunch = kSmemTotal + 1024;        // slack to align the base to 1024 B
@@ -150,8 +162,10 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < kNumBars; ++i) {
-            const bool four = (i >= kBarPFull && i < kBarPFull + 2) || (i >= kBarOEmpty && i < kBarOEmpty + 2);
-            mbar_init(bar(i), four ? 4u : 1u);  // one arrival per softmax warp, else one commit / TMA
+            const bool four = i >= kBarPFull && i < kBarPFull + 2;
+            const bool two = i >= kBarKVFull && i < kBarKVFull + kStages;
+            // one arrival per softmax warp / per entry of a K/V pair / else one commit or TMA
+            mbar_init(bar(i), four ? 4u : (two ? 2u : 1u));
         }
         *abort_flag = 0;
         mbar_fence_init();
@@ -172,14 +186,40 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     tc_fence_after_sync();
     const uint32_t tmem = *tmem_slot;
 
-    if (warp == kLoadWarp) {
+    if (warp >= kMmaWarp) {
+      asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsIssue));
+      if (warp == kLoadWarp) {
         // ------------------------------ TMA producer ------------------------------
         if (lane == 0) {
             bool ok = true;
-            int ring = 0;              // K/V tiles loaded so far: K0 V0 K1 V1 ... across items
+            // K/V tiles are loaded in the order the MMAs use them, across items:
+            //   K0 | V0 K1 | V1 K2 | ... | V_last K0' | V0' K1' | ...
+            // Entry r goes to pair (r+1)/2: an odd entry (V) opens a pair, the following even
+            // entry (K of the next step, or K0 of the next item) completes it.  One full and one
+            // empty barrier per pair: the issuing thread pays one wait and one commit per step.
+            // Each entry arrives once on the pair's full barrier (count 2) with its own byte
+            // count; the V-less first pair and the K-less last pair get a plain arrival instead.
+            int r = 0;
             uint32_t qcnt[2] = {0, 0};  // items that used query tile t
+            auto load_entry = [&](const CUtensorMap* map, int row, int hk, int b) -> bool {
+                const int g = (r + 1) >> 1, slot = g & 1;
+                const uint32_t full = bar(kBarKVFull + slot);
+                if ((r & 1) || r == 0) {  // first entry of the pair: the slot must have been released
+                    if (!mbar_wait(bar(kBarKVEmpty + slot), ((g >> 1) & 1) ^ 1u, abort_flag, 2)) return false;
+                    if (r == 0) mbar_arrive(full);
+                }
+                mbar_arrive_expect_tx(full, kTileBytes);
+                const uint32_t dst = smem_base + kSmemKV + slot * kPairBytes + ((r & 1) ? 0 : kTileBytes);
+                tma_load_4d(dst, map, full, 0, row, hk, b);
+                tma_load_4d(dst + kChunkBytes, map, full, 64, row, hk, b);
+                ++r;
+                return true;
+            };
             Item it;
             for (int seq = 0; ok && get_item(p, seq, &it); ++seq) {
+                if (it.n == 0) continue;
+                ok = load_entry(&map_k, 0, it.hk, it.b);  // K0 completes the previous item's last pair
+                if (!ok) break;
 #pragma unroll
                 for (int t = 0; t < 2; ++t) {
                     if (ok && it.ntile[t] > 0) {
@@ -193,28 +233,19 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                         tma_load_4d(dst + kChunkBytes, &map_q, bar(kBarQFull + t), 64, it.start[t], it.h, it.b);
                     }
                 }
-                for (int x = 0; ok && x < 2 * it.n; ++x, ++ring) {
-                    const int slot = ring % kStages;
-                    const uint32_t ph = (ring / kStages) & 1;
-                    ok = mbar_wait(bar(kBarKVEmpty + slot), ph ^ 1u, abort_flag, 2);
-                    if (!ok) break;
-                    const int j = x >> 1;
-                    const CUtensorMap* map = (x & 1) ? &map_v : &map_k;
-                    mbar_arrive_expect_tx(bar(kBarKVFull + slot), kTileBytes);
-                    const uint32_t dst = smem_base + kSmemKV + slot * kTileBytes;
-                    tma_load_4d(dst, map, bar(kBarKVFull + slot), 0, j * BN, it.hk, it.b);
-                    tma_load_4d(dst + kChunkBytes, map, bar(kBarKVFull + slot), 64, j * BN, it.hk, it.b);
-                }
+                for (int x = 1; ok && x < 2 * it.n; ++x)
+                    ok = load_entry((x & 1) ? &map_v : &map_k, (x >> 1) * BN, it.hk, it.b);
             }
+            if (ok && r > 0) mbar_arrive(bar(kBarKVFull + ((r >> 1) & 1)));  // the last pair has no K
         }
-    } else if (warp == kMmaWarp) {
+      } else if (warp == kMmaWarp) {
         // ------------------------------ MMA issuer --------------------------------
         if (lane == 0) {
             constexpr uint32_t idesc_qk = instr_desc_f16(BF16 ? 1 : 0, BM, BN, false, false);
             constexpr uint32_t idesc_pv = instr_desc_f16(BF16 ? 1 : 0, BM, HD, false, true);
-            auto issue_qk = [&](int t, int slot) {
+            auto issue_qk = [&](int t, int pair) {
                 const uint32_t qa = smem_base + kSmemQ + t * kTileBytes;
-                const uint32_t ka = smem_base + kSmemKV + slot * kTileBytes;
+                const uint32_t ka = smem_base + kSmemKV + (pair & 1) * kPairBytes + kTileBytes;
 #pragma unroll
                 for (int c = 0; c < 2; ++c)
 #pragma unroll
@@ -224,8 +255,8 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                                smem_desc_sw128(ka + off, 16, 1024), idesc_qk, (c | i) ? 1u : 0u);
                     }
             };
-            auto issue_pv = [&](int t, int slot, bool acc) {
-                const uint32_t va = smem_base + kSmemKV + slot * kTileBytes;
+            auto issue_pv = [&](int t, int pair, bool acc) {
+                const uint32_t va = smem_base + kSmemKV + (pair & 1) * kPairBytes;
 #pragma unroll
                 for (int ks = 0; ks < BN / 16; ++ks) {
                     // 16 keys = 16 rows of 128 B inside each 64-wide half of the head dim
@@ -235,33 +266,31 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                 }
             };
             bool ok = true;
-            int ring = 0;               // ring index of the current item's K0
+            int G = 0;                  // pair that holds the current item's K0 (and the previous item's last V)
+            bool have = false;          // pair G has already been waited for (by the previous item's last step)
             uint32_t qcnt[2] = {0, 0};   // items that used tile t (Q / O barriers)
             uint32_t pcnt[2] = {0, 0};   // softmax iterations of tile t so far (P barrier)
             Item it;
             for (int seq = 0; ok && get_item(p, seq, &it); ++seq) {
                 if (it.n == 0) continue;
-                ok = mbar_wait(bar(kBarKVFull + ring % kStages), (ring / kStages) & 1, abort_flag, 3);  // K0
+                if (!have) ok = mbar_wait(bar(kBarKVFull + (G & 1)), (G >> 1) & 1, abort_flag, 3);
 #pragma unroll
                 for (int t = 0; t < 2; ++t) {
                     if (ok && it.ntile[t] > 0) {
                         ok = mbar_wait(bar(kBarQFull + t), qcnt[t] & 1u, abort_flag, 4 + t);
                         if (ok) {
                             tc_fence_after_sync();
-                            issue_qk(t, ring % kStages);
+                            issue_qk(t, G);
                             tc_commit(bar(kBarSFull + t));
                             if (it.ntile[t] == 1) tc_commit(bar(kBarQEmpty + t));
                         }
                     }
                 }
                 if (!ok) break;
-                tc_commit(bar(kBarKVEmpty + ring % kStages));
+                tc_commit(bar(kBarKVEmpty + (G & 1)));  // after the previous item's last PV and these QK^T
                 for (int j = 0; ok && j < it.n; ++j) {
-                    const int item_v = ring + 2 * j + 1, item_k = ring + 2 * j + 2;
-                    const int slot_v = item_v % kStages, slot_k = item_k % kStages;
-                    ok = mbar_wait(bar(kBarKVFull + slot_v), (item_v / kStages) & 1, abort_flag, 3);
-                    if (ok && j + 1 < it.n)
-                        ok = mbar_wait(bar(kBarKVFull + slot_k), (item_k / kStages) & 1, abort_flag, 3);
+                    const int g = G + j + 1;  // (V_j, K_j+1)
+                    ok = mbar_wait(bar(kBarKVFull + (g & 1)), (g >> 1) & 1, abort_flag, 3);
                     if (!ok) break;
 #pragma unroll
                     for (int t = 0; t < 2; ++t) {
@@ -269,15 +298,13 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                             ok = mbar_wait(bar(kBarPFull + t), pcnt[t] & 1u, abort_flag, 6 + t);
                             if (!ok) break;
                             ++pcnt[t];
-                            if (j == 0) {
-                                // the first PV overwrites O_t: the previous item's epilogue has read it
-                                ok = mbar_wait(bar(kBarOEmpty + t), (qcnt[t] & 1u) ^ 1u, abort_flag, 8 + t);
-                                if (!ok) break;
-                            }
+                            // (the first PV of an item overwrites O_t: these warps read the previous
+                            // item's O_t out before they started on this item's first S tile, so the
+                            // P barrier covers that too)
                             tc_fence_after_sync();
-                            issue_pv(t, slot_v, j > 0);
+                            issue_pv(t, g, j > 0);
                             if (j + 1 < it.ntile[t]) {
-                                issue_qk(t, slot_k);
+                                issue_qk(t, g);
                                 tc_commit(bar(kBarSFull + t));
                                 if (j + 2 == it.ntile[t]) tc_commit(bar(kBarQEmpty + t));
                             } else {
@@ -286,18 +313,21 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                         }
                     }
                     if (!ok) break;
-                    tc_commit(bar(kBarKVEmpty + slot_v));
-                    if (j + 1 < it.n) tc_commit(bar(kBarKVEmpty + slot_k));
+                    // the last pair of the item also holds the next item's K0: released there
+                    if (j + 1 < it.n) tc_commit(bar(kBarKVEmpty + (g & 1)));
                 }
 #pragma unroll
                 for (int t = 0; t < 2; ++t)
                     if (it.ntile[t] > 0) ++qcnt[t];
-                ring += 2 * it.n;
+                G += it.n;
+                have = true;
             }
         }
         __syncwarp();
+      }
     } else {
         // ------------------------------ softmax + epilogue --------------------------
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsSoftmax));
         const int t = warp >> 2;
         const int wq = warp & 3;
         const uint32_t lane_base = uint32_t(wq * 32) << 16;
@@ -412,12 +442,6 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                 tmem_ld32(o_addr + 32 * c, o);
                 tmem_wait_ld();
                 tmem_ld_fence32(o);
-                if (c == 3) {
-                    // O_t is in registers: the next item's first PV may overwrite it
-                    tc_fence_before_sync();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(bar(kBarOEmpty + t));
-                }
                 if ((c & 1) == 0) {
                     if (lane == 0) tma_store_wait_read();  // the previous store has read the buffer
                     __syncwarp();
