@@ -27,10 +27,14 @@
 // traffic shares.
 //
 // Per kv tile j and query tile t:  S_t = Q_t K_j^T  (8 MMAs, K=16 each)
-//                                  P_t = exp2(S_t*c - m_t*c), row sums l_t, running max m_t
+//                                  P_t = exp2(S_t*c - m_t*c), row sums l_t
 //                                  O_t += P_t V_j     (8 MMAs)
-// O_t is rescaled in TMEM only when a row's max grew by more than 2^8 (the stale max is
-// used consistently for P and l, so the final O/l is exact).
+// m_t is a per-row reference, not the running max: it is the row max of the item's first kv
+// tile, and afterwards only moves (with O_t and l_t rescaled in TMEM) when a tile's row sum
+// shows that it has fallen behind by more than 2^8.  Any reference gives the exact O/l as long
+// as P, l and O use it consistently; not looking for each tile's max first takes a full pass
+// over the row off the chain  S ready -> P ready -> next S  that bounds the kernel.  A tile
+// whose sums say that P may overflow is redone against its true max before P is stored.
 //
 // Every wait is bounded (tc_prims.cuh); a wait that runs out raises the CTA's abort flag,
 // all roles fall through to the common exit, TMEM is freed and the GPU's status word is set to
@@ -65,7 +69,8 @@ constexpr int kThreads = 384;       // warps 10-11 only complete the third warpg
 constexpr int kRegsSoftmax = 200, kRegsIssue = 96;
 constexpr int kTmemCols = 512;
 constexpr int kColS = 0, kColO = 256;  // + 128 * tile
-constexpr float kRescaleThreshold = 8.0f;    // log2 units
+constexpr float kRescaleSum = 256.0f;         // a tile's row sum above this moves the reference
+constexpr float kRedoSum = 32768.0f;          // a tile's row sum above this (every P is below it) redoes the tile
 
 constexpr int kSmemQ = 0;
 constexpr int kSmemKV = kTilesPerCta * kTileBytes;
@@ -98,6 +103,7 @@ struct TcParams {
     int causal;
     float scale;
     float scale_log2;
+    float inv_scale_log2;
     int* status;
     int nq;      // 256-row query blocks per (batch, head)
     int npair;   // ceil(nq / 2)
@@ -343,86 +349,105 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             const int nt = it.ntile[t];
             if (nt == 0) continue;
             const int row_q = it.start[t] + wq * 32 + lane;
-            float m = -INFINITY, l = 0.f;
+            float m = -INFINITY, m_next = -INFINITY, l = 0.f;
+            bool move_ref = false;
             for (int j = 0; j < nt; ++j) {
                 ok = mbar_wait(bar(kBarSFull + t), scnt & 1u, abort_flag, 10 + t);
                 if (!ok) break;
                 ++scnt;
                 tc_fence_after_sync();
-                uint32_t s[BN];
-#pragma unroll
-                for (int c = 0; c < 4; ++c)
-                    tmem_ld32(s_addr + 32 * c, reinterpret_cast<uint32_t(&)[32]>(s[32 * c]));
-                tmem_wait_ld();
-#pragma unroll
-                for (int c = 0; c < 4; ++c) tmem_ld_fence32(reinterpret_cast<uint32_t(&)[32]>(s[32 * c]));
-
-                const int col0 = j * BN;
-                const bool need_mask = (p.causal && col0 + BN - 1 > it.start[t]) || (col0 + BN > p.Lk);
-                if (need_mask) {
-                    const int limit = (p.causal ? min(row_q, p.Lk - 1) : p.Lk - 1) - col0;
-#pragma unroll
-                    for (int i = 0; i < BN; ++i)
-                        if (i > limit) s[i] = 0xff800000u;  // -inf
-                }
-                float mx0 = -INFINITY, mx1 = -INFINITY;
-#pragma unroll
-                for (int i = 0; i < BN; i += 4) {
-                    mx0 = fmax3(mx0, __uint_as_float(s[i]), __uint_as_float(s[i + 1]));
-                    mx1 = fmax3(mx1, __uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]));
-                }
-                const float mx = fmaxf(mx0, mx1);
-
-                float alpha = 1.f;
-                bool grew = false;
-                if (j == 0) {
-                    m = mx;
-                } else {
-                    const float m_new = fmaxf(m, mx);
-                    if ((m_new - m) * c2 > kRescaleThreshold) {
-                        alpha = ex2_approx((m - m_new) * c2);
-                        l *= alpha;
-                        m = m_new;
-                        grew = true;
-                    }
-                }
-                if (j > 0 && __any_sync(0xffffffffu, grew)) {
-                    // PV_t(j-1) has completed (S_t(j) was committed after it) and PV_t(j) waits
-                    // for this tile's P barrier, so O_t is quiescent here.
+                // O_t *= alpha (per row), in TMEM.  PV_t(j-1) has completed (S_t(j) was committed
+                // after it) and PV_t(j) waits for this tile's P barrier, so O_t is quiescent here.
+                auto rescale_o = [&](float alpha) {
 #pragma unroll 1
-                    for (int c = 0; c < 4; ++c) {
-                        uint32_t o[32];
-                        tmem_ld32(o_addr + 32 * c, o);
+                    for (int c = 0; c < 8; ++c) {
+                        uint32_t o[16];
+                        tmem_ld16(o_addr + 16 * c, o);
                         tmem_wait_ld();
-                        tmem_ld_fence32(o);
+                        tmem_ld_fence16(o);
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                        tmem_st32(o_addr + 32 * c, o);
+                        for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                        tmem_st16(o_addr + 16 * c, o);
                     }
+                };
+                // Only the item's first tile looks for its row max before exponentiating: that pass
+                // heads the tile's dependency chain (S ready -> P ready -> next S ...).  Later tiles
+                // exponentiate against the reference m they are given, and the row sum they get
+                // tells whether m was good enough:
+                //   sum > kRedoSum (or not finite): a P could overflow.  P has not been stored yet,
+                //       so S_t is intact: load it again, take the row's max as m, and redo (rare)
+                //   sum > kRescaleSum: m moves up by log2(sum)/c from the next tile on
+                // Any reference gives the exact O/l as long as l and O are rescaled when it moves,
+                // so m need not be the true max.
+                if (j > 0 && move_ref) {  // voted on after the previous hand-over, while waiting for this S
+                    const float alpha = ex2_approx((m - m_next) * c2);  // 1 for rows that keep theirs
+                    l *= alpha;
+                    rescale_o(alpha);
+                    m = m_next;
                 }
-                // two columns per instruction on the FMA pipe (fp32x2 FMA / ADD)
-                const float neg_m = -m * c2;
-                const float2 c22 = make_float2(c2, c2), nm2 = make_float2(neg_m, neg_m);
-                float2 ls0 = make_float2(0.f, 0.f), ls1 = make_float2(0.f, 0.f);
+                uint32_t pk[BN / 2];
+                float l_tile;
+                bool bad = false;
+#pragma unroll 1
+                for (int attempt = 0;; ++attempt) {
+                    uint32_t s[BN];
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    uint32_t pk[16];
+                    for (int c = 0; c < 4; ++c)
+                        tmem_ld32(s_addr + 32 * c, reinterpret_cast<uint32_t(&)[32]>(s[32 * c]));
+                    tmem_wait_ld();
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        const int e = 32 * c + 2 * i;
-                        const float2 x = ffma2(make_float2(__uint_as_float(s[e]), __uint_as_float(s[e + 1])), c22, nm2);
+                    for (int c = 0; c < 4; ++c) tmem_ld_fence32(reinterpret_cast<uint32_t(&)[32]>(s[32 * c]));
+                    const int col0 = j * BN;
+                    const bool need_mask = (p.causal && col0 + BN - 1 > it.start[t]) || (col0 + BN > p.Lk);
+                    if (need_mask) {
+                        const int limit = (p.causal ? min(row_q, p.Lk - 1) : p.Lk - 1) - col0;
+#pragma unroll
+                        for (int i = 0; i < BN; ++i)
+                            if (i > limit) s[i] = 0xff800000u;  // -inf
+                    }
+                    if (j == 0 || attempt == 1) {
+                        float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+                        for (int i = 0; i < BN; i += 4) {
+                            mx0 = fmax3(mx0, __uint_as_float(s[i]), __uint_as_float(s[i + 1]));
+                            mx1 = fmax3(mx1, __uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]));
+                        }
+                        const float m_new = (j == 0 || bad) ? fmaxf(mx0, mx1) : m;
+                        if (j > 0) {
+                            const float alpha = ex2_approx((m - m_new) * c2);
+                            l *= alpha;
+                            rescale_o(alpha);
+                        }
+                        m = m_new;
+                    }
+                    // two columns per instruction on the FMA pipe (fp32x2 FMA / ADD)
+                    const float neg_m = -m * c2;
+                    const float2 c22 = make_float2(c2, c2), nm2 = make_float2(neg_m, neg_m);
+                    float2 ls0 = make_float2(0.f, 0.f), ls1 = make_float2(0.f, 0.f);
+#pragma unroll
+                    for (int i = 0; i < BN / 2; ++i) {
+                        const float2 x = ffma2(make_float2(__uint_as_float(s[2 * i]), __uint_as_float(s[2 * i + 1])), c22, nm2);
                         const float p0 = ex2_approx(x.x), p1 = ex2_approx(x.y);
                         if (i & 1) ls1 = fadd2(ls1, make_float2(p0, p1));
                         else ls0 = fadd2(ls0, make_float2(p0, p1));
                         pk[i] = pack16<BF16>(p0, p1);
                     }
-                    tmem_st16(s_addr + 16 * c, pk);  // P_t over the first 64 columns of S_t
+                    l_tile = (ls0.x + ls0.y) + (ls1.x + ls1.y);
+                    if (j == 0 || attempt == 1) break;
+                    bad = !(l_tile <= kRedoSum);
+                    if (!__any_sync(0xffffffffu, bad)) break;
                 }
-                l += (ls0.x + ls0.y) + (ls1.x + ls1.y);
+#pragma unroll
+                for (int c = 0; c < 4; ++c)  // P_t over the first 64 columns of S_t
+                    tmem_st16(s_addr + 16 * c, reinterpret_cast<uint32_t(&)[16]>(pk[16 * c]));
+                l += l_tile;
                 tmem_wait_st();
                 tc_fence_before_sync();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar(kBarPFull + t));
+                // off the chain: these warps now wait for the tensor core anyway
+                m_next = l_tile > kRescaleSum ? m + lg2_approx(l_tile) * p.inv_scale_log2 : m;
+                move_ref = __any_sync(0xffffffffu, m_next != m);
             }
             if (!ok) break;
             ok = mbar_wait(bar(kBarOFull + t), ocnt & 1u, abort_flag, 16 + t);
@@ -578,6 +603,7 @@ int sdpa_tc_launch(Gpu* g, const paras_sdpa_args& a, float scale, cudaStream_t s
     p.causal = a.causal;
     p.scale = scale;
     p.scale_log2 = scale * 1.4426950408889634f;
+    p.inv_scale_log2 = 1.0f / p.scale_log2;
     p.status = g->status_dev;
     p.nq = (a.Lq + kTilesPerCta * BM - 1) / (kTilesPerCta * BM);
     p.npair = (p.nq + 1) / 2;

@@ -296,6 +296,12 @@ __device__ __forceinline__ float ex2_approx(float x) {
 #endif
 }
 
+__device__ __forceinline__ float lg2_approx(float x) {
+    float y;
+    asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 // Packed fp32 pairs (one instruction for two lanes of the FMA pipe) and 3-input max.
 __device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
     uint64_t ra, rb, rc, rd;

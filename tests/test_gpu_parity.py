@@ -193,6 +193,39 @@ def test_sdpa_strided_inputs_and_lse():
     assert torch.allclose(lse.cpu(), torch.logsumexp(s, -1), atol=2e-3, rtol=2e-3)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("causal", [True, False])
+@pytest.mark.parametrize("factor", [3.0, 6.0, 30.0, 200.0])
+def test_sdpa_scores_that_grow_from_tile_to_tile(factor, causal, dtype):
+    # Every third 128-key tile has keys scaled up, more so the later it comes, so a row's
+    # largest score keeps moving as the kernel walks the keys: by a little (the reference of
+    # the online softmax moves lazily), and by far more than the exponent range of the
+    # probabilities (the tile has to be redone against its own max).
+    B, Hq, Hkv, L = 1, 2, 1, 1024
+    q, k, v = _qkv(B, Hq, Hkv, L, L, 128, dtype, seed=17)
+    for j in range(L // 128):
+        if j % 3 == 2:
+            k[:, :, 128 * j:128 * (j + 1)] *= factor * (1 + j) / 8.0
+    # Checked against float64 attention, not against the reference's numerics: the reference
+    # rounds the scores to 16 bits before the softmax (attention_ops.cpp:96-118), which at
+    # scores of this size (tens to thousands) is an error of whole units in the exponent.
+    got, lse = abi.sdpa_fwd(q.to(DEV), k.to(DEV), v.to(DEV), causal=causal, return_lse=True,
+                            flags=abi.SDPA_REF_SCALE)
+    assert abi.sdpa_last_kernel() == "tcgen05"
+    sc = float(torch.tensor(1 / math.sqrt(128)).to(dtype))
+    s = (q.double() @ k.double().repeat_interleave(Hq // Hkv, 1).transpose(-1, -2)) * sc
+    if causal:
+        s = s.masked_fill(~torch.ones(L, L, dtype=torch.bool).tril(), float("-inf"))
+    want = torch.softmax(s, -1) @ v.double().repeat_interleave(Hq // Hkv, 1)
+    g = got.cpu().double()
+    assert torch.isfinite(g).all()
+    # 2e-2 relative to max(1, |want|): the softmax is nearly one-hot for the larger factors, so
+    # outputs are single V entries of size up to 4 and more (one bf16 ulp at 4 is 3.1e-2)
+    err = ((g - want).abs() / want.abs().clamp(min=1.0)).max().item()
+    assert err <= 2e-2, f"growing scores x{factor} causal={causal} {dtype}: {err:.3e}"
+    assert torch.allclose(lse.cpu().double(), torch.logsumexp(s, -1), atol=2e-3, rtol=2e-3)
+
+
 def test_sdpa_empty_and_degenerate_shapes():
     z = torch.empty(1, 2, 0, 128, dtype=torch.bfloat16, device=DEV)
     kv = torch.randn(1, 2, 16, 128, device=DEV).bfloat16()
