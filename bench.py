@@ -374,6 +374,23 @@ def run_ours(args):
         res["global_batch_all_ranks"] = Bp * world
         extra["config5_decoder_block_share"] = res
         del xh, qb, kb, vb, gb, ub, y1, ob, y2, sb
+    if want("gemm"):
+        # The projections either side of the path at config 2 / 5 sizes (hidden 4096, FFN 14336):
+        # fused QKV projection [rows,4096] x [6144,4096]^T (Hq=32, Hkv=8, D=128) and the gate/up
+        # projection with SwiGLU in the epilogue; FLOPs = 2*M*N*K (x2 for the two FFN weights).
+        rows = 4096 if args.small else 16384
+        xg = gen((rows, 4096), 21)
+        wqkv = gen((6144, 4096), 22, std=0.02)
+        wgate, wup = gen((14336, 4096), 23, std=0.02), gen((14336, 4096), 24, std=0.02)
+        oq = torch.empty((rows, 6144), dtype=torch.bfloat16, device=dev)
+        of = torch.empty((rows, 14336), dtype=torch.bfloat16, device=dev)
+        t = loop_ms(lambda: abi.gemm(xg, wqkv, out=oq), s3, 3)
+        tf = 2.0 * rows * 6144 * 4096 / (t * 1e-3) / 1e12
+        extra[f"gemm_qkv_{rows}x6144x4096"] = {"ms": t, "tflops": tf, "frac_of_bf16_peak": tf / peaks["bf16_tflops"]}
+        t = loop_ms(lambda: abi.gemm(xg, wgate, up_weight=wup, out=of), s3, 3)
+        tf = 4.0 * rows * 14336 * 4096 / (t * 1e-3) / 1e12
+        extra[f"gemm_swiglu_{rows}x14336x4096"] = {"ms": t, "tflops": tf, "frac_of_bf16_peak": tf / peaks["bf16_tflops"]}
+        del xg, wqkv, wgate, wup, oq, of
     torch.cuda.empty_cache()
 
     if only:
@@ -458,7 +475,7 @@ def main():
     ap.add_argument("--small", action="store_true",
                     help="shrink the extra workloads (SwiGLU 8192 rows, decode batch 8) so that a profiler "
                          "capture holds about 1 GB on the device; rates stay per-byte comparable")
-    ap.add_argument("--only", choices=["rmsnorm", "swiglu", "gqa", "decode", "block"],
+    ap.add_argument("--only", choices=["rmsnorm", "swiglu", "gqa", "decode", "block", "gemm"],
                     help="after the headline loop run just this extra workload and print it (for profiling)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-repeat", type=int, default=3)

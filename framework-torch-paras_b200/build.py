@@ -26,9 +26,9 @@ PKG = os.path.join(HERE, "python", "torch_paras")
 OBJ = os.path.join(HERE, "build")
 
 CUDA_SOURCES = ["runtime.cu", "elementwise.cu", "rmsnorm.cu", "sdpa.cu", "sdpa_simt.cu",
-                "sdpa_tc.cu", "sdpa_decode.cu"]
+                "sdpa_tc.cu", "sdpa_decode.cu", "gemm_tc.cu"]
 EXT_SOURCES = ["core/device_runtime.cpp", "ops/lifecycle_ops.cpp", "ops/attention_ops.cpp",
-               "ops/norm_glu_ops.cpp", "python/module.cpp"]
+               "ops/norm_glu_ops.cpp", "ops/matmul_ops.cpp", "python/module.cpp"]
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-diag-suppress", "177,550"]

@@ -1,0 +1,374 @@
+// 16-bit GEMM for sm_100a with fp32 accumulation in TMEM: the projections on either side of
+// the attention / RMSNorm / SwiGLU path (mm, bmm, addmm, linear: csrc/ops/vision_ops.cpp:
+// 248-309, 388-423 hand these to the host's libtorch and copy the result back).
+//
+//   C[b][M,N] = A[b][M,K] * B[b]        A: rows of K contiguous elements
+//                                       B: [N,K] rows of K (a Linear weight), or [K,N] rows of N
+//   epilogues: none | + bias[N] | SwiGLU: C[M,F] = silu(A Wg^T) * (A Wu^T) from one pass over A
+//
+// Persistent CTAs, one per SM, 128 x 256 output tiles, K in steps of 64:
+//   warps 0-3  epilogue: TMEM -> registers -> 16 bit -> swizzled shared memory -> TMA store
+//   warp  4    allocates TMEM; one lane issues tcgen05.mma (M128 x N256 x K16, 4 per K step)
+//   warp  5    one lane issues the TMA loads: 4-stage ring of (A 16 KB, B 32 KB)
+// TMEM holds two 256-column accumulators, so the epilogue of a tile runs under the next
+// tile's main loop.  For SwiGLU the B tile is 128 rows of the gate weight followed by 128
+// rows of the up weight: one N=256 MMA leaves [gate | up] side by side in the accumulator.
+// Tiles are taken in an order that keeps a 16 x 9 block of tiles (its A and B panels fit in
+// L2 many times over) in flight at a time.
+//
+// Every wait is bounded (tc_prims.cuh); a wait that runs out raises the CTA's abort flag, all
+// roles leave through the common exit, TMEM is freed and the GPU's status word is set.
+#include <cmath>
+
+#include "common.cuh"
+#include "tc_prims.cuh"
+#include "tma_host.cuh"
+
+namespace pb {
+namespace {
+
+using namespace tc;
+
+constexpr int BM = 128, BN = 256, BK = 64;
+constexpr int kStages = 4;
+constexpr int kABytes = BM * BK * 2;         // 16 KB
+constexpr int kBBytes = BN * BK * 2;         // 32 KB
+constexpr int kStageBytes = kABytes + kBBytes;
+constexpr int kEpiWarps = 4;
+constexpr int kMmaWarp = 4, kLoadWarp = 5;
+constexpr int kThreads = 192;
+constexpr int kTmemCols = 512;               // two accumulators of BN columns
+constexpr int kOutStage = 32 * 128;          // 32 rows x 64 columns of 16 bit
+constexpr int kGroupM = 16;                  // tile order: 16 row blocks at a time
+
+constexpr int kSmemOut = kStages * kStageBytes;                 // [4 warps][2] staging buffers
+constexpr int kSmemBars = kSmemOut + kEpiWarps * 2 * kOutStage;
+constexpr int kBarFull = 0, kBarEmpty = kStages, kBarAccFull = 2 * kStages, kBarAccEmpty = 2 * kStages + 2;
+constexpr int kNumBars = 2 * kStages + 4;
+constexpr int kSmemMisc = kSmemBars + kNumBars * 8;             // tmem base word, abort flag
+constexpr int kSmemTotal = kSmemMisc + 16;
+
+enum { kEpiNone = 0, kEpiBias = 1, kEpiSwiglu = 2 };
+
+__device__ int g_gemm_abort_latch = 0;
+
+struct GemmParams {
+    int M, N, K;          // N = output columns (for SwiGLU: F)
+    int batch;
+    int tiles_m, tiles_n, tiles;   // per batch: tiles_m * tiles_n; tiles = all batches
+    int k_iters;
+    const void* bias;
+    int* status;
+};
+
+struct Tile { int b, m0, n0; };
+
+__device__ __forceinline__ Tile get_tile(const GemmParams& p, int id, int n_per_tile) {
+    const int per_batch = p.tiles_m * p.tiles_n;
+    Tile t;
+    t.b = id / per_batch;
+    const int r = id - t.b * per_batch;
+    const int in_group = kGroupM * p.tiles_n;
+    const int group = r / in_group;
+    const int first_m = group * kGroupM;
+    const int gm = min(p.tiles_m - first_m, kGroupM);
+    const int q = r - group * in_group;
+    t.m0 = (first_m + q % gm) * BM;
+    t.n0 = (q / gm) * n_per_tile;
+    return t;
+}
+
+template <bool BF16, bool B_ROWS_OF_N, int EPI>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+               const __grid_constant__ CUtensorMap map_b2, const __grid_constant__ CUtensorMap map_c,
+               const GemmParams p) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    const uint32_t smem_base = smem_u32(smem_raw);
+    auto bar = [&](int i) { return smem_base + kSmemBars + 8u * i; };
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_raw + kSmemMisc);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_raw + kSmemMisc + 4);
+    constexpr int kNPerTile = EPI == kEpiSwiglu ? BN / 2 : BN;   // output columns per tile
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (*reinterpret_cast<volatile int*>(&g_gemm_abort_latch)) return;  // uniform: before any barrier or TMEM use
+    if (smem_base & 1023u) {
+        // the 128-byte swizzle of TMA and of the MMA descriptors assumes 1024-byte aligned tiles
+        if (threadIdx.x == 0) {
+            g_gemm_abort_latch = 1;
+            *p.status = int(0x40000000u | (1u << 29));
+            __threadfence_system();
+        }
+        return;
+    }
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < kNumBars; ++i) mbar_init(bar(i), i >= kBarAccEmpty ? uint32_t(kEpiWarps) : 1u);
+        *abort_flag = 0;
+        mbar_fence_init();
+        fence_proxy_async_smem();
+    }
+    if (warp == kMmaWarp) {
+        tmem_alloc(smem_base + kSmemMisc, kTmemCols);
+        tmem_relinquish();
+    }
+    if (warp == kLoadWarp && lane == 0) {
+        tma_prefetch_desc(&map_a);
+        tma_prefetch_desc(&map_b);
+        if (EPI == kEpiSwiglu) tma_prefetch_desc(&map_b2);
+        tma_prefetch_desc(&map_c);
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == kLoadWarp) {
+        // ------------------------------ TMA producer ------------------------------
+        if (lane == 0) {
+            bool ok = true;
+            int it = 0;  // K steps loaded so far, across tiles
+            for (int id = blockIdx.x; ok && id < p.tiles; id += gridDim.x) {
+                const Tile t = get_tile(p, id, kNPerTile);
+                for (int kk = 0; kk < p.k_iters; ++kk, ++it) {
+                    const int st = it % kStages;
+                    ok = mbar_wait(bar(kBarEmpty + st), ((it / kStages) & 1) ^ 1u, abort_flag, 0);
+                    if (!ok) break;
+                    const uint32_t full = bar(kBarFull + st);
+                    mbar_arrive_expect_tx(full, kStageBytes);
+                    const uint32_t a_dst = smem_base + st * kStageBytes;
+                    const uint32_t b_dst = a_dst + kABytes;
+                    tma_load_3d(a_dst, &map_a, full, kk * BK, t.m0, t.b);
+                    if (B_ROWS_OF_N) {
+                        // B is [K, N]: four 64-column slabs of 64 K-rows each
+#pragma unroll
+                        for (int i = 0; i < BN / 64; ++i)
+                            tma_load_3d(b_dst + i * (BK * 128), &map_b, full, t.n0 + 64 * i, kk * BK, t.b);
+                    } else if (EPI == kEpiSwiglu) {
+                        tma_load_3d(b_dst, &map_b, full, kk * BK, t.n0, t.b);                // gate rows
+                        tma_load_3d(b_dst + kBBytes / 2, &map_b2, full, kk * BK, t.n0, t.b);  // up rows
+                    } else {
+                        tma_load_3d(b_dst, &map_b, full, kk * BK, t.n0, t.b);
+                    }
+                }
+            }
+        }
+    } else if (warp == kMmaWarp) {
+        // ------------------------------ MMA issuer --------------------------------
+        if (lane == 0) {
+            constexpr uint32_t idesc = instr_desc_f16(BF16 ? 1 : 0, BM, BN, false, B_ROWS_OF_N);
+            bool ok = true;
+            int it = 0, local = 0;
+            for (int id = blockIdx.x; ok && id < p.tiles; id += gridDim.x, ++local) {
+                const int buf = local & 1;
+                // the epilogue has read this accumulator's previous tile
+                ok = mbar_wait(bar(kBarAccEmpty + buf), ((local >> 1) & 1) ^ 1u, abort_flag, 1);
+                if (!ok) break;
+                const uint32_t d_tm = tmem + buf * BN;
+                for (int kk = 0; kk < p.k_iters; ++kk, ++it) {
+                    const int st = it % kStages;
+                    ok = mbar_wait(bar(kBarFull + st), (it / kStages) & 1, abort_flag, 2);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    const uint32_t a_addr = smem_base + st * kStageBytes;
+                    const uint32_t b_addr = a_addr + kABytes;
+#pragma unroll
+                    for (int ks = 0; ks < BK / 16; ++ks) {
+                        const uint64_t a_desc = smem_desc_sw128(a_addr + ks * 32, 16, 1024);
+                        const uint64_t b_desc = B_ROWS_OF_N
+                            ? smem_desc_sw128(b_addr + ks * 16 * 128, BK * 128, 1024)
+                            : smem_desc_sw128(b_addr + ks * 32, 16, 1024);
+                        mma_ss(d_tm, a_desc, b_desc, idesc, (kk | ks) ? 1u : 0u);
+                    }
+                    tc_commit(bar(kBarEmpty + st));
+                }
+                if (!ok) break;
+                tc_commit(bar(kBarAccFull + buf));
+            }
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------ epilogue -----------------------------------
+        const int wq = warp;  // TMEM lanes 32*wq .. 32*wq+31
+        const uint32_t lane_base = uint32_t(wq * 32) << 16;
+        const uint32_t stage0 = smem_base + kSmemOut + wq * 2 * kOutStage;
+        bool ok = true;
+        int local = 0;
+        uint32_t nstore = 0;  // stores issued by this warp (picks the staging buffer)
+        for (int id = blockIdx.x; ok && id < p.tiles; id += gridDim.x, ++local) {
+            const Tile t = get_tile(p, id, kNPerTile);
+            const int buf = local & 1;
+            ok = mbar_wait<32>(bar(kBarAccFull + buf), (local >> 1) & 1, abort_flag, 3);
+            if (!ok) break;
+            tc_fence_after_sync();
+            const uint32_t acc = tmem + lane_base + buf * BN;
+            const int row_w = t.m0 + wq * 32;
+            constexpr int kChunks = kNPerTile / 64;  // 64 output columns per store
+#pragma unroll 1
+            for (int c = 0; c < kChunks; ++c) {
+                uint32_t out[32];  // 64 outputs, packed in pairs
+                if (EPI == kEpiSwiglu) {
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        uint32_t g[32], u[32];
+                        tmem_ld32(acc + 64 * c + 32 * h, g);
+                        tmem_ld32(acc + BN / 2 + 64 * c + 32 * h, u);
+                        tmem_wait_ld();
+                        tmem_ld_fence32(g);
+                        tmem_ld_fence32(u);
+#pragma unroll
+                        for (int i = 0; i < 32; i += 2) {
+                            // the two projections are rounded to the tensor dtype as separate
+                            // GEMMs would leave them; silu(g)*u is then rounded once
+                            float r[2];
+#pragma unroll
+                            for (int e = 0; e < 2; ++e) {
+                                const float gg = round16<BF16>(__uint_as_float(g[i + e]));
+                                const float uu = round16<BF16>(__uint_as_float(u[i + e]));
+                                r[e] = gg / (1.0f + __expf(-gg)) * uu;
+                            }
+                            out[16 * h + i / 2] = pack16<BF16>(r[0], r[1]);
+                        }
+                    }
+                } else {
+                    uint32_t o[64];
+                    tmem_ld32(acc + 64 * c, reinterpret_cast<uint32_t(&)[32]>(o[0]));
+                    tmem_ld32(acc + 64 * c + 32, reinterpret_cast<uint32_t(&)[32]>(o[32]));
+                    tmem_wait_ld();
+                    tmem_ld_fence32(reinterpret_cast<uint32_t(&)[32]>(o[0]));
+                    tmem_ld_fence32(reinterpret_cast<uint32_t(&)[32]>(o[32]));
+#pragma unroll
+                    for (int i = 0; i < 64; i += 2) {
+                        float x0 = __uint_as_float(o[i]), x1 = __uint_as_float(o[i + 1]);
+                        if (EPI == kEpiBias) {
+                            const int col = t.n0 + 64 * c + i;
+                            const uint16_t* bias = static_cast<const uint16_t*>(p.bias);
+                            if (col < p.N) x0 += from16<BF16>(bias[col]);
+                            if (col + 1 < p.N) x1 += from16<BF16>(bias[col + 1]);
+                        }
+                        out[i / 2] = pack16<BF16>(x0, x1);
+                    }
+                }
+                if (c == kChunks - 1) {
+                    // the accumulator is in registers: the MMA warp may start the tile after next
+                    tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar(kBarAccEmpty + buf));
+                }
+                const uint32_t stage = stage0 + (nstore & 1u) * kOutStage;
+                if (lane == 0) tma_store_wait_read_but_last();  // the store before last has read this buffer
+                __syncwarp();
+#pragma unroll
+                for (int v = 0; v < 8; ++v)
+                    st_shared_v4(stage + lane * 128 + ((v ^ (lane & 7)) << 4),
+                                 make_uint4(out[4 * v], out[4 * v + 1], out[4 * v + 2], out[4 * v + 3]));
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    if (row_w < p.M && t.n0 + 64 * c < p.N)
+                        tma_store_3d(&map_c, stage, t.n0 + 64 * c, row_w, t.b);
+                    tma_store_commit();  // always: the waits above count groups
+                }
+                ++nstore;
+            }
+        }
+        if (lane == 0) tma_store_wait_read();  // shared memory stays valid until the last store has read it
+    }
+
+    // ------------------------------ common exit ------------------------------------
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == kMmaWarp) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem, kTmemCols);
+    }
+    if (threadIdx.x == 0 && *abort_flag) {
+        g_gemm_abort_latch = 1;
+        *p.status = *abort_flag;
+        __threadfence_system();
+    }
+}
+
+bool aligned16(const void* ptr, int64_t ld) {
+    return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0 && ld % 8 == 0 && ld > 0;
+}
+
+template <bool BF16, bool B_ROWS_OF_N, int EPI>
+int launch(Gpu* g, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mb2,
+           const CUtensorMap& mc, const GemmParams& p, cudaStream_t s) {
+    auto kernel = gemm_tc_kernel<BF16, B_ROWS_OF_N, EPI>;
+    PB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal));
+    const int sms = g->sm_count > 0 ? g->sm_count : 148;
+    kernel<<<dim3(unsigned(p.tiles < sms ? p.tiles : sms)), kThreads, kSmemTotal, s>>>(ma, mb, mb2, mc, p);
+    PB_LAUNCH_CHECK("gemm_tc_kernel");
+    return PARAS_OK;
+}
+
+}  // namespace
+}  // namespace pb
+
+extern "C" int paras_b200_gemm(const paras_gemm_args* a) {
+    using namespace pb;
+    if (!a) return fail(PARAS_E_INVALID, "paras gemm: null args");
+    if (a->dtype != PARAS_BF16 && a->dtype != PARAS_F16)
+        return fail(PARAS_E_UNSUPPORTED, "paras gemm: only 16-bit tensors run on the tensor-core kernel");
+    if (a->M < 0 || a->N < 0 || a->K < 0 || a->batch < 0)
+        return fail(PARAS_E_INVALID, "paras gemm: negative size");
+    if (a->epilogue < kEpiNone || a->epilogue > kEpiSwiglu)
+        return fail(PARAS_E_INVALID, "paras gemm: bad epilogue %d", a->epilogue);
+    if (a->b_layout != PARAS_GEMM_B_NK && a->b_layout != PARAS_GEMM_B_KN)
+        return fail(PARAS_E_INVALID, "paras gemm: bad b_layout %d", a->b_layout);
+    int st;
+    Gpu* g = use_gpu(a->gpu, &st);
+    if (!g) return st;
+    if (g->cc_major != 10) return fail(PARAS_E_UNSUPPORTED, "paras gemm: GPU is not compute capability 10.x");
+    if (a->M == 0 || a->N == 0 || a->batch == 0) return PARAS_OK;
+    if (a->K == 0) return fail(PARAS_E_UNSUPPORTED, "paras gemm: K = 0");
+    if (a->M > INT32_MAX || a->N > INT32_MAX || a->K > INT32_MAX || a->batch > 65535)
+        return fail(PARAS_E_UNSUPPORTED, "paras gemm: sizes exceed 32-bit tile coordinates");
+    if (!a->a || !a->b || !a->c) return fail(PARAS_E_INVALID, "paras gemm: null pointer");
+    if (a->epilogue == kEpiBias && !a->bias) return fail(PARAS_E_INVALID, "paras gemm: bias epilogue without bias");
+    if (a->epilogue == kEpiSwiglu && (!a->b2 || a->b_layout != PARAS_GEMM_B_NK))
+        return fail(PARAS_E_INVALID, "paras gemm: the SwiGLU epilogue takes two [F,K] weights");
+    if (!aligned16(a->a, a->lda) || !aligned16(a->b, a->ldb) || !aligned16(a->c, a->ldc) ||
+        (a->epilogue == kEpiSwiglu && !aligned16(a->b2, a->ldb)) ||
+        (a->batch > 1 && (a->stride_a % 8 || a->stride_b % 8 || a->stride_c % 8)))
+        return fail(PARAS_E_UNSUPPORTED, "paras gemm: pointers or strides are not 16-byte aligned");
+    if (g->smem_optin < size_t(kSmemTotal)) return fail(PARAS_E_UNSUPPORTED, "paras gemm: not enough shared memory");
+    if ((st = check_status_word(g)) != PARAS_OK) {
+        const int zero = 0;
+        cudaMemcpyToSymbol(g_gemm_abort_latch, &zero, sizeof(int));
+        return st;
+    }
+
+    const bool kn = a->b_layout == PARAS_GEMM_B_KN;
+    const int n_per_tile = a->epilogue == kEpiSwiglu ? BN / 2 : BN;
+    CUtensorMap ma, mb, mb2, mc;
+    if ((st = make_tensor_map_3d(&ma, a->a, a->dtype, a->K, a->M, a->batch, a->lda, a->stride_a, BK, BM)) != PARAS_OK) return st;
+    if (kn) {
+        if ((st = make_tensor_map_3d(&mb, a->b, a->dtype, a->N, a->K, a->batch, a->ldb, a->stride_b, 64, BK)) != PARAS_OK) return st;
+    } else {
+        if ((st = make_tensor_map_3d(&mb, a->b, a->dtype, a->K, a->N, a->batch, a->ldb, a->stride_b, BK, n_per_tile)) != PARAS_OK) return st;
+    }
+    mb2 = mb;
+    if (a->epilogue == kEpiSwiglu &&
+        (st = make_tensor_map_3d(&mb2, a->b2, a->dtype, a->K, a->N, a->batch, a->ldb, a->stride_b, BK, n_per_tile)) != PARAS_OK) return st;
+    if ((st = make_tensor_map_3d(&mc, a->c, a->dtype, a->N, a->M, a->batch, a->ldc, a->stride_c, 64, 32)) != PARAS_OK) return st;
+
+    GemmParams p{};
+    p.M = int(a->M); p.N = int(a->N); p.K = int(a->K); p.batch = int(a->batch);
+    p.tiles_m = int((a->M + BM - 1) / BM);
+    p.tiles_n = int((a->N + n_per_tile - 1) / n_per_tile);
+    const int64_t tiles = int64_t(p.tiles_m) * p.tiles_n * p.batch;
+    if (tiles > INT32_MAX) return fail(PARAS_E_UNSUPPORTED, "paras gemm: too many tiles");
+    p.tiles = int(tiles);
+    p.k_iters = int((a->K + BK - 1) / BK);
+    p.bias = a->bias;
+    p.status = g->status_dev;
+    cudaStream_t s = pick_stream(g, a->stream);
+    const bool bf = a->dtype == PARAS_BF16;
+#define PB_GEMM(KN, EPI) (bf ? launch<true, KN, EPI>(g, ma, mb, mb2, mc, p, s) : launch<false, KN, EPI>(g, ma, mb, mb2, mc, p, s))
+    if (a->epilogue == kEpiSwiglu) return PB_GEMM(false, kEpiSwiglu);
+    if (a->epilogue == kEpiBias) return kn ? PB_GEMM(true, kEpiBias) : PB_GEMM(false, kEpiBias);
+    return kn ? PB_GEMM(true, kEpiNone) : PB_GEMM(false, kEpiNone);
+#undef PB_GEMM
+}

@@ -120,6 +120,22 @@ __device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, uint32_t sr
         ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src_smem), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
         : "memory");
 }
+// 3-D forms (GEMM operands: inner dim, rows, batch)
+__device__ __forceinline__ void tma_load_3d(uint32_t dst_smem, const CUtensorMap* map, uint32_t bar,
+                                            int c0, int c1, int c2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cta.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst_smem), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t src_smem,
+                                             int c0, int c1, int c2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+        ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src_smem), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
 __device__ __forceinline__ void tma_store_commit() {
     asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
@@ -338,6 +354,22 @@ __device__ __forceinline__ uint32_t pack16(float lo, float hi) {
         asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
     }
     return r;
+}
+
+// One 16-bit value (raw bits) -> fp32, and fp32 rounded to the 16-bit type and back.
+template <bool BF16>
+__device__ __forceinline__ float from16(uint16_t bits) {
+    if constexpr (BF16) {
+        return __uint_as_float(uint32_t(bits) << 16);
+    } else {
+        float r;
+        asm("cvt.f32.f16 %0, %1;" : "=f"(r) : "h"(bits));
+        return r;
+    }
+}
+template <bool BF16>
+__device__ __forceinline__ float round16(float x) {
+    return from16<BF16>(uint16_t(pack16<BF16>(x, 0.f) & 0xffffu));
 }
 
 }  // namespace tc

@@ -34,7 +34,7 @@ EXPORTS = [
     "paras_b200_sdpa_workspace_bytes", "paras_b200_sdpa_last_kernel", "paras_b200_rmsnorm_fwd",
     "paras_b200_sdpa_fwd_static_scratch", "paras_b200_sdpa_static_scratch_bytes",
     "paras_b200_rmsnorm_bwd", "paras_b200_swiglu_fwd", "paras_b200_swiglu_bwd",
-    "paras_b200_rotate_half",
+    "paras_b200_rotate_half", "paras_b200_gemm",
 ]
 
 
@@ -52,6 +52,22 @@ class SdpaArgs(C.Structure):
     ]
 
 
+class GemmArgs(C.Structure):
+    _fields_ = [
+        ("a", C.c_void_p), ("b", C.c_void_p), ("b2", C.c_void_p), ("bias", C.c_void_p),
+        ("c", C.c_void_p),
+        ("M", C.c_int64), ("N", C.c_int64), ("K", C.c_int64),
+        ("lda", C.c_int64), ("ldb", C.c_int64), ("ldc", C.c_int64),
+        ("batch", C.c_int64),
+        ("stride_a", C.c_int64), ("stride_b", C.c_int64), ("stride_c", C.c_int64),
+        ("dtype", C.c_int32), ("b_layout", C.c_int32), ("epilogue", C.c_int32), ("gpu", C.c_int32),
+        ("stream", C.c_void_p),
+    ]
+
+
+GEMM_B_NK, GEMM_B_KN = 0, 1
+GEMM_EPI_NONE, GEMM_EPI_BIAS, GEMM_EPI_SWIGLU = 0, 1, 2
+
 _lib = None
 
 
@@ -67,6 +83,7 @@ def lib() -> C.CDLL:
         L.paras_b200_sdpa_fwd.argtypes = [C.POINTER(SdpaArgs)]
         L.paras_b200_sdpa_workspace_bytes.argtypes = [C.POINTER(SdpaArgs), C.POINTER(C.c_size_t)]
         L.paras_b200_sdpa_fwd_static_scratch.argtypes = [C.POINTER(SdpaArgs)]
+        L.paras_b200_gemm.argtypes = [C.POINTER(GemmArgs)]
         L.paras_b200_rmsnorm_fwd.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                              C.c_int64, C.c_int64, C.c_double, C.c_int, C.c_int, C.c_void_p]
         L.paras_b200_rmsnorm_bwd.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
@@ -180,6 +197,41 @@ def sdpa_fwd_static_scratch(q, k, v, *, causal=False, scale=None, mask=None, fla
         out = torch.empty(q.shape, dtype=q.dtype, device=q.device)
     a = sdpa_args(q, k, v, out, causal=causal, scale=scale, mask=mask, flags=flags, stream=stream)
     check(lib().paras_b200_sdpa_fwd_static_scratch(C.byref(a)))
+    return out
+
+
+def gemm(a, b, *, b_layout=GEMM_B_NK, bias=None, up_weight=None, out=None, stream=None):
+    """``paras_b200_gemm`` on 2-D ([M,K]) or 3-D ([batch,M,K]) operands with contiguous rows.
+
+    ``b_layout=GEMM_B_NK``: b is [N,K] (a Linear weight), result a @ b^T;
+    ``GEMM_B_KN``: b is [K,N], result a @ b.  ``bias`` [N] adds a bias; ``up_weight`` [N,K]
+    makes b the gate weight of a fused SwiGLU: swiglu(a @ b^T, a @ up_weight^T).
+    """
+    batched = a.dim() == 3
+    a3 = a if batched else a.unsqueeze(0)
+    b3 = b if b.dim() == 3 else b.unsqueeze(0)
+    if a3.stride(-1) != 1 or b3.stride(-1) != 1:
+        raise RuntimeError("paras abi: gemm operands need contiguous rows")
+    Bt, M, K = a3.shape
+    N = b3.shape[1] if b_layout == GEMM_B_NK else b3.shape[2]
+    if out is None:
+        out = torch.empty((Bt, M, N) if batched else (M, N), dtype=a.dtype, device=a.device)
+    c3 = out if out.dim() == 3 else out.unsqueeze(0)
+    g = GemmArgs()
+    g.a, g.b, g.c = a3.data_ptr(), b3.data_ptr(), c3.data_ptr()
+    g.b2 = up_weight.data_ptr() if up_weight is not None else None
+    g.bias = bias.data_ptr() if bias is not None else None
+    g.M, g.N, g.K = M, N, K
+    g.lda, g.ldb, g.ldc = a3.stride(1), b3.stride(1), c3.stride(1)
+    g.batch = Bt
+    g.stride_a, g.stride_c = a3.stride(0), c3.stride(0)
+    g.stride_b = b3.stride(0) if b3.shape[0] > 1 else 0
+    g.dtype = dtype_code(a)
+    g.b_layout = b_layout
+    g.epilogue = GEMM_EPI_SWIGLU if up_weight is not None else (GEMM_EPI_BIAS if bias is not None else GEMM_EPI_NONE)
+    g.gpu = _gpu_of(a)
+    g.stream = _stream_of(a, stream)
+    check(lib().paras_b200_gemm(C.byref(g)))
     return out
 
 

@@ -8,7 +8,7 @@ import torch
 
 from . import _C  # noqa: F401  (loads the operator registrations)
 
-__all__ = ["rms_norm", "swiglu", "rotate_half"]
+__all__ = ["rms_norm", "swiglu", "rotate_half", "swiglu_linear"]
 
 
 class _RMSNorm(torch.autograd.Function):
@@ -55,6 +55,13 @@ def rms_norm(input: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6) -> to
 def swiglu(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     """``silu(gate) * up`` in one kernel."""
     return _SwiGLU.apply(gate, up)
+
+
+def swiglu_linear(x: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor) -> torch.Tensor:
+    """``swiglu(F.linear(x, w_gate), F.linear(x, w_up))`` as one GEMM kernel (forward only):
+    both projections share one pass over ``x`` and SwiGLU runs in the epilogue.  16-bit
+    operands; the weights are ``[features, in_features]`` like ``nn.Linear.weight``."""
+    return torch.ops.paras.swiglu_linear(x, w_gate, w_up)
 
 
 def rotate_half(x: torch.Tensor) -> torch.Tensor:

@@ -206,6 +206,42 @@ int paras_b200_swiglu_bwd(int gpu, const void* grad_out, const void* gate, const
 int paras_b200_rotate_half(int gpu, const void* x, void* out, int64_t rows, int64_t D, int dtype,
                            int backward, void* stream);
 
+/* ---- 16-bit GEMM (the projections either side of the path) ----
+ * Replaces the host round trip of mm / bmm / addmm / linear (csrc/ops/vision_ops.cpp:248-309,
+ * 388-423: both operands copied to the host, at::mm / at::bmm / at::addmm / at::linear in
+ * libtorch's CPU library, result copied back).  fp32 accumulation, one rounding of the result.
+ *   C[i][M,N] = A[i][M,K] * B[i]  for i < batch
+ *   A: rows of K contiguous elements, row stride lda.
+ *   b_layout PARAS_GEMM_B_NK: B is [N,K], rows of K elements (a Linear weight; C = A B^T)
+ *            PARAS_GEMM_B_KN: B is [K,N], rows of N elements (mm / bmm; C = A B)
+ *   epilogue PARAS_GEMM_EPI_NONE
+ *            PARAS_GEMM_EPI_BIAS:   C += bias[N] (same dtype), added in fp32 before the rounding
+ *            PARAS_GEMM_EPI_SWIGLU: b = gate weight [N,K], b2 = up weight [N,K] (layout NK only);
+ *                C[M,N] = swiglu(A b^T, A b2^T) with both projections rounded to `dtype` first,
+ *                i.e. what linear, linear, paras::swiglu (csrc/ops/fused_ops.cpp:162-194) give.
+ * All leading dimensions and batch strides are in elements and must be multiples of 8 (16
+ * bytes), all base pointers 16-byte aligned; otherwise PARAS_E_UNSUPPORTED (the caller keeps
+ * its own path for such operands).  dtype: PARAS_BF16 or PARAS_F16. */
+enum { PARAS_GEMM_B_NK = 0, PARAS_GEMM_B_KN = 1 };
+enum { PARAS_GEMM_EPI_NONE = 0, PARAS_GEMM_EPI_BIAS = 1, PARAS_GEMM_EPI_SWIGLU = 2 };
+typedef struct paras_gemm_args {
+    const void* a;
+    const void* b;
+    const void* b2;     /* up weight, SwiGLU epilogue only */
+    const void* bias;   /* [N], bias epilogue only */
+    void* c;
+    int64_t M, N, K;
+    int64_t lda, ldb, ldc;
+    int64_t batch;      /* >= 1 */
+    int64_t stride_a, stride_b, stride_c;  /* elements between consecutive matrices (batch > 1) */
+    int32_t dtype;
+    int32_t b_layout;
+    int32_t epilogue;
+    int32_t gpu;
+    void* stream;
+} paras_gemm_args;
+int paras_b200_gemm(const paras_gemm_args* args);
+
 #ifdef __cplusplus
 }
 #endif

@@ -230,6 +230,35 @@ def rotate_half_backward(g: Tensor) -> Tensor:
 
 
 # ----------------------------------------------------------------------------------
+# matrix products either side of the path: the reference hands them to libtorch on the host
+# ----------------------------------------------------------------------------------
+def mm(a: Tensor, b: Tensor) -> Tensor:
+    """mm_out (vision_ops.cpp:388-396): at::mm on host copies of both operands."""
+    return torch.mm(a.contiguous(), b.contiguous())
+
+
+def bmm(a: Tensor, b: Tensor) -> Tensor:
+    """bmm_out (vision_ops.cpp:398-406): at::bmm on host copies."""
+    return torch.bmm(a.contiguous(), b.contiguous())
+
+
+def addmm(c: Tensor, a: Tensor, b: Tensor, beta=1, alpha=1) -> Tensor:
+    """addmm_out (vision_ops.cpp:408-423): at::addmm on host copies."""
+    return torch.addmm(c, a.contiguous(), b.contiguous(), beta=beta, alpha=alpha)
+
+
+def linear(x: Tensor, w: Tensor, bias: Optional[Tensor] = None) -> Tensor:
+    """LinearFunction::forward (vision_ops.cpp:248-270): at::linear on host copies."""
+    return torch.nn.functional.linear(x, w, bias)
+
+
+def swiglu_linear(x: Tensor, w_gate: Tensor, w_up: Tensor) -> Tensor:
+    """What the reference computes for a gated MLP's first half: two linear calls, each rounded
+    to the tensor dtype, then paras::swiglu (fused_ops.cpp:162-194)."""
+    return swiglu_fused(linear(x, w_gate), linear(x, w_up))
+
+
+# ----------------------------------------------------------------------------------
 # synthetic inputs of the five benchmark configurations
 # ----------------------------------------------------------------------------------
 def gen_seed(config_index: int, batch: Optional[int] = None) -> int:

@@ -1,0 +1,135 @@
+"""The projections either side of the path: the tcgen05 GEMM behind paras_b200_gemm, called
+through the C ABI and through the `paras` device (aten::mm / bmm / addmm / linear and
+paras::swiglu_linear), against what the reference computes for them: libtorch's CPU GEMM on
+host copies (csrc/ops/vision_ops.cpp:248-309, 388-423).
+
+Tolerance: both sides accumulate in fp32 and round once, but not in the same order, so a
+result may land on the neighbouring 16-bit value: |got - want| <= 2^-7 |want| + 2e-2 for bf16
+(2^-10 |want| + 2e-2 for fp16), and at least 99 % of the elements must be bit-equal.
+"""
+import pytest
+import torch
+import torch.nn.functional as F
+
+from oracle import oracle as O
+
+import torch_paras
+from torch_paras import abi, nn as paras_nn
+
+pytestmark = pytest.mark.gpu
+CUDA = "cuda:0"
+DEV = "paras:1"
+
+
+def close16(got, want, name, exact_share=0.99):
+    got = got.detach().cpu()
+    assert got.dtype == want.dtype and got.shape == want.shape, name
+    g, w = got.double(), want.double()
+    rel = 2.0 ** -7 if want.dtype == torch.bfloat16 else 2.0 ** -10
+    bad = (g - w).abs() > rel * w.abs() + 2e-2
+    assert not bad.any(), f"{name}: {int(bad.sum())} elements off, worst {(g - w).abs().max():.3e}"
+    if want.numel():
+        share = (got == want).double().mean().item()
+        assert share >= exact_share, f"{name}: only {share:.4f} of the elements are bit-equal"
+
+
+def rand(shape, seed, dtype, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).to(dtype)
+
+
+SHAPES = [(128, 256, 64), (256, 512, 512), (300, 520, 136), (1, 8, 8), (77, 1000, 264),
+          (640, 384, 1000), (129, 257 * 8, 72)]
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("shape", SHAPES)
+def test_gemm_abi_against_host_gemm(shape, dtype):
+    M, N, K = shape
+    a, w, b = rand((M, K), 1, dtype), rand((N, K), 2, dtype), rand((K, N), 3, dtype)
+    bias = rand((N,), 4, dtype)
+    close16(abi.gemm(a.to(CUDA), w.to(CUDA)), O.linear(a, w), f"A W^T {shape}")
+    close16(abi.gemm(a.to(CUDA), b.to(CUDA), b_layout=abi.GEMM_B_KN), O.mm(a, b), f"A B {shape}")
+    close16(abi.gemm(a.to(CUDA), w.to(CUDA), bias=bias.to(CUDA)), O.linear(a, w, bias), f"bias {shape}")
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("shape", [(256, 256, 128), (500, 1000, 264), (64, 136, 2048)])
+def test_swiglu_epilogue_against_two_linears_and_swiglu(shape, dtype):
+    M, Fd, K = shape
+    x, wg, wu = rand((M, K), 1, dtype), rand((Fd, K), 2, dtype, 0.05), rand((Fd, K), 3, dtype, 0.05)
+    got = abi.gemm(x.to(CUDA), wg.to(CUDA), up_weight=wu.to(CUDA))
+    # a neighbouring 16-bit value of either projection moves the product, so fewer exact hits
+    close16(got, O.swiglu_linear(x, wg, wu), f"swiglu epilogue {shape}", exact_share=0.97)
+
+
+def test_batched_and_strided_operands():
+    dtype = torch.bfloat16
+    a, b = rand((6, 200, 136), 1, dtype), rand((6, 136, 328), 2, dtype)
+    close16(abi.gemm(a.to(CUDA), b.to(CUDA), b_layout=abi.GEMM_B_KN), O.bmm(a, b), "bmm")
+    # rows that are slices of a wider matrix (leading dimension > row length)
+    wide = rand((300, 512), 3, dtype)
+    w = rand((264, 256), 4, dtype)
+    close16(abi.gemm(wide.to(CUDA)[:, 128:384], w.to(CUDA)), O.linear(wide[:, 128:384], w), "strided A")
+    out = torch.zeros(300, 512, dtype=dtype, device=CUDA)
+    abi.gemm(wide.to(CUDA)[:, 128:384], w.to(CUDA), out=out[:, 8:272])
+    close16(out[:, 8:272], O.linear(wide[:, 128:384], w), "strided C")
+    assert float(out[:, :8].abs().sum()) == 0.0 and float(out[:, 272:].abs().sum()) == 0.0
+
+
+def test_operands_the_kernel_does_not_take_are_refused():
+    a = torch.randn(64, 64, device=CUDA)
+    with pytest.raises(RuntimeError):
+        abi.gemm(a, a)                                   # fp32
+    h = torch.randn(64, 68, device=CUDA).bfloat16()
+    with pytest.raises(RuntimeError):
+        abi.gemm(h[:, :60], h[:, :60])                   # leading dimension not a multiple of 8
+    z = abi.gemm(torch.empty(0, 64, device=CUDA).bfloat16(), torch.empty(32, 64, device=CUDA).bfloat16())
+    assert z.shape == (0, 32)
+
+
+def test_device_ops_route_to_the_kernel_and_fall_back_like_the_reference():
+    dtype = torch.bfloat16
+    x, w, bias = rand((4, 50, 256), 1, dtype), rand((384, 256), 2, dtype), rand((384,), 3, dtype)
+    dx, dw, db = x.to(DEV), w.to(DEV), bias.to(DEV)
+    close16(F.linear(dx, dw, db), O.linear(x, w, bias), "F.linear")
+    close16(F.linear(dx, dw), O.linear(x, w), "F.linear no bias")
+    a, b = rand((200, 256), 4, dtype), rand((256, 136), 5, dtype)
+    close16(torch.mm(a.to(DEV), b.to(DEV)), O.mm(a, b), "mm")
+    close16(a.to(DEV) @ w.to(DEV).t(), O.mm(a, w.t()), "x @ w.t()")
+    c = rand((136,), 6, dtype)
+    close16(torch.addmm(c.to(DEV), a.to(DEV), b.to(DEV)), O.addmm(c, a, b), "addmm")
+    a3, b3 = rand((3, 64, 72), 7, dtype), rand((3, 72, 40), 8, dtype)
+    close16(torch.bmm(a3.to(DEV), b3.to(DEV)), O.bmm(a3, b3), "bmm")
+    # fp32 and odd shapes keep the reference's host route: results are libtorch's, exactly
+    a32, b32 = torch.randn(33, 17), torch.randn(17, 5)
+    assert torch.equal(torch.mm(a32.to(DEV), b32.to(DEV)).cpu(), torch.mm(a32, b32))
+    odd_a, odd_b = rand((9, 13), 9, dtype), rand((13, 7), 10, dtype)
+    assert torch.equal(torch.mm(odd_a.to(DEV), odd_b.to(DEV)).cpu(), torch.mm(odd_a, odd_b))
+    with pytest.raises(RuntimeError):
+        torch.mm(a.to(DEV), a.to(DEV))                   # 200x256 @ 200x256
+
+
+def test_swiglu_linear_operator():
+    dtype = torch.bfloat16
+    x, wg, wu = rand((2, 100, 256), 1, dtype), rand((520, 256), 2, dtype, 0.05), rand((520, 256), 3, dtype, 0.05)
+    got = paras_nn.swiglu_linear(x.to(DEV), wg.to(DEV), wu.to(DEV))
+    assert got.shape == (2, 100, 520)
+    close16(got, O.swiglu_linear(x, wg, wu), "swiglu_linear", exact_share=0.97)
+    with pytest.raises(RuntimeError):
+        paras_nn.swiglu_linear(x.float().to(DEV), wg.float().to(DEV), wu.float().to(DEV))
+
+
+def test_linearity_at_projection_size():
+    # full-size property check (no CPU oracle at this size): A (W1 + W2)^T computed by the kernel
+    # equals A W1^T + A W2^T up to the roundings involved, on a 4096-wide projection
+    dtype = torch.bfloat16
+    g = torch.Generator(device=CUDA).manual_seed(5)
+    a = torch.randn(2048, 4096, generator=g, device=CUDA).to(dtype)
+    w1 = (torch.randn(4096, 4096, generator=g, device=CUDA) * 0.02).to(dtype)
+    w2 = (torch.randn(4096, 4096, generator=g, device=CUDA) * 0.02).to(dtype)
+    lhs = abi.gemm(a, (w1.float() + w2.float()).to(dtype)).float()
+    rhs = abi.gemm(a, w1).float() + abi.gemm(a, w2).float()
+    scale = rhs.abs().mean().item()
+    assert (lhs - rhs).abs().max().item() <= 0.05 * scale + 0.1
+    assert (lhs - rhs).abs().mean().item() <= 0.01 * scale
