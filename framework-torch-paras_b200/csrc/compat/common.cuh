@@ -38,6 +38,8 @@ struct Gpu {
 // Returns PARAS_E_TIMEOUT (and clears the word) when a kernel on `g` reported that one of
 // its bounded waits gave up; PARAS_OK otherwise.
 int check_status_word(Gpu* g);
+// True when `p` lies in page-locked host memory (allocated by this library or registered with CUDA).
+bool host_ptr_is_pinned(const void* p);
 
 // Makes `gpu` current on the calling thread and returns its state; nullptr (and an error
 // message) when the ordinal is bad or there is no device.

@@ -112,14 +112,6 @@ int ensure_staging(Gpu* g, Staging* st) {
     return PARAS_OK;
 }
 
-bool host_ptr_is_pinned(const void* p) {
-    cudaPointerAttributes a{};
-    if (cudaPointerGetAttributes(&a, p) != cudaSuccess) {
-        cudaGetLastError();
-        return false;
-    }
-    return a.type == cudaMemoryTypeHost;
-}
 
 // memcpy split over a few host threads: one core moves ~10 GB/s, PCIe Gen5 takes ~50.
 void parallel_memcpy(void* dst, const void* src, size_t bytes) {
@@ -147,6 +139,15 @@ void parallel_memcpy(void* dst, const void* src, size_t bytes) {
 }
 
 }  // namespace
+
+bool host_ptr_is_pinned(const void* p) {
+    cudaPointerAttributes a{};
+    if (cudaPointerGetAttributes(&a, p) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    return a.type == cudaMemoryTypeHost;
+}
 
 int fail(int code, const char* fmt, ...) {
     va_list ap;

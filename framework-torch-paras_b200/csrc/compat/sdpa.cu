@@ -7,7 +7,9 @@
 //   * 16-bit, D == 128, no mask tensor, few queries   -> tensor-core split-KV decode kernel
 //   * everything else                                  -> CUDA-core kernel (sdpa_simt.cu)
 // There is no host fallback: an unsupported request is an error.
+#include <algorithm>
 #include <cmath>
+#include <mutex>
 
 #include "sdpa_common.cuh"
 
@@ -146,6 +148,146 @@ int paras_b200_sdpa_fwd(const paras_sdpa_args* a) {
         if (st == PARAS_OK) st = st2;
     }
     return st;
+}
+
+// ---- attention on host-resident operands ------------------------------------------------
+// Per-GPU streams and events of the pipeline below (created on first use, never destroyed).
+namespace pb {
+namespace {
+constexpr int kHostSlots = 3;
+struct HostPipe {
+    std::mutex mu;
+    bool ready = false;
+    cudaStream_t h2d = nullptr, d2h = nullptr;
+    cudaEvent_t in_done[kHostSlots], comp_done[kHostSlots], out_done[kHostSlots];
+};
+HostPipe g_host_pipe[16];
+}  // namespace
+}  // namespace pb
+
+int paras_b200_sdpa_fwd_host(const paras_sdpa_args* a) {
+    int st = pb::validate(a);
+    if (st != PARAS_OK) return st;
+    Gpu* g = pb::use_gpu(a->gpu, &st);
+    if (!g) return st;
+    if (a->gpu < 0 || a->gpu >= 16) return fail(PARAS_E_UNSUPPORTED, "paras sdpa (host): GPU ordinal out of range");
+    if (a->mask || a->lse || a->workspace)
+        return fail(PARAS_E_UNSUPPORTED, "paras sdpa (host): mask, lse and workspace are not taken here");
+    if (int64_t(a->B) * a->Hq * a->Lq * a->D == 0) return PARAS_OK;
+    if (!a->q || !a->out || (a->Lk > 0 && (!a->k || !a->v)))
+        return fail(PARAS_E_INVALID, "paras sdpa (host): null pointer");
+    // each batch element must be one dense [H, L, D] block, so that it moves in one copy
+    auto dense = [&](const int64_t* s, int H, int L) {
+        return (L <= 1 || s[2] == a->D) && (H <= 1 || s[1] == int64_t(L) * a->D) &&
+               (a->B <= 1 || s[0] >= int64_t(H) * L * a->D);
+    };
+    if (!dense(a->q_strides, a->Hq, a->Lq) || !dense(a->k_strides, a->Hkv, a->Lk) ||
+        !dense(a->v_strides, a->Hkv, a->Lk) || !dense(a->o_strides, a->Hq, a->Lq))
+        return fail(PARAS_E_UNSUPPORTED, "paras sdpa (host): every batch element must be a dense [H, L, D] block");
+
+    pb::HostPipe& hp = pb::g_host_pipe[a->gpu];
+    std::lock_guard<std::mutex> lk(hp.mu);  // one pipeline per GPU at a time
+    if (!hp.ready) {
+        PB_CUDA(cudaStreamCreateWithFlags(&hp.h2d, cudaStreamNonBlocking));
+        PB_CUDA(cudaStreamCreateWithFlags(&hp.d2h, cudaStreamNonBlocking));
+        for (int i = 0; i < pb::kHostSlots; ++i) {
+            PB_CUDA(cudaEventCreateWithFlags(&hp.in_done[i], cudaEventDisableTiming));
+            PB_CUDA(cudaEventCreateWithFlags(&hp.comp_done[i], cudaEventDisableTiming));
+            PB_CUDA(cudaEventCreateWithFlags(&hp.out_done[i], cudaEventDisableTiming));
+        }
+        hp.ready = true;
+    }
+    cudaStream_t comp = pb::pick_stream(g, a->stream);
+    const size_t es = pb::dtype_size(a->dtype);
+    const size_t q_b = size_t(a->Hq) * a->Lq * a->D * es, kv_b = size_t(a->Hkv) * a->Lk * a->D * es;
+    // batch elements per chunk: about 64 MB of operands, so that a copy is long enough to run at
+    // the link's rate and short enough for the pipeline to fill quickly
+    const size_t per_b = 2 * q_b + 2 * kv_b;
+    int nb = int(std::max<size_t>(1, (size_t(64) << 20) / std::max<size_t>(per_b, 1)));
+    nb = std::min(nb, a->B);
+    auto up = [](size_t x) { return (x + 255) & ~size_t(255); };
+    const size_t slot_bytes = 2 * up(q_b * nb) + 2 * up(kv_b * nb);
+    void* block = nullptr;
+    st = paras_b200_malloc_async(a->gpu, slot_bytes * pb::kHostSlots, comp, &block);
+    if (st != PARAS_OK) return st;
+    // the copy streams may touch the block only after the allocation is ordered before them
+    cudaEvent_t alloc_ev = hp.comp_done[0];
+    cudaError_t ce = cudaEventRecord(alloc_ev, comp);
+    if (ce == cudaSuccess) ce = cudaStreamWaitEvent(hp.h2d, alloc_ev, 0);
+    const bool pinned = pb::host_ptr_is_pinned(a->q) && pb::host_ptr_is_pinned(a->k) &&
+                        pb::host_ptr_is_pinned(a->v) && pb::host_ptr_is_pinned(a->out);
+    int rc = ce == cudaSuccess ? PARAS_OK : fail(PARAS_E_CUDA, "paras sdpa (host): %s", cudaGetErrorString(ce));
+    int chunk = 0;
+    for (int b0 = 0; rc == PARAS_OK && b0 < a->B; b0 += nb, ++chunk) {
+        const int n = std::min(nb, a->B - b0);
+        const int slot = chunk % pb::kHostSlots;
+        char* base = static_cast<char*>(block) + size_t(slot) * slot_bytes;
+        char* dq = base;
+        char* dk = dq + up(q_b * nb);
+        char* dv = dk + up(kv_b * nb);
+        char* dout = dv + up(kv_b * nb);
+        // the slot is free once the chunk that used it last has been copied out
+        if (chunk >= pb::kHostSlots) ce = cudaStreamWaitEvent(hp.h2d, hp.out_done[slot], 0);
+        auto h2d = [&](char* dst, const void* src, const int64_t* strides, size_t bytes_per_b) {
+            if (rc != PARAS_OK) return;
+            const char* s0 = static_cast<const char*>(src) + size_t(b0) * size_t(strides[0]) * es;
+            if (a->B <= 1 || size_t(strides[0]) * es == bytes_per_b) {
+                rc = paras_b200_memcpy_h2d(a->gpu, dst, s0, bytes_per_b * n, hp.h2d, 0);
+            } else {
+                for (int i = 0; i < n && rc == PARAS_OK; ++i)
+                    rc = paras_b200_memcpy_h2d(a->gpu, dst + i * bytes_per_b, s0 + size_t(i) * size_t(strides[0]) * es,
+                                               bytes_per_b, hp.h2d, 0);
+            }
+        };
+        h2d(dq, a->q, a->q_strides, q_b);
+        h2d(dk, a->k, a->k_strides, kv_b);
+        h2d(dv, a->v, a->v_strides, kv_b);
+        if (rc != PARAS_OK) break;
+        if (ce == cudaSuccess) ce = cudaEventRecord(hp.in_done[slot], hp.h2d);
+        if (ce == cudaSuccess) ce = cudaStreamWaitEvent(comp, hp.in_done[slot], 0);
+        if (ce != cudaSuccess) break;
+        paras_sdpa_args sub = *a;
+        sub.q = dq; sub.k = dk; sub.v = dv; sub.out = dout;
+        sub.B = n;
+        sub.q_strides[0] = sub.o_strides[0] = int64_t(a->Hq) * a->Lq * a->D;
+        sub.k_strides[0] = sub.v_strides[0] = int64_t(a->Hkv) * a->Lk * a->D;
+        sub.q_strides[1] = sub.o_strides[1] = int64_t(a->Lq) * a->D;
+        sub.k_strides[1] = sub.v_strides[1] = int64_t(a->Lk) * a->D;
+        sub.q_strides[2] = sub.o_strides[2] = sub.k_strides[2] = sub.v_strides[2] = a->D;
+        sub.stream = comp;
+        rc = paras_b200_sdpa_fwd(&sub);
+        if (rc != PARAS_OK) break;
+        ce = cudaEventRecord(hp.comp_done[slot], comp);
+        if (ce == cudaSuccess) ce = cudaStreamWaitEvent(hp.d2h, hp.comp_done[slot], 0);
+        if (ce != cudaSuccess) break;
+        char* o0 = static_cast<char*>(a->out) + size_t(b0) * size_t(a->o_strides[0]) * es;
+        if (pinned) {
+            if (a->B <= 1 || size_t(a->o_strides[0]) * es == q_b) {
+                ce = cudaMemcpyAsync(o0, dout, q_b * n, cudaMemcpyDeviceToHost, hp.d2h);
+            } else {
+                for (int i = 0; i < n && ce == cudaSuccess; ++i)
+                    ce = cudaMemcpyAsync(o0 + size_t(i) * size_t(a->o_strides[0]) * es, dout + i * q_b, q_b,
+                                         cudaMemcpyDeviceToHost, hp.d2h);
+            }
+        } else {
+            // pageable result: the staged copy blocks this thread until the chunk is on the host
+            for (int i = 0; i < n && rc == PARAS_OK; ++i)
+                rc = paras_b200_memcpy_d2h(a->gpu, o0 + size_t(i) * size_t(a->o_strides[0]) * es, dout + i * q_b,
+                                           q_b, hp.d2h);
+        }
+        if (ce == cudaSuccess) ce = cudaEventRecord(hp.out_done[slot], hp.d2h);
+        if (ce != cudaSuccess) break;
+    }
+    // everything drains before the block goes back to the pool and the caller reads the result
+    cudaError_t c1 = cudaStreamSynchronize(hp.h2d);
+    cudaError_t c2 = cudaStreamSynchronize(comp);
+    cudaError_t c3 = cudaStreamSynchronize(hp.d2h);
+    const int st2 = paras_b200_free_async(a->gpu, block, comp);
+    if (rc != PARAS_OK) return rc;
+    for (cudaError_t e : {ce, c1, c2, c3})
+        if (e != cudaSuccess) return fail(PARAS_E_CUDA, "paras sdpa (host): %s", cudaGetErrorString(e));
+    if (st2 != PARAS_OK) return st2;
+    return pb::check_status_word(g);
 }
 
 }  // extern "C"

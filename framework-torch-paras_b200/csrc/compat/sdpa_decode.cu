@@ -20,10 +20,10 @@
 // legacy mma.sync path is ample; tcgen05 with its 128-row tiles would waste 32x instead.
 #include <algorithm>
 #include <cmath>
-#include <mutex>
 
 #include "sdpa_common.cuh"
 #include "tc_prims.cuh"
+#include "tma_host.cuh"
 
 namespace pb {
 namespace {
@@ -326,44 +326,8 @@ sdpa_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
     }
 }
 
-using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
-                              CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
-                              CUtensorMapFloatOOBfill);
-
-EncodeFn encode_fn() {
-    static EncodeFn fn = nullptr;
-    static std::once_flag once;
-    std::call_once(once, [] {
-        void* sym = nullptr;
-        cudaDriverEntryPointQueryResult qres;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) ==
-                cudaSuccess && qres == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeFn>(sym);
-        else
-            cudaGetLastError();
-    });
-    return fn;
-}
-
 int make_kv_map(CUtensorMap* map, const void* base, int dtype, int B, int H, int L, const int64_t* st) {
-    EncodeFn fn = encode_fn();
-    if (!fn) return fail(PARAS_E_CUDA, "paras sdpa: cuTensorMapEncodeTiled is unavailable");
-    const cuuint64_t dims[4] = {cuuint64_t(HD), cuuint64_t(L), cuuint64_t(H), cuuint64_t(B)};
-    const int64_t sl = L > 1 ? st[2] : HD;
-    const int64_t sh = H > 1 ? st[1] : sl * L;
-    const int64_t sb = B > 1 ? st[0] : sh * H;
-    const cuuint64_t strides[3] = {cuuint64_t(sl) * 2, cuuint64_t(sh) * 2, cuuint64_t(sb) * 2};
-    const cuuint32_t box[4] = {64, cuuint32_t(TK), 1, 1};
-    const cuuint32_t estr[4] = {1, 1, 1, 1};
-    const CUresult r = fn(map, dtype == PARAS_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
-                                                  : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
-                          4, const_cast<void*>(base), dims, strides, box, estr,
-                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS)
-        return fail(PARAS_E_CUDA, "paras sdpa: cuTensorMapEncodeTiled failed with code %d", int(r));
-    return PARAS_OK;
+    return make_tensor_map_bhld(map, base, dtype, B, H, L, HD, st, TK);
 }
 
 bool kv_strides_ok(const void* base, const int64_t* st, int B, int H, int L) {

@@ -48,10 +48,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
+constexpr uint64_t kWaitLimitNs = 200000000ull;  // 0.2 s: orders of magnitude above any real wait
+
 // Bounded wait: gives up after `limit_ns` of wall time, or as soon as another thread of
 // the CTA has raised `*abort_flag` (a shared-memory word, set to the caller's `tag`).  Returns false when it gave up;
 // the caller then stops issuing work and leaves through the kernel's common exit.
-constexpr uint64_t kWaitLimitNs = 200000000ull;  // 0.2 s: orders of magnitude above any real wait
 
 template <int SLEEP_NS = 0>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
@@ -72,26 +73,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
     while (!mbar_try_wait(bar, parity)) {
         if constexpr (SLEEP_NS > 0) __nanosleep(SLEEP_NS);
         if ((++polls & 0xffu) == 0) {
-            if (*abort_flag || global_timer_ns() - t0 > kWaitLimitNs) {
-                atomicOr(const_cast<int*>(abort_flag), int(0x40000000u | (1u << tag)));
-                return false;
-            }
-        }
-    }
-    return true;
-}
-
-// Same bounded wait for roles that are off the critical path and wait for a long time (an
-// epilogue waiting for a whole work item): sleeps between polls so that it does not take
-// issue slots from the warps sharing its scheduler.
-__device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity,
-                                                  volatile int* abort_flag, int tag = 0) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const uint64_t t0 = global_timer_ns();
-    uint32_t polls = 0;
-    while (!mbar_try_wait(bar, parity)) {
-        __nanosleep(256);
-        if ((++polls & 0x3fu) == 0) {
             if (*abort_flag || global_timer_ns() - t0 > kWaitLimitNs) {
                 atomicOr(const_cast<int*>(abort_flag), int(0x40000000u | (1u << tag)));
                 return false;
@@ -303,13 +284,9 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
 }
 
 __device__ __forceinline__ float ex2_approx(float x) {
-#if defined(PB_EXPERIMENT_NO_MUFU)
-    return x * 0.001f + 0.5f;  // timing experiment only: results are wrong
-#else
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
-#endif
 }
 
 __device__ __forceinline__ float lg2_approx(float x) {

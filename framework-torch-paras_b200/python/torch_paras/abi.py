@@ -34,7 +34,7 @@ EXPORTS = [
     "paras_b200_sdpa_workspace_bytes", "paras_b200_sdpa_last_kernel", "paras_b200_rmsnorm_fwd",
     "paras_b200_sdpa_fwd_static_scratch", "paras_b200_sdpa_static_scratch_bytes",
     "paras_b200_rmsnorm_bwd", "paras_b200_swiglu_fwd", "paras_b200_swiglu_bwd",
-    "paras_b200_rotate_half", "paras_b200_gemm",
+    "paras_b200_rotate_half", "paras_b200_gemm", "paras_b200_sdpa_fwd_host",
 ]
 
 
@@ -84,6 +84,7 @@ def lib() -> C.CDLL:
         L.paras_b200_sdpa_workspace_bytes.argtypes = [C.POINTER(SdpaArgs), C.POINTER(C.c_size_t)]
         L.paras_b200_sdpa_fwd_static_scratch.argtypes = [C.POINTER(SdpaArgs)]
         L.paras_b200_gemm.argtypes = [C.POINTER(GemmArgs)]
+        L.paras_b200_sdpa_fwd_host.argtypes = [C.POINTER(SdpaArgs)]
         L.paras_b200_rmsnorm_fwd.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                              C.c_int64, C.c_int64, C.c_double, C.c_int, C.c_int, C.c_void_p]
         L.paras_b200_rmsnorm_bwd.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
@@ -185,6 +186,33 @@ def sdpa_fwd(q, k, v, *, causal=False, scale=None, mask=None, return_lse=False, 
                   workspace=workspace, stream=stream)
     check(lib().paras_b200_sdpa_fwd(C.byref(a)))
     return (out, lse) if return_lse else out
+
+
+def sdpa_fwd_host(q, k, v, *, causal=False, scale=None, flags=0, out=None, gpu=0):
+    """Attention on host tensors through ``paras_b200_sdpa_fwd_host``: batch chunks are copied
+    in, computed and copied out as a pipeline on GPU ``gpu``.  Pass page-locked tensors
+    (``pin_memory()``) for full overlap; ``out`` (host, same shape as q) is created pinned when
+    omitted."""
+    for t in (q, k, v):
+        if t.device.type != "cpu" or not t.is_contiguous():
+            raise RuntimeError("paras abi: sdpa_fwd_host takes contiguous host tensors")
+    if out is None:
+        out = torch.empty(q.shape, dtype=q.dtype, pin_memory=True)
+    a = SdpaArgs()
+    a.q, a.k, a.v, a.out = q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr()
+    a.dtype = dtype_code(q)
+    a.B, a.Hq, a.Lq, a.D = q.shape
+    a.Hkv, a.Lk = k.shape[1], k.shape[2]
+    for i in range(3):
+        a.q_strides[i], a.k_strides[i] = q.stride(i), k.stride(i)
+        a.v_strides[i], a.o_strides[i] = v.stride(i), out.stride(i)
+    a.causal = 1 if causal else 0
+    a.flags = flags
+    a.scale = float(scale) if scale is not None else 1.0 / (q.shape[-1] ** 0.5)
+    a.gpu = gpu
+    a.stream = None
+    check(lib().paras_b200_sdpa_fwd_host(C.byref(a)))
+    return out
 
 
 def sdpa_fwd_static_scratch(q, k, v, *, causal=False, scale=None, mask=None, flags=0, out=None,

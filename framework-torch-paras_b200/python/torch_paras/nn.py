@@ -8,7 +8,7 @@ import torch
 
 from . import _C  # noqa: F401  (loads the operator registrations)
 
-__all__ = ["rms_norm", "swiglu", "rotate_half", "swiglu_linear"]
+__all__ = ["rms_norm", "swiglu", "rotate_half", "swiglu_linear", "attention_host"]
 
 
 class _RMSNorm(torch.autograd.Function):
@@ -62,6 +62,23 @@ def swiglu_linear(x: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor) -> 
     both projections share one pass over ``x`` and SwiGLU runs in the epilogue.  16-bit
     operands; the weights are ``[features, in_features]`` like ``nn.Linear.weight``."""
     return torch.ops.paras.swiglu_linear(x, w_gate, w_up)
+
+
+def attention_host(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, *,
+                   is_causal: bool = False, scale=None, out=None, device: int = 1) -> torch.Tensor:
+    """Scaled dot-product attention for operands that live on the HOST ([B, H, L, D], 16-bit
+    or fp32, GQA by head count): batch chunks stream through GPU ``paras:device`` -- copy in,
+    attention, copy out, the three overlapping -- and the result is returned as a host tensor
+    (page-locked unless ``out`` is given).  Same numerics as
+    ``F.scaled_dot_product_attention`` on the ``paras`` device; use it instead of
+    ``.to("paras:N")`` + attention + ``.cpu()`` when the data does not stay on the GPU.
+    Pass ``pin_memory()``-ed tensors: pageable ones are staged and lose most of the overlap."""
+    from . import abi
+    if device < 1:
+        raise RuntimeError("paras attention_host: device must be a GPU index (paras:1 and up)")
+    return abi.sdpa_fwd_host(query.contiguous(), key.contiguous(), value.contiguous(),
+                             causal=is_causal, scale=scale, flags=abi.SDPA_REF_SCALE, out=out,
+                             gpu=device - 1)
 
 
 def rotate_half(x: torch.Tensor) -> torch.Tensor:

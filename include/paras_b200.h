@@ -156,6 +156,18 @@ int paras_b200_sdpa_workspace_bytes(const paras_sdpa_args* args, size_t* bytes);
  * ("tcgen05", "simt", "decode_mma", ...); for tests and logs. */
 const char* paras_b200_sdpa_last_kernel(void);
 
+/* The same attention on HOST-resident operands: q, k, v and out are host pointers ([B,H,L,D],
+ * every batch element a dense [H,L,D] block; strides[0] may be larger).  The call moves batch
+ * chunks (about 64 MB of operands each) through the GPU as a three-stage pipeline on three
+ * streams -- host-to-device copy of chunk i+1, attention on chunk i, device-to-host copy of
+ * chunk i-1 -- so that both directions of the link and the kernel overlap, and returns when the
+ * result is in `out`.  Page-locked buffers (paras_b200_host_alloc, or registered with CUDA) are
+ * copied directly; pageable ones go through the library's staging ring and lose most of the
+ * overlap.  mask, lse and workspace must be NULL.  This is what the reference does implicitly on
+ * every call when tensors live on the host (its attention copies operands to the device engine
+ * and results back, csrc/ops/vision_ops.cpp:35-37, tensor_ops.cpp:270-322), as one call. */
+int paras_b200_sdpa_fwd_host(const paras_sdpa_args* args);
+
 /* No counterpart in the reference.  The same attention, for callers that cannot allocate
  * device memory when they call -- for example a server whose memory manager claimed the whole
  * GPU at start-up, or a latency-bound decode loop: this entry point calls no cudaMalloc /

@@ -254,3 +254,24 @@ def test_concurrent_dispatch_from_python_threads():
     [t.start() for t in ts]
     [t.join() for t in ts]
     assert not errs, errs[0]
+
+
+def test_attention_host_streams_batches_through_the_gpu():
+    # host operands in, host result out, in one call; pinned and pageable, GQA, causal and not
+    g = torch.Generator().manual_seed(3)
+    for (B, Hq, Hkv, L, causal, dtype) in [(5, 4, 2, 384, True, torch.bfloat16),
+                                           (3, 2, 2, 200, False, torch.float16),
+                                           (2, 2, 1, 64, True, torch.float32)]:
+        q = torch.randn(B, Hq, L, 128, generator=g).to(dtype)
+        k = torch.randn(B, Hkv, L, 128, generator=g).to(dtype)
+        v = torch.randn(B, Hkv, L, 128, generator=g).to(dtype)
+        want = O.sdpa(q, k, v, is_causal=causal, enable_gqa=Hq != Hkv)
+        tol = 1e-4 if dtype == torch.float32 else 2e-2
+        got = paras_nn.attention_host(q.pin_memory(), k.pin_memory(), v.pin_memory(), is_causal=causal)
+        assert got.device.type == "cpu" and got.is_pinned() and got.dtype == dtype
+        assert (got.double() - want.double()).abs().max().item() <= tol
+        out = torch.empty_like(q)  # pageable operands and result
+        got2 = paras_nn.attention_host(q, k, v, is_causal=causal, out=out)
+        assert got2 is out and torch.equal(out, got)
+    with pytest.raises(RuntimeError):
+        paras_nn.attention_host(q, k, v, device=0)
