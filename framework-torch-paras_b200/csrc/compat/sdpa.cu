@@ -3,8 +3,8 @@
 // Mirrors the checks of the reference's sdpa_math (csrc/ops/attention_ops.cpp:77-98):
 // heads must divide for GQA, is_causal and a mask tensor are exclusive, the default scale
 // is 1/sqrt(D).  Selection:
-//   * 16-bit, D == 128, no mask tensor, long queries  -> tcgen05/TMEM/TMA kernel
 //   * 16-bit, D == 128, no mask tensor, few queries   -> tensor-core split-KV decode kernel
+//   * 16-bit, D == 128 otherwise (masks included)     -> tcgen05/TMEM/TMA kernel
 //   * everything else                                  -> CUDA-core kernel (sdpa_simt.cu)
 // There is no host fallback: an unsupported request is an error.
 #include <algorithm>
@@ -200,13 +200,25 @@ int paras_b200_sdpa_fwd_host(const paras_sdpa_args* a) {
     cudaStream_t comp = pb::pick_stream(g, a->stream);
     const size_t es = pb::dtype_size(a->dtype);
     const size_t q_b = size_t(a->Hq) * a->Lq * a->D * es, kv_b = size_t(a->Hkv) * a->Lk * a->D * es;
-    // batch elements per chunk: about 64 MB of operands, so that a copy is long enough to run at
-    // the link's rate and short enough for the pipeline to fill quickly
+    // Chunks of about 64 MB of operands (16 MB chunks measured 12 % slower end to end: more
+    // launches and events per byte, and short copies in both directions share the link worse).  A chunk is a range of batch elements
+    // with all their heads or, when one batch element is larger than that, a range of query
+    // heads of one batch element together with the kv heads they share (both are dense blocks).
+    const int r = a->Hq / a->Hkv;  // query heads per kv head
+    const size_t q_h = size_t(a->Lq) * a->D * es, kv_h = size_t(a->Lk) * a->D * es;  // bytes per head
     const size_t per_b = 2 * q_b + 2 * kv_b;
-    int nb = int(std::max<size_t>(1, (size_t(64) << 20) / std::max<size_t>(per_b, 1)));
-    nb = std::min(nb, a->B);
+    const size_t target = size_t(64) << 20;
+    int nb = 1, nh = a->Hq;
+    if (per_b <= target) {
+        nb = int(std::min<size_t>(size_t(a->B), std::max<size_t>(1, target / std::max<size_t>(per_b, 1))));
+    } else {
+        const size_t per_group = 2 * q_h * r + 2 * kv_h;  // one kv head and its query heads
+        nh = r * int(std::max<size_t>(1, target / std::max<size_t>(per_group, 1)));
+        nh = std::min(nh, a->Hq);
+    }
     auto up = [](size_t x) { return (x + 255) & ~size_t(255); };
-    const size_t slot_bytes = 2 * up(q_b * nb) + 2 * up(kv_b * nb);
+    const size_t q_c = up(q_h * nh * nb), kv_c = up(kv_h * (nh / r) * nb);  // per chunk
+    const size_t slot_bytes = 2 * q_c + 2 * kv_c;
     void* block = nullptr;
     st = paras_b200_malloc_async(a->gpu, slot_bytes * pb::kHostSlots, comp, &block);
     if (st != PARAS_OK) return st;
@@ -218,65 +230,69 @@ int paras_b200_sdpa_fwd_host(const paras_sdpa_args* a) {
                         pb::host_ptr_is_pinned(a->v) && pb::host_ptr_is_pinned(a->out);
     int rc = ce == cudaSuccess ? PARAS_OK : fail(PARAS_E_CUDA, "paras sdpa (host): %s", cudaGetErrorString(ce));
     int chunk = 0;
-    for (int b0 = 0; rc == PARAS_OK && b0 < a->B; b0 += nb, ++chunk) {
-        const int n = std::min(nb, a->B - b0);
-        const int slot = chunk % pb::kHostSlots;
-        char* base = static_cast<char*>(block) + size_t(slot) * slot_bytes;
-        char* dq = base;
-        char* dk = dq + up(q_b * nb);
-        char* dv = dk + up(kv_b * nb);
-        char* dout = dv + up(kv_b * nb);
-        // the slot is free once the chunk that used it last has been copied out
-        if (chunk >= pb::kHostSlots) ce = cudaStreamWaitEvent(hp.h2d, hp.out_done[slot], 0);
-        auto h2d = [&](char* dst, const void* src, const int64_t* strides, size_t bytes_per_b) {
-            if (rc != PARAS_OK) return;
-            const char* s0 = static_cast<const char*>(src) + size_t(b0) * size_t(strides[0]) * es;
-            if (a->B <= 1 || size_t(strides[0]) * es == bytes_per_b) {
-                rc = paras_b200_memcpy_h2d(a->gpu, dst, s0, bytes_per_b * n, hp.h2d, 0);
-            } else {
-                for (int i = 0; i < n && rc == PARAS_OK; ++i)
-                    rc = paras_b200_memcpy_h2d(a->gpu, dst + i * bytes_per_b, s0 + size_t(i) * size_t(strides[0]) * es,
-                                               bytes_per_b, hp.h2d, 0);
+    for (int b0 = 0; rc == PARAS_OK && ce == cudaSuccess && b0 < a->B; b0 += nb) {
+        for (int h0 = 0; rc == PARAS_OK && ce == cudaSuccess && h0 < a->Hq; h0 += nh, ++chunk) {
+            const int n = std::min(nb, a->B - b0);
+            const int hq = std::min(nh, a->Hq - h0), hk = hq / r;
+            const int slot = chunk % pb::kHostSlots;
+            char* dq = static_cast<char*>(block) + size_t(slot) * slot_bytes;
+            char* dk = dq + q_c;
+            char* dv = dk + kv_c;
+            char* dout = dv + kv_c;
+            // the slot is free once the chunk that used it last has been copied out
+            if (chunk >= pb::kHostSlots) ce = cudaStreamWaitEvent(hp.h2d, hp.out_done[slot], 0);
+            if (ce != cudaSuccess) break;
+            // n batch elements x `heads` heads starting at head `first`: one dense block per batch element
+            auto h2d = [&](char* dst, const void* src, const int64_t* strides, size_t head_bytes, int first, int heads) {
+                const size_t bytes = head_bytes * heads;
+                for (int i = 0; i < n && rc == PARAS_OK; ++i) {
+                    const char* s0 = static_cast<const char*>(src) + size_t(b0 + i) * size_t(strides[0]) * es +
+                                     size_t(first) * head_bytes;
+                    // consecutive batch elements that are also consecutive in memory go in one copy
+                    if (i == 0 && n > 1 && size_t(strides[0]) * es == bytes) {
+                        rc = paras_b200_memcpy_h2d(a->gpu, dst, s0, bytes * n, hp.h2d, 0);
+                        break;
+                    }
+                    rc = paras_b200_memcpy_h2d(a->gpu, dst + i * bytes, s0, bytes, hp.h2d, 0);
+                }
+            };
+            h2d(dq, a->q, a->q_strides, q_h, h0, hq);
+            h2d(dk, a->k, a->k_strides, kv_h, h0 / r, hk);
+            h2d(dv, a->v, a->v_strides, kv_h, h0 / r, hk);
+            if (rc != PARAS_OK) break;
+            ce = cudaEventRecord(hp.in_done[slot], hp.h2d);
+            if (ce == cudaSuccess) ce = cudaStreamWaitEvent(comp, hp.in_done[slot], 0);
+            if (ce != cudaSuccess) break;
+            paras_sdpa_args sub = *a;
+            sub.q = dq; sub.k = dk; sub.v = dv; sub.out = dout;
+            sub.B = n; sub.Hq = hq; sub.Hkv = hk;
+            sub.q_strides[0] = sub.o_strides[0] = int64_t(hq) * a->Lq * a->D;
+            sub.k_strides[0] = sub.v_strides[0] = int64_t(hk) * a->Lk * a->D;
+            sub.q_strides[1] = sub.o_strides[1] = int64_t(a->Lq) * a->D;
+            sub.k_strides[1] = sub.v_strides[1] = int64_t(a->Lk) * a->D;
+            sub.q_strides[2] = sub.o_strides[2] = sub.k_strides[2] = sub.v_strides[2] = a->D;
+            sub.stream = comp;
+            rc = paras_b200_sdpa_fwd(&sub);
+            if (rc != PARAS_OK) break;
+            ce = cudaEventRecord(hp.comp_done[slot], comp);
+            if (ce == cudaSuccess) ce = cudaStreamWaitEvent(hp.d2h, hp.comp_done[slot], 0);
+            if (ce != cudaSuccess) break;
+            const size_t o_bytes = q_h * hq;
+            for (int i = 0; i < n && rc == PARAS_OK && ce == cudaSuccess; ++i) {
+                char* o0 = static_cast<char*>(a->out) + size_t(b0 + i) * size_t(a->o_strides[0]) * es + size_t(h0) * q_h;
+                if (pinned) {
+                    if (i == 0 && n > 1 && size_t(a->o_strides[0]) * es == o_bytes) {
+                        ce = cudaMemcpyAsync(o0, dout, o_bytes * n, cudaMemcpyDeviceToHost, hp.d2h);
+                        break;
+                    }
+                    ce = cudaMemcpyAsync(o0, dout + i * o_bytes, o_bytes, cudaMemcpyDeviceToHost, hp.d2h);
+                } else {
+                    // pageable result: the staged copy blocks this thread until the piece is on the host
+                    rc = paras_b200_memcpy_d2h(a->gpu, o0, dout + i * o_bytes, o_bytes, hp.d2h);
+                }
             }
-        };
-        h2d(dq, a->q, a->q_strides, q_b);
-        h2d(dk, a->k, a->k_strides, kv_b);
-        h2d(dv, a->v, a->v_strides, kv_b);
-        if (rc != PARAS_OK) break;
-        if (ce == cudaSuccess) ce = cudaEventRecord(hp.in_done[slot], hp.h2d);
-        if (ce == cudaSuccess) ce = cudaStreamWaitEvent(comp, hp.in_done[slot], 0);
-        if (ce != cudaSuccess) break;
-        paras_sdpa_args sub = *a;
-        sub.q = dq; sub.k = dk; sub.v = dv; sub.out = dout;
-        sub.B = n;
-        sub.q_strides[0] = sub.o_strides[0] = int64_t(a->Hq) * a->Lq * a->D;
-        sub.k_strides[0] = sub.v_strides[0] = int64_t(a->Hkv) * a->Lk * a->D;
-        sub.q_strides[1] = sub.o_strides[1] = int64_t(a->Lq) * a->D;
-        sub.k_strides[1] = sub.v_strides[1] = int64_t(a->Lk) * a->D;
-        sub.q_strides[2] = sub.o_strides[2] = sub.k_strides[2] = sub.v_strides[2] = a->D;
-        sub.stream = comp;
-        rc = paras_b200_sdpa_fwd(&sub);
-        if (rc != PARAS_OK) break;
-        ce = cudaEventRecord(hp.comp_done[slot], comp);
-        if (ce == cudaSuccess) ce = cudaStreamWaitEvent(hp.d2h, hp.comp_done[slot], 0);
-        if (ce != cudaSuccess) break;
-        char* o0 = static_cast<char*>(a->out) + size_t(b0) * size_t(a->o_strides[0]) * es;
-        if (pinned) {
-            if (a->B <= 1 || size_t(a->o_strides[0]) * es == q_b) {
-                ce = cudaMemcpyAsync(o0, dout, q_b * n, cudaMemcpyDeviceToHost, hp.d2h);
-            } else {
-                for (int i = 0; i < n && ce == cudaSuccess; ++i)
-                    ce = cudaMemcpyAsync(o0 + size_t(i) * size_t(a->o_strides[0]) * es, dout + i * q_b, q_b,
-                                         cudaMemcpyDeviceToHost, hp.d2h);
-            }
-        } else {
-            // pageable result: the staged copy blocks this thread until the chunk is on the host
-            for (int i = 0; i < n && rc == PARAS_OK; ++i)
-                rc = paras_b200_memcpy_d2h(a->gpu, o0 + size_t(i) * size_t(a->o_strides[0]) * es, dout + i * q_b,
-                                           q_b, hp.d2h);
+            if (rc == PARAS_OK && ce == cudaSuccess) ce = cudaEventRecord(hp.out_done[slot], hp.d2h);
         }
-        if (ce == cudaSuccess) ce = cudaEventRecord(hp.out_done[slot], hp.d2h);
-        if (ce != cudaSuccess) break;
     }
     // everything drains before the block goes back to the pool and the caller reads the result
     cudaError_t c1 = cudaStreamSynchronize(hp.h2d);

@@ -1,6 +1,7 @@
 // Flash attention forward for sm_100a: tcgen05 tensor cores, TMEM accumulators, TMA-fed
 // K/V ring, warp-specialised roles.  16-bit tensors, head dim 128, causal (top-left
-// aligned, csrc/ops/attention_ops.cpp:103-116) or full attention, GQA by indexing the
+// aligned, csrc/ops/attention_ops.cpp:103-116), full, or explicitly masked (bool / additive,
+// attention_ops.cpp:117-126) attention, GQA by indexing the
 // shared kv head (never materialising the repeat_interleave of attention_ops.cpp:83-93).
 //
 // One CTA owns 256 consecutive query rows of one (batch, head) as two 128-row tiles that
@@ -104,6 +105,10 @@ struct TcParams {
     float scale;
     float scale_log2;
     float inv_scale_log2;
+    float inv_scale;     // additive mask values are divided by the scale before they join S
+    const void* mask;    // [B, Hq, Lq, Lk] with element strides ms (0 = broadcast), or null
+    int mask_kind;       // 1 bool (true = attend), 2 additive in the tensors' dtype, 3 additive fp32
+    int64_t ms[4];
     int* status;
     int nq;      // 256-row query blocks per (batch, head)
     int npair;   // ceil(nq / 2)
@@ -151,7 +156,9 @@ __device__ __forceinline__ bool get_item(const TcParams& p, int seq, Item* it) {
     return true;
 }
 
-template <bool BF16>
+// MASK: an explicit attn_mask is applied (a separate instantiation: the unmasked kernel pays
+// nothing for it, not even registers).
+template <bool BF16, bool MASK>
 __global__ void __launch_bounds__(kThreads, 1)
 sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o,
@@ -349,6 +356,73 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             const int nt = it.ntile[t];
             if (nt == 0) continue;
             const int row_q = it.start[t] + wq * 32 + lane;
+            // Explicit attn_mask (csrc/ops/attention_ops.cpp:117-126): this thread's row of it, 128
+            // entries per kv tile.  Bool: false -> -inf.  Additive: S is still unscaled here, so the
+            // mask value joins it divided by the scale.  Rows past the end reuse the last row.
+            const char* mrow = nullptr;
+            if (MASK) {
+                const int esz = p.mask_kind == 1 ? 1 : (p.mask_kind == 2 ? 2 : 4);
+                mrow = static_cast<const char*>(p.mask) +
+                       (int64_t(it.b) * p.ms[0] + int64_t(it.h) * p.ms[1] + int64_t(min(row_q, p.Lq - 1)) * p.ms[2]) * esz;
+            }
+            auto apply_mask = [&](uint32_t (&s)[BN], int col0) {
+                const int ncols = min(BN, p.Lk - col0);
+                const bool vec = p.ms[3] == 1 && ncols == BN;
+                if (p.mask_kind == 1) {
+                    const unsigned char* mp = reinterpret_cast<const unsigned char*>(mrow) + int64_t(col0) * p.ms[3];
+                    if (vec && (reinterpret_cast<uintptr_t>(mp) & 15u) == 0) {
+#pragma unroll
+                        for (int v = 0; v < BN / 16; ++v) {
+                            const uint4 w = __ldg(reinterpret_cast<const uint4*>(mp) + v);
+                            const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+                            for (int e = 0; e < 16; ++e)
+                                if (((ww[e >> 2] >> (8 * (e & 3))) & 0xffu) == 0) s[16 * v + e] = 0xff800000u;
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < BN; ++i)
+                            if (i < ncols && mp[int64_t(i) * p.ms[3]] == 0) s[i] = 0xff800000u;
+                    }
+                } else if (p.mask_kind == 2) {
+                    const uint16_t* mp = reinterpret_cast<const uint16_t*>(mrow) + int64_t(col0) * p.ms[3];
+                    if (vec && (reinterpret_cast<uintptr_t>(mp) & 15u) == 0) {
+#pragma unroll
+                        for (int v = 0; v < BN / 8; ++v) {
+                            const uint4 w = __ldg(reinterpret_cast<const uint4*>(mp) + v);
+                            const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) {
+                                const float a = from16<BF16>(uint16_t((ww[e >> 1] >> (16 * (e & 1))) & 0xffffu));
+                                s[8 * v + e] = __float_as_uint(fmaf(a, p.inv_scale, __uint_as_float(s[8 * v + e])));
+                            }
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < BN; ++i)
+                            if (i < ncols)
+                                s[i] = __float_as_uint(fmaf(from16<BF16>(mp[int64_t(i) * p.ms[3]]), p.inv_scale,
+                                                            __uint_as_float(s[i])));
+                    }
+                } else {
+                    const float* mp = reinterpret_cast<const float*>(mrow) + int64_t(col0) * p.ms[3];
+                    if (vec && (reinterpret_cast<uintptr_t>(mp) & 15u) == 0) {
+#pragma unroll
+                        for (int v = 0; v < BN / 4; ++v) {
+                            const float4 w = __ldg(reinterpret_cast<const float4*>(mp) + v);
+                            s[4 * v + 0] = __float_as_uint(fmaf(w.x, p.inv_scale, __uint_as_float(s[4 * v + 0])));
+                            s[4 * v + 1] = __float_as_uint(fmaf(w.y, p.inv_scale, __uint_as_float(s[4 * v + 1])));
+                            s[4 * v + 2] = __float_as_uint(fmaf(w.z, p.inv_scale, __uint_as_float(s[4 * v + 2])));
+                            s[4 * v + 3] = __float_as_uint(fmaf(w.w, p.inv_scale, __uint_as_float(s[4 * v + 3])));
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < BN; ++i)
+                            if (i < ncols)
+                                s[i] = __float_as_uint(fmaf(mp[int64_t(i) * p.ms[3]], p.inv_scale, __uint_as_float(s[i])));
+                    }
+                }
+            };
             float m = -INFINITY, m_next = -INFINITY, l = 0.f;
             bool move_ref = false;
             for (int j = 0; j < nt; ++j) {
@@ -405,6 +479,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                         for (int i = 0; i < BN; ++i)
                             if (i > limit) s[i] = 0xff800000u;  // -inf
                     }
+                    if (MASK) apply_mask(s, col0);
                     if (j == 0 || attempt == 1) {
                         float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
@@ -412,7 +487,10 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                             mx0 = fmax3(mx0, __uint_as_float(s[i]), __uint_as_float(s[i + 1]));
                             mx1 = fmax3(mx1, __uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]));
                         }
-                        const float m_new = (j == 0 || bad) ? fmaxf(mx0, mx1) : m;
+                        float m_new = (j == 0 || bad) ? fmaxf(mx0, mx1) : m;
+                        // every key so far masked out for this row: any finite reference will do (all
+                        // its P are 0); a row that stays that way ends as 0/0 = NaN like the reference
+                        if (MASK && m_new == -INFINITY) m_new = 0.f;
                         if (j > 0) {
                             const float alpha = ex2_approx((m - m_new) * c2);
                             l *= alpha;
@@ -531,7 +609,7 @@ bool sdpa_tc_supported(const Gpu* g, const paras_sdpa_args& a, const char** why)
     if (g->cc_major != 10) { *why = "GPU is not compute capability 10.x"; return false; }
     if (a.dtype != PARAS_BF16 && a.dtype != PARAS_F16) { *why = "dtype is not 16-bit"; return false; }
     if (a.D != HD) { *why = "head dim is not 128"; return false; }
-    if (a.mask) { *why = "explicit attn_mask"; return false; }
+    if (a.mask && (a.mask_kind < 1 || a.mask_kind > 3)) { *why = "unknown mask kind"; return false; }
     if (a.Lq < 1 || a.Lk < 1) { *why = "empty sequence"; return false; }
     if (!(a.scale > 0.0) || !std::isfinite(a.scale)) { *why = "scale is not positive"; return false; }
     if (a.Hq > 65535 || a.B > 65535) { *why = "batch or heads exceed the grid limit"; return false; }
@@ -566,6 +644,10 @@ int sdpa_tc_launch(Gpu* g, const paras_sdpa_args& a, float scale, cudaStream_t s
     p.scale = scale;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.inv_scale_log2 = 1.0f / p.scale_log2;
+    p.inv_scale = 1.0f / scale;
+    p.mask = a.mask;
+    p.mask_kind = a.mask ? a.mask_kind : 0;
+    for (int i = 0; i < 4; ++i) p.ms[i] = a.mask_strides[i];
     p.status = g->status_dev;
     p.nq = (a.Lq + kTilesPerCta * BM - 1) / (kTilesPerCta * BM);
     p.npair = (p.nq + 1) / 2;
@@ -574,15 +656,15 @@ int sdpa_tc_launch(Gpu* g, const paras_sdpa_args& a, float scale, cudaStream_t s
     p.units = int(units);
     const int sms = g->sm_count > 0 ? g->sm_count : 148;
     dim3 grid(unsigned(units < sms ? units : sms));  // persistent: one CTA per SM
-    if (a.dtype == PARAS_BF16) {
-        PB_CUDA(cudaFuncSetAttribute(sdpa_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     kSmemLaunch));
-        sdpa_tc_kernel<true><<<grid, kThreads, kSmemLaunch, s>>>(mq, mk, mv, mo, p);
-    } else {
-        PB_CUDA(cudaFuncSetAttribute(sdpa_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     kSmemLaunch));
-        sdpa_tc_kernel<false><<<grid, kThreads, kSmemLaunch, s>>>(mq, mk, mv, mo, p);
-    }
+    auto launch = [&](auto kernel) -> int {
+        PB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLaunch));
+        kernel<<<grid, kThreads, kSmemLaunch, s>>>(mq, mk, mv, mo, p);
+        return PARAS_OK;
+    };
+    const bool bf = a.dtype == PARAS_BF16;
+    if (p.mask_kind) st = bf ? launch(sdpa_tc_kernel<true, true>) : launch(sdpa_tc_kernel<false, true>);
+    else st = bf ? launch(sdpa_tc_kernel<true, false>) : launch(sdpa_tc_kernel<false, false>);
+    if (st != PARAS_OK) return st;
     PB_LAUNCH_CHECK("sdpa_tc_kernel");
     return PARAS_OK;
 }

@@ -158,7 +158,7 @@ const char* paras_b200_sdpa_last_kernel(void);
 
 /* The same attention on HOST-resident operands: q, k, v and out are host pointers ([B,H,L,D],
  * every batch element a dense [H,L,D] block; strides[0] may be larger).  The call moves batch
- * chunks (about 64 MB of operands each) through the GPU as a three-stage pipeline on three
+ * chunks (about 64 MB of operands each: batch elements, or head groups of one) through the GPU as a three-stage pipeline on three
  * streams -- host-to-device copy of chunk i+1, attention on chunk i, device-to-host copy of
  * chunk i-1 -- so that both directions of the link and the kernel overlap, and returns when the
  * result is in `out`.  Page-locked buffers (paras_b200_host_alloc, or registered with CUDA) are

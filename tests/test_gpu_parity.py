@@ -226,6 +226,54 @@ def test_sdpa_scores_that_grow_from_tile_to_tile(factor, causal, dtype):
     assert torch.allclose(lse.cpu().double(), torch.logsumexp(s, -1), atol=2e-3, rtol=2e-3)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("kind", ["bool_padding", "bool_blocks", "additive_same", "additive_f32", "ragged_bool"])
+def test_tensor_core_kernel_with_explicit_masks(kind, dtype):
+    # attn_mask on the tcgen05 path (16 bit, D = 128): bool and additive, broadcast strides,
+    # vector and element-wise reads, rows whose first key tiles are masked out entirely, and rows
+    # with no key at all (NaN, as in the reference)
+    B, Hq, Hkv = 2, 4, 2
+    Lq, Lk = (300, 333) if kind == "ragged_bool" else (384, 512)
+    q, k, v = _qkv(B, Hq, Hkv, Lq, Lk, 128, dtype, seed=23)
+    g = torch.Generator().manual_seed(29)
+    if kind == "bool_padding":      # per batch element: keys past its length are padding
+        lens = [Lk, 200]
+        mask = torch.zeros(B, 1, 1, Lk, dtype=torch.bool)
+        for b, n in enumerate(lens):
+            mask[b, :, :, :n] = True
+    elif kind == "bool_blocks":     # rows see a window that starts after the first key tile(s)
+        mask = torch.zeros(1, 1, Lq, Lk, dtype=torch.bool)
+        for r in range(Lq):
+            lo = 130 + (r % 7) * 40
+            mask[0, 0, r, lo:lo + 60] = True
+        mask[0, 0, 5] = False        # a row without any key
+        mask[0, 0, 200] = False
+    elif kind == "additive_same":
+        mask = (torch.randn(Lq, Lk, generator=g) * 2).to(dtype)
+    elif kind == "additive_f32":
+        mask = torch.randn(B, Hq, Lq, Lk, generator=g) * 2
+        mask[:, :, :, 100:160] = float("-inf")
+    else:
+        mask = torch.rand(B, Hq, Lq, Lk, generator=g) > 0.3
+    got = abi.sdpa_fwd(q.to(DEV), k.to(DEV), v.to(DEV), mask=mask.to(DEV), flags=abi.SDPA_REF_SCALE)
+    assert abi.sdpa_last_kernel() == "tcgen05"
+    if mask.dtype == torch.bool:
+        tol_check(got, O.sdpa(q, k, v, attn_mask=mask, enable_gqa=True), f"masked sdpa {kind} {dtype}")
+    else:
+        # The reference adds the mask to scores it has already rounded to 16 bits and rounds the sum
+        # again (attention_ops.cpp:96-126): with mask values of several units that is an error of
+        # a few percent in the probabilities.  The kernel keeps the sum in fp32, so it is checked
+        # against float64 attention on the same 16-bit inputs.
+        sc = float(torch.tensor(1 / math.sqrt(128)).to(dtype))
+        s = (q.double() @ k.double().repeat_interleave(Hq // Hkv, 1).transpose(-1, -2)) * sc + mask.double()
+        want = torch.softmax(s, -1) @ v.double().repeat_interleave(Hq // Hkv, 1)
+        assert (got.cpu().double() - want).abs().max().item() <= 2e-2, f"masked sdpa {kind} {dtype}"
+    simt = abi.sdpa_fwd(q.to(DEV), k.to(DEV), v.to(DEV), mask=mask.to(DEV),
+                        flags=abi.SDPA_REF_SCALE | abi.SDPA_FORCE_SIMT)
+    assert torch.equal(torch.isnan(got), torch.isnan(simt))
+    assert (got.float() - simt.float()).nan_to_num(0.0).abs().max().item() <= 2e-2
+
+
 def test_sdpa_empty_and_degenerate_shapes():
     z = torch.empty(1, 2, 0, 128, dtype=torch.bfloat16, device=DEV)
     kv = torch.randn(1, 2, 16, 128, device=DEV).bfloat16()
