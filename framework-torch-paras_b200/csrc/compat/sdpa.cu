@@ -4,7 +4,7 @@
 // heads must divide for GQA, is_causal and a mask tensor are exclusive, the default scale
 // is 1/sqrt(D).  Selection:
 //   * 16-bit, D == 128, no mask tensor, few queries   -> tensor-core split-KV decode kernel
-//   * 16-bit, D == 128 otherwise (masks included)     -> tcgen05/TMEM/TMA kernel
+//   * 16-bit, D == 128 or 64 otherwise (masks incl.)  -> tcgen05/TMEM/TMA kernel
 //   * everything else                                  -> CUDA-core kernel (sdpa_simt.cu)
 // There is no host fallback: an unsupported request is an error.
 #include <algorithm>

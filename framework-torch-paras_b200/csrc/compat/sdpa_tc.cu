@@ -1,5 +1,5 @@
 // Flash attention forward for sm_100a: tcgen05 tensor cores, TMEM accumulators, TMA-fed
-// K/V ring, warp-specialised roles.  16-bit tensors, head dim 128, causal (top-left
+// K/V ring, warp-specialised roles.  16-bit tensors, head dim 128 or 64, causal (top-left
 // aligned, csrc/ops/attention_ops.cpp:103-116), full, or explicitly masked (bool / additive,
 // attention_ops.cpp:117-126) attention, GQA by indexing the
 // shared kv head (never materialising the repeat_interleave of attention_ops.cpp:83-93).
@@ -54,7 +54,7 @@ using namespace tc;
 
 constexpr int BM = 128;            // query rows per tile (MMA M)
 constexpr int BN = 128;            // keys per tile (MMA N of QK^T, K of PV)
-constexpr int HD = 128;            // head dim
+constexpr int kMaxHD = 128;        // head dim: 128 or 64 (template parameter HD); shared memory and TMEM are laid out for 128
 constexpr int kTilesPerCta = 2;
 constexpr int kStages = 2;         // K/V ring slots; a slot holds the pair (V_j, K_j+1) that one step consumes
 constexpr int kChunkBytes = 64 * 2 * 128;    // 64 elements x 128 rows
@@ -158,7 +158,7 @@ __device__ __forceinline__ bool get_item(const TcParams& p, int seq, Item* it) {
 
 // MASK: an explicit attn_mask is applied (a separate instantiation: the unmasked kernel pays
 // nothing for it, not even registers).
-template <bool BF16, bool MASK>
+template <bool BF16, bool MASK, int HD>
 __global__ void __launch_bounds__(kThreads, 1)
 sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o,
@@ -170,6 +170,8 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + kSmemMisc);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + kSmemMisc + 4);
 
+    constexpr int kChunks = HD / 64;                 // 64-element slabs of the head dim
+    constexpr uint32_t kLoadBytes = kChunks * kChunkBytes;   // bytes one Q / K / V tile brings in
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (*reinterpret_cast<volatile int*>(&g_abort_latch)) return;  // uniform: before any barrier or TMEM use
 
@@ -221,10 +223,10 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                     if (!mbar_wait(bar(kBarKVEmpty + slot), ((g >> 1) & 1) ^ 1u, abort_flag, 2)) return false;
                     if (r == 0) mbar_arrive(full);
                 }
-                mbar_arrive_expect_tx(full, kTileBytes);
+                mbar_arrive_expect_tx(full, kLoadBytes);
                 const uint32_t dst = smem_base + kSmemKV + slot * kPairBytes + ((r & 1) ? 0 : kTileBytes);
-                tma_load_4d(dst, map, full, 0, row, hk, b);
-                tma_load_4d(dst + kChunkBytes, map, full, 64, row, hk, b);
+#pragma unroll
+                for (int c = 0; c < kChunks; ++c) tma_load_4d(dst + c * kChunkBytes, map, full, 64 * c, row, hk, b);
                 ++r;
                 return true;
             };
@@ -240,10 +242,11 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                         ok = mbar_wait(bar(kBarQEmpty + t), (qcnt[t] & 1u) ^ 1u, abort_flag, 0 + t);
                         if (!ok) break;
                         ++qcnt[t];
-                        mbar_arrive_expect_tx(bar(kBarQFull + t), kTileBytes);
+                        mbar_arrive_expect_tx(bar(kBarQFull + t), kLoadBytes);
                         const uint32_t dst = smem_base + kSmemQ + t * kTileBytes;
-                        tma_load_4d(dst, &map_q, bar(kBarQFull + t), 0, it.start[t], it.h, it.b);
-                        tma_load_4d(dst + kChunkBytes, &map_q, bar(kBarQFull + t), 64, it.start[t], it.h, it.b);
+#pragma unroll
+                        for (int c = 0; c < kChunks; ++c)
+                            tma_load_4d(dst + c * kChunkBytes, &map_q, bar(kBarQFull + t), 64 * c, it.start[t], it.h, it.b);
                     }
                 }
                 for (int x = 1; ok && x < 2 * it.n; ++x)
@@ -260,7 +263,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                 const uint32_t qa = smem_base + kSmemQ + t * kTileBytes;
                 const uint32_t ka = smem_base + kSmemKV + (pair & 1) * kPairBytes + kTileBytes;
 #pragma unroll
-                for (int c = 0; c < 2; ++c)
+                for (int c = 0; c < kChunks; ++c)
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
                         const uint32_t off = c * kChunkBytes + i * 32;  // 16 elements = 32 B
@@ -434,7 +437,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                 // after it) and PV_t(j) waits for this tile's P barrier, so O_t is quiescent here.
                 auto rescale_o = [&](float alpha) {
 #pragma unroll 1
-                    for (int c = 0; c < 8; ++c) {
+                    for (int c = 0; c < HD / 16; ++c) {
                         uint32_t o[16];
                         tmem_ld16(o_addr + 16 * c, o);
                         tmem_wait_ld();
@@ -540,7 +543,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             // chunk c ^ (r & 7)); rows past the end of the sequence are clipped by the tensor map.
             const int row_w = it.start[t] + wq * 32;
 #pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
+            for (int c = 0; c < HD / 32; ++c) {
                 uint32_t o[32];
                 tmem_ld32(o_addr + 32 * c, o);
                 tmem_wait_ld();
@@ -588,15 +591,15 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 }
 
 // ---- host side -------------------------------------------------------------------------
-// [B, H, L, 128] tensor with element strides st = {B, H, L}
-int make_map(CUtensorMap* map, const void* base, int dtype, int B, int H, int L,
+// [B, H, L, D] tensor with element strides st = {B, H, L}
+int make_map(CUtensorMap* map, const void* base, int dtype, int B, int H, int L, int D,
              const int64_t* st, int box_rows = BN) {
-    return make_tensor_map_bhld(map, base, dtype, B, H, L, HD, st, box_rows);
+    return make_tensor_map_bhld(map, base, dtype, B, H, L, D, st, box_rows);
 }
 
-bool strides_ok(const void* base, const int64_t* st, int B, int H, int L) {
+bool strides_ok(const void* base, const int64_t* st, int B, int H, int L, int D) {
     if (reinterpret_cast<uintptr_t>(base) & 15u) return false;
-    if (L > 1 && (st[2] < HD || (st[2] * 2) % 16)) return false;
+    if (L > 1 && (st[2] < D || (st[2] * 2) % 16)) return false;
     if (H > 1 && (st[1] <= 0 || (st[1] * 2) % 16)) return false;
     if (B > 1 && (st[0] <= 0 || (st[0] * 2) % 16)) return false;
     return true;
@@ -608,14 +611,14 @@ bool sdpa_tc_supported(const Gpu* g, const paras_sdpa_args& a, const char** why)
     *why = "";
     if (g->cc_major != 10) { *why = "GPU is not compute capability 10.x"; return false; }
     if (a.dtype != PARAS_BF16 && a.dtype != PARAS_F16) { *why = "dtype is not 16-bit"; return false; }
-    if (a.D != HD) { *why = "head dim is not 128"; return false; }
+    if (a.D != 128 && a.D != 64) { *why = "head dim is neither 128 nor 64"; return false; }
     if (a.mask && (a.mask_kind < 1 || a.mask_kind > 3)) { *why = "unknown mask kind"; return false; }
     if (a.Lq < 1 || a.Lk < 1) { *why = "empty sequence"; return false; }
     if (!(a.scale > 0.0) || !std::isfinite(a.scale)) { *why = "scale is not positive"; return false; }
     if (a.Hq > 65535 || a.B > 65535) { *why = "batch or heads exceed the grid limit"; return false; }
     if (g->smem_optin < size_t(kSmemLaunch)) { *why = "not enough shared memory"; return false; }
-    if (!strides_ok(a.q, a.q_strides, a.B, a.Hq, a.Lq) || !strides_ok(a.k, a.k_strides, a.B, a.Hkv, a.Lk) ||
-        !strides_ok(a.v, a.v_strides, a.B, a.Hkv, a.Lk) || !strides_ok(a.out, a.o_strides, a.B, a.Hq, a.Lq)) {
+    if (!strides_ok(a.q, a.q_strides, a.B, a.Hq, a.Lq, a.D) || !strides_ok(a.k, a.k_strides, a.B, a.Hkv, a.Lk, a.D) ||
+        !strides_ok(a.v, a.v_strides, a.B, a.Hkv, a.Lk, a.D) || !strides_ok(a.out, a.o_strides, a.B, a.Hq, a.Lq, a.D)) {
         *why = "pointers or strides are not 16-byte aligned";
         return false;
     }
@@ -631,10 +634,10 @@ int sdpa_tc_launch(Gpu* g, const paras_sdpa_args& a, float scale, cudaStream_t s
         return st;
     }
     CUtensorMap mq, mk, mv, mo;
-    if ((st = make_map(&mq, a.q, a.dtype, a.B, a.Hq, a.Lq, a.q_strides)) != PARAS_OK) return st;
-    if ((st = make_map(&mk, a.k, a.dtype, a.B, a.Hkv, a.Lk, a.k_strides)) != PARAS_OK) return st;
-    if ((st = make_map(&mv, a.v, a.dtype, a.B, a.Hkv, a.Lk, a.v_strides)) != PARAS_OK) return st;
-    if ((st = make_map(&mo, a.out, a.dtype, a.B, a.Hq, a.Lq, a.o_strides, 32)) != PARAS_OK) return st;
+    if ((st = make_map(&mq, a.q, a.dtype, a.B, a.Hq, a.Lq, a.D, a.q_strides)) != PARAS_OK) return st;
+    if ((st = make_map(&mk, a.k, a.dtype, a.B, a.Hkv, a.Lk, a.D, a.k_strides)) != PARAS_OK) return st;
+    if ((st = make_map(&mv, a.v, a.dtype, a.B, a.Hkv, a.Lk, a.D, a.v_strides)) != PARAS_OK) return st;
+    if ((st = make_map(&mo, a.out, a.dtype, a.B, a.Hq, a.Lq, a.D, a.o_strides, 32)) != PARAS_OK) return st;
     TcParams p{};
     p.out = a.out;
     p.lse = a.lse;
@@ -662,8 +665,13 @@ int sdpa_tc_launch(Gpu* g, const paras_sdpa_args& a, float scale, cudaStream_t s
         return PARAS_OK;
     };
     const bool bf = a.dtype == PARAS_BF16;
-    if (p.mask_kind) st = bf ? launch(sdpa_tc_kernel<true, true>) : launch(sdpa_tc_kernel<false, true>);
-    else st = bf ? launch(sdpa_tc_kernel<true, false>) : launch(sdpa_tc_kernel<false, false>);
+    if (a.D == 128) {
+        if (p.mask_kind) st = bf ? launch(sdpa_tc_kernel<true, true, 128>) : launch(sdpa_tc_kernel<false, true, 128>);
+        else st = bf ? launch(sdpa_tc_kernel<true, false, 128>) : launch(sdpa_tc_kernel<false, false, 128>);
+    } else {
+        if (p.mask_kind) st = bf ? launch(sdpa_tc_kernel<true, true, 64>) : launch(sdpa_tc_kernel<false, true, 64>);
+        else st = bf ? launch(sdpa_tc_kernel<true, false, 64>) : launch(sdpa_tc_kernel<false, false, 64>);
+    }
     if (st != PARAS_OK) return st;
     PB_LAUNCH_CHECK("sdpa_tc_kernel");
     return PARAS_OK;

@@ -100,6 +100,8 @@ SDPA_CASES = [
     (2, 8, 2, 1, 700, 128, False),      # decode step, GQA
     (1, 4, 4, 7, 260, 128, False),      # a few query rows
     (1, 2, 2, 129, 129, 64, True),      # D = 64
+    (2, 4, 2, 640, 640, 64, True),      # D = 64 on the tensor-core kernel: GQA, several kv tiles
+    (1, 2, 2, 300, 456, 64, False),     # D = 64, ragged, Lq != Lk
     (1, 3, 1, 50, 77, 32, False),       # small D, GQA 3:1
 ]
 
@@ -272,6 +274,20 @@ def test_tensor_core_kernel_with_explicit_masks(kind, dtype):
                         flags=abi.SDPA_REF_SCALE | abi.SDPA_FORCE_SIMT)
     assert torch.equal(torch.isnan(got), torch.isnan(simt))
     assert (got.float() - simt.float()).nan_to_num(0.0).abs().max().item() <= 2e-2
+
+
+def test_head_dim_64_runs_on_the_tensor_core_kernel_with_masks_and_lse():
+    q, k, v = _qkv(2, 4, 2, 333, 400, 64, torch.bfloat16, seed=31)
+    mask = torch.rand(2, 1, 333, 400, generator=torch.Generator().manual_seed(5)) > 0.4
+    want = O.sdpa(q, k, v, attn_mask=mask, enable_gqa=True)
+    got, lse = abi.sdpa_fwd(q.to(DEV), k.to(DEV), v.to(DEV), mask=mask.to(DEV), return_lse=True,
+                            flags=abi.SDPA_REF_SCALE)
+    assert abi.sdpa_last_kernel() == "tcgen05"
+    tol_check(got, want, "D=64 masked")
+    sc = float(torch.tensor(1 / math.sqrt(64)).bfloat16())
+    s = (q.float() @ k.float().repeat_interleave(2, 1).transpose(-1, -2)) * sc
+    s = s.masked_fill(~mask, float("-inf"))
+    assert torch.allclose(lse.cpu(), torch.logsumexp(s, -1), atol=2e-3, rtol=2e-3)
 
 
 def test_sdpa_empty_and_degenerate_shapes():
