@@ -215,69 +215,6 @@ __device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_
         : "memory");
 }
 
-// Eight K=16 MMAs over one 128-byte-swizzled K=128 operand pair in ONE asm block, so that the
-// issuing thread spends as few instructions per MMA as possible (it is a single thread, every
-// instruction of it is latency on the chain that bounds the attention kernel): the descriptors
-// differ only in their address field, which is stepped by adds on the low word.
-//   a_lo / b_lo: low words of the two descriptors for k-step 0; hi words are shared
-//   STEP_A / STEP_B: address-field increment per K=16 step inside a 64-element slab (bytes >> 4)
-//   SLAB_A / SLAB_B: address-field distance between the two slabs (k-steps 0-3 and 4-7)
-template <int STEP_A, int SLAB_A, int STEP_B, int SLAB_B>
-__device__ __forceinline__ void mma_ss_x8(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
-                                          uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t.reg .b32 al, bl;\n\t.reg .b64 da, db;\n\t"
-        "setp.ne.b32 p, %6, 0;\n\t"
-        "mov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t"
-        "setp.eq.b32 p, %5, %5;\n\t"
-        "add.u32 al, %1, %7;\n\tadd.u32 bl, %3, %9;\n\tmov.b64 da, {al, %2};\n\tmov.b64 db, {bl, %4};\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t"
-        "add.u32 al, %1, 2*%7;\n\tadd.u32 bl, %3, 2*%9;\n\tmov.b64 da, {al, %2};\n\tmov.b64 db, {bl, %4};\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t"
-        "add.u32 al, %1, 3*%7;\n\tadd.u32 bl, %3, 3*%9;\n\tmov.b64 da, {al, %2};\n\tmov.b64 db, {bl, %4};\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t"
-        "add.u32 al, %1, %8;\n\tadd.u32 bl, %3, %10;\n\tmov.b64 da, {al, %2};\n\tmov.b64 db, {bl, %4};\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t"
-        "add.u32 al, %1, %8+%7;\n\tadd.u32 bl, %3, %10+%9;\n\tmov.b64 da, {al, %2};\n\tmov.b64 db, {bl, %4};\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t"
-        "add.u32 al, %1, %8+2*%7;\n\tadd.u32 bl, %3, %10+2*%9;\n\tmov.b64 da, {al, %2};\n\tmov.b64 db, {bl, %4};\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t"
-        "add.u32 al, %1, %8+3*%7;\n\tadd.u32 bl, %3, %10+3*%9;\n\tmov.b64 da, {al, %2};\n\tmov.b64 db, {bl, %4};\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}"
-        ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate),
-          "n"(STEP_A), "n"(SLAB_A), "n"(STEP_B), "n"(SLAB_B)
-        : "memory");
-}
-// Eight K=16 MMAs with A from TMEM (8 columns of packed 16-bit values per step) and B stepping
-// through one shared-memory operand by STEP_B.
-template <int STEP_B>
-__device__ __forceinline__ void mma_ts_x8(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t b_hi,
-                                          uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t.reg .b32 at, bl;\n\t.reg .b64 db;\n\t"
-        "setp.ne.b32 p, %5, 0;\n\t"
-        "mov.b64 db, {%2, %3};\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t"
-        "setp.eq.b32 p, %4, %4;\n\t"
-        "add.u32 at, %1, 8;\n\tadd.u32 bl, %2, %6;\n\tmov.b64 db, {bl, %3};\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [at], db, %4, p;\n\t"
-        "add.u32 at, %1, 16;\n\tadd.u32 bl, %2, 2*%6;\n\tmov.b64 db, {bl, %3};\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [at], db, %4, p;\n\t"
-        "add.u32 at, %1, 24;\n\tadd.u32 bl, %2, 3*%6;\n\tmov.b64 db, {bl, %3};\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [at], db, %4, p;\n\t"
-        "add.u32 at, %1, 32;\n\tadd.u32 bl, %2, 4*%6;\n\tmov.b64 db, {bl, %3};\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [at], db, %4, p;\n\t"
-        "add.u32 at, %1, 40;\n\tadd.u32 bl, %2, 5*%6;\n\tmov.b64 db, {bl, %3};\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [at], db, %4, p;\n\t"
-        "add.u32 at, %1, 48;\n\tadd.u32 bl, %2, 6*%6;\n\tmov.b64 db, {bl, %3};\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [at], db, %4, p;\n\t"
-        "add.u32 at, %1, 56;\n\tadd.u32 bl, %2, 7*%6;\n\tmov.b64 db, {bl, %3};\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [at], db, %4, p;\n\t}"
-        ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate), "n"(STEP_B)
-        : "memory");
-}
-
 // ---- TMEM <-> registers: 32 lanes x 32 bit, N consecutive columns; thread i of the warp
 // addresses TMEM lane (lane field of taddr) + i --------------------------------------------
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
