@@ -377,6 +377,19 @@ def run_ours(args):
         res["global_batch_all_ranks"] = Bp * world
         extra["config5_decoder_block_share"] = res
         del xh, qb, kb, vb, gb, ub, y1, ob, y2, sb
+    if want("bwd"):
+        # Attention backward at the headline shape (config 2): forward with lse, then dq, dk, dv.
+        # FLOPs counted as 2.5x the forward's algorithmic FLOPs (five products instead of two),
+        # causal half included, although this implementation computes the full [L, L] matrices.
+        Bb = 2 if args.small else c["B"]
+        qb_, kb_, vb_ = q[:Bb].contiguous(), k[:Bb].contiguous(), v[:Bb].contiguous()
+        dob = gen((Bb, c["Hq"], c["S"], c["D"]), 25)
+        ob, lseb = abi.sdpa_fwd(qb_, kb_, vb_, causal=True, return_lse=True)
+        t = loop_ms(lambda: abi.sdpa_bwd(dob, qb_, kb_, vb_, ob, lseb, causal=True), s3, 3)
+        fl = 2.5 * sdpa_flops(Bb, c["Hq"], c["S"], c["S"], c["D"], True)
+        extra[f"sdpa_backward_B{Bb}_H{c['Hq']}_S{c['S']}"] = {"ms": t, "tflops": fl / (t * 1e-3) / 1e12,
+                                                            "note": "five batched GEMMs + two element-wise passes over materialised [L,L] matrices"}
+        del qb_, kb_, vb_, dob, ob, lseb
     if want("gemm"):
         # The projections either side of the path at config 2 / 5 sizes (hidden 4096, FFN 14336):
         # fused QKV projection [rows,4096] x [6144,4096]^T (Hq=32, Hkv=8, D=128) and the gate/up
@@ -489,7 +502,7 @@ def main():
     ap.add_argument("--small", action="store_true",
                     help="shrink the extra workloads (SwiGLU 8192 rows, decode batch 8) so that a profiler "
                          "capture holds about 1 GB on the device; rates stay per-byte comparable")
-    ap.add_argument("--only", choices=["rmsnorm", "swiglu", "gqa", "decode", "block", "gemm"],
+    ap.add_argument("--only", choices=["rmsnorm", "swiglu", "gqa", "decode", "block", "gemm", "bwd"],
                     help="after the headline loop run just this extra workload and print it (for profiling)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-repeat", type=int, default=3)

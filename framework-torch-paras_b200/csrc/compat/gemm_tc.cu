@@ -2,7 +2,7 @@
 // the attention / RMSNorm / SwiGLU path (mm, bmm, addmm, linear: csrc/ops/vision_ops.cpp:
 // 248-309, 388-423 hand these to the host's libtorch and copy the result back).
 //
-//   C[b][M,N] = A[b][M,K] * B[b]        A: rows of K contiguous elements
+//   C[b][M,N] = A[b][M,K] * B[b]        A: [M,K] rows of K, or [K,M] rows of M (a transposed operand)
 //                                       B: [N,K] rows of K (a Linear weight), or [K,N] rows of N
 //   epilogues: none | + bias[N] | SwiGLU: C[M,F] = silu(A Wg^T) * (A Wu^T) from one pass over A
 //
@@ -78,7 +78,7 @@ __device__ __forceinline__ Tile get_tile(const GemmParams& p, int id, int n_per_
     return t;
 }
 
-template <bool BF16, bool B_ROWS_OF_N, int EPI>
+template <bool BF16, bool A_ROWS_OF_M, bool B_ROWS_OF_N, int EPI>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const __grid_constant__ CUtensorMap map_b2, const __grid_constant__ CUtensorMap map_c,
@@ -137,7 +137,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     mbar_arrive_expect_tx(full, kStageBytes);
                     const uint32_t a_dst = smem_base + st * kStageBytes;
                     const uint32_t b_dst = a_dst + kABytes;
-                    tma_load_3d(a_dst, &map_a, full, kk * BK, t.m0, t.b);
+                    if (A_ROWS_OF_M) {
+                        // A is [K, M]: two 64-row-of-M slabs of 64 K-rows each
+#pragma unroll
+                        for (int i = 0; i < BM / 64; ++i)
+                            tma_load_3d(a_dst + i * (BK * 128), &map_a, full, t.m0 + 64 * i, kk * BK, t.b);
+                    } else {
+                        tma_load_3d(a_dst, &map_a, full, kk * BK, t.m0, t.b);
+                    }
                     if (B_ROWS_OF_N) {
                         // B is [K, N]: four 64-column slabs of 64 K-rows each
 #pragma unroll
@@ -155,7 +162,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     } else if (warp == kMmaWarp) {
         // ------------------------------ MMA issuer --------------------------------
         if (lane == 0) {
-            constexpr uint32_t idesc = instr_desc_f16(BF16 ? 1 : 0, BM, BN, false, B_ROWS_OF_N);
+            constexpr uint32_t idesc = instr_desc_f16(BF16 ? 1 : 0, BM, BN, A_ROWS_OF_M, B_ROWS_OF_N);
             bool ok = true;
             int it = 0, local = 0;
             for (int id = blockIdx.x; ok && id < p.tiles; id += gridDim.x, ++local) {
@@ -173,7 +180,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     const uint32_t b_addr = a_addr + kABytes;
 #pragma unroll
                     for (int ks = 0; ks < BK / 16; ++ks) {
-                        const uint64_t a_desc = smem_desc_sw128(a_addr + ks * 32, 16, 1024);
+                        const uint64_t a_desc = A_ROWS_OF_M
+                            ? smem_desc_sw128(a_addr + ks * 16 * 128, BK * 128, 1024)
+                            : smem_desc_sw128(a_addr + ks * 32, 16, 1024);
                         const uint64_t b_desc = B_ROWS_OF_N
                             ? smem_desc_sw128(b_addr + ks * 16 * 128, BK * 128, 1024)
                             : smem_desc_sw128(b_addr + ks * 32, 16, 1024);
@@ -292,10 +301,10 @@ bool aligned16(const void* ptr, int64_t ld) {
     return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0 && ld % 8 == 0 && ld > 0;
 }
 
-template <bool BF16, bool B_ROWS_OF_N, int EPI>
+template <bool BF16, bool A_ROWS_OF_M, bool B_ROWS_OF_N, int EPI>
 int launch(Gpu* g, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mb2,
            const CUtensorMap& mc, const GemmParams& p, cudaStream_t s) {
-    auto kernel = gemm_tc_kernel<BF16, B_ROWS_OF_N, EPI>;
+    auto kernel = gemm_tc_kernel<BF16, A_ROWS_OF_M, B_ROWS_OF_N, EPI>;
     PB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal));
     const int sms = g->sm_count > 0 ? g->sm_count : 148;
     kernel<<<dim3(unsigned(p.tiles < sms ? p.tiles : sms)), kThreads, kSmemTotal, s>>>(ma, mb, mb2, mc, p);
@@ -317,6 +326,10 @@ extern "C" int paras_b200_gemm(const paras_gemm_args* a) {
         return fail(PARAS_E_INVALID, "paras gemm: bad epilogue %d", a->epilogue);
     if (a->b_layout != PARAS_GEMM_B_NK && a->b_layout != PARAS_GEMM_B_KN)
         return fail(PARAS_E_INVALID, "paras gemm: bad b_layout %d", a->b_layout);
+    if (a->a_layout != PARAS_GEMM_A_MK && a->a_layout != PARAS_GEMM_A_KM)
+        return fail(PARAS_E_INVALID, "paras gemm: bad a_layout %d", a->a_layout);
+    if (a->a_layout == PARAS_GEMM_A_KM && a->epilogue != kEpiNone)
+        return fail(PARAS_E_UNSUPPORTED, "paras gemm: epilogues take A as rows of K");
     int st;
     Gpu* g = use_gpu(a->gpu, &st);
     if (!g) return st;
@@ -341,9 +354,14 @@ extern "C" int paras_b200_gemm(const paras_gemm_args* a) {
     }
 
     const bool kn = a->b_layout == PARAS_GEMM_B_KN;
+    const bool at = a->a_layout == PARAS_GEMM_A_KM;
     const int n_per_tile = a->epilogue == kEpiSwiglu ? BN / 2 : BN;
     CUtensorMap ma, mb, mb2, mc;
-    if ((st = make_tensor_map_3d(&ma, a->a, a->dtype, a->K, a->M, a->batch, a->lda, a->stride_a, BK, BM)) != PARAS_OK) return st;
+    if (at) {
+        if ((st = make_tensor_map_3d(&ma, a->a, a->dtype, a->M, a->K, a->batch, a->lda, a->stride_a, 64, BK)) != PARAS_OK) return st;
+    } else {
+        if ((st = make_tensor_map_3d(&ma, a->a, a->dtype, a->K, a->M, a->batch, a->lda, a->stride_a, BK, BM)) != PARAS_OK) return st;
+    }
     if (kn) {
         if ((st = make_tensor_map_3d(&mb, a->b, a->dtype, a->N, a->K, a->batch, a->ldb, a->stride_b, 64, BK)) != PARAS_OK) return st;
     } else {
@@ -366,9 +384,10 @@ extern "C" int paras_b200_gemm(const paras_gemm_args* a) {
     p.status = g->status_dev;
     cudaStream_t s = pick_stream(g, a->stream);
     const bool bf = a->dtype == PARAS_BF16;
-#define PB_GEMM(KN, EPI) (bf ? launch<true, KN, EPI>(g, ma, mb, mb2, mc, p, s) : launch<false, KN, EPI>(g, ma, mb, mb2, mc, p, s))
-    if (a->epilogue == kEpiSwiglu) return PB_GEMM(false, kEpiSwiglu);
-    if (a->epilogue == kEpiBias) return kn ? PB_GEMM(true, kEpiBias) : PB_GEMM(false, kEpiBias);
-    return kn ? PB_GEMM(true, kEpiNone) : PB_GEMM(false, kEpiNone);
+#define PB_GEMM(AT, KN, EPI) (bf ? launch<true, AT, KN, EPI>(g, ma, mb, mb2, mc, p, s) : launch<false, AT, KN, EPI>(g, ma, mb, mb2, mc, p, s))
+    if (a->epilogue == kEpiSwiglu) return PB_GEMM(false, false, kEpiSwiglu);
+    if (a->epilogue == kEpiBias) return kn ? PB_GEMM(false, true, kEpiBias) : PB_GEMM(false, false, kEpiBias);
+    if (at) return kn ? PB_GEMM(true, true, kEpiNone) : PB_GEMM(true, false, kEpiNone);
+    return kn ? PB_GEMM(false, true, kEpiNone) : PB_GEMM(false, false, kEpiNone);
 #undef PB_GEMM
 }

@@ -1,0 +1,204 @@
+// Attention backward (the gradient the reference obtains by autograd through its composite
+// sdpa_math, csrc/ops/attention_ops.cpp:71-136: mm / mul / masked_fill / softmax / mm, each with
+// 16-bit intermediates).  Not a fused kernel: the row statistics the forward pass returns (lse)
+// make the probabilities a pure element-wise function of the scores, so the gradient is five
+// batched GEMMs on the tcgen05 GEMM of gemm_tc.cu and two element-wise passes, per kv-head group:
+//
+//   S  = Q K^T                      [R, Lk]   R = (Hq/Hkv) * Lq rows: the group's query heads stacked
+//   P  = exp(S*scale - lse[row])    in place, causal entries zeroed
+//   dV = P^T dO                     [Lk, D]   (sums over the group's heads by construction)
+//   dP = dO V^T                     [R, Lk]
+//   dS = P o (dP - delta[row]) * scale        delta = rowsum(dO o O), in place
+//   dK = dS^T Q                     [Lk, D]
+//   dQ = dS K                       [R, D]
+//
+// S and dP are materialised for a chunk of groups at a time (about 1 GB each), so the work is
+// bound by HBM traffic on those two matrices, not by the tensor pipe.
+#include <algorithm>
+#include <cmath>
+
+#include "common.cuh"
+
+namespace pb {
+namespace {
+
+template <typename T>
+__global__ void sdpa_bwd_delta_kernel(const T* __restrict__ dout, const T* __restrict__ out,
+                                      float* __restrict__ delta, int64_t rows, int D) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    const int64_t nwarps = (int64_t(gridDim.x) * blockDim.x) >> 5;
+    constexpr int N = Vec16<T>::N;
+    for (int64_t row = warp; row < rows; row += nwarps) {
+        const T* a = dout + row * D;
+        const T* b = out + row * D;
+        float acc = 0.f;
+        for (int d = lane * N; d < D; d += 32 * N) {
+            const Vec16<T> x = ld16(a + d), y = ld16(b + d);
+#pragma unroll
+            for (int e = 0; e < N; ++e) acc = fmaf(to_f32<T>(x.v[e]), to_f32<T>(y.v[e]), acc);
+        }
+        acc = warp_sum(acc);
+        if (lane == 0) delta[row] = acc;
+    }
+}
+
+// mat: [groups][R][Lk] 16-bit, 16-byte vectors along Lk.  MODE 0: S -> P;  MODE 1: dP -> dS (needs P).
+template <typename T, int MODE>
+__global__ void sdpa_bwd_rowwise_kernel(T* __restrict__ mat, const T* __restrict__ prob,
+                                        const float* __restrict__ row_stat, int64_t groups, int R, int Lq,
+                                        int Lk, int causal, float scale, float scale_log2) {
+    constexpr int N = Vec16<T>::N;
+    const int vec_per_row = Lk / N;
+    const int64_t total = groups * int64_t(R) * vec_per_row;
+    for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+         i += int64_t(gridDim.x) * blockDim.x) {
+        const int64_t row = i / vec_per_row;          // global row: group * R + r
+        const int col0 = int(i - row * vec_per_row) * N;
+        const int qpos = int(row % R) % Lq;           // query position inside its head
+        const float stat = row_stat[row];
+        Vec16<T> x = ld16(mat + row * Lk + col0);
+        Vec16<T> y;
+        if (MODE == 1) {
+            const Vec16<T> pr = ld16(prob + row * Lk + col0);
+#pragma unroll
+            for (int e = 0; e < N; ++e)
+                y.v[e] = from_f32<T>(to_f32<T>(pr.v[e]) * (to_f32<T>(x.v[e]) - stat) * scale);
+        } else {
+            const float neg = -stat * 1.4426950408889634f;
+#pragma unroll
+            for (int e = 0; e < N; ++e) {
+                const bool keep = !causal || col0 + e <= qpos;
+                y.v[e] = from_f32<T>(keep ? exp2f(fmaf(to_f32<T>(x.v[e]), scale_log2, neg)) : 0.f);
+            }
+        }
+        st16(mat + row * Lk + col0, y);
+    }
+}
+
+}  // namespace
+}  // namespace pb
+
+using pb::fail;
+using pb::Gpu;
+
+extern "C" int paras_b200_sdpa_bwd(const paras_sdpa_bwd_args* a) {
+    using namespace pb;
+    if (!a) return fail(PARAS_E_INVALID, "paras sdpa backward: null argument block");
+    if (a->dtype != PARAS_BF16 && a->dtype != PARAS_F16)
+        return fail(PARAS_E_UNSUPPORTED, "paras sdpa backward: bfloat16 or float16 tensors");
+    if (a->B < 0 || a->Hq < 0 || a->Hkv < 0 || a->Lq < 0 || a->Lk < 0 || a->D < 0)
+        return fail(PARAS_E_INVALID, "paras sdpa backward: negative dimension");
+    if (a->Hkv == 0 ? a->Hq != 0 : (a->Hq % a->Hkv) != 0)
+        return fail(PARAS_E_INVALID, "paras sdpa backward: query heads must be a multiple of key/value heads");
+    int st;
+    Gpu* g = use_gpu(a->gpu, &st);
+    if (!g) return st;
+    if (int64_t(a->B) * a->Hq * a->Lq * a->D == 0 || int64_t(a->B) * a->Hkv * a->Lk * a->D == 0) {
+        // nothing flows: gradients of empty tensors are empty, of unreached keys zero
+        cudaStream_t s0 = pick_stream(g, a->stream);
+        const size_t es0 = 2;
+        if (a->dq && int64_t(a->B) * a->Hq * a->Lq * a->D)
+            PB_CUDA(cudaMemsetAsync(a->dq, 0, size_t(a->B) * a->Hq * a->Lq * a->D * es0, s0));
+        if (a->dk && int64_t(a->B) * a->Hkv * a->Lk * a->D) {
+            PB_CUDA(cudaMemsetAsync(a->dk, 0, size_t(a->B) * a->Hkv * a->Lk * a->D * es0, s0));
+            PB_CUDA(cudaMemsetAsync(a->dv, 0, size_t(a->B) * a->Hkv * a->Lk * a->D * es0, s0));
+        }
+        return PARAS_OK;
+    }
+    if (!a->q || !a->k || !a->v || !a->out || !a->dout || !a->lse || !a->dq || !a->dk || !a->dv)
+        return fail(PARAS_E_INVALID, "paras sdpa backward: null pointer");
+    const int r = a->Hq / a->Hkv;
+    const int64_t R = int64_t(r) * a->Lq;
+    if (a->D % 8 || a->Lk % 8 || R > INT32_MAX)
+        return fail(PARAS_E_UNSUPPORTED,
+                    "paras sdpa backward: head dim and key length must be multiples of 8 (16-byte rows)");
+    for (const void* ptr : {a->q, a->k, a->v, a->out, a->dout, (const void*)a->dq, (const void*)a->dk, (const void*)a->dv})
+        if (reinterpret_cast<uintptr_t>(ptr) & 15u)
+            return fail(PARAS_E_UNSUPPORTED, "paras sdpa backward: tensors must be 16-byte aligned");
+    cudaStream_t s = pick_stream(g, a->stream);
+    const size_t es = 2;
+    const int64_t groups = int64_t(a->B) * a->Hkv;     // (batch, kv head): its r query heads are adjacent
+    const int64_t rows = groups * R;
+
+    // scratch: delta [rows] fp32, S/P and dP/dS for a chunk of groups
+    const size_t mat_bytes_per_group = size_t(R) * a->Lk * es;
+    int64_t chunk = std::max<int64_t>(1, (int64_t(1) << 30) / int64_t(std::max<size_t>(mat_bytes_per_group, 1)));
+    chunk = std::min(chunk, groups);
+    const size_t delta_bytes = (size_t(rows) * sizeof(float) + 255) & ~size_t(255);
+    const size_t mat_bytes = (mat_bytes_per_group * size_t(chunk) + 255) & ~size_t(255);
+    void* scratch = nullptr;
+    st = paras_b200_malloc_async(a->gpu, delta_bytes + 2 * mat_bytes, s, &scratch);
+    if (st != PARAS_OK) return st;
+    float* delta = static_cast<float*>(scratch);
+    char* smat = static_cast<char*>(scratch) + delta_bytes;
+    char* dpmat = smat + mat_bytes;
+
+    const int sms = g->sm_count > 0 ? g->sm_count : 148;
+    const float scale = float(a->scale);
+    const float scale_log2 = scale * 1.4426950408889634f;
+    auto run = [&]() -> int {
+        if (a->dtype == PARAS_BF16)
+            sdpa_bwd_delta_kernel<__nv_bfloat16><<<sms * 8, 256, 0, s>>>(
+                static_cast<const __nv_bfloat16*>(a->dout), static_cast<const __nv_bfloat16*>(a->out), delta, rows, a->D);
+        else
+            sdpa_bwd_delta_kernel<__half><<<sms * 8, 256, 0, s>>>(
+                static_cast<const __half*>(a->dout), static_cast<const __half*>(a->out), delta, rows, a->D);
+        PB_LAUNCH_CHECK("sdpa_bwd_delta_kernel");
+        for (int64_t g0 = 0; g0 < groups; g0 += chunk) {
+            const int64_t n = std::min(chunk, groups - g0);
+            const char* q = static_cast<const char*>(a->q) + size_t(g0) * R * a->D * es;
+            const char* dO = static_cast<const char*>(a->dout) + size_t(g0) * R * a->D * es;
+            const char* k = static_cast<const char*>(a->k) + size_t(g0) * a->Lk * a->D * es;
+            const char* v = static_cast<const char*>(a->v) + size_t(g0) * a->Lk * a->D * es;
+            char* dq = static_cast<char*>(a->dq) + size_t(g0) * R * a->D * es;
+            char* dk = static_cast<char*>(a->dk) + size_t(g0) * a->Lk * a->D * es;
+            char* dv = static_cast<char*>(a->dv) + size_t(g0) * a->Lk * a->D * es;
+            auto gemm = [&](const void* A, int a_layout, int64_t lda, int64_t sa, const void* Bm, int b_layout,
+                            int64_t ldb, int64_t sb, void* C, int64_t ldc, int64_t sc, int64_t M, int64_t N,
+                            int64_t K) -> int {
+                paras_gemm_args ga{};
+                ga.a = A; ga.b = Bm; ga.c = C;
+                ga.M = M; ga.N = N; ga.K = K;
+                ga.lda = lda; ga.ldb = ldb; ga.ldc = ldc;
+                ga.batch = n; ga.stride_a = sa; ga.stride_b = sb; ga.stride_c = sc;
+                ga.dtype = a->dtype; ga.a_layout = a_layout; ga.b_layout = b_layout;
+                ga.epilogue = PARAS_GEMM_EPI_NONE; ga.gpu = a->gpu; ga.stream = s;
+                return paras_b200_gemm(&ga);
+            };
+            const int64_t qs = R * a->D, ks = int64_t(a->Lk) * a->D, ms = R * a->Lk;
+            int rc;
+            // S = Q K^T
+            if ((rc = gemm(q, PARAS_GEMM_A_MK, a->D, qs, k, PARAS_GEMM_B_NK, a->D, ks, smat, a->Lk, ms, R, a->Lk, a->D)) != PARAS_OK) return rc;
+            const int blocks = sms * 16;
+#define PB_ROWWISE(MODE, MAT, PROB, STAT)                                                                 \
+    if (a->dtype == PARAS_BF16)                                                                            \
+        sdpa_bwd_rowwise_kernel<__nv_bfloat16, MODE><<<blocks, 256, 0, s>>>(                               \
+            reinterpret_cast<__nv_bfloat16*>(MAT), reinterpret_cast<const __nv_bfloat16*>(PROB), STAT, n,  \
+            int(R), a->Lq, a->Lk, a->causal, scale, scale_log2);                                          \
+    else                                                                                                   \
+        sdpa_bwd_rowwise_kernel<__half, MODE><<<blocks, 256, 0, s>>>(                                      \
+            reinterpret_cast<__half*>(MAT), reinterpret_cast<const __half*>(PROB), STAT, n, int(R), a->Lq, \
+            a->Lk, a->causal, scale, scale_log2);
+            // P = exp(S*scale - lse)
+            PB_ROWWISE(0, smat, smat, a->lse + g0 * R)
+            PB_LAUNCH_CHECK("sdpa_bwd_rowwise_kernel");
+            // dV = P^T dO
+            if ((rc = gemm(smat, PARAS_GEMM_A_KM, a->Lk, ms, dO, PARAS_GEMM_B_KN, a->D, qs, dv, a->D, ks, a->Lk, a->D, R)) != PARAS_OK) return rc;
+            // dP = dO V^T
+            if ((rc = gemm(dO, PARAS_GEMM_A_MK, a->D, qs, v, PARAS_GEMM_B_NK, a->D, ks, dpmat, a->Lk, ms, R, a->Lk, a->D)) != PARAS_OK) return rc;
+            // dS = P o (dP - delta) * scale
+            PB_ROWWISE(1, dpmat, smat, delta + g0 * R)
+            PB_LAUNCH_CHECK("sdpa_bwd_rowwise_kernel");
+#undef PB_ROWWISE
+            // dK = dS^T Q
+            if ((rc = gemm(dpmat, PARAS_GEMM_A_KM, a->Lk, ms, q, PARAS_GEMM_B_KN, a->D, qs, dk, a->D, ks, a->Lk, a->D, R)) != PARAS_OK) return rc;
+            // dQ = dS K
+            if ((rc = gemm(dpmat, PARAS_GEMM_A_MK, a->Lk, ms, k, PARAS_GEMM_B_KN, a->D, ks, dq, a->D, qs, R, a->D, a->Lk)) != PARAS_OK) return rc;
+        }
+        return PARAS_OK;
+    };
+    st = run();
+    const int st2 = paras_b200_free_async(a->gpu, scratch, s);
+    return st != PARAS_OK ? st : st2;
+}

@@ -140,10 +140,92 @@ Tensor sdpa(const Tensor& query, const Tensor& key, const Tensor& value,
     return sdpa_forward(query, key, value, attn_mask, dropout_p, is_causal, scale, enable_gqa);
 }
 
+
+// ---- training: forward that also returns the row statistics, and the backward built on them ----
+// paras::sdpa_train_forward(q, k, v, is_causal, scale) -> (out, lse);  paras::sdpa_backward(...)
+// New operators (the reference differentiates through its composite); 4-D [B,H,L,E] 16-bit
+// tensors, GQA by head count, no mask tensor.  Wrapped for autograd in torch_paras.nn.
+std::tuple<Tensor, Tensor> sdpa_train_forward(const Tensor& query, const Tensor& key, const Tensor& value,
+                                              bool is_causal, std::optional<double> scale) {
+    PARAS_TRACE_OP("paras::sdpa_train_forward");
+    TORCH_CHECK(query.dim() == 4 && key.dim() == 4 && value.dim() == 4,
+                "paras sdpa_train_forward: [batch, heads, seq, head_dim] tensors");
+    TORCH_CHECK(query.scalar_type() == c10::kBFloat16 || query.scalar_type() == c10::kHalf,
+                "paras sdpa_train_forward: bfloat16 or float16 tensors");
+    TORCH_CHECK(key.scalar_type() == query.scalar_type() && value.scalar_type() == query.scalar_type(),
+                "paras sdpa_train_forward: query, key and value must have the same dtype");
+    TORCH_CHECK(key.sizes() == value.sizes() && key.size(0) == query.size(0) && key.size(3) == query.size(3) &&
+                    key.size(1) > 0 && query.size(1) % key.size(1) == 0,
+                "paras sdpa_train_forward: shapes do not fit (query heads must be a multiple of key/value heads)");
+    Runtime& rt = Runtime::get();
+    c10::DeviceGuard guard(query.device());
+    Tensor q = query.contiguous(), k = key.contiguous(), v = value.contiguous();
+    const int64_t B = q.size(0), Hq = q.size(1), Lq = q.size(2), E = q.size(3);
+    Tensor out = at::empty_like(q);
+    Tensor lse = at::empty({B, Hq, Lq}, q.options().dtype(c10::kFloat));
+    paras_sdpa_args a{};
+    a.q = q.data_ptr(); a.k = k.data_ptr(); a.v = v.data_ptr(); a.out = out.data_ptr();
+    a.lse = lse.numel() ? lse.data_ptr<float>() : nullptr;
+    a.dtype = dtype_code(q.scalar_type());
+    a.B = int32_t(B); a.Hq = int32_t(Hq); a.Hkv = int32_t(k.size(1));
+    a.Lq = int32_t(Lq); a.Lk = int32_t(k.size(2)); a.D = int32_t(E);
+    for (int i = 0; i < 3; ++i) {
+        a.q_strides[i] = q.stride(i); a.k_strides[i] = k.stride(i);
+        a.v_strides[i] = v.stride(i); a.o_strides[i] = out.stride(i);
+    }
+    a.causal = is_causal ? 1 : 0;
+    a.scale = scale.has_value() ? *scale : 1.0 / std::sqrt(double(E));
+    a.flags = ref_scale_rounding() ? PARAS_SDPA_REF_SCALE : 0;
+    a.gpu = rt.gpu_of(query);
+    PARAS_ABI(paras_b200_sdpa_fwd(&a));
+    return {out, lse};
+}
+
+std::tuple<Tensor, Tensor, Tensor> sdpa_backward(const Tensor& grad_out, const Tensor& query, const Tensor& key,
+                                                 const Tensor& value, const Tensor& out, const Tensor& lse,
+                                                 bool is_causal, std::optional<double> scale) {
+    PARAS_TRACE_OP("paras::sdpa_backward");
+    TORCH_CHECK(query.dim() == 4 && key.dim() == 4 && value.dim() == 4 && grad_out.sizes() == query.sizes() &&
+                    out.sizes() == query.sizes() && key.sizes() == value.sizes(),
+                "paras sdpa_backward: shape mismatch");
+    TORCH_CHECK(lse.scalar_type() == c10::kFloat && lse.numel() == query.numel() / std::max<int64_t>(query.size(3), 1),
+                "paras sdpa_backward: lse must be the float32 [batch, heads, seq] tensor of the forward pass");
+    Runtime& rt = Runtime::get();
+    c10::DeviceGuard guard(query.device());
+    Tensor q = query.contiguous(), k = key.contiguous(), v = value.contiguous();
+    Tensor o = out.contiguous(), go = grad_out.contiguous(), l = lse.contiguous();
+    Tensor dq = at::empty_like(q), dk = at::empty_like(k), dv = at::empty_like(v);
+    paras_sdpa_bwd_args a{};
+    a.q = q.data_ptr(); a.k = k.data_ptr(); a.v = v.data_ptr(); a.out = o.data_ptr(); a.dout = go.data_ptr();
+    a.lse = l.numel() ? l.data_ptr<float>() : nullptr;
+    a.dq = dq.data_ptr(); a.dk = dk.data_ptr(); a.dv = dv.data_ptr();
+    a.B = int32_t(q.size(0)); a.Hq = int32_t(q.size(1)); a.Hkv = int32_t(k.size(1));
+    a.Lq = int32_t(q.size(2)); a.Lk = int32_t(k.size(2)); a.D = int32_t(q.size(3));
+    a.dtype = dtype_code(q.scalar_type());
+    a.causal = is_causal ? 1 : 0;
+    double sc = scale.has_value() ? *scale : 1.0 / std::sqrt(double(q.size(3)));
+    if (ref_scale_rounding())  // the forward pass rounded the scale to the tensor dtype
+        sc = at::scalar_tensor(sc, at::TensorOptions().dtype(q.scalar_type())).item<double>();
+    a.scale = sc;
+    a.gpu = rt.gpu_of(query);
+    PARAS_ABI(paras_b200_sdpa_bwd(&a));
+    return {dq, dk, dv};
+}
+
 }  // namespace
 }  // namespace paras
 
 TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
     m.impl("aten::_scaled_dot_product_attention_math", &paras::sdpa_math);
     m.impl("aten::scaled_dot_product_attention", &paras::sdpa);
+}
+
+TORCH_LIBRARY_FRAGMENT(paras, m) {
+    m.def("sdpa_train_forward(Tensor query, Tensor key, Tensor value, bool is_causal, float? scale) -> (Tensor, Tensor)");
+    m.def("sdpa_backward(Tensor grad_out, Tensor query, Tensor key, Tensor value, Tensor out, Tensor lse, "
+          "bool is_causal, float? scale) -> (Tensor, Tensor, Tensor)");
+}
+TORCH_LIBRARY_IMPL(paras, PrivateUse1, m) {
+    m.impl("sdpa_train_forward", &paras::sdpa_train_forward);
+    m.impl("sdpa_backward", &paras::sdpa_backward);
 }

@@ -34,7 +34,7 @@ EXPORTS = [
     "paras_b200_sdpa_workspace_bytes", "paras_b200_sdpa_last_kernel", "paras_b200_rmsnorm_fwd",
     "paras_b200_sdpa_fwd_static_scratch", "paras_b200_sdpa_static_scratch_bytes",
     "paras_b200_rmsnorm_bwd", "paras_b200_swiglu_fwd", "paras_b200_swiglu_bwd",
-    "paras_b200_rotate_half", "paras_b200_gemm", "paras_b200_sdpa_fwd_host",
+    "paras_b200_rotate_half", "paras_b200_gemm", "paras_b200_sdpa_fwd_host", "paras_b200_sdpa_bwd",
 ]
 
 
@@ -61,7 +61,18 @@ class GemmArgs(C.Structure):
         ("batch", C.c_int64),
         ("stride_a", C.c_int64), ("stride_b", C.c_int64), ("stride_c", C.c_int64),
         ("dtype", C.c_int32), ("b_layout", C.c_int32), ("epilogue", C.c_int32), ("gpu", C.c_int32),
-        ("stream", C.c_void_p),
+        ("stream", C.c_void_p), ("a_layout", C.c_int32), ("reserved", C.c_int32),
+    ]
+
+
+class SdpaBwdArgs(C.Structure):
+    _fields_ = [
+        ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("out", C.c_void_p),
+        ("dout", C.c_void_p), ("lse", C.c_void_p), ("dq", C.c_void_p), ("dk", C.c_void_p),
+        ("dv", C.c_void_p),
+        ("B", C.c_int32), ("Hq", C.c_int32), ("Hkv", C.c_int32), ("Lq", C.c_int32),
+        ("Lk", C.c_int32), ("D", C.c_int32), ("dtype", C.c_int32), ("causal", C.c_int32),
+        ("scale", C.c_double), ("gpu", C.c_int32), ("reserved", C.c_int32), ("stream", C.c_void_p),
     ]
 
 
@@ -85,6 +96,7 @@ def lib() -> C.CDLL:
         L.paras_b200_sdpa_fwd_static_scratch.argtypes = [C.POINTER(SdpaArgs)]
         L.paras_b200_gemm.argtypes = [C.POINTER(GemmArgs)]
         L.paras_b200_sdpa_fwd_host.argtypes = [C.POINTER(SdpaArgs)]
+        L.paras_b200_sdpa_bwd.argtypes = [C.POINTER(SdpaBwdArgs)]
         L.paras_b200_rmsnorm_fwd.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                              C.c_int64, C.c_int64, C.c_double, C.c_int, C.c_int, C.c_void_p]
         L.paras_b200_rmsnorm_bwd.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
@@ -215,6 +227,28 @@ def sdpa_fwd_host(q, k, v, *, causal=False, scale=None, flags=0, out=None, gpu=0
     return out
 
 
+def sdpa_bwd(dout, q, k, v, out, lse, *, causal=False, scale=None, stream=None):
+    """(dq, dk, dv) through ``paras_b200_sdpa_bwd``; contiguous [B,H,L,D] tensors, ``lse`` from
+    ``sdpa_fwd(..., return_lse=True)`` with the same causal flag and scale."""
+    for t in (dout, q, k, v, out):
+        if not t.is_contiguous():
+            raise RuntimeError("paras abi: sdpa_bwd takes contiguous tensors")
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    a = SdpaBwdArgs()
+    a.q, a.k, a.v, a.out, a.dout = q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), dout.data_ptr()
+    a.lse = lse.data_ptr()
+    a.dq, a.dk, a.dv = dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
+    a.B, a.Hq, a.Lq, a.D = q.shape
+    a.Hkv, a.Lk = k.shape[1], k.shape[2]
+    a.dtype = dtype_code(q)
+    a.causal = 1 if causal else 0
+    a.scale = float(scale) if scale is not None else 1.0 / (q.shape[-1] ** 0.5)
+    a.gpu = _gpu_of(q)
+    a.stream = _stream_of(q, stream)
+    check(lib().paras_b200_sdpa_bwd(C.byref(a)))
+    return dq, dk, dv
+
+
 def sdpa_fwd_static_scratch(q, k, v, *, causal=False, scale=None, mask=None, flags=0, out=None,
                             stream=None):
     """Attention through ``paras_b200_sdpa_fwd_static_scratch``: for callers that must not
@@ -228,7 +262,7 @@ def sdpa_fwd_static_scratch(q, k, v, *, causal=False, scale=None, mask=None, fla
     return out
 
 
-def gemm(a, b, *, b_layout=GEMM_B_NK, bias=None, up_weight=None, out=None, stream=None):
+def gemm(a, b, *, b_layout=GEMM_B_NK, a_transposed=False, bias=None, up_weight=None, out=None, stream=None):
     """``paras_b200_gemm`` on 2-D ([M,K]) or 3-D ([batch,M,K]) operands with contiguous rows.
 
     ``b_layout=GEMM_B_NK``: b is [N,K] (a Linear weight), result a @ b^T;
@@ -240,7 +274,10 @@ def gemm(a, b, *, b_layout=GEMM_B_NK, bias=None, up_weight=None, out=None, strea
     b3 = b if b.dim() == 3 else b.unsqueeze(0)
     if a3.stride(-1) != 1 or b3.stride(-1) != 1:
         raise RuntimeError("paras abi: gemm operands need contiguous rows")
-    Bt, M, K = a3.shape
+    if a_transposed:  # a is [.., K, M]: the product is a^T @ b
+        Bt, K, M = a3.shape
+    else:
+        Bt, M, K = a3.shape
     N = b3.shape[1] if b_layout == GEMM_B_NK else b3.shape[2]
     if out is None:
         out = torch.empty((Bt, M, N) if batched else (M, N), dtype=a.dtype, device=a.device)
@@ -256,6 +293,7 @@ def gemm(a, b, *, b_layout=GEMM_B_NK, bias=None, up_weight=None, out=None, strea
     g.stride_b = b3.stride(0) if b3.shape[0] > 1 else 0
     g.dtype = dtype_code(a)
     g.b_layout = b_layout
+    g.a_layout = 1 if a_transposed else 0
     g.epilogue = GEMM_EPI_SWIGLU if up_weight is not None else (GEMM_EPI_BIAS if bias is not None else GEMM_EPI_NONE)
     g.gpu = _gpu_of(a)
     g.stream = _stream_of(a, stream)

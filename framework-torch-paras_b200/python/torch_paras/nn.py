@@ -8,7 +8,8 @@ import torch
 
 from . import _C  # noqa: F401  (loads the operator registrations)
 
-__all__ = ["rms_norm", "swiglu", "rotate_half", "swiglu_linear", "attention_host"]
+__all__ = ["rms_norm", "swiglu", "rotate_half", "swiglu_linear", "attention_host",
+           "scaled_dot_product_attention"]
 
 
 class _RMSNorm(torch.autograd.Function):
@@ -35,6 +36,22 @@ class _SwiGLU(torch.autograd.Function):
     def backward(ctx, grad):
         gate, up = ctx.saved_tensors
         return torch.ops.paras.swiglu_backward(grad.contiguous(), gate, up)
+
+
+class _SDPA(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, is_causal, scale):
+        out, lse = torch.ops.paras.sdpa_train_forward(q, k, v, is_causal, scale)
+        ctx.save_for_backward(q, k, v, out, lse)
+        ctx.is_causal, ctx.scale = is_causal, scale
+        return out
+
+    @staticmethod
+    def backward(ctx, grad):
+        q, k, v, out, lse = ctx.saved_tensors
+        dq, dk, dv = torch.ops.paras.sdpa_backward(grad.contiguous(), q, k, v, out, lse,
+                                                   ctx.is_causal, ctx.scale)
+        return dq, dk, dv, None, None
 
 
 class _RotateHalf(torch.autograd.Function):
@@ -79,6 +96,16 @@ def attention_host(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, 
     return abi.sdpa_fwd_host(query.contiguous(), key.contiguous(), value.contiguous(),
                              causal=is_causal, scale=scale, flags=abi.SDPA_REF_SCALE, out=out,
                              gpu=device - 1)
+
+
+def scaled_dot_product_attention(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, *,
+                                 is_causal: bool = False, scale=None) -> torch.Tensor:
+    """Differentiable attention on ``paras`` tensors ([batch, heads, seq, head_dim], bfloat16 or
+    float16, fewer key/value heads than query heads = GQA).  Forward is the fused kernel (it also
+    keeps each row's log-sum-exp); backward rebuilds the probabilities from it and runs as five
+    batched GEMMs and two element-wise passes.  ``F.scaled_dot_product_attention`` on the device is
+    the inference entry point (forward only, masks, any rank)."""
+    return _SDPA.apply(query, key, value, is_causal, scale)
 
 
 def rotate_half(x: torch.Tensor) -> torch.Tensor:

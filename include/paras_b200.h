@@ -218,12 +218,41 @@ int paras_b200_swiglu_bwd(int gpu, const void* grad_out, const void* gate, const
 int paras_b200_rotate_half(int gpu, const void* x, void* out, int64_t rows, int64_t D, int dtype,
                            int backward, void* stream);
 
+/* ---- attention backward ----
+ * The gradient the reference obtains by autograd through sdpa_math (csrc/ops/attention_ops.cpp:
+ * 71-136) and its softmax backward (csrc/ops/pointwise_ops.cpp:994-1062).  q, out, dout, dq:
+ * dense [B,Hq,Lq,D]; k, v, dk, dv: dense [B,Hkv,Lk,D]; lse: f32 [B,Hq,Lq] as returned by
+ * paras_b200_sdpa_fwd (args->lse) for the same inputs, causal flag and scale.  dtype BF16 or F16;
+ * D and Lk multiples of 8, all pointers 16-byte aligned (else PARAS_E_UNSUPPORTED).  Scratch
+ * (two [rows, Lk] matrices for a chunk of kv-head groups, about 1 GB each at most) comes from
+ * the GPU's pool, stream-ordered.  No mask tensor, no dropout. */
+typedef struct paras_sdpa_bwd_args {
+    const void* q;
+    const void* k;
+    const void* v;
+    const void* out;
+    const void* dout;
+    const float* lse;
+    void* dq;
+    void* dk;
+    void* dv;
+    int32_t B, Hq, Hkv, Lq, Lk, D;
+    int32_t dtype;
+    int32_t causal;
+    double scale;
+    int32_t gpu;
+    int32_t reserved;
+    void* stream;
+} paras_sdpa_bwd_args;
+int paras_b200_sdpa_bwd(const paras_sdpa_bwd_args* args);
+
 /* ---- 16-bit GEMM (the projections either side of the path) ----
  * Replaces the host round trip of mm / bmm / addmm / linear (csrc/ops/vision_ops.cpp:248-309,
  * 388-423: both operands copied to the host, at::mm / at::bmm / at::addmm / at::linear in
  * libtorch's CPU library, result copied back).  fp32 accumulation, one rounding of the result.
  *   C[i][M,N] = A[i][M,K] * B[i]  for i < batch
- *   A: rows of K contiguous elements, row stride lda.
+ *   a_layout PARAS_GEMM_A_MK (0, default): A is [M,K], rows of K elements, row stride lda
+ *            PARAS_GEMM_A_KM: A is [K,M], rows of M elements (C = A^T B; no epilogue)
  *   b_layout PARAS_GEMM_B_NK: B is [N,K], rows of K elements (a Linear weight; C = A B^T)
  *            PARAS_GEMM_B_KN: B is [K,N], rows of N elements (mm / bmm; C = A B)
  *   epilogue PARAS_GEMM_EPI_NONE
@@ -235,6 +264,7 @@ int paras_b200_rotate_half(int gpu, const void* x, void* out, int64_t rows, int6
  * bytes), all base pointers 16-byte aligned; otherwise PARAS_E_UNSUPPORTED (the caller keeps
  * its own path for such operands).  dtype: PARAS_BF16 or PARAS_F16. */
 enum { PARAS_GEMM_B_NK = 0, PARAS_GEMM_B_KN = 1 };
+enum { PARAS_GEMM_A_MK = 0, PARAS_GEMM_A_KM = 1 };
 enum { PARAS_GEMM_EPI_NONE = 0, PARAS_GEMM_EPI_BIAS = 1, PARAS_GEMM_EPI_SWIGLU = 2 };
 typedef struct paras_gemm_args {
     const void* a;
@@ -251,6 +281,8 @@ typedef struct paras_gemm_args {
     int32_t epilogue;
     int32_t gpu;
     void* stream;
+    int32_t a_layout;
+    int32_t reserved;
 } paras_gemm_args;
 int paras_b200_gemm(const paras_gemm_args* args);
 

@@ -77,6 +77,17 @@ def test_batched_and_strided_operands():
     assert float(out[:, :8].abs().sum()) == 0.0 and float(out[:, 272:].abs().sum()) == 0.0
 
 
+@pytest.mark.parametrize("shape", [(128, 256, 64), (304, 520, 136), (1000, 264, 392)])
+def test_transposed_a_operand(shape):
+    # A given as [K, M] (rows of M): C = A^T B, with B in either layout
+    M, N, K = shape
+    dtype = torch.bfloat16
+    at, w, b = rand((K, M), 1, dtype), rand((N, K), 2, dtype), rand((K, N), 3, dtype)
+    close16(abi.gemm(at.to(CUDA), w.to(CUDA), a_transposed=True), O.mm(at.t(), w.t()), f"A^T W^T {shape}")
+    close16(abi.gemm(at.to(CUDA), b.to(CUDA), a_transposed=True, b_layout=abi.GEMM_B_KN),
+            O.mm(at.t(), b), f"A^T B {shape}")
+
+
 def test_operands_the_kernel_does_not_take_are_refused():
     a = torch.randn(64, 64, device=CUDA)
     with pytest.raises(RuntimeError):
