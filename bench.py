@@ -388,7 +388,7 @@ def run_ours(args):
         t = loop_ms(lambda: abi.sdpa_bwd(dob, qb_, kb_, vb_, ob, lseb, causal=True), s3, 3)
         fl = 2.5 * sdpa_flops(Bb, c["Hq"], c["S"], c["S"], c["D"], True)
         extra[f"sdpa_backward_B{Bb}_H{c['Hq']}_S{c['S']}"] = {"ms": t, "tflops": fl / (t * 1e-3) / 1e12,
-                                                            "note": "five batched GEMMs + two element-wise passes over materialised [L,L] matrices"}
+                                                            "note": "five batched GEMMs over two materialised [L,L] matrices, element-wise steps in their epilogues"}
         del qb_, kb_, vb_, dob, ob, lseb
     if want("gemm"):
         # The projections either side of the path at config 2 / 5 sizes (hidden 4096, FFN 14336):

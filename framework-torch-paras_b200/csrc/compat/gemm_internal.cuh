@@ -1,0 +1,23 @@
+// Internal entry to the tcgen05 GEMM for callers inside the library that need an epilogue the
+// public paras_b200_gemm does not offer (attention backward).
+#pragma once
+
+#include "common.cuh"
+
+namespace pb {
+
+struct GemmExtra {
+    int epilogue;           // 3: C = exp(acc*scale - row_stat[row]), causally masked (col <= row % Lq)
+                            // 4: C = prob[row, col] * (acc - row_stat[row]) * scale
+    const float* row_stat;  // [batch * M]
+    const void* prob;       // [batch * M, prob_ld] in the GEMM's dtype (epilogue 4)
+    int64_t prob_ld;
+    int Lq;
+    int causal;
+    float scale;
+};
+
+// paras_b200_gemm with `ex` (may be null); A must be [M, K] rows when `ex` is given.
+int gemm_run(const paras_gemm_args* a, const GemmExtra* ex);
+
+}  // namespace pb

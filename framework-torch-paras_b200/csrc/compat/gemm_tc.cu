@@ -23,6 +23,7 @@
 #include "common.cuh"
 #include "tc_prims.cuh"
 #include "tma_host.cuh"
+#include "gemm_internal.cuh"
 
 namespace pb {
 namespace {
@@ -48,7 +49,7 @@ constexpr int kNumBars = 2 * kStages + 4;
 constexpr int kSmemMisc = kSmemBars + kNumBars * 8;             // tmem base word, abort flag
 constexpr int kSmemTotal = kSmemMisc + 16;
 
-enum { kEpiNone = 0, kEpiBias = 1, kEpiSwiglu = 2 };
+enum { kEpiNone = 0, kEpiBias = 1, kEpiSwiglu = 2, kEpiProb = 3, kEpiDs = 4 };  // 3, 4: attention backward only
 
 __device__ int g_gemm_abort_latch = 0;
 
@@ -59,6 +60,12 @@ struct GemmParams {
     int k_iters;
     const void* bias;
     int* status;
+    // attention backward epilogues (gemm_internal.cuh): per-row statistic, the probabilities, masking
+    const float* row_stat;
+    const void* prob;
+    int64_t prob_ld;
+    int Lq, causal;
+    float scale, scale_log2;
 };
 
 struct Tile { int b, m0, n0; };
@@ -245,6 +252,36 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     tmem_wait_ld();
                     tmem_ld_fence32(reinterpret_cast<uint32_t(&)[32]>(o[0]));
                     tmem_ld_fence32(reinterpret_cast<uint32_t(&)[32]>(o[32]));
+                    if (EPI == kEpiProb || EPI == kEpiDs) {
+                        // C = exp(acc*scale - stat[row]) with causal masking, or C = P o (acc - stat[row]) * scale:
+                        // a thread owns a row, so the row's statistic is one value per thread
+                        const int row = min(row_w + lane, p.M - 1);
+                        const int64_t grow = int64_t(t.b) * p.M + row;
+                        const float stat = p.row_stat[grow];
+                        const int col0 = t.n0 + 64 * c;
+                        if (EPI == kEpiProb) {
+                            const float neg = -stat * 1.4426950408889634f;
+                            const int qpos = row % p.Lq;
+#pragma unroll
+                            for (int i = 0; i < 64; ++i) {
+                                const bool keep = !p.causal || col0 + i <= qpos;
+                                o[i] = __float_as_uint(keep ? exp2f(fmaf(__uint_as_float(o[i]), p.scale_log2, neg)) : 0.f);
+                            }
+                        } else {
+                            const uint16_t* pr = static_cast<const uint16_t*>(p.prob) + grow * p.prob_ld + col0;
+#pragma unroll
+                            for (int v = 0; v < 8; ++v) {
+                                uint4 w = make_uint4(0, 0, 0, 0);
+                                if (col0 + 8 * v < p.N) w = __ldg(reinterpret_cast<const uint4*>(pr) + v);
+                                const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+                                for (int e = 0; e < 8; ++e) {
+                                    const float pv = from16<BF16>(uint16_t((ww[e >> 1] >> (16 * (e & 1))) & 0xffffu));
+                                    o[8 * v + e] = __float_as_uint(pv * (__uint_as_float(o[8 * v + e]) - stat) * p.scale);
+                                }
+                            }
+                        }
+                    }
 #pragma unroll
                     for (int i = 0; i < 64; i += 2) {
                         float x0 = __uint_as_float(o[i]), x1 = __uint_as_float(o[i + 1]);
@@ -315,15 +352,19 @@ int launch(Gpu* g, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorM
 }  // namespace
 }  // namespace pb
 
-extern "C" int paras_b200_gemm(const paras_gemm_args* a) {
-    using namespace pb;
+namespace pb {
+int gemm_run(const paras_gemm_args* a, const GemmExtra* ex) {
     if (!a) return fail(PARAS_E_INVALID, "paras gemm: null args");
     if (a->dtype != PARAS_BF16 && a->dtype != PARAS_F16)
         return fail(PARAS_E_UNSUPPORTED, "paras gemm: only 16-bit tensors run on the tensor-core kernel");
     if (a->M < 0 || a->N < 0 || a->K < 0 || a->batch < 0)
         return fail(PARAS_E_INVALID, "paras gemm: negative size");
+    const int epi = ex ? ex->epilogue : a->epilogue;
     if (a->epilogue < kEpiNone || a->epilogue > kEpiSwiglu)
         return fail(PARAS_E_INVALID, "paras gemm: bad epilogue %d", a->epilogue);
+    if (ex && (a->a_layout != PARAS_GEMM_A_MK || (epi != kEpiProb && epi != kEpiDs) || !ex->row_stat ||
+               (epi == kEpiDs && !ex->prob)))
+        return fail(PARAS_E_INVALID, "paras gemm: bad internal epilogue request");
     if (a->b_layout != PARAS_GEMM_B_NK && a->b_layout != PARAS_GEMM_B_KN)
         return fail(PARAS_E_INVALID, "paras gemm: bad b_layout %d", a->b_layout);
     if (a->a_layout != PARAS_GEMM_A_MK && a->a_layout != PARAS_GEMM_A_KM)
@@ -382,12 +423,22 @@ extern "C" int paras_b200_gemm(const paras_gemm_args* a) {
     p.k_iters = int((a->K + BK - 1) / BK);
     p.bias = a->bias;
     p.status = g->status_dev;
+    if (ex) {
+        p.row_stat = ex->row_stat; p.prob = ex->prob; p.prob_ld = ex->prob_ld;
+        p.Lq = ex->Lq > 0 ? ex->Lq : 1; p.causal = ex->causal; p.scale = ex->scale;
+        p.scale_log2 = ex->scale * 1.4426950408889634f;
+    }
     cudaStream_t s = pick_stream(g, a->stream);
     const bool bf = a->dtype == PARAS_BF16;
 #define PB_GEMM(AT, KN, EPI) (bf ? launch<true, AT, KN, EPI>(g, ma, mb, mb2, mc, p, s) : launch<false, AT, KN, EPI>(g, ma, mb, mb2, mc, p, s))
+    if (epi == kEpiProb) return kn ? PB_GEMM(false, true, kEpiProb) : PB_GEMM(false, false, kEpiProb);
+    if (epi == kEpiDs) return kn ? PB_GEMM(false, true, kEpiDs) : PB_GEMM(false, false, kEpiDs);
     if (a->epilogue == kEpiSwiglu) return PB_GEMM(false, false, kEpiSwiglu);
     if (a->epilogue == kEpiBias) return kn ? PB_GEMM(false, true, kEpiBias) : PB_GEMM(false, false, kEpiBias);
     if (at) return kn ? PB_GEMM(true, true, kEpiNone) : PB_GEMM(true, false, kEpiNone);
     return kn ? PB_GEMM(false, true, kEpiNone) : PB_GEMM(false, false, kEpiNone);
 #undef PB_GEMM
 }
+}  // namespace pb
+
+extern "C" int paras_b200_gemm(const paras_gemm_args* a) { return pb::gemm_run(a, nullptr); }

@@ -2,22 +2,23 @@
 // sdpa_math, csrc/ops/attention_ops.cpp:71-136: mm / mul / masked_fill / softmax / mm, each with
 // 16-bit intermediates).  Not a fused kernel: the row statistics the forward pass returns (lse)
 // make the probabilities a pure element-wise function of the scores, so the gradient is five
-// batched GEMMs on the tcgen05 GEMM of gemm_tc.cu and two element-wise passes, per kv-head group:
+// batched GEMMs on the tcgen05 GEMM of gemm_tc.cu, per kv-head group, with the element-wise
+// steps in the epilogues of two of them:
 //
-//   S  = Q K^T                      [R, Lk]   R = (Hq/Hkv) * Lq rows: the group's query heads stacked
-//   P  = exp(S*scale - lse[row])    in place, causal entries zeroed
-//   dV = P^T dO                     [Lk, D]   (sums over the group's heads by construction)
-//   dP = dO V^T                     [R, Lk]
-//   dS = P o (dP - delta[row]) * scale        delta = rowsum(dO o O), in place
-//   dK = dS^T Q                     [Lk, D]
-//   dQ = dS K                       [R, D]
+//   P  = exp(Q K^T * scale - lse[row])        [R, Lk]   R = (Hq/Hkv) * Lq rows: the group's query heads
+//                                                       stacked; causal entries zeroed (GEMM epilogue)
+//   dV = P^T dO                               [Lk, D]   (sums over the group's heads by construction)
+//   dS = P o (dO V^T - delta[row]) * scale    [R, Lk]   delta = rowsum(dO o O) (GEMM epilogue)
+//   dK = dS^T Q                               [Lk, D]
+//   dQ = dS K                                 [R, D]
 //
-// S and dP are materialised for a chunk of groups at a time (about 1 GB each), so the work is
+// P and dS are materialised for a chunk of groups at a time (about 1 GB each), so the work is
 // bound by HBM traffic on those two matrices, not by the tensor pipe.
 #include <algorithm>
 #include <cmath>
 
 #include "common.cuh"
+#include "gemm_internal.cuh"
 
 namespace pb {
 namespace {
@@ -40,39 +41,6 @@ __global__ void sdpa_bwd_delta_kernel(const T* __restrict__ dout, const T* __res
         }
         acc = warp_sum(acc);
         if (lane == 0) delta[row] = acc;
-    }
-}
-
-// mat: [groups][R][Lk] 16-bit, 16-byte vectors along Lk.  MODE 0: S -> P;  MODE 1: dP -> dS (needs P).
-template <typename T, int MODE>
-__global__ void sdpa_bwd_rowwise_kernel(T* __restrict__ mat, const T* __restrict__ prob,
-                                        const float* __restrict__ row_stat, int64_t groups, int R, int Lq,
-                                        int Lk, int causal, float scale, float scale_log2) {
-    constexpr int N = Vec16<T>::N;
-    const int vec_per_row = Lk / N;
-    const int64_t total = groups * int64_t(R) * vec_per_row;
-    for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
-         i += int64_t(gridDim.x) * blockDim.x) {
-        const int64_t row = i / vec_per_row;          // global row: group * R + r
-        const int col0 = int(i - row * vec_per_row) * N;
-        const int qpos = int(row % R) % Lq;           // query position inside its head
-        const float stat = row_stat[row];
-        Vec16<T> x = ld16(mat + row * Lk + col0);
-        Vec16<T> y;
-        if (MODE == 1) {
-            const Vec16<T> pr = ld16(prob + row * Lk + col0);
-#pragma unroll
-            for (int e = 0; e < N; ++e)
-                y.v[e] = from_f32<T>(to_f32<T>(pr.v[e]) * (to_f32<T>(x.v[e]) - stat) * scale);
-        } else {
-            const float neg = -stat * 1.4426950408889634f;
-#pragma unroll
-            for (int e = 0; e < N; ++e) {
-                const bool keep = !causal || col0 + e <= qpos;
-                y.v[e] = from_f32<T>(keep ? exp2f(fmaf(to_f32<T>(x.v[e]), scale_log2, neg)) : 0.f);
-            }
-        }
-        st16(mat + row * Lk + col0, y);
     }
 }
 
@@ -136,7 +104,6 @@ extern "C" int paras_b200_sdpa_bwd(const paras_sdpa_bwd_args* a) {
 
     const int sms = g->sm_count > 0 ? g->sm_count : 148;
     const float scale = float(a->scale);
-    const float scale_log2 = scale * 1.4426950408889634f;
     auto run = [&]() -> int {
         if (a->dtype == PARAS_BF16)
             sdpa_bwd_delta_kernel<__nv_bfloat16><<<sms * 8, 256, 0, s>>>(
@@ -156,7 +123,7 @@ extern "C" int paras_b200_sdpa_bwd(const paras_sdpa_bwd_args* a) {
             char* dv = static_cast<char*>(a->dv) + size_t(g0) * a->Lk * a->D * es;
             auto gemm = [&](const void* A, int a_layout, int64_t lda, int64_t sa, const void* Bm, int b_layout,
                             int64_t ldb, int64_t sb, void* C, int64_t ldc, int64_t sc, int64_t M, int64_t N,
-                            int64_t K) -> int {
+                            int64_t K, const GemmExtra* ex = nullptr) -> int {
                 paras_gemm_args ga{};
                 ga.a = A; ga.b = Bm; ga.c = C;
                 ga.M = M; ga.N = N; ga.K = K;
@@ -164,33 +131,19 @@ extern "C" int paras_b200_sdpa_bwd(const paras_sdpa_bwd_args* a) {
                 ga.batch = n; ga.stride_a = sa; ga.stride_b = sb; ga.stride_c = sc;
                 ga.dtype = a->dtype; ga.a_layout = a_layout; ga.b_layout = b_layout;
                 ga.epilogue = PARAS_GEMM_EPI_NONE; ga.gpu = a->gpu; ga.stream = s;
-                return paras_b200_gemm(&ga);
+                return gemm_run(&ga, ex);
             };
             const int64_t qs = R * a->D, ks = int64_t(a->Lk) * a->D, ms = R * a->Lk;
             int rc;
-            // S = Q K^T
-            if ((rc = gemm(q, PARAS_GEMM_A_MK, a->D, qs, k, PARAS_GEMM_B_NK, a->D, ks, smat, a->Lk, ms, R, a->Lk, a->D)) != PARAS_OK) return rc;
-            const int blocks = sms * 16;
-#define PB_ROWWISE(MODE, MAT, PROB, STAT)                                                                 \
-    if (a->dtype == PARAS_BF16)                                                                            \
-        sdpa_bwd_rowwise_kernel<__nv_bfloat16, MODE><<<blocks, 256, 0, s>>>(                               \
-            reinterpret_cast<__nv_bfloat16*>(MAT), reinterpret_cast<const __nv_bfloat16*>(PROB), STAT, n,  \
-            int(R), a->Lq, a->Lk, a->causal, scale, scale_log2);                                          \
-    else                                                                                                   \
-        sdpa_bwd_rowwise_kernel<__half, MODE><<<blocks, 256, 0, s>>>(                                      \
-            reinterpret_cast<__half*>(MAT), reinterpret_cast<const __half*>(PROB), STAT, n, int(R), a->Lq, \
-            a->Lk, a->causal, scale, scale_log2);
-            // P = exp(S*scale - lse)
-            PB_ROWWISE(0, smat, smat, a->lse + g0 * R)
-            PB_LAUNCH_CHECK("sdpa_bwd_rowwise_kernel");
+            // P = exp(Q K^T * scale - lse)
+            GemmExtra ex{};
+            ex.epilogue = 3; ex.row_stat = a->lse + g0 * R; ex.Lq = a->Lq; ex.causal = a->causal; ex.scale = scale;
+            if ((rc = gemm(q, PARAS_GEMM_A_MK, a->D, qs, k, PARAS_GEMM_B_NK, a->D, ks, smat, a->Lk, ms, R, a->Lk, a->D, &ex)) != PARAS_OK) return rc;
             // dV = P^T dO
             if ((rc = gemm(smat, PARAS_GEMM_A_KM, a->Lk, ms, dO, PARAS_GEMM_B_KN, a->D, qs, dv, a->D, ks, a->Lk, a->D, R)) != PARAS_OK) return rc;
-            // dP = dO V^T
-            if ((rc = gemm(dO, PARAS_GEMM_A_MK, a->D, qs, v, PARAS_GEMM_B_NK, a->D, ks, dpmat, a->Lk, ms, R, a->Lk, a->D)) != PARAS_OK) return rc;
-            // dS = P o (dP - delta) * scale
-            PB_ROWWISE(1, dpmat, smat, delta + g0 * R)
-            PB_LAUNCH_CHECK("sdpa_bwd_rowwise_kernel");
-#undef PB_ROWWISE
+            // dS = P o (dO V^T - delta) * scale
+            ex.epilogue = 4; ex.row_stat = delta + g0 * R; ex.prob = smat; ex.prob_ld = a->Lk;
+            if ((rc = gemm(dO, PARAS_GEMM_A_MK, a->D, qs, v, PARAS_GEMM_B_NK, a->D, ks, dpmat, a->Lk, ms, R, a->Lk, a->D, &ex)) != PARAS_OK) return rc;
             // dK = dS^T Q
             if ((rc = gemm(dpmat, PARAS_GEMM_A_KM, a->Lk, ms, q, PARAS_GEMM_B_KN, a->D, qs, dk, a->D, ks, a->Lk, a->D, R)) != PARAS_OK) return rc;
             // dQ = dS K
