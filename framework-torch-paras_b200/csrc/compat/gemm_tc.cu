@@ -262,11 +262,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         if (EPI == kEpiProb) {
                             const float neg = -stat * 1.4426950408889634f;
                             const int qpos = row % p.Lq;
+                            // whole 64-column pieces are usually either visible to all 32 rows or to none
+                            const int qmin = __reduce_min_sync(0xffffffffu, qpos);
+                            const int qmax = __reduce_max_sync(0xffffffffu, qpos);
+                            if (!p.causal || col0 + 63 <= qmin) {
 #pragma unroll
-                            for (int i = 0; i < 64; ++i) {
-                                const bool keep = !p.causal || col0 + i <= qpos;
-                                o[i] = __float_as_uint(keep ? exp2f(fmaf(__uint_as_float(o[i]), p.scale_log2, neg)) : 0.f);
+                                for (int i = 0; i < 64; ++i)
+                                    o[i] = __float_as_uint(ex2_approx(fmaf(__uint_as_float(o[i]), p.scale_log2, neg)));
+                            } else if (col0 > qmax) {
+#pragma unroll
+                                for (int i = 0; i < 64; ++i) o[i] = 0u;
+                            } else {
+#pragma unroll
+                                for (int i = 0; i < 64; ++i)
+                                    o[i] = col0 + i <= qpos
+                                               ? __float_as_uint(ex2_approx(fmaf(__uint_as_float(o[i]), p.scale_log2, neg)))
+                                               : 0u;
                             }
+                        } else if (p.causal && col0 > __reduce_max_sync(0xffffffffu, row % p.Lq)) {
+                            // every probability of this piece is zero
+#pragma unroll
+                            for (int i = 0; i < 64; ++i) o[i] = 0u;
                         } else {
                             const uint16_t* pr = static_cast<const uint16_t*>(p.prob) + grow * p.prob_ld + col0;
 #pragma unroll
