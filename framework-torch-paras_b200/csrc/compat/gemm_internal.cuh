@@ -7,7 +7,8 @@
 namespace pb {
 
 struct GemmExtra {
-    int epilogue;           // 3: C = exp(acc*scale - row_stat[row]), causally masked (col <= row % Lq)
+    int epilogue;           // 0: none (only k_skip is used)
+                            // 3: C = exp(acc*scale - row_stat[row]), causally masked (col <= row % Lq)
                             // 4: C = prob[row, col] * (acc - row_stat[row]) * scale
     const float* row_stat;  // [batch * M]
     const void* prob;       // [batch * M, prob_ld] in the GEMM's dtype (epilogue 4)
@@ -15,9 +16,11 @@ struct GemmExtra {
     int Lq;
     int causal;
     float scale;
+    int k_skip;             // with causal: skip K steps whose operand slice is entirely masked;
+                            // 1: A rows are queries, K runs over keys; 2: A rows are keys, K over stacked queries
 };
 
-// paras_b200_gemm with `ex` (may be null); A must be [M, K] rows when `ex` is given.
+// paras_b200_gemm with `ex` (may be null); A must be [M, K] rows for epilogues 3 and 4.
 int gemm_run(const paras_gemm_args* a, const GemmExtra* ex);
 
 }  // namespace pb

@@ -66,6 +66,7 @@ struct GemmParams {
     int64_t prob_ld;
     int Lq, causal;
     float scale, scale_log2;
+    int k_skip;   // 0 none; 1: rows = queries, K = keys (dQ); 2: rows = keys, K = stacked queries (dV, dK)
 };
 
 struct Tile { int b, m0, n0; };
@@ -83,6 +84,23 @@ __device__ __forceinline__ Tile get_tile(const GemmParams& p, int id, int n_per_
     t.m0 = (first_m + q % gm) * BM;
     t.n0 = (q / gm) * n_per_tile;
     return t;
+}
+
+// Causal attention backward: K steps whose slice of P / dS is entirely masked contribute nothing.
+// The same test runs in the loading and in the issuing thread; the last K step always runs, so
+// that a tile with nothing visible still gets a (zero) accumulator.
+__device__ __forceinline__ bool skip_k_step(const GemmParams& p, int m0, int kk) {
+    if (p.k_skip == 0 || kk + 1 == p.k_iters) return false;
+    if (p.k_skip == 1) {
+        // rows m0.. are queries (stacked heads): keys from kk*BK on are masked for all of them?
+        const int q0 = m0 % p.Lq;
+        const int qmax = q0 + BM - 1 >= p.Lq ? p.Lq - 1 : q0 + BM - 1;
+        return kk * BK > qmax;
+    }
+    // rows m0.. are keys; the K step covers stacked queries kk*BK .. kk*BK+BK-1
+    const int q0 = (kk * BK) % p.Lq;
+    const int qmax = q0 + BK - 1 >= p.Lq ? p.Lq - 1 : q0 + BK - 1;
+    return qmax < m0;
 }
 
 template <bool BF16, bool A_ROWS_OF_M, bool B_ROWS_OF_N, int EPI>
@@ -136,7 +154,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             int it = 0;  // K steps loaded so far, across tiles
             for (int id = blockIdx.x; ok && id < p.tiles; id += gridDim.x) {
                 const Tile t = get_tile(p, id, kNPerTile);
-                for (int kk = 0; kk < p.k_iters; ++kk, ++it) {
+                for (int kk = 0; kk < p.k_iters; ++kk) {
+                    if (skip_k_step(p, t.m0, kk)) continue;
                     const int st = it % kStages;
                     ok = mbar_wait(bar(kBarEmpty + st), ((it / kStages) & 1) ^ 1u, abort_flag, 0);
                     if (!ok) break;
@@ -163,6 +182,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     } else {
                         tma_load_3d(b_dst, &map_b, full, kk * BK, t.n0, t.b);
                     }
+                    ++it;
                 }
             }
         }
@@ -178,7 +198,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 ok = mbar_wait(bar(kBarAccEmpty + buf), ((local >> 1) & 1) ^ 1u, abort_flag, 1);
                 if (!ok) break;
                 const uint32_t d_tm = tmem + buf * BN;
-                for (int kk = 0; kk < p.k_iters; ++kk, ++it) {
+                const int m0 = p.k_skip ? get_tile(p, id, kNPerTile).m0 : 0;
+                bool first = true;  // the first K step that runs overwrites the accumulator
+                for (int kk = 0; kk < p.k_iters; ++kk) {
+                    if (skip_k_step(p, m0, kk)) continue;
                     const int st = it % kStages;
                     ok = mbar_wait(bar(kBarFull + st), (it / kStages) & 1, abort_flag, 2);
                     if (!ok) break;
@@ -193,9 +216,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         const uint64_t b_desc = B_ROWS_OF_N
                             ? smem_desc_sw128(b_addr + ks * 16 * 128, BK * 128, 1024)
                             : smem_desc_sw128(b_addr + ks * 32, 16, 1024);
-                        mma_ss(d_tm, a_desc, b_desc, idesc, (kk | ks) ? 1u : 0u);
+                        mma_ss(d_tm, a_desc, b_desc, idesc, (!first || ks) ? 1u : 0u);
                     }
+                    first = false;
                     tc_commit(bar(kBarEmpty + st));
+                    ++it;
                 }
                 if (!ok) break;
                 tc_commit(bar(kBarAccFull + buf));
@@ -378,8 +403,9 @@ int gemm_run(const paras_gemm_args* a, const GemmExtra* ex) {
     const int epi = ex ? ex->epilogue : a->epilogue;
     if (a->epilogue < kEpiNone || a->epilogue > kEpiSwiglu)
         return fail(PARAS_E_INVALID, "paras gemm: bad epilogue %d", a->epilogue);
-    if (ex && (a->a_layout != PARAS_GEMM_A_MK || (epi != kEpiProb && epi != kEpiDs) || !ex->row_stat ||
-               (epi == kEpiDs && !ex->prob)))
+    if (ex && ex->epilogue != kEpiNone &&
+        (a->a_layout != PARAS_GEMM_A_MK || (epi != kEpiProb && epi != kEpiDs) || !ex->row_stat ||
+         (epi == kEpiDs && !ex->prob)))
         return fail(PARAS_E_INVALID, "paras gemm: bad internal epilogue request");
     if (a->b_layout != PARAS_GEMM_B_NK && a->b_layout != PARAS_GEMM_B_KN)
         return fail(PARAS_E_INVALID, "paras gemm: bad b_layout %d", a->b_layout);
@@ -443,6 +469,7 @@ int gemm_run(const paras_gemm_args* a, const GemmExtra* ex) {
         p.row_stat = ex->row_stat; p.prob = ex->prob; p.prob_ld = ex->prob_ld;
         p.Lq = ex->Lq > 0 ? ex->Lq : 1; p.causal = ex->causal; p.scale = ex->scale;
         p.scale_log2 = ex->scale * 1.4426950408889634f;
+        p.k_skip = ex->causal ? ex->k_skip : 0;
     }
     cudaStream_t s = pick_stream(g, a->stream);
     const bool bf = a->dtype == PARAS_BF16;

@@ -139,15 +139,18 @@ extern "C" int paras_b200_sdpa_bwd(const paras_sdpa_bwd_args* a) {
             GemmExtra ex{};
             ex.epilogue = 3; ex.row_stat = a->lse + g0 * R; ex.Lq = a->Lq; ex.causal = a->causal; ex.scale = scale;
             if ((rc = gemm(q, PARAS_GEMM_A_MK, a->D, qs, k, PARAS_GEMM_B_NK, a->D, ks, smat, a->Lk, ms, R, a->Lk, a->D, &ex)) != PARAS_OK) return rc;
-            // dV = P^T dO
-            if ((rc = gemm(smat, PARAS_GEMM_A_KM, a->Lk, ms, dO, PARAS_GEMM_B_KN, a->D, qs, dv, a->D, ks, a->Lk, a->D, R)) != PARAS_OK) return rc;
+            // dV = P^T dO  (under a causal mask the query rows before a key tile hold only zeros: skipped)
+            GemmExtra skip{};
+            skip.epilogue = 0; skip.Lq = a->Lq; skip.causal = a->causal; skip.k_skip = 2;
+            if ((rc = gemm(smat, PARAS_GEMM_A_KM, a->Lk, ms, dO, PARAS_GEMM_B_KN, a->D, qs, dv, a->D, ks, a->Lk, a->D, R, &skip)) != PARAS_OK) return rc;
             // dS = P o (dO V^T - delta) * scale
             ex.epilogue = 4; ex.row_stat = delta + g0 * R; ex.prob = smat; ex.prob_ld = a->Lk;
             if ((rc = gemm(dO, PARAS_GEMM_A_MK, a->D, qs, v, PARAS_GEMM_B_NK, a->D, ks, dpmat, a->Lk, ms, R, a->Lk, a->D, &ex)) != PARAS_OK) return rc;
             // dK = dS^T Q
-            if ((rc = gemm(dpmat, PARAS_GEMM_A_KM, a->Lk, ms, q, PARAS_GEMM_B_KN, a->D, qs, dk, a->D, ks, a->Lk, a->D, R)) != PARAS_OK) return rc;
+            if ((rc = gemm(dpmat, PARAS_GEMM_A_KM, a->Lk, ms, q, PARAS_GEMM_B_KN, a->D, qs, dk, a->D, ks, a->Lk, a->D, R, &skip)) != PARAS_OK) return rc;
             // dQ = dS K
-            if ((rc = gemm(dpmat, PARAS_GEMM_A_MK, a->Lk, ms, k, PARAS_GEMM_B_KN, a->D, ks, dq, a->D, qs, R, a->D, a->Lk)) != PARAS_OK) return rc;
+            skip.k_skip = 1;  // keys past a query tile's last row
+            if ((rc = gemm(dpmat, PARAS_GEMM_A_MK, a->Lk, ms, k, PARAS_GEMM_B_KN, a->D, ks, dq, a->D, qs, R, a->D, a->Lk, &skip)) != PARAS_OK) return rc;
         }
         return PARAS_OK;
     };
