@@ -18,6 +18,9 @@ struct GemmExtra {
     float scale;
     int k_skip;             // with causal: skip K steps whose operand slice is entirely masked;
                             // 1: A rows are queries, K runs over keys; 2: A rows are keys, K over stacked queries
+    int tile_skip;          // with causal, epilogues 3 and 4: 128 x 256 output tiles all of whose keys follow
+                            // all of their queries are not computed and NOT WRITTEN; only for Lk <= Lq, and
+                            // only when every reader of C skips the same parts (k_skip does)
 };
 
 // paras_b200_gemm with `ex` (may be null); A must be [M, K] rows for epilogues 3 and 4.

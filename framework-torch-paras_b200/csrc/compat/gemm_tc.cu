@@ -67,6 +67,7 @@ struct GemmParams {
     int Lq, causal;
     float scale, scale_log2;
     int k_skip;   // 0 none; 1: rows = queries, K = keys (dQ); 2: rows = keys, K = stacked queries (dV, dK)
+    int tile_skip;  // rows = queries, columns = keys (P, dS): tiles with nothing visible are left alone
 };
 
 struct Tile { int b, m0, n0; };
@@ -86,17 +87,29 @@ __device__ __forceinline__ Tile get_tile(const GemmParams& p, int id, int n_per_
     return t;
 }
 
+// The last query position among rows m0 .. m0+BM-1 of the stacked query heads (Lq rows each).
+__device__ __forceinline__ int last_query_of_rows(const GemmParams& p, int m0) {
+    const int q0 = m0 % p.Lq;
+    return q0 + BM - 1 >= p.Lq ? p.Lq - 1 : q0 + BM - 1;
+}
+
+// Causal attention backward, P and dS: a tile all of whose keys come after all of its queries holds
+// only zeros.  It is neither computed nor written; the products that read P and dS skip exactly
+// those parts (skip_k_step), so what the memory holds there is never used.  All three roles apply
+// the same test.
+__device__ __forceinline__ bool skip_tile(const GemmParams& p, const Tile& t) {
+    return p.tile_skip && t.n0 > last_query_of_rows(p, t.m0);
+}
+
 // Causal attention backward: K steps whose slice of P / dS is entirely masked contribute nothing.
-// The same test runs in the loading and in the issuing thread; the last K step always runs, so
-// that a tile with nothing visible still gets a (zero) accumulator.
+// The same test runs in the loading and in the issuing thread.  With keys along K the first step
+// is visible to every query, so an accumulator is always written; with queries along K the last
+// step always runs, so that a key tile no query sees still gets a (zero) accumulator.
 __device__ __forceinline__ bool skip_k_step(const GemmParams& p, int m0, int kk) {
-    if (p.k_skip == 0 || kk + 1 == p.k_iters) return false;
-    if (p.k_skip == 1) {
-        // rows m0.. are queries (stacked heads): keys from kk*BK on are masked for all of them?
-        const int q0 = m0 % p.Lq;
-        const int qmax = q0 + BM - 1 >= p.Lq ? p.Lq - 1 : q0 + BM - 1;
-        return kk * BK > qmax;
-    }
+    if (p.k_skip == 0) return false;
+    if (p.k_skip == 1)  // rows m0.. are queries (stacked heads): keys from kk*BK on are masked for all of them?
+        return kk * BK > last_query_of_rows(p, m0);
+    if (kk + 1 == p.k_iters) return false;
     // rows m0.. are keys; the K step covers stacked queries kk*BK .. kk*BK+BK-1
     const int q0 = (kk * BK) % p.Lq;
     const int qmax = q0 + BK - 1 >= p.Lq ? p.Lq - 1 : q0 + BK - 1;
@@ -154,6 +167,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             int it = 0;  // K steps loaded so far, across tiles
             for (int id = blockIdx.x; ok && id < p.tiles; id += gridDim.x) {
                 const Tile t = get_tile(p, id, kNPerTile);
+                if (skip_tile(p, t)) continue;
                 for (int kk = 0; kk < p.k_iters; ++kk) {
                     if (skip_k_step(p, t.m0, kk)) continue;
                     const int st = it % kStages;
@@ -192,13 +206,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             constexpr uint32_t idesc = instr_desc_f16(BF16 ? 1 : 0, BM, BN, A_ROWS_OF_M, B_ROWS_OF_N);
             bool ok = true;
             int it = 0, local = 0;
-            for (int id = blockIdx.x; ok && id < p.tiles; id += gridDim.x, ++local) {
+            for (int id = blockIdx.x; ok && id < p.tiles; id += gridDim.x) {
+                Tile t{0, 0, 0};
+                if (p.k_skip || p.tile_skip) {
+                    t = get_tile(p, id, kNPerTile);
+                    if (skip_tile(p, t)) continue;
+                }
                 const int buf = local & 1;
                 // the epilogue has read this accumulator's previous tile
                 ok = mbar_wait(bar(kBarAccEmpty + buf), ((local >> 1) & 1) ^ 1u, abort_flag, 1);
                 if (!ok) break;
                 const uint32_t d_tm = tmem + buf * BN;
-                const int m0 = p.k_skip ? get_tile(p, id, kNPerTile).m0 : 0;
+                const int m0 = t.m0;
                 bool first = true;  // the first K step that runs overwrites the accumulator
                 for (int kk = 0; kk < p.k_iters; ++kk) {
                     if (skip_k_step(p, m0, kk)) continue;
@@ -224,6 +243,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 }
                 if (!ok) break;
                 tc_commit(bar(kBarAccFull + buf));
+                ++local;
             }
         }
         __syncwarp();
@@ -235,8 +255,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         bool ok = true;
         int local = 0;
         uint32_t nstore = 0;  // stores issued by this warp (picks the staging buffer)
-        for (int id = blockIdx.x; ok && id < p.tiles; id += gridDim.x, ++local) {
+        for (int id = blockIdx.x; ok && id < p.tiles; id += gridDim.x) {
             const Tile t = get_tile(p, id, kNPerTile);
+            if (skip_tile(p, t)) continue;
             const int buf = local & 1;
             ok = mbar_wait<32>(bar(kBarAccFull + buf), (local >> 1) & 1, abort_flag, 3);
             if (!ok) break;
@@ -357,6 +378,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 }
                 ++nstore;
             }
+            ++local;
         }
         if (lane == 0) tma_store_wait_read();  // shared memory stays valid until the last store has read it
     }
@@ -470,6 +492,7 @@ int gemm_run(const paras_gemm_args* a, const GemmExtra* ex) {
         p.Lq = ex->Lq > 0 ? ex->Lq : 1; p.causal = ex->causal; p.scale = ex->scale;
         p.scale_log2 = ex->scale * 1.4426950408889634f;
         p.k_skip = ex->causal ? ex->k_skip : 0;
+        p.tile_skip = ex->causal && (epi == kEpiProb || epi == kEpiDs) ? ex->tile_skip : 0;
     }
     cudaStream_t s = pick_stream(g, a->stream);
     const bool bf = a->dtype == PARAS_BF16;

@@ -138,6 +138,9 @@ extern "C" int paras_b200_sdpa_bwd(const paras_sdpa_bwd_args* a) {
             // P = exp(Q K^T * scale - lse)
             GemmExtra ex{};
             ex.epilogue = 3; ex.row_stat = a->lse + g0 * R; ex.Lq = a->Lq; ex.causal = a->causal; ex.scale = scale;
+            // tiles of P and dS no query sees are left unwritten: the three reductions below skip them.
+            // With more keys than queries a key tile past the last query still needs its zeros.
+            ex.tile_skip = a->Lk <= a->Lq;
             if ((rc = gemm(q, PARAS_GEMM_A_MK, a->D, qs, k, PARAS_GEMM_B_NK, a->D, ks, smat, a->Lk, ms, R, a->Lk, a->D, &ex)) != PARAS_OK) return rc;
             // dV = P^T dO  (under a causal mask the query rows before a key tile hold only zeros: skipped)
             GemmExtra skip{};

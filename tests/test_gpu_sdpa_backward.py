@@ -48,6 +48,9 @@ CASES = [
     (2, 4, 2, 384, 384, 128, True),      # GQA: dk / dv sum over the group's query heads
     (1, 4, 1, 200, 328, 128, False),     # ragged rows, Lq != Lk
     (1, 2, 2, 136, 264, 64, True),       # D = 64, top-left aligned causal mask with Lk > Lq
+    (1, 4, 2, 1000, 1000, 128, True),    # stacked heads whose 128-row tiles straddle two heads
+    (1, 2, 2, 640, 320, 128, True),      # fewer keys than queries
+    (2, 2, 1, 1024, 1024, 64, True),     # several causally empty 128 x 256 tiles per head
 ]
 
 
@@ -62,6 +65,12 @@ def test_backward_through_the_c_abi(case, dtype):
     dout = torch.randn(B, Hq, Lq, D, generator=g).to(dtype)
     qd, kd, vd, dd = (t.to(CUDA) for t in (q, k, v, dout))
     out, lse = abi.sdpa_fwd(qd, kd, vd, causal=causal, return_lse=True)
+    # Causally empty tiles of the two [rows, Lk] scratch matrices are never written and must never be
+    # read: fill the library's pool with NaN first, so that a read of one would show in the gradients.
+    scratch = B * Hq * Lq * 4 + 2 * B * Hq * Lq * Lk * 2 + 4096
+    poison = torch.full((scratch // 4,), float("nan"), dtype=torch.float32, device=DEV)
+    torch_paras.synchronize()
+    del poison
     dq, dk, dv = abi.sdpa_bwd(dd, qd, kd, vd, out, lse, causal=causal)
     wq, wk, wv = reference_grads(q, k, v, dout, causal)
     check(dq, wq, f"dq {case} {dtype}")
