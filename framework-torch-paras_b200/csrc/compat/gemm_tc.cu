@@ -68,6 +68,7 @@ struct GemmParams {
     float scale, scale_log2;
     int k_skip;   // 0 none; 1: rows = queries, K = keys (dQ); 2: rows = keys, K = stacked queries (dV, dK)
     int tile_skip;  // rows = queries, columns = keys (P, dS): tiles with nothing visible are left alone
+    int narrow;     // N <= 128: the B tile, the MMA and the epilogue cover 128 columns instead of 256
 };
 
 struct Tile { int b, m0, n0; };
@@ -174,7 +175,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     ok = mbar_wait(bar(kBarEmpty + st), ((it / kStages) & 1) ^ 1u, abort_flag, 0);
                     if (!ok) break;
                     const uint32_t full = bar(kBarFull + st);
-                    mbar_arrive_expect_tx(full, kStageBytes);
+                    mbar_arrive_expect_tx(full, p.narrow ? kABytes + kBBytes / 2 : kStageBytes);
                     const uint32_t a_dst = smem_base + st * kStageBytes;
                     const uint32_t b_dst = a_dst + kABytes;
                     if (A_ROWS_OF_M) {
@@ -186,10 +187,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         tma_load_3d(a_dst, &map_a, full, kk * BK, t.m0, t.b);
                     }
                     if (B_ROWS_OF_N) {
-                        // B is [K, N]: four 64-column slabs of 64 K-rows each
+                        // B is [K, N]: four (narrow: two) 64-column slabs of 64 K-rows each
 #pragma unroll
                         for (int i = 0; i < BN / 64; ++i)
-                            tma_load_3d(b_dst + i * (BK * 128), &map_b, full, t.n0 + 64 * i, kk * BK, t.b);
+                            if (i < 2 || !p.narrow)
+                                tma_load_3d(b_dst + i * (BK * 128), &map_b, full, t.n0 + 64 * i, kk * BK, t.b);
                     } else if (EPI == kEpiSwiglu) {
                         tma_load_3d(b_dst, &map_b, full, kk * BK, t.n0, t.b);                // gate rows
                         tma_load_3d(b_dst + kBBytes / 2, &map_b2, full, kk * BK, t.n0, t.b);  // up rows
@@ -203,7 +205,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     } else if (warp == kMmaWarp) {
         // ------------------------------ MMA issuer --------------------------------
         if (lane == 0) {
-            constexpr uint32_t idesc = instr_desc_f16(BF16 ? 1 : 0, BM, BN, A_ROWS_OF_M, B_ROWS_OF_N);
+            const uint32_t idesc = p.narrow ? instr_desc_f16(BF16 ? 1 : 0, BM, BN / 2, A_ROWS_OF_M, B_ROWS_OF_N)
+                                            : instr_desc_f16(BF16 ? 1 : 0, BM, BN, A_ROWS_OF_M, B_ROWS_OF_N);
             bool ok = true;
             int it = 0, local = 0;
             for (int id = blockIdx.x; ok && id < p.tiles; id += gridDim.x) {
@@ -264,7 +267,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             tc_fence_after_sync();
             const uint32_t acc = tmem + lane_base + buf * BN;
             const int row_w = t.m0 + wq * 32;
-            constexpr int kChunks = kNPerTile / 64;  // 64 output columns per store
+            const int kChunks = p.narrow ? kNPerTile / 128 : kNPerTile / 64;  // 64 output columns per store
 #pragma unroll 1
             for (int c = 0; c < kChunks; ++c) {
                 uint32_t out[32];  // 64 outputs, packed in pairs
@@ -460,7 +463,9 @@ int gemm_run(const paras_gemm_args* a, const GemmExtra* ex) {
 
     const bool kn = a->b_layout == PARAS_GEMM_B_KN;
     const bool at = a->a_layout == PARAS_GEMM_A_KM;
-    const int n_per_tile = a->epilogue == kEpiSwiglu ? BN / 2 : BN;
+    // N <= 128 (the [.., head dim] products of attention backward): half-width B tiles and MMAs
+    const bool narrow = a->N <= BN / 2 && (epi == kEpiNone || epi == kEpiBias);
+    const int n_per_tile = a->epilogue == kEpiSwiglu || narrow ? BN / 2 : BN;
     CUtensorMap ma, mb, mb2, mc;
     if (at) {
         if ((st = make_tensor_map_3d(&ma, a->a, a->dtype, a->M, a->K, a->batch, a->lda, a->stride_a, 64, BK)) != PARAS_OK) return st;
@@ -485,6 +490,7 @@ int gemm_run(const paras_gemm_args* a, const GemmExtra* ex) {
     if (tiles > INT32_MAX) return fail(PARAS_E_UNSUPPORTED, "paras gemm: too many tiles");
     p.tiles = int(tiles);
     p.k_iters = int((a->K + BK - 1) / BK);
+    p.narrow = narrow;
     p.bias = a->bias;
     p.status = g->status_dev;
     if (ex) {

@@ -39,7 +39,8 @@ def rand(shape, seed, dtype, scale=1.0):
 
 
 SHAPES = [(128, 256, 64), (256, 512, 512), (300, 520, 136), (1, 8, 8), (77, 1000, 264),
-          (640, 384, 1000), (129, 257 * 8, 72)]
+          (640, 384, 1000), (129, 257 * 8, 72),
+          (1000, 128, 520), (333, 72, 264), (4096, 128, 2048)]   # N <= 128: half-width tiles
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
@@ -77,7 +78,7 @@ def test_batched_and_strided_operands():
     assert float(out[:, :8].abs().sum()) == 0.0 and float(out[:, 272:].abs().sum()) == 0.0
 
 
-@pytest.mark.parametrize("shape", [(128, 256, 64), (304, 520, 136), (1000, 264, 392)])
+@pytest.mark.parametrize("shape", [(128, 256, 64), (304, 520, 136), (1000, 264, 392), (520, 128, 1000), (304, 64, 136)])
 def test_transposed_a_operand(shape):
     # A given as [K, M] (rows of M): C = A^T B, with B in either layout
     M, N, K = shape
