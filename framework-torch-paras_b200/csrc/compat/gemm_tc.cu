@@ -262,15 +262,47 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const Tile t = get_tile(p, id, kNPerTile);
             if (skip_tile(p, t)) continue;
             const int buf = local & 1;
+            const int row_w = t.m0 + wq * 32;
+            const int kChunks = p.narrow ? kNPerTile / 128 : kNPerTile / 64;  // 64 output columns per store
+            // Attention-backward epilogues: a thread owns a row, so the row's statistic is one value per
+            // thread.  It, and the first piece of P, are fetched before the wait for the accumulator, so
+            // that their latency runs under the tile's main loop; the four epilogue warps have nothing
+            // else to hide it behind.
+            float stat = 0.f;
+            int qpos = 0, qmin = 0, qmax = 0;
+            const uint16_t* prow = nullptr;
+            uint4 pcur[8];
+            auto load_prob = [&](int c, uint4 (&dst)[8]) {
+                const int col0 = t.n0 + 64 * c;
+                const bool visible = !(p.causal && col0 > qmax);   // else every probability of the piece is zero
+#pragma unroll
+                for (int v = 0; v < 8; ++v) {
+                    dst[v] = make_uint4(0, 0, 0, 0);
+                    if (visible && col0 + 8 * v < p.N) dst[v] = __ldg(reinterpret_cast<const uint4*>(prow + col0) + v);
+                }
+            };
+            if (EPI == kEpiProb || EPI == kEpiDs) {
+                const int row = min(row_w + lane, p.M - 1);
+                const int64_t grow = int64_t(t.b) * p.M + row;
+                stat = __ldg(p.row_stat + grow);
+                qpos = row % p.Lq;
+                // whole 64-column pieces are usually either visible to all 32 rows or to none
+                qmin = __reduce_min_sync(0xffffffffu, qpos);
+                qmax = __reduce_max_sync(0xffffffffu, qpos);
+                if (EPI == kEpiDs) {
+                    prow = static_cast<const uint16_t*>(p.prob) + grow * p.prob_ld;
+                    load_prob(0, pcur);
+                }
+            }
             ok = mbar_wait<32>(bar(kBarAccFull + buf), (local >> 1) & 1, abort_flag, 3);
             if (!ok) break;
             tc_fence_after_sync();
             const uint32_t acc = tmem + lane_base + buf * BN;
-            const int row_w = t.m0 + wq * 32;
-            const int kChunks = p.narrow ? kNPerTile / 128 : kNPerTile / 64;  // 64 output columns per store
 #pragma unroll 1
             for (int c = 0; c < kChunks; ++c) {
                 uint32_t out[32];  // 64 outputs, packed in pairs
+                uint4 pnext[8];
+                if (EPI == kEpiDs && c + 1 < kChunks) load_prob(c + 1, pnext);  // in flight during this piece
                 if (EPI == kEpiSwiglu) {
 #pragma unroll
                     for (int h = 0; h < 2; ++h) {
@@ -301,51 +333,37 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     tmem_wait_ld();
                     tmem_ld_fence32(reinterpret_cast<uint32_t(&)[32]>(o[0]));
                     tmem_ld_fence32(reinterpret_cast<uint32_t(&)[32]>(o[32]));
-                    if (EPI == kEpiProb || EPI == kEpiDs) {
-                        // C = exp(acc*scale - stat[row]) with causal masking, or C = P o (acc - stat[row]) * scale:
-                        // a thread owns a row, so the row's statistic is one value per thread
-                        const int row = min(row_w + lane, p.M - 1);
-                        const int64_t grow = int64_t(t.b) * p.M + row;
-                        const float stat = p.row_stat[grow];
+                    if (EPI == kEpiProb) {
+                        // C = exp(acc * scale - stat[row]), zero where the key comes after the query
+                        const float neg = -stat * 1.4426950408889634f;
                         const int col0 = t.n0 + 64 * c;
-                        if (EPI == kEpiProb) {
-                            const float neg = -stat * 1.4426950408889634f;
-                            const int qpos = row % p.Lq;
-                            // whole 64-column pieces are usually either visible to all 32 rows or to none
-                            const int qmin = __reduce_min_sync(0xffffffffu, qpos);
-                            const int qmax = __reduce_max_sync(0xffffffffu, qpos);
-                            if (!p.causal || col0 + 63 <= qmin) {
+                        if (!p.causal || col0 + 63 <= qmin) {
 #pragma unroll
-                                for (int i = 0; i < 64; ++i)
-                                    o[i] = __float_as_uint(ex2_approx(fmaf(__uint_as_float(o[i]), p.scale_log2, neg)));
-                            } else if (col0 > qmax) {
-#pragma unroll
-                                for (int i = 0; i < 64; ++i) o[i] = 0u;
-                            } else {
-#pragma unroll
-                                for (int i = 0; i < 64; ++i)
-                                    o[i] = col0 + i <= qpos
-                                               ? __float_as_uint(ex2_approx(fmaf(__uint_as_float(o[i]), p.scale_log2, neg)))
-                                               : 0u;
-                            }
-                        } else if (p.causal && col0 > __reduce_max_sync(0xffffffffu, row % p.Lq)) {
-                            // every probability of this piece is zero
+                            for (int i = 0; i < 64; ++i)
+                                o[i] = __float_as_uint(ex2_approx(fmaf(__uint_as_float(o[i]), p.scale_log2, neg)));
+                        } else if (col0 > qmax) {
 #pragma unroll
                             for (int i = 0; i < 64; ++i) o[i] = 0u;
                         } else {
-                            const uint16_t* pr = static_cast<const uint16_t*>(p.prob) + grow * p.prob_ld + col0;
 #pragma unroll
-                            for (int v = 0; v < 8; ++v) {
-                                uint4 w = make_uint4(0, 0, 0, 0);
-                                if (col0 + 8 * v < p.N) w = __ldg(reinterpret_cast<const uint4*>(pr) + v);
-                                const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+                            for (int i = 0; i < 64; ++i)
+                                o[i] = col0 + i <= qpos
+                                           ? __float_as_uint(ex2_approx(fmaf(__uint_as_float(o[i]), p.scale_log2, neg)))
+                                           : 0u;
+                        }
+                    } else if (EPI == kEpiDs) {
+                        // C = P o (acc - stat[row]) * scale; P is zero where the key comes after the query
 #pragma unroll
-                                for (int e = 0; e < 8; ++e) {
-                                    const float pv = from16<BF16>(uint16_t((ww[e >> 1] >> (16 * (e & 1))) & 0xffffu));
-                                    o[8 * v + e] = __float_as_uint(pv * (__uint_as_float(o[8 * v + e]) - stat) * p.scale);
-                                }
+                        for (int v = 0; v < 8; ++v) {
+                            const uint32_t ww[4] = {pcur[v].x, pcur[v].y, pcur[v].z, pcur[v].w};
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) {
+                                const float pv = from16<BF16>(uint16_t((ww[e >> 1] >> (16 * (e & 1))) & 0xffffu));
+                                o[8 * v + e] = __float_as_uint(pv * (__uint_as_float(o[8 * v + e]) - stat) * p.scale);
                             }
                         }
+#pragma unroll
+                        for (int v = 0; v < 8; ++v) pcur[v] = pnext[v];
                     }
 #pragma unroll
                     for (int i = 0; i < 64; i += 2) {
