@@ -10,6 +10,7 @@
 //   warps 0-3  epilogue: TMEM -> registers -> 16 bit -> swizzled shared memory -> TMA store
 //   warp  4    allocates TMEM; one lane issues tcgen05.mma (M128 x N256 x K16, 4 per K step)
 //   warp  5    one lane issues the TMA loads: 4-stage ring of (A 16 KB, B 32 KB)
+//   warps 6-9  (attention-backward epilogues only) a second epilogue group on every other 64 columns
 // TMEM holds two 256-column accumulators, so the epilogue of a tile runs under the next
 // tile's main loop.  For SwiGLU the B tile is 128 rows of the gate weight followed by 128
 // rows of the up weight: one N=256 MMA leaves [gate | up] side by side in the accumulator.
@@ -38,6 +39,10 @@ constexpr int kStageBytes = kABytes + kBBytes;
 constexpr int kEpiWarps = 4;
 constexpr int kMmaWarp = 4, kLoadWarp = 5;
 constexpr int kThreads = 192;
+// The attention-backward epilogues do per-element work on two-K-step tiles, so the epilogue is their
+// critical path: those kernels run a second group of four epilogue warps (warps 6-9) that takes every
+// other 64-column piece, and a three-stage ring whose fourth stage is the second group's staging.
+constexpr int kThreadsWide = 320;
 constexpr int kTmemCols = 512;               // two accumulators of BN columns
 constexpr int kOutStage = 32 * 128;          // 32 rows x 64 columns of 16 bit
 constexpr int kGroupM = 16;                  // tile order: 16 row blocks at a time
@@ -118,7 +123,7 @@ __device__ __forceinline__ bool skip_k_step(const GemmParams& p, int m0, int kk)
 }
 
 template <bool BF16, bool A_ROWS_OF_M, bool B_ROWS_OF_N, int EPI>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(EPI >= kEpiProb ? kThreadsWide : kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const __grid_constant__ CUtensorMap map_b2, const __grid_constant__ CUtensorMap map_c,
                const GemmParams p) {
@@ -128,6 +133,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_raw + kSmemMisc);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_raw + kSmemMisc + 4);
     constexpr int kNPerTile = EPI == kEpiSwiglu ? BN / 2 : BN;   // output columns per tile
+    constexpr int kEpiGroups = EPI >= kEpiProb ? 2 : 1;          // groups of four epilogue warps
+    constexpr int kRing = EPI >= kEpiProb ? kStages - 1 : kStages;  // stages of the operand ring in use
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (*reinterpret_cast<volatile int*>(&g_gemm_abort_latch)) return;  // uniform: before any barrier or TMEM use
@@ -141,7 +148,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         return;
     }
     if (threadIdx.x == 0) {
-        for (int i = 0; i < kNumBars; ++i) mbar_init(bar(i), i >= kBarAccEmpty ? uint32_t(kEpiWarps) : 1u);
+        for (int i = 0; i < kNumBars; ++i)
+            mbar_init(bar(i), i >= kBarAccEmpty ? uint32_t(kEpiWarps * kEpiGroups) : 1u);
         *abort_flag = 0;
         mbar_fence_init();
         fence_proxy_async_smem();
@@ -171,8 +179,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 if (skip_tile(p, t)) continue;
                 for (int kk = 0; kk < p.k_iters; ++kk) {
                     if (skip_k_step(p, t.m0, kk)) continue;
-                    const int st = it % kStages;
-                    ok = mbar_wait(bar(kBarEmpty + st), ((it / kStages) & 1) ^ 1u, abort_flag, 0);
+                    const int st = it % kRing;
+                    ok = mbar_wait(bar(kBarEmpty + st), ((it / kRing) & 1) ^ 1u, abort_flag, 0);
                     if (!ok) break;
                     const uint32_t full = bar(kBarFull + st);
                     mbar_arrive_expect_tx(full, p.narrow ? kABytes + kBBytes / 2 : kStageBytes);
@@ -224,8 +232,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 bool first = true;  // the first K step that runs overwrites the accumulator
                 for (int kk = 0; kk < p.k_iters; ++kk) {
                     if (skip_k_step(p, m0, kk)) continue;
-                    const int st = it % kStages;
-                    ok = mbar_wait(bar(kBarFull + st), (it / kStages) & 1, abort_flag, 2);
+                    const int st = it % kRing;
+                    ok = mbar_wait(bar(kBarFull + st), (it / kRing) & 1, abort_flag, 2);
                     if (!ok) break;
                     tc_fence_after_sync();
                     const uint32_t a_addr = smem_base + st * kStageBytes;
@@ -252,9 +260,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         __syncwarp();
     } else {
         // ------------------------------ epilogue -----------------------------------
-        const int wq = warp;  // TMEM lanes 32*wq .. 32*wq+31
+        const int wq = warp & 3;                 // TMEM lanes 32*wq .. 32*wq+31: a warp reaches its own quarter only
+        const int eg = warp < kEpiWarps ? 0 : 1; // second group: warps 6-9, only in the wide kernels
         const uint32_t lane_base = uint32_t(wq * 32) << 16;
-        const uint32_t stage0 = smem_base + kSmemOut + wq * 2 * kOutStage;
+        const uint32_t stage0 = (eg == 0 ? smem_base + kSmemOut : smem_base + (kStages - 1) * kStageBytes) +
+                                wq * 2 * kOutStage;
         bool ok = true;
         int local = 0;
         uint32_t nstore = 0;  // stores issued by this warp (picks the staging buffer)
@@ -291,7 +301,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 qmax = __reduce_max_sync(0xffffffffu, qpos);
                 if (EPI == kEpiDs) {
                     prow = static_cast<const uint16_t*>(p.prob) + grow * p.prob_ld;
-                    load_prob(0, pcur);
+                    load_prob(eg, pcur);
                 }
             }
             ok = mbar_wait<32>(bar(kBarAccFull + buf), (local >> 1) & 1, abort_flag, 3);
@@ -299,10 +309,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             tc_fence_after_sync();
             const uint32_t acc = tmem + lane_base + buf * BN;
 #pragma unroll 1
-            for (int c = 0; c < kChunks; ++c) {
+            for (int c = eg; c < kChunks; c += kEpiGroups) {
                 uint32_t out[32];  // 64 outputs, packed in pairs
                 uint4 pnext[8];
-                if (EPI == kEpiDs && c + 1 < kChunks) load_prob(c + 1, pnext);  // in flight during this piece
+                if (EPI == kEpiDs && c + kEpiGroups < kChunks) load_prob(c + kEpiGroups, pnext);  // in flight during this piece
                 if (EPI == kEpiSwiglu) {
 #pragma unroll
                     for (int h = 0; h < 2; ++h) {
@@ -377,7 +387,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         out[i / 2] = pack16<BF16>(x0, x1);
                     }
                 }
-                if (c == kChunks - 1) {
+                if (c + kEpiGroups >= kChunks) {
                     // the accumulator is in registers: the MMA warp may start the tile after next
                     tc_fence_before_sync();
                     __syncwarp();
@@ -428,7 +438,8 @@ int launch(Gpu* g, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorM
     auto kernel = gemm_tc_kernel<BF16, A_ROWS_OF_M, B_ROWS_OF_N, EPI>;
     PB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal));
     const int sms = g->sm_count > 0 ? g->sm_count : 148;
-    kernel<<<dim3(unsigned(p.tiles < sms ? p.tiles : sms)), kThreads, kSmemTotal, s>>>(ma, mb, mb2, mc, p);
+    kernel<<<dim3(unsigned(p.tiles < sms ? p.tiles : sms)), EPI >= kEpiProb ? kThreadsWide : kThreads, kSmemTotal, s>>>(
+        ma, mb, mb2, mc, p);
     PB_LAUNCH_CHECK("gemm_tc_kernel");
     return PARAS_OK;
 }
