@@ -74,13 +74,33 @@ struct GemmParams {
     int k_skip;   // 0 none; 1: rows = queries, K = keys (dQ); 2: rows = keys, K = stacked queries (dV, dK)
     int tile_skip;  // rows = queries, columns = keys (P, dS): tiles with nothing visible are left alone
     int narrow;     // N <= 128: the B tile, the MMA and the epilogue cover 128 columns instead of 256
+    int pair;       // causal reductions: tiles taken in heavy/light pairs (get_tile); the span they pair within
 };
 
 struct Tile { int b, m0, n0; };
 
+// Causal reductions: a tile's work is the number of K steps it can see, which varies 16-fold with
+// its row position.  There (p.pair, one column of tiles) ids 2i and 2i+1 are the i-th tile from the
+// heavy end and the i-th from the light end of the same matrix (mode 2) or query head (mode 1), and a
+// CTA takes both, so every CTA gets about the same work and both tiles read the same B operand.
+__device__ __forceinline__ int first_tile(const GemmParams& p) { return p.pair ? 2 * int(blockIdx.x) : int(blockIdx.x); }
+__device__ __forceinline__ int next_tile(const GemmParams& p, int id) {
+    if (!p.pair) return id + int(gridDim.x);
+    return (id & 1) ? id - 1 + 2 * int(gridDim.x) : id + 1;   // an odd count's last id + 1 ends the loop
+}
+
 __device__ __forceinline__ Tile get_tile(const GemmParams& p, int id, int n_per_tile) {
     const int per_batch = p.tiles_m * p.tiles_n;
     Tile t;
+    if (p.pair) {
+        t.b = id / p.tiles_m;
+        const int q = id - t.b * p.tiles_m;
+        const int span = p.pair;                 // tiles per matrix (mode 2) or per query head (mode 1)
+        const int h = q / span, j = q - h * span;
+        t.m0 = (h * span + ((j & 1) ? span - 1 - (j >> 1) : (j >> 1))) * BM;
+        t.n0 = 0;
+        return t;
+    }
     t.b = id / per_batch;
     const int r = id - t.b * per_batch;
     const int in_group = kGroupM * p.tiles_n;
@@ -174,7 +194,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         if (lane == 0) {
             bool ok = true;
             int it = 0;  // K steps loaded so far, across tiles
-            for (int id = blockIdx.x; ok && id < p.tiles; id += gridDim.x) {
+            for (int id = first_tile(p); ok && id < p.tiles; id = next_tile(p, id)) {
                 const Tile t = get_tile(p, id, kNPerTile);
                 if (skip_tile(p, t)) continue;
                 for (int kk = 0; kk < p.k_iters; ++kk) {
@@ -217,7 +237,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                                             : instr_desc_f16(BF16 ? 1 : 0, BM, BN, A_ROWS_OF_M, B_ROWS_OF_N);
             bool ok = true;
             int it = 0, local = 0;
-            for (int id = blockIdx.x; ok && id < p.tiles; id += gridDim.x) {
+            for (int id = first_tile(p); ok && id < p.tiles; id = next_tile(p, id)) {
                 Tile t{0, 0, 0};
                 if (p.k_skip || p.tile_skip) {
                     t = get_tile(p, id, kNPerTile);
@@ -268,7 +288,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         bool ok = true;
         int local = 0;
         uint32_t nstore = 0;  // stores issued by this warp (picks the staging buffer)
-        for (int id = blockIdx.x; ok && id < p.tiles; id += gridDim.x) {
+        for (int id = first_tile(p); ok && id < p.tiles; id = next_tile(p, id)) {
             const Tile t = get_tile(p, id, kNPerTile);
             if (skip_tile(p, t)) continue;
             const int buf = local & 1;
@@ -438,7 +458,8 @@ int launch(Gpu* g, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorM
     auto kernel = gemm_tc_kernel<BF16, A_ROWS_OF_M, B_ROWS_OF_N, EPI>;
     PB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal));
     const int sms = g->sm_count > 0 ? g->sm_count : 148;
-    kernel<<<dim3(unsigned(p.tiles < sms ? p.tiles : sms)), EPI >= kEpiProb ? kThreadsWide : kThreads, kSmemTotal, s>>>(
+    const int units = p.pair ? (p.tiles + 1) / 2 : p.tiles;   // what a CTA takes per round
+    kernel<<<dim3(unsigned(units < sms ? units : sms)), EPI >= kEpiProb ? kThreadsWide : kThreads, kSmemTotal, s>>>(
         ma, mb, mb2, mc, p);
     PB_LAUNCH_CHECK("gemm_tc_kernel");
     return PARAS_OK;
@@ -528,6 +549,8 @@ int gemm_run(const paras_gemm_args* a, const GemmExtra* ex) {
         p.scale_log2 = ex->scale * 1.4426950408889634f;
         p.k_skip = ex->causal ? ex->k_skip : 0;
         p.tile_skip = ex->causal && (epi == kEpiProb || epi == kEpiDs) ? ex->tile_skip : 0;
+        if (p.k_skip == 2 && p.tiles_n == 1) p.pair = p.tiles_m;
+        if (p.k_skip == 1 && p.tiles_n == 1 && p.Lq % BM == 0 && p.tiles_m % (p.Lq / BM) == 0) p.pair = p.Lq / BM;
     }
     cudaStream_t s = pick_stream(g, a->stream);
     const bool bf = a->dtype == PARAS_BF16;
