@@ -49,8 +49,14 @@ constexpr int kGroupM = 16;                  // tile order: 16 row blocks at a t
 
 constexpr int kSmemOut = kStages * kStageBytes;                 // [4 warps][2] staging buffers
 constexpr int kSmemBars = kSmemOut + kEpiWarps * 2 * kOutStage;
-constexpr int kBarFull = 0, kBarEmpty = kStages, kBarAccFull = 2 * kStages, kBarAccEmpty = 2 * kStages + 2;
-constexpr int kNumBars = 2 * kStages + 4;
+// With half-width B tiles a stage is 32 KB instead of 48 KB, and the same 192 KB hold a ring of six:
+// the N <= 128 products of attention backward stream one operand from HBM, so bytes in flight are
+// what bounds them.
+constexpr int kNarrowStageBytes = kABytes + kBBytes / 2;
+constexpr int kNarrowRing = kStages * kStageBytes / kNarrowStageBytes;   // 6
+constexpr int kMaxRing = kNarrowRing;
+constexpr int kBarFull = 0, kBarEmpty = kMaxRing, kBarAccFull = 2 * kMaxRing, kBarAccEmpty = 2 * kMaxRing + 2;
+constexpr int kNumBars = 2 * kMaxRing + 4;
 constexpr int kSmemMisc = kSmemBars + kNumBars * 8;             // tmem base word, abort flag
 constexpr int kSmemTotal = kSmemMisc + 16;
 
@@ -193,18 +199,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         // ------------------------------ TMA producer ------------------------------
         if (lane == 0) {
             bool ok = true;
-            int it = 0;  // K steps loaded so far, across tiles
+            const int ring = p.narrow ? kNarrowRing : kRing;
+            const uint32_t stage_bytes = p.narrow ? kNarrowStageBytes : kStageBytes;
+            int st = 0;            // ring position and its phase, across tiles
+            uint32_t phase = 0;
             for (int id = first_tile(p); ok && id < p.tiles; id = next_tile(p, id)) {
                 const Tile t = get_tile(p, id, kNPerTile);
                 if (skip_tile(p, t)) continue;
                 for (int kk = 0; kk < p.k_iters; ++kk) {
                     if (skip_k_step(p, t.m0, kk)) continue;
-                    const int st = it % kRing;
-                    ok = mbar_wait(bar(kBarEmpty + st), ((it / kRing) & 1) ^ 1u, abort_flag, 0);
+                    ok = mbar_wait(bar(kBarEmpty + st), phase ^ 1u, abort_flag, 0);
                     if (!ok) break;
                     const uint32_t full = bar(kBarFull + st);
-                    mbar_arrive_expect_tx(full, p.narrow ? kABytes + kBBytes / 2 : kStageBytes);
-                    const uint32_t a_dst = smem_base + st * kStageBytes;
+                    mbar_arrive_expect_tx(full, stage_bytes);
+                    const uint32_t a_dst = smem_base + st * stage_bytes;
                     const uint32_t b_dst = a_dst + kABytes;
                     if (A_ROWS_OF_M) {
                         // A is [K, M]: two 64-row-of-M slabs of 64 K-rows each
@@ -226,7 +234,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     } else {
                         tma_load_3d(b_dst, &map_b, full, kk * BK, t.n0, t.b);
                     }
-                    ++it;
+                    if (++st == ring) { st = 0; phase ^= 1u; }
                 }
             }
         }
@@ -236,7 +244,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const uint32_t idesc = p.narrow ? instr_desc_f16(BF16 ? 1 : 0, BM, BN / 2, A_ROWS_OF_M, B_ROWS_OF_N)
                                             : instr_desc_f16(BF16 ? 1 : 0, BM, BN, A_ROWS_OF_M, B_ROWS_OF_N);
             bool ok = true;
-            int it = 0, local = 0;
+            const int ring = p.narrow ? kNarrowRing : kRing;
+            const uint32_t stage_bytes = p.narrow ? kNarrowStageBytes : kStageBytes;
+            int st = 0, local = 0;
+            uint32_t phase = 0;
             for (int id = first_tile(p); ok && id < p.tiles; id = next_tile(p, id)) {
                 Tile t{0, 0, 0};
                 if (p.k_skip || p.tile_skip) {
@@ -252,11 +263,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 bool first = true;  // the first K step that runs overwrites the accumulator
                 for (int kk = 0; kk < p.k_iters; ++kk) {
                     if (skip_k_step(p, m0, kk)) continue;
-                    const int st = it % kRing;
-                    ok = mbar_wait(bar(kBarFull + st), (it / kRing) & 1, abort_flag, 2);
+                    ok = mbar_wait(bar(kBarFull + st), phase, abort_flag, 2);
                     if (!ok) break;
                     tc_fence_after_sync();
-                    const uint32_t a_addr = smem_base + st * kStageBytes;
+                    const uint32_t a_addr = smem_base + st * stage_bytes;
                     const uint32_t b_addr = a_addr + kABytes;
 #pragma unroll
                     for (int ks = 0; ks < BK / 16; ++ks) {
@@ -270,7 +280,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     }
                     first = false;
                     tc_commit(bar(kBarEmpty + st));
-                    ++it;
+                    if (++st == ring) { st = 0; phase ^= 1u; }
                 }
                 if (!ok) break;
                 tc_commit(bar(kBarAccFull + buf));
