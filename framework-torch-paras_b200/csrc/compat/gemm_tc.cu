@@ -49,12 +49,13 @@ constexpr int kGroupM = 16;                  // tile order: 16 row blocks at a t
 
 constexpr int kSmemOut = kStages * kStageBytes;                 // [4 warps][2] staging buffers
 constexpr int kSmemBars = kSmemOut + kEpiWarps * 2 * kOutStage;
-// With half-width B tiles a stage is 32 KB instead of 48 KB, and the same 192 KB hold a ring of six:
-// the N <= 128 products of attention backward stream one operand from HBM, so bytes in flight are
-// what bounds them.
-constexpr int kNarrowStageBytes = kABytes + kBBytes / 2;
-constexpr int kNarrowRing = kStages * kStageBytes / kNarrowStageBytes;   // 6
-constexpr int kMaxRing = kNarrowRing;
+// With half-width B tiles a K step is 32 KB instead of 48 KB and its four MMAs take less time than the
+// issuing thread needs per barrier round trip, so such a kernel moves two K steps per stage: the
+// same 192 KB hold a ring of three 64 KB stages, and the waits and commits per byte halve.
+constexpr int kNarrowStepBytes = kABytes + kBBytes / 2;
+constexpr int kNarrowStageBytes = 2 * kNarrowStepBytes;
+constexpr int kNarrowRing = kStages * kStageBytes / kNarrowStageBytes;   // 3
+constexpr int kMaxRing = kStages;
 constexpr int kBarFull = 0, kBarEmpty = kMaxRing, kBarAccFull = 2 * kMaxRing, kBarAccEmpty = 2 * kMaxRing + 2;
 constexpr int kNumBars = 2 * kMaxRing + 4;
 constexpr int kSmemMisc = kSmemBars + kNumBars * 8;             // tmem base word, abort flag
@@ -148,6 +149,12 @@ __device__ __forceinline__ bool skip_k_step(const GemmParams& p, int m0, int kk)
     return qmax < m0;
 }
 
+// The first K step at or after kk that runs (k_iters if none).
+__device__ __forceinline__ int next_k_step(const GemmParams& p, int m0, int kk) {
+    while (kk < p.k_iters && skip_k_step(p, m0, kk)) ++kk;
+    return kk;
+}
+
 template <bool BF16, bool A_ROWS_OF_M, bool B_ROWS_OF_N, int EPI>
 __global__ void __launch_bounds__(EPI >= kEpiProb ? kThreadsWide : kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -201,38 +208,50 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             bool ok = true;
             const int ring = p.narrow ? kNarrowRing : kRing;
             const uint32_t stage_bytes = p.narrow ? kNarrowStageBytes : kStageBytes;
+            const uint32_t step_bytes = p.narrow ? kNarrowStepBytes : kStageBytes;
             int st = 0;            // ring position and its phase, across tiles
             uint32_t phase = 0;
             for (int id = first_tile(p); ok && id < p.tiles; id = next_tile(p, id)) {
                 const Tile t = get_tile(p, id, kNPerTile);
                 if (skip_tile(p, t)) continue;
-                for (int kk = 0; kk < p.k_iters; ++kk) {
-                    if (skip_k_step(p, t.m0, kk)) continue;
+                int kk = next_k_step(p, t.m0, 0);
+                while (kk < p.k_iters) {
+                    // the K steps of this stage: one, or (half-width tiles) the next two that run
+                    int ks[2], n = 0;
+                    ks[n++] = kk;
+                    kk = next_k_step(p, t.m0, kk + 1);
+                    if (p.narrow && kk < p.k_iters) {
+                        ks[n++] = kk;
+                        kk = next_k_step(p, t.m0, kk + 1);
+                    }
                     ok = mbar_wait(bar(kBarEmpty + st), phase ^ 1u, abort_flag, 0);
                     if (!ok) break;
                     const uint32_t full = bar(kBarFull + st);
-                    mbar_arrive_expect_tx(full, stage_bytes);
-                    const uint32_t a_dst = smem_base + st * stage_bytes;
-                    const uint32_t b_dst = a_dst + kABytes;
-                    if (A_ROWS_OF_M) {
-                        // A is [K, M]: two 64-row-of-M slabs of 64 K-rows each
+                    mbar_arrive_expect_tx(full, uint32_t(n) * step_bytes);
+                    for (int j = 0; j < n; ++j) {
+                        const int k0 = ks[j] * BK;
+                        const uint32_t a_dst = smem_base + st * stage_bytes + j * step_bytes;
+                        const uint32_t b_dst = a_dst + kABytes;
+                        if (A_ROWS_OF_M) {
+                            // A is [K, M]: two 64-row-of-M slabs of 64 K-rows each
 #pragma unroll
-                        for (int i = 0; i < BM / 64; ++i)
-                            tma_load_3d(a_dst + i * (BK * 128), &map_a, full, t.m0 + 64 * i, kk * BK, t.b);
-                    } else {
-                        tma_load_3d(a_dst, &map_a, full, kk * BK, t.m0, t.b);
-                    }
-                    if (B_ROWS_OF_N) {
-                        // B is [K, N]: four (narrow: two) 64-column slabs of 64 K-rows each
+                            for (int i = 0; i < BM / 64; ++i)
+                                tma_load_3d(a_dst + i * (BK * 128), &map_a, full, t.m0 + 64 * i, k0, t.b);
+                        } else {
+                            tma_load_3d(a_dst, &map_a, full, k0, t.m0, t.b);
+                        }
+                        if (B_ROWS_OF_N) {
+                            // B is [K, N]: four (narrow: two) 64-column slabs of 64 K-rows each
 #pragma unroll
-                        for (int i = 0; i < BN / 64; ++i)
-                            if (i < 2 || !p.narrow)
-                                tma_load_3d(b_dst + i * (BK * 128), &map_b, full, t.n0 + 64 * i, kk * BK, t.b);
-                    } else if (EPI == kEpiSwiglu) {
-                        tma_load_3d(b_dst, &map_b, full, kk * BK, t.n0, t.b);                // gate rows
-                        tma_load_3d(b_dst + kBBytes / 2, &map_b2, full, kk * BK, t.n0, t.b);  // up rows
-                    } else {
-                        tma_load_3d(b_dst, &map_b, full, kk * BK, t.n0, t.b);
+                            for (int i = 0; i < BN / 64; ++i)
+                                if (i < 2 || !p.narrow)
+                                    tma_load_3d(b_dst + i * (BK * 128), &map_b, full, t.n0 + 64 * i, k0, t.b);
+                        } else if (EPI == kEpiSwiglu) {
+                            tma_load_3d(b_dst, &map_b, full, k0, t.n0, t.b);                // gate rows
+                            tma_load_3d(b_dst + kBBytes / 2, &map_b2, full, k0, t.n0, t.b);  // up rows
+                        } else {
+                            tma_load_3d(b_dst, &map_b, full, k0, t.n0, t.b);
+                        }
                     }
                     if (++st == ring) { st = 0; phase ^= 1u; }
                 }
@@ -246,6 +265,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             bool ok = true;
             const int ring = p.narrow ? kNarrowRing : kRing;
             const uint32_t stage_bytes = p.narrow ? kNarrowStageBytes : kStageBytes;
+            const uint32_t step_bytes = p.narrow ? kNarrowStepBytes : kStageBytes;
             int st = 0, local = 0;
             uint32_t phase = 0;
             for (int id = first_tile(p); ok && id < p.tiles; id = next_tile(p, id)) {
@@ -261,24 +281,33 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 const uint32_t d_tm = tmem + buf * BN;
                 const int m0 = t.m0;
                 bool first = true;  // the first K step that runs overwrites the accumulator
-                for (int kk = 0; kk < p.k_iters; ++kk) {
-                    if (skip_k_step(p, m0, kk)) continue;
+                int kk = next_k_step(p, m0, 0);
+                while (kk < p.k_iters) {
+                    // as in the loading thread: one K step per stage, or the next two that run
+                    int n = 1;
+                    kk = next_k_step(p, m0, kk + 1);
+                    if (p.narrow && kk < p.k_iters) {
+                        n = 2;
+                        kk = next_k_step(p, m0, kk + 1);
+                    }
                     ok = mbar_wait(bar(kBarFull + st), phase, abort_flag, 2);
                     if (!ok) break;
                     tc_fence_after_sync();
-                    const uint32_t a_addr = smem_base + st * stage_bytes;
-                    const uint32_t b_addr = a_addr + kABytes;
+                    for (int j = 0; j < n; ++j) {
+                        const uint32_t a_addr = smem_base + st * stage_bytes + j * step_bytes;
+                        const uint32_t b_addr = a_addr + kABytes;
 #pragma unroll
-                    for (int ks = 0; ks < BK / 16; ++ks) {
-                        const uint64_t a_desc = A_ROWS_OF_M
-                            ? smem_desc_sw128(a_addr + ks * 16 * 128, BK * 128, 1024)
-                            : smem_desc_sw128(a_addr + ks * 32, 16, 1024);
-                        const uint64_t b_desc = B_ROWS_OF_N
-                            ? smem_desc_sw128(b_addr + ks * 16 * 128, BK * 128, 1024)
-                            : smem_desc_sw128(b_addr + ks * 32, 16, 1024);
-                        mma_ss(d_tm, a_desc, b_desc, idesc, (!first || ks) ? 1u : 0u);
+                        for (int ks = 0; ks < BK / 16; ++ks) {
+                            const uint64_t a_desc = A_ROWS_OF_M
+                                ? smem_desc_sw128(a_addr + ks * 16 * 128, BK * 128, 1024)
+                                : smem_desc_sw128(a_addr + ks * 32, 16, 1024);
+                            const uint64_t b_desc = B_ROWS_OF_N
+                                ? smem_desc_sw128(b_addr + ks * 16 * 128, BK * 128, 1024)
+                                : smem_desc_sw128(b_addr + ks * 32, 16, 1024);
+                            mma_ss(d_tm, a_desc, b_desc, idesc, (!first || ks) ? 1u : 0u);
+                        }
+                        first = false;
                     }
-                    first = false;
                     tc_commit(bar(kBarEmpty + st));
                     if (++st == ring) { st = 0; phase ^= 1u; }
                 }
