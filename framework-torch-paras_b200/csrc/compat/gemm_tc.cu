@@ -211,7 +211,40 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const uint32_t step_bytes = p.narrow ? kNarrowStepBytes : kStageBytes;
             int st = 0;            // ring position and its phase, across tiles
             uint32_t phase = 0;
-            for (int id = first_tile(p); ok && id < p.tiles; id = next_tile(p, id)) {
+            // full-width tiles: one K step per stage, constants known at compile time
+            for (int id = first_tile(p); !p.narrow && ok && id < p.tiles; id = next_tile(p, id)) {
+                const Tile t = get_tile(p, id, kNPerTile);
+                if (skip_tile(p, t)) continue;
+                for (int kk = 0; kk < p.k_iters; ++kk) {
+                    if (skip_k_step(p, t.m0, kk)) continue;
+                    ok = mbar_wait(bar(kBarEmpty + st), phase ^ 1u, abort_flag, 0);
+                    if (!ok) break;
+                    const uint32_t full = bar(kBarFull + st);
+                    mbar_arrive_expect_tx(full, kStageBytes);
+                    const uint32_t a_dst = smem_base + st * kStageBytes;
+                    const uint32_t b_dst = a_dst + kABytes;
+                    if (A_ROWS_OF_M) {
+#pragma unroll
+                        for (int i = 0; i < BM / 64; ++i)
+                            tma_load_3d(a_dst + i * (BK * 128), &map_a, full, t.m0 + 64 * i, kk * BK, t.b);
+                    } else {
+                        tma_load_3d(a_dst, &map_a, full, kk * BK, t.m0, t.b);
+                    }
+                    if (B_ROWS_OF_N) {
+#pragma unroll
+                        for (int i = 0; i < BN / 64; ++i)
+                            tma_load_3d(b_dst + i * (BK * 128), &map_b, full, t.n0 + 64 * i, kk * BK, t.b);
+                    } else if (EPI == kEpiSwiglu) {
+                        tma_load_3d(b_dst, &map_b, full, kk * BK, t.n0, t.b);                // gate rows
+                        tma_load_3d(b_dst + kBBytes / 2, &map_b2, full, kk * BK, t.n0, t.b);  // up rows
+                    } else {
+                        tma_load_3d(b_dst, &map_b, full, kk * BK, t.n0, t.b);
+                    }
+                    if (++st == kRing) { st = 0; phase ^= 1u; }
+                }
+            }
+            // half-width tiles: two K steps per stage
+            for (int id = first_tile(p); p.narrow && ok && id < p.tiles; id = next_tile(p, id)) {
                 const Tile t = get_tile(p, id, kNPerTile);
                 if (skip_tile(p, t)) continue;
                 int kk = next_k_step(p, t.m0, 0);
@@ -281,7 +314,30 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 const uint32_t d_tm = tmem + buf * BN;
                 const int m0 = t.m0;
                 bool first = true;  // the first K step that runs overwrites the accumulator
-                int kk = next_k_step(p, m0, 0);
+                // full-width tiles: one K step per stage
+                for (int kk = 0; !p.narrow && kk < p.k_iters; ++kk) {
+                    if (skip_k_step(p, m0, kk)) continue;
+                    ok = mbar_wait(bar(kBarFull + st), phase, abort_flag, 2);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    const uint32_t a_addr = smem_base + st * kStageBytes;
+                    const uint32_t b_addr = a_addr + kABytes;
+#pragma unroll
+                    for (int ks = 0; ks < BK / 16; ++ks) {
+                        const uint64_t a_desc = A_ROWS_OF_M
+                            ? smem_desc_sw128(a_addr + ks * 16 * 128, BK * 128, 1024)
+                            : smem_desc_sw128(a_addr + ks * 32, 16, 1024);
+                        const uint64_t b_desc = B_ROWS_OF_N
+                            ? smem_desc_sw128(b_addr + ks * 16 * 128, BK * 128, 1024)
+                            : smem_desc_sw128(b_addr + ks * 32, 16, 1024);
+                        mma_ss(d_tm, a_desc, b_desc, idesc, (!first || ks) ? 1u : 0u);
+                    }
+                    first = false;
+                    tc_commit(bar(kBarEmpty + st));
+                    if (++st == kRing) { st = 0; phase ^= 1u; }
+                }
+                // half-width tiles: two K steps per stage
+                int kk = p.narrow ? next_k_step(p, m0, 0) : p.k_iters;
                 while (kk < p.k_iters) {
                     // as in the loading thread: one K step per stage, or the next two that run
                     int n = 1;
