@@ -23,25 +23,42 @@
 namespace pb {
 namespace {
 
-template <typename T>
+// delta[row] = sum_d dO[row, d] * O[row, d].  LPR lanes share a row (16 bytes per lane and pass), so
+// a warp takes 32 / LPR rows at a time and no lane idles on short head dims.
+template <typename T, int LPR>
 __global__ void sdpa_bwd_delta_kernel(const T* __restrict__ dout, const T* __restrict__ out,
                                       float* __restrict__ delta, int64_t rows, int D) {
+    constexpr int N = Vec16<T>::N;
+    constexpr int kRowsPerWarp = 32 / LPR;
     const int lane = threadIdx.x & 31;
+    const int sub = lane / LPR, l = lane % LPR;
     const int64_t warp = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
     const int64_t nwarps = (int64_t(gridDim.x) * blockDim.x) >> 5;
-    constexpr int N = Vec16<T>::N;
-    for (int64_t row = warp; row < rows; row += nwarps) {
-        const T* a = dout + row * D;
-        const T* b = out + row * D;
+    for (int64_t row0 = warp * kRowsPerWarp; row0 < rows; row0 += nwarps * kRowsPerWarp) {
+        const int64_t row = row0 + sub;
         float acc = 0.f;
-        for (int d = lane * N; d < D; d += 32 * N) {
-            const Vec16<T> x = ld16(a + d), y = ld16(b + d);
+        if (row < rows) {
+            const T* a = dout + row * D;
+            const T* b = out + row * D;
+            for (int d = l * N; d < D; d += LPR * N) {
+                const Vec16<T> x = ld16(a + d), y = ld16(b + d);
 #pragma unroll
-            for (int e = 0; e < N; ++e) acc = fmaf(to_f32<T>(x.v[e]), to_f32<T>(y.v[e]), acc);
+                for (int e = 0; e < N; ++e) acc = fmaf(to_f32<T>(x.v[e]), to_f32<T>(y.v[e]), acc);
+            }
         }
-        acc = warp_sum(acc);
-        if (lane == 0) delta[row] = acc;
+#pragma unroll
+        for (int o = LPR / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        if (l == 0 && row < rows) delta[row] = acc;
     }
+}
+
+template <typename T>
+void launch_delta(const void* dout, const void* out, float* delta, int64_t rows, int D, int sms, cudaStream_t s) {
+    const T* a = static_cast<const T*>(dout);
+    const T* b = static_cast<const T*>(out);
+    if (D <= 64) sdpa_bwd_delta_kernel<T, 8><<<sms * 8, 256, 0, s>>>(a, b, delta, rows, D);
+    else if (D <= 128) sdpa_bwd_delta_kernel<T, 16><<<sms * 8, 256, 0, s>>>(a, b, delta, rows, D);
+    else sdpa_bwd_delta_kernel<T, 32><<<sms * 8, 256, 0, s>>>(a, b, delta, rows, D);
 }
 
 }  // namespace
@@ -105,12 +122,8 @@ extern "C" int paras_b200_sdpa_bwd(const paras_sdpa_bwd_args* a) {
     const int sms = g->sm_count > 0 ? g->sm_count : 148;
     const float scale = float(a->scale);
     auto run = [&]() -> int {
-        if (a->dtype == PARAS_BF16)
-            sdpa_bwd_delta_kernel<__nv_bfloat16><<<sms * 8, 256, 0, s>>>(
-                static_cast<const __nv_bfloat16*>(a->dout), static_cast<const __nv_bfloat16*>(a->out), delta, rows, a->D);
-        else
-            sdpa_bwd_delta_kernel<__half><<<sms * 8, 256, 0, s>>>(
-                static_cast<const __half*>(a->dout), static_cast<const __half*>(a->out), delta, rows, a->D);
+        if (a->dtype == PARAS_BF16) launch_delta<__nv_bfloat16>(a->dout, a->out, delta, rows, a->D, sms, s);
+        else launch_delta<__half>(a->dout, a->out, delta, rows, a->D, sms, s);
         PB_LAUNCH_CHECK("sdpa_bwd_delta_kernel");
         for (int64_t g0 = 0; g0 < groups; g0 += chunk) {
             const int64_t n = std::min(chunk, groups - g0);
