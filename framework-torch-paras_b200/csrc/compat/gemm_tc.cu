@@ -63,8 +63,6 @@ constexpr int kSmemTotal = kSmemMisc + 16;
 
 enum { kEpiNone = 0, kEpiBias = 1, kEpiSwiglu = 2, kEpiProb = 3, kEpiDs = 4 };  // 3, 4: attention backward only
 
-__device__ int g_gemm_abort_latch = 0;
-
 struct GemmParams {
     int M, N, K;          // N = output columns (for SwiGLU: F)
     int batch;
@@ -170,11 +168,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     constexpr int kRing = EPI >= kEpiProb ? kStages - 1 : kStages;  // stages of the operand ring in use
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    if (*reinterpret_cast<volatile int*>(&g_gemm_abort_latch)) return;  // uniform: before any barrier or TMEM use
     if (smem_base & 1023u) {
         // the 128-byte swizzle of TMA and of the MMA descriptors assumes 1024-byte aligned tiles
         if (threadIdx.x == 0) {
-            g_gemm_abort_latch = 1;
             *p.status = int(0x40000000u | (1u << 29));
             __threadfence_system();
         }
@@ -537,7 +533,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         tmem_dealloc(tmem, kTmemCols);
     }
     if (threadIdx.x == 0 && *abort_flag) {
-        g_gemm_abort_latch = 1;
         *p.status = *abort_flag;
         __threadfence_system();
     }
@@ -600,11 +595,7 @@ int gemm_run(const paras_gemm_args* a, const GemmExtra* ex) {
         (a->batch > 1 && (a->stride_a % 8 || a->stride_b % 8 || a->stride_c % 8)))
         return fail(PARAS_E_UNSUPPORTED, "paras gemm: pointers or strides are not 16-byte aligned");
     if (g->smem_optin < size_t(kSmemTotal)) return fail(PARAS_E_UNSUPPORTED, "paras gemm: not enough shared memory");
-    if ((st = check_status_word(g)) != PARAS_OK) {
-        const int zero = 0;
-        cudaMemcpyToSymbol(g_gemm_abort_latch, &zero, sizeof(int));
-        return st;
-    }
+    if ((st = check_status_word(g)) != PARAS_OK) return st;
 
     const bool kn = a->b_layout == PARAS_GEMM_B_KN;
     const bool at = a->a_layout == PARAS_GEMM_A_KM;

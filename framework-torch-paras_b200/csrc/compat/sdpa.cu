@@ -73,6 +73,18 @@ using pb::Gpu;
 
 extern "C" {
 
+int paras_b200_sdpa_split_layout(int64_t rows, int32_t D, int32_t splits, size_t* ml_offset,
+                                 size_t* o_offset, size_t* bytes) {
+    if (rows < 0 || D < 0 || splits < 1) return fail(PARAS_E_INVALID, "paras sdpa: bad split layout request");
+    // carve an imaginary scratch at a 16-byte aligned address and report the distances from it
+    const uintptr_t base = 1u << 20;
+    const pb::SplitWorkspace w = pb::carve_workspace(reinterpret_cast<void*>(base), rows, D, splits);
+    if (ml_offset) *ml_offset = splits > 1 ? reinterpret_cast<uintptr_t>(w.ml_part) - base : 0;
+    if (o_offset) *o_offset = splits > 1 ? reinterpret_cast<uintptr_t>(w.o_part) - base : 0;
+    if (bytes) *bytes = pb::split_workspace_bytes(rows, D, splits);
+    return PARAS_OK;
+}
+
 int paras_b200_sdpa_workspace_bytes(const paras_sdpa_args* a, size_t* bytes) {
     if (!bytes) return fail(PARAS_E_INVALID, "paras sdpa: null output");
     *bytes = 0;

@@ -14,18 +14,25 @@ struct SplitWorkspace {
     int splits = 1;
 };
 
+// Layout: ml_part first (8-byte entries), then o_part at the next multiple of 16 bytes.  With
+// the base 16-byte aligned both parts are aligned for their access width (float2 / float)
+// whatever rows, D and splits are -- odd D with an odd number of splits included.
+inline size_t split_ml_bytes(int64_t rows, int splits) {
+    return (size_t(splits) * size_t(rows) * sizeof(float2) + 15u) & ~size_t(15);
+}
+
 inline size_t split_workspace_bytes(int64_t rows, int D, int splits) {
     if (splits <= 1) return 0;
-    // o_part then ml_part; both 16-byte aligned as long as the base is
-    return size_t(splits) * size_t(rows) * (size_t(D) * sizeof(float) + sizeof(float2));
+    return split_ml_bytes(rows, splits) + size_t(splits) * size_t(rows) * size_t(D) * sizeof(float);
 }
 
 inline SplitWorkspace carve_workspace(void* base, int64_t rows, int D, int splits) {
     SplitWorkspace w;
     w.splits = splits;
+    (void)D;
     if (splits > 1) {
-        w.o_part = static_cast<float*>(base);
-        w.ml_part = reinterpret_cast<float2*>(w.o_part + size_t(splits) * rows * D);
+        w.ml_part = static_cast<float2*>(base);
+        w.o_part = reinterpret_cast<float*>(static_cast<char*>(base) + split_ml_bytes(rows, splits));
     }
     return w;
 }

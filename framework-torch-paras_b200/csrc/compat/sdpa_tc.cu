@@ -92,10 +92,6 @@ constexpr int kSmemMisc = kSmemBars + kNumBars * 8;   // tmem base word, abort f
 constexpr int kSmemTotal = kSmemMisc + 16;
 constexpr int kSmemLaunch = kSmemTotal + 1024;        // slack to align the base to 1024 B
 
-// Set by any CTA whose bounded wait ran out; later CTAs of the same (already failed) launch
-// see it and leave at once, so a broken launch costs one wave of timeouts, not one per CTA.
-__device__ int g_abort_latch = 0;
-
 struct TcParams {
     void* out;
     float* lse;
@@ -173,7 +169,6 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     constexpr int kChunks = HD / 64;                 // 64-element slabs of the head dim
     constexpr uint32_t kLoadBytes = kChunks * kChunkBytes;   // bytes one Q / K / V tile brings in
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    if (*reinterpret_cast<volatile int*>(&g_abort_latch)) return;  // uniform: before any barrier or TMEM use
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < kNumBars; ++i) {
@@ -584,8 +579,9 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         tmem_dealloc(tmem, kTmemCols);
     }
     if (threadIdx.x == 0 && *abort_flag) {
-        g_abort_latch = 1;
-        *p.status = *abort_flag;  // 0x40000000 | one bit per wait that was still pending
+        // 0x40000000 | one bit per wait that was still pending.  The grid is persistent (one wave),
+        // so a broken launch costs every CTA one time limit in parallel, not one after another.
+        *p.status = *abort_flag;
         __threadfence_system();
     }
 }
@@ -626,13 +622,8 @@ bool sdpa_tc_supported(const Gpu* g, const paras_sdpa_args& a, const char** why)
 }
 
 int sdpa_tc_launch(Gpu* g, const paras_sdpa_args& a, float scale, cudaStream_t s) {
-    int st = check_status_word(g);
-    if (st != PARAS_OK) {
-        // report the earlier failure once and re-arm the kernel
-        const int zero = 0;
-        cudaMemcpyToSymbol(g_abort_latch, &zero, sizeof(int));
-        return st;
-    }
+    int st = check_status_word(g);  // an earlier launch's failure is reported once, here
+    if (st != PARAS_OK) return st;
     CUtensorMap mq, mk, mv, mo;
     if ((st = make_map(&mq, a.q, a.dtype, a.B, a.Hq, a.Lq, a.D, a.q_strides)) != PARAS_OK) return st;
     if ((st = make_map(&mk, a.k, a.dtype, a.B, a.Hkv, a.Lk, a.D, a.k_strides)) != PARAS_OK) return st;

@@ -56,7 +56,8 @@ constexpr uint64_t kWaitLimitNs = 200000000ull;  // 0.2 s: orders of magnitude a
 
 template <int SLEEP_NS = 0>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
-                                          volatile int* abort_flag, int tag = 0) {
+                                          volatile int* abort_flag, int tag = 0,
+                                          uint64_t limit_ns = kWaitLimitNs) {
     // Plain polling first (each try_wait already blocks for a hardware time slice); the
     // clock and the abort flag are only consulted once a wait has become unusually long.
     // `tag` (0..30) names the wait: every wait that was still pending when the CTA gave up
@@ -73,7 +74,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
     while (!mbar_try_wait(bar, parity)) {
         if constexpr (SLEEP_NS > 0) __nanosleep(SLEEP_NS);
         if ((++polls & 0xffu) == 0) {
-            if (*abort_flag || global_timer_ns() - t0 > kWaitLimitNs) {
+            if (*abort_flag || global_timer_ns() - t0 > limit_ns) {
                 atomicOr(const_cast<int*>(abort_flag), int(0x40000000u | (1u << tag)));
                 return false;
             }

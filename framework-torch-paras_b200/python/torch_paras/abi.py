@@ -35,6 +35,7 @@ EXPORTS = [
     "paras_b200_sdpa_fwd_static_scratch", "paras_b200_sdpa_static_scratch_bytes",
     "paras_b200_rmsnorm_bwd", "paras_b200_swiglu_fwd", "paras_b200_swiglu_bwd",
     "paras_b200_rotate_half", "paras_b200_gemm", "paras_b200_sdpa_fwd_host", "paras_b200_sdpa_bwd",
+    "paras_b200_sdpa_split_layout", "paras_b200_selftest_bounded_wait",
 ]
 
 
@@ -116,6 +117,9 @@ def lib() -> C.CDLL:
         L.paras_b200_host_alloc.argtypes = [C.c_size_t, C.POINTER(C.c_void_p)]
         L.paras_b200_host_free.argtypes = [C.c_void_p]
         L.paras_b200_host_is_pinned.argtypes = [C.c_void_p]
+        L.paras_b200_sdpa_split_layout.argtypes = [C.c_int64, C.c_int32, C.c_int32, C.POINTER(C.c_size_t),
+                                                   C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)]
+        L.paras_b200_selftest_bounded_wait.argtypes = [C.c_int, C.c_uint32, C.POINTER(C.c_int)]
         _lib = L
     return _lib
 
@@ -306,6 +310,20 @@ def sdpa_workspace_bytes(q, k, v, *, causal=False, flags=0) -> int:
     n = C.c_size_t(0)
     check(lib().paras_b200_sdpa_workspace_bytes(C.byref(a), C.byref(n)))
     return int(n.value)
+
+
+def sdpa_split_layout(rows: int, D: int, splits: int):
+    """(ml_offset, o_offset, bytes) of the split-KV scratch; host arithmetic, needs no GPU."""
+    ml, o, n = C.c_size_t(0), C.c_size_t(0), C.c_size_t(0)
+    check(lib().paras_b200_sdpa_split_layout(rows, D, splits, C.byref(ml), C.byref(o), C.byref(n)))
+    return int(ml.value), int(o.value), int(n.value)
+
+
+def selftest_bounded_wait(gpu: int, limit_us: int = 1000):
+    """Runs the bounded-wait self-test kernel; returns (status code, raw status word)."""
+    word = C.c_int(0)
+    st = lib().paras_b200_selftest_bounded_wait(gpu, limit_us, C.byref(word))
+    return int(st), int(word.value)
 
 
 def sdpa_last_kernel() -> str:

@@ -156,6 +156,15 @@ int paras_b200_sdpa_workspace_bytes(const paras_sdpa_args* args, size_t* bytes);
  * ("tcgen05", "simt", "decode_mma", ...); for tests and logs. */
 const char* paras_b200_sdpa_last_kernel(void);
 
+/* Layout of the split-KV scratch for `splits` > 1 partial results over `rows` = B*Hq*Lq query
+ * rows of D elements: byte offsets of the {max, sum} pairs (8-byte entries) and of the fp32
+ * partial outputs inside the scratch, and its total size (what paras_b200_sdpa_workspace_bytes
+ * reports once the kernel and the number of splits are chosen).  Host arithmetic only; needs no
+ * GPU.  Both offsets are multiples of 16 for every rows, D and splits.  (The reference has no
+ * split-KV path; its scratch is the [B,H,Lq,Lk] score tensor of attention_ops.cpp:101.) */
+int paras_b200_sdpa_split_layout(int64_t rows, int32_t D, int32_t splits, size_t* ml_offset,
+                                 size_t* o_offset, size_t* bytes);
+
 /* The same attention on HOST-resident operands: q, k, v and out are host pointers ([B,H,L,D],
  * every batch element a dense [H,L,D] block; strides[0] may be larger).  The call moves batch
  * chunks (about 64 MB of operands each: batch elements, or head groups of one) through the GPU as a three-stage pipeline on three
@@ -285,6 +294,17 @@ typedef struct paras_gemm_args {
     int32_t reserved;
 } paras_gemm_args;
 int paras_b200_gemm(const paras_gemm_args* args);
+
+/* ---- failure path self-test ----
+ * No counterpart in the reference (its kernels have no device-side waits; a stuck queue there
+ * hangs the process in Queue::synchronize, csrc/compat/paras_compat.cpp:354-364).  Launches a
+ * one-warp kernel on the library's stream of `gpu` whose single bounded wait -- the same
+ * primitive every tensor-core kernel here waits with -- is on a barrier nobody arrives at, with
+ * a limit of `limit_us` microseconds (1..1000000).  The wait gives up, the kernel returns by
+ * itself and the call returns what any later call would after a production kernel gave up:
+ * PARAS_E_TIMEOUT, once; `status_word` (optional) receives the raw word the kernel wrote
+ * (0x40000000 | 1 << 27).  The GPU and the library stay usable afterwards. */
+int paras_b200_selftest_bounded_wait(int gpu, uint32_t limit_us, int* status_word);
 
 #ifdef __cplusplus
 }

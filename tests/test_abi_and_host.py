@@ -69,6 +69,19 @@ def test_argument_validation_comes_before_device_use():
     assert lib.paras_b200_rotate_half(0, buf, buf, 1, 3, abi.F32, 0, None) == -1
 
 
+def test_split_kv_scratch_parts_are_aligned_for_every_shape():
+    # the {max, sum} pairs are read and written as 8-byte float2, the partial outputs as fp32;
+    # odd head dims with odd split counts must not push either part off its alignment
+    for rows in (1, 2, 3, 5, 7, 63, 64, 1000, 4097):
+        for D in (1, 3, 63, 64, 65, 127, 128, 255, 256):
+            for splits in (2, 3, 5, 7, 8, 33):
+                ml, o, n = abi.sdpa_split_layout(rows, D, splits)
+                assert ml % 16 == 0 and o % 16 == 0, (rows, D, splits, ml, o)
+                assert o >= ml + 8 * rows * splits            # the parts do not overlap
+                assert n >= o + 4 * rows * splits * D         # and the total covers both
+    assert abi.sdpa_split_layout(5, 63, 1) == (0, 0, 0)       # one split needs no scratch
+
+
 def test_device_numbering_and_host_device():
     assert torch_paras.device_count() == 1 + torch_paras.gpu_count()
     assert torch_paras.device_name(0) == "host"

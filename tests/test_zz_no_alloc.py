@@ -3,12 +3,9 @@
 It exists for callers that cannot allocate device memory at call time -- e.g. a serving
 process that handed the whole GPU to its own memory manager at start-up, or a decode loop
 with no latency budget for an allocator call.  Its split-KV scratch is a fixed array inside
-the library, so the checks here are: same result as the regular entry point, twice in a row
-(the array is shared between calls and keeps the previous call's contents), and a clear
-refusal when a problem's partial results do not fit the array.
-
-Collected last on purpose (file name): a run that stops at the first failure has then already
-run every other test.
+the library, so the checks here are: same result as the regular entry point and as the CPU
+oracle, twice in a row (the array is shared between calls and keeps the previous call's
+contents), and a clear refusal when a problem's partial results do not fit the array.
 """
 import ctypes
 
@@ -17,6 +14,7 @@ import torch
 
 import torch_paras  # noqa: F401
 from torch_paras import abi
+from oracle import oracle as O
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
@@ -38,7 +36,12 @@ def test_static_scratch_matches_regular_entry_point_twice(dtype, tol):
         assert abi.sdpa_last_kernel() == "simt_splitkv_static"   # the scratch really was used
         want = abi.sdpa_fwd(q, k, v, flags=abi.SDPA_REF_SCALE)
         err = (out.float() - want.float()).abs().max().item()
-        assert err <= tol, f"call {call}: max-abs {err} > {tol}"
+        assert err <= tol, f"call {call}: max-abs {err} > {tol} against the regular entry point"
+        # for fp32 the regular entry point runs the same kernel (with pool scratch), so the
+        # independent expectation is the oracle: the reference's arithmetic on the host
+        gold = O.sdpa(q.cpu(), k.cpu(), v.cpu(), enable_gqa=True)
+        err = (out.cpu().double() - gold.double()).abs().max().item()
+        assert err <= tol, f"call {call}: max-abs {err} > {tol} against the oracle"
         assert torch.isfinite(out.float()).all()
         outs.append(out)
     assert not torch.equal(outs[0], outs[1])    # different inputs gave different results
@@ -50,6 +53,8 @@ def test_static_scratch_causal_prefill_shape_needs_no_scratch():
     out = abi.sdpa_fwd_static_scratch(q, q, q, causal=True)
     want = abi.sdpa_fwd(q, q, q, causal=True)
     assert (out - want).abs().max().item() <= 1e-4
+    gold = O.sdpa(q.cpu(), q.cpu(), q.cpu(), is_causal=True)
+    assert (out.cpu() - gold).abs().max().item() <= 1e-4
 
 
 def test_static_scratch_rejects_what_does_not_fit():
