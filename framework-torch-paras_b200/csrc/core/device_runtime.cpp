@@ -137,7 +137,34 @@ public:
         PARAS_ABI(paras_b200_host_alloc(cls, &p));
         return p;
     }
+    // blocks in use, for note_async_read(): start address -> size class
+    void track(void* p, size_t cls) {
+        std::lock_guard<std::mutex> lk(mu_);
+        live_[p] = cls;
+    }
+    void note_async_read(const void* ptr, int gpu) {
+        if (gpu < 0 || gpu >= 64) return;
+        std::lock_guard<std::mutex> lk(mu_);
+        auto it = live_.upper_bound(const_cast<void*>(ptr));
+        if (it == live_.begin()) return;
+        --it;
+        const char* base = static_cast<const char*>(it->first);
+        if (static_cast<const char*>(ptr) < base + it->second) in_flight_[it->first] |= uint64_t(1) << gpu;
+    }
     void give(void* p, size_t cls) {
+        uint64_t gpus = 0;
+        {
+            std::lock_guard<std::mutex> lk(mu_);
+            live_.erase(p);
+            auto it = in_flight_.find(p);
+            if (it != in_flight_.end()) {
+                gpus = it->second;
+                in_flight_.erase(it);
+            }
+        }
+        // queued non-blocking copies may still have to read the block: let them finish first
+        for (int g = 0; gpus; ++g, gpus >>= 1)
+            if (gpus & 1) paras_b200_synchronize(g);
         std::lock_guard<std::mutex> lk(mu_);
         free_[cls].push_back(p);
         cached_ += cls;
@@ -167,6 +194,8 @@ private:
     }
     std::mutex mu_;
     std::map<size_t, std::vector<void*>> free_;
+    std::map<void*, size_t> live_;
+    std::map<void*, uint64_t> in_flight_;
     size_t cached_ = 0;
 };
 
@@ -188,6 +217,7 @@ public:
         if (nbytes == 0) return c10::DataPtr(nullptr, nullptr, &delete_pinned, c10::Device(c10::kCPU));
         size_t cls = 0;
         void* p = PinnedCache::get().take(nbytes, &cls);
+        PinnedCache::get().track(p, cls);
         return c10::DataPtr(p, new PinnedRecord{p, cls}, &delete_pinned, c10::Device(c10::kCPU));
     }
     c10::DeleterFnPtr raw_deleter() const override { return nullptr; }
@@ -221,6 +251,7 @@ HooksRegistrar g_hooks_registrar;
 REGISTER_ALLOCATOR(kDevice, &g_allocator);
 
 c10::Allocator* device_allocator() { return &g_allocator; }
+void note_pinned_async_read(const void* ptr, int gpu) { PinnedCache::get().note_async_read(ptr, gpu); }
 c10::Device current_device() { return tl_device; }
 
 Runtime::Runtime() {

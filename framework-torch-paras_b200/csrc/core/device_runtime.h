@@ -88,6 +88,11 @@ private:
 };
 
 c10::Allocator* device_allocator();
+// A non-blocking host-to-GPU copy is about to read `ptr` on GPU ordinal `gpu`.  If `ptr` lies in
+// a block of the cached pinned allocator, the block is not handed out again before that GPU's
+// stream has drained (the freeing thread waits for it), so a later pin_memory() cannot
+// overwrite bytes a queued DMA has yet to read.
+void note_pinned_async_read(const void* ptr, int gpu);
 // thread-local current device (csrc/core/registration.cpp:34)
 c10::Device current_device();
 

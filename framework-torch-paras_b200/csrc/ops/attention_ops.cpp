@@ -13,6 +13,7 @@
 // top-level registration keeps PyTorch from pre-converting a bool mask into an additive one.
 // Dropout is not part of the fused path and raises.
 #include <torch/library.h>
+#include <torch/csrc/autograd/custom_function.h>
 
 #include <cmath>
 #include <cstdlib>
@@ -99,8 +100,16 @@ Tensor sdpa_forward(const Tensor& query, const Tensor& key, const Tensor& value,
         else if (mask.scalar_type() == query.scalar_type()) a.mask_kind = 2;
         else if (mask.scalar_type() == c10::kFloat) a.mask_kind = 3;
         else { mask = mask.to(query.scalar_type()); a.mask_kind = 2; }
-        while (mask.dim() < 4) mask = mask.unsqueeze(0);
-        if (mask.dim() > 4) mask = mask.reshape({-1, mask.size(-3), mask.size(-2), mask.size(-1)});
+        // The reference adds the mask to scores of shape (..., Lq, Lk) (attention_ops.cpp:117-126), so
+        // it broadcasts from the right against the query's own leading dims; only then does the mask
+        // follow the query into [B, H, Lq, Lk] (a 3-D query's [B, Lq, Lk] mask is per batch element).
+        std::vector<int64_t> score_shape(query.sizes().begin(), query.sizes().end() - 1);
+        score_shape.push_back(Lk);
+        TORCH_CHECK(mask.dim() <= int64_t(score_shape.size()),
+                    "paras sdpa: attn_mask has more dimensions than the attention scores");
+        mask = mask.expand(score_shape);
+        if (query.dim() == 3) mask = mask.unsqueeze(1);
+        else if (query.dim() > 4) mask = mask.reshape({-1, Hq, Lq, Lk});
         mask = mask.expand({B, Hq, Lq, Lk});
         a.mask = mask.data_ptr();
         for (int i = 0; i < 4; ++i) a.mask_strides[i] = mask.stride(i);
@@ -212,12 +221,77 @@ std::tuple<Tensor, Tensor, Tensor> sdpa_backward(const Tensor& grad_out, const T
     return {dq, dk, dv};
 }
 
+// ---- autograd for F.scaled_dot_product_attention on `paras` tensors ----------------------
+// The reference's sdpa_math is built from at:: operators, so autograd differentiates through it
+// (attention_ops.cpp:71-136).  A fused kernel registered for the backend replaces that
+// composite for the autograd key too, so the gradient has to be tied on explicitly: when any of
+// q, k, v requires grad the call goes to the differentiable pair sdpa_train_forward /
+// sdpa_backward; what that pair does not cover raises instead of returning a result without a
+// grad_fn.
+struct SdpaFunction : public torch::autograd::Function<SdpaFunction> {
+    static Tensor forward(torch::autograd::AutogradContext* ctx, const Tensor& q, const Tensor& k,
+                          const Tensor& v, bool is_causal, std::optional<double> scale) {
+        auto [out, lse] = sdpa_train_forward(q, k, v, is_causal, scale);
+        ctx->save_for_backward({q, k, v, out, lse});
+        ctx->saved_data["is_causal"] = is_causal;
+        ctx->saved_data["has_scale"] = scale.has_value();
+        ctx->saved_data["scale"] = scale.value_or(0.0);
+        return out;
+    }
+    static torch::autograd::variable_list backward(torch::autograd::AutogradContext* ctx,
+                                                   torch::autograd::variable_list grads) {
+        const auto saved = ctx->get_saved_variables();
+        std::optional<double> scale;
+        if (ctx->saved_data["has_scale"].toBool()) scale = ctx->saved_data["scale"].toDouble();
+        auto [dq, dk, dv] = sdpa_backward(grads[0], saved[0], saved[1], saved[2], saved[3], saved[4],
+                                          ctx->saved_data["is_causal"].toBool(), scale);
+        return {dq, dk, dv, Tensor(), Tensor()};
+    }
+};
+
+Tensor sdpa_autograd(const Tensor& query, const Tensor& key, const Tensor& value,
+                     const std::optional<Tensor>& attn_mask, double dropout_p, bool is_causal,
+                     std::optional<double> scale, bool enable_gqa) {
+    const bool needs_grad = at::GradMode::is_enabled() &&
+                            (query.requires_grad() || key.requires_grad() || value.requires_grad());
+    if (!needs_grad) {
+        at::AutoDispatchBelowADInplaceOrView below;
+        return at::scaled_dot_product_attention(query, key, value, attn_mask, dropout_p, is_causal, scale,
+                                                enable_gqa);
+    }
+    const bool has_mask = attn_mask.has_value() && attn_mask->defined();
+    TORCH_CHECK(!has_mask && dropout_p == 0.0,
+                "paras sdpa: the gradient of the fused attention covers is_causal / full attention without "
+                "attn_mask and dropout; detach the inputs or drop the mask");
+    TORCH_CHECK(query.scalar_type() == c10::kBFloat16 || query.scalar_type() == c10::kHalf,
+                "paras sdpa: the gradient of the fused attention needs bfloat16 or float16 tensors, got ",
+                query.scalar_type());
+    TORCH_CHECK(query.dim() >= 3 && key.dim() == query.dim() && value.dim() == query.dim(),
+                "paras sdpa: query, key and value must have the same rank (>= 3)");
+    Tensor q = query, k = key, v = value;
+    if (q.dim() == 3) { q = q.unsqueeze(1); k = k.unsqueeze(1); v = v.unsqueeze(1); }
+    else if (q.dim() > 4) {
+        q = q.reshape({-1, q.size(-3), q.size(-2), q.size(-1)});
+        k = k.reshape({-1, k.size(-3), k.size(-2), k.size(-1)});
+        v = v.reshape({-1, v.size(-3), v.size(-2), v.size(-1)});
+    }
+    TORCH_CHECK(k.size(1) == q.size(1) || enable_gqa, "paras sdpa: key/value have ", k.size(1),
+                " heads but query has ", q.size(1), "; pass enable_gqa=True for grouped-query attention");
+    Tensor out = SdpaFunction::apply(q, k, v, is_causal, scale);
+    if (query.dim() == 3) return out.squeeze(1);
+    if (query.dim() > 4) return out.reshape(query.sizes());
+    return out;
+}
+
 }  // namespace
 }  // namespace paras
 
 TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
     m.impl("aten::_scaled_dot_product_attention_math", &paras::sdpa_math);
     m.impl("aten::scaled_dot_product_attention", &paras::sdpa);
+}
+TORCH_LIBRARY_IMPL(aten, AutogradPrivateUse1, m) {
+    m.impl("aten::scaled_dot_product_attention", &paras::sdpa_autograd);
 }
 
 TORCH_LIBRARY_FRAGMENT(paras, m) {

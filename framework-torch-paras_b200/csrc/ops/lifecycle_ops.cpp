@@ -165,6 +165,7 @@ Tensor copy_from(const Tensor& self, const Tensor& dst, bool non_blocking) {
         if (staged.scalar_type() != dst.scalar_type()) staged = staged.to(dst.scalar_type());
         staged = staged.contiguous();
         if (dst.is_contiguous()) {
+            if (non_blocking) note_pinned_async_read(staged.data_ptr(), gpu);
             PARAS_ABI(paras_b200_memcpy_h2d(gpu, dst.data_ptr(), staged.data_ptr(), dst.nbytes(),
                                             nullptr, non_blocking ? 0 : 1));
         } else {

@@ -182,8 +182,29 @@ Tensor swiglu_linear(const Tensor& x, const Tensor& w_gate, const Tensor& w_up) 
     return out.reshape(shape);
 }
 
+// aten::linear with inputs that require grad: as a product autograd knows (matmul -> mm / bmm,
+// whose derivative formulas call mm on this device again), like the reference's own
+// differentiable linear (vision_ops.cpp:248-309).  Without grad the fused kernel runs.
+Tensor linear_autograd(const Tensor& input, const Tensor& weight, const std::optional<Tensor>& bias) {
+    const bool has_bias = bias.has_value() && bias->defined();
+    const bool needs_grad = at::GradMode::is_enabled() &&
+                            (input.requires_grad() || weight.requires_grad() || (has_bias && bias->requires_grad()));
+    if (!needs_grad) {
+        at::AutoDispatchBelowADInplaceOrView below;
+        return at::linear(input, weight, bias);
+    }
+    TORCH_CHECK(weight.dim() == 2, "paras linear: weight must be [out_features, in_features]");
+    Tensor x2d = input.reshape({-1, input.size(-1)});
+    Tensor out = has_bias ? at::addmm(*bias, x2d, weight.t()) : at::mm(x2d, weight.t());
+    auto shape = input.sizes().vec();
+    shape.back() = weight.size(0);
+    return out.reshape(shape);
+}
+
 }  // namespace
 }  // namespace paras
+
+TORCH_LIBRARY_IMPL(aten, AutogradPrivateUse1, m) { m.impl("aten::linear", &paras::linear_autograd); }
 
 TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
     m.impl("aten::mm", &paras::mm);

@@ -13,6 +13,7 @@
 // tensor dtype after every step in the reference; the kernels reproduce that
 // (PARAS_ROUND_PER_OP) so 16-bit results agree.
 #include <torch/library.h>
+#include <torch/csrc/autograd/custom_function.h>
 
 #include "core/device_runtime.h"
 
@@ -174,10 +175,55 @@ Tensor rotate_half_backward(const Tensor& grad_out) {
     return rotate_half_impl(grad_out, 1, "rotate_half_backward");
 }
 
+// ---- autograd for F.rms_norm on `paras` tensors -------------------------------------------
+// The reference's aten::rms_norm is a composition of at:: operators that autograd follows
+// (rms_swiglu_ops.cpp:66-73).  With a fused backend kernel in its place the gradient is tied on
+// here: inputs that require grad go through paras::rms_norm + paras::rms_norm_backward
+// (fused_ops.cpp:43-157), over the trailing normalized_shape dims flattened into one.
+struct RmsNormFunction : public torch::autograd::Function<RmsNormFunction> {
+    static Tensor forward(torch::autograd::AutogradContext* ctx, const Tensor& x2d, const Tensor& w, double eps) {
+        auto [out, rstd] = rms_norm_fused(x2d, w, eps);
+        ctx->save_for_backward({x2d, w, rstd});
+        return out;
+    }
+    static torch::autograd::variable_list backward(torch::autograd::AutogradContext* ctx,
+                                                   torch::autograd::variable_list grads) {
+        const auto saved = ctx->get_saved_variables();
+        auto [gx, gw] = rms_norm_backward(grads[0], saved[0], saved[1], saved[2]);
+        return {gx, gw, Tensor()};
+    }
+};
+
+Tensor rms_norm_autograd(const Tensor& input, at::IntArrayRef normalized_shape,
+                         const std::optional<Tensor>& weight, std::optional<double> eps) {
+    const bool has_w = weight.has_value() && weight->defined();
+    const bool needs_grad = at::GradMode::is_enabled() &&
+                            (input.requires_grad() || (has_w && weight->requires_grad()));
+    if (!needs_grad) {
+        at::AutoDispatchBelowADInplaceOrView below;
+        return at::rms_norm(input, normalized_shape, weight, eps);
+    }
+    const int64_t nd = int64_t(normalized_shape.size());
+    TORCH_CHECK(nd >= 1 && input.dim() >= nd, "paras rms_norm: normalized_shape does not fit the input");
+    int64_t H = 1;
+    for (int64_t i = 0; i < nd; ++i) {
+        TORCH_CHECK(input.size(input.dim() - nd + i) == normalized_shape[i],
+                    "paras rms_norm: normalized_shape does not match the trailing dims of input");
+        H *= normalized_shape[i];
+    }
+    if (has_w)
+        TORCH_CHECK(weight->sizes().equals(normalized_shape),
+                    "paras rms_norm: weight shape must equal normalized_shape");
+    Tensor w = has_w ? weight->reshape({H}) : at::ones({H}, input.options());
+    Tensor out = RmsNormFunction::apply(input.reshape({-1, H}), w, eps.value_or(1e-6));
+    return out.reshape(input.sizes());
+}
+
 }  // namespace
 }  // namespace paras
 
 TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) { m.impl("aten::rms_norm", &paras::rms_norm_aten); }
+TORCH_LIBRARY_IMPL(aten, AutogradPrivateUse1, m) { m.impl("aten::rms_norm", &paras::rms_norm_autograd); }
 
 TORCH_LIBRARY_FRAGMENT(torch_paras, m) { m.def("swiglu(Tensor x, Tensor gate) -> Tensor"); }
 TORCH_LIBRARY_IMPL(torch_paras, PrivateUse1, m) { m.impl("swiglu", &paras::swiglu_composite); }

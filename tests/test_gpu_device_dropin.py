@@ -126,6 +126,25 @@ def test_sdpa_bf16_llama_shape_hits_the_tensor_core_kernel():
                  F.scaled_dot_product_attention(*(qt.transpose(1, 2),) * 3, is_causal=True))
 
 
+def test_sdpa_masks_broadcast_from_the_right_for_3d_and_5d_queries():
+    g = torch.Generator().manual_seed(77)
+    # 3-D query (batch, seq, dim) with a per-batch mask [B, Lq, Lk]
+    q3, k3 = torch.randn(3, 10, 16, generator=g), torch.randn(3, 12, 16, generator=g)
+    m3 = torch.rand(3, 10, 12, generator=g) > 0.3
+    m3[:, :, 0] = True
+    assert_close(F.scaled_dot_product_attention(q3.to(DEV), k3.to(DEV), k3.to(DEV), attn_mask=m3.to(DEV)),
+                 F.scaled_dot_product_attention(q3, k3, k3, attn_mask=m3))
+    b3 = torch.randn(10, 12, generator=g)                     # shared additive mask
+    assert_close(F.scaled_dot_product_attention(q3.to(DEV), k3.to(DEV), k3.to(DEV), attn_mask=b3.to(DEV)),
+                 F.scaled_dot_product_attention(q3, k3, k3, attn_mask=b3))
+    # 5-D query (a, b, heads, seq, dim) with a mask that broadcasts over some leading dims only
+    q5, k5 = torch.randn(2, 3, 2, 6, 8, generator=g), torch.randn(2, 3, 2, 7, 8, generator=g)
+    m5 = torch.rand(3, 1, 6, 7, generator=g) > 0.3
+    m5[..., 0] = True
+    assert_close(F.scaled_dot_product_attention(q5.to(DEV), k5.to(DEV), k5.to(DEV), attn_mask=m5.to(DEV)),
+                 F.scaled_dot_product_attention(q5, k5, k5, attn_mask=m5))
+
+
 def test_sdpa_dropout_is_refused_not_emulated():
     q = torch.randn(1, 2, 8, 16).to(DEV)
     with pytest.raises(RuntimeError, match="dropout"):

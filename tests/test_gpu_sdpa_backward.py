@@ -11,6 +11,7 @@ import math
 
 import pytest
 import torch
+import torch.nn.functional as F
 
 import torch_paras
 from torch_paras import abi, nn as paras_nn
@@ -101,3 +102,62 @@ def test_unsupported_operands_raise():
     h = torch.randn(1, 2, 60, 128, device=CUDA).bfloat16()
     with pytest.raises(RuntimeError):
         abi.sdpa_bwd(h, h, h, h, h, torch.zeros(1, 2, 60, device=CUDA))           # key length not a multiple of 8
+
+
+def test_functional_ops_with_requires_grad_give_gradients_not_silence():
+    # F.scaled_dot_product_attention / F.rms_norm / F.linear on `paras` tensors that require grad:
+    # the reference differentiates through its composites, so the same Python calls must train here.
+    g = torch.Generator().manual_seed(47)
+    q = torch.randn(1, 4, 256, 128, generator=g).bfloat16()
+    k = torch.randn(1, 2, 256, 128, generator=g).bfloat16()
+    v = torch.randn(1, 2, 256, 128, generator=g).bfloat16()
+    dout = torch.randn(1, 4, 256, 128, generator=g).bfloat16()
+    qd, kd, vd = (t.to(DEV).requires_grad_(True) for t in (q, k, v))
+    out = F.scaled_dot_product_attention(qd, kd, vd, is_causal=True, enable_gqa=True)
+    assert out.grad_fn is not None
+    out.backward(dout.to(DEV))
+    wq, wk, wv = reference_grads(q, k, v, dout, True)
+    check(qd.grad, wq, "F.sdpa dq")
+    check(kd.grad, wk, "F.sdpa dk")
+    check(vd.grad, wv, "F.sdpa dv")
+    # without grad the same call is the plain fused forward, and gives the same values
+    with torch.no_grad():
+        plain = F.scaled_dot_product_attention(qd, kd, vd, is_causal=True, enable_gqa=True)
+    assert plain.grad_fn is None and torch.equal(plain.cpu(), out.detach().cpu())
+    # what the gradient does not cover raises instead of returning a result without grad_fn
+    with pytest.raises(RuntimeError, match="gradient of the fused attention"):
+        F.scaled_dot_product_attention(qd.float(), kd.float().repeat_interleave(2, 1),
+                                       vd.float().repeat_interleave(2, 1))
+    with pytest.raises(RuntimeError, match="gradient of the fused attention"):
+        F.scaled_dot_product_attention(qd, qd, qd, attn_mask=torch.ones(256, 256, dtype=torch.bool).to(DEV))
+
+    # rms_norm: fp32 (the reference's own test dtype) against CPU autograd
+    x = torch.randn(6, 5, 32, generator=g)
+    w = torch.randn(32, generator=g)
+    xr, wr = x.clone().requires_grad_(), w.clone().requires_grad_()
+    F.rms_norm(xr, (32,), wr, 1e-6).sum().backward()
+    xd, wd = x.to(DEV).requires_grad_(), w.to(DEV).requires_grad_()
+    y = F.rms_norm(xd, (32,), wd, 1e-6)
+    assert y.grad_fn is not None and y.shape == x.shape
+    y.sum().backward()
+    assert torch.allclose(xd.grad.cpu(), xr.grad, atol=1e-4, rtol=1e-4)
+    assert torch.allclose(wd.grad.cpu(), wr.grad, atol=1e-4, rtol=1e-4)
+    x2 = x.clone().requires_grad_()
+    F.rms_norm(x2, (5, 32)).sum().backward()          # two trailing dims, no weight
+    x2d = x.to(DEV).requires_grad_()
+    F.rms_norm(x2d, (5, 32)).sum().backward()
+    assert torch.allclose(x2d.grad.cpu(), x2.grad, atol=1e-4, rtol=1e-4)
+
+    # linear: bf16 on the tensor-core GEMM, gradients by mm on the device
+    a = torch.randn(3, 64, 256, generator=g).bfloat16()
+    wl = (torch.randn(128, 256, generator=g) * 0.05).bfloat16()
+    bl = torch.randn(128, generator=g).bfloat16()
+    ar, wlr, blr = (t.double().requires_grad_() for t in (a, wl, bl))
+    F.linear(ar, wlr, blr).sum().backward()
+    ad, wld, bld = (t.to(DEV).requires_grad_() for t in (a, wl, bl))
+    yl = F.linear(ad, wld, bld)
+    assert yl.grad_fn is not None and yl.shape == (3, 64, 128)
+    yl.sum().backward()
+    for got, want, name in ((ad.grad, ar.grad, "dx"), (wld.grad, wlr.grad, "dw"), (bld.grad, blr.grad, "db")):
+        err = (got.cpu().double() - want).abs().max().item()
+        assert err <= 2e-2 * max(1.0, want.abs().max().item()), f"linear {name}: {err}"
