@@ -51,7 +51,7 @@ import torch  # noqa: E402
 WORKLOAD = "config2: bf16 causal SDPA B=8 Hq=Hkv=32 S=2048 D=128 (Llama-style)"
 C2 = dict(B=8, Hq=32, Hkv=32, S=2048, D=128)
 # bounded CPU sample of config 2: one batch element, 16 of its 32 heads, full sequence
-CPU_SAMPLE = dict(B=1, H=16, S=2048, D=128)
+CPU_SAMPLE = dict(B=1, H=16, S=2048, D=128)   # used where the whole workload does not fit the time
 
 
 def sdpa_flops(B, Hq, Lq, Lk, D, causal):
@@ -125,6 +125,50 @@ class ClockSampler:
                 "reasons": sorted(self.reasons), "samples": len(self.samples)}
 
 
+TRAFFIC_FILE = os.path.join(ROOT, "profiles", "sdpa_tc_kernel_config2_dram_traffic.txt")
+
+
+def read_ncu_traffic():
+    """DRAM bytes of one launch of the headline kernel, from the text file `--ingest-ncu` wrote out
+    of an ncu capture (dram__bytes_read.sum + dram__bytes_write.sum); None when there is none."""
+    try:
+        vals = dict(line.split("=", 1) for line in open(TRAFFIC_FILE).read().split() if "=" in line)
+        return float(vals["dram_bytes_read"]) + float(vals["dram_bytes_write"])
+    except (OSError, KeyError, ValueError):
+        return None
+
+
+def ingest_ncu(csv_path: str):
+    """`ncu -i X.ncu-rep --page raw --csv > X.csv` of a capture of this bench's headline kernel ->
+    profiles/sdpa_tc_kernel_config2_dram_traffic.txt (key=value lines; mean over captured launches)."""
+    import csv
+    rows = list(csv.reader(open(csv_path)))
+    hdr = next(i for i, r in enumerate(rows) if "Kernel Name" in r)
+    names, units = rows[hdr], rows[hdr + 1]
+    col = {n: i for i, n in enumerate(names)}
+    mult = {"byte": 1.0, "Kbyte": 1e3, "Mbyte": 1e6, "Gbyte": 1e9, "ns": 1.0, "us": 1e3, "usecond": 1e3,
+            "ms": 1e6, "msecond": 1e6, "nsecond": 1.0, "%": 1.0, "": 1.0}
+    launches = [r for r in rows[hdr + 2:] if len(r) == len(names) and "sdpa_tc_kernel" in r[col["Kernel Name"]]]
+    if not launches:
+        raise SystemExit("no sdpa_tc_kernel launch in " + csv_path)
+
+    def mean(metric):
+        i = col[metric]
+        return sum(float(r[i].replace(",", "")) * mult.get(units[i], 1.0) for r in launches) / len(launches)
+
+    out = {"kernel": launches[0][col["Kernel Name"]].split("(")[0].replace(" ", ""), "launches": len(launches),
+           "dram_bytes_read": mean("dram__bytes_read.sum"), "dram_bytes_write": mean("dram__bytes_write.sum"),
+           "gpu_time_ns": mean("gpu__time_duration.sum")}
+    for extra_metric, key in (("sm__pipe_tensor_cycles_active.avg.pct_of_peak_sustained_elapsed", "tensor_pipe_pct"),
+                              ("gpu__dram_throughput.avg.pct_of_peak_sustained_elapsed", "dram_throughput_pct")):
+        if extra_metric in col:
+            out[key] = mean(extra_metric)
+    with open(TRAFFIC_FILE, "w") as f:
+        for k_, v_ in out.items():
+            f.write(f"{k_}={v_}\n")
+    print(open(TRAFFIC_FILE).read())
+
+
 def dist_env():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -135,28 +179,42 @@ def dist_env():
 # --------------------------------------------------------------------------------------
 # reference arm: the reference's CPU implementation on the host cores
 # --------------------------------------------------------------------------------------
-def cpu_sample_inputs():
+def host_cores() -> int:
+    """Cores this process may run on (torchrun sets OMP_NUM_THREADS=1 for its children: the CPU
+    arm must not inherit that, so the count is taken from the affinity mask)."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
+def cpu_inputs(shape):
     g = torch.Generator().manual_seed(1001)
-    s = CPU_SAMPLE
-    mk = lambda: torch.randn(s["B"], s["H"], s["S"], s["D"], generator=g).bfloat16()  # noqa: E731
+    mk = lambda: torch.randn(shape["B"], shape["H"], shape["S"], shape["D"], generator=g).bfloat16()  # noqa: E731
     return mk(), mk(), mk()
 
 
-def time_cpu_reference(repeat: int, warmup: int):
-    """Returns (seconds per pass list, kind, threads).  kind = "reference" when the unmodified
-    reference build is present, else "port" (the oracle restatement)."""
-    q, k, v = cpu_sample_inputs()
+def time_cpu_reference(shape, repeat: int, warmup: int):
+    """Times causal bf16 attention of `shape` on the host.  Returns (seconds per pass list, kind,
+    threads).  kind = "reference" when the unmodified reference build is present (run in a child
+    process with every core this process may use), else "port" (the oracle restatement)."""
+    q, k, v = cpu_inputs(shape)
+    cores = host_cores()
     ref_so = os.path.join(ROOT, "oracle", "_ref", "_C.so")
     if os.path.exists(ref_so):
         jobs = [{"op": "sdpa", "args": {"q": q, "k": k, "v": v, "is_causal": True},
                  "repeat": 1, "keep_out": False} for _ in range(warmup + repeat)]
+        env = dict(os.environ)
+        for key in ("OMP_NUM_THREADS", "MKL_NUM_THREADS", "PARAS_REF_THREADS"):
+            env[key] = str(cores)
         with tempfile.TemporaryDirectory() as td:
             torch.save(jobs, os.path.join(td, "j.pt"))
             subprocess.check_call([sys.executable, os.path.join(ROOT, "oracle", "ref_run.py"),
-                                   os.path.join(td, "j.pt"), os.path.join(td, "r.pt")])
+                                   os.path.join(td, "j.pt"), os.path.join(td, "r.pt")], env=env)
             res = torch.load(os.path.join(td, "r.pt"))
         return [r["seconds"] for r in res[warmup:]], "reference", res[0]["threads"]
     from oracle import oracle as O
+    torch.set_num_threads(cores)
     times = []
     for i in range(warmup + repeat):
         t0 = time.perf_counter()
@@ -166,29 +224,51 @@ def time_cpu_reference(repeat: int, warmup: int):
     return times, "port", torch.get_num_threads()
 
 
-def sample_desc():
-    s = CPU_SAMPLE
-    return (f"B={s['B']} H={s['H']} S={s['S']} D={s['D']} causal bf16 = "
-            f"{s['B'] * s['H']}/{C2['B'] * C2['Hq']} of the workload's (batch, head) units")
+FULL = dict(B=C2["B"], H=C2["Hq"], S=C2["S"], D=C2["D"])
+
+
+def sample_desc(shape):
+    if shape == FULL:
+        return (f"B={shape['B']} H={shape['H']} S={shape['S']} D={shape['D']} causal bf16 = the whole workload "
+                f"({shape['B'] * shape['H']}/{C2['B'] * C2['Hq']} (batch, head) units)")
+    return (f"B={shape['B']} H={shape['H']} S={shape['S']} D={shape['D']} causal bf16 = "
+            f"{shape['B'] * shape['H']}/{C2['B'] * C2['Hq']} of the workload's (batch, head) units")
+
+
+def choose_cpu_shape(passes: int, budget_s: float):
+    """The whole config-2 workload when `passes` passes of it fit `budget_s` on this box's cores
+    (estimated from one pass of the 16/256 sample), else the sample.  Returns (shape, estimate)."""
+    t, _, _ = time_cpu_reference(CPU_SAMPLE, 1, 0)
+    scale = (FULL["B"] * FULL["H"]) / (CPU_SAMPLE["B"] * CPU_SAMPLE["H"])
+    est_full = t[0] * scale
+    try:
+        mem_ok = os.sysconf("SC_PHYS_PAGES") * os.sysconf("SC_PAGE_SIZE") >= 24 << 30  # the reference peaks at about 9 GB on it
+    except (ValueError, OSError):
+        mem_ok = False
+    if mem_ok and passes * est_full <= budget_s:
+        return FULL, est_full
+    return CPU_SAMPLE, t[0]
 
 
 def run_reference_arm(args):
     rank, world, _ = dist_env()
     if rank != 0:
         return
-    times, kind, threads = time_cpu_reference(args.steps, args.warmup)
-    s = CPU_SAMPLE
-    fl = sdpa_flops(s["B"], s["H"], s["S"], s["S"], s["D"], True)
+    budget = float(os.environ.get("PARAS_REF_BUDGET_S", "600"))
+    shape, _ = choose_cpu_shape(args.steps + args.warmup, budget)
+    times, kind, threads = time_cpu_reference(shape, args.steps, args.warmup)
+    fl = sdpa_flops(shape["B"], shape["H"], shape["S"], shape["S"], shape["D"], True)
     total = sum(times)
     val = fl * len(times) / total / 1e12
+    step = "the whole workload per step" if shape == FULL else "bounded CPU sample: " + sample_desc(shape)
     line = {
         "impl": "reference", "metric": "sdpa_fwd_tflops", "value": val, "unit": "TFLOP/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": 1e3 * total / len(times), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "step": "bounded CPU sample: " + sample_desc()},
+        "config": {"workload": WORKLOAD, "step": step, "per_gpu_batch": shape["B"]},
         "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": threads, "kind": kind,
-                         "sample": sample_desc()},
+                         "sample": sample_desc(shape)},
         "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -275,14 +355,31 @@ def run_ours(args):
     ms_step = ms / steps
     tflops = world * flops / (ms_step * 1e-3) / 1e12
     per_gpu_tflops = tflops / world
+
+    # The same launch back to back for at least `--sustain-s` seconds: what the kernel holds once the
+    # power cap and the clock have settled (the K-step loop above is a few milliseconds: a burst).
+    sustained = None
+    if args.sustain_s > 0 and not args.quick and not args.only:
+        n_sus = max(steps, int(math.ceil(args.sustain_s * 1e3 / ms_step)))
+        with ClockSampler(local, period_s=0.02) as clk_s:
+            ms_s = max_over_ranks(timed_loop(step, n_sus, 1, barrier))
+        cs = clk_s.summary()
+        tf_s = flops / (ms_s / n_sus * 1e-3) / 1e12
+        sustained = {"value": world * tf_s, "unit": "TFLOP/s", "per_gpu": tf_s, "launches": n_sus,
+                     "seconds": ms_s * 1e-3, "ms_per_step": ms_s / n_sus,
+                     "peak": peaks["bf16_tflops_sustained"],
+                     "frac_of_sustained_peak": (tf_s / peaks["bf16_tflops_sustained"]) if peaks["bf16_tflops_sustained"] else None,
+                     "clocks": cs,
+                     # time x clock: comparable across runs whose clocks differ
+                     "ms_x_mhz": (ms_s / n_sus * cs["sm_mhz"]) if cs["sm_mhz"] else None}
     roofline = {"bound": "tensor", "kernel": f"sdpa_tc_kernel ({kernel_name})",
                 "achieved": per_gpu_tflops, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                 "frac": per_gpu_tflops / peaks["bf16_tflops"], "peak_source": peaks["source"] + " (burst)",
                 "frac_of_nominal_2250": per_gpu_tflops / 2250.0,
-                # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this workload from the
-                # committed ncu capture (profiles/sdpa_tc_kernel_config2_causal_bf16.md); algorithmic
-                # q+k+v+o = 536.9 MB
-                "traffic": 514.6e6, "traffic_unit": "bytes per launch (ncu)",
+                # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this workload, read from
+                # the file `bench.py --ingest-ncu` wrote out of an ncu capture (null without one);
+                # algorithmic q+k+v+o = 536.9 MB
+                "traffic": read_ncu_traffic(), "traffic_unit": "bytes per launch (ncu)",
                 "algorithmic_bytes": 4 * c["B"] * c["Hq"] * c["S"] * c["D"] * 2}
 
     extra = {}
@@ -295,6 +392,22 @@ def run_ours(args):
 
     def loop_ms(fn, n, w=warmup):
         return max_over_ranks(timed_loop(fn, n, w, barrier)) / n
+
+    if want("config1"):
+        # config 1, the fp32 parity configuration (latency-bound): causal attention B=2 H=4 S=128 D=64
+        # on the CUDA-core kernel (fp32 at tolerance 1e-4 rules out TF32) + RMSNorm on [256, 256]
+        g1 = torch.Generator(device=dev).manual_seed(1000)
+        q1, k1, v1 = (torch.randn(2, 4, 128, 64, generator=g1, device=dev) for _ in range(3))
+        o1 = torch.empty_like(q1)
+        x1 = torch.randn(256, 256, generator=g1, device=dev)
+        w1 = 1 + 0.1 * torch.randn(256, generator=g1, device=dev)
+        y1_ = torch.empty_like(x1)
+        t_a = loop_ms(lambda: abi.sdpa_fwd(q1, k1, v1, causal=True, out=o1, flags=abi.SDPA_REF_SCALE), esteps)
+        kname = abi.sdpa_last_kernel()
+        t_n = loop_ms(lambda: abi.rmsnorm_fwd(x1, w1, 1e-6, out=y1_, mode=abi.ROUND_PER_OP), esteps)
+        extra["config1_fp32_B2_H4_S128_D64"] = {"sdpa_ms": t_a, "sdpa_kernel": kname, "rmsnorm_256x256_ms": t_n,
+                                                 "note": "launch-latency bound; parity at 1e-4 is checked by the tests and smoke()"}
+        del q1, k1, v1, o1, x1, w1, y1_
 
     if want("rmsnorm"):
         # RMSNorm, config 2 shape: bytes = 2*rows*H*2 + H*2
@@ -420,6 +533,10 @@ def run_ours(args):
 
     # ---------------- e2e: public operator on the paras device, host buffers ----------------
     pdev = f"paras:{local + 1}"
+    # each rank feeds its GPU from host memory of the GPU's own NUMA node (buffers are pinned below,
+    # after the binding, so their pages land there)
+    from torch_paras import sharding as _sh
+    numa_cpus = _sh.bind_host_to_gpu_node(local) if not args.no_numa_bind else []
     hq, hk, hv = (t_.cpu().pin_memory() for t_ in (q, k, v))
     h2d = (hq.numel() + hk.numel() + hv.numel()) * 2
     d2h = hq.numel() * 2
@@ -446,6 +563,25 @@ def run_ours(args):
         torch_paras.synchronize(local + 1)
         return max_over_ranks((time.perf_counter() - t0) / n * 1e3) * 1e-3
 
+    def link_gbs():
+        """Plain pinned copies of q to the GPU and of the result back, one direction at a time: the
+        link's own rate on this box, beside which the pipelined figure can be read."""
+        dq_ = torch.empty_like(q)
+        res = {}
+        for name, fn, nbytes in (("h2d", lambda: dq_.copy_(hq, non_blocking=True), hq.numel() * 2),
+                                 ("d2h", lambda: hout.copy_(dq_, non_blocking=True), hq.numel() * 2)):
+            fn()
+            torch.cuda.synchronize()
+            barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(3):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            res[name] = 3 * nbytes / (max_over_ranks(e0.elapsed_time(e1)) * 1e-3) / 1e9
+        return res
+
     e2e_steps = max(2, min(steps, 5))
     dev_s = time_host_loop(e2e_device_step, e2e_steps)
     e2e_s = time_host_loop(e2e_step, e2e_steps)
@@ -453,16 +589,20 @@ def run_ours(args):
            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
            "api": "torch_paras.nn.attention_host: pinned host q/k/v in, pinned host result out, "
                   "batch chunks pipelined over three streams",
+           "link_gbs_per_gpu_alone": link_gbs(), "numa_bound_cpus": len(numa_cpus),
+           "achieved_h2d_gbs_per_gpu": h2d / e2e_s / 1e9,
            "device_api": {"value": world * flops / dev_s / 1e12, "ms_per_step": dev_s * 1e3,
                           "api": "pinned host q/k/v .to(paras:N), F.scaled_dot_product_attention, .cpu()"}}
 
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        times, kind, threads = time_cpu_reference(args.cpu_repeat, 1)
-        s = CPU_SAMPLE
-        fl = sdpa_flops(s["B"], s["H"], s["S"], s["S"], s["D"], True)
+        # about 10-30 s of CPU work: one pass of the whole workload where that fits, else the sample
+        shape, _ = choose_cpu_shape(1, 30.0)
+        rep = 1 if shape == FULL else args.cpu_repeat
+        times, kind, threads = time_cpu_reference(shape, rep, 0 if shape == FULL else 1)
+        fl = sdpa_flops(shape["B"], shape["H"], shape["S"], shape["S"], shape["D"], True)
         cpu_baseline = {"value": fl * len(times) / sum(times) / 1e12, "unit": "TFLOP/s", "cores": threads,
-                        "kind": kind, "sample": sample_desc(), "seconds_per_pass": sum(times) / len(times)}
+                        "kind": kind, "sample": sample_desc(shape), "seconds_per_pass": sum(times) / len(times)}
 
     gathered = None
     if dist is not None:
@@ -483,6 +623,7 @@ def run_ours(args):
                        "l2": "inputs (537 MB per step) larger than the 126 MB L2; no flush",
                        "sharding": "batch shards, one per rank, no collective on the forward path",
                        "gathered_output_shape": gathered},
+            "value_sustained": sustained["value"] if sustained else None, "sustained": sustained,
             "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e,
             "gpu_launches": steps, "clocks": clk.summary(), "extra": extra,
         }
@@ -502,11 +643,20 @@ def main():
     ap.add_argument("--small", action="store_true",
                     help="shrink the extra workloads (SwiGLU 8192 rows, decode batch 8) so that a profiler "
                          "capture holds about 1 GB on the device; rates stay per-byte comparable")
-    ap.add_argument("--only", choices=["rmsnorm", "swiglu", "gqa", "decode", "block", "gemm", "bwd"],
+    ap.add_argument("--sustain-s", type=float, default=2.0,
+                    help="seconds of back-to-back headline launches for the sustained figure (0 = skip)")
+    ap.add_argument("--ingest-ncu", metavar="CSV",
+                    help="write profiles/sdpa_tc_kernel_config2_dram_traffic.txt from `ncu --page raw --csv` output and exit")
+    ap.add_argument("--only", choices=["config1", "rmsnorm", "swiglu", "gqa", "decode", "block", "gemm", "bwd"],
                     help="after the headline loop run just this extra workload and print it (for profiling)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-numa-bind", action="store_true",
+                    help="leave the process where the launcher put it instead of binding it to the GPU's NUMA node for e2e")
     ap.add_argument("--cpu-repeat", type=int, default=3)
     args = ap.parse_args()
+    if args.ingest_ncu:
+        ingest_ncu(args.ingest_ncu)
+        return
     if args.impl == "reference":
         run_reference_arm(args)
     else:

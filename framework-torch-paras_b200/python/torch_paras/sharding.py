@@ -82,3 +82,50 @@ def gather_shards(local: torch.Tensor, sizes: Sequence[int], dim: int = 0, group
     dist.all_gather(bufs, padded, group=group)
     out = torch.cat([b[:n] for b, n in zip(bufs, sizes)], 0)
     return out.movedim(0, dim)
+
+
+def _parse_cpulist(text: str) -> List[int]:
+    cpus: List[int] = []
+    for part in text.strip().split(","):
+        if not part:
+            continue
+        lo, _, hi = part.partition("-")
+        cpus.extend(range(int(lo), int(hi or lo) + 1))
+    return cpus
+
+
+def gpu_numa_cpus(pci_bus_id: str, sysfs: str = "/sys") -> List[int]:
+    """CPUs of the NUMA node a GPU hangs off, from sysfs (`pci_bus_id` like "0000:1b:00.0");
+    empty when the platform does not say (single node, or no numa_node entry)."""
+    import os
+    dev = os.path.join(sysfs, "bus", "pci", "devices", pci_bus_id.lower())
+    try:
+        node = int(open(os.path.join(dev, "numa_node")).read())
+        if node < 0:
+            return []
+        return _parse_cpulist(open(os.path.join(sysfs, "devices", "system", "node", f"node{node}", "cpulist")).read())
+    except (OSError, ValueError):
+        return []
+
+
+def bind_host_to_gpu_node(gpu: int) -> List[int]:
+    """Pins the calling process to the CPUs of the NUMA node of CUDA GPU `gpu`, so that the pinned
+    host buffers it allocates afterwards (first touch) and the threads that fill them sit next to
+    that GPU's PCIe root instead of across the socket link.  One rank per GPU feeding its GPU from
+    host memory is bound by exactly that path.  Returns the CPUs bound to ([] = left as it was)."""
+    import os
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        bus = pynvml.nvmlDeviceGetPciInfo(pynvml.nvmlDeviceGetHandleByIndex(gpu)).busId
+        bus = bus.decode() if isinstance(bus, bytes) else bus
+        if len(bus.split(":")[0]) == 8:      # NVML prints an 8-digit domain, sysfs a 4-digit one
+            bus = bus[4:]
+        cpus = gpu_numa_cpus(bus)
+        allowed = os.sched_getaffinity(0)
+        cpus = [c for c in cpus if c in allowed]
+        if cpus:
+            os.sched_setaffinity(0, cpus)
+        return cpus
+    except Exception:  # noqa: BLE001  (no NVML, no sysfs entry, not permitted: stay unbound)
+        return []

@@ -75,6 +75,11 @@ def run_op(op, a):
 
 def main():
     jobs_path, out_path = sys.argv[1], sys.argv[2]
+    # The reference's host engine runs on torch.get_num_threads() threads (host_thread_count,
+    # csrc/compat/paras_compat.cpp:70-82).  A launcher may have exported OMP_NUM_THREADS=1 to
+    # this process; PARAS_REF_THREADS states the count the caller wants instead.
+    if os.environ.get("PARAS_REF_THREADS"):
+        torch.set_num_threads(int(os.environ["PARAS_REF_THREADS"]))
     mod = ref_loader.load()
     jobs = torch.load(jobs_path)
     results = []

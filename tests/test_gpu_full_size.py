@@ -5,6 +5,7 @@ import pytest
 import torch
 
 from oracle import oracle as O
+from oracle import stats
 
 import torch_paras  # noqa: F401
 from torch_paras import abi
@@ -19,17 +20,28 @@ def gen(shape, seed, dtype=torch.bfloat16, mean=0.0, std=1.0):
     return (mean + std * t).to(dtype)
 
 
+def oracle_check(got, want, name):
+    """16-bit result against the oracle: max-abs <= 2e-2 and nothing over it; the share within one
+    unit in the last place is printed.  That share is about 64 % for any kernel that keeps the scores
+    in fp32 (the reference rounds them to 16 bits twice before its softmax, so outputs near zero
+    differ by several of their own small ulps); far less would mean a real error."""
+    r = stats.report(got, want, 2e-2)
+    print(f"{name}: {stats.fmt(r)}")
+    assert r["over_tol"] == 0 and r["max_abs"] <= 2e-2, f"{name}: {stats.fmt(r)}"
+    assert r["within_1ulp"] >= 0.4, f"{name}: {stats.fmt(r)}"
+
+
 def test_config2_llama_causal_sdpa_full_size():
     # bf16 B=8 Hq=Hkv=32 S=2048 D=128
     q, k, v = gen((8, 32, 2048, 128), 1), gen((8, 32, 2048, 128), 2), gen((8, 32, 2048, 128), 3)
     out = abi.sdpa_fwd(q, k, v, causal=True, flags=abi.SDPA_REF_SCALE)
     assert abi.sdpa_last_kernel() == "tcgen05"
-    # oracle on two (batch, head) slices
-    for b, h in ((0, 0), (7, 31)):
+    # oracle on ten whole (batch, head) units spread over the persistent grid's schedule (a unit =
+    # all 16 query blocks of the head, so every pairing of long and short blocks is covered)
+    for b, h in ((0, 0), (0, 31), (1, 5), (2, 17), (3, 30), (4, 9), (5, 26), (6, 13), (7, 1), (7, 31)):
         want = O.sdpa(q[b:b + 1, h:h + 1].cpu(), k[b:b + 1, h:h + 1].cpu(), v[b:b + 1, h:h + 1].cpu(),
                       is_causal=True)
-        err = (out[b:b + 1, h:h + 1].cpu().double() - want.double()).abs().max().item()
-        assert err <= 2e-2, f"slice ({b},{h}): max-abs {err}"
+        oracle_check(out[b:b + 1, h:h + 1], want, f"config 2 unit ({b},{h})")
     # causality: changing keys/values from position p on leaves rows < p bit-identical
     p = 1111
     k2, v2 = k.clone(), v.clone()
@@ -51,11 +63,14 @@ def test_config3_gqa_causal_sdpa_long_sequence_slice():
     q, k, v = gen((1, 64, 8192, 128), 6), gen((1, 8, 8192, 128), 7), gen((1, 8, 8192, 128), 8)
     out = abi.sdpa_fwd(q, k, v, causal=True, flags=abi.SDPA_REF_SCALE)
     assert abi.sdpa_last_kernel() == "tcgen05"
-    # GQA: query head 13 must read kv head 13 // 8 = 1 -- check against the oracle on rows 0..1023
-    h = 13
-    want = O.sdpa(q[:, h:h + 1, :1024].cpu(), k[:, 1:2, :1024].cpu(), v[:, 1:2, :1024].cpu(), is_causal=True)
-    err = (out[:, h:h + 1, :1024].cpu().double() - want.double()).abs().max().item()
-    assert err <= 2e-2, f"gqa slice max-abs {err}"
+    # GQA: query head 13 must read kv head 13 // 8 = 1, head 63 kv head 7.  Whole heads against the
+    # oracle, all 8192 rows: rows >= 4096 walk 33-64 key tiles, over which the softmax reference of
+    # a row has moved many times.
+    for h in (13, 63):
+        g_ = h // 8
+        want = O.sdpa(q[:, h:h + 1].cpu(), k[:, g_:g_ + 1].cpu(), v[:, g_:g_ + 1].cpu(), is_causal=True)
+        oracle_check(out[:, h:h + 1], want, f"config 3 head {h}, 8192 rows")
+        oracle_check(out[:, h:h + 1, 4096:], want[:, :, 4096:], f"config 3 head {h}, rows 4096..8191")
     # agreement with the independent CUDA-core kernel on the last rows of one head
     sl = slice(8192 - 64, 8192)
     ref = abi.sdpa_fwd(q[:, 63:64, sl].contiguous(), k[:, 7:8], v[:, 7:8], causal=False,
@@ -69,9 +84,10 @@ def test_config4_decode_step_full_size_slice():
     # bf16 B=64 q_len=1 kv_len=32768 Hq=32 Hkv=8 D=128, non-causal; 8 of the 64 batch rows
     q, k, v = gen((8, 32, 1, 128), 9), gen((8, 8, 32768, 128), 10), gen((8, 8, 32768, 128), 11)
     out = abi.sdpa_fwd(q, k, v, flags=abi.SDPA_REF_SCALE)
-    want = O.sdpa(q[:1].cpu(), k[:1].cpu(), v[:1].cpu(), enable_gqa=True)
-    err = (out[:1].cpu().double() - want.double()).abs().max().item()
-    assert err <= 2e-2, f"decode slice max-abs {err}"
+    want = O.sdpa(q[:4].cpu(), k[:4].cpu(), v[:4].cpu(), enable_gqa=True)     # four whole batch rows
+    oracle_check(out[:4], want, "config 4 decode, batch rows 0..3")
+    want = O.sdpa(q[7:].cpu(), k[7:].cpu(), v[7:].cpu(), enable_gqa=True)
+    oracle_check(out[7:], want, "config 4 decode, batch row 7")
     # permuting the cache positions must not change a non-causal result (up to summation order)
     perm = torch.randperm(32768, device=DEV)
     out_p = abi.sdpa_fwd(q, k[:, :, perm].contiguous(), v[:, :, perm].contiguous(), flags=abi.SDPA_REF_SCALE)
@@ -133,8 +149,9 @@ def test_config5_decoder_block_share_of_one_gpu():
     assert (y1[rows].cpu().double() - want1.double()).abs().max().item() <= 2e-2
     # attention: query heads 0-3 share kv head 0; oracle on the first 1024 positions
     want_a = O.sdpa(q[:, :4, :1024].cpu(), k[:, :1, :1024].cpu(), v[:, :1, :1024].cpu(), is_causal=True, enable_gqa=True)
-    err = (att[:, :4, :1024].cpu().double() - want_a.double()).abs().max().item()
-    assert err <= 2e-2, f"attention slice max-abs {err}"
+    oracle_check(att[:, :4, :1024], want_a, "config 5 attention, heads 0-3, rows 0..1023")
+    want_b = O.sdpa(q[:, 29:30].cpu(), k[:, 7:8].cpu(), v[:, 7:8].cpu(), is_causal=True)
+    oracle_check(att[:, 29:30], want_b, "config 5 attention, head 29, all 4096 rows")
     a2 = att.transpose(1, 2).reshape(S, 4096)[rows].contiguous()
     want2 = O.rms_norm_composite(a2.cpu(), [4096], w.cpu(), 1e-6)
     assert (y2[rows].cpu().double() - want2.double()).abs().max().item() <= 2e-2
