@@ -5,8 +5,9 @@
 // composite (csrc/ops/rms_swiglu_ops.cpp:43-75: pow, mean, add, rsqrt, mul, mul = six
 // full passes over HBM, each rounding to the tensor dtype).
 //
-// Forward kernel: one WARP per row, the whole row held in registers, so HBM sees exactly
-// one 128-bit coalesced read and one 128-bit write per element (algorithmic traffic
+// Forward kernels: the whole row held in registers -- by one WARP for rows up to 128 vectors of
+// 16 bytes, by a CTA of 4 or 8 warps for longer ones -- so HBM sees exactly one 128-bit
+// coalesced read and one 128-bit write per element (algorithmic traffic
 // 2*rows*H*sizeof(T) + H*sizeof(T)); sum of squares via warp shuffles, accumulated in
 // double so that 16-bit results reproduce the reference's double arithmetic.  Rows too
 // long for registers take a CTA-per-row two-pass kernel whose second read hits L2.
@@ -175,6 +176,107 @@ rmsnorm_fwd_warp_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __r
     }
 }
 
+// One CTA of W warps per row, the row still held in registers (KV 16-byte vectors per thread).
+// For long rows this is the better geometry: a warp that owns a whole 8 KB row alternates between
+// a load phase, a reduction and a store phase with nothing in flight in between, and few such
+// warps fit an SM; W warps sharing the row hold a quarter (W = 4) of it each, four times as many
+// rows are resident per SM at the same registers, and the unit of the tail is one row.
+// MINB (CTAs per SM the register allocation must allow) was measured on [16384, 4096] bf16 rows
+// with W = 4: 10 gave 5.9 / 6.2 TB/s (single-rounding / per-op-rounding mode) where the compiler's
+// own choice (8) gave 5.4 / 5.9 and 12 or more spilled.
+template <typename T, int MODE, int KV, int W, int MINB>
+__global__ void __launch_bounds__(32 * W, MINB)
+rmsnorm_fwd_cta_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__ y,
+                       float* __restrict__ rstd, int64_t rows, int64_t H, int nvec, double eps) {
+    constexpr int N = Vec16<T>::N;
+    __shared__ double part_sum[2][W];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    int flip = 0;
+    for (int64_t row = blockIdx.x; row < rows; row += gridDim.x, flip ^= 1) {
+        const T* xr = x + row * H;
+        Vec16<T> v[KV];
+#pragma unroll
+        for (int k = 0; k < KV; ++k) {
+            const int i = tid + 32 * W * k;
+            if (i < nvec) v[k] = ld16_stream(xr + int64_t(i) * N);
+        }
+        double acc = 0.0;
+#pragma unroll
+        for (int k = 0; k < KV; ++k) {
+            const int i = tid + 32 * W * k;
+            if (i < nvec) {
+                if constexpr (sizeof(T) == 4) {
+#pragma unroll
+                    for (int e = 0; e < N; ++e) {
+                        const float f = v[k].v[e];
+                        acc += (MODE == PARAS_ROUND_ONCE) ? double(f) * double(f) : double(f * f);
+                    }
+                } else if constexpr (MODE == PARAS_ROUND_PER_OP) {
+                    using T2 = typename Packed<T>::T2;
+                    const T2* x2 = reinterpret_cast<const T2*>(&v[k]);
+                    float part = 0.f;
+#pragma unroll
+                    for (int e = 0; e < N / 2; ++e) {
+                        const float2 f = Packed<T>::unpack(__hmul2(x2[e], x2[e]));  // pow(2), rounded
+                        part += f.x + f.y;
+                    }
+                    acc += double(part);
+                } else {
+                    float part = 0.f;
+#pragma unroll
+                    for (int e = 0; e < N; ++e)
+                        part += RowMath<T>::template sq<MODE>(to_f32<T>(v[k].v[e]));
+                    acc += double(part);
+                }
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < KV; ++k) {  // keep the row packed across the reduction (see above)
+            uint4& u = *reinterpret_cast<uint4*>(&v[k]);
+            asm volatile("" : "+r"(u.x), "+r"(u.y), "+r"(u.z), "+r"(u.w));
+        }
+        acc = warp_sum(acc);
+        if (lane == 0) part_sum[flip][warp] = acc;
+        __syncthreads();  // one barrier per row: the two sets of partials take turns
+        double total = 0.0;
+#pragma unroll
+        for (int i = 0; i < W; ++i) total += part_sum[flip][i];
+        float inv_f;
+        double inv_d;
+        row_scalars<T, MODE>(total, H, eps, &inv_f, &inv_d);
+        if (rstd && tid == 0) rstd[row] = inv_f;
+        T* yr = y + row * H;
+#pragma unroll
+        for (int k = 0; k < KV; ++k) {
+            const int i = tid + 32 * W * k;
+            if (i < nvec) {
+                Vec16<T> wv;
+                if (w) wv = ld16(w + int64_t(i) * N);
+                Vec16<T> o;
+                if constexpr (sizeof(T) == 2 && MODE == PARAS_ROUND_PER_OP) {
+                    using T2 = typename Packed<T>::T2;
+                    const T2 inv2 = Packed<T>::dup(inv_f);
+                    const T2* x2 = reinterpret_cast<const T2*>(&v[k]);
+                    const T2* w2 = reinterpret_cast<const T2*>(&wv);
+                    T2* o2 = reinterpret_cast<T2*>(&o);
+#pragma unroll
+                    for (int e = 0; e < N / 2; ++e) {
+                        T2 t = __hmul2(x2[e], inv2);
+                        if (w) t = __hmul2(t, w2[e]);
+                        o2[e] = t;
+                    }
+                } else {
+#pragma unroll
+                    for (int e = 0; e < N; ++e)
+                        o.v[e] = finish<T, MODE>(v[k].v[e], inv_f, inv_d, w != nullptr,
+                                                 w ? wv.v[e] : v[k].v[e]);
+                }
+                st16_stream(yr + int64_t(i) * N, o);
+            }
+        }
+    }
+}
+
 // Any H, any alignment: one CTA per row, two passes (the second read is an L2 hit).
 template <typename T, int MODE>
 __global__ void __launch_bounds__(256)
@@ -280,6 +382,18 @@ int launch_fwd(Gpu* g, const void* x, const void* w, void* y, float* rstd, int64
     const bool vec_ok = (H % N == 0) && aligned16(x) && aligned16(y) && (!w || aligned16(w));
     const int64_t nvec = H / N;
     const int sms = g->sm_count > 0 ? g->sm_count : 148;
+    if (vec_ok && nvec > 32 * 4 && nvec <= 32 * 8 * 4) {
+        // long rows: W warps share a row, 4 vectors per thread (4 warps up to 8 KB rows, else 8)
+        int64_t blocks = rows;
+        const int64_t cap = int64_t(1) << 30;
+        if (blocks > cap) blocks = cap;
+        if (nvec <= 32 * 4 * 4)
+            rmsnorm_fwd_cta_kernel<T, MODE, 4, 4, 10><<<int(blocks), 128, 0, s>>>(px, pw, py, rstd, rows, H, int(nvec), eps);
+        else
+            rmsnorm_fwd_cta_kernel<T, MODE, 4, 8, 5><<<int(blocks), 256, 0, s>>>(px, pw, py, rstd, rows, H, int(nvec), eps);
+        PB_LAUNCH_CHECK("rmsnorm_fwd_cta_kernel");
+        return PARAS_OK;
+    }
     if (vec_ok && nvec <= 32 * 16) {
         // One row per warp and as many small CTAs as there are row groups: the block scheduler
         // balances them, and every resident warp keeps a whole row (up to 8 KB) in flight.
