@@ -499,9 +499,13 @@ def run_ours(args):
         dob = gen((Bb, c["Hq"], c["S"], c["D"]), 25)
         ob, lseb = abi.sdpa_fwd(qb_, kb_, vb_, causal=True, return_lse=True)
         t = loop_ms(lambda: abi.sdpa_bwd(dob, qb_, kb_, vb_, ob, lseb, causal=True), s3, 3)
+        t_c = loop_ms(lambda: abi.sdpa_bwd(dob, qb_, kb_, vb_, ob, lseb, causal=True, composite=True), s3, 3)
         fl = 2.5 * sdpa_flops(Bb, c["Hq"], c["S"], c["S"], c["D"], True)
-        extra[f"sdpa_backward_B{Bb}_H{c['Hq']}_S{c['S']}"] = {"ms": t, "tflops": fl / (t * 1e-3) / 1e12,
-                                                            "note": "five batched GEMMs over two materialised [L,L] matrices, element-wise steps in their epilogues"}
+        extra[f"sdpa_backward_B{Bb}_H{c['Hq']}_S{c['S']}"] = {
+            "ms": t, "tflops": fl / (t * 1e-3) / 1e12, "frac_of_bf16_peak": fl / (t * 1e-3) / 1e12 / peaks["bf16_tflops"],
+            "note": "fused tcgen05 kernels (dK/dV, then dQ; S and dP recomputed in each: 7 tile products, "
+                    "counted as the 5 the gradient needs); delta pre-pass included",
+            "composite_ms": t_c, "composite_tflops": fl / (t_c * 1e-3) / 1e12}
         del qb_, kb_, vb_, dob, ob, lseb
     if want("gemm"):
         # The projections either side of the path at config 2 / 5 sizes (hidden 4096, FFN 14336):

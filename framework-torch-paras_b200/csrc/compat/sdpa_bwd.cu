@@ -19,6 +19,7 @@
 
 #include "common.cuh"
 #include "gemm_internal.cuh"
+#include "sdpa_common.cuh"
 
 namespace pb {
 namespace {
@@ -95,9 +96,8 @@ extern "C" int paras_b200_sdpa_bwd(const paras_sdpa_bwd_args* a) {
         return fail(PARAS_E_INVALID, "paras sdpa backward: null pointer");
     const int r = a->Hq / a->Hkv;
     const int64_t R = int64_t(r) * a->Lq;
-    if (a->D % 8 || a->Lk % 8 || R > INT32_MAX)
-        return fail(PARAS_E_UNSUPPORTED,
-                    "paras sdpa backward: head dim and key length must be multiples of 8 (16-byte rows)");
+    if (a->D % 8 || R > INT32_MAX)
+        return fail(PARAS_E_UNSUPPORTED, "paras sdpa backward: head dim must be a multiple of 8 (16-byte rows)");
     for (const void* ptr : {a->q, a->k, a->v, a->out, a->dout, (const void*)a->dq, (const void*)a->dk, (const void*)a->dv})
         if (reinterpret_cast<uintptr_t>(ptr) & 15u)
             return fail(PARAS_E_UNSUPPORTED, "paras sdpa backward: tensors must be 16-byte aligned");
@@ -105,6 +105,25 @@ extern "C" int paras_b200_sdpa_bwd(const paras_sdpa_bwd_args* a) {
     const size_t es = 2;
     const int64_t groups = int64_t(a->B) * a->Hkv;     // (batch, kv head): its r query heads are adjacent
     const int64_t rows = groups * R;
+    const int sms_ = g->sm_count > 0 ? g->sm_count : 148;
+
+    // Head dim 128 / 64: the fused kernels; their only scratch is delta.
+    if (!(a->reserved & PARAS_SDPA_BWD_COMPOSITE) && sdpa_bwd_tc_supported(g, *a)) {
+        void* dmem = nullptr;
+        st = paras_b200_malloc_async(a->gpu, size_t(rows) * sizeof(float), s, &dmem);
+        if (st != PARAS_OK) return st;
+        float* delta_f = static_cast<float*>(dmem);
+        if (a->dtype == PARAS_BF16) launch_delta<__nv_bfloat16>(a->dout, a->out, delta_f, rows, a->D, sms_, s);
+        else launch_delta<__half>(a->dout, a->out, delta_f, rows, a->D, sms_, s);
+        st = cudaGetLastError() == cudaSuccess ? sdpa_bwd_tc_launch(g, *a, delta_f, s)
+                                               : fail(PARAS_E_CUDA, "paras sdpa backward: launch of the delta kernel failed");
+        const int st2 = paras_b200_free_async(a->gpu, dmem, s);
+        return st != PARAS_OK ? st : st2;
+    }
+    if (a->Lk % 8)
+        return fail(PARAS_E_UNSUPPORTED,
+                    "paras sdpa backward: this head dim takes the composite path, which needs a key length "
+                    "that is a multiple of 8 (16-byte rows)");
 
     // scratch: delta [rows] fp32, S/P and dP/dS for a chunk of groups
     const size_t mat_bytes_per_group = size_t(R) * a->Lk * es;

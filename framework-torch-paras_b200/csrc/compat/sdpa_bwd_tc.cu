@@ -1,0 +1,769 @@
+// Fused flash-attention backward for sm_100a: tcgen05 tensor cores, TMEM accumulators, TMA.
+//
+// The gradient the reference obtains by autograd through its composite sdpa_math
+// (csrc/ops/attention_ops.cpp:71-136) and its softmax backward (csrc/ops/pointwise_ops.cpp:
+// 994-1062), without ever forming a [Lq, Lk] matrix in memory: the probabilities are rebuilt
+// tile by tile from the forward's row statistics,
+//
+//     P  = exp(S * scale - lse[q])            S  = Q K^T
+//     dS = P o (dP - delta[q]) * scale        dP = dO V^T,  delta[q] = sum_d dO[q,d] O[q,d]
+//     dV = P^T dO      dK = dS^T Q      dQ = dS K
+//
+// Two kernels, each a persistent grid of one 320-thread CTA per SM, neither with atomics nor
+// with scratch beyond delta (so the result is deterministic):
+//
+//   sdpa_bwd_dkv_kernel   a CTA keeps one 128-key tile (K_j, V_j) in shared memory and streams
+//       the query tiles that see it (all query heads of the kv head's group, so GQA sums happen
+//       in the accumulator).  S^T = K_j Q_i^T and dP^T = V_j dO_i^T land in TMEM with one KEY per
+//       lane; P^T and dS^T go back to TMEM as 16-bit A operands of dV += P^T dO_i, dK += dS^T Q_i.
+//   sdpa_bwd_dq_kernel    the mirror image: a CTA keeps one 128-query tile (Q_i, dO_i) and
+//       streams the key tiles it sees; S and dP land with one QUERY per lane, dS goes back to
+//       TMEM as the A operand of dQ += dS K_j.
+//
+// S and dP are computed twice (7 tile products instead of 5) in exchange for no fp32 dQ
+// accumulator in memory, no atomics and no conversion pass.
+//
+//   warps 0-3  element-wise work on columns 0-63 of the S / dP tiles (a lane owns a row)
+//   warps 4-7  the same on columns 64-127
+//   warp  8    one lane issues every tcgen05.mma
+//   warp  9    TMA loads (and, for the dK/dV kernel, the per-query statistics of each tile)
+//
+// Shared memory (both kernels): the CTA's own pair of tiles (2 x 32 KB) and a ring of two
+// stages of the streamed pair (2 x 64 KB), all 128-byte swizzled as TMA writes them.
+// TMEM: S @0, dP @128, then dV @256 / dK @384 (dK/dV kernel) or dQ @256 / dS @384,448.
+// Every wait is bounded (tc_prims.cuh): a wait that runs out raises the CTA's abort flag, all
+// roles leave through the common exit, TMEM is freed and the GPU's status word is set.
+#include <cmath>
+
+#include "sdpa_common.cuh"
+#include "tc_prims.cuh"
+#include "tma_host.cuh"
+
+namespace pb {
+namespace {
+
+using namespace tc;
+
+constexpr int BT = 128;                       // rows of every tile: queries or keys
+constexpr int kChunkBytes = 64 * 2 * 128;     // one 64-element slab of 128 rows
+constexpr int kTileBytes = 2 * kChunkBytes;   // 128 x 128 x 2 B (head dim 64 uses the first slab)
+constexpr int kThreads = 320;
+constexpr int kMmaWarp = 8, kLoadWarp = 9;
+constexpr int kTmemCols = 512;
+
+// shared memory map
+constexpr int kSmemOwn = 0;                              // the CTA's own pair: tile 0, tile 1
+constexpr int kSmemRing = 2 * kTileBytes;                // 2 stages x (tile 0, tile 1)
+constexpr int kStageBytes = 2 * kTileBytes;
+constexpr int kSmemStats = kSmemRing + 2 * kStageBytes;  // 2 stages x (lse2[128], delta[128]) fp32
+constexpr int kStatsBytes = 2 * BT * 4;
+constexpr int kSmemBars = kSmemStats + 2 * kStatsBytes;
+// barriers
+constexpr int kBarOwnFull = 0;     // TMA -> MMA: the own pair landed
+constexpr int kBarOwnEmpty = 1;    // MMA -> TMA: the item's last MMA that reads the own pair is done
+constexpr int kBarRingFull = 2;    // [2]
+constexpr int kBarRingEmpty = 4;   // [2]
+constexpr int kBarSFull = 6;       // MMA -> compute: S tile ready
+constexpr int kBarDpFull = 7;      // MMA -> compute: dP tile ready
+constexpr int kBarPFull = 8;       // compute -> MMA: P^T stored (dK/dV kernel) / S and dP taken (dQ kernel)
+constexpr int kBarDsFull = 9;      // compute -> MMA: dS stored
+constexpr int kBarAccFull = 10;    // MMA -> compute: the item's accumulators are complete
+constexpr int kBarAccEmpty = 11;   // compute -> MMA: the accumulators have been read out
+constexpr int kNumBars = 12;
+constexpr int kSmemMisc = kSmemBars + kNumBars * 8;
+constexpr int kSmemTotal = kSmemMisc + 16;
+constexpr int kSmemLaunch = kSmemTotal + 1024;
+
+struct BwdParams {
+    void* dq;
+    void* dk;
+    void* dv;
+    const float* lse;     // [B, Hq, Lq]
+    const float* delta;   // [B, Hq, Lq]
+    int B, Hq, Hkv, Lq, Lk;
+    int causal;
+    float scale;
+    float scale_log2;     // scale * log2(e)
+    int* status;
+    int nq, nk;           // 128-row tiles of queries / keys
+    int npair;            // paired tiles per head (ceil(n / 2))
+    int units;
+};
+
+__device__ __forceinline__ void named_barrier_sync(int id, int threads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+// Query tiles that see key tile j, as the range [first, nq): under the top-left aligned causal
+// mask query row r sees keys 0..r, so tile i qualifies when its last row reaches the tile's
+// first key.
+__device__ __forceinline__ int first_query_tile(const BwdParams& p, int j) {
+    return p.causal ? min(j, p.nq) : 0;
+}
+// Key tiles query tile i sees: [0, n).
+__device__ __forceinline__ int key_tiles_for(const BwdParams& p, int i) {
+    int last = p.Lk;
+    if (p.causal) last = min(last, min(p.Lq, (i + 1) * BT));
+    return (last + BT - 1) / BT;
+}
+
+// One work item = one 128-row tile of the CTA's own pair: a key tile of one (batch, kv head) for
+// the dK/dV kernel, a query tile of one (batch, query head) for the dQ kernel.  A unit pairs tiles
+// (n-1-pair) and (pair) of one head: under a causal mask their work adds up to the same total for
+// every pair, so handing out units round-robin keeps the persistent CTAs balanced.
+struct Item {
+    int b, h;   // batch, head of the own tile (kv head / query head)
+    int t;      // tile index
+    int n;      // streamed tiles (iterations); 0 = nothing streams (the outputs are zeros)
+};
+
+template <bool DKV>
+__device__ __forceinline__ bool get_item(const BwdParams& p, int seq, Item* it) {
+    const int unit = int(blockIdx.x) + (seq >> 1) * int(gridDim.x);
+    if (unit >= p.units) return false;
+    const int heads = DKV ? p.Hkv : p.Hq;
+    const int tiles = DKV ? p.nk : p.nq;
+    const int hb = unit / p.npair;
+    const int pair = unit - hb * p.npair;
+    const int hi = tiles - 1 - pair;
+    it->b = hb / heads;
+    it->h = hb - it->b * heads;
+    it->t = (seq & 1) ? pair : hi;
+    const bool dup = (seq & 1) && pair == hi;   // odd tile count: the middle tile has no partner
+    if (dup) {
+        it->n = -1;                              // not an item at all
+    } else if (DKV) {
+        it->n = (p.Hq / p.Hkv) * (p.nq - first_query_tile(p, it->t));
+    } else {
+        it->n = key_tiles_for(p, it->t);
+    }
+    return true;
+}
+
+// Stores 32 fp32 accumulator columns of this lane's row as 16-bit values: 64 contiguous bytes.
+template <bool BF16>
+__device__ __forceinline__ void store_row32(void* dst, const uint32_t (&o)[32]) {
+    uint4* d = static_cast<uint4*>(dst);
+#pragma unroll
+    for (int v = 0; v < 4; ++v) {
+        uint4 w;
+        w.x = pack16<BF16>(__uint_as_float(o[8 * v + 0]), __uint_as_float(o[8 * v + 1]));
+        w.y = pack16<BF16>(__uint_as_float(o[8 * v + 2]), __uint_as_float(o[8 * v + 3]));
+        w.z = pack16<BF16>(__uint_as_float(o[8 * v + 4]), __uint_as_float(o[8 * v + 5]));
+        w.w = pack16<BF16>(__uint_as_float(o[8 * v + 6]), __uint_as_float(o[8 * v + 7]));
+        d[v] = w;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// dK / dV: own pair = (K_j, V_j), streamed pair = (Q_i, dO_i) over the group's query heads.
+// ---------------------------------------------------------------------------------------------
+template <bool BF16, int HD>
+__global__ void __launch_bounds__(kThreads, 1)
+sdpa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                    const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
+                    const BwdParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    auto bar = [&](int i) { return smem_base + kSmemBars + 8u * i; };
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + kSmemMisc);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + kSmemMisc + 4);
+    constexpr int kChunks = HD / 64;
+    constexpr uint32_t kLoadBytes = kChunks * kChunkBytes;   // bytes one tile brings in
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int r = p.Hq / p.Hkv;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < kNumBars; ++i) {
+            const bool eight = i == kBarPFull || i == kBarDsFull || i == kBarAccEmpty;
+            mbar_init(bar(i), eight ? 8u : 1u);   // one arrival per compute warp / one commit or TMA
+        }
+        *abort_flag = 0;
+        mbar_fence_init();
+        fence_proxy_async_smem();
+    }
+    if (warp == kMmaWarp) {
+        tmem_alloc(smem_base + kSmemMisc, kTmemCols);
+        tmem_relinquish();
+    }
+    if (warp == kLoadWarp && lane == 0) {
+        tma_prefetch_desc(&map_q);
+        tma_prefetch_desc(&map_k);
+        tma_prefetch_desc(&map_v);
+        tma_prefetch_desc(&map_do);
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = *tmem_slot;
+    constexpr int kColS = 0, kColDp = 128, kColDv = 256, kColDk = 384;
+
+    if (warp == kLoadWarp) {
+        // ------------------------------ loads ------------------------------------------------
+        bool ok = true;
+        uint32_t items = 0, rc = 0;   // items loaded, ring stages filled
+        Item it;
+        for (int seq = 0; ok && get_item<true>(p, seq, &it); ++seq) {
+            if (it.n <= 0) continue;
+            if (lane == 0) {
+                ok = mbar_wait(bar(kBarOwnEmpty), (items & 1u) ^ 1u, abort_flag, 0);
+                if (ok) {
+                    mbar_arrive_expect_tx(bar(kBarOwnFull), 2 * kLoadBytes);
+#pragma unroll
+                    for (int c = 0; c < kChunks; ++c) {
+                        tma_load_4d(smem_base + kSmemOwn + c * kChunkBytes, &map_k, bar(kBarOwnFull), 64 * c, it.t * BT, it.h, it.b);
+                        tma_load_4d(smem_base + kSmemOwn + kTileBytes + c * kChunkBytes, &map_v, bar(kBarOwnFull), 64 * c, it.t * BT, it.h, it.b);
+                    }
+                }
+            }
+            ++items;
+            const int i0 = first_query_tile(p, it.t), cnt = p.nq - i0;
+            for (int x = 0; x < it.n; ++x, ++rc) {
+                const int hh = x / cnt, i = i0 + (x - hh * cnt);
+                const int h = it.h * r + hh;
+                const int stage = rc & 1u;
+                if (lane == 0) ok = mbar_wait(bar(kBarRingEmpty + stage), ((rc >> 1) & 1u) ^ 1u, abort_flag, 1);
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) break;
+                // per-query statistics of this tile, in the form the element-wise warps use them:
+                // lse in the base-2 domain (+inf past the last query: its probabilities are 0) and delta
+                float* st = reinterpret_cast<float*>(smem_gen + kSmemStats + stage * kStatsBytes);
+                const int64_t row0 = (int64_t(it.b) * p.Hq + h) * p.Lq;
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int q = i * BT + lane * 4 + e;
+                    const bool live = q < p.Lq;
+                    st[lane * 4 + e] = live ? p.lse[row0 + q] * 1.4426950408889634f : INFINITY;
+                    st[BT + lane * 4 + e] = live ? p.delta[row0 + q] : 0.f;
+                }
+                __syncwarp();
+                if (lane == 0) {
+                    const uint32_t full = bar(kBarRingFull + stage);
+                    mbar_arrive_expect_tx(full, 2 * kLoadBytes);
+                    const uint32_t dst = smem_base + kSmemRing + stage * kStageBytes;
+#pragma unroll
+                    for (int c = 0; c < kChunks; ++c) {
+                        tma_load_4d(dst + c * kChunkBytes, &map_q, full, 64 * c, i * BT, h, it.b);
+                        tma_load_4d(dst + kTileBytes + c * kChunkBytes, &map_do, full, 64 * c, i * BT, h, it.b);
+                    }
+                }
+            }
+        }
+    } else if (warp == kMmaWarp) {
+        // ------------------------------ MMA issuer -------------------------------------------
+        if (lane == 0) {
+            constexpr uint32_t idesc_kk = instr_desc_f16(BF16 ? 1 : 0, BT, BT, false, false);
+            constexpr uint32_t idesc_acc = instr_desc_f16(BF16 ? 1 : 0, BT, HD, false, true);
+            const uint32_t own_k = smem_base + kSmemOwn, own_v = own_k + kTileBytes;
+            // D[128 keys x 128 queries] = own[keys x HD] * streamed[queries x HD]^T
+            auto issue_t = [&](uint32_t d_col, uint32_t a_tile, uint32_t b_tile) {
+#pragma unroll
+                for (int c = 0; c < kChunks; ++c)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const uint32_t off = c * kChunkBytes + i * 32;
+                        mma_ss(tmem + d_col, smem_desc_sw128(a_tile + off, 16, 1024),
+                               smem_desc_sw128(b_tile + off, 16, 1024), idesc_kk, (c | i) ? 1u : 0u);
+                    }
+            };
+            // D[128 keys x HD] (+)= A^T[keys x 128 queries] (16-bit, in TMEM) * streamed[queries x HD]
+            auto issue_acc = [&](uint32_t d_col, uint32_t a_col, uint32_t b_tile, bool acc) {
+#pragma unroll
+                for (int ks = 0; ks < BT / 16; ++ks) {
+                    // queries 0-63 sit in packed columns 0-31, queries 64-127 in columns 64-95: each
+                    // half overlays the fp32 columns the warps that wrote it had read themselves
+                    const uint32_t a = tmem + a_col + (ks < 4 ? ks * 8 : 64 + (ks - 4) * 8);
+                    mma_ts(tmem + d_col, a, smem_desc_sw128(b_tile + ks * 16 * 128, kChunkBytes, 1024), idesc_acc,
+                           (acc || ks) ? 1u : 0u);
+                }
+            };
+            bool ok = true;
+            uint32_t items = 0, rc = 0, pc = 0, dc = 0;   // items, ring stages used, P and dS hand-overs
+            Item it;
+            for (int seq = 0; ok && get_item<true>(p, seq, &it); ++seq) {
+                if (it.n <= 0) continue;
+                ok = mbar_wait(bar(kBarOwnFull), items & 1u, abort_flag, 2);
+                if (!ok) break;
+                auto ring_tile = [&](uint32_t c) { return smem_base + kSmemRing + (c & 1u) * kStageBytes; };
+                ok = mbar_wait(bar(kBarRingFull + (rc & 1u)), (rc >> 1) & 1u, abort_flag, 3);
+                if (!ok) break;
+                tc_fence_after_sync();
+                issue_t(kColS, own_k, ring_tile(rc));
+                tc_commit(bar(kBarSFull));
+                issue_t(kColDp, own_v, ring_tile(rc) + kTileBytes);
+                tc_commit(bar(kBarDpFull));
+                for (int x = 0; ok && x < it.n; ++x) {
+                    const uint32_t cur = rc + x;
+                    ok = mbar_wait(bar(kBarPFull), pc & 1u, abort_flag, 4);
+                    if (!ok) break;
+                    ++pc;
+                    if (x == 0 && items > 0) {   // the previous item's dK / dV have been read out
+                        ok = mbar_wait(bar(kBarAccEmpty), (items - 1) & 1u, abort_flag, 5);
+                        if (!ok) break;
+                    }
+                    tc_fence_after_sync();
+                    issue_acc(kColDv, kColS, ring_tile(cur) + kTileBytes, x > 0);   // dV += P^T dO
+                    if (x + 1 < it.n) {
+                        ok = mbar_wait(bar(kBarRingFull + ((cur + 1) & 1u)), ((cur + 1) >> 1) & 1u, abort_flag, 3);
+                        if (!ok) break;
+                        tc_fence_after_sync();
+                        issue_t(kColS, own_k, ring_tile(cur + 1));                   // next S^T over P^T
+                        tc_commit(bar(kBarSFull));
+                    }
+                    ok = mbar_wait(bar(kBarDsFull), dc & 1u, abort_flag, 6);
+                    if (!ok) break;
+                    ++dc;
+                    tc_fence_after_sync();
+                    issue_acc(kColDk, kColDp, ring_tile(cur), x > 0);               // dK += dS^T Q
+                    tc_commit(bar(kBarRingEmpty + (cur & 1u)));
+                    if (x + 1 < it.n) {
+                        issue_t(kColDp, own_v, ring_tile(cur + 1) + kTileBytes);     // next dP^T over dS^T
+                        tc_commit(bar(kBarDpFull));
+                    }
+                }
+                if (!ok) break;
+                rc += it.n;
+                tc_commit(bar(kBarAccFull));
+                tc_commit(bar(kBarOwnEmpty));
+                ++items;
+            }
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------ element-wise warps -----------------------------------
+        const int wg = warp >> 2, wq = warp & 3;
+        const uint32_t lane_base = uint32_t(wq * 32) << 16;
+        const int col0 = wg * 64;                        // this warp's query columns of the tile
+        const uint32_t s_addr = tmem + lane_base + kColS + col0;
+        const uint32_t dp_addr = tmem + lane_base + kColDp + col0;
+        const float c2 = p.scale_log2;
+        bool ok = true;
+        uint32_t items = 0, rc = 0;
+        Item it;
+        for (int seq = 0; ok && get_item<true>(p, seq, &it); ++seq) {
+            if (it.n < 0) continue;
+            const int key = it.t * BT + wq * 32 + lane;
+            const bool key_live = key < p.Lk;
+            const int64_t out_row = (int64_t(it.b) * p.Hkv + it.h) * p.Lk + key;
+            char* out = static_cast<char*>(wg == 0 ? p.dv : p.dk) + out_row * HD * 2;
+            if (it.n == 0) {   // no query sees these keys: their gradients are zero
+                if (key_live)
+#pragma unroll
+                    for (int v = 0; v < HD / 8; ++v) reinterpret_cast<uint4*>(out)[v] = make_uint4(0, 0, 0, 0);
+                continue;
+            }
+            const int i0 = first_query_tile(p, it.t), cnt = p.nq - i0;
+            for (int x = 0; x < it.n; ++x, ++rc) {
+                const int i = i0 + x % cnt;
+                const int stage = rc & 1u;
+                // (the statistics were written by the load warp before it armed this barrier)
+                ok = mbar_wait(bar(kBarRingFull + stage), (rc >> 1) & 1u, abort_flag, 10);
+                if (!ok) break;
+                const float4* st_lse = reinterpret_cast<const float4*>(smem_gen + kSmemStats + stage * kStatsBytes) + col0 / 4;
+                const float4* st_del = st_lse + BT / 4;
+                ok = mbar_wait(bar(kBarSFull), rc & 1u, abort_flag, 11);
+                if (!ok) break;
+                tc_fence_after_sync();
+                uint32_t s[64];
+                tmem_ld32(s_addr, reinterpret_cast<uint32_t(&)[32]>(s[0]));
+                tmem_ld32(s_addr + 32, reinterpret_cast<uint32_t(&)[32]>(s[32]));
+                tmem_wait_ld();
+                tmem_ld_fence32(reinterpret_cast<uint32_t(&)[32]>(s[0]));
+                tmem_ld_fence32(reinterpret_cast<uint32_t(&)[32]>(s[32]));
+                // P^T[key, q] = exp2(S * c - lse2[q]); zero where the query does not see the key
+                const int q0 = i * BT + col0;
+                const bool diag = p.causal && q0 < it.t * BT + BT;   // some query of these columns precedes some key
+                uint32_t pk[32];
+#pragma unroll
+                for (int v = 0; v < 16; ++v) {
+                    const float4 l4 = st_lse[v];
+                    const float ls[4] = {l4.x, l4.y, l4.z, l4.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int c = 4 * v + e;
+                        float pv = ex2_approx(fmaf(__uint_as_float(s[c]), c2, -ls[e]));
+                        if (!key_live || (diag && q0 + c < key)) pv = 0.f;
+                        s[c] = __float_as_uint(pv);
+                    }
+                    pk[2 * v] = pack16<BF16>(__uint_as_float(s[4 * v]), __uint_as_float(s[4 * v + 1]));
+                    pk[2 * v + 1] = pack16<BF16>(__uint_as_float(s[4 * v + 2]), __uint_as_float(s[4 * v + 3]));
+                }
+                // 16-bit P^T over the first half of the fp32 columns this warp has just read
+                tmem_st16(s_addr, reinterpret_cast<uint32_t(&)[16]>(pk[0]));
+                tmem_st16(s_addr + 16, reinterpret_cast<uint32_t(&)[16]>(pk[16]));
+                tmem_wait_st();
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar(kBarPFull));
+                // dS^T = P^T o (dP^T - delta[q]) * scale, with the unrounded P
+                ok = mbar_wait(bar(kBarDpFull), rc & 1u, abort_flag, 12);
+                if (!ok) break;
+                tc_fence_after_sync();
+                uint32_t dp[64];
+                tmem_ld32(dp_addr, reinterpret_cast<uint32_t(&)[32]>(dp[0]));
+                tmem_ld32(dp_addr + 32, reinterpret_cast<uint32_t(&)[32]>(dp[32]));
+                tmem_wait_ld();
+                tmem_ld_fence32(reinterpret_cast<uint32_t(&)[32]>(dp[0]));
+                tmem_ld_fence32(reinterpret_cast<uint32_t(&)[32]>(dp[32]));
+#pragma unroll
+                for (int v = 0; v < 16; ++v) {
+                    const float4 d4 = st_del[v];
+                    const float dl[4] = {d4.x, d4.y, d4.z, d4.w};
+                    float ds[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int c = 4 * v + e;
+                        ds[e] = __uint_as_float(s[c]) * (__uint_as_float(dp[c]) - dl[e]) * p.scale;
+                    }
+                    pk[2 * v] = pack16<BF16>(ds[0], ds[1]);
+                    pk[2 * v + 1] = pack16<BF16>(ds[2], ds[3]);
+                }
+                tmem_st16(dp_addr, reinterpret_cast<uint32_t(&)[16]>(pk[0]));
+                tmem_st16(dp_addr + 16, reinterpret_cast<uint32_t(&)[16]>(pk[16]));
+                tmem_wait_st();
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar(kBarDsFull));
+            }
+            if (!ok) break;
+            // read the item's accumulator out: warps 0-3 dV, warps 4-7 dK (one key row per lane)
+            ok = mbar_wait(bar(kBarAccFull), items & 1u, abort_flag, 13);
+            if (!ok) break;
+            ++items;
+            tc_fence_after_sync();
+            const uint32_t acc_addr = tmem + lane_base + (wg == 0 ? kColDv : kColDk);
+#pragma unroll 1
+            for (int c = 0; c < HD / 32; ++c) {
+                uint32_t o[32];
+                tmem_ld32(acc_addr + 32 * c, o);
+                tmem_wait_ld();
+                tmem_ld_fence32(o);
+                if (key_live) store_row32<BF16>(out + c * 64, o);
+            }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(kBarAccEmpty));
+        }
+    }
+
+    // ------------------------------ common exit ------------------------------------------------
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == kMmaWarp) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem, kTmemCols);
+    }
+    if (threadIdx.x == 0 && *abort_flag) {
+        *p.status = *abort_flag;
+        __threadfence_system();
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// dQ: own pair = (Q_i, dO_i), streamed pair = (K_j, V_j).
+// ---------------------------------------------------------------------------------------------
+template <bool BF16, int HD>
+__global__ void __launch_bounds__(kThreads, 1)
+sdpa_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                   const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
+                   const BwdParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    auto bar = [&](int i) { return smem_base + kSmemBars + 8u * i; };
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + kSmemMisc);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + kSmemMisc + 4);
+    constexpr int kChunks = HD / 64;
+    constexpr uint32_t kLoadBytes = kChunks * kChunkBytes;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int r = p.Hq / p.Hkv;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < kNumBars; ++i) {
+            const bool eight = i == kBarPFull || i == kBarDsFull || i == kBarAccEmpty;
+            mbar_init(bar(i), eight ? 8u : 1u);
+        }
+        *abort_flag = 0;
+        mbar_fence_init();
+        fence_proxy_async_smem();
+    }
+    if (warp == kMmaWarp) {
+        tmem_alloc(smem_base + kSmemMisc, kTmemCols);
+        tmem_relinquish();
+    }
+    if (warp == kLoadWarp && lane == 0) {
+        tma_prefetch_desc(&map_q);
+        tma_prefetch_desc(&map_k);
+        tma_prefetch_desc(&map_v);
+        tma_prefetch_desc(&map_do);
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = *tmem_slot;
+    constexpr int kColS = 0, kColDp = 128, kColDq = 256, kColDs = 384;   // dS: two buffers of 64 columns
+
+    if (warp == kLoadWarp) {
+        // ------------------------------ loads ------------------------------------------------
+        if (lane == 0) {
+            bool ok = true;
+            uint32_t items = 0, rc = 0;
+            Item it;
+            for (int seq = 0; ok && get_item<false>(p, seq, &it); ++seq) {
+                if (it.n <= 0) continue;
+                const int hk = it.h / r;
+                ok = mbar_wait(bar(kBarOwnEmpty), (items & 1u) ^ 1u, abort_flag, 0);
+                if (!ok) break;
+                ++items;
+                mbar_arrive_expect_tx(bar(kBarOwnFull), 2 * kLoadBytes);
+#pragma unroll
+                for (int c = 0; c < kChunks; ++c) {
+                    tma_load_4d(smem_base + kSmemOwn + c * kChunkBytes, &map_q, bar(kBarOwnFull), 64 * c, it.t * BT, it.h, it.b);
+                    tma_load_4d(smem_base + kSmemOwn + kTileBytes + c * kChunkBytes, &map_do, bar(kBarOwnFull), 64 * c, it.t * BT, it.h, it.b);
+                }
+                for (int x = 0; ok && x < it.n; ++x, ++rc) {
+                    const int stage = rc & 1u;
+                    ok = mbar_wait(bar(kBarRingEmpty + stage), ((rc >> 1) & 1u) ^ 1u, abort_flag, 1);
+                    if (!ok) break;
+                    const uint32_t full = bar(kBarRingFull + stage);
+                    mbar_arrive_expect_tx(full, 2 * kLoadBytes);
+                    const uint32_t dst = smem_base + kSmemRing + stage * kStageBytes;
+#pragma unroll
+                    for (int c = 0; c < kChunks; ++c) {
+                        tma_load_4d(dst + c * kChunkBytes, &map_k, full, 64 * c, x * BT, hk, it.b);
+                        tma_load_4d(dst + kTileBytes + c * kChunkBytes, &map_v, full, 64 * c, x * BT, hk, it.b);
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == kMmaWarp) {
+        // ------------------------------ MMA issuer -------------------------------------------
+        if (lane == 0) {
+            constexpr uint32_t idesc_kk = instr_desc_f16(BF16 ? 1 : 0, BT, BT, false, false);
+            constexpr uint32_t idesc_acc = instr_desc_f16(BF16 ? 1 : 0, BT, HD, false, true);
+            const uint32_t own_q = smem_base + kSmemOwn, own_do = own_q + kTileBytes;
+            // D[128 queries x 128 keys] = own[queries x HD] * streamed[keys x HD]^T
+            auto issue_t = [&](uint32_t d_col, uint32_t a_tile, uint32_t b_tile) {
+#pragma unroll
+                for (int c = 0; c < kChunks; ++c)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const uint32_t off = c * kChunkBytes + i * 32;
+                        mma_ss(tmem + d_col, smem_desc_sw128(a_tile + off, 16, 1024),
+                               smem_desc_sw128(b_tile + off, 16, 1024), idesc_kk, (c | i) ? 1u : 0u);
+                    }
+            };
+            bool ok = true;
+            uint32_t items = 0, rc = 0, pc = 0, dc = 0;
+            Item it;
+            for (int seq = 0; ok && get_item<false>(p, seq, &it); ++seq) {
+                if (it.n <= 0) continue;
+                auto ring_tile = [&](uint32_t c) { return smem_base + kSmemRing + (c & 1u) * kStageBytes; };
+                ok = mbar_wait(bar(kBarOwnFull), items & 1u, abort_flag, 2);
+                if (!ok) break;
+                ok = mbar_wait(bar(kBarRingFull + (rc & 1u)), (rc >> 1) & 1u, abort_flag, 3);
+                if (!ok) break;
+                tc_fence_after_sync();
+                issue_t(kColS, own_q, ring_tile(rc));
+                tc_commit(bar(kBarSFull));
+                issue_t(kColDp, own_do, ring_tile(rc) + kTileBytes);
+                tc_commit(bar(kBarDpFull));
+                for (int x = 0; ok && x < it.n; ++x) {
+                    const uint32_t cur = rc + x;
+                    // the element-wise warps hold S and dP of this step in registers: the next
+                    // step's products may overwrite them while this step's dS is being formed
+                    ok = mbar_wait(bar(kBarPFull), pc & 1u, abort_flag, 4);
+                    if (!ok) break;
+                    ++pc;
+                    if (x + 1 < it.n) {
+                        ok = mbar_wait(bar(kBarRingFull + ((cur + 1) & 1u)), ((cur + 1) >> 1) & 1u, abort_flag, 3);
+                        if (!ok) break;
+                        tc_fence_after_sync();
+                        issue_t(kColS, own_q, ring_tile(cur + 1));
+                        tc_commit(bar(kBarSFull));
+                        issue_t(kColDp, own_do, ring_tile(cur + 1) + kTileBytes);
+                        tc_commit(bar(kBarDpFull));
+                    }
+                    ok = mbar_wait(bar(kBarDsFull), dc & 1u, abort_flag, 6);
+                    if (!ok) break;
+                    ++dc;
+                    if (x == 0 && items > 0) {   // the previous item's dQ has been read out
+                        ok = mbar_wait(bar(kBarAccEmpty), (items - 1) & 1u, abort_flag, 5);
+                        if (!ok) break;
+                    }
+                    tc_fence_after_sync();
+                    // dQ += dS K_j: dS (16-bit) from TMEM, K_j as [keys x HD] rows
+                    const uint32_t ds_col = kColDs + (cur & 1u) * 64;
+                    const uint32_t kt = ring_tile(cur);
+#pragma unroll
+                    for (int ks = 0; ks < BT / 16; ++ks)
+                        mma_ts(tmem + kColDq, tmem + ds_col + ks * 8,
+                               smem_desc_sw128(kt + ks * 16 * 128, kChunkBytes, 1024), idesc_acc, (x > 0 || ks) ? 1u : 0u);
+                    tc_commit(bar(kBarRingEmpty + (cur & 1u)));
+                }
+                if (!ok) break;
+                rc += it.n;
+                tc_commit(bar(kBarAccFull));
+                tc_commit(bar(kBarOwnEmpty));
+                ++items;
+            }
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------ element-wise warps -----------------------------------
+        const int wg = warp >> 2, wq = warp & 3;
+        const uint32_t lane_base = uint32_t(wq * 32) << 16;
+        const int col0 = wg * 64;                        // this warp's key columns of the tile
+        const uint32_t s_addr = tmem + lane_base + kColS + col0;
+        const uint32_t dp_addr = tmem + lane_base + kColDp + col0;
+        const float c2 = p.scale_log2;
+        bool ok = true;
+        uint32_t items = 0, rc = 0;
+        Item it;
+        for (int seq = 0; ok && get_item<false>(p, seq, &it); ++seq) {
+            if (it.n <= 0) continue;
+            const int row = it.t * BT + wq * 32 + lane;
+            const bool live = row < p.Lq;
+            const int64_t grow = (int64_t(it.b) * p.Hq + it.h) * p.Lq + row;
+            const float lse2 = live ? p.lse[grow] * 1.4426950408889634f : INFINITY;
+            const float delta = live ? p.delta[grow] : 0.f;
+            for (int x = 0; x < it.n; ++x, ++rc) {
+                ok = mbar_wait(bar(kBarSFull), rc & 1u, abort_flag, 11);
+                if (!ok) break;
+                tc_fence_after_sync();
+                uint32_t s[64], dp[64];
+                tmem_ld32(s_addr, reinterpret_cast<uint32_t(&)[32]>(s[0]));
+                tmem_ld32(s_addr + 32, reinterpret_cast<uint32_t(&)[32]>(s[32]));
+                ok = mbar_wait(bar(kBarDpFull), rc & 1u, abort_flag, 12);
+                if (!ok) break;
+                tc_fence_after_sync();
+                tmem_ld32(dp_addr, reinterpret_cast<uint32_t(&)[32]>(dp[0]));
+                tmem_ld32(dp_addr + 32, reinterpret_cast<uint32_t(&)[32]>(dp[32]));
+                tmem_wait_ld();
+                tmem_ld_fence32(reinterpret_cast<uint32_t(&)[32]>(s[0]));
+                tmem_ld_fence32(reinterpret_cast<uint32_t(&)[32]>(s[32]));
+                tmem_ld_fence32(reinterpret_cast<uint32_t(&)[32]>(dp[0]));
+                tmem_ld_fence32(reinterpret_cast<uint32_t(&)[32]>(dp[32]));
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar(kBarPFull));   // S and dP are in registers
+                // P = exp2(S * c - lse2), zero where the query does not see the key;
+                // dS = P o (dP - delta) * scale
+                const int k0 = x * BT + col0;
+                const int limit = (p.causal ? min(row, p.Lk - 1) : p.Lk - 1) - k0;   // last visible column
+                uint32_t pk[32];
+#pragma unroll
+                for (int c = 0; c < 64; c += 2) {
+                    float p0 = ex2_approx(fmaf(__uint_as_float(s[c]), c2, -lse2));
+                    float p1 = ex2_approx(fmaf(__uint_as_float(s[c + 1]), c2, -lse2));
+                    if (c > limit) p0 = 0.f;
+                    if (c + 1 > limit) p1 = 0.f;
+                    const float d0 = p0 * (__uint_as_float(dp[c]) - delta) * p.scale;
+                    const float d1 = p1 * (__uint_as_float(dp[c + 1]) - delta) * p.scale;
+                    pk[c >> 1] = pack16<BF16>(d0, d1);
+                }
+                const uint32_t ds_addr = tmem + lane_base + kColDs + (rc & 1u) * 64 + wg * 32;
+                tmem_st16(ds_addr, reinterpret_cast<uint32_t(&)[16]>(pk[0]));
+                tmem_st16(ds_addr + 16, reinterpret_cast<uint32_t(&)[16]>(pk[16]));
+                tmem_wait_st();
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar(kBarDsFull));
+            }
+            if (!ok) break;
+            ok = mbar_wait(bar(kBarAccFull), items & 1u, abort_flag, 13);
+            if (!ok) break;
+            ++items;
+            tc_fence_after_sync();
+            // warps 0-3 store the first half of the head dim, warps 4-7 the second
+            const uint32_t acc_addr = tmem + lane_base + kColDq + wg * (HD / 2);
+            char* out = static_cast<char*>(p.dq) + (grow * HD + wg * (HD / 2)) * 2;
+#pragma unroll 1
+            for (int c = 0; c < HD / 64; ++c) {
+                uint32_t o[32];
+                tmem_ld32(acc_addr + 32 * c, o);
+                tmem_wait_ld();
+                tmem_ld_fence32(o);
+                if (live) store_row32<BF16>(out + c * 64, o);
+            }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(kBarAccEmpty));
+        }
+    }
+
+    // ------------------------------ common exit ------------------------------------------------
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == kMmaWarp) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem, kTmemCols);
+    }
+    if (threadIdx.x == 0 && *abort_flag) {
+        *p.status = *abort_flag;
+        __threadfence_system();
+    }
+}
+
+}  // namespace
+
+bool sdpa_bwd_tc_supported(const Gpu* g, const paras_sdpa_bwd_args& a) {
+    if (g->cc_major != 10) return false;
+    if (a.dtype != PARAS_BF16 && a.dtype != PARAS_F16) return false;
+    if (a.D != 128 && a.D != 64) return false;
+    if (a.Lq < 1 || a.Lk < 1 || a.Hkv < 1 || a.Hq % a.Hkv) return false;
+    if (!(a.scale > 0.0) || !std::isfinite(a.scale)) return false;
+    if (g->smem_optin < size_t(kSmemLaunch)) return false;
+    return true;
+}
+
+// dq, dk, dv from dense [B, H, L, D] tensors; `delta` = rowsum(dO o O), fp32 [B, Hq, Lq].
+int sdpa_bwd_tc_launch(Gpu* g, const paras_sdpa_bwd_args& a, const float* delta, cudaStream_t s) {
+    int st = check_status_word(g);
+    if (st != PARAS_OK) return st;
+    const int64_t sq[3] = {int64_t(a.Hq) * a.Lq * a.D, int64_t(a.Lq) * a.D, a.D};
+    const int64_t sk[3] = {int64_t(a.Hkv) * a.Lk * a.D, int64_t(a.Lk) * a.D, a.D};
+    CUtensorMap mq, mk, mv, mdo;
+    if ((st = make_tensor_map_bhld(&mq, a.q, a.dtype, a.B, a.Hq, a.Lq, a.D, sq, BT)) != PARAS_OK) return st;
+    if ((st = make_tensor_map_bhld(&mk, a.k, a.dtype, a.B, a.Hkv, a.Lk, a.D, sk, BT)) != PARAS_OK) return st;
+    if ((st = make_tensor_map_bhld(&mv, a.v, a.dtype, a.B, a.Hkv, a.Lk, a.D, sk, BT)) != PARAS_OK) return st;
+    if ((st = make_tensor_map_bhld(&mdo, a.dout, a.dtype, a.B, a.Hq, a.Lq, a.D, sq, BT)) != PARAS_OK) return st;
+    BwdParams p{};
+    p.dq = a.dq; p.dk = a.dk; p.dv = a.dv;
+    p.lse = a.lse; p.delta = delta;
+    p.B = a.B; p.Hq = a.Hq; p.Hkv = a.Hkv; p.Lq = a.Lq; p.Lk = a.Lk;
+    p.causal = a.causal;
+    p.scale = float(a.scale);
+    p.scale_log2 = p.scale * 1.4426950408889634f;
+    p.status = g->status_dev;
+    p.nq = (a.Lq + BT - 1) / BT;
+    p.nk = (a.Lk + BT - 1) / BT;
+    const int sms = g->sm_count > 0 ? g->sm_count : 148;
+    const bool bf = a.dtype == PARAS_BF16;
+    auto launch = [&](auto kernel, int64_t units) -> int {
+        if (units > INT32_MAX) return fail(PARAS_E_UNSUPPORTED, "paras sdpa backward: too many work units");
+        p.units = int(units);
+        PB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLaunch));
+        kernel<<<unsigned(units < sms ? units : sms), kThreads, kSmemLaunch, s>>>(mq, mk, mv, mdo, p);
+        return PARAS_OK;
+    };
+    // dK, dV: units of paired key tiles per (batch, kv head)
+    p.npair = (p.nk + 1) / 2;
+    const int64_t u_kv = int64_t(a.B) * a.Hkv * p.npair;
+    if (a.D == 128) st = bf ? launch(sdpa_bwd_dkv_kernel<true, 128>, u_kv) : launch(sdpa_bwd_dkv_kernel<false, 128>, u_kv);
+    else st = bf ? launch(sdpa_bwd_dkv_kernel<true, 64>, u_kv) : launch(sdpa_bwd_dkv_kernel<false, 64>, u_kv);
+    if (st != PARAS_OK) return st;
+    PB_LAUNCH_CHECK("sdpa_bwd_dkv_kernel");
+    // dQ: units of paired query tiles per (batch, query head)
+    p.npair = (p.nq + 1) / 2;
+    const int64_t u_q = int64_t(a.B) * a.Hq * p.npair;
+    if (a.D == 128) st = bf ? launch(sdpa_bwd_dq_kernel<true, 128>, u_q) : launch(sdpa_bwd_dq_kernel<false, 128>, u_q);
+    else st = bf ? launch(sdpa_bwd_dq_kernel<true, 64>, u_q) : launch(sdpa_bwd_dq_kernel<false, 64>, u_q);
+    if (st != PARAS_OK) return st;
+    PB_LAUNCH_CHECK("sdpa_bwd_dq_kernel");
+    return PARAS_OK;
+}
+
+}  // namespace pb

@@ -231,9 +231,13 @@ def sdpa_fwd_host(q, k, v, *, causal=False, scale=None, flags=0, out=None, gpu=0
     return out
 
 
-def sdpa_bwd(dout, q, k, v, out, lse, *, causal=False, scale=None, stream=None):
+SDPA_BWD_COMPOSITE = 1
+
+
+def sdpa_bwd(dout, q, k, v, out, lse, *, causal=False, scale=None, stream=None, composite=False):
     """(dq, dk, dv) through ``paras_b200_sdpa_bwd``; contiguous [B,H,L,D] tensors, ``lse`` from
-    ``sdpa_fwd(..., return_lse=True)`` with the same causal flag and scale."""
+    ``sdpa_fwd(..., return_lse=True)`` with the same causal flag and scale.  ``composite`` forces
+    the five-GEMM path that other head dims than 128 / 64 take."""
     for t in (dout, q, k, v, out):
         if not t.is_contiguous():
             raise RuntimeError("paras abi: sdpa_bwd takes contiguous tensors")
@@ -248,6 +252,7 @@ def sdpa_bwd(dout, q, k, v, out, lse, *, causal=False, scale=None, stream=None):
     a.causal = 1 if causal else 0
     a.scale = float(scale) if scale is not None else 1.0 / (q.shape[-1] ** 0.5)
     a.gpu = _gpu_of(q)
+    a.reserved = SDPA_BWD_COMPOSITE if composite else 0
     a.stream = _stream_of(q, stream)
     check(lib().paras_b200_sdpa_bwd(C.byref(a)))
     return dq, dk, dv

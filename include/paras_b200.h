@@ -232,9 +232,13 @@ int paras_b200_rotate_half(int gpu, const void* x, void* out, int64_t rows, int6
  * 71-136) and its softmax backward (csrc/ops/pointwise_ops.cpp:994-1062).  q, out, dout, dq:
  * dense [B,Hq,Lq,D]; k, v, dk, dv: dense [B,Hkv,Lk,D]; lse: f32 [B,Hq,Lq] as returned by
  * paras_b200_sdpa_fwd (args->lse) for the same inputs, causal flag and scale.  dtype BF16 or F16;
- * D and Lk multiples of 8, all pointers 16-byte aligned (else PARAS_E_UNSUPPORTED).  Scratch
- * (two [rows, Lk] matrices for a chunk of kv-head groups, about 1 GB each at most) comes from
- * the GPU's pool, stream-ordered.  No mask tensor, no dropout. */
+ * D a multiple of 8 (the composite path: Lk too), all pointers 16-byte aligned (else PARAS_E_UNSUPPORTED).
+ * D = 128 or 64: two fused tcgen05 kernels (dK/dV, then dQ) that rebuild the probabilities tile by
+ * tile in TMEM; deterministic, no atomics, scratch = one fp32 per query row.  Other head dims, or
+ * `reserved` = PARAS_SDPA_BWD_COMPOSITE: five batched GEMMs over two [rows, Lk] matrices
+ * materialised per chunk of kv-head groups (about 1 GB each at most).  Scratch comes from the
+ * GPU's pool, stream-ordered.  No mask tensor, no dropout. */
+enum { PARAS_SDPA_BWD_COMPOSITE = 1 };
 typedef struct paras_sdpa_bwd_args {
     const void* q;
     const void* k;
@@ -250,7 +254,7 @@ typedef struct paras_sdpa_bwd_args {
     int32_t causal;
     double scale;
     int32_t gpu;
-    int32_t reserved;
+    int32_t reserved; /* flags: PARAS_SDPA_BWD_COMPOSITE */
     void* stream;
 } paras_sdpa_bwd_args;
 int paras_b200_sdpa_bwd(const paras_sdpa_bwd_args* args);

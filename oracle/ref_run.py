@@ -46,6 +46,18 @@ def run_op(op, a):
             kw["enable_gqa"] = True
         return lambda: F.scaled_dot_product_attention(
             q, k, v, attn_mask=mask, is_causal=bool(a.get("is_causal", False)), **kw)
+    if op == "sdpa_grad":
+        # gradients by autograd through the reference's composite attention (attention_ops.cpp:71-136
+        # and the backward kernels its operators register, e.g. softmax backward, pointwise_ops.cpp:
+        # 994-1062): returns (out, dq, dk, dv)
+        kw = {"enable_gqa": True} if a.get("enable_gqa") else {}
+
+        def run():
+            q, k, v = (_dev(a[n]).detach().requires_grad_(True) for n in ("q", "k", "v"))
+            out = F.scaled_dot_product_attention(q, k, v, is_causal=bool(a.get("is_causal", False)), **kw)
+            out.backward(_dev(a["dout"]))
+            return out.detach(), q.grad, k.grad, v.grad
+        return run
     if op == "rms_norm_aten":
         x, w = _dev(a["x"]), _dev(a.get("weight"))
         return lambda: torch.ops.aten.rms_norm(x, list(a["normalized_shape"]), w, a.get("eps"))

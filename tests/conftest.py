@@ -45,4 +45,8 @@ def load_golden(name):
 
 
 def golden_names(prefix=""):
-    return sorted(f[:-3] for f in os.listdir(GOLDEN) if f.endswith(".pt") and f.startswith(prefix))
+    """Fixture names.  Without a prefix: the forward operators' fixtures, the ones the oracle is pinned
+    to; the attention-gradient fixtures ("sdpa_grad_...", the reference's autograd output, for which
+    the oracle holds no restatement) are listed only when asked for by prefix."""
+    names = sorted(f[:-3] for f in os.listdir(GOLDEN) if f.endswith(".pt") and f.startswith(prefix))
+    return names if prefix else [n for n in names if not n.startswith("sdpa_grad")]

@@ -83,7 +83,31 @@ def cases():
     return out
 
 
+def grad_cases():
+    """Attention gradients of the reference (autograd through its composite).  A generator of their
+    own, so that adding cases here leaves the draws of cases() unchanged."""
+    g = torch.Generator().manual_seed(20261126)
+
+    def R(*shape, dt=torch.float32):
+        return torch.randn(*shape, generator=g).to(dt)
+
+    # 3-D (batch, seq, dim) inputs: the reference differentiates those; with 4-D inputs its own
+    # backward of the batched product fails ("BmmBackward0 returned an invalid gradient ... got
+    # [2, 200, 200] but expected shape compatible with [1, 2, 200, 200]"), so there is nothing to pin
+    out = []
+    for dt, tag in ((torch.bfloat16, "bf16"),):   # the gradient kernels take 16-bit tensors only
+        # two query tiles over two key tiles, causal: the diagonal tiles and an off-diagonal one
+        q, k, v, d = R(1, 200, 128, dt=dt), R(1, 200, 128, dt=dt), R(1, 200, 128, dt=dt), R(1, 200, 128, dt=dt)
+        out.append((f"sdpa_grad_causal_{tag}", "sdpa_grad", {"q": q, "k": k, "v": v, "dout": d, "is_causal": True}))
+        # full attention, Lq != Lk, head dim 64
+        q, k, v, d = R(2, 72, 64, dt=dt), R(2, 136, 64, dt=dt), R(2, 136, 64, dt=dt), R(2, 72, 64, dt=dt)
+        out.append((f"sdpa_grad_full_d64_{tag}", "sdpa_grad", {"q": q, "k": k, "v": v, "dout": d}))
+    return out
+
+
 def main():
+    if "--grad" in sys.argv:     # only the gradient fixtures
+        globals()["cases"] = grad_cases
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
     import ref_loader
     if not ref_loader.available():
