@@ -74,6 +74,20 @@ constexpr int kSmemMisc = kSmemBars + kNumBars * 8;
 constexpr int kSmemTotal = kSmemMisc + 16;
 constexpr int kSmemLaunch = kSmemTotal + 1024;
 
+// The dQ kernel streams K and V through rings of their own: V_j is done with after dP = dO V_j^T,
+// K_j only after dQ += dS K_j at the end of the step, so K gets three stages and V two (with one
+// two-stage ring for the pair, every step waited about 1300 cycles for a load that could only
+// start once the step before last had released its stage).
+constexpr int kDqKStages = 3, kDqVStages = 2;
+constexpr int kDqSmemK = 2 * kTileBytes;
+constexpr int kDqSmemV = kDqSmemK + kDqKStages * kTileBytes;
+constexpr int kDqSmemBars = kDqSmemV + kDqVStages * kTileBytes;
+constexpr int kDqBarOwnFull = 0, kDqBarOwnEmpty = 1, kDqBarKFull = 2, kDqBarKEmpty = 5, kDqBarVFull = 8,
+              kDqBarVEmpty = 10, kDqBarSFull = 12, kDqBarDpFull = 13, kDqBarTaken = 14, kDqBarDsFull = 15,
+              kDqBarAccFull = 16, kDqBarAccEmpty = 17, kDqNumBars = 18;
+constexpr int kDqSmemMisc = kDqSmemBars + kDqNumBars * 8;
+constexpr int kDqSmemLaunch = kDqSmemMisc + 16 + 1024;
+
 struct BwdParams {
     void* dq;
     void* dk;
@@ -226,16 +240,17 @@ sdpa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 if (lane == 0) ok = mbar_wait(bar(kBarRingEmpty + stage), ((rc >> 1) & 1u) ^ 1u, abort_flag, 1);
                 ok = __shfl_sync(0xffffffffu, ok, 0);
                 if (!ok) break;
-                // per-query statistics of this tile, in the form the element-wise warps use them:
-                // lse in the base-2 domain (+inf past the last query: its probabilities are 0) and delta
+                // per-query statistics of this tile, in the form the element-wise warps add them:
+                // -lse in the base-2 domain (-inf past the last query: its probabilities are 0) and
+                // -delta * scale
                 float* st = reinterpret_cast<float*>(smem_gen + kSmemStats + stage * kStatsBytes);
                 const int64_t row0 = (int64_t(it.b) * p.Hq + h) * p.Lq;
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const int q = i * BT + lane * 4 + e;
                     const bool live = q < p.Lq;
-                    st[lane * 4 + e] = live ? p.lse[row0 + q] * 1.4426950408889634f : INFINITY;
-                    st[BT + lane * 4 + e] = live ? p.delta[row0 + q] : 0.f;
+                    st[lane * 4 + e] = live ? -p.lse[row0 + q] * 1.4426950408889634f : -INFINITY;
+                    st[BT + lane * 4 + e] = live ? -p.delta[row0 + q] * p.scale : 0.f;
                 }
                 __syncwarp();
                 if (lane == 0) {
@@ -256,26 +271,33 @@ sdpa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             constexpr uint32_t idesc_kk = instr_desc_f16(BF16 ? 1 : 0, BT, BT, false, false);
             constexpr uint32_t idesc_acc = instr_desc_f16(BF16 ? 1 : 0, BT, HD, false, true);
             const uint32_t own_k = smem_base + kSmemOwn, own_v = own_k + kTileBytes;
+            // Descriptors as 32-bit halves (tc_prims.cuh): the high word is shared by all operands
+            // (stride between 8-row groups = 1024 B), the low word of a tile is computed once per
+            // step and advanced by one add per MMA.
+            constexpr uint32_t hi = desc_hi_sw128(1024);
             // D[128 keys x 128 queries] = own[keys x HD] * streamed[queries x HD]^T
             auto issue_t = [&](uint32_t d_col, uint32_t a_tile, uint32_t b_tile) {
+                const uint32_t a0 = desc_lo_sw128(a_tile, 16), b0 = desc_lo_sw128(b_tile, 16);
 #pragma unroll
                 for (int c = 0; c < kChunks; ++c)
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
-                        const uint32_t off = c * kChunkBytes + i * 32;
-                        mma_ss(tmem + d_col, smem_desc_sw128(a_tile + off, 16, 1024),
-                               smem_desc_sw128(b_tile + off, 16, 1024), idesc_kk, (c | i) ? 1u : 0u);
+                        const uint32_t step = desc_step(c * kChunkBytes + i * 32);
+                        if (c | i) mma_ss_lo<true>(tmem + d_col, a0 + step, b0 + step, hi, idesc_kk);
+                        else mma_ss_lo<false>(tmem + d_col, a0 + step, b0 + step, hi, idesc_kk);
                     }
             };
             // D[128 keys x HD] (+)= A^T[keys x 128 queries] (16-bit, in TMEM) * streamed[queries x HD]
             auto issue_acc = [&](uint32_t d_col, uint32_t a_col, uint32_t b_tile, bool acc) {
+                const uint32_t b0 = desc_lo_sw128(b_tile, kChunkBytes);
 #pragma unroll
                 for (int ks = 0; ks < BT / 16; ++ks) {
                     // queries 0-63 sit in packed columns 0-31, queries 64-127 in columns 64-95: each
                     // half overlays the fp32 columns the warps that wrote it had read themselves
                     const uint32_t a = tmem + a_col + (ks < 4 ? ks * 8 : 64 + (ks - 4) * 8);
-                    mma_ts(tmem + d_col, a, smem_desc_sw128(b_tile + ks * 16 * 128, kChunkBytes, 1024), idesc_acc,
-                           (acc || ks) ? 1u : 0u);
+                    const uint32_t b = b0 + desc_step(ks * 16 * 128);
+                    if (ks) mma_ts_lo<true>(tmem + d_col, a, b, hi, idesc_acc);
+                    else mma_ts_lo(tmem + d_col, a, b, hi, idesc_acc, acc ? 1u : 0u);
                 }
             };
             bool ok = true;
@@ -371,23 +393,28 @@ sdpa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 tmem_wait_ld();
                 tmem_ld_fence32(reinterpret_cast<uint32_t(&)[32]>(s[0]));
                 tmem_ld_fence32(reinterpret_cast<uint32_t(&)[32]>(s[32]));
-                // P^T[key, q] = exp2(S * c - lse2[q]); zero where the query does not see the key
+                // P^T[key, q] = exp2(S * c - lse2[q]); zero where the query does not see the key.
+                // Two columns per instruction on the FMA pipe (fp32x2).
                 const int q0 = i * BT + col0;
                 const bool diag = p.causal && q0 < it.t * BT + BT;   // some query of these columns precedes some key
+                const bool need_mask = diag || it.t * BT + BT > p.Lk;   // the same for the whole warp
+                const float2 c22 = make_float2(c2, c2);
                 uint32_t pk[32];
 #pragma unroll
                 for (int v = 0; v < 16; ++v) {
                     const float4 l4 = st_lse[v];
-                    const float ls[4] = {l4.x, l4.y, l4.z, l4.w};
+                    const float2 e0 = ffma2(make_float2(__uint_as_float(s[4 * v]), __uint_as_float(s[4 * v + 1])), c22, make_float2(l4.x, l4.y));
+                    const float2 e1 = ffma2(make_float2(__uint_as_float(s[4 * v + 2]), __uint_as_float(s[4 * v + 3])), c22, make_float2(l4.z, l4.w));
+                    float pv[4] = {ex2_approx(e0.x), ex2_approx(e0.y), ex2_approx(e1.x), ex2_approx(e1.y)};
+                    if (need_mask) {
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const int c = 4 * v + e;
-                        float pv = ex2_approx(fmaf(__uint_as_float(s[c]), c2, -ls[e]));
-                        if (!key_live || (diag && q0 + c < key)) pv = 0.f;
-                        s[c] = __float_as_uint(pv);
+                        for (int e = 0; e < 4; ++e)
+                            if (!key_live || (diag && q0 + 4 * v + e < key)) pv[e] = 0.f;
                     }
-                    pk[2 * v] = pack16<BF16>(__uint_as_float(s[4 * v]), __uint_as_float(s[4 * v + 1]));
-                    pk[2 * v + 1] = pack16<BF16>(__uint_as_float(s[4 * v + 2]), __uint_as_float(s[4 * v + 3]));
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) s[4 * v + e] = __float_as_uint(pv[e]);
+                    pk[2 * v] = pack16<BF16>(pv[0], pv[1]);
+                    pk[2 * v + 1] = pack16<BF16>(pv[2], pv[3]);
                 }
                 // 16-bit P^T over the first half of the fp32 columns this warp has just read
                 tmem_st16(s_addr, reinterpret_cast<uint32_t(&)[16]>(pk[0]));
@@ -406,18 +433,16 @@ sdpa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 tmem_wait_ld();
                 tmem_ld_fence32(reinterpret_cast<uint32_t(&)[32]>(dp[0]));
                 tmem_ld_fence32(reinterpret_cast<uint32_t(&)[32]>(dp[32]));
+                const float2 sc2 = make_float2(p.scale, p.scale);
 #pragma unroll
                 for (int v = 0; v < 16; ++v) {
-                    const float4 d4 = st_del[v];
-                    const float dl[4] = {d4.x, d4.y, d4.z, d4.w};
-                    float ds[4];
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const int c = 4 * v + e;
-                        ds[e] = __uint_as_float(s[c]) * (__uint_as_float(dp[c]) - dl[e]) * p.scale;
-                    }
-                    pk[2 * v] = pack16<BF16>(ds[0], ds[1]);
-                    pk[2 * v + 1] = pack16<BF16>(ds[2], ds[3]);
+                    const float4 d4 = st_del[v];   // -delta * scale
+                    const float2 t0 = ffma2(make_float2(__uint_as_float(dp[4 * v]), __uint_as_float(dp[4 * v + 1])), sc2, make_float2(d4.x, d4.y));
+                    const float2 t1 = ffma2(make_float2(__uint_as_float(dp[4 * v + 2]), __uint_as_float(dp[4 * v + 3])), sc2, make_float2(d4.z, d4.w));
+                    const float2 d0 = fmul2(make_float2(__uint_as_float(s[4 * v]), __uint_as_float(s[4 * v + 1])), t0);
+                    const float2 d1 = fmul2(make_float2(__uint_as_float(s[4 * v + 2]), __uint_as_float(s[4 * v + 3])), t1);
+                    pk[2 * v] = pack16<BF16>(d0.x, d0.y);
+                    pk[2 * v + 1] = pack16<BF16>(d1.x, d1.y);
                 }
                 tmem_st16(dp_addr, reinterpret_cast<uint32_t(&)[16]>(pk[0]));
                 tmem_st16(dp_addr + 16, reinterpret_cast<uint32_t(&)[16]>(pk[16]));
@@ -471,17 +496,17 @@ sdpa_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-    auto bar = [&](int i) { return smem_base + kSmemBars + 8u * i; };
-    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + kSmemMisc);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + kSmemMisc + 4);
+    auto bar = [&](int i) { return smem_base + kDqSmemBars + 8u * i; };
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + kDqSmemMisc);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + kDqSmemMisc + 4);
     constexpr int kChunks = HD / 64;
     constexpr uint32_t kLoadBytes = kChunks * kChunkBytes;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int r = p.Hq / p.Hkv;
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < kNumBars; ++i) {
-            const bool eight = i == kBarPFull || i == kBarDsFull || i == kBarAccEmpty;
+        for (int i = 0; i < kDqNumBars; ++i) {
+            const bool eight = i == kDqBarTaken || i == kDqBarDsFull || i == kDqBarAccEmpty;
             mbar_init(bar(i), eight ? 8u : 1u);
         }
         *abort_flag = 0;
@@ -489,7 +514,7 @@ sdpa_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         fence_proxy_async_smem();
     }
     if (warp == kMmaWarp) {
-        tmem_alloc(smem_base + kSmemMisc, kTmemCols);
+        tmem_alloc(smem_base + kDqSmemMisc, kTmemCols);
         tmem_relinquish();
     }
     if (warp == kLoadWarp && lane == 0) {
@@ -513,27 +538,29 @@ sdpa_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             for (int seq = 0; ok && get_item<false>(p, seq, &it); ++seq) {
                 if (it.n <= 0) continue;
                 const int hk = it.h / r;
-                ok = mbar_wait(bar(kBarOwnEmpty), (items & 1u) ^ 1u, abort_flag, 0);
+                ok = mbar_wait(bar(kDqBarOwnEmpty), (items & 1u) ^ 1u, abort_flag, 0);
                 if (!ok) break;
                 ++items;
-                mbar_arrive_expect_tx(bar(kBarOwnFull), 2 * kLoadBytes);
+                mbar_arrive_expect_tx(bar(kDqBarOwnFull), 2 * kLoadBytes);
 #pragma unroll
                 for (int c = 0; c < kChunks; ++c) {
-                    tma_load_4d(smem_base + kSmemOwn + c * kChunkBytes, &map_q, bar(kBarOwnFull), 64 * c, it.t * BT, it.h, it.b);
-                    tma_load_4d(smem_base + kSmemOwn + kTileBytes + c * kChunkBytes, &map_do, bar(kBarOwnFull), 64 * c, it.t * BT, it.h, it.b);
+                    tma_load_4d(smem_base + kSmemOwn + c * kChunkBytes, &map_q, bar(kDqBarOwnFull), 64 * c, it.t * BT, it.h, it.b);
+                    tma_load_4d(smem_base + kSmemOwn + kTileBytes + c * kChunkBytes, &map_do, bar(kDqBarOwnFull), 64 * c, it.t * BT, it.h, it.b);
                 }
                 for (int x = 0; ok && x < it.n; ++x, ++rc) {
-                    const int stage = rc & 1u;
-                    ok = mbar_wait(bar(kBarRingEmpty + stage), ((rc >> 1) & 1u) ^ 1u, abort_flag, 1);
+                    const uint32_t ks = rc % kDqKStages, vs = rc % kDqVStages;
+                    ok = mbar_wait(bar(kDqBarKEmpty + ks), ((rc / kDqKStages) & 1u) ^ 1u, abort_flag, 1);
                     if (!ok) break;
-                    const uint32_t full = bar(kBarRingFull + stage);
-                    mbar_arrive_expect_tx(full, 2 * kLoadBytes);
-                    const uint32_t dst = smem_base + kSmemRing + stage * kStageBytes;
+                    mbar_arrive_expect_tx(bar(kDqBarKFull + ks), kLoadBytes);
 #pragma unroll
-                    for (int c = 0; c < kChunks; ++c) {
-                        tma_load_4d(dst + c * kChunkBytes, &map_k, full, 64 * c, x * BT, hk, it.b);
-                        tma_load_4d(dst + kTileBytes + c * kChunkBytes, &map_v, full, 64 * c, x * BT, hk, it.b);
-                    }
+                    for (int c = 0; c < kChunks; ++c)
+                        tma_load_4d(smem_base + kDqSmemK + ks * kTileBytes + c * kChunkBytes, &map_k, bar(kDqBarKFull + ks), 64 * c, x * BT, hk, it.b);
+                    ok = mbar_wait(bar(kDqBarVEmpty + vs), ((rc / kDqVStages) & 1u) ^ 1u, abort_flag, 7);
+                    if (!ok) break;
+                    mbar_arrive_expect_tx(bar(kDqBarVFull + vs), kLoadBytes);
+#pragma unroll
+                    for (int c = 0; c < kChunks; ++c)
+                        tma_load_4d(smem_base + kDqSmemV + vs * kTileBytes + c * kChunkBytes, &map_v, bar(kDqBarVFull + vs), 64 * c, x * BT, hk, it.b);
                 }
             }
         }
@@ -544,15 +571,17 @@ sdpa_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             constexpr uint32_t idesc_kk = instr_desc_f16(BF16 ? 1 : 0, BT, BT, false, false);
             constexpr uint32_t idesc_acc = instr_desc_f16(BF16 ? 1 : 0, BT, HD, false, true);
             const uint32_t own_q = smem_base + kSmemOwn, own_do = own_q + kTileBytes;
+            constexpr uint32_t hi = desc_hi_sw128(1024);
             // D[128 queries x 128 keys] = own[queries x HD] * streamed[keys x HD]^T
             auto issue_t = [&](uint32_t d_col, uint32_t a_tile, uint32_t b_tile) {
+                const uint32_t a0 = desc_lo_sw128(a_tile, 16), b0 = desc_lo_sw128(b_tile, 16);
 #pragma unroll
                 for (int c = 0; c < kChunks; ++c)
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
-                        const uint32_t off = c * kChunkBytes + i * 32;
-                        mma_ss(tmem + d_col, smem_desc_sw128(a_tile + off, 16, 1024),
-                               smem_desc_sw128(b_tile + off, 16, 1024), idesc_kk, (c | i) ? 1u : 0u);
+                        const uint32_t step = desc_step(c * kChunkBytes + i * 32);
+                        if (c | i) mma_ss_lo<true>(tmem + d_col, a0 + step, b0 + step, hi, idesc_kk);
+                        else mma_ss_lo<false>(tmem + d_col, a0 + step, b0 + step, hi, idesc_kk);
                     }
             };
             bool ok = true;
@@ -560,53 +589,57 @@ sdpa_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             Item it;
             for (int seq = 0; ok && get_item<false>(p, seq, &it); ++seq) {
                 if (it.n <= 0) continue;
-                auto ring_tile = [&](uint32_t c) { return smem_base + kSmemRing + (c & 1u) * kStageBytes; };
-                ok = mbar_wait(bar(kBarOwnFull), items & 1u, abort_flag, 2);
+                auto k_tile = [&](uint32_t c) { return smem_base + kDqSmemK + (c % kDqKStages) * kTileBytes; };
+                auto v_tile = [&](uint32_t c) { return smem_base + kDqSmemV + (c % kDqVStages) * kTileBytes; };
+                // S = Q K^T and dP = dO V^T of step c; V's stage is free as soon as dP has run
+                auto issue_s_dp = [&](uint32_t c) -> bool {
+                    if (!mbar_wait(bar(kDqBarKFull + c % kDqKStages), (c / kDqKStages) & 1u, abort_flag, 3)) return false;
+                    tc_fence_after_sync();
+                    issue_t(kColS, own_q, k_tile(c));
+                    tc_commit(bar(kDqBarSFull));
+                    if (!mbar_wait(bar(kDqBarVFull + c % kDqVStages), (c / kDqVStages) & 1u, abort_flag, 8)) return false;
+                    tc_fence_after_sync();
+                    issue_t(kColDp, own_do, v_tile(c));
+                    tc_commit(bar(kDqBarDpFull));
+                    tc_commit(bar(kDqBarVEmpty + c % kDqVStages));
+                    return true;
+                };
+                ok = mbar_wait(bar(kDqBarOwnFull), items & 1u, abort_flag, 2);
                 if (!ok) break;
-                ok = mbar_wait(bar(kBarRingFull + (rc & 1u)), (rc >> 1) & 1u, abort_flag, 3);
-                if (!ok) break;
-                tc_fence_after_sync();
-                issue_t(kColS, own_q, ring_tile(rc));
-                tc_commit(bar(kBarSFull));
-                issue_t(kColDp, own_do, ring_tile(rc) + kTileBytes);
-                tc_commit(bar(kBarDpFull));
+                ok = issue_s_dp(rc);
                 for (int x = 0; ok && x < it.n; ++x) {
                     const uint32_t cur = rc + x;
                     // the element-wise warps hold S and dP of this step in registers: the next
                     // step's products may overwrite them while this step's dS is being formed
-                    ok = mbar_wait(bar(kBarPFull), pc & 1u, abort_flag, 4);
+                    ok = mbar_wait(bar(kDqBarTaken), pc & 1u, abort_flag, 4);
                     if (!ok) break;
                     ++pc;
                     if (x + 1 < it.n) {
-                        ok = mbar_wait(bar(kBarRingFull + ((cur + 1) & 1u)), ((cur + 1) >> 1) & 1u, abort_flag, 3);
+                        ok = issue_s_dp(cur + 1);
                         if (!ok) break;
-                        tc_fence_after_sync();
-                        issue_t(kColS, own_q, ring_tile(cur + 1));
-                        tc_commit(bar(kBarSFull));
-                        issue_t(kColDp, own_do, ring_tile(cur + 1) + kTileBytes);
-                        tc_commit(bar(kBarDpFull));
                     }
-                    ok = mbar_wait(bar(kBarDsFull), dc & 1u, abort_flag, 6);
+                    ok = mbar_wait(bar(kDqBarDsFull), dc & 1u, abort_flag, 6);
                     if (!ok) break;
                     ++dc;
                     if (x == 0 && items > 0) {   // the previous item's dQ has been read out
-                        ok = mbar_wait(bar(kBarAccEmpty), (items - 1) & 1u, abort_flag, 5);
+                        ok = mbar_wait(bar(kDqBarAccEmpty), (items - 1) & 1u, abort_flag, 5);
                         if (!ok) break;
                     }
                     tc_fence_after_sync();
                     // dQ += dS K_j: dS (16-bit) from TMEM, K_j as [keys x HD] rows
                     const uint32_t ds_col = kColDs + (cur & 1u) * 64;
-                    const uint32_t kt = ring_tile(cur);
+                    const uint32_t k0 = desc_lo_sw128(k_tile(cur), kChunkBytes);
 #pragma unroll
-                    for (int ks = 0; ks < BT / 16; ++ks)
-                        mma_ts(tmem + kColDq, tmem + ds_col + ks * 8,
-                               smem_desc_sw128(kt + ks * 16 * 128, kChunkBytes, 1024), idesc_acc, (x > 0 || ks) ? 1u : 0u);
-                    tc_commit(bar(kBarRingEmpty + (cur & 1u)));
+                    for (int ks = 0; ks < BT / 16; ++ks) {
+                        if (ks) mma_ts_lo<true>(tmem + kColDq, tmem + ds_col + ks * 8, k0 + desc_step(ks * 16 * 128), hi, idesc_acc);
+                        else mma_ts_lo(tmem + kColDq, tmem + ds_col, k0, hi, idesc_acc, x > 0 ? 1u : 0u);
+                    }
+                    tc_commit(bar(kDqBarKEmpty + cur % kDqKStages));
                 }
                 if (!ok) break;
                 rc += it.n;
-                tc_commit(bar(kBarAccFull));
-                tc_commit(bar(kBarOwnEmpty));
+                tc_commit(bar(kDqBarAccFull));
+                tc_commit(bar(kDqBarOwnEmpty));
                 ++items;
             }
         }
@@ -627,16 +660,16 @@ sdpa_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             const int row = it.t * BT + wq * 32 + lane;
             const bool live = row < p.Lq;
             const int64_t grow = (int64_t(it.b) * p.Hq + it.h) * p.Lq + row;
-            const float lse2 = live ? p.lse[grow] * 1.4426950408889634f : INFINITY;
+            const float lse2 = live ? p.lse[grow] * 1.4426950408889634f : INFINITY;   // dead rows: P = exp2(-inf) = 0
             const float delta = live ? p.delta[grow] : 0.f;
             for (int x = 0; x < it.n; ++x, ++rc) {
-                ok = mbar_wait(bar(kBarSFull), rc & 1u, abort_flag, 11);
+                ok = mbar_wait(bar(kDqBarSFull), rc & 1u, abort_flag, 11);
                 if (!ok) break;
                 tc_fence_after_sync();
                 uint32_t s[64], dp[64];
                 tmem_ld32(s_addr, reinterpret_cast<uint32_t(&)[32]>(s[0]));
                 tmem_ld32(s_addr + 32, reinterpret_cast<uint32_t(&)[32]>(s[32]));
-                ok = mbar_wait(bar(kBarDpFull), rc & 1u, abort_flag, 12);
+                ok = mbar_wait(bar(kDqBarDpFull), rc & 1u, abort_flag, 12);
                 if (!ok) break;
                 tc_fence_after_sync();
                 tmem_ld32(dp_addr, reinterpret_cast<uint32_t(&)[32]>(dp[0]));
@@ -648,21 +681,27 @@ sdpa_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 tmem_ld_fence32(reinterpret_cast<uint32_t(&)[32]>(dp[32]));
                 tc_fence_before_sync();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(bar(kBarPFull));   // S and dP are in registers
+                if (lane == 0) mbar_arrive(bar(kDqBarTaken));   // S and dP are in registers
                 // P = exp2(S * c - lse2), zero where the query does not see the key;
                 // dS = P o (dP - delta) * scale
                 const int k0 = x * BT + col0;
                 const int limit = (p.causal ? min(row, p.Lk - 1) : p.Lk - 1) - k0;   // last visible column
+                // some column of these 64 is invisible to some row of this warp (the same for all lanes)
+                const bool need_mask = (p.causal && k0 + 63 > it.t * BT + wq * 32) || k0 + 64 > p.Lk;
+                const float2 c22 = make_float2(c2, c2), nl2 = make_float2(-lse2, -lse2);
+                const float2 sc2 = make_float2(p.scale, p.scale), nd2 = make_float2(-delta * p.scale, -delta * p.scale);
                 uint32_t pk[32];
 #pragma unroll
                 for (int c = 0; c < 64; c += 2) {
-                    float p0 = ex2_approx(fmaf(__uint_as_float(s[c]), c2, -lse2));
-                    float p1 = ex2_approx(fmaf(__uint_as_float(s[c + 1]), c2, -lse2));
-                    if (c > limit) p0 = 0.f;
-                    if (c + 1 > limit) p1 = 0.f;
-                    const float d0 = p0 * (__uint_as_float(dp[c]) - delta) * p.scale;
-                    const float d1 = p1 * (__uint_as_float(dp[c + 1]) - delta) * p.scale;
-                    pk[c >> 1] = pack16<BF16>(d0, d1);
+                    const float2 e = ffma2(make_float2(__uint_as_float(s[c]), __uint_as_float(s[c + 1])), c22, nl2);
+                    float p0 = ex2_approx(e.x), p1 = ex2_approx(e.y);
+                    if (need_mask) {
+                        if (c > limit) p0 = 0.f;
+                        if (c + 1 > limit) p1 = 0.f;
+                    }
+                    const float2 t = ffma2(make_float2(__uint_as_float(dp[c]), __uint_as_float(dp[c + 1])), sc2, nd2);
+                    const float2 d = fmul2(make_float2(p0, p1), t);
+                    pk[c >> 1] = pack16<BF16>(d.x, d.y);
                 }
                 const uint32_t ds_addr = tmem + lane_base + kColDs + (rc & 1u) * 64 + wg * 32;
                 tmem_st16(ds_addr, reinterpret_cast<uint32_t(&)[16]>(pk[0]));
@@ -670,10 +709,10 @@ sdpa_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 tmem_wait_st();
                 tc_fence_before_sync();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(bar(kBarDsFull));
+                if (lane == 0) mbar_arrive(bar(kDqBarDsFull));
             }
             if (!ok) break;
-            ok = mbar_wait(bar(kBarAccFull), items & 1u, abort_flag, 13);
+            ok = mbar_wait(bar(kDqBarAccFull), items & 1u, abort_flag, 13);
             if (!ok) break;
             ++items;
             tc_fence_after_sync();
@@ -690,7 +729,7 @@ sdpa_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             }
             tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar(kBarAccEmpty));
+            if (lane == 0) mbar_arrive(bar(kDqBarAccEmpty));
         }
     }
 
@@ -715,7 +754,7 @@ bool sdpa_bwd_tc_supported(const Gpu* g, const paras_sdpa_bwd_args& a) {
     if (a.D != 128 && a.D != 64) return false;
     if (a.Lq < 1 || a.Lk < 1 || a.Hkv < 1 || a.Hq % a.Hkv) return false;
     if (!(a.scale > 0.0) || !std::isfinite(a.scale)) return false;
-    if (g->smem_optin < size_t(kSmemLaunch)) return false;
+    if (g->smem_optin < size_t(kSmemLaunch) || g->smem_optin < size_t(kDqSmemLaunch)) return false;
     return true;
 }
 
@@ -742,25 +781,25 @@ int sdpa_bwd_tc_launch(Gpu* g, const paras_sdpa_bwd_args& a, const float* delta,
     p.nk = (a.Lk + BT - 1) / BT;
     const int sms = g->sm_count > 0 ? g->sm_count : 148;
     const bool bf = a.dtype == PARAS_BF16;
-    auto launch = [&](auto kernel, int64_t units) -> int {
+    auto launch = [&](auto kernel, int64_t units, int smem) -> int {
         if (units > INT32_MAX) return fail(PARAS_E_UNSUPPORTED, "paras sdpa backward: too many work units");
         p.units = int(units);
-        PB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLaunch));
-        kernel<<<unsigned(units < sms ? units : sms), kThreads, kSmemLaunch, s>>>(mq, mk, mv, mdo, p);
+        PB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        kernel<<<unsigned(units < sms ? units : sms), kThreads, smem, s>>>(mq, mk, mv, mdo, p);
         return PARAS_OK;
     };
     // dK, dV: units of paired key tiles per (batch, kv head)
     p.npair = (p.nk + 1) / 2;
     const int64_t u_kv = int64_t(a.B) * a.Hkv * p.npair;
-    if (a.D == 128) st = bf ? launch(sdpa_bwd_dkv_kernel<true, 128>, u_kv) : launch(sdpa_bwd_dkv_kernel<false, 128>, u_kv);
-    else st = bf ? launch(sdpa_bwd_dkv_kernel<true, 64>, u_kv) : launch(sdpa_bwd_dkv_kernel<false, 64>, u_kv);
+    if (a.D == 128) st = bf ? launch(sdpa_bwd_dkv_kernel<true, 128>, u_kv, kSmemLaunch) : launch(sdpa_bwd_dkv_kernel<false, 128>, u_kv, kSmemLaunch);
+    else st = bf ? launch(sdpa_bwd_dkv_kernel<true, 64>, u_kv, kSmemLaunch) : launch(sdpa_bwd_dkv_kernel<false, 64>, u_kv, kSmemLaunch);
     if (st != PARAS_OK) return st;
     PB_LAUNCH_CHECK("sdpa_bwd_dkv_kernel");
     // dQ: units of paired query tiles per (batch, query head)
     p.npair = (p.nq + 1) / 2;
     const int64_t u_q = int64_t(a.B) * a.Hq * p.npair;
-    if (a.D == 128) st = bf ? launch(sdpa_bwd_dq_kernel<true, 128>, u_q) : launch(sdpa_bwd_dq_kernel<false, 128>, u_q);
-    else st = bf ? launch(sdpa_bwd_dq_kernel<true, 64>, u_q) : launch(sdpa_bwd_dq_kernel<false, 64>, u_q);
+    if (a.D == 128) st = bf ? launch(sdpa_bwd_dq_kernel<true, 128>, u_q, kDqSmemLaunch) : launch(sdpa_bwd_dq_kernel<false, 128>, u_q, kDqSmemLaunch);
+    else st = bf ? launch(sdpa_bwd_dq_kernel<true, 64>, u_q, kDqSmemLaunch) : launch(sdpa_bwd_dq_kernel<false, 64>, u_q, kDqSmemLaunch);
     if (st != PARAS_OK) return st;
     PB_LAUNCH_CHECK("sdpa_bwd_dq_kernel");
     return PARAS_OK;
