@@ -84,6 +84,15 @@ swiglu_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ gate, const T*
     }
 }
 
+// out[n, k] = weight[n, k] * scale[k], one rounding: the RMSNorm weight folded into the rows of the
+// projection weight that follows the norm.
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+scale_columns_kernel(const T* __restrict__ w, const T* __restrict__ scale, T* __restrict__ out, int64_t n, int64_t K) {
+    for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += int64_t(gridDim.x) * blockDim.x)
+        out[i] = from_f32<T>(to_f32<T>(w[i]) * to_f32<T>(scale[i % K]));
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
 rotate_half_kernel(const T* __restrict__ x, T* __restrict__ out, int64_t n, int64_t D,
@@ -265,6 +274,32 @@ int paras_b200_swiglu_bwd(int gpu, const void* grad_out, const void* gate, const
     }
 #undef PB_BWD
     PB_LAUNCH_CHECK("swiglu_bwd_kernel");
+    return PARAS_OK;
+}
+
+int paras_b200_scale_columns(int gpu, const void* weight, const void* scale, void* out, int64_t N, int64_t K,
+                             int dtype, void* stream) {
+    if (N < 0 || K < 0) return fail(PARAS_E_INVALID, "paras scale_columns: negative size");
+    if (dtype != PARAS_F32 && dtype != PARAS_BF16 && dtype != PARAS_F16)
+        return fail(PARAS_E_UNSUPPORTED, "paras scale_columns: unsupported dtype %d", dtype);
+    int st;
+    Gpu* g = pb::use_gpu(gpu, &st);
+    if (!g) return st;
+    const int64_t n = N * K;
+    if (n == 0) return PARAS_OK;
+    if (!weight || !scale || !out) return fail(PARAS_E_INVALID, "paras scale_columns: null pointer");
+    cudaStream_t s = pb::pick_stream(g, stream);
+    const int blocks = pb::grid_for(g, n, pb::kThreads);
+#define PB_SCL(T)                                                                    \
+    pb::scale_columns_kernel<T><<<blocks, pb::kThreads, 0, s>>>(                      \
+        static_cast<const T*>(weight), static_cast<const T*>(scale), static_cast<T*>(out), n, K)
+    switch (dtype) {
+        case PARAS_F32: PB_SCL(float); break;
+        case PARAS_BF16: PB_SCL(__nv_bfloat16); break;
+        default: PB_SCL(__half); break;
+    }
+#undef PB_SCL
+    PB_LAUNCH_CHECK("scale_columns_kernel");
     return PARAS_OK;
 }
 

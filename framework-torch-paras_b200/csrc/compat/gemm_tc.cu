@@ -5,6 +5,9 @@
 //   C[b][M,N] = A[b][M,K] * B[b]        A: [M,K] rows of K, or [K,M] rows of M (a transposed operand)
 //                                       B: [N,K] rows of K (a Linear weight), or [K,N] rows of N
 //   epilogues: none | + bias[N] | SwiGLU: C[M,F] = silu(A Wg^T) * (A Wu^T) from one pass over A
+//              | * row_scale[M] (fp32): with B = W o w and row_scale = rstd this is RMSNorm(A) W^T,
+//                the normalised activations never written (csrc/ops/rms_swiglu_ops.cpp:43-75 feeding
+//                vision_ops.cpp:248-309)
 //
 // Persistent CTAs, one per SM, 128 x 256 output tiles, K in steps of 64:
 //   warps 0-3  epilogue: TMEM -> registers -> 16 bit -> swizzled shared memory -> TMA store
@@ -61,7 +64,8 @@ constexpr int kNumBars = 2 * kMaxRing + 4;
 constexpr int kSmemMisc = kSmemBars + kNumBars * 8;             // tmem base word, abort flag
 constexpr int kSmemTotal = kSmemMisc + 16;
 
-enum { kEpiNone = 0, kEpiBias = 1, kEpiSwiglu = 2, kEpiProb = 3, kEpiDs = 4 };  // 3, 4: attention backward only
+enum { kEpiNone = 0, kEpiBias = 1, kEpiSwiglu = 2, kEpiProb = 3, kEpiDs = 4,   // 3, 4: attention backward only
+       kEpiRowScale = 5 };   // C = (A B^T) * row_scale[row]: RMSNorm folded into the projection that follows it
 
 struct GemmParams {
     int M, N, K;          // N = output columns (for SwiGLU: F)
@@ -154,7 +158,7 @@ __device__ __forceinline__ int next_k_step(const GemmParams& p, int m0, int kk) 
 }
 
 template <bool BF16, bool A_ROWS_OF_M, bool B_ROWS_OF_N, int EPI>
-__global__ void __launch_bounds__(EPI >= kEpiProb ? kThreadsWide : kThreads, 1)
+__global__ void __launch_bounds__((EPI == kEpiProb || EPI == kEpiDs) ? kThreadsWide : kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const __grid_constant__ CUtensorMap map_b2, const __grid_constant__ CUtensorMap map_c,
                const GemmParams p) {
@@ -164,8 +168,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_raw + kSmemMisc);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_raw + kSmemMisc + 4);
     constexpr int kNPerTile = EPI == kEpiSwiglu ? BN / 2 : BN;   // output columns per tile
-    constexpr int kEpiGroups = EPI >= kEpiProb ? 2 : 1;          // groups of four epilogue warps
-    constexpr int kRing = EPI >= kEpiProb ? kStages - 1 : kStages;  // stages of the operand ring in use
+    constexpr bool kWide = EPI == kEpiProb || EPI == kEpiDs;
+    constexpr int kEpiGroups = kWide ? 2 : 1;                    // groups of four epilogue warps
+    constexpr int kRing = kWide ? kStages - 1 : kStages;          // stages of the operand ring in use
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (smem_base & 1023u) {
@@ -402,6 +407,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     if (visible && col0 + 8 * v < p.N) dst[v] = __ldg(reinterpret_cast<const uint4*>(prow + col0) + v);
                 }
             };
+            if (EPI == kEpiRowScale) stat = __ldg(p.row_stat + int64_t(t.b) * p.M + min(row_w + lane, p.M - 1));
             if (EPI == kEpiProb || EPI == kEpiDs) {
                 const int row = min(row_w + lane, p.M - 1);
                 const int64_t grow = int64_t(t.b) * p.M + row;
@@ -489,6 +495,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
                     for (int i = 0; i < 64; i += 2) {
                         float x0 = __uint_as_float(o[i]), x1 = __uint_as_float(o[i + 1]);
+                        if (EPI == kEpiRowScale) {
+                            x0 *= stat;
+                            x1 *= stat;
+                        }
                         if (EPI == kEpiBias) {
                             const int col = t.n0 + 64 * c + i;
                             const uint16_t* bias = static_cast<const uint16_t*>(p.bias);
@@ -549,7 +559,7 @@ int launch(Gpu* g, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorM
     PB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal));
     const int sms = g->sm_count > 0 ? g->sm_count : 148;
     const int units = p.pair ? (p.tiles + 1) / 2 : p.tiles;   // what a CTA takes per round
-    kernel<<<dim3(unsigned(units < sms ? units : sms)), EPI >= kEpiProb ? kThreadsWide : kThreads, kSmemTotal, s>>>(
+    kernel<<<dim3(unsigned(units < sms ? units : sms)), (EPI == kEpiProb || EPI == kEpiDs) ? kThreadsWide : kThreads, kSmemTotal, s>>>(
         ma, mb, mb2, mc, p);
     PB_LAUNCH_CHECK("gemm_tc_kernel");
     return PARAS_OK;
@@ -566,8 +576,10 @@ int gemm_run(const paras_gemm_args* a, const GemmExtra* ex) {
     if (a->M < 0 || a->N < 0 || a->K < 0 || a->batch < 0)
         return fail(PARAS_E_INVALID, "paras gemm: negative size");
     const int epi = ex ? ex->epilogue : a->epilogue;
-    if (a->epilogue < kEpiNone || a->epilogue > kEpiSwiglu)
+    if ((a->epilogue < kEpiNone || a->epilogue > kEpiSwiglu) && a->epilogue != kEpiRowScale)
         return fail(PARAS_E_INVALID, "paras gemm: bad epilogue %d", a->epilogue);
+    if (a->epilogue == kEpiRowScale && !a->row_scale)
+        return fail(PARAS_E_INVALID, "paras gemm: row-scale epilogue without row_scale");
     if (ex && ex->epilogue != kEpiNone &&
         (a->a_layout != PARAS_GEMM_A_MK || (epi != kEpiProb && epi != kEpiDs) || !ex->row_stat ||
          (epi == kEpiDs && !ex->prob)))
@@ -600,7 +612,7 @@ int gemm_run(const paras_gemm_args* a, const GemmExtra* ex) {
     const bool kn = a->b_layout == PARAS_GEMM_B_KN;
     const bool at = a->a_layout == PARAS_GEMM_A_KM;
     // N <= 128 (the [.., head dim] products of attention backward): half-width B tiles and MMAs
-    const bool narrow = a->N <= BN / 2 && (epi == kEpiNone || epi == kEpiBias);
+    const bool narrow = a->N <= BN / 2 && (epi == kEpiNone || epi == kEpiBias || epi == kEpiRowScale);
     const int n_per_tile = a->epilogue == kEpiSwiglu || narrow ? BN / 2 : BN;
     CUtensorMap ma, mb, mb2, mc;
     if (at) {
@@ -628,6 +640,7 @@ int gemm_run(const paras_gemm_args* a, const GemmExtra* ex) {
     p.k_iters = int((a->K + BK - 1) / BK);
     p.narrow = narrow;
     p.bias = a->bias;
+    p.row_stat = a->epilogue == kEpiRowScale ? a->row_scale : nullptr;
     p.status = g->status_dev;
     if (ex) {
         p.row_stat = ex->row_stat; p.prob = ex->prob; p.prob_ld = ex->prob_ld;
@@ -645,6 +658,7 @@ int gemm_run(const paras_gemm_args* a, const GemmExtra* ex) {
     if (epi == kEpiDs) return kn ? PB_GEMM(false, true, kEpiDs) : PB_GEMM(false, false, kEpiDs);
     if (a->epilogue == kEpiSwiglu) return PB_GEMM(false, false, kEpiSwiglu);
     if (a->epilogue == kEpiBias) return kn ? PB_GEMM(false, true, kEpiBias) : PB_GEMM(false, false, kEpiBias);
+    if (a->epilogue == kEpiRowScale) return kn ? PB_GEMM(false, true, kEpiRowScale) : PB_GEMM(false, false, kEpiRowScale);
     if (at) return kn ? PB_GEMM(true, true, kEpiNone) : PB_GEMM(true, false, kEpiNone);
     return kn ? PB_GEMM(false, true, kEpiNone) : PB_GEMM(false, false, kEpiNone);
 #undef PB_GEMM

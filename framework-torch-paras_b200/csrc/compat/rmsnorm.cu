@@ -314,6 +314,43 @@ rmsnorm_fwd_block_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __
     }
 }
 
+// rstd only (the statistic of paras::rms_norm, fused_ops.cpp:67-75): four warps per row, one read
+// of x, no output tensor.  Feeds the row-scale epilogue of the GEMM.
+template <typename T>
+__global__ void __launch_bounds__(128)
+rms_rstd_kernel(const T* __restrict__ x, float* __restrict__ rstd, int64_t rows, int64_t H, double eps, bool vec) {
+    constexpr int N = Vec16<T>::N;
+    __shared__ double part[4];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+        const T* xr = x + row * H;
+        double acc = 0.0;
+        if (vec) {
+            for (int64_t i = tid; i < H / N; i += 128) {
+                const Vec16<T> v = ld16_stream(xr + i * N);
+                float pf = 0.f;
+#pragma unroll
+                for (int e = 0; e < N; ++e) {
+                    const float f = to_f32<T>(v.v[e]);
+                    if constexpr (sizeof(T) == 4) acc += double(f) * double(f);
+                    else pf = fmaf(f, f, pf);
+                }
+                acc += double(pf);
+            }
+        } else {
+            for (int64_t j = tid; j < H; j += 128) {
+                const double f = to_f32<T>(xr[j]);
+                acc += f * f;
+            }
+        }
+        acc = warp_sum(acc);
+        if (lane == 0) part[warp] = acc;
+        __syncthreads();
+        if (tid == 0) rstd[row] = float(1.0 / sqrt((part[0] + part[1] + part[2] + part[3]) / double(H) + eps));
+        __syncthreads();
+    }
+}
+
 // grad_x (fused_ops.cpp:111-135): one warp per row.
 template <typename T>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
@@ -454,6 +491,30 @@ int paras_b200_rmsnorm_fwd(int gpu, const void* x, const void* weight, void* y, 
         default: return PB_RMS(__half);
     }
 #undef PB_RMS
+}
+
+int paras_b200_rms_rstd(int gpu, const void* x, float* rstd, int64_t rows, int64_t H, double eps, int dtype,
+                        void* stream) {
+    if (rows < 0 || H < 0) return fail(PARAS_E_INVALID, "paras rms_rstd: negative size");
+    if (dtype != PARAS_F32 && dtype != PARAS_BF16 && dtype != PARAS_F16)
+        return fail(PARAS_E_UNSUPPORTED, "paras rms_rstd: unsupported dtype %d", dtype);
+    int st;
+    Gpu* g = pb::use_gpu(gpu, &st);
+    if (!g) return st;
+    if (rows == 0) return PARAS_OK;
+    if (H == 0 || !x || !rstd) return fail(PARAS_E_INVALID, "paras rms_rstd: null pointer or empty rows");
+    cudaStream_t s = pb::pick_stream(g, stream);
+    const int64_t cap = int64_t(1) << 30;
+    const int blocks = int(rows < cap ? rows : cap);
+    const size_t es = pb::dtype_size(dtype);
+    const bool vec = pb::aligned16(x) && (size_t(H) * es) % 16 == 0;
+    switch (dtype) {
+        case PARAS_F32: pb::rms_rstd_kernel<float><<<blocks, 128, 0, s>>>(static_cast<const float*>(x), rstd, rows, H, eps, vec); break;
+        case PARAS_BF16: pb::rms_rstd_kernel<__nv_bfloat16><<<blocks, 128, 0, s>>>(static_cast<const __nv_bfloat16*>(x), rstd, rows, H, eps, vec); break;
+        default: pb::rms_rstd_kernel<__half><<<blocks, 128, 0, s>>>(static_cast<const __half*>(x), rstd, rows, H, eps, vec); break;
+    }
+    PB_LAUNCH_CHECK("rms_rstd_kernel");
+    return PARAS_OK;
 }
 
 int paras_b200_rmsnorm_bwd(int gpu, const void* grad_out, const void* x, const void* weight,

@@ -6,6 +6,7 @@
 //   * 16-bit, D == 128, no mask tensor, few queries   -> tensor-core split-KV decode kernel
 //   * 16-bit, D == 128 or 64 otherwise (masks incl.)  -> tcgen05/TMEM/TMA kernel
 //   * everything else                                  -> CUDA-core kernel (sdpa_simt.cu)
+//   * dropout, a dropout mask or the weights as output -> two-pass CUDA-core kernel (sdpa_weights.cu)
 // There is no host fallback: an unsupported request is an error.
 #include <algorithm>
 #include <cmath>
@@ -94,6 +95,7 @@ int paras_b200_sdpa_workspace_bytes(const paras_sdpa_args* a, size_t* bytes) {
     if (!g) return st;
     const char* why;
     const int64_t rows = int64_t(a->B) * a->Hq * a->Lq;
+    if (pb::sdpa_wants_weights(*a)) return PARAS_OK;   // the two-pass kernel needs no scratch
     switch (pb::choose(g, *a, &why)) {
         case pb::Path::Tensor: break;
         case pb::Path::Decode:
@@ -116,6 +118,14 @@ int paras_b200_sdpa_fwd(const paras_sdpa_args* a) {
     if (a->Lk > 0 && (!a->k || !a->v)) return fail(PARAS_E_INVALID, "paras sdpa: null pointer");
     cudaStream_t s = pb::pick_stream(g, a->stream);
     const float scale = pb::effective_scale(*a);
+    if (pb::sdpa_wants_weights(*a)) {
+        if (a->flags & PARAS_SDPA_FORCE_TENSOR)
+            return fail(PARAS_E_UNSUPPORTED, "paras sdpa: dropout and the weights output run on CUDA cores only");
+        if (a->Lk == 0) return fail(PARAS_E_UNSUPPORTED, "paras sdpa: dropout / weights output with no keys");
+        st = pb::sdpa_weights_launch(g, *a, scale, s);
+        if (st == PARAS_OK) pb::set_last_kernel("weights");
+        return st;
+    }
     const char* why = "";
     const pb::Path path = pb::choose(g, *a, &why);
     if ((a->flags & PARAS_SDPA_FORCE_TENSOR) && path == pb::Path::Simt)
@@ -183,8 +193,8 @@ int paras_b200_sdpa_fwd_host(const paras_sdpa_args* a) {
     Gpu* g = pb::use_gpu(a->gpu, &st);
     if (!g) return st;
     if (a->gpu < 0 || a->gpu >= 16) return fail(PARAS_E_UNSUPPORTED, "paras sdpa (host): GPU ordinal out of range");
-    if (a->mask || a->lse || a->workspace)
-        return fail(PARAS_E_UNSUPPORTED, "paras sdpa (host): mask, lse and workspace are not taken here");
+    if (a->mask || a->lse || a->workspace || pb::sdpa_wants_weights(*a))
+        return fail(PARAS_E_UNSUPPORTED, "paras sdpa (host): mask, lse, workspace, dropout and weights output are not taken here");
     if (int64_t(a->B) * a->Hq * a->Lq * a->D == 0) return PARAS_OK;
     if (!a->q || !a->out || (a->Lk > 0 && (!a->k || !a->v)))
         return fail(PARAS_E_INVALID, "paras sdpa (host): null pointer");

@@ -56,6 +56,10 @@ int sdpa_decode_pick_splits(const Gpu* g, const paras_sdpa_args& a);
 int sdpa_decode_launch(Gpu* g, const paras_sdpa_args& a, float scale, const SplitWorkspace& ws,
                        cudaStream_t s);
 
+// Dropout on the weights / a given dropout mask / the weights as an output (sdpa_weights.cu).
+bool sdpa_wants_weights(const paras_sdpa_args& a);
+int sdpa_weights_launch(Gpu* g, const paras_sdpa_args& a, float scale, cudaStream_t s);
+
 // Fused tcgen05 attention backward (sdpa_bwd_tc.cu): 16-bit, D == 128 or 64, dense tensors.
 bool sdpa_bwd_tc_supported(const Gpu* g, const paras_sdpa_bwd_args& a);
 int sdpa_bwd_tc_launch(Gpu* g, const paras_sdpa_bwd_args& a, const float* delta, cudaStream_t s);

@@ -318,6 +318,8 @@ extern "C" int paras_b200_sdpa_fwd_static_scratch(const paras_sdpa_args* a) {
         return fail(PARAS_E_INVALID, "paras sdpa: is_causal and attn_mask are mutually exclusive");
     if (a->mask && (a->mask_kind < 1 || a->mask_kind > 3))
         return fail(PARAS_E_INVALID, "paras sdpa: bad mask kind %d", a->mask_kind);
+    if (pb::sdpa_wants_weights(*a))
+        return fail(PARAS_E_UNSUPPORTED, "paras sdpa: dropout and the weights output go through paras_b200_sdpa_fwd");
     int count = 0;
     if (cudaGetDeviceCount(&count) != cudaSuccess || count == 0) {
         cudaGetLastError();

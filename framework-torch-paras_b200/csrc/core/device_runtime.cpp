@@ -257,6 +257,7 @@ c10::Device current_device() { return tl_device; }
 Runtime::Runtime() {
     gpu_count_ = paras_b200_device_count();
     seeds_.assign(size_t(1 + gpu_count_), 0x5deece66dULL);
+    sequences_.assign(size_t(1 + gpu_count_), 0);
     static std::once_flag once;
     std::call_once(once, [] { pthread_atfork(nullptr, nullptr, &on_fork_child); });
     g_initialised.store(true);
@@ -326,11 +327,23 @@ uint64_t Runtime::cached_bytes(int index) {
 
 void Runtime::set_seed(int index, uint64_t seed) {
     check_index(index);
+    std::lock_guard<std::mutex> lk(rng_mu_);
     seeds_[size_t(index)] = seed;
+    sequences_[size_t(index)] = 0;
 }
 
 void Runtime::set_seed_all(uint64_t seed) {
+    std::lock_guard<std::mutex> lk(rng_mu_);
     for (auto& s : seeds_) s = seed;
+    for (auto& q : sequences_) q = 0;
+}
+
+std::pair<uint64_t, uint64_t> Runtime::rng_draw(int index, int64_t items) {
+    check_index(index);
+    std::lock_guard<std::mutex> lk(rng_mu_);
+    const uint64_t seq = sequences_[size_t(index)];
+    sequences_[size_t(index)] += uint64_t((items + 1) / 2) + 1;
+    return {seeds_[size_t(index)], seq};
 }
 
 void* Runtime::allocate(int index, size_t bytes) {

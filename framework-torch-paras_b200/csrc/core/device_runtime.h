@@ -16,6 +16,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <string>
+#include <mutex>
 #include <vector>
 
 #include "paras_b200.h"
@@ -73,6 +74,11 @@ public:
 
     void set_seed(int index, uint64_t seed);
     void set_seed_all(uint64_t seed);
+    // (seed, sequence) for an operator that draws `items` random numbers on device `index`, and the
+    // sequence advanced as the reference's Context::rng_draw does (csrc/core/context.cpp:76-83: two
+    // 32-bit values per Philox2x32 counter tick, plus one), so that a stream of random operators
+    // sees the counters it would see there.  manual_seed resets the sequence to 0.
+    std::pair<uint64_t, uint64_t> rng_draw(int index, int64_t items);
 
     static bool bad_fork();
 
@@ -85,6 +91,8 @@ private:
     int gpu_count_ = 0;
     std::atomic<uint64_t> host_bytes_{0};
     std::vector<uint64_t> seeds_;
+    std::vector<uint64_t> sequences_;
+    std::mutex rng_mu_;
 };
 
 c10::Allocator* device_allocator();

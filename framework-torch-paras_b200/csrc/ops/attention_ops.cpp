@@ -11,7 +11,9 @@
 // Both the math op and the top-level aten::scaled_dot_product_attention are registered for
 // PrivateUse1 (the reference suggests the second at attention_ops.cpp:144-150); the
 // top-level registration keeps PyTorch from pre-converting a bool mask into an additive one.
-// Dropout is not part of the fused path and raises.
+// Dropout (the reference's Philox stream, or a caller's dropout_mask) and the attention weights
+// that the math op returns need every normalised weight: those calls take a two-pass CUDA-core
+// kernel instead of the flash kernels (attention_ops.cpp:128-135, random_ops.cpp:140-176).
 #include <torch/library.h>
 #include <torch/csrc/autograd/custom_function.h>
 
@@ -42,16 +44,19 @@ bool ref_scale_rounding() {
     return on;
 }
 
+// Largest attention-weights tensor the math op will materialise (elements): 2^28 = 512 MB in 16 bit.
+constexpr int64_t kMaxWeightsElements = int64_t(1) << 28;
+
 Tensor sdpa_forward(const Tensor& query, const Tensor& key, const Tensor& value,
                     const std::optional<Tensor>& attn_mask, double dropout_p, bool is_causal,
-                    std::optional<double> scale, bool enable_gqa) {
+                    std::optional<double> scale, bool enable_gqa,
+                    const std::optional<Tensor>& dropout_mask = std::nullopt, Tensor* weights = nullptr) {
     TORCH_CHECK(query.dim() >= 3 && key.dim() >= 3 && value.dim() >= 3,
                 "paras sdpa: query/key/value must be at least 3-D (..., seq, head_dim)");
     const bool has_mask = attn_mask.has_value() && attn_mask->defined();
     TORCH_CHECK(!(is_causal && has_mask),
                 "paras sdpa: is_causal and attn_mask are mutually exclusive");
-    TORCH_CHECK(dropout_p == 0.0,
-                "paras sdpa: dropout_p > 0 is not supported by the fused B200 attention kernel");
+    TORCH_CHECK(dropout_p >= 0.0 && dropout_p < 1.0, "paras sdpa: dropout_p must be in [0, 1), got ", dropout_p);
     TORCH_CHECK(query.scalar_type() == key.scalar_type() && query.scalar_type() == value.scalar_type(),
                 "paras sdpa: query, key and value must have the same dtype");
     const int dt = dtype_code(query.scalar_type());
@@ -68,7 +73,8 @@ Tensor sdpa_forward(const Tensor& query, const Tensor& key, const Tensor& value,
     TORCH_CHECK(k.size(0) == B && v.size(0) == B, "paras sdpa: batch dimensions of query, key and value differ");
     TORCH_CHECK(k.size(3) == E, "paras sdpa: query and key head_dim differ");
     TORCH_CHECK(v.size(1) == Hkv && v.size(2) == Lk, "paras sdpa: key and value shapes differ");
-    TORCH_CHECK(v.size(3) == E, "paras sdpa: value head_dim must equal query head_dim in the fused kernel");
+    TORCH_CHECK(v.size(3) == E, "paras sdpa: value head_dim (", v.size(3), ") must equal query head_dim (", E,
+                "): the kernels share one head dim; pad the narrower operand with zero columns");
     if (Hkv != Hq) {
         TORCH_CHECK(enable_gqa, "paras sdpa: key/value have ", Hkv, " heads but query has ", Hq,
                     "; pass enable_gqa=True for grouped-query attention");
@@ -119,7 +125,48 @@ Tensor sdpa_forward(const Tensor& query, const Tensor& key, const Tensor& value,
     a.flags = ref_scale_rounding() ? PARAS_SDPA_REF_SCALE : 0;
     a.gpu = gpu;
     a.stream = nullptr;
+    Tensor dmask;   // keeps a converted dropout mask alive until the launch is queued
+    if (dropout_p > 0.0 && Lk > 0 && out.numel() > 0) {
+        a.dropout_p = dropout_p;
+        if (dropout_mask.has_value() && dropout_mask->defined()) {
+            dmask = *dropout_mask;
+            TORCH_CHECK(dmask.device() == query.device(), "paras sdpa: dropout_mask must be on the query's device");
+            if (dmask.scalar_type() == c10::kBool) a.dropout_mask_kind = 1;
+            else if (dmask.scalar_type() == query.scalar_type()) a.dropout_mask_kind = 2;
+            else if (dmask.scalar_type() == c10::kFloat) a.dropout_mask_kind = 3;
+            else { dmask = dmask.to(query.scalar_type()); a.dropout_mask_kind = 2; }
+            std::vector<int64_t> score_shape(query.sizes().begin(), query.sizes().end() - 1);
+            score_shape.push_back(Lk);
+            dmask = dmask.expand(score_shape);
+            if (query.dim() == 3) dmask = dmask.unsqueeze(1);
+            else if (query.dim() > 4) dmask = dmask.reshape({-1, Hq, Lq, Lk});
+            dmask = dmask.expand({B, Hq, Lq, Lk});
+            a.dropout_mask = dmask.data_ptr();
+            for (int i = 0; i < 4; ++i) a.dropout_mask_strides[i] = dmask.stride(i);
+        } else {
+            // the counters the reference's native_dropout would draw for its [B,Hq,Lq,Lk] weights
+            const auto state = rt.rng_draw(int(query.device().index()), B * Hq * Lq * Lk);
+            a.rng_seed = state.first;
+            a.rng_sequence = state.second;
+        }
+    }
+    if (weights) {
+        TORCH_CHECK(B * Hq * Lq * Lk <= kMaxWeightsElements,
+                    "paras sdpa: the attention weights [", B, ", ", Hq, ", ", Lq, ", ", Lk, "] are too large to "
+                    "materialise; call F.scaled_dot_product_attention, which returns no weights and runs the "
+                    "fused kernel");
+        *weights = at::empty({B, Hq, Lq, Lk}, q.options());
+        if (weights->numel() > 0 && Lk > 0) a.attn_out = weights->data_ptr();
+    }
     PARAS_ABI(paras_b200_sdpa_fwd(&a));
+    if (weights) {
+        if (query.dim() == 3) *weights = weights->squeeze(1);
+        else if (query.dim() > 4) {
+            std::vector<int64_t> wshape(query.sizes().begin(), query.sizes().end() - 1);
+            wshape.push_back(Lk);
+            *weights = weights->reshape(wshape);
+        }
+    }
 
     if (query.dim() == 3) return out.squeeze(1);
     if (query.dim() > 4) {
@@ -129,17 +176,19 @@ Tensor sdpa_forward(const Tensor& query, const Tensor& key, const Tensor& value,
     return out;
 }
 
-// aten::_scaled_dot_product_attention_math: the second result (attention weights) is what
-// a flash kernel never forms; an empty tensor is returned in its place.
+// aten::_scaled_dot_product_attention_math returns (output, attention weights after dropout) like the
+// reference.  The weights are O(Lq * Lk) per head: this entry point therefore always runs the
+// two-pass kernel, and refuses shapes whose weights exceed kMaxWeightsElements -- F.scaled_dot_product_
+// attention (no weights) is the entry point for those.
 std::tuple<Tensor, Tensor> sdpa_math(const Tensor& query, const Tensor& key, const Tensor& value,
                                      const std::optional<Tensor>& attn_mask, double dropout_p,
                                      bool is_causal, const std::optional<Tensor>& dropout_mask,
                                      std::optional<double> scale, bool enable_gqa) {
     PARAS_TRACE_OP("_scaled_dot_product_attention_math");
-    TORCH_CHECK(!(dropout_mask.has_value() && dropout_mask->defined()),
-                "paras sdpa: dropout_mask is not supported by the fused B200 attention kernel");
-    Tensor out = sdpa_forward(query, key, value, attn_mask, dropout_p, is_causal, scale, enable_gqa);
-    return {out, at::empty({0}, query.options())};
+    Tensor weights;
+    Tensor out = sdpa_forward(query, key, value, attn_mask, dropout_p, is_causal, scale, enable_gqa, dropout_mask,
+                              &weights);
+    return {out, weights};
 }
 
 Tensor sdpa(const Tensor& query, const Tensor& key, const Tensor& value,

@@ -182,6 +182,64 @@ Tensor swiglu_linear(const Tensor& x, const Tensor& w_gate, const Tensor& w_up) 
     return out.reshape(shape);
 }
 
+// ---- RMSNorm folded into the projection that follows it ------------------------------------
+// linear(rms_norm(x, w_norm), W) = rstd[row] * (x @ (W o w_norm)^T): the per-column norm weight moves
+// into the projection weight (once per weight, fold_norm_weight), the per-row rstd into the GEMM's
+// epilogue.  What the reference runs as rms_norm (csrc/ops/rms_swiglu_ops.cpp:43-75, fused_ops.cpp:
+// 43-88) followed by linear (vision_ops.cpp:248-309) -- a write and a read of the normalised
+// activations in between -- becomes one read of x for rstd and the GEMM.  New operators, 16-bit.
+Tensor fold_norm_weight(const Tensor& weight, const Tensor& norm_weight) {
+    PARAS_TRACE_OP("paras::fold_norm_weight");
+    TORCH_CHECK(weight.dim() == 2 && norm_weight.dim() == 1 && norm_weight.size(0) == weight.size(1),
+                "paras fold_norm_weight: weight [out_features, in_features], norm_weight [in_features]");
+    TORCH_CHECK(dtype_code(weight.scalar_type()) >= 0 && norm_weight.scalar_type() == weight.scalar_type(),
+                "paras fold_norm_weight: float32, bfloat16 or float16 tensors of one dtype");
+    c10::DeviceGuard guard(weight.device());
+    Tensor w = weight.contiguous(), nw = norm_weight.contiguous();
+    Tensor out = at::empty_like(w);
+    PARAS_ABI(paras_b200_scale_columns(Runtime::get().gpu_of(w), w.data_ptr(), nw.data_ptr(), out.data_ptr(),
+                                       w.size(0), w.size(1), dtype_code(w.scalar_type()), nullptr));
+    return out;
+}
+
+Tensor rms_norm_linear_folded(const Tensor& x, const Tensor& folded_weight, double eps) {
+    PARAS_TRACE_OP("paras::rms_norm_linear_folded");
+    TORCH_CHECK(folded_weight.dim() == 2 && x.dim() >= 1 && x.size(-1) == folded_weight.size(1),
+                "paras rms_norm_linear: input's last dimension must equal in_features");
+    TORCH_CHECK(sixteen_bit(x) && folded_weight.scalar_type() == x.scalar_type(),
+                "paras rms_norm_linear: bfloat16 or float16 operands of one dtype");
+    c10::DeviceGuard guard(x.device());
+    const int64_t K = folded_weight.size(1), N = folded_weight.size(0);
+    Tensor a = x.reshape({-1, K}).contiguous();
+    Tensor w = row_major(folded_weight);
+    const int gpu = Runtime::get().gpu_of(a);
+    Tensor rstd = at::empty({a.size(0)}, a.options().dtype(c10::kFloat));
+    Tensor out = at::empty({a.size(0), N}, x.options());
+    if (a.size(0) > 0) {
+        PARAS_ABI(paras_b200_rms_rstd(gpu, a.data_ptr(), rstd.data_ptr<float>(), a.size(0), K, eps,
+                                      dtype_code(a.scalar_type()), nullptr));
+        paras_gemm_args g{};
+        g.a = a.data_ptr(); g.b = w.data_ptr(); g.c = out.data_ptr();
+        g.M = a.size(0); g.N = N; g.K = K;
+        g.lda = a.stride(0); g.ldb = w.stride(0); g.ldc = out.stride(0);
+        g.batch = 1;
+        g.dtype = dtype_code(a.scalar_type());
+        g.b_layout = PARAS_GEMM_B_NK;
+        g.epilogue = PARAS_GEMM_EPI_ROWSCALE;
+        g.row_scale = rstd.data_ptr<float>();
+        g.gpu = gpu;
+        PARAS_ABI(paras_b200_gemm(&g));
+    }
+    auto shape = x.sizes().vec();
+    shape.back() = N;
+    return out.reshape(shape);
+}
+
+Tensor rms_norm_linear(const Tensor& x, const Tensor& norm_weight, const Tensor& weight, double eps) {
+    PARAS_TRACE_OP("paras::rms_norm_linear");
+    return rms_norm_linear_folded(x, fold_norm_weight(weight, norm_weight), eps);
+}
+
 // aten::linear with inputs that require grad: as a product autograd knows (matmul -> mm / bmm,
 // whose derivative formulas call mm on this device again), like the reference's own
 // differentiable linear (vision_ops.cpp:248-309).  Without grad the fused kernel runs.
@@ -213,5 +271,15 @@ TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
     m.impl("aten::linear", &paras::linear);
 }
 
-TORCH_LIBRARY_FRAGMENT(paras, m) { m.def("swiglu_linear(Tensor x, Tensor w_gate, Tensor w_up) -> Tensor"); }
-TORCH_LIBRARY_IMPL(paras, PrivateUse1, m) { m.impl("swiglu_linear", &paras::swiglu_linear); }
+TORCH_LIBRARY_FRAGMENT(paras, m) {
+    m.def("swiglu_linear(Tensor x, Tensor w_gate, Tensor w_up) -> Tensor");
+    m.def("fold_norm_weight(Tensor weight, Tensor norm_weight) -> Tensor");
+    m.def("rms_norm_linear(Tensor x, Tensor norm_weight, Tensor weight, float eps) -> Tensor");
+    m.def("rms_norm_linear_folded(Tensor x, Tensor folded_weight, float eps) -> Tensor");
+}
+TORCH_LIBRARY_IMPL(paras, PrivateUse1, m) {
+    m.impl("swiglu_linear", &paras::swiglu_linear);
+    m.impl("fold_norm_weight", &paras::fold_norm_weight);
+    m.impl("rms_norm_linear", &paras::rms_norm_linear);
+    m.impl("rms_norm_linear_folded", &paras::rms_norm_linear_folded);
+}

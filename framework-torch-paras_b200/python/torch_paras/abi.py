@@ -36,6 +36,7 @@ EXPORTS = [
     "paras_b200_rmsnorm_bwd", "paras_b200_swiglu_fwd", "paras_b200_swiglu_bwd",
     "paras_b200_rotate_half", "paras_b200_gemm", "paras_b200_sdpa_fwd_host", "paras_b200_sdpa_bwd",
     "paras_b200_sdpa_split_layout", "paras_b200_selftest_bounded_wait",
+    "paras_b200_rms_rstd", "paras_b200_scale_columns",
 ]
 
 
@@ -50,6 +51,9 @@ class SdpaArgs(C.Structure):
         ("causal", C.c_int32), ("flags", C.c_int32), ("scale", C.c_double),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
         ("gpu", C.c_int32), ("reserved", C.c_int32), ("stream", C.c_void_p),
+        ("dropout_p", C.c_double), ("rng_seed", C.c_uint64), ("rng_sequence", C.c_uint64),
+        ("dropout_mask", C.c_void_p), ("dropout_mask_strides", C.c_int64 * 4),
+        ("dropout_mask_kind", C.c_int32), ("reserved2", C.c_int32), ("attn_out", C.c_void_p),
     ]
 
 
@@ -63,6 +67,7 @@ class GemmArgs(C.Structure):
         ("stride_a", C.c_int64), ("stride_b", C.c_int64), ("stride_c", C.c_int64),
         ("dtype", C.c_int32), ("b_layout", C.c_int32), ("epilogue", C.c_int32), ("gpu", C.c_int32),
         ("stream", C.c_void_p), ("a_layout", C.c_int32), ("reserved", C.c_int32),
+        ("row_scale", C.c_void_p),
     ]
 
 
@@ -78,7 +83,7 @@ class SdpaBwdArgs(C.Structure):
 
 
 GEMM_B_NK, GEMM_B_KN = 0, 1
-GEMM_EPI_NONE, GEMM_EPI_BIAS, GEMM_EPI_SWIGLU = 0, 1, 2
+GEMM_EPI_NONE, GEMM_EPI_BIAS, GEMM_EPI_SWIGLU, GEMM_EPI_ROWSCALE = 0, 1, 2, 5
 
 _lib = None
 
@@ -120,6 +125,10 @@ def lib() -> C.CDLL:
         L.paras_b200_sdpa_split_layout.argtypes = [C.c_int64, C.c_int32, C.c_int32, C.POINTER(C.c_size_t),
                                                    C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)]
         L.paras_b200_selftest_bounded_wait.argtypes = [C.c_int, C.c_uint32, C.POINTER(C.c_int)]
+        L.paras_b200_rms_rstd.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_double,
+                                          C.c_int, C.c_void_p]
+        L.paras_b200_scale_columns.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64,
+                                               C.c_int, C.c_void_p]
         _lib = L
     return _lib
 
@@ -193,15 +202,36 @@ def sdpa_args(q, k, v, out, *, causal=False, scale=None, mask=None, lse=None, fl
 
 
 def sdpa_fwd(q, k, v, *, causal=False, scale=None, mask=None, return_lse=False, flags=0,
-             out=None, workspace=None, stream=None):
-    """softmax(q k^T * scale [+mask]) v through ``paras_b200_sdpa_fwd``."""
+             out=None, workspace=None, stream=None, dropout_p=0.0, rng=None, dropout_mask=None,
+             return_weights=False):
+    """softmax(q k^T * scale [+mask]) v through ``paras_b200_sdpa_fwd``.  ``dropout_p`` with
+    ``rng=(seed, sequence)`` draws the reference's Philox stream, ``dropout_mask`` multiplies a given
+    mask in instead, ``return_weights`` also returns the [B,Hq,Lq,Lk] attention weights."""
     if out is None:
         out = torch.empty(q.shape, dtype=q.dtype, device=q.device)
     lse = torch.empty(q.shape[:3], dtype=torch.float32, device=q.device) if return_lse else None
     a = sdpa_args(q, k, v, out, causal=causal, scale=scale, mask=mask, lse=lse, flags=flags,
                   workspace=workspace, stream=stream)
+    weights = None
+    a.dropout_p = float(dropout_p)
+    if rng is not None:
+        a.rng_seed, a.rng_sequence = int(rng[0]), int(rng[1])
+    if dropout_mask is not None:
+        m = dropout_mask
+        while m.dim() < 4:
+            m = m.unsqueeze(0)
+        m = m.expand(q.shape[0], q.shape[1], q.shape[2], k.shape[2])
+        a.dropout_mask = m.data_ptr()
+        a.dropout_mask_kind = 1 if m.dtype == torch.bool else (2 if m.dtype == q.dtype else 3)
+        for i in range(4):
+            a.dropout_mask_strides[i] = m.stride(i)
+        a._keep_dm = m
+    if return_weights:
+        weights = torch.empty((q.shape[0], q.shape[1], q.shape[2], k.shape[2]), dtype=q.dtype, device=q.device)
+        a.attn_out = weights.data_ptr()
     check(lib().paras_b200_sdpa_fwd(C.byref(a)))
-    return (out, lse) if return_lse else out
+    res = (out,) + ((lse,) if return_lse else ()) + ((weights,) if return_weights else ())
+    return res if len(res) > 1 else out
 
 
 def sdpa_fwd_host(q, k, v, *, causal=False, scale=None, flags=0, out=None, gpu=0):
@@ -271,7 +301,38 @@ def sdpa_fwd_static_scratch(q, k, v, *, causal=False, scale=None, mask=None, fla
     return out
 
 
-def gemm(a, b, *, b_layout=GEMM_B_NK, a_transposed=False, bias=None, up_weight=None, out=None, stream=None):
+def rms_rstd(x, eps=1e-6, *, stream=None):
+    """1 / sqrt(mean(x^2, -1) + eps) per row of a contiguous [rows, H] tensor, fp32."""
+    h = x.shape[-1]
+    rows = x.numel() // h if h else 0
+    rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+    check(lib().paras_b200_rms_rstd(_gpu_of(x), x.data_ptr(), rstd.data_ptr(), rows, h, float(eps), dtype_code(x),
+                                    _stream_of(x, stream)))
+    return rstd
+
+
+def scale_columns(weight, scale, *, stream=None):
+    """weight[n, k] * scale[k] with one rounding (the RMSNorm weight folded into a projection weight)."""
+    assert weight.is_contiguous() and scale.is_contiguous() and weight.shape[-1] == scale.numel()
+    out = torch.empty_like(weight)
+    check(lib().paras_b200_scale_columns(_gpu_of(weight), weight.data_ptr(), scale.data_ptr(), out.data_ptr(),
+                                         weight.numel() // scale.numel(), scale.numel(), dtype_code(weight),
+                                         _stream_of(weight, stream)))
+    return out
+
+
+def rms_norm_linear(x, norm_weight, weight, eps=1e-6, *, folded_weight=None, stream=None):
+    """linear(rms_norm(x, norm_weight), weight) without writing the normalised activations: rstd in one
+    read of x, the norm weight folded into the projection weight (pass ``folded_weight`` to reuse it),
+    and the GEMM's epilogue scaling its rows by rstd."""
+    wf = folded_weight if folded_weight is not None else scale_columns(weight, norm_weight, stream=stream)
+    x2 = x.reshape(-1, x.shape[-1])
+    out = gemm(x2, wf, row_scale=rms_rstd(x2, eps, stream=stream), stream=stream)
+    return out.reshape(*x.shape[:-1], wf.shape[0])
+
+
+def gemm(a, b, *, b_layout=GEMM_B_NK, a_transposed=False, bias=None, up_weight=None, row_scale=None, out=None,
+         stream=None):
     """``paras_b200_gemm`` on 2-D ([M,K]) or 3-D ([batch,M,K]) operands with contiguous rows.
 
     ``b_layout=GEMM_B_NK``: b is [N,K] (a Linear weight), result a @ b^T;
@@ -304,6 +365,11 @@ def gemm(a, b, *, b_layout=GEMM_B_NK, a_transposed=False, bias=None, up_weight=N
     g.b_layout = b_layout
     g.a_layout = 1 if a_transposed else 0
     g.epilogue = GEMM_EPI_SWIGLU if up_weight is not None else (GEMM_EPI_BIAS if bias is not None else GEMM_EPI_NONE)
+    if row_scale is not None:
+        if g.epilogue != GEMM_EPI_NONE:
+            raise RuntimeError("paras abi: row_scale cannot be combined with another epilogue")
+        g.epilogue = GEMM_EPI_ROWSCALE
+        g.row_scale = row_scale.data_ptr()
     g.gpu = _gpu_of(a)
     g.stream = _stream_of(a, stream)
     check(lib().paras_b200_gemm(C.byref(g)))

@@ -8,8 +8,8 @@ import torch
 
 from . import _C  # noqa: F401  (loads the operator registrations)
 
-__all__ = ["rms_norm", "swiglu", "rotate_half", "swiglu_linear", "attention_host",
-           "scaled_dot_product_attention"]
+__all__ = ["rms_norm", "swiglu", "rotate_half", "swiglu_linear", "rms_norm_linear", "fold_norm_weight",
+           "attention_host", "scaled_dot_product_attention"]
 
 
 class _RMSNorm(torch.autograd.Function):
@@ -79,6 +79,23 @@ def swiglu_linear(x: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor) -> 
     both projections share one pass over ``x`` and SwiGLU runs in the epilogue.  16-bit
     operands; the weights are ``[features, in_features]`` like ``nn.Linear.weight``."""
     return torch.ops.paras.swiglu_linear(x, w_gate, w_up)
+
+
+def fold_norm_weight(weight: torch.Tensor, norm_weight: torch.Tensor) -> torch.Tensor:
+    """``weight * norm_weight`` (broadcast over rows): the RMSNorm weight moved into the ``[out, in]``
+    weight of the projection that follows the norm.  Do it once per weight and pass the result to
+    ``rms_norm_linear(..., folded_weight=...)``."""
+    return torch.ops.paras.fold_norm_weight(weight, norm_weight)
+
+
+def rms_norm_linear(x: torch.Tensor, norm_weight: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6, *,
+                    folded_weight: torch.Tensor = None) -> torch.Tensor:
+    """``F.linear(rms_norm(x, norm_weight, eps), weight)`` (forward only, 16-bit) without the normalised
+    activations ever being written: one read of ``x`` for the row statistic, then the projection GEMM
+    whose epilogue scales each output row by it."""
+    if folded_weight is not None:
+        return torch.ops.paras.rms_norm_linear_folded(x, folded_weight, eps)
+    return torch.ops.paras.rms_norm_linear(x, norm_weight, weight, eps)
 
 
 def attention_host(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, *,

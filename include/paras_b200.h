@@ -34,7 +34,7 @@
 extern "C" {
 #endif
 
-#define PARAS_B200_ABI_VERSION 1
+#define PARAS_B200_ABI_VERSION 2
 
 enum {
     PARAS_OK = 0,
@@ -148,6 +148,23 @@ typedef struct paras_sdpa_args {
     int32_t gpu;
     int32_t reserved;
     void* stream;
+    /* Dropout on the attention weights and the weights themselves (attention_ops.cpp:128-135).  Any
+     * of the three below sends the call to a CUDA-core kernel that forms each row of weights twice
+     * (statistics, then values) -- the reference's O(Lq*Lk) result cannot come out of a flash kernel:
+     *   dropout_p > 0, no dropout_mask: weight i (flat index into the contiguous [B,Hq,Lq,Lk] weights)
+     *     is kept when Philox2x32-10(rng_seed, rng_sequence, i).r0 >> 8, as a fraction of 2^24, is below
+     *     1 - p, and scaled by 1 / (1 - p) in fp32 -- native_dropout, csrc/ops/random_ops.cpp:27-59,140-176;
+     *   dropout_mask: weights * dropout_mask / (1 - p) instead of drawing (kind as for `mask`);
+     *   attn_out: receives the weights after dropout, contiguous [B,Hq,Lq,Lk] in `dtype`.
+     * All zero / NULL = the fused kernels above. */
+    double dropout_p;
+    uint64_t rng_seed;
+    uint64_t rng_sequence;
+    const void* dropout_mask;
+    int64_t dropout_mask_strides[4];
+    int32_t dropout_mask_kind;
+    int32_t reserved2;
+    void* attn_out;
 } paras_sdpa_args;
 
 int paras_b200_sdpa_fwd(const paras_sdpa_args* args);
@@ -273,12 +290,16 @@ int paras_b200_sdpa_bwd(const paras_sdpa_bwd_args* args);
  *            PARAS_GEMM_EPI_SWIGLU: b = gate weight [N,K], b2 = up weight [N,K] (layout NK only);
  *                C[M,N] = swiglu(A b^T, A b2^T) with both projections rounded to `dtype` first,
  *                i.e. what linear, linear, paras::swiglu (csrc/ops/fused_ops.cpp:162-194) give.
+ *            PARAS_GEMM_EPI_ROWSCALE: C[m, :] *= row_scale[m] (fp32 [batch * M]) before the rounding.
+ *                With b = W o w (paras_b200_scale_columns) and row_scale = rstd (paras_b200_rms_rstd)
+ *                this is linear(rms_norm(A, w), W) -- csrc/ops/rms_swiglu_ops.cpp:43-75 feeding
+ *                vision_ops.cpp:248-309 -- without the normalised activations ever being written.
  * All leading dimensions and batch strides are in elements and must be multiples of 8 (16
  * bytes), all base pointers 16-byte aligned; otherwise PARAS_E_UNSUPPORTED (the caller keeps
  * its own path for such operands).  dtype: PARAS_BF16 or PARAS_F16. */
 enum { PARAS_GEMM_B_NK = 0, PARAS_GEMM_B_KN = 1 };
 enum { PARAS_GEMM_A_MK = 0, PARAS_GEMM_A_KM = 1 };
-enum { PARAS_GEMM_EPI_NONE = 0, PARAS_GEMM_EPI_BIAS = 1, PARAS_GEMM_EPI_SWIGLU = 2 };
+enum { PARAS_GEMM_EPI_NONE = 0, PARAS_GEMM_EPI_BIAS = 1, PARAS_GEMM_EPI_SWIGLU = 2, PARAS_GEMM_EPI_ROWSCALE = 5 };
 typedef struct paras_gemm_args {
     const void* a;
     const void* b;
@@ -296,8 +317,18 @@ typedef struct paras_gemm_args {
     void* stream;
     int32_t a_layout;
     int32_t reserved;
+    const float* row_scale; /* [batch * M], row-scale epilogue only */
 } paras_gemm_args;
 int paras_b200_gemm(const paras_gemm_args* args);
+
+/* The two small passes that fold RMSNorm (csrc/ops/fused_ops.cpp:43-88) into the projection after it:
+ *   rstd[r] = 1 / sqrt(mean(x[r, :]^2) + eps)        fp32 [rows]; x [rows, H] contiguous (one read of x)
+ *   out[n, k] = weight[n, k] * scale[k]               [N, K] contiguous rows, one rounding; done once per
+ *                                                     weight when the caller keeps the result */
+int paras_b200_rms_rstd(int gpu, const void* x, float* rstd, int64_t rows, int64_t H, double eps, int dtype,
+                        void* stream);
+int paras_b200_scale_columns(int gpu, const void* weight, const void* scale, void* out, int64_t N, int64_t K,
+                             int dtype, void* stream);
 
 /* ---- failure path self-test ----
  * No counterpart in the reference (its kernels have no device-side waits; a stuck queue there

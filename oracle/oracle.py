@@ -83,11 +83,51 @@ def matmul_ref(a: Tensor, b: Tensor) -> Tensor:
 
 
 # ----------------------------------------------------------------------------------
+# dropout  (random_ops.cpp:27-59 Philox2x32-10, 140-176 native_dropout; context.cpp:76-83)
+# ----------------------------------------------------------------------------------
+def philox2x32_r0(seed: int, sequence: int, n: int) -> np.ndarray:
+    """First output word of Philox2x32-10 for counters 0..n-1 (random_ops.cpp:27-47): counter
+    (idx low word, sequence + idx high word), key = seed's low word bumped by 0x9E3779B9 per round."""
+    idx = np.arange(n, dtype=np.uint64)
+    c0 = (idx & np.uint64(0xFFFFFFFF)).astype(np.uint64)
+    c1 = ((np.uint64(sequence) + (idx >> np.uint64(32))) & np.uint64(0xFFFFFFFF)).astype(np.uint64)
+    k0 = int(seed) & 0xFFFFFFFF
+    m = np.uint64(0xD256D193)
+    for _ in range(10):
+        prod = m * c0                                   # both below 2^32: the product fits 64 bits
+        n0 = ((prod >> np.uint64(32)) ^ np.uint64(k0) ^ c1) & np.uint64(0xFFFFFFFF)
+        c1 = prod & np.uint64(0xFFFFFFFF)
+        c0 = n0
+        k0 = (k0 + 0x9E3779B9) & 0xFFFFFFFF
+    return c0.astype(np.uint32)
+
+
+def rng_advance(sequence: int, items: int) -> int:
+    """Context::rng_draw: the sequence after an operator that drew `items` numbers."""
+    return sequence + (items + 1) // 2 + 1
+
+
+def native_dropout(x: Tensor, p: float, seed: int, sequence: int) -> Tensor:
+    """random_ops.cpp:140-176 on a contiguous tensor: element i is kept when
+    (r0 >> 8) * 2^-24 < float(1 - p) and becomes dtype(float(x) * (1.0f / keep))."""
+    keep = np.float32(1.0 - p)
+    scale = np.float32(1.0) / keep
+    r0 = philox2x32_r0(seed, sequence, x.numel())
+    u = (r0 >> np.uint32(8)).astype(np.float32) * np.float32(1.0 / (1 << 24))
+    kept = torch.from_numpy(u < keep).reshape(x.shape)
+    scaled = (x.contiguous().to(torch.float32) * float(scale)).to(x.dtype)
+    return torch.where(kept, scaled, torch.zeros_like(scaled))
+
+
+# ----------------------------------------------------------------------------------
 # scaled dot product attention  (attention_ops.cpp:71-136)
 # ----------------------------------------------------------------------------------
 def sdpa(q: Tensor, k: Tensor, v: Tensor, attn_mask: Optional[Tensor] = None,
          is_causal: bool = False, scale: Optional[float] = None,
-         enable_gqa: bool = False, return_weights: bool = False):
+         enable_gqa: bool = False, return_weights: bool = False, dropout_p: float = 0.0,
+         dropout_mask: Optional[Tensor] = None, rng: Tuple[int, int] = (0x5deece66d, 0)):
+    """`rng` = (seed, sequence) of the device when the call is made; the weights returned are the
+    ones after dropout, as the reference returns them (attention_ops.cpp:128-135)."""
     if q.dim() < 3 or k.dim() < 3 or v.dim() < 3:
         raise RuntimeError("paras sdpa: query/key/value must be at least 3-D")
     if is_causal and attn_mask is not None:
@@ -113,6 +153,13 @@ def sdpa(q: Tensor, k: Tensor, v: Tensor, attn_mask: Optional[Tensor] = None,
             out_dtype = torch.result_type(scores, attn_mask)
             scores = _cast(scores.to(torch.float64) + attn_mask.to(torch.float64), out_dtype)
     attn = softmax_lastdim(scores)
+    if dropout_p > 0.0:
+        if dropout_mask is not None:      # attn * mask / (1 - p): two binary kernels, each rounding
+            dt = torch.result_type(attn, dropout_mask)
+            attn = _cast(attn.to(torch.float64) * dropout_mask.to(torch.float64), dt)
+            attn = _cast(attn.to(torch.float64) / _scalar_as(1.0 - dropout_p, dt), dt)
+        else:                             # at::dropout -> native_dropout on the device
+            attn = native_dropout(attn, dropout_p, rng[0], rng[1])
     out = matmul_ref(attn, v)
     return (out, attn) if return_weights else out
 

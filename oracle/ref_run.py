@@ -21,6 +21,7 @@ sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 import ref_loader  # noqa: E402
 
 DEV = "paras:0"
+_MOD = None   # the reference's extension module, set by main()
 
 
 def _dev(t):
@@ -46,6 +47,18 @@ def run_op(op, a):
             kw["enable_gqa"] = True
         return lambda: F.scaled_dot_product_attention(
             q, k, v, attn_mask=mask, is_causal=bool(a.get("is_causal", False)), **kw)
+    if op == "sdpa_math":
+        # the math op with its two results (output, weights after dropout); the device's generator is
+        # re-seeded first, so the dropout draws counters (seed, sequence 0)
+        q, k, v = _dev(a["q"]), _dev(a["k"]), _dev(a["v"])
+        mask, dmask = _dev(a.get("attn_mask")), _dev(a.get("dropout_mask"))
+
+        def run_math():
+            _MOD.manual_seed_all(int(a.get("seed", 0)))
+            return torch.ops.aten._scaled_dot_product_attention_math(
+                q, k, v, mask, float(a.get("dropout_p", 0.0)), bool(a.get("is_causal", False)), dmask,
+                scale=a.get("scale"), enable_gqa=bool(a.get("enable_gqa", False)))
+        return run_math
     if op == "sdpa_grad":
         # gradients by autograd through the reference's composite attention (attention_ops.cpp:71-136
         # and the backward kernels its operators register, e.g. softmax backward, pointwise_ops.cpp:
@@ -92,7 +105,8 @@ def main():
     # this process; PARAS_REF_THREADS states the count the caller wants instead.
     if os.environ.get("PARAS_REF_THREADS"):
         torch.set_num_threads(int(os.environ["PARAS_REF_THREADS"]))
-    mod = ref_loader.load()
+    global _MOD
+    mod = _MOD = ref_loader.load()
     jobs = torch.load(jobs_path)
     results = []
     for job in jobs:

@@ -105,7 +105,30 @@ def grad_cases():
     return out
 
 
+def dropout_cases():
+    """The math op's two results (output, weights after dropout) with the reference's own dropout:
+    its Philox stream re-seeded per case, and a caller's dropout_mask."""
+    g = torch.Generator().manual_seed(20261127)
+
+    def R(*shape, dt=torch.float32):
+        return torch.randn(*shape, generator=g).to(dt)
+
+    out = []
+    for dt, tag in ((torch.float32, "f32"), (torch.bfloat16, "bf16")):
+        q, k, v = R(1, 4, 24, 16, dt=dt), R(1, 2, 40, 16, dt=dt), R(1, 2, 40, 16, dt=dt)
+        out.append((f"sdpa_math_dropout_{tag}", "sdpa_math",
+                    {"q": q, "k": k, "v": v, "dropout_p": 0.25, "seed": 1234, "enable_gqa": True}))
+        out.append((f"sdpa_math_weights_causal_{tag}", "sdpa_math",
+                    {"q": q, "k": k, "v": v, "is_causal": True, "enable_gqa": True}))
+        dm = (torch.rand(1, 4, 24, 40, generator=g) > 0.5).to(dt)
+        out.append((f"sdpa_math_dropout_mask_{tag}", "sdpa_math",
+                    {"q": q, "k": k, "v": v, "dropout_p": 0.3, "dropout_mask": dm, "enable_gqa": True}))
+    return out
+
+
 def main():
+    if "--dropout" in sys.argv:  # only the dropout / weights fixtures
+        globals()["cases"] = dropout_cases
     if "--grad" in sys.argv:     # only the gradient fixtures
         globals()["cases"] = grad_cases
     sys.path.insert(0, os.path.join(ROOT, "oracle"))

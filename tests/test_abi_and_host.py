@@ -33,7 +33,7 @@ def test_header_symbols_are_exported():
 
 def test_abi_version_and_backend_name():
     lib = abi.lib()
-    assert lib.paras_b200_abi_version() == 1
+    assert lib.paras_b200_abi_version() == 2
     assert lib.paras_b200_backend_name().decode().startswith("paras-b200")
 
 

@@ -48,7 +48,8 @@ def same_bits(a, b):
         torch.equal(a.contiguous().view(torch.uint8), b.contiguous().view(torch.uint8))
 
 
-@pytest.mark.parametrize("name", golden_names())
+# the C restatement has no dropout / weights output: those fixtures pin the torch restatement only
+@pytest.mark.parametrize("name", [n for n in golden_names() if not n.startswith("sdpa_math")])
 def test_c_oracle_matches_reference_golden(name):
     g = load_golden(name)
     got = as_tuple(run_c(g["op"], g["args"]))

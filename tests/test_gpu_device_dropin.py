@@ -145,10 +145,45 @@ def test_sdpa_masks_broadcast_from_the_right_for_3d_and_5d_queries():
                  F.scaled_dot_product_attention(q5, k5, k5, attn_mask=m5))
 
 
-def test_sdpa_dropout_is_refused_not_emulated():
-    q = torch.randn(1, 2, 8, 16).to(DEV)
-    with pytest.raises(RuntimeError, match="dropout"):
-        F.scaled_dot_product_attention(q, q, q, dropout_p=0.1)
+def test_sdpa_dropout_draws_the_references_random_stream():
+    # F.scaled_dot_product_attention(dropout_p=...) on the device keeps exactly the weights the
+    # reference keeps: Philox2x32-10 on (seed, sequence, flat index), the sequence advancing per call
+    # as Context::rng_draw does (random_ops.cpp:27-59,140-176, context.cpp:76-83)
+    g = torch.Generator().manual_seed(5)
+    q, k, v = torch.randn(2, 4, 20, 16, generator=g), torch.randn(2, 4, 33, 16, generator=g), torch.randn(2, 4, 33, 16, generator=g)
+    torch_paras.manual_seed(777)
+    out1 = F.scaled_dot_product_attention(q.to(DEV), k.to(DEV), v.to(DEV), dropout_p=0.3)
+    out2 = F.scaled_dot_product_attention(q.to(DEV), k.to(DEV), v.to(DEV), dropout_p=0.3)
+    want1 = O.sdpa(q, k, v, dropout_p=0.3, rng=(777, 0))
+    want2 = O.sdpa(q, k, v, dropout_p=0.3, rng=(777, O.rng_advance(0, 2 * 4 * 20 * 33)))
+    assert_close(out1, want1, "dropout, first draw")
+    assert_close(out2, want2, "dropout, second draw")
+    assert not torch.allclose(out1.cpu(), out2.cpu())
+    # the math op returns the weights after dropout; a given dropout_mask replaces the draw
+    torch_paras.manual_seed(777)
+    o, w = torch.ops.aten._scaled_dot_product_attention_math(q.to(DEV), k.to(DEV), v.to(DEV), None, 0.3, False, None,
+                                                             scale=None, enable_gqa=False)
+    wo, ww = O.sdpa(q, k, v, dropout_p=0.3, rng=(777, 0), return_weights=True)
+    assert_close(o, wo, "math op output")
+    assert_close(w, ww, "math op weights")
+    assert (w.cpu() == 0).float().mean().item() > 0.2            # about 30 % of the weights were dropped
+    dm = (torch.rand(2, 4, 20, 33, generator=g) > 0.5).float()
+    o, w = torch.ops.aten._scaled_dot_product_attention_math(q.to(DEV), k.to(DEV), v.to(DEV), None, 0.5, True, dm.to(DEV),
+                                                             scale=None, enable_gqa=False)
+    wo, ww = O.sdpa(q, k, v, is_causal=True, dropout_p=0.5, dropout_mask=dm, return_weights=True)
+    assert_close(o, wo, "dropout_mask output")
+    assert_close(w, ww, "dropout_mask weights")
+    # bf16, GQA: weights are the reference's own 16-bit values
+    qb, kb, vb = q.bfloat16(), k[:, :2].bfloat16(), v[:, :2].bfloat16()
+    o, w = torch.ops.aten._scaled_dot_product_attention_math(qb.to(DEV), kb.to(DEV), vb.to(DEV), None, 0.0, True, None,
+                                                             scale=None, enable_gqa=True)
+    wo, ww = O.sdpa(qb, kb, vb, is_causal=True, enable_gqa=True, return_weights=True)
+    assert w.shape == (2, 4, 20, 33) and w.dtype == torch.bfloat16
+    assert (w.cpu().float() - ww.float()).abs().max().item() <= 2.0 ** -8     # one bf16 ulp below 1
+    assert (o.cpu().float() - wo.float()).abs().max().item() <= 2e-2
+    with pytest.raises(RuntimeError, match="too large to materialise"):
+        big = torch.empty(1, 64, 4096, 16, dtype=torch.bfloat16).to(DEV)
+        torch.ops.aten._scaled_dot_product_attention_math(big, big, big, None, 0.0, True, None, scale=None, enable_gqa=False)
 
 
 def test_rms_norm_no_weight():

@@ -145,3 +145,39 @@ def test_linearity_at_projection_size():
     scale = rhs.abs().mean().item()
     assert (lhs - rhs).abs().max().item() <= 0.05 * scale + 0.1
     assert (lhs - rhs).abs().mean().item() <= 0.01 * scale
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("shape", [(256, 512, 256), (300, 520, 1000), (1000, 128, 4096), (5, 264, 72)])
+def test_rms_norm_folded_into_the_projection(shape, dtype):
+    # linear(rms_norm(x, w), W) in one GEMM (row-scale epilogue) against the reference's two steps:
+    # paras::rms_norm (fused_ops.cpp:43-88) rounded to 16 bits, then the host GEMM of linear
+    # (vision_ops.cpp:248-309).  The fused form rounds W o w instead of the normalised activations,
+    # so elements differ by rounding noise of the same size: the bound is 2 ulp of the result plus
+    # 2e-2 of the result's scale, and most elements must agree to 1 ulp.
+    M, N, K = shape
+    x = rand((M, K), 11, dtype, 1.5)
+    wn = (1 + 0.1 * torch.randn(K, generator=torch.Generator().manual_seed(12))).to(dtype)
+    w = rand((N, K), 13, dtype, 0.05)
+    y, _ = O.rms_norm_fused(x, wn, 1e-6)
+    want = O.linear(y, w)
+    xd, wnd, wd = x.to(CUDA), wn.to(CUDA), w.to(CUDA)
+    # the pieces
+    rstd = abi.rms_rstd(xd, 1e-6)
+    _, rstd_want = O.rms_norm_fused(x, wn, 1e-6)
+    assert torch.allclose(rstd.cpu(), rstd_want, rtol=1e-5, atol=1e-6)
+    wf = abi.scale_columns(wd, wnd)
+    assert torch.equal(wf.cpu(), (w.float() * wn.float()).to(dtype))
+    got = abi.rms_norm_linear(xd, wnd, wd, 1e-6).cpu()
+    assert got.shape == want.shape and got.dtype == want.dtype
+    g, t = got.double(), want.double()
+    scale = t.abs().max().item()
+    ulp = 2.0 ** -7 if dtype == torch.bfloat16 else 2.0 ** -10
+    err = (g - t).abs()
+    assert (err <= 2 * ulp * t.abs() + 2e-2 * scale).all(), f"worst {err.max().item():.3e} at scale {scale:.3e}"
+    assert (err <= ulp * t.abs() + 1e-3 * scale).double().mean().item() > 0.9
+    # the operators on the device give the same bits, folded once or per call
+    xp, wnp, wp = x.to(DEV), wn.to(DEV), w.to(DEV)
+    o1 = paras_nn.rms_norm_linear(xp, wnp, wp, 1e-6)
+    o2 = paras_nn.rms_norm_linear(xp.reshape(1, M, K), None, None, 1e-6, folded_weight=paras_nn.fold_norm_weight(wp, wnp))
+    assert torch.equal(o1.cpu(), got) and torch.equal(o2.cpu().reshape(M, N), got)

@@ -42,6 +42,12 @@ def run_cuda(op, a, **kw):
         q, k, v = c(a["q"]), c(a["k"]), c(a["v"])
         return abi.sdpa_fwd(q, k, v, causal=bool(a.get("is_causal", False)), scale=a.get("scale"),
                             mask=c(a.get("attn_mask")), flags=abi.SDPA_REF_SCALE | kw.get("flags", 0))
+    if op == "sdpa_math":   # (output, weights after dropout) with the reference's Philox stream re-seeded
+        q, k, v = c(a["q"]), c(a["k"]), c(a["v"])
+        return abi.sdpa_fwd(q, k, v, causal=bool(a.get("is_causal", False)), scale=a.get("scale"),
+                            mask=c(a.get("attn_mask")), flags=abi.SDPA_REF_SCALE,
+                            dropout_p=float(a.get("dropout_p", 0.0)), rng=(int(a.get("seed", 0)), 0),
+                            dropout_mask=c(a.get("dropout_mask")), return_weights=True)
     if op == "rms_norm_aten":
         x = c(a["x"])
         n = 1

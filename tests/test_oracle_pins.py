@@ -25,6 +25,12 @@ def run_oracle(op, a):
         return O.sdpa(a["q"], a["k"], a["v"], attn_mask=a.get("attn_mask"),
                       is_causal=bool(a.get("is_causal", False)), scale=a.get("scale"),
                       enable_gqa=bool(a.get("enable_gqa", False)))
+    if op == "sdpa_math":   # (output, weights after dropout); the reference was re-seeded: sequence 0
+        return O.sdpa(a["q"], a["k"], a["v"], attn_mask=a.get("attn_mask"),
+                      is_causal=bool(a.get("is_causal", False)), scale=a.get("scale"),
+                      enable_gqa=bool(a.get("enable_gqa", False)), return_weights=True,
+                      dropout_p=float(a.get("dropout_p", 0.0)), dropout_mask=a.get("dropout_mask"),
+                      rng=(int(a.get("seed", 0)), 0))
     if op == "rms_norm_aten":
         return O.rms_norm_composite(a["x"], a["normalized_shape"], a.get("weight"), a.get("eps"))
     if op == "rms_norm_paras":
