@@ -491,6 +491,23 @@ def run_ours(args):
                     "counted as the 5 the gradient needs); delta pre-pass included",
             "composite_ms": t_c, "composite_tflops": fl / (t_c * 1e-3) / 1e12}
         del qb_, kb_, vb_, dob, ob, lseb
+    if want("rope"):
+        # Rotary embedding in front of the headline attention: two rotation passes + attention against the
+        # one call that rotates the queries inside the attention kernel and the keys once on the way in
+        pos = torch.arange(c["S"], device=dev, dtype=torch.float64)[:, None]
+        inv = 1.0 / (10000.0 ** (torch.arange(0, c["D"], 2, device=dev, dtype=torch.float64) / c["D"]))
+        ang = torch.cat((pos * inv, pos * inv), dim=-1)
+        cos_t, sin_t = ang.cos().bfloat16().contiguous(), ang.sin().bfloat16().contiguous()
+        t_sep = loop_ms(lambda: abi.sdpa_fwd(abi.rope(q, cos_t, sin_t), abi.rope(k, cos_t, sin_t), v, causal=True,
+                                             out=out, flags=abi.SDPA_REF_SCALE), s3, 3)
+        t_fus = loop_ms(lambda: abi.sdpa_rope_fwd(q, k, v, cos_t, sin_t, causal=True, out=out, flags=abi.SDPA_REF_SCALE), s3, 3)
+        extra["rope_then_sdpa_config2"] = {
+            "ms_separate": t_sep, "ms_fused": t_fus, "ms_attention_alone": ms_step, "kernel": abi.sdpa_last_kernel(),
+            "hbm_bytes_saved": 2 * q.numel() * 2,
+            "note": "fused = keys rotated once into scratch, queries rotated in shared memory inside the attention "
+                    "kernel (no rotated copy of q is written or read)"}
+        del cos_t, sin_t
+
     if want("gemm"):
         # The projections either side of the path at config 2 / 5 sizes (hidden 4096, FFN 14336):
         # fused QKV projection [rows,4096] x [6144,4096]^T (Hq=32, Hkv=8, D=128) and the gate/up
@@ -664,7 +681,7 @@ def main():
                     help="seconds of back-to-back headline launches for the sustained figure (0 = skip)")
     ap.add_argument("--ingest-ncu", metavar="CSV",
                     help="write profiles/sdpa_tc_kernel_config2_dram_traffic.txt from `ncu --page raw --csv` output and exit")
-    ap.add_argument("--only", choices=["config1", "rmsnorm", "swiglu", "gqa", "decode", "block", "gemm", "bwd"],
+    ap.add_argument("--only", choices=["rope", "config1", "rmsnorm", "swiglu", "gqa", "decode", "block", "gemm", "bwd"],
                     help="after the headline loop run just this extra workload and print it (for profiling)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-numa-bind", action="store_true",

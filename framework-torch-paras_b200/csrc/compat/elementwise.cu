@@ -108,6 +108,36 @@ rotate_half_kernel(const T* __restrict__ x, T* __restrict__ out, int64_t n, int6
     }
 }
 
+// Rotary embedding out = x * cos + rotate_half(x) * sin for x [B, H, L, D] (element strides for
+// B, H, L; unit stride on D) and cos / sin [Lmax, D] read at rows pos0 + l.  The reference composes
+// this from three binary kernels that each round to the tensor dtype (pointwise_ops.cpp:62-85) around
+// its exact rotate_half (fused_ops.cpp:234-267); the two products and the sum round here the same way.
+// One thread per pair (d, d + D/2).  `out` is dense [B, H, L, D].
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+rope_kernel(const T* __restrict__ x, const T* __restrict__ cosv, const T* __restrict__ sinv, T* __restrict__ out,
+            int64_t n_pairs, int H, int L, int D, int64_t sb, int64_t sh, int64_t sl, int64_t pos0) {
+    const int half = D / 2;
+    for (int64_t i = int64_t(blockIdx.x) * kThreads + threadIdx.x; i < n_pairs; i += int64_t(gridDim.x) * kThreads) {
+        const int d = int(i % half);
+        int64_t r = i / half;
+        const int l = int(r % L);
+        r /= L;
+        const int h = int(r % H);
+        const int64_t b = r / H;
+        const T* xr = x + b * sb + h * sh + int64_t(l) * sl;
+        const T* cr = cosv + (pos0 + l) * D;
+        const T* sr = sinv + (pos0 + l) * D;
+        const float x1 = to_f32<T>(xr[d]), x2 = to_f32<T>(xr[d + half]);
+        T* o = out + ((b * H + h) * int64_t(L) + l) * D;
+        // (__fmul_rn / __fadd_rn: no contraction into a fused multiply-add, which would skip a rounding)
+        o[d] = from_f32<T>(__fadd_rn(round_to<T>(__fmul_rn(x1, to_f32<T>(cr[d]))),
+                                     round_to<T>(__fmul_rn(-x2, to_f32<T>(sr[d])))));
+        o[d + half] = from_f32<T>(__fadd_rn(round_to<T>(__fmul_rn(x2, to_f32<T>(cr[d + half]))),
+                                            round_to<T>(__fmul_rn(x1, to_f32<T>(sr[d + half])))));
+    }
+}
+
 // ---- strided copy with conversion ----------------------------------------------------
 struct CopySpec {
     int ndim;
@@ -300,6 +330,34 @@ int paras_b200_scale_columns(int gpu, const void* weight, const void* scale, voi
     }
 #undef PB_SCL
     PB_LAUNCH_CHECK("scale_columns_kernel");
+    return PARAS_OK;
+}
+
+int paras_b200_rope(int gpu, const void* x, const int64_t* x_strides, const void* cosv, const void* sinv, void* out,
+                    int B, int H, int L, int D, int64_t pos0, int dtype, void* stream) {
+    if (B < 0 || H < 0 || L < 0 || D < 0 || pos0 < 0) return fail(PARAS_E_INVALID, "paras rope: negative size");
+    if (D % 2) return fail(PARAS_E_INVALID, "paras rope: last dimension must be even");
+    if (dtype != PARAS_F32 && dtype != PARAS_BF16 && dtype != PARAS_F16)
+        return fail(PARAS_E_UNSUPPORTED, "paras rope: unsupported dtype %d", dtype);
+    int st;
+    Gpu* g = pb::use_gpu(gpu, &st);
+    if (!g) return st;
+    const int64_t n = int64_t(B) * H * L * (D / 2);
+    if (n == 0) return PARAS_OK;
+    if (!x || !x_strides || !cosv || !sinv || !out) return fail(PARAS_E_INVALID, "paras rope: null pointer");
+    cudaStream_t s = pb::pick_stream(g, stream);
+    const int blocks = pb::grid_for(g, n, pb::kThreads);
+#define PB_ROPE(T)                                                                                   \
+    pb::rope_kernel<T><<<blocks, pb::kThreads, 0, s>>>(                                               \
+        static_cast<const T*>(x), static_cast<const T*>(cosv), static_cast<const T*>(sinv),          \
+        static_cast<T*>(out), n, H, L, D, x_strides[0], x_strides[1], x_strides[2], pos0)
+    switch (dtype) {
+        case PARAS_F32: PB_ROPE(float); break;
+        case PARAS_BF16: PB_ROPE(__nv_bfloat16); break;
+        default: PB_ROPE(__half); break;
+    }
+#undef PB_ROPE
+    PB_LAUNCH_CHECK("rope_kernel");
     return PARAS_OK;
 }
 

@@ -6,6 +6,7 @@
 // explicit per-GPU pool: device memory is never host-addressable here, so unified-memory
 // page faults cannot occur.
 #include <atomic>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <thread>
@@ -68,6 +69,19 @@ void init_table() {
     t.count = n;
 }
 
+// PTSYCL_NO_CACHE / PTSYCL_DEBUG_ALLOC, the reference's allocator switches (csrc/core/allocator.cpp:
+// 48-49): the first makes the pool hand freed memory back to the driver at the next synchronisation
+// (release threshold 0) instead of caching it, for leak hunting; the second logs every allocation
+// and release to stderr.
+bool env_flag(const char* name) {
+    const char* e = std::getenv(name);
+    return e && *e && std::strcmp(e, "0") != 0;
+}
+bool debug_alloc() {
+    static const bool on = env_flag("PTSYCL_DEBUG_ALLOC");
+    return on;
+}
+
 // Streams and pools are created the first time a GPU is used, so that a process that
 // only touches one GPU (one rank per GPU) creates no context on the others.
 std::mutex g_lazy_mu;
@@ -86,7 +100,8 @@ int lazy_init_gpu(Gpu& g) {
     props.location.id = g.ordinal;
     cudaMemPool_t pool = nullptr;
     PB_CUDA(cudaMemPoolCreate(&pool, &props));
-    uint64_t keep = ~uint64_t(0);  // never trim on sync: 180 GB of HBM is there to be cached
+    // never trim on sync (180 GB of HBM is there to be cached) unless caching is switched off
+    uint64_t keep = env_flag("PTSYCL_NO_CACHE") ? 0 : ~uint64_t(0);
     PB_CUDA(cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep));
     int* hs = nullptr;
     int* ds = nullptr;
@@ -283,6 +298,7 @@ int paras_b200_malloc_async(int gpu, size_t bytes, void* stream, void** ptr) {
                     "paras_b200: cudaMallocFromPoolAsync(%zu bytes) on gpu %d: %s", bytes, gpu,
                     cudaGetErrorString(e));
     }
+    if (pb::debug_alloc()) std::fprintf(stderr, "[paras_b200] gpu %d alloc %zu bytes -> %p\n", gpu, bytes, *ptr);
     return PARAS_OK;
 }
 
@@ -292,6 +308,7 @@ int paras_b200_free_async(int gpu, void* ptr, void* stream) {
     Gpu* g = use_gpu(gpu, &st);
     if (!g) return st;
     PB_CUDA(cudaFreeAsync(ptr, pb::pick_stream(g, stream)));
+    if (pb::debug_alloc()) std::fprintf(stderr, "[paras_b200] gpu %d free %p\n", gpu, ptr);
     return PARAS_OK;
 }
 

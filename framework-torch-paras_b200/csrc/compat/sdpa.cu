@@ -172,6 +172,67 @@ int paras_b200_sdpa_fwd(const paras_sdpa_args* a) {
     return st;
 }
 
+// ---- attention with the rotary embedding in its prologue -------------------------------------
+int paras_b200_sdpa_rope_fwd(const paras_sdpa_args* a, const void* cosv, const void* sinv, int64_t table_rows,
+                             int64_t q_pos0) {
+    int st = pb::validate(a);
+    if (st != PARAS_OK) return st;
+    if (a->mask || pb::sdpa_wants_weights(*a))
+        return fail(PARAS_E_UNSUPPORTED, "paras sdpa_rope: no mask tensor, dropout or weights output");
+    if (a->D % 2) return fail(PARAS_E_INVALID, "paras sdpa_rope: head dim must be even");
+    if (q_pos0 < 0 || q_pos0 + a->Lq > table_rows || a->Lk > table_rows)
+        return fail(PARAS_E_INVALID, "paras sdpa_rope: cos / sin tables of %lld rows do not cover the positions",
+                    (long long)table_rows);
+    Gpu* g = pb::use_gpu(a->gpu, &st);
+    if (!g) return st;
+    if (int64_t(a->B) * a->Hq * a->Lq * a->D == 0) return PARAS_OK;
+    if (!a->q || !a->out || !cosv || !sinv || (a->Lk > 0 && (!a->k || !a->v)))
+        return fail(PARAS_E_INVALID, "paras sdpa_rope: null pointer");
+    if (a->Lk == 0) return paras_b200_sdpa_fwd(a);   // nothing to rotate against
+    cudaStream_t s = pb::pick_stream(g, a->stream);
+    const size_t es = pb::dtype_size(a->dtype);
+    const size_t k_bytes = (size_t(a->B) * a->Hkv * a->Lk * a->D * es + 255) & ~size_t(255);
+    const size_t q_bytes = (size_t(a->B) * a->Hq * a->Lq * a->D * es + 255) & ~size_t(255);
+
+    // Q is rotated inside the tensor-core kernel when that kernel runs (and its tables can be read
+    // 16 bytes at a time); otherwise by the same streaming pass as K.
+    paras_sdpa_args sub = *a;
+    sub.stream = s;
+    const char* why = "";
+    const bool q_in_kernel = pb::choose(g, sub, &why) == pb::Path::Tensor && a->D == 128 &&
+                             ((reinterpret_cast<uintptr_t>(cosv) | reinterpret_cast<uintptr_t>(sinv)) & 15u) == 0;
+    void* scratch = nullptr;
+    st = paras_b200_malloc_async(a->gpu, k_bytes + (q_in_kernel ? 0 : q_bytes), s, &scratch);
+    if (st != PARAS_OK) return st;
+    char* k_rot = static_cast<char*>(scratch);
+    char* q_rot = k_rot + k_bytes;
+    // K: every query block reads every key tile it sees, so rotating K where it is consumed would
+    // repeat the work once per query block; it is rotated once, here, into scratch.
+    st = paras_b200_rope(a->gpu, a->k, a->k_strides, cosv, sinv, k_rot, a->B, a->Hkv, a->Lk, a->D, 0, a->dtype, s);
+    sub.k = k_rot;
+    sub.k_strides[0] = int64_t(a->Hkv) * a->Lk * a->D;
+    sub.k_strides[1] = int64_t(a->Lk) * a->D;
+    sub.k_strides[2] = a->D;
+    if (st == PARAS_OK && !q_in_kernel) {
+        st = paras_b200_rope(a->gpu, a->q, a->q_strides, cosv, sinv, q_rot, a->B, a->Hq, a->Lq, a->D, q_pos0, a->dtype, s);
+        sub.q = q_rot;
+        sub.q_strides[0] = int64_t(a->Hq) * a->Lq * a->D;
+        sub.q_strides[1] = int64_t(a->Lq) * a->D;
+        sub.q_strides[2] = a->D;
+    }
+    if (st == PARAS_OK) {
+        if (q_in_kernel) {
+            const pb::RopeTables rope{cosv, sinv, q_pos0};
+            st = pb::sdpa_tc_launch(g, sub, pb::effective_scale(sub), s, &rope);
+            if (st == PARAS_OK) pb::set_last_kernel("tcgen05_rope");
+        } else {
+            st = paras_b200_sdpa_fwd(&sub);
+        }
+    }
+    const int st2 = paras_b200_free_async(a->gpu, scratch, s);
+    return st != PARAS_OK ? st : st2;
+}
+
 // ---- attention on host-resident operands ------------------------------------------------
 // Per-GPU streams and events of the pipeline below (created on first use, never destroyed).
 namespace pb {

@@ -46,9 +46,16 @@ int sdpa_simt_pick_splits(const Gpu* g, const paras_sdpa_args& a);
 int sdpa_combine_launch(Gpu* g, const paras_sdpa_args& a, const SplitWorkspace& ws,
                         cudaStream_t s);
 
-// tcgen05/TMEM/TMA kernel: bf16/f16, D == 128, no mask tensor.
+// tcgen05/TMEM/TMA kernel: bf16/f16, D == 128 or 64.  `rope` (optional, D == 128, no mask tensor):
+// the queries are rotated in the kernel's prologue with these tables ([rows, 128] in the tensors'
+// dtype, row = pos0 + query index).
+struct RopeTables {
+    const void* cos;
+    const void* sin;
+    int64_t pos0;
+};
 bool sdpa_tc_supported(const Gpu* g, const paras_sdpa_args& a, const char** why);
-int sdpa_tc_launch(Gpu* g, const paras_sdpa_args& a, float scale, cudaStream_t s);
+int sdpa_tc_launch(Gpu* g, const paras_sdpa_args& a, float scale, cudaStream_t s, const RopeTables* rope = nullptr);
 
 // Tensor-core split-KV decode kernel: 16-bit, D == 128, short Lq, no mask tensor.
 bool sdpa_decode_supported(const Gpu* g, const paras_sdpa_args& a, const char** why);

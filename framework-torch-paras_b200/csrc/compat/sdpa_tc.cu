@@ -87,7 +87,8 @@ constexpr int kBarKVEmpty = kBarKVFull + kStages;  // [kStages]
 constexpr int kBarSFull = kBarKVEmpty + kStages;   // [2]  MMA -> softmax: S_t ready
 constexpr int kBarPFull = kBarSFull + 2;           // [2]  softmax -> MMA: P_t written, O_t rescaled
 constexpr int kBarOFull = kBarPFull + 2;           // [2]  MMA -> softmax: last PV of the item is done
-constexpr int kNumBars = kBarOFull + 2;
+constexpr int kBarQRot = kBarOFull + 2;            // [2]  softmax -> MMA: the Q tile has been rotated in place (RoPE)
+constexpr int kNumBars = kBarQRot + 2;
 constexpr int kSmemMisc = kSmemBars + kNumBars * 8;   // tmem base word, abort flag
 constexpr int kSmemTotal = kSmemMisc + 16;
 constexpr int kSmemLaunch = kSmemTotal + 1024;        // slack to align the base to 1024 B
@@ -106,6 +107,11 @@ struct TcParams {
     int mask_kind;       // 1 bool (true = attend), 2 additive in the tensors' dtype, 3 additive fp32
     int64_t ms[4];
     int* status;
+    // rotary embedding of the queries in the prologue (ROPE kernels): cos / sin [rows, 128] in the
+    // tensors' dtype, read at row rope_pos0 + query index
+    const void* rope_cos;
+    const void* rope_sin;
+    int64_t rope_pos0;
     int nq;      // 256-row query blocks per (batch, head)
     int npair;   // ceil(nq / 2)
     int units;   // B * Hq * npair
@@ -152,9 +158,40 @@ __device__ __forceinline__ bool get_item(const TcParams& p, int seq, Item* it) {
     return true;
 }
 
+// 16-bit pairs for the in-place rotation of a Q row: products and sum each round once to the
+// tensors' dtype, which is what the reference's three binary kernels do (pointwise_ops.cpp:62-85).
+template <bool BF16> struct Pair16;
+template <> struct Pair16<true> {
+    using T2 = __nv_bfloat162;
+};
+template <> struct Pair16<false> {
+    using T2 = __half2;
+};
+// x1, x2: eight elements d.. and d+64.. of a row; c1, s1 / c2, s2: cos and sin at the same columns.
+// out1 = x1*c1 + (-x2)*s1, out2 = x2*c2 + x1*s2  (x*cos + rotate_half(x)*sin, fused_ops.cpp:234-267)
+template <bool BF16>
+__device__ __forceinline__ void rope_rotate8(uint4& x1, uint4& x2, const uint4& c1, const uint4& s1,
+                                             const uint4& c2, const uint4& s2) {
+    using T2 = typename Pair16<BF16>::T2;
+    T2* a = reinterpret_cast<T2*>(&x1);
+    T2* b = reinterpret_cast<T2*>(&x2);
+    const T2* pc1 = reinterpret_cast<const T2*>(&c1);
+    const T2* ps1 = reinterpret_cast<const T2*>(&s1);
+    const T2* pc2 = reinterpret_cast<const T2*>(&c2);
+    const T2* ps2 = reinterpret_cast<const T2*>(&s2);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const T2 o1 = __hadd2(__hmul2(a[i], pc1[i]), __hmul2(__hneg2(b[i]), ps1[i]));
+        const T2 o2 = __hadd2(__hmul2(b[i], pc2[i]), __hmul2(a[i], ps2[i]));
+        a[i] = o1;
+        b[i] = o2;
+    }
+}
+
 // MASK: an explicit attn_mask is applied (a separate instantiation: the unmasked kernel pays
-// nothing for it, not even registers).
-template <bool BF16, bool MASK, int HD>
+// nothing for it, not even registers).  ROPE: the query tile is rotated in shared memory, by the
+// softmax warps that own its rows, between its TMA load and the first QK^T (head dim 128).
+template <bool BF16, bool MASK, int HD, bool ROPE = false>
 __global__ void __launch_bounds__(kThreads, 1)
 sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o,
@@ -172,7 +209,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < kNumBars; ++i) {
-            const bool four = i >= kBarPFull && i < kBarPFull + 2;
+            const bool four = (i >= kBarPFull && i < kBarPFull + 2) || i >= kBarQRot;
             const bool two = i >= kBarKVFull && i < kBarKVFull + kStages;
             // one arrival per softmax warp / per entry of a K/V pair / else one commit or TMA
             mbar_init(bar(i), four ? 4u : (two ? 2u : 1u));
@@ -288,7 +325,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 #pragma unroll
                 for (int t = 0; t < 2; ++t) {
                     if (ok && it.ntile[t] > 0) {
-                        ok = mbar_wait(bar(kBarQFull + t), qcnt[t] & 1u, abort_flag, 4 + t);
+                        ok = mbar_wait(bar((ROPE ? kBarQRot : kBarQFull) + t), qcnt[t] & 1u, abort_flag, 4 + t);
                         if (ok) {
                             tc_fence_after_sync();
                             issue_qk(t, G);
@@ -354,6 +391,31 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             const int nt = it.ntile[t];
             if (nt == 0) continue;
             const int row_q = it.start[t] + wq * 32 + lane;
+            if (ROPE) {
+                // this lane's row of the freshly landed Q tile, rotated in place: 16-byte unit u of row r
+                // sits at u ^ (r & 7) in each 64-column slab; columns d and d + 64 share the offset
+                ok = mbar_wait(bar(kBarQFull + t), ocnt & 1u, abort_flag, 18 + t);
+                if (!ok) break;
+                if (row_q < p.Lq) {
+                    const int r = wq * 32 + lane;
+                    const uint32_t row_addr = smem_base + kSmemQ + t * kTileBytes + r * 128;
+                    const uint4* cs = static_cast<const uint4*>(p.rope_cos) + (p.rope_pos0 + row_q) * (HD / 8);
+                    const uint4* sn = static_cast<const uint4*>(p.rope_sin) + (p.rope_pos0 + row_q) * (HD / 8);
+#pragma unroll 2
+                    for (int u = 0; u < 8; ++u) {
+                        const uint32_t off = uint32_t((u ^ (r & 7)) << 4);
+                        uint4 x1, x2;
+                        asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(x1.x), "=r"(x1.y), "=r"(x1.z), "=r"(x1.w) : "r"(row_addr + off));
+                        asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(x2.x), "=r"(x2.y), "=r"(x2.z), "=r"(x2.w) : "r"(row_addr + kChunkBytes + off));
+                        rope_rotate8<BF16>(x1, x2, __ldg(cs + u), __ldg(sn + u), __ldg(cs + 8 + u), __ldg(sn + 8 + u));
+                        st_shared_v4(row_addr + off, x1);
+                        st_shared_v4(row_addr + kChunkBytes + off, x2);
+                    }
+                }
+                fence_proxy_async_smem();   // generic-proxy stores -> visible to the tensor core's reads
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar(kBarQRot + t));
+            }
             // Explicit attn_mask (csrc/ops/attention_ops.cpp:117-126): this thread's row of it, 128
             // entries per kv tile.  Bool: false -> -inf.  Additive: S is still unscaled here, so the
             // mask value joins it divided by the scale.  Rows past the end reuse the last row.
@@ -621,7 +683,7 @@ bool sdpa_tc_supported(const Gpu* g, const paras_sdpa_args& a, const char** why)
     return true;
 }
 
-int sdpa_tc_launch(Gpu* g, const paras_sdpa_args& a, float scale, cudaStream_t s) {
+int sdpa_tc_launch(Gpu* g, const paras_sdpa_args& a, float scale, cudaStream_t s, const RopeTables* rope) {
     int st = check_status_word(g);  // an earlier launch's failure is reported once, here
     if (st != PARAS_OK) return st;
     CUtensorMap mq, mk, mv, mo;
@@ -643,6 +705,11 @@ int sdpa_tc_launch(Gpu* g, const paras_sdpa_args& a, float scale, cudaStream_t s
     p.mask_kind = a.mask ? a.mask_kind : 0;
     for (int i = 0; i < 4; ++i) p.ms[i] = a.mask_strides[i];
     p.status = g->status_dev;
+    if (rope) {
+        if (a.D != 128 || p.mask_kind)
+            return fail(PARAS_E_UNSUPPORTED, "paras sdpa: the rotary prologue takes head dim 128 and no mask tensor");
+        p.rope_cos = rope->cos; p.rope_sin = rope->sin; p.rope_pos0 = rope->pos0;
+    }
     p.nq = (a.Lq + kTilesPerCta * BM - 1) / (kTilesPerCta * BM);
     p.npair = (p.nq + 1) / 2;
     const int64_t units = int64_t(a.B) * a.Hq * p.npair;
@@ -656,7 +723,9 @@ int sdpa_tc_launch(Gpu* g, const paras_sdpa_args& a, float scale, cudaStream_t s
         return PARAS_OK;
     };
     const bool bf = a.dtype == PARAS_BF16;
-    if (a.D == 128) {
+    if (rope) {
+        st = bf ? launch(sdpa_tc_kernel<true, false, 128, true>) : launch(sdpa_tc_kernel<false, false, 128, true>);
+    } else if (a.D == 128) {
         if (p.mask_kind) st = bf ? launch(sdpa_tc_kernel<true, true, 128>) : launch(sdpa_tc_kernel<false, true, 128>);
         else st = bf ? launch(sdpa_tc_kernel<true, false, 128>) : launch(sdpa_tc_kernel<false, false, 128>);
     } else {

@@ -270,6 +270,69 @@ std::tuple<Tensor, Tensor, Tensor> sdpa_backward(const Tensor& grad_out, const T
     return {dq, dk, dv};
 }
 
+// ---- rotary embedding fused into the attention prologue ----------------------------------------
+// paras::sdpa_rope(q, k, v, cos, sin, is_causal, scale, q_pos0) = sdpa(rope(q), rope(k), v) with
+// rope(x) = x * cos + rotate_half(x) * sin -- the composition a model builds from paras::rotate_half
+// (fused_ops.cpp:234-267) and the reference's mul / add in front of its attention.  New operators
+// (forward only); [batch, heads, seq, head_dim] tensors, cos / sin [positions, head_dim].
+Tensor sdpa_rope(const Tensor& query, const Tensor& key, const Tensor& value, const Tensor& cos, const Tensor& sin,
+                 bool is_causal, std::optional<double> scale, int64_t q_pos0) {
+    PARAS_TRACE_OP("paras::sdpa_rope");
+    TORCH_CHECK(query.dim() == 4 && key.dim() == 4 && value.dim() == 4,
+                "paras sdpa_rope: [batch, heads, seq, head_dim] tensors");
+    const int dt = dtype_code(query.scalar_type());
+    TORCH_CHECK(dt >= 0 && key.scalar_type() == query.scalar_type() && value.scalar_type() == query.scalar_type() &&
+                    cos.scalar_type() == query.scalar_type() && sin.scalar_type() == query.scalar_type(),
+                "paras sdpa_rope: query, key, value, cos and sin must share one of float32, bfloat16, float16");
+    const int64_t B = query.size(0), Hq = query.size(1), Lq = query.size(2), E = query.size(3);
+    const int64_t Hkv = key.size(1), Lk = key.size(2);
+    TORCH_CHECK(key.size(0) == B && value.sizes() == key.sizes() && key.size(3) == E && Hkv > 0 && Hq % Hkv == 0,
+                "paras sdpa_rope: shapes do not fit (query heads must be a multiple of key/value heads)");
+    TORCH_CHECK(cos.dim() == 2 && cos.size(1) == E && sin.sizes() == cos.sizes(),
+                "paras sdpa_rope: cos and sin must be [positions, head_dim]");
+    TORCH_CHECK(q_pos0 >= 0 && q_pos0 + Lq <= cos.size(0) && Lk <= cos.size(0),
+                "paras sdpa_rope: cos / sin cover ", cos.size(0), " positions, fewer than the sequence needs");
+    Runtime& rt = Runtime::get();
+    c10::DeviceGuard guard(query.device());
+    auto unit = [](const Tensor& t) { return (t.size(-1) > 1 && t.stride(-1) != 1) ? t.contiguous() : t; };
+    Tensor q = unit(query), k = unit(key), v = unit(value), c = cos.contiguous(), sn = sin.contiguous();
+    Tensor out = at::empty({B, Hq, Lq, E}, q.options());
+    paras_sdpa_args a{};
+    a.q = q.data_ptr(); a.k = k.data_ptr(); a.v = v.data_ptr(); a.out = out.data_ptr();
+    a.dtype = dt;
+    a.B = int32_t(B); a.Hq = int32_t(Hq); a.Hkv = int32_t(Hkv); a.Lq = int32_t(Lq); a.Lk = int32_t(Lk); a.D = int32_t(E);
+    for (int i = 0; i < 3; ++i) {
+        a.q_strides[i] = q.stride(i); a.k_strides[i] = k.stride(i);
+        a.v_strides[i] = v.stride(i); a.o_strides[i] = out.stride(i);
+    }
+    a.causal = is_causal ? 1 : 0;
+    a.scale = scale.has_value() ? *scale : 1.0 / std::sqrt(double(E));
+    a.flags = ref_scale_rounding() ? PARAS_SDPA_REF_SCALE : 0;
+    a.gpu = rt.gpu_of(query);
+    PARAS_ABI(paras_b200_sdpa_rope_fwd(&a, c.data_ptr(), sn.data_ptr(), c.size(0), q_pos0));
+    return out;
+}
+
+Tensor rope(const Tensor& x, const Tensor& cos, const Tensor& sin, int64_t pos0) {
+    PARAS_TRACE_OP("paras::rope");
+    TORCH_CHECK(x.dim() == 4, "paras rope: [batch, heads, seq, head_dim] tensor");
+    const int dt = dtype_code(x.scalar_type());
+    TORCH_CHECK(dt >= 0 && cos.scalar_type() == x.scalar_type() && sin.scalar_type() == x.scalar_type(),
+                "paras rope: x, cos and sin must share one of float32, bfloat16, float16");
+    TORCH_CHECK(x.size(3) % 2 == 0, "paras rope: last dimension must be even");
+    TORCH_CHECK(cos.dim() == 2 && cos.size(1) == x.size(3) && sin.sizes() == cos.sizes() && pos0 >= 0 &&
+                    pos0 + x.size(2) <= cos.size(0),
+                "paras rope: cos and sin must be [positions, head_dim] and cover the sequence");
+    c10::DeviceGuard guard(x.device());
+    Tensor xs = (x.size(-1) > 1 && x.stride(-1) != 1) ? x.contiguous() : x;
+    Tensor c = cos.contiguous(), sn = sin.contiguous();
+    Tensor out = at::empty(x.sizes(), x.options());
+    const int64_t st[3] = {xs.stride(0), xs.stride(1), xs.stride(2)};
+    PARAS_ABI(paras_b200_rope(Runtime::get().gpu_of(x), xs.data_ptr(), st, c.data_ptr(), sn.data_ptr(), out.data_ptr(),
+                              int(x.size(0)), int(x.size(1)), int(x.size(2)), int(x.size(3)), pos0, dt, nullptr));
+    return out;
+}
+
 // ---- autograd for F.scaled_dot_product_attention on `paras` tensors ----------------------
 // The reference's sdpa_math is built from at:: operators, so autograd differentiates through it
 // (attention_ops.cpp:71-136).  A fused kernel registered for the backend replaces that
@@ -347,8 +410,13 @@ TORCH_LIBRARY_FRAGMENT(paras, m) {
     m.def("sdpa_train_forward(Tensor query, Tensor key, Tensor value, bool is_causal, float? scale) -> (Tensor, Tensor)");
     m.def("sdpa_backward(Tensor grad_out, Tensor query, Tensor key, Tensor value, Tensor out, Tensor lse, "
           "bool is_causal, float? scale) -> (Tensor, Tensor, Tensor)");
+    m.def("sdpa_rope(Tensor query, Tensor key, Tensor value, Tensor cos, Tensor sin, bool is_causal, float? scale, "
+          "int q_pos0=0) -> Tensor");
+    m.def("rope(Tensor x, Tensor cos, Tensor sin, int pos0=0) -> Tensor");
 }
 TORCH_LIBRARY_IMPL(paras, PrivateUse1, m) {
     m.impl("sdpa_train_forward", &paras::sdpa_train_forward);
     m.impl("sdpa_backward", &paras::sdpa_backward);
+    m.impl("sdpa_rope", &paras::sdpa_rope);
+    m.impl("rope", &paras::rope);
 }

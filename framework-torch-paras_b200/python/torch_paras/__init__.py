@@ -35,7 +35,7 @@ __all__ = [
 
 
 def device_count() -> int:
-    """Number of paras devices: the host (index 0) plus the visible GPUs."""
+    """How many ``paras`` devices there are: index 0 is the host, 1.. are the visible GPUs."""
     return _C.device_count()
 
 
@@ -60,7 +60,8 @@ def is_gpu_device(device: int) -> bool:
 
 
 def synchronize(device: int | None = None) -> None:
-    """Blocks until queued work on one device (or all devices) completes."""
+    """Waits for everything launched so far on ``device`` -- on every device when none is given.  This
+    is also where a kernel's bounded wait that ran out is reported (RuntimeError)."""
     if device is None:
         _C.synchronize_all()
     else:
@@ -79,7 +80,8 @@ def manual_seed_all(seed: int) -> None:
 
 
 def empty_cache() -> None:
-    """Returns cached blocks of the per-GPU stream-ordered pools to the driver."""
+    """Gives the memory the per-GPU stream-ordered pools hold but do not use back to the driver
+    (``PTSYCL_NO_CACHE=1`` in the environment keeps the pools from caching in the first place)."""
     _C.empty_cache()
 
 

@@ -36,7 +36,7 @@ EXPORTS = [
     "paras_b200_rmsnorm_bwd", "paras_b200_swiglu_fwd", "paras_b200_swiglu_bwd",
     "paras_b200_rotate_half", "paras_b200_gemm", "paras_b200_sdpa_fwd_host", "paras_b200_sdpa_bwd",
     "paras_b200_sdpa_split_layout", "paras_b200_selftest_bounded_wait",
-    "paras_b200_rms_rstd", "paras_b200_scale_columns",
+    "paras_b200_rms_rstd", "paras_b200_scale_columns", "paras_b200_sdpa_rope_fwd", "paras_b200_rope",
 ]
 
 
@@ -125,6 +125,9 @@ def lib() -> C.CDLL:
         L.paras_b200_sdpa_split_layout.argtypes = [C.c_int64, C.c_int32, C.c_int32, C.POINTER(C.c_size_t),
                                                    C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)]
         L.paras_b200_selftest_bounded_wait.argtypes = [C.c_int, C.c_uint32, C.POINTER(C.c_int)]
+        L.paras_b200_sdpa_rope_fwd.argtypes = [C.POINTER(SdpaArgs), C.c_void_p, C.c_void_p, C.c_int64, C.c_int64]
+        L.paras_b200_rope.argtypes = [C.c_int, C.c_void_p, C.POINTER(C.c_int64), C.c_void_p, C.c_void_p, C.c_void_p,
+                                      C.c_int, C.c_int, C.c_int, C.c_int, C.c_int64, C.c_int, C.c_void_p]
         L.paras_b200_rms_rstd.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_double,
                                           C.c_int, C.c_void_p]
         L.paras_b200_scale_columns.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64,
@@ -232,6 +235,26 @@ def sdpa_fwd(q, k, v, *, causal=False, scale=None, mask=None, return_lse=False, 
     check(lib().paras_b200_sdpa_fwd(C.byref(a)))
     res = (out,) + ((lse,) if return_lse else ()) + ((weights,) if return_weights else ())
     return res if len(res) > 1 else out
+
+
+def sdpa_rope_fwd(q, k, v, cos, sin, *, causal=False, scale=None, q_pos0=0, flags=0, out=None, stream=None):
+    """sdpa(rope(q), rope(k), v) through ``paras_b200_sdpa_rope_fwd``; cos / sin [rows, D] in q's dtype."""
+    if out is None:
+        out = torch.empty(q.shape, dtype=q.dtype, device=q.device)
+    assert cos.is_contiguous() and sin.is_contiguous() and cos.shape == sin.shape and cos.dtype == q.dtype
+    a = sdpa_args(q, k, v, out, causal=causal, scale=scale, flags=flags, stream=stream)
+    check(lib().paras_b200_sdpa_rope_fwd(C.byref(a), cos.data_ptr(), sin.data_ptr(), cos.shape[0], q_pos0))
+    return out
+
+
+def rope(x, cos, sin, *, pos0=0, stream=None):
+    """x * cos + rotate_half(x) * sin for x [B, H, L, D] (any B/H/L strides), rounding per operation."""
+    out = torch.empty(x.shape, dtype=x.dtype, device=x.device)
+    st = (C.c_int64 * 3)(x.stride(0), x.stride(1), x.stride(2))
+    check(lib().paras_b200_rope(_gpu_of(x), x.data_ptr(), st, cos.data_ptr(), sin.data_ptr(), out.data_ptr(),
+                                x.shape[0], x.shape[1], x.shape[2], x.shape[3], pos0, dtype_code(x),
+                                _stream_of(x, stream)))
+    return out
 
 
 def sdpa_fwd_host(q, k, v, *, causal=False, scale=None, flags=0, out=None, gpu=0):

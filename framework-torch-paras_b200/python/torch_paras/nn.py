@@ -8,7 +8,8 @@ import torch
 
 from . import _C  # noqa: F401  (loads the operator registrations)
 
-__all__ = ["rms_norm", "swiglu", "rotate_half", "swiglu_linear", "rms_norm_linear", "fold_norm_weight",
+__all__ = ["rms_norm", "swiglu", "rotate_half", "rope", "attention_rope", "swiglu_linear", "rms_norm_linear",
+           "fold_norm_weight",
            "attention_host", "scaled_dot_product_attention"]
 
 
@@ -123,6 +124,20 @@ def scaled_dot_product_attention(query: torch.Tensor, key: torch.Tensor, value: 
     batched GEMMs and two element-wise passes.  ``F.scaled_dot_product_attention`` on the device is
     the inference entry point (forward only, masks, any rank)."""
     return _SDPA.apply(query, key, value, is_causal, scale)
+
+
+def rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, pos0: int = 0) -> torch.Tensor:
+    """Rotary embedding ``x * cos + rotate_half(x) * sin`` in one kernel (forward only): ``x`` is
+    ``[batch, heads, seq, head_dim]``, ``cos`` / ``sin`` ``[positions, head_dim]`` read from row ``pos0``."""
+    return torch.ops.paras.rope(x, cos, sin, pos0)
+
+
+def attention_rope(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, cos: torch.Tensor,
+                   sin: torch.Tensor, *, is_causal: bool = False, scale=None, q_pos0: int = 0) -> torch.Tensor:
+    """``scaled_dot_product_attention(rope(query), rope(key), value)`` (forward only) without the rotated
+    queries ever reaching memory: with 16-bit tensors and head dim 128 they are rotated inside the
+    attention kernel; the keys are rotated once, on the way in."""
+    return torch.ops.paras.sdpa_rope(query, key, value, cos, sin, is_causal, scale, q_pos0)
 
 
 def rotate_half(x: torch.Tensor) -> torch.Tensor:

@@ -173,6 +173,22 @@ int paras_b200_sdpa_workspace_bytes(const paras_sdpa_args* args, size_t* bytes);
  * ("tcgen05", "simt", "decode_mma", ...); for tests and logs. */
 const char* paras_b200_sdpa_last_kernel(void);
 
+/* Attention with the rotary position embedding applied to q and k first:
+ *     q' = q * cos + rotate_half(q) * sin      (rows q_pos0 .. q_pos0+Lq-1 of the tables)
+ *     k' = k * cos + rotate_half(k) * sin      (rows 0 .. Lk-1)
+ *     out = sdpa(q', k', v)
+ * i.e. what a model composes from paras::rotate_half (csrc/ops/fused_ops.cpp:234-267), two mul and an
+ * add (pointwise_ops.cpp:62-85, each rounding to the dtype) in front of sdpa_math
+ * (attention_ops.cpp:71-136).  cos, sin: [table_rows, D] contiguous in `dtype`.  With 16-bit tensors
+ * and D = 128 the queries are rotated inside the tensor-core kernel, between their TMA load and the
+ * first QK^T; the keys -- which every query block re-reads -- are rotated once into pool scratch.
+ * No mask tensor, dropout or weights output. */
+int paras_b200_sdpa_rope_fwd(const paras_sdpa_args* args, const void* cos, const void* sin,
+                             int64_t table_rows, int64_t q_pos0);
+/* The rotation alone, out dense [B, H, L, D]; x with element strides {B, H, L} and unit stride on D. */
+int paras_b200_rope(int gpu, const void* x, const int64_t* x_strides, const void* cos, const void* sin,
+                    void* out, int B, int H, int L, int D, int64_t pos0, int dtype, void* stream);
+
 /* Layout of the split-KV scratch for `splits` > 1 partial results over `rows` = B*Hq*Lq query
  * rows of D elements: byte offsets of the {max, sum} pairs (8-byte entries) and of the fp32
  * partial outputs inside the scratch, and its total size (what paras_b200_sdpa_workspace_bytes

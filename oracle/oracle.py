@@ -269,6 +269,18 @@ def rotate_half(x: Tensor) -> Tensor:
     return torch.cat((-x2, x1), dim=-1)
 
 
+def rope(x: Tensor, cos: Tensor, sin: Tensor, pos0: int = 0) -> Tensor:
+    """Rotary embedding as a user of the reference composes it from its operators:
+    x * cos + rotate_half(x) * sin, with x [..., L, D] and cos/sin [Lmax, D] rows pos0 .. pos0+L-1;
+    each of the two products and the sum is a binary kernel that rounds to the tensor dtype
+    (pointwise_ops.cpp:62-85), rotate_half is exact (fused_ops.cpp:234-267)."""
+    L = x.size(-2)
+    c, sn = cos[pos0:pos0 + L].to(torch.float64), sin[pos0:pos0 + L].to(torch.float64)
+    t1 = _cast(x.to(torch.float64) * c, x.dtype)
+    t2 = _cast(rotate_half(x).to(torch.float64) * sn, x.dtype)
+    return _cast(t1.to(torch.float64) + t2.to(torch.float64), x.dtype)
+
+
 def rotate_half_backward(g: Tensor) -> Tensor:
     """paras::rotate_half_backward (fused_ops.cpp:269-302): cat(g2, -g1)."""
     d = g.size(-1)
