@@ -116,6 +116,38 @@ __device__ __forceinline__ void st16_stream(T* p, const Vec16<T>& r) {
     __stcs(reinterpret_cast<uint4*>(p), *reinterpret_cast<const uint4*>(&r));
 }
 
+// Rotary embedding on packed 16-bit pairs: the two products and the sum each round once to the
+// tensors' dtype, which is what the reference's three binary kernels do (pointwise_ops.cpp:62-85).
+template <bool BF16> struct Pair16;
+template <> struct Pair16<true> {
+    using T2 = __nv_bfloat162;
+};
+template <> struct Pair16<false> {
+    using T2 = __half2;
+};
+// x1, x2: eight elements d.. and d+64.. of a row; c1, s1 / c2, s2: cos and sin at the same columns.
+// out1 = x1*c1 + (-x2)*s1, out2 = x2*c2 + x1*s2  (x*cos + rotate_half(x)*sin, fused_ops.cpp:234-267)
+template <bool BF16>
+__device__ __forceinline__ void rope_rotate8(uint4& x1, uint4& x2, const uint4& c1, const uint4& s1,
+                                             const uint4& c2, const uint4& s2) {
+    using T2 = typename Pair16<BF16>::T2;
+    T2* a = reinterpret_cast<T2*>(&x1);
+    T2* b = reinterpret_cast<T2*>(&x2);
+    const T2* pc1 = reinterpret_cast<const T2*>(&c1);
+    const T2* ps1 = reinterpret_cast<const T2*>(&s1);
+    const T2* pc2 = reinterpret_cast<const T2*>(&c2);
+    const T2* ps2 = reinterpret_cast<const T2*>(&s2);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        // (_rn forms: no contraction of a product and the sum into a fused multiply-add, which would
+        // skip the product's rounding)
+        const T2 o1 = __hadd2_rn(__hmul2_rn(a[i], pc1[i]), __hmul2_rn(__hneg2(b[i]), ps1[i]));
+        const T2 o2 = __hadd2_rn(__hmul2_rn(b[i], pc2[i]), __hmul2_rn(a[i], ps2[i]));
+        a[i] = o1;
+        b[i] = o2;
+    }
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

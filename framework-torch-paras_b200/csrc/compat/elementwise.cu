@@ -138,6 +138,35 @@ rope_kernel(const T* __restrict__ x, const T* __restrict__ cosv, const T* __rest
     }
 }
 
+// The same for 16-bit tensors whose rows can be read 16 bytes at a time: a thread takes eight
+// columns d.. and the matching eight at d + D/2 (six 128-bit loads, two stores, packed arithmetic).
+template <bool BF16>
+__global__ void __launch_bounds__(kThreads)
+rope_vec16_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ cosv, const uint16_t* __restrict__ sinv,
+                  uint16_t* __restrict__ out, int64_t n_units, int H, int L, int D, int64_t sb, int64_t sh, int64_t sl,
+                  int64_t pos0) {
+    const int upr = D / 16;   // 8-element units per half row
+    for (int64_t i = int64_t(blockIdx.x) * kThreads + threadIdx.x; i < n_units; i += int64_t(gridDim.x) * kThreads) {
+        const int u = int(i % upr);
+        int64_t r = i / upr;
+        const int l = int(r % L);
+        r /= L;
+        const int h = int(r % H);
+        const int64_t b = r / H;
+        const uint16_t* xr = x + b * sb + h * sh + int64_t(l) * sl;
+        const uint16_t* cr = cosv + (pos0 + l) * D;
+        const uint16_t* sr = sinv + (pos0 + l) * D;
+        uint4 x1 = __ldcs(reinterpret_cast<const uint4*>(xr + 8 * u));
+        uint4 x2 = __ldcs(reinterpret_cast<const uint4*>(xr + D / 2 + 8 * u));
+        rope_rotate8<BF16>(x1, x2, __ldg(reinterpret_cast<const uint4*>(cr + 8 * u)), __ldg(reinterpret_cast<const uint4*>(sr + 8 * u)),
+                           __ldg(reinterpret_cast<const uint4*>(cr + D / 2 + 8 * u)),
+                           __ldg(reinterpret_cast<const uint4*>(sr + D / 2 + 8 * u)));
+        uint16_t* o = out + ((b * H + h) * int64_t(L) + l) * D;
+        __stcs(reinterpret_cast<uint4*>(o + 8 * u), x1);
+        __stcs(reinterpret_cast<uint4*>(o + D / 2 + 8 * u), x2);
+    }
+}
+
 // ---- strided copy with conversion ----------------------------------------------------
 struct CopySpec {
     int ndim;
@@ -346,6 +375,25 @@ int paras_b200_rope(int gpu, const void* x, const int64_t* x_strides, const void
     if (n == 0) return PARAS_OK;
     if (!x || !x_strides || !cosv || !sinv || !out) return fail(PARAS_E_INVALID, "paras rope: null pointer");
     cudaStream_t s = pb::pick_stream(g, stream);
+    // 16-bit rows readable 16 bytes at a time (both halves): the vector kernel
+    const bool vec = dtype != PARAS_F32 && D % 16 == 0 && x_strides[2] % 8 == 0 && x_strides[1] % 8 == 0 &&
+                     x_strides[0] % 8 == 0 &&
+                     ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(cosv) | reinterpret_cast<uintptr_t>(sinv) |
+                       reinterpret_cast<uintptr_t>(out)) & 15u) == 0;
+    if (vec) {
+        const int64_t units = int64_t(B) * H * L * (D / 16);
+        const int vblocks = pb::grid_for(g, units, pb::kThreads);
+        auto px = static_cast<const uint16_t*>(x);
+        auto pc = static_cast<const uint16_t*>(cosv);
+        auto ps = static_cast<const uint16_t*>(sinv);
+        auto po = static_cast<uint16_t*>(out);
+        if (dtype == PARAS_BF16)
+            pb::rope_vec16_kernel<true><<<vblocks, pb::kThreads, 0, s>>>(px, pc, ps, po, units, H, L, D, x_strides[0], x_strides[1], x_strides[2], pos0);
+        else
+            pb::rope_vec16_kernel<false><<<vblocks, pb::kThreads, 0, s>>>(px, pc, ps, po, units, H, L, D, x_strides[0], x_strides[1], x_strides[2], pos0);
+        PB_LAUNCH_CHECK("rope_vec16_kernel");
+        return PARAS_OK;
+    }
     const int blocks = pb::grid_for(g, n, pb::kThreads);
 #define PB_ROPE(T)                                                                                   \
     pb::rope_kernel<T><<<blocks, pb::kThreads, 0, s>>>(                                               \

@@ -158,36 +158,6 @@ __device__ __forceinline__ bool get_item(const TcParams& p, int seq, Item* it) {
     return true;
 }
 
-// 16-bit pairs for the in-place rotation of a Q row: products and sum each round once to the
-// tensors' dtype, which is what the reference's three binary kernels do (pointwise_ops.cpp:62-85).
-template <bool BF16> struct Pair16;
-template <> struct Pair16<true> {
-    using T2 = __nv_bfloat162;
-};
-template <> struct Pair16<false> {
-    using T2 = __half2;
-};
-// x1, x2: eight elements d.. and d+64.. of a row; c1, s1 / c2, s2: cos and sin at the same columns.
-// out1 = x1*c1 + (-x2)*s1, out2 = x2*c2 + x1*s2  (x*cos + rotate_half(x)*sin, fused_ops.cpp:234-267)
-template <bool BF16>
-__device__ __forceinline__ void rope_rotate8(uint4& x1, uint4& x2, const uint4& c1, const uint4& s1,
-                                             const uint4& c2, const uint4& s2) {
-    using T2 = typename Pair16<BF16>::T2;
-    T2* a = reinterpret_cast<T2*>(&x1);
-    T2* b = reinterpret_cast<T2*>(&x2);
-    const T2* pc1 = reinterpret_cast<const T2*>(&c1);
-    const T2* ps1 = reinterpret_cast<const T2*>(&s1);
-    const T2* pc2 = reinterpret_cast<const T2*>(&c2);
-    const T2* ps2 = reinterpret_cast<const T2*>(&s2);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const T2 o1 = __hadd2(__hmul2(a[i], pc1[i]), __hmul2(__hneg2(b[i]), ps1[i]));
-        const T2 o2 = __hadd2(__hmul2(b[i], pc2[i]), __hmul2(a[i], ps2[i]));
-        a[i] = o1;
-        b[i] = o2;
-    }
-}
-
 // MASK: an explicit attn_mask is applied (a separate instantiation: the unmasked kernel pays
 // nothing for it, not even registers).  ROPE: the query tile is rotated in shared memory, by the
 // softmax warps that own its rows, between its TMA load and the first QK^T (head dim 128).
@@ -396,20 +366,40 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                 // sits at u ^ (r & 7) in each 64-column slab; columns d and d + 64 share the offset
                 ok = mbar_wait(bar(kBarQFull + t), ocnt & 1u, abort_flag, 18 + t);
                 if (!ok) break;
-                if (row_q < p.Lq) {
-                    const int r = wq * 32 + lane;
-                    const uint32_t row_addr = smem_base + kSmemQ + t * kTileBytes + r * 128;
-                    const uint4* cs = static_cast<const uint4*>(p.rope_cos) + (p.rope_pos0 + row_q) * (HD / 8);
-                    const uint4* sn = static_cast<const uint4*>(p.rope_sin) + (p.rope_pos0 + row_q) * (HD / 8);
-#pragma unroll 2
-                    for (int u = 0; u < 8; ++u) {
-                        const uint32_t off = uint32_t((u ^ (r & 7)) << 4);
-                        uint4 x1, x2;
-                        asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(x1.x), "=r"(x1.y), "=r"(x1.z), "=r"(x1.w) : "r"(row_addr + off));
-                        asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(x2.x), "=r"(x2.y), "=r"(x2.z), "=r"(x2.w) : "r"(row_addr + kChunkBytes + off));
-                        rope_rotate8<BF16>(x1, x2, __ldg(cs + u), __ldg(sn + u), __ldg(cs + 8 + u), __ldg(sn + 8 + u));
-                        st_shared_v4(row_addr + off, x1);
-                        st_shared_v4(row_addr + kChunkBytes + off, x2);
+                {
+                    // The warp rotates its 32 rows four at a time, eight lanes per row: lane l takes
+                    // 16-byte unit (l & 7) of row 4g + (l >> 3) in both 64-column slabs.  The table rows
+                    // are then read 128 contiguous bytes per row (a lane per row would touch 32 rows
+                    // per instruction), and sixteen of those loads are in flight before the first use.
+                    const int u = lane & 7;
+                    const uint32_t tile = smem_base + kSmemQ + t * kTileBytes;
+                    const int64_t pos_w = p.rope_pos0 + it.start[t] + wq * 32;
+                    const uint4* cs = static_cast<const uint4*>(p.rope_cos);
+                    const uint4* sn = static_cast<const uint4*>(p.rope_sin);
+#pragma unroll 1
+                    for (int g0 = 0; g0 < 8; g0 += 4) {
+                        uint4 c1[4], s1[4], c2[4], s2[4];
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const int rr = 4 * (g0 + i) + (lane >> 3);                 // row within the warp's 32
+                            const bool live = it.start[t] + wq * 32 + rr < p.Lq;
+                            const int64_t trow = live ? (pos_w + rr) * (HD / 8) : 0;   // rows past the end: any valid row
+                            c1[i] = __ldg(cs + trow + u);
+                            s1[i] = __ldg(sn + trow + u);
+                            c2[i] = __ldg(cs + trow + 8 + u);
+                            s2[i] = __ldg(sn + trow + 8 + u);
+                        }
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const int r = wq * 32 + 4 * (g0 + i) + (lane >> 3);        // row within the tile
+                            const uint32_t addr = tile + r * 128 + uint32_t((u ^ (r & 7)) << 4);
+                            uint4 x1, x2;
+                            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(x1.x), "=r"(x1.y), "=r"(x1.z), "=r"(x1.w) : "r"(addr));
+                            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(x2.x), "=r"(x2.y), "=r"(x2.z), "=r"(x2.w) : "r"(addr + kChunkBytes));
+                            rope_rotate8<BF16>(x1, x2, c1[i], s1[i], c2[i], s2[i]);
+                            st_shared_v4(addr, x1);
+                            st_shared_v4(addr + kChunkBytes, x2);
+                        }
                     }
                 }
                 fence_proxy_async_smem();   // generic-proxy stores -> visible to the tensor core's reads
