@@ -156,7 +156,8 @@ def ingest_ncu(csv_path: str):
         i = col[metric]
         return sum(float(r[i].replace(",", "")) * mult.get(units[i], 1.0) for r in launches) / len(launches)
 
-    out = {"kernel": launches[0][col["Kernel Name"]].split("(")[0].replace(" ", ""), "launches": len(launches),
+    name = launches[0][col["Kernel Name"]]
+    out = {"kernel": name[name.index("sdpa_tc_kernel"):].split("(")[0].replace(" ", ""), "launches": len(launches),
            "dram_bytes_read": mean("dram__bytes_read.sum"), "dram_bytes_write": mean("dram__bytes_write.sum"),
            "gpu_time_ns": mean("gpu__time_duration.sum")}
     for extra_metric, key in (("sm__pipe_tensor_cycles_active.avg.pct_of_peak_sustained_elapsed", "tensor_pipe_pct"),

@@ -170,27 +170,63 @@ __device__ __forceinline__ void store_row32(void* dst, const uint32_t (&o)[32]) 
 }
 
 // ---------------------------------------------------------------------------------------------
-// dK / dV: own pair = (K_j, V_j), streamed pair = (Q_i, dO_i) over the group's query heads.
+// dK / dV: own pair = (K_j, V_j), streamed = (Q, dO) of the query tiles that see the keys, 64
+// queries per step, over the group's query heads.
+//
+// A step's chain is  S^T ready -> exponentials -> P^T handed back -> dV,  and with whole 128-query
+// tiles that chain was the step: P^T overlays S^T in TMEM, so the next S^T had to wait for dV.  With
+// 64 queries per step S^T and dP^T are 64 columns each and fit twice: the tensor core forms step
+// x+1's pair in the other buffer while the element-wise warps work on step x, and the same shared
+// memory holds a ring of four 64-query stages instead of two 128-query ones.
+//
+// Two threads issue MMAs, from different warps: one forms the (S^T, dP^T) pairs as soon as a ring
+// stage and a TMEM buffer are free, the other issues dV and dK when the element-wise warps hand
+// P^T and dS^T back.  An issuing thread is serial -- every wait costs it a few hundred cycles
+// during which it issues nothing -- so with a single one the tensor core idled through each wait;
+// the two streams wait on different things and keep it fed.
 // ---------------------------------------------------------------------------------------------
+constexpr int kDkvHalf = 64;                          // queries per step
+constexpr int kDkvStages = 4;
+constexpr int kDkvHalfChunkBytes = kDkvHalf * 128;    // one 64-column slab of 64 rows
+constexpr int kDkvHalfTileBytes = 2 * kDkvHalfChunkBytes;
+constexpr int kDkvStageBytes = 2 * kDkvHalfTileBytes; // Q half tile, dO half tile
+constexpr int kDkvSmemRing = 2 * kTileBytes;
+constexpr int kDkvSmemStats = kDkvSmemRing + kDkvStages * kDkvStageBytes;   // per stage: -lse2[64], -delta*scale[64]
+constexpr int kDkvStatsBytes = 2 * kDkvHalf * 4;
+constexpr int kDkvSmemBars = kDkvSmemStats + kDkvStages * kDkvStatsBytes;
+constexpr int kDkvBarOwnFull = 0, kDkvBarOwnEmpty = 1, kDkvBarRingFull = 2, kDkvBarRingEmpty = 6,
+              kDkvBarSFull = 10,    // [2] MMA -> compute: S^T in buffer b
+              kDkvBarDpFull = 12,   // [2] MMA -> compute: dP^T in buffer b
+              kDkvBarPFull = 14,    // compute -> MMA: P^T stored
+              kDkvBarDsFull = 15,   // compute -> MMA: dS^T stored
+              kDkvBarAccFull = 16, kDkvBarAccEmpty = 17,
+              kDkvBarBufFree = 18,  // [2] accumulating issuer -> pair issuer: buffer b's P^T and dS^T are consumed
+              kDkvNumBars = 20;
+constexpr int kDkvThreads = 352;     // 8 element-wise warps, pair issuer, loader, accumulating issuer
+constexpr int kAccWarp = 10;
+constexpr int kDkvSmemMisc = kDkvSmemBars + kDkvNumBars * 8;
+constexpr int kDkvSmemLaunch = kDkvSmemMisc + 16 + 1024;
+
 template <bool BF16, int HD>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kDkvThreads, 1)
 sdpa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                     const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
                     const BwdParams p) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-    auto bar = [&](int i) { return smem_base + kSmemBars + 8u * i; };
-    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + kSmemMisc);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + kSmemMisc + 4);
+    auto bar = [&](int i) { return smem_base + kDkvSmemBars + 8u * i; };
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + kDkvSmemMisc);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + kDkvSmemMisc + 4);
     constexpr int kChunks = HD / 64;
-    constexpr uint32_t kLoadBytes = kChunks * kChunkBytes;   // bytes one tile brings in
+    constexpr uint32_t kOwnBytes = kChunks * kChunkBytes;            // K_j or V_j
+    constexpr uint32_t kHalfBytes = kChunks * kDkvHalfChunkBytes;    // 64 rows of Q or dO
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int r = p.Hq / p.Hkv;
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < kNumBars; ++i) {
-            const bool eight = i == kBarPFull || i == kBarDsFull || i == kBarAccEmpty;
+        for (int i = 0; i < kDkvNumBars; ++i) {
+            const bool eight = i == kDkvBarPFull || i == kDkvBarDsFull || i == kDkvBarAccEmpty;
             mbar_init(bar(i), eight ? 8u : 1u);   // one arrival per compute warp / one commit or TMA
         }
         *abort_flag = 0;
@@ -198,7 +234,7 @@ sdpa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         fence_proxy_async_smem();
     }
     if (warp == kMmaWarp) {
-        tmem_alloc(smem_base + kSmemMisc, kTmemCols);
+        tmem_alloc(smem_base + kDkvSmemMisc, kTmemCols);
         tmem_relinquish();
     }
     if (warp == kLoadWarp && lane == 0) {
@@ -211,8 +247,11 @@ sdpa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = *tmem_slot;
+    // TMEM: S^T buffers @0, @64; dP^T buffers @128, @192; dV @256; dK @384
     constexpr int kColS = 0, kColDp = 128, kColDv = 256, kColDk = 384;
 
+    // Step x of an item: query head hh of the group, query tile i, half (0 / 1) of the tile.
+    // steps = 2 * (group size) * (query tiles that see the key tile)
     if (warp == kLoadWarp) {
         // ------------------------------ loads ------------------------------------------------
         bool ok = true;
@@ -221,133 +260,147 @@ sdpa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         for (int seq = 0; ok && get_item<true>(p, seq, &it); ++seq) {
             if (it.n <= 0) continue;
             if (lane == 0) {
-                ok = mbar_wait(bar(kBarOwnEmpty), (items & 1u) ^ 1u, abort_flag, 0);
+                ok = mbar_wait(bar(kDkvBarOwnEmpty), (items & 1u) ^ 1u, abort_flag, 0);
                 if (ok) {
-                    mbar_arrive_expect_tx(bar(kBarOwnFull), 2 * kLoadBytes);
+                    mbar_arrive_expect_tx(bar(kDkvBarOwnFull), 2 * kOwnBytes);
 #pragma unroll
                     for (int c = 0; c < kChunks; ++c) {
-                        tma_load_4d(smem_base + kSmemOwn + c * kChunkBytes, &map_k, bar(kBarOwnFull), 64 * c, it.t * BT, it.h, it.b);
-                        tma_load_4d(smem_base + kSmemOwn + kTileBytes + c * kChunkBytes, &map_v, bar(kBarOwnFull), 64 * c, it.t * BT, it.h, it.b);
+                        tma_load_4d(smem_base + kSmemOwn + c * kChunkBytes, &map_k, bar(kDkvBarOwnFull), 64 * c, it.t * BT, it.h, it.b);
+                        tma_load_4d(smem_base + kSmemOwn + kTileBytes + c * kChunkBytes, &map_v, bar(kDkvBarOwnFull), 64 * c, it.t * BT, it.h, it.b);
                     }
                 }
             }
             ++items;
-            const int i0 = first_query_tile(p, it.t), cnt = p.nq - i0;
-            for (int x = 0; x < it.n; ++x, ++rc) {
-                const int hh = x / cnt, i = i0 + (x - hh * cnt);
+            const int i0 = first_query_tile(p, it.t), cnt = 2 * (p.nq - i0);   // half tiles per query head
+            const int steps = 2 * it.n;
+            for (int x = 0; x < steps; ++x, ++rc) {
+                const int hh = x / cnt, hx = x - hh * cnt;
+                const int q_first = (i0 + (hx >> 1)) * BT + (hx & 1) * kDkvHalf;   // first query of the step
                 const int h = it.h * r + hh;
-                const int stage = rc & 1u;
-                if (lane == 0) ok = mbar_wait(bar(kBarRingEmpty + stage), ((rc >> 1) & 1u) ^ 1u, abort_flag, 1);
+                const int stage = rc % kDkvStages;
+                if (lane == 0)
+                    ok = mbar_wait(bar(kDkvBarRingEmpty + stage), ((rc / kDkvStages) & 1u) ^ 1u, abort_flag, 1);
                 ok = __shfl_sync(0xffffffffu, ok, 0);
                 if (!ok) break;
-                // per-query statistics of this tile, in the form the element-wise warps add them:
+                // per-query statistics of this step, in the form the element-wise warps add them:
                 // -lse in the base-2 domain (-inf past the last query: its probabilities are 0) and
                 // -delta * scale
-                float* st = reinterpret_cast<float*>(smem_gen + kSmemStats + stage * kStatsBytes);
+                float* st = reinterpret_cast<float*>(smem_gen + kDkvSmemStats + stage * kDkvStatsBytes);
                 const int64_t row0 = (int64_t(it.b) * p.Hq + h) * p.Lq;
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int q = i * BT + lane * 4 + e;
+                for (int e = 0; e < 2; ++e) {
+                    const int q = q_first + lane * 2 + e;
                     const bool live = q < p.Lq;
-                    st[lane * 4 + e] = live ? -p.lse[row0 + q] * 1.4426950408889634f : -INFINITY;
-                    st[BT + lane * 4 + e] = live ? -p.delta[row0 + q] * p.scale : 0.f;
+                    st[lane * 2 + e] = live ? -p.lse[row0 + q] * 1.4426950408889634f : -INFINITY;
+                    st[kDkvHalf + lane * 2 + e] = live ? -p.delta[row0 + q] * p.scale : 0.f;
                 }
                 __syncwarp();
                 if (lane == 0) {
-                    const uint32_t full = bar(kBarRingFull + stage);
-                    mbar_arrive_expect_tx(full, 2 * kLoadBytes);
-                    const uint32_t dst = smem_base + kSmemRing + stage * kStageBytes;
+                    const uint32_t full = bar(kDkvBarRingFull + stage);
+                    mbar_arrive_expect_tx(full, 2 * kHalfBytes);
+                    const uint32_t dst = smem_base + kDkvSmemRing + stage * kDkvStageBytes;
 #pragma unroll
                     for (int c = 0; c < kChunks; ++c) {
-                        tma_load_4d(dst + c * kChunkBytes, &map_q, full, 64 * c, i * BT, h, it.b);
-                        tma_load_4d(dst + kTileBytes + c * kChunkBytes, &map_do, full, 64 * c, i * BT, h, it.b);
+                        tma_load_4d(dst + c * kDkvHalfChunkBytes, &map_q, full, 64 * c, q_first, h, it.b);
+                        tma_load_4d(dst + kDkvHalfTileBytes + c * kDkvHalfChunkBytes, &map_do, full, 64 * c, q_first, h, it.b);
                     }
                 }
             }
         }
     } else if (warp == kMmaWarp) {
-        // ------------------------------ MMA issuer -------------------------------------------
+        // ------------------------------ MMA issuer: S^T, dP^T pairs ---------------------------
         if (lane == 0) {
-            constexpr uint32_t idesc_kk = instr_desc_f16(BF16 ? 1 : 0, BT, BT, false, false);
-            constexpr uint32_t idesc_acc = instr_desc_f16(BF16 ? 1 : 0, BT, HD, false, true);
-            const uint32_t own_k = smem_base + kSmemOwn, own_v = own_k + kTileBytes;
-            // Descriptors as 32-bit halves (tc_prims.cuh): the high word is shared by all operands
-            // (stride between 8-row groups = 1024 B), the low word of a tile is computed once per
-            // step and advanced by one add per MMA.
+            constexpr uint32_t idesc_t = instr_desc_f16(BF16 ? 1 : 0, BT, kDkvHalf, false, false);
             constexpr uint32_t hi = desc_hi_sw128(1024);
-            // D[128 keys x 128 queries] = own[keys x HD] * streamed[queries x HD]^T
+            const uint32_t own_k = smem_base + kSmemOwn, own_v = own_k + kTileBytes;
+            // D[128 keys x 64 queries] = own[keys x HD] * streamed[64 queries x HD]^T
             auto issue_t = [&](uint32_t d_col, uint32_t a_tile, uint32_t b_tile) {
                 const uint32_t a0 = desc_lo_sw128(a_tile, 16), b0 = desc_lo_sw128(b_tile, 16);
 #pragma unroll
                 for (int c = 0; c < kChunks; ++c)
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
-                        const uint32_t step = desc_step(c * kChunkBytes + i * 32);
-                        if (c | i) mma_ss_lo<true>(tmem + d_col, a0 + step, b0 + step, hi, idesc_kk);
-                        else mma_ss_lo<false>(tmem + d_col, a0 + step, b0 + step, hi, idesc_kk);
+                        const uint32_t sa = desc_step(c * kChunkBytes + i * 32);
+                        const uint32_t sb = desc_step(c * kDkvHalfChunkBytes + i * 32);
+                        if (c | i) mma_ss_lo<true>(tmem + d_col, a0 + sa, b0 + sb, hi, idesc_t);
+                        else mma_ss_lo<false>(tmem + d_col, a0 + sa, b0 + sb, hi, idesc_t);
                     }
             };
-            // D[128 keys x HD] (+)= A^T[keys x 128 queries] (16-bit, in TMEM) * streamed[queries x HD]
+            bool ok = true;
+            uint32_t items = 0, rc = 0;   // items, steps so far
+            Item it;
+            for (int seq = 0; ok && get_item<true>(p, seq, &it); ++seq) {
+                if (it.n <= 0) continue;
+                const int steps = 2 * it.n;
+                ok = mbar_wait(bar(kDkvBarOwnFull), items & 1u, abort_flag, 2);
+                if (!ok) break;
+                for (int x = 0; ok && x < steps; ++x) {
+                    // S^T and dP^T of step c into buffer c & 1, once step c-2's P^T and dS^T have been consumed
+                    const uint32_t c = rc + x, b = c & 1u;
+                    ok = mbar_wait(bar(kDkvBarRingFull + c % kDkvStages), (c / kDkvStages) & 1u, abort_flag, 3);
+                    if (!ok) break;
+                    ok = mbar_wait(bar(kDkvBarBufFree + b), ((c >> 1) & 1u) ^ 1u, abort_flag, 7);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    const uint32_t ring = smem_base + kDkvSmemRing + (c % kDkvStages) * kDkvStageBytes;
+                    issue_t(kColS + 64 * b, own_k, ring);
+                    tc_commit(bar(kDkvBarSFull + b));
+                    issue_t(kColDp + 64 * b, own_v, ring + kDkvHalfTileBytes);
+                    tc_commit(bar(kDkvBarDpFull + b));
+                }
+                if (!ok) break;
+                rc += steps;
+                tc_commit(bar(kDkvBarOwnEmpty));
+                ++items;
+            }
+        }
+        __syncwarp();
+    } else if (warp == kAccWarp) {
+        // ------------------------------ MMA issuer: dV, dK -----------------------------------
+        if (lane == 0) {
+            constexpr uint32_t idesc_acc = instr_desc_f16(BF16 ? 1 : 0, BT, HD, false, true);
+            constexpr uint32_t hi = desc_hi_sw128(1024);
+            // D[128 keys x HD] (+)= A^T[keys x 64 queries] (16-bit, in TMEM) * streamed[64 queries x HD]
             auto issue_acc = [&](uint32_t d_col, uint32_t a_col, uint32_t b_tile, bool acc) {
-                const uint32_t b0 = desc_lo_sw128(b_tile, kChunkBytes);
+                const uint32_t b0 = desc_lo_sw128(b_tile, kDkvHalfChunkBytes);
 #pragma unroll
-                for (int ks = 0; ks < BT / 16; ++ks) {
-                    // queries 0-63 sit in packed columns 0-31, queries 64-127 in columns 64-95: each
+                for (int ks = 0; ks < kDkvHalf / 16; ++ks) {
+                    // queries 0-31 sit in packed columns 0-15, queries 32-63 in columns 32-47: each
                     // half overlays the fp32 columns the warps that wrote it had read themselves
-                    const uint32_t a = tmem + a_col + (ks < 4 ? ks * 8 : 64 + (ks - 4) * 8);
+                    const uint32_t a = tmem + a_col + (ks < 2 ? ks * 8 : 32 + (ks - 2) * 8);
                     const uint32_t b = b0 + desc_step(ks * 16 * 128);
                     if (ks) mma_ts_lo<true>(tmem + d_col, a, b, hi, idesc_acc);
                     else mma_ts_lo(tmem + d_col, a, b, hi, idesc_acc, acc ? 1u : 0u);
                 }
             };
             bool ok = true;
-            uint32_t items = 0, rc = 0, pc = 0, dc = 0;   // items, ring stages used, P and dS hand-overs
+            uint32_t items = 0, rc = 0;
             Item it;
             for (int seq = 0; ok && get_item<true>(p, seq, &it); ++seq) {
                 if (it.n <= 0) continue;
-                ok = mbar_wait(bar(kBarOwnFull), items & 1u, abort_flag, 2);
-                if (!ok) break;
-                auto ring_tile = [&](uint32_t c) { return smem_base + kSmemRing + (c & 1u) * kStageBytes; };
-                ok = mbar_wait(bar(kBarRingFull + (rc & 1u)), (rc >> 1) & 1u, abort_flag, 3);
-                if (!ok) break;
-                tc_fence_after_sync();
-                issue_t(kColS, own_k, ring_tile(rc));
-                tc_commit(bar(kBarSFull));
-                issue_t(kColDp, own_v, ring_tile(rc) + kTileBytes);
-                tc_commit(bar(kBarDpFull));
-                for (int x = 0; ok && x < it.n; ++x) {
-                    const uint32_t cur = rc + x;
-                    ok = mbar_wait(bar(kBarPFull), pc & 1u, abort_flag, 4);
+                const int steps = 2 * it.n;
+                for (int x = 0; ok && x < steps; ++x) {
+                    const uint32_t cur = rc + x, b = cur & 1u;
+                    const uint32_t ring = smem_base + kDkvSmemRing + (cur % kDkvStages) * kDkvStageBytes;
+                    ok = mbar_wait(bar(kDkvBarPFull), cur & 1u, abort_flag, 4);
                     if (!ok) break;
-                    ++pc;
                     if (x == 0 && items > 0) {   // the previous item's dK / dV have been read out
-                        ok = mbar_wait(bar(kBarAccEmpty), (items - 1) & 1u, abort_flag, 5);
+                        ok = mbar_wait(bar(kDkvBarAccEmpty), (items - 1) & 1u, abort_flag, 5);
                         if (!ok) break;
                     }
                     tc_fence_after_sync();
-                    issue_acc(kColDv, kColS, ring_tile(cur) + kTileBytes, x > 0);   // dV += P^T dO
-                    if (x + 1 < it.n) {
-                        ok = mbar_wait(bar(kBarRingFull + ((cur + 1) & 1u)), ((cur + 1) >> 1) & 1u, abort_flag, 3);
-                        if (!ok) break;
-                        tc_fence_after_sync();
-                        issue_t(kColS, own_k, ring_tile(cur + 1));                   // next S^T over P^T
-                        tc_commit(bar(kBarSFull));
-                    }
-                    ok = mbar_wait(bar(kBarDsFull), dc & 1u, abort_flag, 6);
+                    issue_acc(kColDv, kColS + 64 * b, ring + kDkvHalfTileBytes, x > 0);   // dV += P^T dO
+                    ok = mbar_wait(bar(kDkvBarDsFull), cur & 1u, abort_flag, 6);
                     if (!ok) break;
-                    ++dc;
                     tc_fence_after_sync();
-                    issue_acc(kColDk, kColDp, ring_tile(cur), x > 0);               // dK += dS^T Q
-                    tc_commit(bar(kBarRingEmpty + (cur & 1u)));
-                    if (x + 1 < it.n) {
-                        issue_t(kColDp, own_v, ring_tile(cur + 1) + kTileBytes);     // next dP^T over dS^T
-                        tc_commit(bar(kBarDpFull));
-                    }
+                    issue_acc(kColDk, kColDp + 64 * b, ring, x > 0);                       // dK += dS^T Q
+                    // (the pair issuer's reads of this stage finished before P^T could be formed)
+                    tc_commit(bar(kDkvBarRingEmpty + cur % kDkvStages));
+                    tc_commit(bar(kDkvBarBufFree + b));
                 }
                 if (!ok) break;
-                rc += it.n;
-                tc_commit(bar(kBarAccFull));
-                tc_commit(bar(kBarOwnEmpty));
+                rc += steps;
+                tc_commit(bar(kDkvBarAccFull));
                 ++items;
             }
         }
@@ -356,9 +409,7 @@ sdpa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         // ------------------------------ element-wise warps -----------------------------------
         const int wg = warp >> 2, wq = warp & 3;
         const uint32_t lane_base = uint32_t(wq * 32) << 16;
-        const int col0 = wg * 64;                        // this warp's query columns of the tile
-        const uint32_t s_addr = tmem + lane_base + kColS + col0;
-        const uint32_t dp_addr = tmem + lane_base + kColDp + col0;
+        const int col0 = wg * 32;                        // this warp's query columns of the 64
         const float c2 = p.scale_log2;
         bool ok = true;
         uint32_t items = 0, rc = 0;
@@ -375,33 +426,35 @@ sdpa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                     for (int v = 0; v < HD / 8; ++v) reinterpret_cast<uint4*>(out)[v] = make_uint4(0, 0, 0, 0);
                 continue;
             }
-            const int i0 = first_query_tile(p, it.t), cnt = p.nq - i0;
-            for (int x = 0; x < it.n; ++x, ++rc) {
-                const int i = i0 + x % cnt;
-                const int stage = rc & 1u;
+            const int i0 = first_query_tile(p, it.t), cnt = 2 * (p.nq - i0);
+            const int steps = 2 * it.n;
+            for (int x = 0; x < steps; ++x, ++rc) {
+                const int hx = x % cnt;
+                const int q0 = (i0 + (hx >> 1)) * BT + (hx & 1) * kDkvHalf + col0;   // first query of this warp's columns
+                const int stage = rc % kDkvStages;
+                const uint32_t b = rc & 1u;
+                const uint32_t s_addr = tmem + lane_base + kColS + 64 * b + col0;
+                const uint32_t dp_addr = tmem + lane_base + kColDp + 64 * b + col0;
                 // (the statistics were written by the load warp before it armed this barrier)
-                ok = mbar_wait(bar(kBarRingFull + stage), (rc >> 1) & 1u, abort_flag, 10);
+                ok = mbar_wait(bar(kDkvBarRingFull + stage), (rc / kDkvStages) & 1u, abort_flag, 10);
                 if (!ok) break;
-                const float4* st_lse = reinterpret_cast<const float4*>(smem_gen + kSmemStats + stage * kStatsBytes) + col0 / 4;
-                const float4* st_del = st_lse + BT / 4;
-                ok = mbar_wait(bar(kBarSFull), rc & 1u, abort_flag, 11);
+                const float4* st_lse = reinterpret_cast<const float4*>(smem_gen + kDkvSmemStats + stage * kDkvStatsBytes) + col0 / 4;
+                const float4* st_del = st_lse + kDkvHalf / 4;
+                ok = mbar_wait(bar(kDkvBarSFull + b), (rc >> 1) & 1u, abort_flag, 11);
                 if (!ok) break;
                 tc_fence_after_sync();
-                uint32_t s[64];
-                tmem_ld32(s_addr, reinterpret_cast<uint32_t(&)[32]>(s[0]));
-                tmem_ld32(s_addr + 32, reinterpret_cast<uint32_t(&)[32]>(s[32]));
+                uint32_t s[32];
+                tmem_ld32(s_addr, s);
                 tmem_wait_ld();
-                tmem_ld_fence32(reinterpret_cast<uint32_t(&)[32]>(s[0]));
-                tmem_ld_fence32(reinterpret_cast<uint32_t(&)[32]>(s[32]));
+                tmem_ld_fence32(s);
                 // P^T[key, q] = exp2(S * c - lse2[q]); zero where the query does not see the key.
                 // Two columns per instruction on the FMA pipe (fp32x2).
-                const int q0 = i * BT + col0;
-                const bool diag = p.causal && q0 < it.t * BT + BT;   // some query of these columns precedes some key
+                const bool diag = p.causal && q0 < it.t * BT + BT;      // some query of these columns precedes some key
                 const bool need_mask = diag || it.t * BT + BT > p.Lk;   // the same for the whole warp
                 const float2 c22 = make_float2(c2, c2);
-                uint32_t pk[32];
+                uint32_t pk[16];
 #pragma unroll
-                for (int v = 0; v < 16; ++v) {
+                for (int v = 0; v < 8; ++v) {
                     const float4 l4 = st_lse[v];
                     const float2 e0 = ffma2(make_float2(__uint_as_float(s[4 * v]), __uint_as_float(s[4 * v + 1])), c22, make_float2(l4.x, l4.y));
                     const float2 e1 = ffma2(make_float2(__uint_as_float(s[4 * v + 2]), __uint_as_float(s[4 * v + 3])), c22, make_float2(l4.z, l4.w));
@@ -417,25 +470,22 @@ sdpa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                     pk[2 * v + 1] = pack16<BF16>(pv[2], pv[3]);
                 }
                 // 16-bit P^T over the first half of the fp32 columns this warp has just read
-                tmem_st16(s_addr, reinterpret_cast<uint32_t(&)[16]>(pk[0]));
-                tmem_st16(s_addr + 16, reinterpret_cast<uint32_t(&)[16]>(pk[16]));
+                tmem_st16(s_addr, pk);
                 tmem_wait_st();
                 tc_fence_before_sync();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(bar(kBarPFull));
+                if (lane == 0) mbar_arrive(bar(kDkvBarPFull));
                 // dS^T = P^T o (dP^T - delta[q]) * scale, with the unrounded P
-                ok = mbar_wait(bar(kBarDpFull), rc & 1u, abort_flag, 12);
+                ok = mbar_wait(bar(kDkvBarDpFull + b), (rc >> 1) & 1u, abort_flag, 12);
                 if (!ok) break;
                 tc_fence_after_sync();
-                uint32_t dp[64];
-                tmem_ld32(dp_addr, reinterpret_cast<uint32_t(&)[32]>(dp[0]));
-                tmem_ld32(dp_addr + 32, reinterpret_cast<uint32_t(&)[32]>(dp[32]));
+                uint32_t dp[32];
+                tmem_ld32(dp_addr, dp);
                 tmem_wait_ld();
-                tmem_ld_fence32(reinterpret_cast<uint32_t(&)[32]>(dp[0]));
-                tmem_ld_fence32(reinterpret_cast<uint32_t(&)[32]>(dp[32]));
+                tmem_ld_fence32(dp);
                 const float2 sc2 = make_float2(p.scale, p.scale);
 #pragma unroll
-                for (int v = 0; v < 16; ++v) {
+                for (int v = 0; v < 8; ++v) {
                     const float4 d4 = st_del[v];   // -delta * scale
                     const float2 t0 = ffma2(make_float2(__uint_as_float(dp[4 * v]), __uint_as_float(dp[4 * v + 1])), sc2, make_float2(d4.x, d4.y));
                     const float2 t1 = ffma2(make_float2(__uint_as_float(dp[4 * v + 2]), __uint_as_float(dp[4 * v + 3])), sc2, make_float2(d4.z, d4.w));
@@ -444,16 +494,15 @@ sdpa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                     pk[2 * v] = pack16<BF16>(d0.x, d0.y);
                     pk[2 * v + 1] = pack16<BF16>(d1.x, d1.y);
                 }
-                tmem_st16(dp_addr, reinterpret_cast<uint32_t(&)[16]>(pk[0]));
-                tmem_st16(dp_addr + 16, reinterpret_cast<uint32_t(&)[16]>(pk[16]));
+                tmem_st16(dp_addr, pk);
                 tmem_wait_st();
                 tc_fence_before_sync();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(bar(kBarDsFull));
+                if (lane == 0) mbar_arrive(bar(kDkvBarDsFull));
             }
             if (!ok) break;
             // read the item's accumulator out: warps 0-3 dV, warps 4-7 dK (one key row per lane)
-            ok = mbar_wait(bar(kBarAccFull), items & 1u, abort_flag, 13);
+            ok = mbar_wait(bar(kDkvBarAccFull), items & 1u, abort_flag, 13);
             if (!ok) break;
             ++items;
             tc_fence_after_sync();
@@ -468,7 +517,7 @@ sdpa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             }
             tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar(kBarAccEmpty));
+            if (lane == 0) mbar_arrive(bar(kDkvBarAccEmpty));
         }
     }
 
@@ -754,7 +803,7 @@ bool sdpa_bwd_tc_supported(const Gpu* g, const paras_sdpa_bwd_args& a) {
     if (a.D != 128 && a.D != 64) return false;
     if (a.Lq < 1 || a.Lk < 1 || a.Hkv < 1 || a.Hq % a.Hkv) return false;
     if (!(a.scale > 0.0) || !std::isfinite(a.scale)) return false;
-    if (g->smem_optin < size_t(kSmemLaunch) || g->smem_optin < size_t(kDqSmemLaunch)) return false;
+    if (g->smem_optin < size_t(kDkvSmemLaunch) || g->smem_optin < size_t(kDqSmemLaunch)) return false;
     return true;
 }
 
@@ -769,6 +818,10 @@ int sdpa_bwd_tc_launch(Gpu* g, const paras_sdpa_bwd_args& a, const float* delta,
     if ((st = make_tensor_map_bhld(&mk, a.k, a.dtype, a.B, a.Hkv, a.Lk, a.D, sk, BT)) != PARAS_OK) return st;
     if ((st = make_tensor_map_bhld(&mv, a.v, a.dtype, a.B, a.Hkv, a.Lk, a.D, sk, BT)) != PARAS_OK) return st;
     if ((st = make_tensor_map_bhld(&mdo, a.dout, a.dtype, a.B, a.Hq, a.Lq, a.D, sq, BT)) != PARAS_OK) return st;
+    // the dK/dV kernel streams queries 64 rows at a time
+    CUtensorMap mq64, mdo64;
+    if ((st = make_tensor_map_bhld(&mq64, a.q, a.dtype, a.B, a.Hq, a.Lq, a.D, sq, kDkvHalf)) != PARAS_OK) return st;
+    if ((st = make_tensor_map_bhld(&mdo64, a.dout, a.dtype, a.B, a.Hq, a.Lq, a.D, sq, kDkvHalf)) != PARAS_OK) return st;
     BwdParams p{};
     p.dq = a.dq; p.dk = a.dk; p.dv = a.dv;
     p.lse = a.lse; p.delta = delta;
@@ -781,21 +834,27 @@ int sdpa_bwd_tc_launch(Gpu* g, const paras_sdpa_bwd_args& a, const float* delta,
     p.nk = (a.Lk + BT - 1) / BT;
     const int sms = g->sm_count > 0 ? g->sm_count : 148;
     const bool bf = a.dtype == PARAS_BF16;
+    const CUtensorMap* use_q = &mq64;
+    const CUtensorMap* use_do = &mdo64;
+    int threads = kDkvThreads;
     auto launch = [&](auto kernel, int64_t units, int smem) -> int {
         if (units > INT32_MAX) return fail(PARAS_E_UNSUPPORTED, "paras sdpa backward: too many work units");
         p.units = int(units);
         PB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        kernel<<<unsigned(units < sms ? units : sms), kThreads, smem, s>>>(mq, mk, mv, mdo, p);
+        kernel<<<unsigned(units < sms ? units : sms), threads, smem, s>>>(*use_q, mk, mv, *use_do, p);
         return PARAS_OK;
     };
     // dK, dV: units of paired key tiles per (batch, kv head)
     p.npair = (p.nk + 1) / 2;
     const int64_t u_kv = int64_t(a.B) * a.Hkv * p.npair;
-    if (a.D == 128) st = bf ? launch(sdpa_bwd_dkv_kernel<true, 128>, u_kv, kSmemLaunch) : launch(sdpa_bwd_dkv_kernel<false, 128>, u_kv, kSmemLaunch);
-    else st = bf ? launch(sdpa_bwd_dkv_kernel<true, 64>, u_kv, kSmemLaunch) : launch(sdpa_bwd_dkv_kernel<false, 64>, u_kv, kSmemLaunch);
+    if (a.D == 128) st = bf ? launch(sdpa_bwd_dkv_kernel<true, 128>, u_kv, kDkvSmemLaunch) : launch(sdpa_bwd_dkv_kernel<false, 128>, u_kv, kDkvSmemLaunch);
+    else st = bf ? launch(sdpa_bwd_dkv_kernel<true, 64>, u_kv, kDkvSmemLaunch) : launch(sdpa_bwd_dkv_kernel<false, 64>, u_kv, kDkvSmemLaunch);
     if (st != PARAS_OK) return st;
     PB_LAUNCH_CHECK("sdpa_bwd_dkv_kernel");
-    // dQ: units of paired query tiles per (batch, query head)
+    // dQ: units of paired query tiles per (batch, query head); whole 128-row tiles of q and dO
+    use_q = &mq;
+    use_do = &mdo;
+    threads = kThreads;
     p.npair = (p.nq + 1) / 2;
     const int64_t u_q = int64_t(a.B) * a.Hq * p.npair;
     if (a.D == 128) st = bf ? launch(sdpa_bwd_dq_kernel<true, 128>, u_q, kDqSmemLaunch) : launch(sdpa_bwd_dq_kernel<false, 128>, u_q, kDqSmemLaunch);
