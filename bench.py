@@ -429,6 +429,30 @@ def run_ours(args):
                                                  "kernel": abi.sdpa_last_kernel()}
         del q3, k3, v3, o3
 
+    if want("variants"):
+        # the other instantiations of the tcgen05 kernel at config 2's batch and sequence: head dim 64
+        # (half the tensor work per exponential) and explicit masks (bool key padding [B,1,1,S];
+        # additive [S,S] in the tensors' dtype, a row of which every softmax thread reads per kv tile)
+        res = {}
+        qv, kv_, vv = gen((8, 32, 2048, 128), 40), gen((8, 32, 2048, 128), 41), gen((8, 32, 2048, 128), 42)
+        ov = torch.empty_like(qv)
+        pad = torch.ones(8, 1, 1, 2048, dtype=torch.bool, device=dev)
+        pad[:, :, :, 1900:] = False
+        add = (0.5 * torch.randn(2048, 2048, device=dev, generator=torch.Generator(device=dev).manual_seed(43))).to(qv.dtype)
+        for key, kw in (("full_nomask", {}), ("bool_padding_mask_B11S", {"mask": pad}), ("additive_mask_SS", {"mask": add})):
+            t = loop_ms(lambda: abi.sdpa_fwd(qv, kv_, vv, out=ov, **kw), esteps)
+            tf = sdpa_flops(8, 32, 2048, 2048, 128, False) / (t * 1e-3) / 1e12
+            res[key] = {"ms": t, "tflops": tf, "frac_of_bf16_peak": tf / peaks["bf16_tflops"], "kernel": abi.sdpa_last_kernel()}
+        del qv, kv_, vv, ov
+        q6, k6, v6 = gen((8, 32, 2048, 64), 44), gen((8, 32, 2048, 64), 45), gen((8, 32, 2048, 64), 46)
+        o6 = torch.empty_like(q6)
+        for key, causal in (("d64_causal", True), ("d64_full", False)):
+            t = loop_ms(lambda: abi.sdpa_fwd(q6, k6, v6, causal=causal, out=o6), esteps)
+            tf = sdpa_flops(8, 32, 2048, 2048, 64, causal) / (t * 1e-3) / 1e12
+            res[key] = {"ms": t, "tflops": tf, "frac_of_bf16_peak": tf / peaks["bf16_tflops"], "kernel": abi.sdpa_last_kernel()}
+        del q6, k6, v6, o6
+        extra["sdpa_variants_B8_H32_S2048"] = res
+
     if want("decode"):
         # config 4 decode: bytes = K + V (once per kv head) + q + o
         db = 8 if args.small else 64
@@ -682,7 +706,7 @@ def main():
                     help="seconds of back-to-back headline launches for the sustained figure (0 = skip)")
     ap.add_argument("--ingest-ncu", metavar="CSV",
                     help="write profiles/sdpa_tc_kernel_config2_dram_traffic.txt from `ncu --page raw --csv` output and exit")
-    ap.add_argument("--only", choices=["rope", "config1", "rmsnorm", "swiglu", "gqa", "decode", "block", "gemm", "bwd"],
+    ap.add_argument("--only", choices=["rope", "config1", "rmsnorm", "swiglu", "gqa", "variants", "decode", "block", "gemm", "bwd"],
                     help="after the headline loop run just this extra workload and print it (for profiling)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-numa-bind", action="store_true",

@@ -410,11 +410,112 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             // entries per kv tile.  Bool: false -> -inf.  Additive: S is still unscaled here, so the
             // mask value joins it divided by the scale.  Rows past the end reuse the last row.
             const char* mrow = nullptr;
+            // Staged reading of a mask whose rows are contiguous along the keys.  A lane owns a query
+            // row, so reading its own row touches 32 rows (cache lines) per instruction and the
+            // lines do not survive in L1 until the lane comes back for their other 16-byte pieces.
+            // Instead the warp reads its 32 rows 128 contiguous bytes at a time (8 lanes per row,
+            // 4 rows per instruction), passes them through its 4 KB staging buffer (the one the O
+            // store uses at the end of the item) and each lane picks its own row up from there.
+            // A "round" is 128 bytes of every row: 128 / 64 / 32 keys for 1 / 2 / 4-byte masks.
+            const char* mask_bh = nullptr;
+            int64_t mpitch = 0;
+            int mesz = 1;
+            bool mfast = false;
             if (MASK) {
-                const int esz = p.mask_kind == 1 ? 1 : (p.mask_kind == 2 ? 2 : 4);
-                mrow = static_cast<const char*>(p.mask) +
-                       (int64_t(it.b) * p.ms[0] + int64_t(it.h) * p.ms[1] + int64_t(min(row_q, p.Lq - 1)) * p.ms[2]) * esz;
+                mesz = p.mask_kind == 1 ? 1 : (p.mask_kind == 2 ? 2 : 4);
+                mask_bh = static_cast<const char*>(p.mask) + (int64_t(it.b) * p.ms[0] + int64_t(it.h) * p.ms[1]) * mesz;
+                mpitch = p.ms[2] * mesz;
+                mrow = mask_bh + int64_t(min(row_q, p.Lq - 1)) * mpitch;
+                // (a row shared by every query, pitch 0, is one line per instruction as it is)
+                mfast = p.ms[3] == 1 && mpitch != 0 && (mpitch & 15) == 0 && (reinterpret_cast<uintptr_t>(mask_bh) & 15u) == 0;
+                if (mfast) {
+                    if (lane == 0) tma_store_wait_read();   // the previous item's O store has read the buffer
+                    __syncwarp();
+                }
             }
+            const int mu = lane & 7, mrs = lane >> 3;
+            auto mask_ldg = [&](int col0, int r, uint4 (&w)[8]) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const int grow = min(it.start[t] + wq * 32 + 4 * i + mrs, p.Lq - 1);
+                    w[i] = __ldg(reinterpret_cast<const uint4*>(mask_bh + int64_t(grow) * mpitch + int64_t(col0) * mesz + r * 128) + mu);
+                }
+            };
+            auto mask_sts = [&](const uint4 (&w)[8]) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const int row = 4 * i + mrs;
+                    st_shared_v4(o_stage + row * 128 + uint32_t((mu ^ (row & 7)) << 4), w[i]);
+                }
+            };
+            auto mask_lds = [&](int v) {
+                uint4 x;
+                const uint32_t addr = o_stage + lane * 128 + uint32_t((v ^ (lane & 7)) << 4);
+                asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(x.x), "=r"(x.y), "=r"(x.z), "=r"(x.w) : "r"(addr));
+                return x;
+            };
+            // round r of the staged mask (already in the staging buffer) joins this lane's scores
+            auto mask_apply_round = [&](uint32_t (&s)[BN], int r) {
+                if (p.mask_kind == 1) {
+#pragma unroll
+                    for (int v = 0; v < 8; ++v) {
+                        const uint4 w = mask_lds(v);
+                        const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+                        for (int e = 0; e < 16; ++e)
+                            if (((ww[e >> 2] >> (8 * (e & 3))) & 0xffu) == 0) s[16 * v + e] = 0xff800000u;
+                    }
+                } else if (p.mask_kind == 2) {
+#pragma unroll
+                    for (int rr = 0; rr < 2; ++rr) {
+                        if (rr != r) continue;
+#pragma unroll
+                        for (int v = 0; v < 8; ++v) {
+                            const uint4 w = mask_lds(v);
+                            const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {   // two keys per packed FMA
+                                const int i0 = 64 * rr + 8 * v + 2 * e;
+                                const float2 r2 = ffma2(pair16_to_f32<BF16>(ww[e]), make_float2(p.inv_scale, p.inv_scale),
+                                                        make_float2(__uint_as_float(s[i0]), __uint_as_float(s[i0 + 1])));
+                                s[i0] = __float_as_uint(r2.x);
+                                s[i0 + 1] = __float_as_uint(r2.y);
+                            }
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int rr = 0; rr < 4; ++rr) {
+                        if (rr != r) continue;
+#pragma unroll
+                        for (int v = 0; v < 8; ++v) {
+                            const uint4 w = mask_lds(v);
+                            const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+                            for (int e = 0; e < 2; ++e) {
+                                const int i0 = 32 * rr + 4 * v + 2 * e;
+                                const float2 r2 = ffma2(make_float2(__uint_as_float(ww[2 * e]), __uint_as_float(ww[2 * e + 1])),
+                                                        make_float2(p.inv_scale, p.inv_scale),
+                                                        make_float2(__uint_as_float(s[i0]), __uint_as_float(s[i0 + 1])));
+                                s[i0] = __float_as_uint(r2.x);
+                                s[i0 + 1] = __float_as_uint(r2.y);
+                            }
+                        }
+                    }
+                }
+            };
+            // the rounds after the first: `w` holds round 1, fetched before the wait for S
+            auto mask_apply_staged = [&](uint32_t (&s)[BN], int col0, uint4 (&w)[8]) {
+                mask_apply_round(s, 0);
+                for (int r = 1; r < mesz; ++r) {
+                    __syncwarp();                       // every lane has read round r-1
+                    mask_sts(w);
+                    if (r + 1 < mesz) mask_ldg(col0, r + 1, w);
+                    __syncwarp();
+                    mask_apply_round(s, r);
+                }
+                __syncwarp();
+            };
             auto apply_mask = [&](uint32_t (&s)[BN], int col0) {
                 const int ncols = min(BN, p.Lk - col0);
                 const bool vec = p.ms[3] == 1 && ncols == BN;
@@ -442,9 +543,12 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                             const uint4 w = __ldg(reinterpret_cast<const uint4*>(mp) + v);
                             const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
-                            for (int e = 0; e < 8; ++e) {
-                                const float a = from16<BF16>(uint16_t((ww[e >> 1] >> (16 * (e & 1))) & 0xffffu));
-                                s[8 * v + e] = __float_as_uint(fmaf(a, p.inv_scale, __uint_as_float(s[8 * v + e])));
+                            for (int e = 0; e < 4; ++e) {   // two keys per packed FMA
+                                const int i0 = 8 * v + 2 * e;
+                                const float2 r2 = ffma2(pair16_to_f32<BF16>(ww[e]), make_float2(p.inv_scale, p.inv_scale),
+                                                        make_float2(__uint_as_float(s[i0]), __uint_as_float(s[i0 + 1])));
+                                s[i0] = __float_as_uint(r2.x);
+                                s[i0 + 1] = __float_as_uint(r2.y);
                             }
                         }
                     } else {
@@ -476,6 +580,20 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             float m = -INFINITY, m_next = -INFINITY, l = 0.f;
             bool move_ref = false;
             for (int j = 0; j < nt; ++j) {
+                uint4 mw[8];
+                bool staged = false;
+                if (MASK) {
+                    // these warps are idle until S arrives: round 0 of this step's mask goes to the staging
+                    // buffer now, round 1 stays in flight across the wait
+                    staged = mfast && (j + 1) * BN <= p.Lk;
+                    if (staged) {
+                        uint4 w0[8];
+                        mask_ldg(j * BN, 0, w0);
+                        if (mesz > 1) mask_ldg(j * BN, 1, mw);
+                        mask_sts(w0);
+                        __syncwarp();
+                    }
+                }
                 ok = mbar_wait(bar(kBarSFull + t), scnt & 1u, abort_flag, 10 + t);
                 if (!ok) break;
                 ++scnt;
@@ -529,7 +647,10 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                         for (int i = 0; i < BN; ++i)
                             if (i > limit) s[i] = 0xff800000u;  // -inf
                     }
-                    if (MASK) apply_mask(s, col0);
+                    if (MASK) {
+                        if (staged && attempt == 0) mask_apply_staged(s, col0, mw);
+                        else apply_mask(s, col0);
+                    }
                     if (j == 0 || attempt == 1) {
                         float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll

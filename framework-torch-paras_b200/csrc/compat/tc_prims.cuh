@@ -415,6 +415,15 @@ __device__ __forceinline__ float from16(uint16_t bits) {
         return r;
     }
 }
+// A packed pair of 16-bit values -> (low, high) as fp32.
+template <bool BF16>
+__device__ __forceinline__ float2 pair16_to_f32(uint32_t w) {
+    if constexpr (BF16) {
+        return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+    } else {
+        return __half22float2(*reinterpret_cast<const __half2*>(&w));
+    }
+}
 template <bool BF16>
 __device__ __forceinline__ float round16(float x) {
     return from16<BF16>(uint16_t(pack16<BF16>(x, 0.f) & 0xffffu));
