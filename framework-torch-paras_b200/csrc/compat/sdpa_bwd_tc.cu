@@ -84,7 +84,7 @@ constexpr int kDqSmemV = kDqSmemK + kDqKStages * kTileBytes;
 constexpr int kDqSmemBars = kDqSmemV + kDqVStages * kTileBytes;
 constexpr int kDqBarOwnFull = 0, kDqBarOwnEmpty = 1, kDqBarKFull = 2, kDqBarKEmpty = 5, kDqBarVFull = 8,
               kDqBarVEmpty = 10, kDqBarSFull = 12, kDqBarDpFull = 13, kDqBarTaken = 14, kDqBarDsFull = 15,
-              kDqBarAccFull = 16, kDqBarAccEmpty = 17, kDqNumBars = 18;
+              kDqBarAccFull = 16, kDqBarAccEmpty = 17, kDqBarDsFree = 18 /* [2] */, kDqNumBars = 20;
 constexpr int kDqSmemMisc = kDqSmemBars + kDqNumBars * 8;
 constexpr int kDqSmemLaunch = kDqSmemMisc + 16 + 1024;
 
@@ -538,7 +538,7 @@ sdpa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 // dQ: own pair = (Q_i, dO_i), streamed pair = (K_j, V_j).
 // ---------------------------------------------------------------------------------------------
 template <bool BF16, int HD>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kDkvThreads, 1)
 sdpa_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                    const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
                    const BwdParams p) {
@@ -634,7 +634,7 @@ sdpa_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                     }
             };
             bool ok = true;
-            uint32_t items = 0, rc = 0, pc = 0, dc = 0;
+            uint32_t items = 0, rc = 0, pc = 0;
             Item it;
             for (int seq = 0; ok && get_item<false>(p, seq, &it); ++seq) {
                 if (it.n <= 0) continue;
@@ -657,43 +657,64 @@ sdpa_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 if (!ok) break;
                 ok = issue_s_dp(rc);
                 for (int x = 0; ok && x < it.n; ++x) {
-                    const uint32_t cur = rc + x;
                     // the element-wise warps hold S and dP of this step in registers: the next
-                    // step's products may overwrite them while this step's dS is being formed
+                    // step's products (or the next item's first) may overwrite them while this
+                    // step's dS is being formed
                     ok = mbar_wait(bar(kDqBarTaken), pc & 1u, abort_flag, 4);
                     if (!ok) break;
                     ++pc;
-                    if (x + 1 < it.n) {
-                        ok = issue_s_dp(cur + 1);
-                        if (!ok) break;
-                    }
-                    ok = mbar_wait(bar(kDqBarDsFull), dc & 1u, abort_flag, 6);
+                    if (x + 1 < it.n) ok = issue_s_dp(rc + x + 1);
+                }
+                if (!ok) break;
+                rc += it.n;
+                tc_commit(bar(kDqBarOwnEmpty));   // every S / dP product of the item has read Q_i, dO_i
+                ++items;
+            }
+        }
+        __syncwarp();
+    } else if (warp == kAccWarp) {
+        // ------------------------------ second MMA issuer: dQ += dS K_j ------------------------
+        // A thread of its own, so that its waits (dS formed, K landed) run while the first issuer is
+        // blocked issuing S and dP of the next step, and the other way round.
+        if (lane == 0) {
+            constexpr uint32_t idesc_acc = instr_desc_f16(BF16 ? 1 : 0, BT, HD, false, true);
+            constexpr uint32_t hi = desc_hi_sw128(1024);
+            bool ok = true;
+            uint32_t items = 0, rc = 0;
+            Item it;
+            for (int seq = 0; ok && get_item<false>(p, seq, &it); ++seq) {
+                if (it.n <= 0) continue;
+                for (int x = 0; ok && x < it.n; ++x) {
+                    const uint32_t cur = rc + x;
+                    ok = mbar_wait(bar(kDqBarDsFull), cur & 1u, abort_flag, 6);
                     if (!ok) break;
-                    ++dc;
                     if (x == 0 && items > 0) {   // the previous item's dQ has been read out
                         ok = mbar_wait(bar(kDqBarAccEmpty), (items - 1) & 1u, abort_flag, 5);
                         if (!ok) break;
                     }
+                    // K_j landed (the first issuer saw that before S; this thread reads the tile too)
+                    ok = mbar_wait(bar(kDqBarKFull + cur % kDqKStages), (cur / kDqKStages) & 1u, abort_flag, 9);
+                    if (!ok) break;
                     tc_fence_after_sync();
-                    // dQ += dS K_j: dS (16-bit) from TMEM, K_j as [keys x HD] rows
+                    // dS (16-bit) from TMEM, K_j as [keys x HD] rows
                     const uint32_t ds_col = kColDs + (cur & 1u) * 64;
-                    const uint32_t k0 = desc_lo_sw128(k_tile(cur), kChunkBytes);
+                    const uint32_t k0 = desc_lo_sw128(smem_base + kDqSmemK + (cur % kDqKStages) * kTileBytes, kChunkBytes);
 #pragma unroll
                     for (int ks = 0; ks < BT / 16; ++ks) {
                         if (ks) mma_ts_lo<true>(tmem + kColDq, tmem + ds_col + ks * 8, k0 + desc_step(ks * 16 * 128), hi, idesc_acc);
                         else mma_ts_lo(tmem + kColDq, tmem + ds_col, k0, hi, idesc_acc, x > 0 ? 1u : 0u);
                     }
                     tc_commit(bar(kDqBarKEmpty + cur % kDqKStages));
+                    tc_commit(bar(kDqBarDsFree + (cur & 1u)));   // this dS buffer may be written again
                 }
                 if (!ok) break;
                 rc += it.n;
                 tc_commit(bar(kDqBarAccFull));
-                tc_commit(bar(kDqBarOwnEmpty));
                 ++items;
             }
         }
         __syncwarp();
-    } else {
+    } else if (warp < 8) {
         // ------------------------------ element-wise warps -----------------------------------
         const int wg = warp >> 2, wq = warp & 3;
         const uint32_t lane_base = uint32_t(wq * 32) << 16;
@@ -753,6 +774,9 @@ sdpa_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                     pk[c >> 1] = pack16<BF16>(d.x, d.y);
                 }
                 const uint32_t ds_addr = tmem + lane_base + kColDs + (rc & 1u) * 64 + wg * 32;
+                // dQ of the step before last has consumed this buffer (its issuer runs on its own)
+                ok = mbar_wait(bar(kDqBarDsFree + (rc & 1u)), ((rc >> 1) & 1u) ^ 1u, abort_flag, 14);
+                if (!ok) break;
                 tmem_st16(ds_addr, reinterpret_cast<uint32_t(&)[16]>(pk[0]));
                 tmem_st16(ds_addr + 16, reinterpret_cast<uint32_t(&)[16]>(pk[16]));
                 tmem_wait_st();
@@ -854,7 +878,7 @@ int sdpa_bwd_tc_launch(Gpu* g, const paras_sdpa_bwd_args& a, const float* delta,
     // dQ: units of paired query tiles per (batch, query head); whole 128-row tiles of q and dO
     use_q = &mq;
     use_do = &mdo;
-    threads = kThreads;
+    threads = kDkvThreads;
     p.npair = (p.nq + 1) / 2;
     const int64_t u_q = int64_t(a.B) * a.Hq * p.npair;
     if (a.D == 128) st = bf ? launch(sdpa_bwd_dq_kernel<true, 128>, u_q, kDqSmemLaunch) : launch(sdpa_bwd_dq_kernel<false, 128>, u_q, kDqSmemLaunch);
