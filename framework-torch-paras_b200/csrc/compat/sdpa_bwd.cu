@@ -105,18 +105,13 @@ extern "C" int paras_b200_sdpa_bwd(const paras_sdpa_bwd_args* a) {
     const size_t es = 2;
     const int64_t groups = int64_t(a->B) * a->Hkv;     // (batch, kv head): its r query heads are adjacent
     const int64_t rows = groups * R;
-    const int sms_ = g->sm_count > 0 ? g->sm_count : 148;
 
     // Head dim 128 / 64: the fused kernels; their only scratch is delta.
     if (!(a->reserved & PARAS_SDPA_BWD_COMPOSITE) && sdpa_bwd_tc_supported(g, *a)) {
         void* dmem = nullptr;
         st = paras_b200_malloc_async(a->gpu, size_t(rows) * sizeof(float), s, &dmem);
         if (st != PARAS_OK) return st;
-        float* delta_f = static_cast<float*>(dmem);
-        if (a->dtype == PARAS_BF16) launch_delta<__nv_bfloat16>(a->dout, a->out, delta_f, rows, a->D, sms_, s);
-        else launch_delta<__half>(a->dout, a->out, delta_f, rows, a->D, sms_, s);
-        st = cudaGetLastError() == cudaSuccess ? sdpa_bwd_tc_launch(g, *a, delta_f, s)
-                                               : fail(PARAS_E_CUDA, "paras sdpa backward: launch of the delta kernel failed");
+        st = sdpa_bwd_tc_launch(g, *a, static_cast<float*>(dmem), s);   // the dQ kernel fills delta
         const int st2 = paras_b200_free_async(a->gpu, dmem, s);
         return st != PARAS_OK ? st : st2;
     }

@@ -86,14 +86,17 @@ constexpr int kDqBarOwnFull = 0, kDqBarOwnEmpty = 1, kDqBarKFull = 2, kDqBarKEmp
               kDqBarVEmpty = 10, kDqBarSFull = 12, kDqBarDpFull = 13, kDqBarTaken = 14, kDqBarDsFull = 15,
               kDqBarAccFull = 16, kDqBarAccEmpty = 17, kDqBarDsFree = 18 /* [2] */, kDqNumBars = 20;
 constexpr int kDqSmemMisc = kDqSmemBars + kDqNumBars * 8;
-constexpr int kDqSmemLaunch = kDqSmemMisc + 16 + 1024;
+constexpr int kDqSmemDelta = kDqSmemMisc + 16;            // fp32 [128]: delta of the item's rows
+constexpr int kDqSmemLaunch = kDqSmemDelta + BT * 4 + 1024;
 
 struct BwdParams {
     void* dq;
     void* dk;
     void* dv;
     const float* lse;     // [B, Hq, Lq]
-    const float* delta;   // [B, Hq, Lq]
+    float* delta;         // [B, Hq, Lq]: rowsum(dO o O); written by the dQ kernel, read by the dK/dV kernel
+    const void* out;      // the forward's output and its gradient, dense [B, Hq, Lq, D] (for delta)
+    const void* dout;
     int B, Hq, Hkv, Lq, Lk;
     int causal;
     float scale;
@@ -103,10 +106,6 @@ struct BwdParams {
     int npair;            // paired tiles per head (ceil(n / 2))
     int units;
 };
-
-__device__ __forceinline__ void named_barrier_sync(int id, int threads) {
-    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
-}
 
 // Query tiles that see key tile j, as the range [first, nq): under the top-left aligned causal
 // mask query row r sees keys 0..r, so tile i qualifies when its last row reaches the tile's
@@ -730,8 +729,66 @@ sdpa_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             const int row = it.t * BT + wq * 32 + lane;
             const bool live = row < p.Lq;
             const int64_t grow = (int64_t(it.b) * p.Hq + it.h) * p.Lq + row;
-            const float lse2 = live ? p.lse[grow] * 1.4426950408889634f : INFINITY;   // dead rows: P = exp2(-inf) = 0
-            const float delta = live ? p.delta[grow] : 0.f;
+            // Row statistics.  delta = sum_d dO[row, d] * O[row, d] is formed here: the eight warps split
+            // the tile's 128 rows sixteen each and read them as they lie in memory (a row is HD * 2
+            // contiguous bytes, HD / 8 lanes per row), reduce within the lanes of a row and pass the sums
+            // through shared memory to the threads that own the rows; the sums also go out for the
+            // dK/dV kernel.  The item's S and dP are usually waiting by now, so this round trip is
+            // exposed: the rows were asked into L2 when the previous item started.
+            constexpr int LPR = HD / 8;        // lanes per row (16 bytes each)
+            constexpr int RPI = 32 / LPR;      // rows per warp-wide load
+            constexpr int NI = 16 / RPI;       // loads per tensor
+            const int64_t tile_row0 = (int64_t(it.b) * p.Hq + it.h) * p.Lq + it.t * BT;
+            const float nlse2 = live ? -p.lse[grow] * 1.4426950408889634f : -INFINITY;   // dead rows: P = exp2(-inf) = 0
+            float delta;
+            {
+                float* xch = reinterpret_cast<float*>(smem_gen + kDqSmemDelta);
+                uint4 ov[NI], dv[NI];
+#pragma unroll
+                for (int i = 0; i < NI; ++i) {
+                    const int rr = 16 * warp + i * RPI + lane / LPR;          // row within the tile
+                    const bool valid = it.t * BT + rr < p.Lq;
+                    const int64_t off = ((tile_row0 + rr) * HD) * 2 + (lane % LPR) * 16;
+                    ov[i] = valid ? __ldg(reinterpret_cast<const uint4*>(static_cast<const char*>(p.out) + off)) : make_uint4(0, 0, 0, 0);
+                    dv[i] = valid ? __ldg(reinterpret_cast<const uint4*>(static_cast<const char*>(p.dout) + off)) : make_uint4(0, 0, 0, 0);
+                }
+                {
+                    // the next item's rows (16 per warp, both tensors) and statistics: towards L2
+                    Item nx;
+                    int sq = seq + 1;
+                    bool have = get_item<false>(p, sq, &nx);
+                    if (have && nx.n <= 0) have = get_item<false>(p, ++sq, &nx);
+                    if (have && nx.n > 0) {
+                        const int64_t nrow = (int64_t(nx.b) * p.Hq + nx.h) * p.Lq + nx.t * BT + 16 * warp;
+                        if (nx.t * BT + 16 * warp < p.Lq) {
+                            constexpr int kLines = 16 * HD * 2 / 128;       // 128-byte lines of 16 rows
+                            if (lane < kLines) {
+                                asm volatile("prefetch.global.L2 [%0];" ::"l"(static_cast<const char*>(p.out) + nrow * HD * 2 + 128 * lane));
+                                asm volatile("prefetch.global.L2 [%0];" ::"l"(static_cast<const char*>(p.dout) + nrow * HD * 2 + 128 * lane));
+                            }
+                            if (lane == 0) asm volatile("prefetch.global.L2 [%0];" ::"l"(p.lse + nrow));
+                        }
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < NI; ++i) {
+                    const uint32_t ow[4] = {ov[i].x, ov[i].y, ov[i].z, ov[i].w};
+                    const uint32_t dw[4] = {dv[i].x, dv[i].y, dv[i].z, dv[i].w};
+                    float part = 0.f;
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float2 a = pair16_to_f32<BF16>(ow[e]), b = pair16_to_f32<BF16>(dw[e]);
+                        part = fmaf(a.x, b.x, part);
+                        part = fmaf(a.y, b.y, part);
+                    }
+#pragma unroll
+                    for (int sh = LPR / 2; sh > 0; sh >>= 1) part += __shfl_xor_sync(0xffffffffu, part, sh);
+                    if (lane % LPR == 0) xch[16 * warp + i * RPI + lane / LPR] = part;
+                }
+                asm volatile("bar.sync 1, 256;" ::: "memory");   // the eight element-wise warps
+                delta = xch[wq * 32 + lane];
+                if (wg == 0 && live) p.delta[grow] = delta;
+            }
             for (int x = 0; x < it.n; ++x, ++rc) {
                 ok = mbar_wait(bar(kDqBarSFull), rc & 1u, abort_flag, 11);
                 if (!ok) break;
@@ -758,7 +815,7 @@ sdpa_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 const int limit = (p.causal ? min(row, p.Lk - 1) : p.Lk - 1) - k0;   // last visible column
                 // some column of these 64 is invisible to some row of this warp (the same for all lanes)
                 const bool need_mask = (p.causal && k0 + 63 > it.t * BT + wq * 32) || k0 + 64 > p.Lk;
-                const float2 c22 = make_float2(c2, c2), nl2 = make_float2(-lse2, -lse2);
+                const float2 c22 = make_float2(c2, c2), nl2 = make_float2(nlse2, nlse2);
                 const float2 sc2 = make_float2(p.scale, p.scale), nd2 = make_float2(-delta * p.scale, -delta * p.scale);
                 uint32_t pk[32];
 #pragma unroll
@@ -831,8 +888,8 @@ bool sdpa_bwd_tc_supported(const Gpu* g, const paras_sdpa_bwd_args& a) {
     return true;
 }
 
-// dq, dk, dv from dense [B, H, L, D] tensors; `delta` = rowsum(dO o O), fp32 [B, Hq, Lq].
-int sdpa_bwd_tc_launch(Gpu* g, const paras_sdpa_bwd_args& a, const float* delta, cudaStream_t s) {
+// dq, dk, dv from dense [B, H, L, D] tensors; `delta` is scratch for rowsum(dO o O), fp32 [B, Hq, Lq].
+int sdpa_bwd_tc_launch(Gpu* g, const paras_sdpa_bwd_args& a, float* delta, cudaStream_t s) {
     int st = check_status_word(g);
     if (st != PARAS_OK) return st;
     const int64_t sq[3] = {int64_t(a.Hq) * a.Lq * a.D, int64_t(a.Lq) * a.D, a.D};
@@ -848,7 +905,7 @@ int sdpa_bwd_tc_launch(Gpu* g, const paras_sdpa_bwd_args& a, const float* delta,
     if ((st = make_tensor_map_bhld(&mdo64, a.dout, a.dtype, a.B, a.Hq, a.Lq, a.D, sq, kDkvHalf)) != PARAS_OK) return st;
     BwdParams p{};
     p.dq = a.dq; p.dk = a.dk; p.dv = a.dv;
-    p.lse = a.lse; p.delta = delta;
+    p.lse = a.lse; p.delta = delta; p.out = a.out; p.dout = a.dout;
     p.B = a.B; p.Hq = a.Hq; p.Hkv = a.Hkv; p.Lq = a.Lq; p.Lk = a.Lk;
     p.causal = a.causal;
     p.scale = float(a.scale);
@@ -858,8 +915,8 @@ int sdpa_bwd_tc_launch(Gpu* g, const paras_sdpa_bwd_args& a, const float* delta,
     p.nk = (a.Lk + BT - 1) / BT;
     const int sms = g->sm_count > 0 ? g->sm_count : 148;
     const bool bf = a.dtype == PARAS_BF16;
-    const CUtensorMap* use_q = &mq64;
-    const CUtensorMap* use_do = &mdo64;
+    const CUtensorMap* use_q = &mq;
+    const CUtensorMap* use_do = &mdo;
     int threads = kDkvThreads;
     auto launch = [&](auto kernel, int64_t units, int smem) -> int {
         if (units > INT32_MAX) return fail(PARAS_E_UNSUPPORTED, "paras sdpa backward: too many work units");
@@ -868,23 +925,26 @@ int sdpa_bwd_tc_launch(Gpu* g, const paras_sdpa_bwd_args& a, const float* delta,
         kernel<<<unsigned(units < sms ? units : sms), threads, smem, s>>>(*use_q, mk, mv, *use_do, p);
         return PARAS_OK;
     };
-    // dK, dV: units of paired key tiles per (batch, kv head)
-    p.npair = (p.nk + 1) / 2;
-    const int64_t u_kv = int64_t(a.B) * a.Hkv * p.npair;
-    if (a.D == 128) st = bf ? launch(sdpa_bwd_dkv_kernel<true, 128>, u_kv, kDkvSmemLaunch) : launch(sdpa_bwd_dkv_kernel<false, 128>, u_kv, kDkvSmemLaunch);
-    else st = bf ? launch(sdpa_bwd_dkv_kernel<true, 64>, u_kv, kDkvSmemLaunch) : launch(sdpa_bwd_dkv_kernel<false, 64>, u_kv, kDkvSmemLaunch);
-    if (st != PARAS_OK) return st;
-    PB_LAUNCH_CHECK("sdpa_bwd_dkv_kernel");
     // dQ: units of paired query tiles per (batch, query head); whole 128-row tiles of q and dO
+    // (it also forms delta, which the dK/dV kernel then reads: this launch comes first)
     use_q = &mq;
     use_do = &mdo;
-    threads = kDkvThreads;
     p.npair = (p.nq + 1) / 2;
     const int64_t u_q = int64_t(a.B) * a.Hq * p.npair;
     if (a.D == 128) st = bf ? launch(sdpa_bwd_dq_kernel<true, 128>, u_q, kDqSmemLaunch) : launch(sdpa_bwd_dq_kernel<false, 128>, u_q, kDqSmemLaunch);
     else st = bf ? launch(sdpa_bwd_dq_kernel<true, 64>, u_q, kDqSmemLaunch) : launch(sdpa_bwd_dq_kernel<false, 64>, u_q, kDqSmemLaunch);
     if (st != PARAS_OK) return st;
     PB_LAUNCH_CHECK("sdpa_bwd_dq_kernel");
+    // dK, dV: units of paired key tiles per (batch, kv head); queries stream 64 rows at a time
+    use_q = &mq64;
+    use_do = &mdo64;
+    threads = kDkvThreads;
+    p.npair = (p.nk + 1) / 2;
+    const int64_t u_kv = int64_t(a.B) * a.Hkv * p.npair;
+    if (a.D == 128) st = bf ? launch(sdpa_bwd_dkv_kernel<true, 128>, u_kv, kDkvSmemLaunch) : launch(sdpa_bwd_dkv_kernel<false, 128>, u_kv, kDkvSmemLaunch);
+    else st = bf ? launch(sdpa_bwd_dkv_kernel<true, 64>, u_kv, kDkvSmemLaunch) : launch(sdpa_bwd_dkv_kernel<false, 64>, u_kv, kDkvSmemLaunch);
+    if (st != PARAS_OK) return st;
+    PB_LAUNCH_CHECK("sdpa_bwd_dkv_kernel");
     return PARAS_OK;
 }
 

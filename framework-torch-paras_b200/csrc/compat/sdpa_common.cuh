@@ -69,6 +69,6 @@ int sdpa_weights_launch(Gpu* g, const paras_sdpa_args& a, float scale, cudaStrea
 
 // Fused tcgen05 attention backward (sdpa_bwd_tc.cu): 16-bit, D == 128 or 64, dense tensors.
 bool sdpa_bwd_tc_supported(const Gpu* g, const paras_sdpa_bwd_args& a);
-int sdpa_bwd_tc_launch(Gpu* g, const paras_sdpa_bwd_args& a, const float* delta, cudaStream_t s);
+int sdpa_bwd_tc_launch(Gpu* g, const paras_sdpa_bwd_args& a, float* delta, cudaStream_t s);
 
 }  // namespace pb
