@@ -502,7 +502,7 @@ def run_ours(args):
     if want("bwd"):
         # Attention backward at the headline shape (config 2): forward with lse, then dq, dk, dv.
         # FLOPs counted as 2.5x the forward's algorithmic FLOPs (five products instead of two),
-        # causal half included, although this implementation computes the full [L, L] matrices.
+        # causal half only (the kernels skip the blocks a causal mask empties).
         Bb = 2 if args.small else c["B"]
         qb_, kb_, vb_ = q[:Bb].contiguous(), k[:Bb].contiguous(), v[:Bb].contiguous()
         dob = gen((Bb, c["Hq"], c["S"], c["D"]), 25)
@@ -512,8 +512,8 @@ def run_ours(args):
         fl = 2.5 * sdpa_flops(Bb, c["Hq"], c["S"], c["S"], c["D"], True)
         extra[f"sdpa_backward_B{Bb}_H{c['Hq']}_S{c['S']}"] = {
             "ms": t, "tflops": fl / (t * 1e-3) / 1e12, "frac_of_bf16_peak": fl / (t * 1e-3) / 1e12 / peaks["bf16_tflops"],
-            "note": "fused tcgen05 kernels (dK/dV, then dQ; S and dP recomputed in each: 7 tile products, "
-                    "counted as the 5 the gradient needs); delta pre-pass included",
+            "note": "fused tcgen05 kernels (dQ, which also forms delta, then dK/dV; S and dP recomputed in each: "
+                    "7 tile products, counted as the 5 the gradient needs)",
             "composite_ms": t_c, "composite_tflops": fl / (t_c * 1e-3) / 1e12}
         del qb_, kb_, vb_, dob, ob, lseb
     if want("rope"):

@@ -9,28 +9,27 @@
 //     dS = P o (dP - delta[q]) * scale        dP = dO V^T,  delta[q] = sum_d dO[q,d] O[q,d]
 //     dV = P^T dO      dK = dS^T Q      dQ = dS K
 //
-// Two kernels, each a persistent grid of one 320-thread CTA per SM, neither with atomics nor
-// with scratch beyond delta (so the result is deterministic):
+// Two kernels, each a persistent grid of one 352-thread CTA per SM, neither with atomics nor
+// with scratch beyond the row statistic delta (so the result is deterministic):
 //
-//   sdpa_bwd_dkv_kernel   a CTA keeps one 128-key tile (K_j, V_j) in shared memory and streams
+//   sdpa_bwd_dq_kernel    (runs first) a CTA keeps one 128-query tile (Q_i, dO_i) in shared memory and
+//       streams the key tiles it sees; S and dP land in TMEM with one QUERY per lane, dS goes back
+//       to TMEM as the 16-bit A operand of dQ += dS K_j.  It also forms delta for its rows and writes
+//       it out for the second kernel.
+//   sdpa_bwd_dkv_kernel   the mirror image: a CTA keeps one 128-key tile (K_j, V_j) and streams
 //       the query tiles that see it (all query heads of the kv head's group, so GQA sums happen
-//       in the accumulator).  S^T = K_j Q_i^T and dP^T = V_j dO_i^T land in TMEM with one KEY per
-//       lane; P^T and dS^T go back to TMEM as 16-bit A operands of dV += P^T dO_i, dK += dS^T Q_i.
-//   sdpa_bwd_dq_kernel    the mirror image: a CTA keeps one 128-query tile (Q_i, dO_i) and
-//       streams the key tiles it sees; S and dP land with one QUERY per lane, dS goes back to
-//       TMEM as the A operand of dQ += dS K_j.
+//       in the accumulator).  S^T = K_j Q_i^T and dP^T = V_j dO_i^T land with one KEY per lane;
+//       P^T and dS^T go back to TMEM as the A operands of dV += P^T dO_i, dK += dS^T Q_i.
 //
 // S and dP are computed twice (7 tile products instead of 5) in exchange for no fp32 dQ
 // accumulator in memory, no atomics and no conversion pass.
 //
-//   warps 0-3  element-wise work on columns 0-63 of the S / dP tiles (a lane owns a row)
-//   warps 4-7  the same on columns 64-127
-//   warp  8    one lane issues every tcgen05.mma
-//   warp  9    TMA loads (and, for the dK/dV kernel, the per-query statistics of each tile)
+//   warps 0-3  element-wise work on one half of the columns of the S / dP tiles (a lane owns a row)
+//   warps 4-7  the same on the other half
+//   warp  8    one lane issues the products that form S and dP (S^T and dP^T)
+//   warp  9    TMA loads (and, for the dK/dV kernel, the per-query statistics of each step)
+//   warp 10    one lane issues the products that accumulate (dQ; dV and dK)
 //
-// Shared memory (both kernels): the CTA's own pair of tiles (2 x 32 KB) and a ring of two
-// stages of the streamed pair (2 x 64 KB), all 128-byte swizzled as TMA writes them.
-// TMEM: S @0, dP @128, then dV @256 / dK @384 (dK/dV kernel) or dQ @256 / dS @384,448.
 // Every wait is bounded (tc_prims.cuh): a wait that runs out raises the CTA's abort flag, all
 // roles leave through the common exit, TMEM is freed and the GPU's status word is set.
 #include <cmath>
@@ -47,32 +46,10 @@ using namespace tc;
 constexpr int BT = 128;                       // rows of every tile: queries or keys
 constexpr int kChunkBytes = 64 * 2 * 128;     // one 64-element slab of 128 rows
 constexpr int kTileBytes = 2 * kChunkBytes;   // 128 x 128 x 2 B (head dim 64 uses the first slab)
-constexpr int kThreads = 320;
 constexpr int kMmaWarp = 8, kLoadWarp = 9;
 constexpr int kTmemCols = 512;
 
-// shared memory map
-constexpr int kSmemOwn = 0;                              // the CTA's own pair: tile 0, tile 1
-constexpr int kSmemRing = 2 * kTileBytes;                // 2 stages x (tile 0, tile 1)
-constexpr int kStageBytes = 2 * kTileBytes;
-constexpr int kSmemStats = kSmemRing + 2 * kStageBytes;  // 2 stages x (lse2[128], delta[128]) fp32
-constexpr int kStatsBytes = 2 * BT * 4;
-constexpr int kSmemBars = kSmemStats + 2 * kStatsBytes;
-// barriers
-constexpr int kBarOwnFull = 0;     // TMA -> MMA: the own pair landed
-constexpr int kBarOwnEmpty = 1;    // MMA -> TMA: the item's last MMA that reads the own pair is done
-constexpr int kBarRingFull = 2;    // [2]
-constexpr int kBarRingEmpty = 4;   // [2]
-constexpr int kBarSFull = 6;       // MMA -> compute: S tile ready
-constexpr int kBarDpFull = 7;      // MMA -> compute: dP tile ready
-constexpr int kBarPFull = 8;       // compute -> MMA: P^T stored (dK/dV kernel) / S and dP taken (dQ kernel)
-constexpr int kBarDsFull = 9;      // compute -> MMA: dS stored
-constexpr int kBarAccFull = 10;    // MMA -> compute: the item's accumulators are complete
-constexpr int kBarAccEmpty = 11;   // compute -> MMA: the accumulators have been read out
-constexpr int kNumBars = 12;
-constexpr int kSmemMisc = kSmemBars + kNumBars * 8;
-constexpr int kSmemTotal = kSmemMisc + 16;
-constexpr int kSmemLaunch = kSmemTotal + 1024;
+constexpr int kSmemOwn = 0;                   // shared memory starts with the CTA's own pair: tile 0, tile 1
 
 // The dQ kernel streams K and V through rings of their own: V_j is done with after dP = dO V_j^T,
 // K_j only after dQ += dS K_j at the end of the step, so K gets three stages and V two (with one
