@@ -276,13 +276,16 @@ def test_sdpa_scores_that_grow_from_tile_to_tile(factor, causal, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
-@pytest.mark.parametrize("kind", ["bool_padding", "bool_blocks", "additive_same", "additive_f32", "ragged_bool"])
+@pytest.mark.parametrize("kind", ["bool_padding", "bool_blocks", "additive_same", "additive_f32", "ragged_bool",
+                                  "additive_ragged_rows"])
 def test_tensor_core_kernel_with_explicit_masks(kind, dtype):
     # attn_mask on the tcgen05 path (16 bit, D = 128): bool and additive, broadcast strides,
     # vector and element-wise reads, rows whose first key tiles are masked out entirely, and rows
     # with no key at all (NaN, as in the reference)
     B, Hq, Hkv = 2, 4, 2
-    Lq, Lk = (300, 333) if kind == "ragged_bool" else (384, 512)
+    # (contiguous, 16-byte aligned mask rows are read by the warp as a block; "additive_ragged_rows"
+    # takes that path with a last query tile that ends at row 300 of 384)
+    Lq, Lk = (300, 333) if kind == "ragged_bool" else ((300, 512) if kind == "additive_ragged_rows" else (384, 512))
     q, k, v = _qkv(B, Hq, Hkv, Lq, Lk, 128, dtype, seed=23)
     g = torch.Generator().manual_seed(29)
     if kind == "bool_padding":      # per batch element: keys past its length are padding
@@ -297,7 +300,7 @@ def test_tensor_core_kernel_with_explicit_masks(kind, dtype):
             mask[0, 0, r, lo:lo + 60] = True
         mask[0, 0, 5] = False        # a row without any key
         mask[0, 0, 200] = False
-    elif kind == "additive_same":
+    elif kind in ("additive_same", "additive_ragged_rows"):
         mask = (torch.randn(Lq, Lk, generator=g) * 2).to(dtype)
     elif kind == "additive_f32":
         mask = torch.randn(B, Hq, Lq, Lk, generator=g) * 2
