@@ -92,6 +92,22 @@ def run_op(op, a):
     if op == "rotate_half":
         x = _dev(a["x"])
         return lambda: torch.ops.paras.rotate_half(x)
+    if op == "rope_sdpa":
+        # rotary embedding composed from the reference's own operators (mul.out, add.out,
+        # paras::rotate_half), then its attention: returns (rotated q, rotated k, attention output)
+        q, k, v = _dev(a["q"]), _dev(a["k"]), _dev(a["v"])
+        cos, sin = _dev(a["cos"]), _dev(a["sin"])
+        pos0 = int(a.get("q_pos0", 0))
+        kw = {"enable_gqa": True} if a.get("enable_gqa") else {}
+
+        def run_rope():
+            cq, sq = cos[pos0:pos0 + q.shape[-2]], sin[pos0:pos0 + q.shape[-2]]
+            ck, sk = cos[:k.shape[-2]], sin[:k.shape[-2]]
+            qr = q * cq + torch.ops.paras.rotate_half(q) * sq
+            kr = k * ck + torch.ops.paras.rotate_half(k) * sk
+            out = F.scaled_dot_product_attention(qr, kr, v, is_causal=bool(a.get("is_causal", False)), **kw)
+            return qr, kr, out
+        return run_rope
     if op == "rotate_half_backward":
         x = _dev(a["grad_out"])
         return lambda: torch.ops.paras.rotate_half_backward(x)

@@ -126,7 +126,42 @@ def dropout_cases():
     return out
 
 
+def rope_cases():
+    """Rotary embedding as a user of the reference composes it (x * cos + rotate_half(x) * sin with the
+    reference's mul, add and paras::rotate_half) in front of its attention."""
+    g = torch.Generator().manual_seed(20261128)
+
+    def R(*shape, dt=torch.float32):
+        return torch.randn(*shape, generator=g).to(dt)
+
+    def tables(rows, D, dt):
+        inv = 1.0 / (10000.0 ** (torch.arange(0, D, 2, dtype=torch.float64) / D))
+        ang = torch.arange(rows, dtype=torch.float64)[:, None] * inv[None, :]
+        emb = torch.cat((ang, ang), dim=-1)
+        return emb.cos().to(dt), emb.sin().to(dt)
+
+    out = []
+    for dt, tag in ((torch.float32, "f32"), (torch.bfloat16, "bf16")):
+        # causal GQA, then a decode step at position 29 of a 30-key cache (small head dim: the
+        # rounding of the three element-wise steps is what is being pinned)
+        cos, sin = tables(30, 32, dt)
+        q, k, v = R(1, 2, 24, 32, dt=dt), R(1, 1, 24, 32, dt=dt), R(1, 1, 24, 32, dt=dt)
+        out.append((f"rope_sdpa_causal_gqa_{tag}", "rope_sdpa",
+                    {"q": q, "k": k, "v": v, "cos": cos, "sin": sin, "is_causal": True, "enable_gqa": True}))
+        q, k, v = R(2, 2, 1, 32, dt=dt), R(2, 1, 30, 32, dt=dt), R(2, 1, 30, 32, dt=dt)
+        out.append((f"rope_sdpa_decode_{tag}", "rope_sdpa",
+                    {"q": q, "k": k, "v": v, "cos": cos, "sin": sin, "q_pos0": 29, "enable_gqa": True}))
+    # head dim 128 (the shape the attention kernel rotates in its prologue), 16 bit
+    cos, sin = tables(40, 128, torch.bfloat16)
+    q, k, v = R(1, 2, 40, 128, dt=torch.bfloat16), R(1, 1, 40, 128, dt=torch.bfloat16), R(1, 1, 40, 128, dt=torch.bfloat16)
+    out.append(("rope_sdpa_causal_d128_bf16", "rope_sdpa",
+                {"q": q, "k": k, "v": v, "cos": cos, "sin": sin, "is_causal": True, "enable_gqa": True}))
+    return out
+
+
 def main():
+    if "--rope" in sys.argv:     # only the rotary-embedding fixtures
+        globals()["cases"] = rope_cases
     if "--dropout" in sys.argv:  # only the dropout / weights fixtures
         globals()["cases"] = dropout_cases
     if "--grad" in sys.argv:     # only the gradient fixtures

@@ -70,6 +70,12 @@ def run_cuda(op, a, **kw):
         return abi.rotate_half(c(a["x"]))
     if op == "rotate_half_backward":
         return abi.rotate_half(c(a["grad_out"]), backward=True)
+    if op == "rope_sdpa":   # (rotated q, rotated k, attention over them): rotation alone, then the fused call
+        q, k, v, cos, sin = c(a["q"]), c(a["k"]), c(a["v"]), c(a["cos"]), c(a["sin"])
+        pos0 = int(a.get("q_pos0", 0))
+        out = abi.sdpa_rope_fwd(q, k, v, cos, sin, q_pos0=pos0, causal=bool(a.get("is_causal", False)),
+                                flags=abi.SDPA_REF_SCALE)
+        return abi.rope(q, cos, sin, pos0=pos0), abi.rope(k, cos, sin, pos0=0), out
     raise AssertionError(op)
 
 
@@ -83,7 +89,10 @@ def test_against_reference_golden_vectors(name):
     got = as_tuple(run_cuda(g["op"], g["args"]))
     want = as_tuple(g["out"])
     for i, (a, b) in enumerate(zip(got, want)):
-        tol_check(a, b, f"{name}[{i}]")
+        if g["op"] == "rope_sdpa" and i < 2:   # the rotation is three rounded element-wise steps: exact
+            assert torch.equal(a.cpu(), b), f"{name}[{i}]: rotated tensor differs from the reference's"
+        else:
+            tol_check(a, b, f"{name}[{i}]")
 
 
 def _qkv(B, Hq, Hkv, Lq, Lk, D, dtype, seed):

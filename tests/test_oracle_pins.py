@@ -47,6 +47,11 @@ def run_oracle(op, a):
         return O.rotate_half(a["x"])
     if op == "rotate_half_backward":
         return O.rotate_half_backward(a["grad_out"])
+    if op == "rope_sdpa":   # (rotated q, rotated k, attention over them)
+        qr = O.rope(a["q"], a["cos"], a["sin"], int(a.get("q_pos0", 0)))
+        kr = O.rope(a["k"], a["cos"], a["sin"], 0)
+        return qr, kr, O.sdpa(qr, kr, a["v"], is_causal=bool(a.get("is_causal", False)),
+                              enable_gqa=bool(a.get("enable_gqa", False)))
     raise AssertionError(op)
 
 
