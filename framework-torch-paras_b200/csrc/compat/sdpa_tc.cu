@@ -158,6 +158,13 @@ __device__ __forceinline__ bool get_item(const TcParams& p, int seq, Item* it) {
     return true;
 }
 
+// True when one of the 16 bytes is zero (bool mask bytes: zero = masked out).
+__device__ __forceinline__ bool any_zero_byte(const uint4& w) {
+    const uint32_t t = ((w.x - 0x01010101u) & ~w.x) | ((w.y - 0x01010101u) & ~w.y) |
+                       ((w.z - 0x01010101u) & ~w.z) | ((w.w - 0x01010101u) & ~w.w);
+    return (t & 0x80808080u) != 0;
+}
+
 // MASK: an explicit attn_mask is applied (a separate instantiation: the unmasked kernel pays
 // nothing for it, not even registers).  ROPE: the query tile is rotated in shared memory, by the
 // softmax warps that own its rows, between its TMA load and the first QK^T (head dim 128).
@@ -420,7 +427,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             const char* mask_bh = nullptr;
             int64_t mpitch = 0;
             int mesz = 1;
-            bool mfast = false;
+            bool mfast = false, mbcast = false;
             if (MASK) {
                 mesz = p.mask_kind == 1 ? 1 : (p.mask_kind == 2 ? 2 : 4);
                 mask_bh = static_cast<const char*>(p.mask) + (int64_t(it.b) * p.ms[0] + int64_t(it.h) * p.ms[1]) * mesz;
@@ -432,6 +439,9 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                     if (lane == 0) tma_store_wait_read();   // the previous item's O store has read the buffer
                     __syncwarp();
                 }
+                // one bool row for every query (a key-padding mask): its 128 bytes per kv tile are
+                // fetched before the wait for S, so that their latency is not part of the tile's chain
+                mbcast = p.mask_kind == 1 && p.ms[3] == 1 && mpitch == 0 && (reinterpret_cast<uintptr_t>(mask_bh) & 15u) == 0;
             }
             const int mu = lane & 7, mrs = lane >> 3;
             auto mask_ldg = [&](int col0, int r, uint4 (&w)[8]) {
@@ -581,7 +591,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             bool move_ref = false;
             for (int j = 0; j < nt; ++j) {
                 uint4 mw[8];
-                bool staged = false;
+                bool staged = false, early = false;
                 if (MASK) {
                     // these warps are idle until S arrives: round 0 of this step's mask goes to the staging
                     // buffer now, round 1 stays in flight across the wait
@@ -592,6 +602,11 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                         if (mesz > 1) mask_ldg(j * BN, 1, mw);
                         mask_sts(w0);
                         __syncwarp();
+                    }
+                    early = mbcast && (j + 1) * BN <= p.Lk;
+                    if (early) {
+#pragma unroll
+                        for (int v = 0; v < 8; ++v) mw[v] = __ldg(reinterpret_cast<const uint4*>(mask_bh + j * BN) + v);
                     }
                 }
                 ok = mbar_wait(bar(kBarSFull + t), scnt & 1u, abort_flag, 10 + t);
@@ -648,8 +663,20 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                             if (i > limit) s[i] = 0xff800000u;  // -inf
                     }
                     if (MASK) {
-                        if (staged && attempt == 0) mask_apply_staged(s, col0, mw);
-                        else apply_mask(s, col0);
+                        if (staged && attempt == 0) {
+                            mask_apply_staged(s, col0, mw);
+                        } else if (early) {
+#pragma unroll
+                            for (int v = 0; v < 8; ++v) {
+                                if (!any_zero_byte(mw[v])) continue;   // these 16 keys are all visible
+                                const uint32_t ww[4] = {mw[v].x, mw[v].y, mw[v].z, mw[v].w};
+#pragma unroll
+                                for (int e = 0; e < 16; ++e)
+                                    if (((ww[e >> 2] >> (8 * (e & 3))) & 0xffu) == 0) s[16 * v + e] = 0xff800000u;
+                            }
+                        } else {
+                            apply_mask(s, col0);
+                        }
                     }
                     if (j == 0 || attempt == 1) {
                         float mx0 = -INFINITY, mx1 = -INFINITY;
