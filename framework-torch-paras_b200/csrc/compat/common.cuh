@@ -33,6 +33,18 @@ struct Gpu {
     // write a non-zero code here instead of trapping or spinning.
     int* status_host = nullptr;
     int* status_dev = nullptr;
+    // Host-side cap on the bytes the pool may have handed out (0 = none): an allocation that would
+    // go past it fails with PARAS_E_NOMEM before any CUDA call.  For sharing a GPU with another
+    // owner, and for exercising the out-of-memory path without exhausting a GPU.
+    size_t limit_bytes = 0;
+};
+
+// Profiler range around a public entry point, active when PARAS_NVTX is set (the reference has only
+// its PTSYCL_LOG op trace, core/log.h:30-60).  Without a profiler attached NVTX calls do nothing.
+struct NvtxRange {
+    explicit NvtxRange(const char* name);
+    ~NvtxRange();
+    bool on;
 };
 
 // Returns PARAS_E_TIMEOUT (and clears the word) when a kernel on `g` reported that one of

@@ -287,6 +287,7 @@ extern "C" {
 
 int paras_b200_swiglu_fwd(int gpu, const void* gate, const void* up, void* out, int64_t n,
                           int dtype, int mode, void* stream) {
+    pb::NvtxRange range("paras_b200_swiglu_fwd");
     if (n < 0) return fail(PARAS_E_INVALID, "paras swiglu: negative element count");
     if (dtype != PARAS_F32 && dtype != PARAS_BF16 && dtype != PARAS_F16)
         return fail(PARAS_E_UNSUPPORTED, "paras swiglu: unsupported dtype %d", dtype);
@@ -311,6 +312,7 @@ int paras_b200_swiglu_fwd(int gpu, const void* gate, const void* up, void* out, 
 
 int paras_b200_swiglu_bwd(int gpu, const void* grad_out, const void* gate, const void* up,
                           void* grad_gate, void* grad_up, int64_t n, int dtype, void* stream) {
+    pb::NvtxRange range("paras_b200_swiglu_bwd");
     if (n < 0) return fail(PARAS_E_INVALID, "paras swiglu_backward: negative element count");
     if (dtype != PARAS_F32 && dtype != PARAS_BF16 && dtype != PARAS_F16)
         return fail(PARAS_E_UNSUPPORTED, "paras swiglu_backward: unsupported dtype %d", dtype);

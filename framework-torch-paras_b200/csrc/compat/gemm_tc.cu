@@ -665,4 +665,7 @@ int gemm_run(const paras_gemm_args* a, const GemmExtra* ex) {
 }
 }  // namespace pb
 
-extern "C" int paras_b200_gemm(const paras_gemm_args* a) { return pb::gemm_run(a, nullptr); }
+extern "C" int paras_b200_gemm(const paras_gemm_args* a) {
+    pb::NvtxRange range("paras_b200_gemm");
+    return pb::gemm_run(a, nullptr);
+}

@@ -469,6 +469,7 @@ extern "C" {
 int paras_b200_rmsnorm_fwd(int gpu, const void* x, const void* weight, void* y, float* rstd,
                            int64_t rows, int64_t H, double eps, int dtype, int mode,
                            void* stream) {
+    pb::NvtxRange range("paras_b200_rmsnorm_fwd");
     if (rows < 0 || H < 0) return fail(PARAS_E_INVALID, "paras rms_norm: negative size");
     if (dtype != PARAS_F32 && dtype != PARAS_BF16 && dtype != PARAS_F16)
         return fail(PARAS_E_UNSUPPORTED, "paras rms_norm: unsupported dtype %d", dtype);
@@ -520,6 +521,7 @@ int paras_b200_rms_rstd(int gpu, const void* x, float* rstd, int64_t rows, int64
 int paras_b200_rmsnorm_bwd(int gpu, const void* grad_out, const void* x, const void* weight,
                            const float* rstd, void* grad_x, void* grad_weight, int64_t rows,
                            int64_t H, int dtype, void* stream) {
+    pb::NvtxRange range("paras_b200_rmsnorm_bwd");
     if (rows < 0 || H < 0) return fail(PARAS_E_INVALID, "paras rms_norm_backward: negative size");
     if (dtype != PARAS_F32 && dtype != PARAS_BF16 && dtype != PARAS_F16)
         return fail(PARAS_E_UNSUPPORTED, "paras rms_norm_backward: unsupported dtype %d", dtype);

@@ -12,6 +12,8 @@
 #include <thread>
 #include <vector>
 
+#include <nvtx3/nvToolsExt.h>
+
 #include "common.cuh"
 
 namespace pb {
@@ -110,6 +112,7 @@ int lazy_init_gpu(Gpu& g) {
     PB_CUDA(cudaHostGetDevicePointer(reinterpret_cast<void**>(&ds), hs, 0));
     g.status_host = hs;
     g.status_dev = ds;
+    if (const char* lim = std::getenv("PARAS_POOL_LIMIT_MB")) g.limit_bytes = size_t(std::strtoull(lim, nullptr, 10)) << 20;
     g.pool = pool;
     g.copy_stream = c;
     g.stream = s;
@@ -154,6 +157,15 @@ void parallel_memcpy(void* dst, const void* src, size_t bytes) {
 }
 
 }  // namespace
+
+NvtxRange::NvtxRange(const char* name) {
+    static const bool enabled = std::getenv("PARAS_NVTX") != nullptr;
+    on = enabled;
+    if (on) nvtxRangePushA(name);
+}
+NvtxRange::~NvtxRange() {
+    if (on) nvtxRangePop();
+}
 
 bool host_ptr_is_pinned(const void* p) {
     cudaPointerAttributes a{};
@@ -276,13 +288,30 @@ int paras_b200_synchronize(int gpu) {
     return pb::check_status_word(g);
 }
 
+int paras_b200_pool_set_limit(int gpu, size_t bytes) {
+    int st;
+    Gpu* g = use_gpu(gpu, &st);
+    if (!g) return st;
+    g->limit_bytes = bytes;
+    return PARAS_OK;
+}
+
 int paras_b200_malloc_async(int gpu, size_t bytes, void* stream, void** ptr) {
+    pb::NvtxRange range("paras_b200_malloc_async");
     if (!ptr) return fail(PARAS_E_INVALID, "paras_b200: null output");
     *ptr = nullptr;
     int st;
     Gpu* g = use_gpu(gpu, &st);
     if (!g) return st;
     if (bytes == 0) return PARAS_OK;
+    if (g->limit_bytes) {
+        uint64_t used = 0;
+        PB_CUDA(cudaMemPoolGetAttribute(g->pool, cudaMemPoolAttrUsedMemCurrent, &used));
+        if (used + bytes > g->limit_bytes)
+            return fail(PARAS_E_NOMEM, "paras_b200: out of memory on gpu %d: %zu bytes asked for with %llu in use and a "
+                        "limit of %zu (paras_b200_pool_set_limit / PARAS_POOL_LIMIT_MB)", gpu, bytes,
+                        static_cast<unsigned long long>(used), g->limit_bytes);
+    }
     cudaError_t e = cudaMallocFromPoolAsync(ptr, bytes, g->pool, pb::pick_stream(g, stream));
     if (e == cudaErrorMemoryAllocation) {
         cudaGetLastError();

@@ -109,6 +109,7 @@ int paras_b200_sdpa_workspace_bytes(const paras_sdpa_args* a, size_t* bytes) {
 }
 
 int paras_b200_sdpa_fwd(const paras_sdpa_args* a) {
+    pb::NvtxRange range("paras_b200_sdpa_fwd");
     int st = pb::validate(a);
     if (st != PARAS_OK) return st;
     Gpu* g = pb::use_gpu(a->gpu, &st);
@@ -175,6 +176,7 @@ int paras_b200_sdpa_fwd(const paras_sdpa_args* a) {
 // ---- attention with the rotary embedding in its prologue -------------------------------------
 int paras_b200_sdpa_rope_fwd(const paras_sdpa_args* a, const void* cosv, const void* sinv, int64_t table_rows,
                              int64_t q_pos0) {
+    pb::NvtxRange range("paras_b200_sdpa_rope_fwd");
     int st = pb::validate(a);
     if (st != PARAS_OK) return st;
     if (a->mask || pb::sdpa_wants_weights(*a))
@@ -249,6 +251,7 @@ HostPipe g_host_pipe[16];
 }  // namespace pb
 
 int paras_b200_sdpa_fwd_host(const paras_sdpa_args* a) {
+    pb::NvtxRange range("paras_b200_sdpa_fwd_host");
     int st = pb::validate(a);
     if (st != PARAS_OK) return st;
     Gpu* g = pb::use_gpu(a->gpu, &st);

@@ -69,6 +69,7 @@ using pb::fail;
 using pb::Gpu;
 
 extern "C" int paras_b200_sdpa_bwd(const paras_sdpa_bwd_args* a) {
+    pb::NvtxRange range("paras_b200_sdpa_bwd");
     using namespace pb;
     if (!a) return fail(PARAS_E_INVALID, "paras sdpa backward: null argument block");
     if (a->dtype != PARAS_BF16 && a->dtype != PARAS_F16)

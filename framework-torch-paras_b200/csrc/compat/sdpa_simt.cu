@@ -305,6 +305,7 @@ int static_scratch_for(int gpu, void** out) {
 extern "C" int paras_b200_sdpa_static_scratch_bytes(void) { return int(pb::kStaticScratchBytes); }
 
 extern "C" int paras_b200_sdpa_fwd_static_scratch(const paras_sdpa_args* a) {
+    pb::NvtxRange range("paras_b200_sdpa_fwd_static_scratch");
     using pb::fail;
     if (!a) return fail(PARAS_E_INVALID, "paras sdpa: null argument block");
     if (a->dtype != PARAS_F32 && a->dtype != PARAS_BF16 && a->dtype != PARAS_F16)

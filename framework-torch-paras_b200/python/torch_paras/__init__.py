@@ -93,6 +93,15 @@ def memory_cached(device: int = 0) -> int:
     return _C.cached_bytes(device)
 
 
+def set_memory_limit(nbytes: int, device: int = 1) -> None:
+    """Caps the device memory `paras:device` (1..N) may hold at any time; 0 lifts the cap.  An
+    allocation that would pass it raises RuntimeError("... out of memory ...") like a full device."""
+    if device < 1:
+        raise ValueError("paras:0 is the host; memory limits apply to paras:1..N")
+    from . import abi
+    abi.pool_set_limit(device - 1, int(nbytes))
+
+
 def get_amp_supported_dtype() -> list[torch.dtype]:
     return [torch.float16, torch.bfloat16, torch.float32]
 

@@ -26,7 +26,7 @@ EXPORTS = [
     "paras_b200_abi_version", "paras_b200_backend_name", "paras_b200_last_error",
     "paras_b200_device_count", "paras_b200_device_name", "paras_b200_device_sm_count",
     "paras_b200_stream", "paras_b200_synchronize", "paras_b200_malloc_async",
-    "paras_b200_free_async", "paras_b200_pool_stats", "paras_b200_pool_trim",
+    "paras_b200_free_async", "paras_b200_pool_stats", "paras_b200_pool_trim", "paras_b200_pool_set_limit",
     "paras_b200_memcpy_h2d", "paras_b200_memcpy_d2h", "paras_b200_memcpy_d2d",
     "paras_b200_memcpy_peer", "paras_b200_memset", "paras_b200_host_alloc", "paras_b200_host_free",
     "paras_b200_host_is_pinned",
@@ -38,6 +38,13 @@ EXPORTS = [
     "paras_b200_sdpa_split_layout", "paras_b200_selftest_bounded_wait",
     "paras_b200_rms_rstd", "paras_b200_scale_columns", "paras_b200_sdpa_rope_fwd", "paras_b200_rope",
 ]
+
+
+def pool_set_limit(gpu: int, nbytes: int) -> None:
+    """Caps the bytes the pool of CUDA GPU `gpu` may have handed out (0 = no cap)."""
+    L = lib()
+    L.paras_b200_pool_set_limit.argtypes = [C.c_int, C.c_size_t]
+    check(L.paras_b200_pool_set_limit(gpu, nbytes))
 
 
 class SdpaArgs(C.Structure):

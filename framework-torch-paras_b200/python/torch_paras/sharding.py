@@ -84,6 +84,48 @@ def gather_shards(local: torch.Tensor, sizes: Sequence[int], dim: int = 0, group
     return out.movedim(0, dim)
 
 
+# ---- failure detection on the host ---------------------------------------------------------
+# The forward path has no collective, so a rank that dies only matters at the optional gather.
+# Ranks announce each step in the rendezvous store before they enter a gather; a rank that finds a
+# peer missing raises on the host instead of launching a collective that would wait for it.  (The
+# other net is the process group's timeout, which turns a gather with a dead peer into an error.)
+def announce_step(store, rank: int, step: int) -> None:
+    """Records that `rank` has finished its work for `step` and is about to exchange results."""
+    store.set(f"paras/step/{rank}", str(step))
+
+
+def absent_ranks(store, world: int, step: int, wait_s: float = 2.0, poll_s: float = 0.02) -> List[int]:
+    """Ranks that have not announced `step` within `wait_s` seconds (empty = everyone is there)."""
+    import time
+    deadline = time.monotonic() + wait_s
+    missing = list(range(world))
+    while missing:
+        still = []
+        for r in missing:
+            try:
+                ok = store.check([f"paras/step/{r}"]) and int(store.get(f"paras/step/{r}")) >= step
+            except Exception:  # noqa: BLE001  (store gone with its owner: the peer is absent)
+                ok = False
+            if not ok:
+                still.append(r)
+        missing = still
+        if not missing or time.monotonic() >= deadline:
+            break
+        time.sleep(poll_s)
+    return missing
+
+
+def gather_shards_checked(store, rank: int, step: int, local: torch.Tensor, sizes: Sequence[int], dim: int = 0,
+                          group=None, wait_s: float = 2.0) -> torch.Tensor:
+    """gather_shards for step `step`, entered only when every rank has announced that step."""
+    import torch.distributed as dist
+    announce_step(store, rank, step)
+    gone = absent_ranks(store, dist.get_world_size(group), step, wait_s)
+    if gone:
+        raise RuntimeError(f"paras sharding: rank(s) {gone} did not reach step {step}; gather not started")
+    return gather_shards(local, sizes, dim, group)
+
+
 def _parse_cpulist(text: str) -> List[int]:
     cpus: List[int] = []
     for part in text.strip().split(","):

@@ -74,6 +74,11 @@ int paras_b200_free_async(int gpu, void* ptr, void* stream);
 int paras_b200_pool_stats(int gpu, uint64_t* used_bytes, uint64_t* reserved_bytes);
 /* MemoryPool::clear (core/allocator.cpp): returns cached memory to the driver. */
 int paras_b200_pool_trim(int gpu);
+/* Caps the bytes the pool of `gpu` may have handed out at any time (0 = no cap; the environment
+ * variable PARAS_POOL_LIMIT_MB sets the initial value): an allocation that would pass the cap
+ * returns PARAS_E_NOMEM without a CUDA call, as Queue::alloc fails when the device is out of
+ * memory (paras_compat.cpp:270-307).  For sharing a GPU and for testing out-of-memory handling. */
+int paras_b200_pool_set_limit(int gpu, size_t bytes);
 
 /* Queue::copy / Queue::memset (paras_compat.cpp:326-352).  Host<->device copies of
  * pageable memory go through the library's pinned staging buffers; `blocking` != 0

@@ -329,3 +329,26 @@ def test_attention_host_streams_batches_through_the_gpu():
         assert got2 is out and torch.equal(out, got)
     with pytest.raises(RuntimeError):
         paras_nn.attention_host(q, k, v, device=0)
+
+
+def test_memory_limit_makes_allocation_fail_like_a_full_device():
+    # out-of-memory handling without exhausting a GPU: a host-side cap on the pool
+    import torch_paras
+    torch_paras.synchronize()
+    base = torch_paras.memory_allocated(1)
+    torch_paras.set_memory_limit(base + (64 << 20), 1)
+    try:
+        small = torch.empty(32 << 20, dtype=torch.uint8, device="paras:1")
+        with pytest.raises(RuntimeError, match="out of memory"):
+            torch.empty(128 << 20, dtype=torch.uint8, device="paras:1")
+        del small
+        # an operator that needs scratch fails the same way and leaves the device usable
+        q = torch.randn(1, 2, 64, 64, device="paras:1")
+        torch_paras.set_memory_limit(torch_paras.memory_allocated(1) + 1024, 1)
+        with pytest.raises(RuntimeError, match="out of memory"):
+            torch.empty(1 << 20, dtype=torch.uint8, device="paras:1")
+    finally:
+        torch_paras.set_memory_limit(0, 1)
+    out = torch.nn.functional.scaled_dot_product_attention(q, q, q, is_causal=True)
+    ref = torch.nn.functional.scaled_dot_product_attention(q.cpu(), q.cpu(), q.cpu(), is_causal=True)
+    assert torch.allclose(out.cpu(), ref, atol=1e-4, rtol=1e-4)

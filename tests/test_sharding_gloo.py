@@ -87,3 +87,45 @@ def test_attention_shard_keeps_gqa_groups_together():
     q8 = torch.zeros(8, 16, 4, 8)
     qs, ks, vs, (kind, lo, hi) = sharding.attention_shard(q8, torch.zeros(8, 4, 4, 8), torch.zeros(8, 4, 4, 8), 3, 8)
     assert kind == "batch" and (lo, hi) == (3, 4) and qs.shape[0] == 1
+
+
+def _leaver(rank, world, port, mode, out_dir):
+    """Step 0: both ranks gather.  Then rank 1 leaves between steps, with nothing in flight.  Rank 0
+    must find that out on the host ("announce") or through the group's timeout ("timeout"), and
+    raise instead of waiting forever."""
+    import datetime
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=4))
+    store = dist.distributed_c10d._get_default_store()
+    x = torch.full((3, 4), float(rank))
+    got = sharding.gather_shards_checked(store, rank, 0, x, [3, 3])
+    assert torch.equal(got[:3], torch.zeros(3, 4)) and torch.equal(got[3:], torch.ones(3, 4))
+    store.set(f"done0/{rank}", "1")
+    if rank == 1:
+        store.wait(["done0/0"])   # rank 0 has its step-0 result too: nothing is in flight any more
+        open(os.path.join(out_dir, "left"), "w").write("left")
+        os._exit(0)           # gone without a word
+    try:
+        if mode == "announce":
+            sharding.gather_shards_checked(store, rank, 1, x, [3, 3], wait_s=1.0)
+        else:
+            sharding.gather_shards(x, [3, 3])     # straight into the collective: the timeout ends it
+    except RuntimeError as e:
+        open(os.path.join(out_dir, "raised"), "w").write(str(e))
+    os._exit(0)               # (destroy_process_group would wait for the dead peer)
+
+
+@pytest.mark.parametrize("mode", ["announce", "timeout"])
+def test_a_rank_that_leaves_is_noticed_on_the_host(mode, tmp_path):
+    ctx = mp.spawn(_leaver, args=(2, _free_port(), mode, str(tmp_path)), nprocs=2, join=False)
+    import time
+    deadline = time.monotonic() + 90
+    while not ctx.join(timeout=5):          # join() returns as each process ends; wait for both
+        assert time.monotonic() < deadline, "a rank is still waiting for the one that left"
+    assert (tmp_path / "left").exists()
+    msg = (tmp_path / "raised").read_text()
+    if mode == "announce":
+        assert "rank(s) [1] did not reach step 1" in msg
+    else:
+        assert msg      # gloo's own error: the peer closed the connection or the wait timed out
