@@ -423,7 +423,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             // Instead the warp reads its 32 rows 128 contiguous bytes at a time (8 lanes per row,
             // 4 rows per instruction), passes them through its 4 KB staging buffer (the one the O
             // store uses at the end of the item) and each lane picks its own row up from there.
-            // A "round" is 128 bytes of every row: 128 / 64 / 32 keys for 1 / 2 / 4-byte masks.
+            // A "slice" is 128 bytes of every row: 128 / 64 / 32 keys for 1 / 2 / 4-byte masks.
             const char* mask_bh = nullptr;
             int64_t mpitch = 0;
             int mesz = 1;
@@ -464,8 +464,8 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                 asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(x.x), "=r"(x.y), "=r"(x.z), "=r"(x.w) : "r"(addr));
                 return x;
             };
-            // round r of the staged mask (already in the staging buffer) joins this lane's scores
-            auto mask_apply_round = [&](uint32_t (&s)[BN], int r) {
+            // slice r of the staged mask (already in the staging buffer) joins this lane's scores
+            auto mask_apply_slice = [&](uint32_t (&s)[BN], int r) {
                 if (p.mask_kind == 1) {
 #pragma unroll
                     for (int v = 0; v < 8; ++v) {
@@ -514,15 +514,15 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                     }
                 }
             };
-            // the rounds after the first: `w` holds round 1, fetched before the wait for S
+            // the slices after the first: `w` holds slice 1, fetched before the wait for S
             auto mask_apply_staged = [&](uint32_t (&s)[BN], int col0, uint4 (&w)[8]) {
-                mask_apply_round(s, 0);
+                mask_apply_slice(s, 0);
                 for (int r = 1; r < mesz; ++r) {
-                    __syncwarp();                       // every lane has read round r-1
+                    __syncwarp();                       // every lane has read slice r-1
                     mask_sts(w);
                     if (r + 1 < mesz) mask_ldg(col0, r + 1, w);
                     __syncwarp();
-                    mask_apply_round(s, r);
+                    mask_apply_slice(s, r);
                 }
                 __syncwarp();
             };
@@ -593,8 +593,8 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                 uint4 mw[8];
                 bool staged = false, early = false;
                 if (MASK) {
-                    // these warps are idle until S arrives: round 0 of this step's mask goes to the staging
-                    // buffer now, round 1 stays in flight across the wait
+                    // these warps are idle until S arrives: slice 0 of this step's mask goes to the staging
+                    // buffer now, slice 1 stays in flight across the wait
                     staged = mfast && (j + 1) * BN <= p.Lk;
                     if (staged) {
                         uint4 w0[8];
