@@ -371,43 +371,41 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             if (ROPE) {
                 // this lane's row of the freshly landed Q tile, rotated in place: 16-byte unit u of row r
                 // sits at u ^ (r & 7) in each 64-column slab; columns d and d + 64 share the offset
-                ok = mbar_wait(bar(kBarQFull + t), ocnt & 1u, abort_flag, 18 + t);
-                if (!ok) break;
+                // The warp rotates its 32 rows four at a time, eight lanes per row: lane l takes
+                // 16-byte unit (l & 7) of row 4g + (l >> 3) in both 64-column slabs.  The table rows
+                // are then read 128 contiguous bytes per row (a lane per row would touch 32 rows
+                // per instruction).  All 32 table loads are issued before the wait for the tile, so
+                // that their latency runs under the tile's own.
+                const int u = lane & 7;
+                const uint32_t tile = smem_base + kSmemQ + t * kTileBytes;
+                uint4 c1[8], s1[8], c2[8], s2[8];
                 {
-                    // The warp rotates its 32 rows four at a time, eight lanes per row: lane l takes
-                    // 16-byte unit (l & 7) of row 4g + (l >> 3) in both 64-column slabs.  The table rows
-                    // are then read 128 contiguous bytes per row (a lane per row would touch 32 rows
-                    // per instruction), and sixteen of those loads are in flight before the first use.
-                    const int u = lane & 7;
-                    const uint32_t tile = smem_base + kSmemQ + t * kTileBytes;
                     const int64_t pos_w = p.rope_pos0 + it.start[t] + wq * 32;
                     const uint4* cs = static_cast<const uint4*>(p.rope_cos);
                     const uint4* sn = static_cast<const uint4*>(p.rope_sin);
-#pragma unroll 1
-                    for (int g0 = 0; g0 < 8; g0 += 4) {
-                        uint4 c1[4], s1[4], c2[4], s2[4];
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            const int rr = 4 * (g0 + i) + (lane >> 3);                 // row within the warp's 32
-                            const bool live = it.start[t] + wq * 32 + rr < p.Lq;
-                            const int64_t trow = live ? (pos_w + rr) * (HD / 8) : 0;   // rows past the end: any valid row
-                            c1[i] = __ldg(cs + trow + u);
-                            s1[i] = __ldg(sn + trow + u);
-                            c2[i] = __ldg(cs + trow + 8 + u);
-                            s2[i] = __ldg(sn + trow + 8 + u);
-                        }
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            const int r = wq * 32 + 4 * (g0 + i) + (lane >> 3);        // row within the tile
-                            const uint32_t addr = tile + r * 128 + uint32_t((u ^ (r & 7)) << 4);
-                            uint4 x1, x2;
-                            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(x1.x), "=r"(x1.y), "=r"(x1.z), "=r"(x1.w) : "r"(addr));
-                            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(x2.x), "=r"(x2.y), "=r"(x2.z), "=r"(x2.w) : "r"(addr + kChunkBytes));
-                            rope_rotate8<BF16>(x1, x2, c1[i], s1[i], c2[i], s2[i]);
-                            st_shared_v4(addr, x1);
-                            st_shared_v4(addr + kChunkBytes, x2);
-                        }
+                    for (int i = 0; i < 8; ++i) {
+                        const int rr = 4 * i + (lane >> 3);                         // row within the warp's 32
+                        const bool live = it.start[t] + wq * 32 + rr < p.Lq;
+                        const int64_t trow = live ? (pos_w + rr) * (HD / 8) : 0;   // rows past the end: any valid row
+                        c1[i] = __ldg(cs + trow + u);
+                        s1[i] = __ldg(sn + trow + u);
+                        c2[i] = __ldg(cs + trow + 8 + u);
+                        s2[i] = __ldg(sn + trow + 8 + u);
                     }
+                }
+                ok = mbar_wait(bar(kBarQFull + t), ocnt & 1u, abort_flag, 18 + t);
+                if (!ok) break;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const int r = wq * 32 + 4 * i + (lane >> 3);        // row within the tile
+                    const uint32_t addr = tile + r * 128 + uint32_t((u ^ (r & 7)) << 4);
+                    uint4 x1, x2;
+                    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(x1.x), "=r"(x1.y), "=r"(x1.z), "=r"(x1.w) : "r"(addr));
+                    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(x2.x), "=r"(x2.y), "=r"(x2.z), "=r"(x2.w) : "r"(addr + kChunkBytes));
+                    rope_rotate8<BF16>(x1, x2, c1[i], s1[i], c2[i], s2[i]);
+                    st_shared_v4(addr, x1);
+                    st_shared_v4(addr + kChunkBytes, x2);
                 }
                 fence_proxy_async_smem();   // generic-proxy stores -> visible to the tensor core's reads
                 __syncwarp();
