@@ -59,8 +59,13 @@ constexpr int kDqKStages = 3, kDqVStages = 2;
 constexpr int kDqSmemK = 2 * kTileBytes;
 constexpr int kDqSmemV = kDqSmemK + kDqKStages * kTileBytes;
 constexpr int kDqSmemBars = kDqSmemV + kDqVStages * kTileBytes;
-constexpr int kDqBarOwnFull = 0, kDqBarOwnEmpty = 1, kDqBarKFull = 2, kDqBarKEmpty = 5, kDqBarVFull = 8,
-              kDqBarVEmpty = 10, kDqBarSFull = 12, kDqBarDpFull = 13, kDqBarTaken = 14, kDqBarDsFull = 15,
+// One "landed" barrier per step for K_j and V_j together (two arrivals, each with its tile's bytes):
+// an issuing thread's wait costs it a few hundred cycles even when the barrier completed long ago,
+// because it is one thread between two busy warps of its scheduler.  Six of them, the least common
+// multiple of the two ring depths, so that a barrier is never re-armed before its step is over.
+constexpr int kDqFullBars = 6;
+constexpr int kDqBarOwnFull = 0, kDqBarOwnEmpty = 1, kDqBarStepFull = 2 /* [6] */, kDqBarKEmpty = 8 /* [3] */,
+              kDqBarVEmpty = 11 /* [2] */, kDqBarDpFull = 13, kDqBarTaken = 14, kDqBarDsFull = 15,
               kDqBarAccFull = 16, kDqBarAccEmpty = 17, kDqBarDsFree = 18 /* [2] */, kDqNumBars = 20;
 constexpr int kDqSmemMisc = kDqSmemBars + kDqNumBars * 8;
 constexpr int kDqSmemDelta = kDqSmemMisc + 16;            // fp32 [128]: delta of the item's rows
@@ -532,7 +537,8 @@ sdpa_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     if (threadIdx.x == 0) {
         for (int i = 0; i < kDqNumBars; ++i) {
             const bool eight = i == kDqBarTaken || i == kDqBarDsFull || i == kDqBarAccEmpty;
-            mbar_init(bar(i), eight ? 8u : 1u);
+            const bool two = i >= kDqBarStepFull && i < kDqBarStepFull + kDqFullBars;
+            mbar_init(bar(i), eight ? 8u : (two ? 2u : 1u));
         }
         *abort_flag = 0;
         mbar_fence_init();
@@ -576,16 +582,17 @@ sdpa_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                     const uint32_t ks = rc % kDqKStages, vs = rc % kDqVStages;
                     ok = mbar_wait(bar(kDqBarKEmpty + ks), ((rc / kDqKStages) & 1u) ^ 1u, abort_flag, 1);
                     if (!ok) break;
-                    mbar_arrive_expect_tx(bar(kDqBarKFull + ks), kLoadBytes);
+                    const uint32_t full = bar(kDqBarStepFull + rc % kDqFullBars);
+                    mbar_arrive_expect_tx(full, kLoadBytes);
 #pragma unroll
                     for (int c = 0; c < kChunks; ++c)
-                        tma_load_4d(smem_base + kDqSmemK + ks * kTileBytes + c * kChunkBytes, &map_k, bar(kDqBarKFull + ks), 64 * c, x * BT, hk, it.b);
+                        tma_load_4d(smem_base + kDqSmemK + ks * kTileBytes + c * kChunkBytes, &map_k, full, 64 * c, x * BT, hk, it.b);
                     ok = mbar_wait(bar(kDqBarVEmpty + vs), ((rc / kDqVStages) & 1u) ^ 1u, abort_flag, 7);
                     if (!ok) break;
-                    mbar_arrive_expect_tx(bar(kDqBarVFull + vs), kLoadBytes);
+                    mbar_arrive_expect_tx(full, kLoadBytes);
 #pragma unroll
                     for (int c = 0; c < kChunks; ++c)
-                        tma_load_4d(smem_base + kDqSmemV + vs * kTileBytes + c * kChunkBytes, &map_v, bar(kDqBarVFull + vs), 64 * c, x * BT, hk, it.b);
+                        tma_load_4d(smem_base + kDqSmemV + vs * kTileBytes + c * kChunkBytes, &map_v, full, 64 * c, x * BT, hk, it.b);
                 }
             }
         }
@@ -618,14 +625,11 @@ sdpa_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 auto v_tile = [&](uint32_t c) { return smem_base + kDqSmemV + (c % kDqVStages) * kTileBytes; };
                 // S = Q K^T and dP = dO V^T of step c; V's stage is free as soon as dP has run
                 auto issue_s_dp = [&](uint32_t c) -> bool {
-                    if (!mbar_wait(bar(kDqBarKFull + c % kDqKStages), (c / kDqKStages) & 1u, abort_flag, 3)) return false;
+                    if (!mbar_wait(bar(kDqBarStepFull + c % kDqFullBars), (c / kDqFullBars) & 1u, abort_flag, 3)) return false;
                     tc_fence_after_sync();
                     issue_t(kColS, own_q, k_tile(c));
-                    tc_commit(bar(kDqBarSFull));
-                    if (!mbar_wait(bar(kDqBarVFull + c % kDqVStages), (c / kDqVStages) & 1u, abort_flag, 8)) return false;
-                    tc_fence_after_sync();
                     issue_t(kColDp, own_do, v_tile(c));
-                    tc_commit(bar(kDqBarDpFull));
+                    tc_commit(bar(kDqBarDpFull));   // covers S too: a commit tracks every MMA this thread has issued
                     tc_commit(bar(kDqBarVEmpty + c % kDqVStages));
                     return true;
                 };
@@ -669,7 +673,7 @@ sdpa_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                         if (!ok) break;
                     }
                     // K_j landed (the first issuer saw that before S; this thread reads the tile too)
-                    ok = mbar_wait(bar(kDqBarKFull + cur % kDqKStages), (cur / kDqKStages) & 1u, abort_flag, 9);
+                    ok = mbar_wait(bar(kDqBarStepFull + cur % kDqFullBars), (cur / kDqFullBars) & 1u, abort_flag, 9);
                     if (!ok) break;
                     tc_fence_after_sync();
                     // dS (16-bit) from TMEM, K_j as [keys x HD] rows
@@ -767,15 +771,13 @@ sdpa_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 if (wg == 0 && live) p.delta[grow] = delta;
             }
             for (int x = 0; x < it.n; ++x, ++rc) {
-                ok = mbar_wait(bar(kDqBarSFull), rc & 1u, abort_flag, 11);
+                // one wait for both products: dP is committed after S by the same thread
+                ok = mbar_wait(bar(kDqBarDpFull), rc & 1u, abort_flag, 12);
                 if (!ok) break;
                 tc_fence_after_sync();
                 uint32_t s[64], dp[64];
                 tmem_ld32(s_addr, reinterpret_cast<uint32_t(&)[32]>(s[0]));
                 tmem_ld32(s_addr + 32, reinterpret_cast<uint32_t(&)[32]>(s[32]));
-                ok = mbar_wait(bar(kDqBarDpFull), rc & 1u, abort_flag, 12);
-                if (!ok) break;
-                tc_fence_after_sync();
                 tmem_ld32(dp_addr, reinterpret_cast<uint32_t(&)[32]>(dp[0]));
                 tmem_ld32(dp_addr + 32, reinterpret_cast<uint32_t(&)[32]>(dp[32]));
                 tmem_wait_ld();
