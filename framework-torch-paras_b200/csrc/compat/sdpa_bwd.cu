@@ -107,12 +107,12 @@ extern "C" int paras_b200_sdpa_bwd(const paras_sdpa_bwd_args* a) {
     const int64_t groups = int64_t(a->B) * a->Hkv;     // (batch, kv head): its r query heads are adjacent
     const int64_t rows = groups * R;
 
-    // Head dim 128 / 64: the fused kernels; their only scratch is delta.
+    // Head dim 128 / 64: the fused kernels; their only scratch is two statistics per query row.
     if (!(a->reserved & PARAS_SDPA_BWD_COMPOSITE) && sdpa_bwd_tc_supported(g, *a)) {
         void* dmem = nullptr;
-        st = paras_b200_malloc_async(a->gpu, size_t(rows) * sizeof(float), s, &dmem);
+        st = paras_b200_malloc_async(a->gpu, sdpa_bwd_tc_scratch_bytes(*a), s, &dmem);
         if (st != PARAS_OK) return st;
-        st = sdpa_bwd_tc_launch(g, *a, static_cast<float*>(dmem), s);   // the dQ kernel fills delta
+        st = sdpa_bwd_tc_launch(g, *a, static_cast<float*>(dmem), s);   // the dQ kernel fills the row statistics
         const int st2 = paras_b200_free_async(a->gpu, dmem, s);
         return st != PARAS_OK ? st : st2;
     }

@@ -76,7 +76,12 @@ struct BwdParams {
     void* dk;
     void* dv;
     const float* lse;     // [B, Hq, Lq]
-    float* delta;         // [B, Hq, Lq]: rowsum(dO o O); written by the dQ kernel, read by the dK/dV kernel
+    // Per-query statistics in the form the dK/dV kernel adds them, [B, Hq, nq * 128] (rows padded to whole
+    // query tiles, so that 128-bit loads need no bounds): nlse2 = -lse * log2(e) (-inf past the last query:
+    // its probabilities are 0) and nds = -delta * scale with delta = rowsum(dO o O) (0 past the last query).
+    // Written by the dQ kernel for the rows of each of its items, read by the dK/dV kernel.
+    float* nlse2;
+    float* nds;
     const void* out;      // the forward's output and its gradient, dense [B, Hq, Lq, D] (for delta)
     const void* dout;
     int B, Hq, Hkv, Lq, Lk;
@@ -172,9 +177,7 @@ constexpr int kDkvHalfChunkBytes = kDkvHalf * 128;    // one 64-column slab of 6
 constexpr int kDkvHalfTileBytes = 2 * kDkvHalfChunkBytes;
 constexpr int kDkvStageBytes = 2 * kDkvHalfTileBytes; // Q half tile, dO half tile
 constexpr int kDkvSmemRing = 2 * kTileBytes;
-constexpr int kDkvSmemStats = kDkvSmemRing + kDkvStages * kDkvStageBytes;   // per stage: -lse2[64], -delta*scale[64]
-constexpr int kDkvStatsBytes = 2 * kDkvHalf * 4;
-constexpr int kDkvSmemBars = kDkvSmemStats + kDkvStages * kDkvStatsBytes;
+constexpr int kDkvSmemBars = kDkvSmemRing + kDkvStages * kDkvStageBytes;
 constexpr int kDkvBarOwnFull = 0, kDkvBarOwnEmpty = 1, kDkvBarRingFull = 2, kDkvBarRingEmpty = 6,
               kDkvBarSFull = 10,    // [2] MMA -> compute: S^T in buffer b
               kDkvBarDpFull = 12,   // [2] MMA -> compute: dP^T in buffer b
@@ -263,19 +266,6 @@ sdpa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                     ok = mbar_wait(bar(kDkvBarRingEmpty + stage), ((rc / kDkvStages) & 1u) ^ 1u, abort_flag, 1);
                 ok = __shfl_sync(0xffffffffu, ok, 0);
                 if (!ok) break;
-                // per-query statistics of this step, in the form the element-wise warps add them:
-                // -lse in the base-2 domain (-inf past the last query: its probabilities are 0) and
-                // -delta * scale
-                float* st = reinterpret_cast<float*>(smem_gen + kDkvSmemStats + stage * kDkvStatsBytes);
-                const int64_t row0 = (int64_t(it.b) * p.Hq + h) * p.Lq;
-#pragma unroll
-                for (int e = 0; e < 2; ++e) {
-                    const int q = q_first + lane * 2 + e;
-                    const bool live = q < p.Lq;
-                    st[lane * 2 + e] = live ? -p.lse[row0 + q] * 1.4426950408889634f : -INFINITY;
-                    st[kDkvHalf + lane * 2 + e] = live ? -p.delta[row0 + q] * p.scale : 0.f;
-                }
-                __syncwarp();
                 if (lane == 0) {
                     const uint32_t full = bar(kDkvBarRingFull + stage);
                     mbar_arrive_expect_tx(full, 2 * kHalfBytes);
@@ -409,18 +399,23 @@ sdpa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             }
             const int i0 = first_query_tile(p, it.t), cnt = 2 * (p.nq - i0);
             const int steps = 2 * it.n;
+            int hh = 0, hx = 0;   // query head of the group and half tile within it (counted, not divided: this loop is the step)
             for (int x = 0; x < steps; ++x, ++rc) {
-                const int hx = x % cnt;
                 const int q0 = (i0 + (hx >> 1)) * BT + (hx & 1) * kDkvHalf + col0;   // first query of this warp's columns
-                const int stage = rc % kDkvStages;
                 const uint32_t b = rc & 1u;
                 const uint32_t s_addr = tmem + lane_base + kColS + 64 * b + col0;
                 const uint32_t dp_addr = tmem + lane_base + kColDp + 64 * b + col0;
-                // (the statistics were written by the load warp before it armed this barrier)
-                ok = mbar_wait(bar(kDkvBarRingFull + stage), (rc / kDkvStages) & 1u, abort_flag, 10);
-                if (!ok) break;
-                const float4* st_lse = reinterpret_cast<const float4*>(smem_gen + kDkvSmemStats + stage * kDkvStatsBytes) + col0 / 4;
-                const float4* st_del = st_lse + kDkvHalf / 4;
+                // The statistics of this warp's 32 queries, straight from the arrays the dQ kernel wrote (every
+                // lane reads the same addresses: one transaction per load); issued before the wait for S^T.
+                float4 st_lse[8], st_del[8];
+                {
+                    const int64_t prow = (int64_t(it.b) * p.Hq + it.h * r + hh) * (int64_t(p.nq) * BT) + q0;
+                    const float4* gl = reinterpret_cast<const float4*>(p.nlse2 + prow);
+                    const float4* gd = reinterpret_cast<const float4*>(p.nds + prow);
+#pragma unroll
+                    for (int v = 0; v < 8; ++v) { st_lse[v] = __ldg(gl + v); st_del[v] = __ldg(gd + v); }
+                }
+                if (++hx == cnt) { hx = 0; ++hh; }
                 ok = mbar_wait(bar(kDkvBarSFull + b), (rc >> 1) & 1u, abort_flag, 11);
                 if (!ok) break;
                 tc_fence_after_sync();
@@ -768,7 +763,11 @@ sdpa_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 }
                 asm volatile("bar.sync 1, 256;" ::: "memory");   // the eight element-wise warps
                 delta = xch[wq * 32 + lane];
-                if (wg == 0 && live) p.delta[grow] = delta;
+                if (wg == 0) {   // every row of the tile, the ones past the end too
+                    const int64_t prow = (int64_t(it.b) * p.Hq + it.h) * (int64_t(p.nq) * BT) + it.t * BT + wq * 32 + lane;
+                    p.nds[prow] = live ? -delta * p.scale : 0.f;
+                    p.nlse2[prow] = nlse2;
+                }
             }
             for (int x = 0; x < it.n; ++x, ++rc) {
                 // one wait for both products: dP is committed after S by the same thread
@@ -867,8 +866,14 @@ bool sdpa_bwd_tc_supported(const Gpu* g, const paras_sdpa_bwd_args& a) {
     return true;
 }
 
-// dq, dk, dv from dense [B, H, L, D] tensors; `delta` is scratch for rowsum(dO o O), fp32 [B, Hq, Lq].
-int sdpa_bwd_tc_launch(Gpu* g, const paras_sdpa_bwd_args& a, float* delta, cudaStream_t s) {
+// Scratch the two kernels share: the two per-query statistics arrays, rows padded to whole query tiles.
+size_t sdpa_bwd_tc_scratch_bytes(const paras_sdpa_bwd_args& a) {
+    const size_t rows = size_t(a.B) * a.Hq * size_t((a.Lq + BT - 1) / BT) * BT;
+    return 2 * rows * sizeof(float);
+}
+
+// dq, dk, dv from dense [B, H, L, D] tensors; `scratch` has sdpa_bwd_tc_scratch_bytes(a) bytes.
+int sdpa_bwd_tc_launch(Gpu* g, const paras_sdpa_bwd_args& a, float* scratch, cudaStream_t s) {
     int st = check_status_word(g);
     if (st != PARAS_OK) return st;
     const int64_t sq[3] = {int64_t(a.Hq) * a.Lq * a.D, int64_t(a.Lq) * a.D, a.D};
@@ -884,7 +889,9 @@ int sdpa_bwd_tc_launch(Gpu* g, const paras_sdpa_bwd_args& a, float* delta, cudaS
     if ((st = make_tensor_map_bhld(&mdo64, a.dout, a.dtype, a.B, a.Hq, a.Lq, a.D, sq, kDkvHalf)) != PARAS_OK) return st;
     BwdParams p{};
     p.dq = a.dq; p.dk = a.dk; p.dv = a.dv;
-    p.lse = a.lse; p.delta = delta; p.out = a.out; p.dout = a.dout;
+    p.lse = a.lse; p.out = a.out; p.dout = a.dout;
+    p.nlse2 = scratch;
+    p.nds = scratch + size_t(a.B) * a.Hq * size_t((a.Lq + BT - 1) / BT) * BT;
     p.B = a.B; p.Hq = a.Hq; p.Hkv = a.Hkv; p.Lq = a.Lq; p.Lk = a.Lk;
     p.causal = a.causal;
     p.scale = float(a.scale);
@@ -905,7 +912,7 @@ int sdpa_bwd_tc_launch(Gpu* g, const paras_sdpa_bwd_args& a, float* delta, cudaS
         return PARAS_OK;
     };
     // dQ: units of paired query tiles per (batch, query head); whole 128-row tiles of q and dO
-    // (it also forms delta, which the dK/dV kernel then reads: this launch comes first)
+    // (it also writes the per-query statistics the dK/dV kernel reads: this launch comes first)
     use_q = &mq;
     use_do = &mdo;
     p.npair = (p.nq + 1) / 2;

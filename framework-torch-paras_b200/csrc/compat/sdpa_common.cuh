@@ -69,6 +69,7 @@ int sdpa_weights_launch(Gpu* g, const paras_sdpa_args& a, float scale, cudaStrea
 
 // Fused tcgen05 attention backward (sdpa_bwd_tc.cu): 16-bit, D == 128 or 64, dense tensors.
 bool sdpa_bwd_tc_supported(const Gpu* g, const paras_sdpa_bwd_args& a);
-int sdpa_bwd_tc_launch(Gpu* g, const paras_sdpa_bwd_args& a, float* delta, cudaStream_t s);
+size_t sdpa_bwd_tc_scratch_bytes(const paras_sdpa_bwd_args& a);
+int sdpa_bwd_tc_launch(Gpu* g, const paras_sdpa_bwd_args& a, float* scratch, cudaStream_t s);
 
 }  // namespace pb
