@@ -206,3 +206,20 @@ def test_functional_ops_with_requires_grad_give_gradients_not_silence():
     for got, want, name in ((ad.grad, ar.grad, "dx"), (wld.grad, wlr.grad, "dw"), (bld.grad, blr.grad, "db")):
         err = (got.cpu().double() - want).abs().max().item()
         assert err <= 2e-2 * max(1.0, want.abs().max().item()), f"linear {name}: {err}"
+
+
+def test_fused_backward_is_deterministic_and_leaves_inputs_alone():
+    # no atomics and one owner per accumulator: two runs give the same bits, with other work in between
+    g = torch.Generator().manual_seed(77)
+    B, Hq, Hkv, L, D = 2, 8, 2, 700, 128
+    q, k, v, do = (torch.randn(B, h, L, D, generator=g).bfloat16().to(CUDA) for h in (Hq, Hkv, Hkv, Hq))
+    o, lse = abi.sdpa_fwd(q, k, v, causal=True, return_lse=True)
+    keep = [t.clone() for t in (q, k, v, do, o, lse)]
+    first = abi.sdpa_bwd(do, q, k, v, o, lse, causal=True)
+    abi.sdpa_fwd(k, k, v, causal=False)                       # other kernels reuse TMEM and the pool's scratch
+    abi.sdpa_bwd(do.flip(0), q, k, v, o, lse, causal=True)
+    second = abi.sdpa_bwd(do, q, k, v, o, lse, causal=True)
+    for a, b, name in zip(first, second, ("dq", "dk", "dv")):
+        assert torch.equal(a, b), f"{name} differs between two runs"
+    for a, b in zip(keep, (q, k, v, do, o, lse)):
+        assert torch.equal(a, b)
