@@ -33,6 +33,8 @@ int validate(const paras_sdpa_args* a) {
     return PARAS_OK;
 }
 
+}  // namespace
+
 float effective_scale(const paras_sdpa_args& a) {
     double sc = a.scale;
     if (a.flags & PARAS_SDPA_REF_SCALE) {
@@ -44,6 +46,8 @@ float effective_scale(const paras_sdpa_args& a) {
     }
     return float(sc);
 }
+
+namespace {
 
 enum class Path { Tensor, Decode, Simt };
 

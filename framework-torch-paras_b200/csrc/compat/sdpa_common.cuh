@@ -67,6 +67,25 @@ int sdpa_decode_launch(Gpu* g, const paras_sdpa_args& a, float scale, const Spli
 bool sdpa_wants_weights(const paras_sdpa_args& a);
 int sdpa_weights_launch(Gpu* g, const paras_sdpa_args& a, float scale, cudaStream_t s);
 
+// Philox2x32 with 10 rounds, key schedule and counter layout of csrc/ops/random_ops.cpp:27-47.
+__device__ __forceinline__ uint32_t philox2x32_r0(uint64_t seed, uint64_t sequence, uint64_t idx) {
+    uint32_t c0 = uint32_t(idx);
+    uint32_t c1 = uint32_t(sequence + (idx >> 32));
+    uint32_t k0 = uint32_t(seed);
+#pragma unroll
+    for (int i = 0; i < 10; ++i) {
+        const uint64_t prod = uint64_t(0xD256D193u) * c0;
+        const uint32_t n0 = uint32_t(prod >> 32) ^ k0 ^ c1;
+        c1 = uint32_t(prod);
+        c0 = n0;
+        k0 += 0x9E3779B9u;
+    }
+    return c0;
+}
+
+// The softmax scale as the kernels use it (rounded to the tensors' dtype with PARAS_SDPA_REF_SCALE).
+float effective_scale(const paras_sdpa_args& a);
+
 // Fused tcgen05 attention backward (sdpa_bwd_tc.cu): 16-bit, D == 128 or 64, dense tensors.
 bool sdpa_bwd_tc_supported(const Gpu* g, const paras_sdpa_bwd_args& a);
 size_t sdpa_bwd_tc_scratch_bytes(const paras_sdpa_bwd_args& a);

@@ -22,22 +22,6 @@ namespace {
 constexpr int kRowsPerBlock = 4;
 constexpr int kMaxD = 256;
 
-// Philox2x32 with 10 rounds, key schedule and counter layout of csrc/ops/random_ops.cpp:27-47.
-__device__ __forceinline__ uint32_t philox2x32_r0(uint64_t seed, uint64_t sequence, uint64_t idx) {
-    uint32_t c0 = uint32_t(idx);
-    uint32_t c1 = uint32_t(sequence + (idx >> 32));
-    uint32_t k0 = uint32_t(seed);
-#pragma unroll
-    for (int i = 0; i < 10; ++i) {
-        const uint64_t prod = uint64_t(0xD256D193u) * c0;
-        const uint32_t n0 = uint32_t(prod >> 32) ^ k0 ^ c1;
-        c1 = uint32_t(prod);
-        c0 = n0;
-        k0 += 0x9E3779B9u;
-    }
-    return c0;
-}
-
 struct WeightsParams {
     const void* q;
     const void* k;

@@ -47,10 +47,25 @@ bool ref_scale_rounding() {
 // Largest attention-weights tensor the math op will materialise (elements): 2^28 = 512 MB in 16 bit.
 constexpr int64_t kMaxWeightsElements = int64_t(1) << 28;
 
+// The Philox (seed, sequence) pair of one dropout draw.
+using RngState = std::pair<uint64_t, uint64_t>;
+
+// What a general gradient call adds to the forward's arguments: the output's gradient in, the three
+// gradients out, and the dropout draw of the forward it differentiates.
+struct GradRequest {
+    const Tensor* grad_out;
+    const RngState* rng;
+    Tensor dq, dk, dv;
+};
+
+// Validates and lays out one attention call.  Without `grad` it runs the forward (drawing dropout
+// counters when it needs them; `rng_used` receives them); with `grad` it runs the general backward of
+// exactly that call instead and returns an undefined tensor.
 Tensor sdpa_forward(const Tensor& query, const Tensor& key, const Tensor& value,
                     const std::optional<Tensor>& attn_mask, double dropout_p, bool is_causal,
                     std::optional<double> scale, bool enable_gqa,
-                    const std::optional<Tensor>& dropout_mask = std::nullopt, Tensor* weights = nullptr) {
+                    const std::optional<Tensor>& dropout_mask = std::nullopt, Tensor* weights = nullptr,
+                    RngState* rng_used = nullptr, GradRequest* grad = nullptr) {
     TORCH_CHECK(query.dim() >= 3 && key.dim() >= 3 && value.dim() >= 3,
                 "paras sdpa: query/key/value must be at least 3-D (..., seq, head_dim)");
     const bool has_mask = attn_mask.has_value() && attn_mask->defined();
@@ -82,13 +97,13 @@ Tensor sdpa_forward(const Tensor& query, const Tensor& key, const Tensor& value,
                     "paras sdpa: query heads must be a multiple of key/value heads for enable_gqa");
     }
     c10::DeviceGuard guard(query.device());
-    Tensor out = at::empty({B, Hq, Lq, E}, q.options());
+    Tensor out = grad ? Tensor() : at::empty({B, Hq, Lq, E}, q.options());
 
     paras_sdpa_args a{};
     a.q = q.data_ptr();
     a.k = k.data_ptr();
     a.v = v.data_ptr();
-    a.out = out.data_ptr();
+    a.out = grad ? nullptr : out.data_ptr();
     a.dtype = dt;
     a.B = int32_t(B); a.Hq = int32_t(Hq); a.Hkv = int32_t(Hkv);
     a.Lq = int32_t(Lq); a.Lk = int32_t(Lk); a.D = int32_t(E);
@@ -96,7 +111,7 @@ Tensor sdpa_forward(const Tensor& query, const Tensor& key, const Tensor& value,
         a.q_strides[i] = q.stride(i);
         a.k_strides[i] = k.stride(i);
         a.v_strides[i] = v.stride(i);
-        a.o_strides[i] = out.stride(i);
+        a.o_strides[i] = grad ? 0 : out.stride(i);
     }
     Tensor mask;  // keeps a converted mask alive until the launch is queued
     if (has_mask) {
@@ -126,7 +141,7 @@ Tensor sdpa_forward(const Tensor& query, const Tensor& key, const Tensor& value,
     a.gpu = gpu;
     a.stream = nullptr;
     Tensor dmask;   // keeps a converted dropout mask alive until the launch is queued
-    if (dropout_p > 0.0 && Lk > 0 && out.numel() > 0) {
+    if (dropout_p > 0.0 && Lk > 0 && B * Hq * Lq * E > 0) {
         a.dropout_p = dropout_p;
         if (dropout_mask.has_value() && dropout_mask->defined()) {
             dmask = *dropout_mask;
@@ -145,10 +160,24 @@ Tensor sdpa_forward(const Tensor& query, const Tensor& key, const Tensor& value,
             for (int i = 0; i < 4; ++i) a.dropout_mask_strides[i] = dmask.stride(i);
         } else {
             // the counters the reference's native_dropout would draw for its [B,Hq,Lq,Lk] weights
-            const auto state = rt.rng_draw(int(query.device().index()), B * Hq * Lq * Lk);
+            const RngState state = grad ? *grad->rng : rt.rng_draw(int(query.device().index()), B * Hq * Lq * Lk);
             a.rng_seed = state.first;
             a.rng_sequence = state.second;
+            if (rng_used) *rng_used = state;
         }
+    }
+    if (grad) {
+        TORCH_CHECK(grad->grad_out->sizes() == query.sizes(), "paras sdpa backward: the output's gradient has shape ",
+                    grad->grad_out->sizes(), ", the output ", query.sizes());
+        Tensor go = as_bhle(grad->grad_out->to(query.scalar_type()));
+        Tensor dq = at::empty({B, Hq, Lq, E}, q.options()), dk = at::empty({B, Hkv, Lk, E}, q.options()),
+               dv = at::empty({B, Hkv, Lk, E}, q.options());
+        const int64_t gs[3] = {go.stride(0), go.stride(1), go.stride(2)};
+        PARAS_ABI(paras_b200_sdpa_bwd_general(&a, go.data_ptr(), gs, dq.data_ptr(), dk.data_ptr(), dv.data_ptr()));
+        grad->dq = dq.reshape(query.sizes());
+        grad->dk = dk.reshape(key.sizes());
+        grad->dv = dv.reshape(value.sizes());
+        return Tensor();
     }
     if (weights) {
         TORCH_CHECK(B * Hq * Lq * Lk <= kMaxWeightsElements,
@@ -361,6 +390,46 @@ struct SdpaFunction : public torch::autograd::Function<SdpaFunction> {
     }
 };
 
+// Everything the fused pair does not take (an attn_mask, dropout, fp32, other head dims): the forward
+// the operator would run anyway, and the CUDA-core backward of exactly that call, with the forward's
+// dropout counters replayed.
+struct SdpaGeneralFunction : public torch::autograd::Function<SdpaGeneralFunction> {
+    static Tensor forward(torch::autograd::AutogradContext* ctx, const Tensor& q, const Tensor& k, const Tensor& v,
+                          const std::optional<Tensor>& mask, double dropout_p, bool is_causal,
+                          std::optional<double> scale, bool enable_gqa) {
+        RngState rng{0, 0};
+        const bool has_mask = mask.has_value() && mask->defined();
+        Tensor out = sdpa_forward(q, k, v, mask, dropout_p, is_causal, scale, enable_gqa, std::nullopt, nullptr, &rng);
+        if (has_mask) ctx->save_for_backward({q, k, v, *mask});
+        else ctx->save_for_backward({q, k, v});
+        ctx->saved_data["has_mask"] = has_mask;
+        ctx->saved_data["dropout_p"] = dropout_p;
+        ctx->saved_data["is_causal"] = is_causal;
+        ctx->saved_data["has_scale"] = scale.has_value();
+        ctx->saved_data["scale"] = scale.value_or(0.0);
+        ctx->saved_data["enable_gqa"] = enable_gqa;
+        ctx->saved_data["seed"] = static_cast<int64_t>(rng.first);
+        ctx->saved_data["sequence"] = static_cast<int64_t>(rng.second);
+        return out;
+    }
+    static torch::autograd::variable_list backward(torch::autograd::AutogradContext* ctx,
+                                                   torch::autograd::variable_list grads) {
+        const auto saved = ctx->get_saved_variables();
+        std::optional<double> scale;
+        if (ctx->saved_data["has_scale"].toBool()) scale = ctx->saved_data["scale"].toDouble();
+        std::optional<Tensor> m;
+        if (ctx->saved_data["has_mask"].toBool()) m = saved[3];
+        const RngState rng{static_cast<uint64_t>(ctx->saved_data["seed"].toInt()),
+                           static_cast<uint64_t>(ctx->saved_data["sequence"].toInt())};
+        Tensor go = grads[0].contiguous();
+        GradRequest req{&go, &rng, Tensor(), Tensor(), Tensor()};
+        sdpa_forward(saved[0], saved[1], saved[2], m, ctx->saved_data["dropout_p"].toDouble(),
+                     ctx->saved_data["is_causal"].toBool(), scale, ctx->saved_data["enable_gqa"].toBool(),
+                     std::nullopt, nullptr, nullptr, &req);
+        return {req.dq, req.dk, req.dv, Tensor(), Tensor(), Tensor(), Tensor(), Tensor()};
+    }
+};
+
 Tensor sdpa_autograd(const Tensor& query, const Tensor& key, const Tensor& value,
                      const std::optional<Tensor>& attn_mask, double dropout_p, bool is_causal,
                      std::optional<double> scale, bool enable_gqa) {
@@ -372,14 +441,17 @@ Tensor sdpa_autograd(const Tensor& query, const Tensor& key, const Tensor& value
                                                 enable_gqa);
     }
     const bool has_mask = attn_mask.has_value() && attn_mask->defined();
-    TORCH_CHECK(!has_mask && dropout_p == 0.0,
-                "paras sdpa: the gradient of the fused attention covers is_causal / full attention without "
-                "attn_mask and dropout; detach the inputs or drop the mask");
-    TORCH_CHECK(query.scalar_type() == c10::kBFloat16 || query.scalar_type() == c10::kHalf,
-                "paras sdpa: the gradient of the fused attention needs bfloat16 or float16 tensors, got ",
-                query.scalar_type());
     TORCH_CHECK(query.dim() >= 3 && key.dim() == query.dim() && value.dim() == query.dim(),
                 "paras sdpa: query, key and value must have the same rank (>= 3)");
+    // the fused kernels: 16-bit, no mask tensor, no dropout, head dim 128 / 64 (or, on the composite of
+    // GEMMs, 16-byte rows of both the head dim and the key length)
+    const int64_t E = query.size(-1), Lk = key.size(-2);
+    const bool half = query.scalar_type() == c10::kBFloat16 || query.scalar_type() == c10::kHalf;
+    const bool fused = !has_mask && dropout_p == 0.0 && half && E % 8 == 0 && (E == 128 || E == 64 || Lk % 8 == 0) &&
+                       query.numel() > 0 && key.numel() > 0;
+    if (!fused)
+        return SdpaGeneralFunction::apply(query, key, value, has_mask ? attn_mask : std::optional<Tensor>(), dropout_p,
+                                          is_causal, scale, enable_gqa);
     Tensor q = query, k = key, v = value;
     if (q.dim() == 3) { q = q.unsqueeze(1); k = k.unsqueeze(1); v = v.unsqueeze(1); }
     else if (q.dim() > 4) {

@@ -37,6 +37,7 @@ EXPORTS = [
     "paras_b200_rotate_half", "paras_b200_gemm", "paras_b200_sdpa_fwd_host", "paras_b200_sdpa_bwd",
     "paras_b200_sdpa_split_layout", "paras_b200_selftest_bounded_wait",
     "paras_b200_rms_rstd", "paras_b200_scale_columns", "paras_b200_sdpa_rope_fwd", "paras_b200_rope",
+    "paras_b200_sdpa_bwd_general",
 ]
 
 
@@ -242,6 +243,35 @@ def sdpa_fwd(q, k, v, *, causal=False, scale=None, mask=None, return_lse=False, 
     check(lib().paras_b200_sdpa_fwd(C.byref(a)))
     res = (out,) + ((lse,) if return_lse else ()) + ((weights,) if return_weights else ())
     return res if len(res) > 1 else out
+
+
+def sdpa_bwd_general(dout, q, k, v, *, causal=False, scale=None, mask=None, flags=0, stream=None,
+                     dropout_p=0.0, rng=None, dropout_mask=None):
+    """(dq, dk, dv) through ``paras_b200_sdpa_bwd_general``: the gradient of ``sdpa_fwd`` called with the
+    same arguments (mask, dropout with the same ``rng`` or ``dropout_mask``), any dtype, any head dim."""
+    if dout.dim() != 4 or (dout.size(-1) > 1 and dout.stride(-1) != 1):
+        raise RuntimeError("paras abi: dout must be [B,H,L,D] with a contiguous last dim")
+    dq, dk, dv = torch.empty(q.shape, dtype=q.dtype, device=q.device), torch.empty(k.shape, dtype=k.dtype, device=k.device), \
+        torch.empty(v.shape, dtype=v.dtype, device=v.device)
+    a = sdpa_args(q, k, v, dq, causal=causal, scale=scale, mask=mask, flags=flags, stream=stream)
+    a.dropout_p = float(dropout_p)
+    if rng is not None:
+        a.rng_seed, a.rng_sequence = int(rng[0]), int(rng[1])
+    if dropout_mask is not None:
+        m = dropout_mask
+        while m.dim() < 4:
+            m = m.unsqueeze(0)
+        m = m.expand(q.shape[0], q.shape[1], q.shape[2], k.shape[2])
+        a.dropout_mask = m.data_ptr()
+        a.dropout_mask_kind = 1 if m.dtype == torch.bool else (2 if m.dtype == q.dtype else 3)
+        for i in range(4):
+            a.dropout_mask_strides[i] = m.stride(i)
+        a._keep_dm = m
+    st = (C.c_int64 * 3)(dout.stride(0), dout.stride(1), dout.stride(2))
+    L = lib()
+    L.paras_b200_sdpa_bwd_general.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
+    check(L.paras_b200_sdpa_bwd_general(C.byref(a), dout.data_ptr(), st, dq.data_ptr(), dk.data_ptr(), dv.data_ptr()))
+    return dq, dk, dv
 
 
 def sdpa_rope_fwd(q, k, v, cos, sin, *, causal=False, scale=None, q_pos0=0, flags=0, out=None, stream=None):

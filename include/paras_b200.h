@@ -297,6 +297,17 @@ typedef struct paras_sdpa_bwd_args {
 } paras_sdpa_bwd_args;
 int paras_b200_sdpa_bwd(const paras_sdpa_bwd_args* args);
 
+/* Attention gradients for the cases the reference reaches by autograd through its composite
+ * (attention_ops.cpp:71-136: mask, softmax, dropout, product with V) and paras_b200_sdpa_bwd does not
+ * take: an explicit attn_mask, dropout (the same rng_seed / rng_sequence or dropout_mask as the forward
+ * call), fp32 tensors, any head dim up to 256, strided q / k / v.  `fwd` is the argument block of the
+ * forward call (its `out`, `lse`, `attn_out` and workspace fields are ignored); `dout` is [B, Hq, Lq, D]
+ * with element strides dout_strides[3] and unit stride on D; dq, dk, dv are dense [B, H, L, D] in the
+ * tensors' dtype.  A CUDA-core path that accumulates dk and dv with atomic adds in fp32: slow, and not
+ * bit-reproducible run to run. */
+int paras_b200_sdpa_bwd_general(const paras_sdpa_args* fwd, const void* dout, const int64_t* dout_strides,
+                                void* dq, void* dk, void* dv);
+
 /* ---- 16-bit GEMM (the projections either side of the path) ----
  * Replaces the host round trip of mm / bmm / addmm / linear (csrc/ops/vision_ops.cpp:248-309,
  * 388-423: both operands copied to the host, at::mm / at::bmm / at::addmm / at::linear in

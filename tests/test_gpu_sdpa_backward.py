@@ -169,12 +169,35 @@ def test_functional_ops_with_requires_grad_give_gradients_not_silence():
     with torch.no_grad():
         plain = F.scaled_dot_product_attention(qd, kd, vd, is_causal=True, enable_gqa=True)
     assert plain.grad_fn is None and torch.equal(plain.cpu(), out.detach().cpu())
-    # what the gradient does not cover raises instead of returning a result without grad_fn
-    with pytest.raises(RuntimeError, match="gradient of the fused attention"):
-        F.scaled_dot_product_attention(qd.float(), kd.float().repeat_interleave(2, 1),
-                                       vd.float().repeat_interleave(2, 1))
-    with pytest.raises(RuntimeError, match="gradient of the fused attention"):
-        F.scaled_dot_product_attention(qd, qd, qd, attn_mask=torch.ones(256, 256, dtype=torch.bool).to(DEV))
+    # what the fused kernels do not take (fp32, a mask tensor, dropout, 3-D inputs) goes to the general
+    # backward, never to a result without grad_fn: checked against CPU autograd on the same inputs
+    g2 = torch.Generator().manual_seed(48)
+    q3, k3, v3, d3 = (torch.randn(3, 50, 32, generator=g2) for _ in range(4))          # 3-D fp32, as the reference's tests
+    pad = torch.ones(3, 50, 50, dtype=torch.bool)
+    pad[:, :, 40:] = False                                                                # per-batch key padding
+    cq, ck, cv = (t.clone().requires_grad_(True) for t in (q3, k3, v3))
+    F.scaled_dot_product_attention(cq, ck, cv, attn_mask=pad).backward(d3)
+    dq3, dk3, dv3 = (t.to(DEV).requires_grad_(True) for t in (q3, k3, v3))
+    o3 = F.scaled_dot_product_attention(dq3, dk3, dv3, attn_mask=pad.to(DEV))
+    assert o3.grad_fn is not None
+    o3.backward(d3.to(DEV))
+    for got, want, name in ((dq3.grad, cq.grad, "dq"), (dk3.grad, ck.grad, "dk"), (dv3.grad, cv.grad, "dv")):
+        assert got.shape == want.shape
+        assert torch.allclose(got.cpu(), want, atol=1e-4, rtol=1e-4), f"masked fp32 3-D {name}"
+    # dropout: the backward replays the forward's draw -- dv = wd^T dO is linear in dO with the same weights
+    torch_paras.manual_seed(5)
+    qh, kh, vh = (torch.randn(1, 2, 64, 64, generator=g2).bfloat16().to(DEV).requires_grad_(True) for _ in range(3))
+    od = F.scaled_dot_product_attention(qh, kh, vh, dropout_p=0.5)
+    assert od.grad_fn is not None
+    od.backward(torch.ones_like(od))
+    assert torch.isfinite(qh.grad.float()).all() and vh.grad.float().abs().sum().item() > 0
+    # column sums of the dropped weights: dv[j, :] = sum_i wd[i, j] for dO = 1; the forward's output row sums
+    # give sum_j wd[i, j] v[j, :]; both come from the same wd, so sum_j dv[j, 0] * 1 == sum_i rowsum(wd[i])
+    with torch.no_grad():
+        torch_paras.manual_seed(5)
+        ones_v = torch.ones_like(vh)
+        rows = F.scaled_dot_product_attention(qh, kh, ones_v, dropout_p=0.5)              # = rowsum(wd), same draw
+    assert abs(vh.grad[..., 0].float().sum().item() - rows[..., 0].float().sum().item()) <= 0.02 * rows[..., 0].numel()
 
     # rms_norm: fp32 (the reference's own test dtype) against CPU autograd
     x = torch.randn(6, 5, 32, generator=g)
@@ -223,3 +246,58 @@ def test_fused_backward_is_deterministic_and_leaves_inputs_alone():
         assert torch.equal(a, b), f"{name} differs between two runs"
     for a, b in zip(keep, (q, k, v, do, o, lse)):
         assert torch.equal(a, b)
+
+
+def _float64_grads(q, k, v, dout, *, causal=False, mask=None, keep=None):
+    """Gradients of float64 attention on the same inputs; `keep` multiplies the weights (dropout)."""
+    q64, k64, v64 = (t.double().requires_grad_(True) for t in (q, k, v))
+    r = q.shape[1] // k.shape[1]
+    kk, vv = k64.repeat_interleave(r, 1), v64.repeat_interleave(r, 1)
+    s = (q64 @ kk.transpose(-1, -2)) / math.sqrt(q.shape[-1])
+    if causal:
+        s = s.masked_fill(~torch.ones(q.shape[2], k.shape[2], dtype=torch.bool).tril(), float("-inf"))
+    if mask is not None:
+        s = s.masked_fill(~mask, float("-inf")) if mask.dtype == torch.bool else s + mask.double()
+    w = torch.softmax(s, -1)
+    if keep is not None:
+        w = w * keep.double()
+    (w @ vv).backward(dout.double())
+    return q64.grad, k64.grad, v64.grad
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("kind", ["bool_mask", "additive_mask", "causal_odd_dim", "dropout_mask", "philox"])
+def test_general_backward_covers_masks_dropout_and_fp32(kind, dtype):
+    # the cases the fused kernels do not take, on the CUDA-core path (paras_b200_sdpa_bwd_general)
+    g = torch.Generator().manual_seed(91)
+    B, Hq, Hkv, Lq, Lk, D = 2, 4, 2, 70, 90, 40 if kind == "causal_odd_dim" else 64
+    q, k, v, do = (torch.randn(B, h, L, D, generator=g).to(dtype) for h, L in ((Hq, Lq), (Hkv, Lk), (Hkv, Lk), (Hq, Lq)))
+    kw, ref_kw = {}, {}
+    if kind == "bool_mask":
+        m = torch.rand(B, 1, Lq, Lk, generator=g) > 0.3
+        m[..., 0] = True
+        kw["mask"], ref_kw["mask"] = m.to(CUDA), m
+    elif kind == "additive_mask":
+        m = torch.randn(Lq, Lk, generator=g).to(dtype)
+        kw["mask"], ref_kw["mask"] = m.to(CUDA), m
+    elif kind == "causal_odd_dim":
+        kw["causal"] = ref_kw["causal"] = True
+    elif kind == "dropout_mask":
+        dm = (torch.rand(B, Hq, Lq, Lk, generator=g) > 0.4).to(dtype)
+        kw.update(dropout_p=0.25, dropout_mask=dm.to(CUDA))
+        one_minus_p = float(torch.tensor(0.75).to(dtype))
+        ref_kw["keep"] = dm.double() / one_minus_p
+    else:
+        # the forward's Philox draws, rebuilt on the host by the oracle (random_ops.cpp:27-47, 140-176)
+        from oracle import oracle as O
+        kw.update(dropout_p=0.2, rng=(1234, 7))
+        import numpy as np
+        r0 = O.philox2x32_r0(1234, 7, B * Hq * Lq * Lk)
+        u = (r0 >> np.uint32(8)).astype(np.float32) * np.float32(1.0 / 16777216.0)
+        keep = torch.from_numpy(u < np.float32(1.0 - 0.2)).reshape(B, Hq, Lq, Lk)
+        ref_kw["keep"] = keep.double() * float(np.float32(1.0) / np.float32(1.0 - 0.2))
+    got = abi.sdpa_bwd_general(do.to(CUDA), q.to(CUDA), k.to(CUDA), v.to(CUDA), **kw)
+    want = _float64_grads(q, k, v, do, **ref_kw)
+    c = 1e-4 if dtype == torch.float32 else 8e-3
+    for a, b, name in zip(got, want, ("dq", "dk", "dv")):
+        check(a, b, f"general {kind} {dtype} {name}", c=c, mean_c=c / 8)
