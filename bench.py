@@ -404,7 +404,14 @@ def run_ours(args):
             t = loop_ms(lambda: abi.rmsnorm_fwd(x, w, 1e-6, out=y, mode=mode), esteps)
             gbs = nbytes / (t * 1e-3) / 1e9
             extra[key] = {"ms": t, "gbs": gbs, "frac_of_hbm_peak": gbs / peaks["hbm_gbs"], "bytes": nbytes}
-        del x, y
+        # its backward (grad_x and grad_weight in one pass over grad_out and x): bytes = 3*rows*H*2
+        _, rstd_ = abi.rmsnorm_fwd(x, w, 1e-6, out=y, return_rstd=True)
+        go_ = gen((16384, 4096), 26)
+        t = loop_ms(lambda: abi.rmsnorm_bwd(go_, x, w, rstd_), esteps)
+        nb = 3 * x.numel() * 2
+        extra["rmsnorm_backward_16384x4096"] = {"ms": t, "gbs": nb / (t * 1e-3) / 1e9,
+                                                "frac_of_hbm_peak": nb / (t * 1e-3) / 1e9 / peaks["hbm_gbs"], "bytes": nb}
+        del x, y, go_, rstd_
 
     if want("swiglu"):
         # SwiGLU, config 3 shape: bytes = 3*n*2
@@ -416,6 +423,11 @@ def run_ours(args):
         gbs = nbytes / (t * 1e-3) / 1e9
         extra[f"swiglu_{srows}x14336"] = {"ms": t, "gbs": gbs, "frac_of_hbm_peak": gbs / peaks["hbm_gbs"],
                                        "bytes": nbytes}
+        # its backward: three tensors read, two written
+        t = loop_ms(lambda: abi.swiglu_bwd(so, gate, up), esteps)
+        nb = 5 * gate.numel() * 2
+        extra[f"swiglu_backward_{srows}x14336"] = {"ms": t, "gbs": nb / (t * 1e-3) / 1e9,
+                                                   "frac_of_hbm_peak": nb / (t * 1e-3) / 1e9 / peaks["hbm_gbs"], "bytes": nb}
         del gate, up, so
 
     if want("gqa"):

@@ -399,6 +399,95 @@ rmsnorm_bwd_dw_kernel(const T* __restrict__ go, const T* __restrict__ x,
     }
 }
 
+// Both gradients in one pass over grad_out and x (fused_ops.cpp:111-155): a CTA of THREADS threads takes
+// whole rows, V 16-byte vectors per thread and tensor, so that a row's grad_out and x stay in registers
+// between the row's dot product and its grad_x; each thread also keeps grad_weight partial sums for
+// the columns it owns over all the rows its CTA walks.  The partials go to [gridDim.x, H] fp32 scratch
+// that rmsnorm_bwd_dw_reduce_kernel sums (in double) and rounds.  HBM traffic: grad_out, x read once,
+// grad_x written once.
+template <typename T, int V, int THREADS>
+__global__ void __launch_bounds__(THREADS)
+rmsnorm_bwd_rows_kernel(const T* __restrict__ go, const T* __restrict__ x, const T* __restrict__ w,
+                        const float* __restrict__ rstd, T* __restrict__ gx, float* __restrict__ dw_part,
+                        int64_t rows, int64_t H) {
+    constexpr int N = Vec16<T>::N;
+    __shared__ float red[2][THREADS / 32];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    Vec16<T> wv[V];
+#pragma unroll
+    for (int i = 0; i < V; ++i) wv[i] = ld16(w + (int64_t(tid) + int64_t(THREADS) * i) * N);
+    float dwacc[V * N];
+#pragma unroll
+    for (int i = 0; i < V * N; ++i) dwacc[i] = 0.f;
+    const float inv_h = 1.0f / float(H);
+    int flip = 0;
+    for (int64_t row = blockIdx.x; row < rows; row += gridDim.x, flip ^= 1) {
+        const T* gr = go + row * H;
+        const T* xr = x + row * H;
+        const float rr = rstd[row];   // asked for with the row: after the reduction it would be a round trip of its own
+        Vec16<T> gv[V], xv[V];
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+            gv[i] = ld16_stream(gr + (int64_t(tid) + int64_t(THREADS) * i) * N);
+            xv[i] = ld16_stream(xr + (int64_t(tid) + int64_t(THREADS) * i) * N);
+        }
+        float dot = 0.f;
+#pragma unroll
+        for (int i = 0; i < V; ++i)
+#pragma unroll
+            for (int e = 0; e < N; ++e)
+                dot = fmaf(to_f32<T>(gv[i].v[e]) * to_f32<T>(wv[i].v[e]), to_f32<T>(xv[i].v[e]), dot);
+        dot = warp_sum(dot);
+        if (lane == 0) red[flip][warp] = dot;
+        __syncthreads();          // (the buffer alternates: the next row's writes cannot overtake these reads)
+        dot = 0.f;
+#pragma unroll
+        for (int i = 0; i < THREADS / 32; ++i) dot += red[flip][i];
+        const float coef = rr * rr * rr * inv_h * dot;
+        T* out = gx + row * H;
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+            Vec16<T> o;
+#pragma unroll
+            for (int e = 0; e < N; ++e) {
+                const float g = to_f32<T>(gv[i].v[e]), xe = to_f32<T>(xv[i].v[e]);
+                o.v[e] = from_f32<T>(fmaf(g * to_f32<T>(wv[i].v[e]), rr, -coef * xe));
+                dwacc[i * N + e] = fmaf(g * xe, rr, dwacc[i * N + e]);
+            }
+            st16_stream(out + (int64_t(tid) + int64_t(THREADS) * i) * N, o);
+        }
+    }
+    float* part = dw_part + int64_t(blockIdx.x) * H;
+#pragma unroll
+    for (int i = 0; i < V; ++i)
+#pragma unroll
+        for (int e = 0; e < N; e += 4)
+            *reinterpret_cast<float4*>(part + (int64_t(tid) + int64_t(THREADS) * i) * N + e) =
+                make_float4(dwacc[i * N + e], dwacc[i * N + e + 1], dwacc[i * N + e + 2], dwacc[i * N + e + 3]);
+}
+
+// grad_weight[j] = sum over the partial rows: 16 threads per column take every sixteenth partial.
+template <typename T>
+__global__ void __launch_bounds__(1024)
+rmsnorm_bwd_dw_reduce_kernel(const float* __restrict__ dw_part, T* __restrict__ gw, int parts, int64_t H) {
+    __shared__ double sh[16][64];
+    const int cx = threadIdx.x & 63, py = threadIdx.x >> 6;
+    const int64_t col = int64_t(blockIdx.x) * 64 + cx;
+    double acc = 0.0;
+    if (col < H) {
+#pragma unroll 4
+        for (int pi = py; pi < parts; pi += 16) acc += double(__ldcs(dw_part + int64_t(pi) * H + col));
+    }
+    sh[py][cx] = acc;
+    __syncthreads();
+    if (py == 0 && col < H) {
+        double t = 0.0;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) t += sh[i][cx];
+        gw[col] = from_f32<T>(float(t));
+    }
+}
+
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 double round_scalar_to(double v, int dtype) {
@@ -538,6 +627,48 @@ int paras_b200_rmsnorm_bwd(int gpu, const void* grad_out, const void* x, const v
     if (!grad_out || !x || !weight || !rstd || !grad_x)
         return fail(PARAS_E_INVALID, "paras rms_norm_backward: null pointer");
     const int sms = g->sm_count > 0 ? g->sm_count : 148;
+    // Rows that split into 1..8 vectors per thread of a 128- or 256-thread CTA take the one-pass kernel.
+    {
+        const int64_t nvec = H * int64_t(pb::dtype_size(dtype)) / 16;
+        const bool vec_ok = (H * int64_t(pb::dtype_size(dtype))) % 16 == 0 && pb::aligned16(grad_out) && pb::aligned16(x) &&
+                            pb::aligned16(weight) && pb::aligned16(grad_x);
+        int threads = 0;
+        if (vec_ok && nvec % 128 == 0 && nvec / 128 <= 8) threads = 128;
+        else if (vec_ok && nvec % 256 == 0 && nvec / 256 <= 8) threads = 256;
+        if (threads) {
+            const int v = int(nvec / threads);
+            const int parts = int(std::min<int64_t>(rows, int64_t(sms) * (threads == 128 ? 4 : 2)));
+            void* scratch = nullptr;
+            st = paras_b200_malloc_async(gpu, size_t(parts) * size_t(H) * sizeof(float), s, &scratch);
+            if (st != PARAS_OK) return st;
+            float* part = static_cast<float*>(scratch);
+#define PB_ROWS(T, V, TH)                                                                                        \
+    pb::rmsnorm_bwd_rows_kernel<T, V, TH><<<parts, TH, 0, s>>>(static_cast<const T*>(grad_out), static_cast<const T*>(x), \
+        static_cast<const T*>(weight), rstd, static_cast<T*>(grad_x), part, rows, H)
+#define PB_ROWS_V(T, TH)                                                                                         \
+    switch (v) {                                                                                                 \
+        case 1: PB_ROWS(T, 1, TH); break; case 2: PB_ROWS(T, 2, TH); break; case 3: PB_ROWS(T, 3, TH); break;     \
+        case 4: PB_ROWS(T, 4, TH); break; case 5: PB_ROWS(T, 5, TH); break; case 6: PB_ROWS(T, 6, TH); break;     \
+        case 7: PB_ROWS(T, 7, TH); break; default: PB_ROWS(T, 8, TH); break;                                      \
+    }
+#define PB_ROWS_T(T)                                                                                             \
+    do {                                                                                                         \
+        if (threads == 128) { PB_ROWS_V(T, 128) } else { PB_ROWS_V(T, 256) }                                     \
+        pb::rmsnorm_bwd_dw_reduce_kernel<T><<<int((H + 63) / 64), 1024, 0, s>>>(part, static_cast<T*>(grad_weight), parts, H); \
+    } while (0)
+            switch (dtype) {
+                case PARAS_F32: PB_ROWS_T(float); break;
+                case PARAS_BF16: PB_ROWS_T(__nv_bfloat16); break;
+                default: PB_ROWS_T(__half); break;
+            }
+#undef PB_ROWS_T
+#undef PB_ROWS_V
+#undef PB_ROWS
+            st = cudaGetLastError() == cudaSuccess ? PARAS_OK : fail(PARAS_E_CUDA, "paras rms_norm_backward: kernel launch failed");
+            const int st2 = paras_b200_free_async(gpu, scratch, s);
+            return st != PARAS_OK ? st : st2;
+        }
+    }
     int64_t blocks = (rows + pb::kWarpsPerBlock - 1) / pb::kWarpsPerBlock;
     if (blocks > int64_t(sms) * 16) blocks = int64_t(sms) * 16;
     const int dwblocks = int((H + 31) / 32);
