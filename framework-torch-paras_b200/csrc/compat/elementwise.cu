@@ -6,6 +6,8 @@
 // arithmetic) and the torch_paras::swiglu composite (csrc/ops/rms_swiglu_ops.cpp:83-86:
 // silu.out then mul.out, two passes over HBM) with ONE pass: 128-bit streaming loads of
 // gate and up, fp32 math, 128-bit streaming store.  Algorithmic traffic 3*n*sizeof(T).
+#include <algorithm>
+
 #include "common.cuh"
 
 namespace pb {
@@ -147,6 +149,24 @@ rotate_half_kernel(const T* __restrict__ x, T* __restrict__ out, int64_t n, int6
     }
 }
 
+// The same on 16-byte vectors (half a row is a whole number of vectors): vector j of the output's first
+// half is minus vector j of the input's second half, and the other way round without the sign.
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+rotate_half_vec_kernel(const T* __restrict__ x, T* __restrict__ out, int64_t nvec, int vec_per_half, int backward) {
+    constexpr int N = Vec16<T>::N;
+    for (int64_t i = int64_t(blockIdx.x) * kThreads + threadIdx.x; i < nvec; i += int64_t(gridDim.x) * kThreads) {
+        const int64_t hrow = i / vec_per_half;            // (row, half) pair
+        const bool lo = (hrow & 1) == 0;                  // this vector lies in the output's first half
+        Vec16<T> v = ld16_stream(x + (lo ? i + vec_per_half : i - vec_per_half) * N);
+        if (backward ? !lo : lo) {
+#pragma unroll
+            for (int e = 0; e < N; ++e) v.v[e] = from_f32<T>(-to_f32<T>(v.v[e]));
+        }
+        st16_stream(out + i * N, v);
+    }
+}
+
 // Rotary embedding out = x * cos + rotate_half(x) * sin for x [B, H, L, D] (element strides for
 // B, H, L; unit stride on D) and cos / sin [Lmax, D] read at rows pos0 + l.  The reference composes
 // this from three binary kernels that each round to the tensor dtype (pointwise_ops.cpp:62-85) around
@@ -273,6 +293,90 @@ strided_copy_kernel(void* dst, int dcode, const void* src, int scode, CopySpec s
     }
 }
 
+// ---- fast paths of the strided copy --------------------------------------------------------
+// Rows: the innermost dimension is contiguous on both sides and a multiple of 8 elements, the element
+// types are floating point (any pair of fp32 / bf16 / fp16).  A group of G lanes takes a row at a time, 8
+// elements per lane and step, with 16-byte accesses; the row's offsets are worked out once per row.
+template <typename T> struct Load8;
+template <> struct Load8<float> {
+    static __device__ __forceinline__ void run(const float* p, float (&f)[8]) {
+        const float4 a = __ldcs(reinterpret_cast<const float4*>(p)), b = __ldcs(reinterpret_cast<const float4*>(p) + 1);
+        f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+    }
+    static __device__ __forceinline__ void store(float* p, const float (&f)[8]) {
+        __stcs(reinterpret_cast<float4*>(p), make_float4(f[0], f[1], f[2], f[3]));
+        __stcs(reinterpret_cast<float4*>(p) + 1, make_float4(f[4], f[5], f[6], f[7]));
+    }
+};
+template <typename T> struct Load8 {
+    static __device__ __forceinline__ void run(const T* p, float (&f)[8]) {
+        const Vec16<T> v = ld16_stream(p);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) f[e] = to_f32<T>(v.v[e]);
+    }
+    static __device__ __forceinline__ void store(T* p, const float (&f)[8]) {
+        Vec16<T> v;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v.v[e] = from_f32<T>(f[e]);
+        st16_stream(p, v);
+    }
+};
+
+template <typename S, typename D, int G>
+__global__ void __launch_bounds__(kThreads)
+row_copy8_kernel(D* __restrict__ dst, const S* __restrict__ src, CopySpec sp, int64_t rows, int64_t inner8) {
+    const int64_t group = (int64_t(blockIdx.x) * kThreads + threadIdx.x) / G, ngroups = int64_t(gridDim.x) * kThreads / G;
+    const int gl = threadIdx.x % G;
+    for (int64_t row = group; row < rows; row += ngroups) {
+        int64_t rem = row, so = 0, dof = 0;
+#pragma unroll 1
+        for (int d = sp.ndim - 2; d >= 0; --d) {
+            const int64_t q = rem / sp.sizes[d];
+            const int64_t r = rem - q * sp.sizes[d];
+            so += r * sp.sstr[d];
+            dof += r * sp.dstr[d];
+            rem = q;
+        }
+        for (int64_t j = gl; j < inner8; j += G) {
+            float f[8];
+            Load8<S>::run(src + so + 8 * j, f);
+            Load8<D>::store(dst + dof + 8 * j, f);
+        }
+    }
+}
+
+// Transposes: the last two dimensions change places (source unit stride on the second to last one,
+// destination on the last one), same element size.  32 x 32 tiles through shared memory, so that both
+// sides are read and written along their unit stride; leading dimensions are walked by blockIdx.z.
+template <typename T>
+__global__ void __launch_bounds__(256)
+transpose_tile_kernel(T* __restrict__ dst, const T* __restrict__ src, CopySpec sp, int64_t R, int64_t C,
+                      int64_t s_ld, int64_t d_ld) {
+    // dst[b][r][c] = src[b][c][r] in memory terms: src element (r, c) sits at c * s_ld + r, dst at r * d_ld + c
+    __shared__ T tile[32][33];
+    int64_t rem = blockIdx.z, so = 0, dof = 0;
+    for (int d = sp.ndim - 3; d >= 0; --d) {
+        const int64_t q = rem / sp.sizes[d];
+        const int64_t r = rem - q * sp.sizes[d];
+        so += r * sp.sstr[d];
+        dof += r * sp.dstr[d];
+        rem = q;
+    }
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;   // 32 x 8
+    const int64_t r0 = int64_t(blockIdx.x) * 32, c0 = int64_t(blockIdx.y) * 32;
+#pragma unroll
+    for (int k = 0; k < 32; k += 8) {
+        const int64_t c = c0 + ty + k, r = r0 + tx;            // read along r (the source's unit stride)
+        if (c < C && r < R) tile[ty + k][tx] = src[so + c * s_ld + r];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < 32; k += 8) {
+        const int64_t r = r0 + ty + k, c = c0 + tx;            // write along c (the destination's unit stride)
+        if (r < R && c < C) dst[dof + r * d_ld + c] = tile[tx][ty + k];
+    }
+}
+
 __global__ void __launch_bounds__(kThreads)
 fill_kernel(void* dst, int code, double value, int64_t n) {
     Wide w{value, (long long)value, false};
@@ -314,6 +418,102 @@ int launch_swiglu(Gpu* g, const void* gate, const void* up, void* out, int64_t n
         PB_LAUNCH_CHECK("swiglu_fwd_scalar_kernel");
     }
     return PARAS_OK;
+}
+
+int code_size(int code) {
+    switch (code) {
+        case PARAS_SC_F64: case PARAS_SC_I64: return 8;
+        case PARAS_SC_F32: case PARAS_SC_I32: return 4;
+        case PARAS_SC_BF16: case PARAS_SC_F16: case PARAS_SC_I16: return 2;
+        default: return 1;
+    }
+}
+bool is_float16_32(int code) { return code == PARAS_SC_F32 || code == PARAS_SC_BF16 || code == PARAS_SC_F16; }
+
+template <typename S, typename D>
+void launch_rows(const Gpu* g, void* dst, const void* src, const CopySpec& sp, int64_t rows, int64_t inner8, cudaStream_t s) {
+    D* d = static_cast<D*>(dst);
+    const S* sr = static_cast<const S*>(src);
+    const int64_t work = rows * std::min<int64_t>(inner8, 32);
+    const int blocks = grid_for(g, work, kThreads, 16);
+    if (inner8 >= 32) row_copy8_kernel<S, D, 32><<<blocks, kThreads, 0, s>>>(d, sr, sp, rows, inner8);
+    else if (inner8 >= 16) row_copy8_kernel<S, D, 16><<<blocks, kThreads, 0, s>>>(d, sr, sp, rows, inner8);
+    else if (inner8 >= 8) row_copy8_kernel<S, D, 8><<<blocks, kThreads, 0, s>>>(d, sr, sp, rows, inner8);
+    else if (inner8 >= 4) row_copy8_kernel<S, D, 4><<<blocks, kThreads, 0, s>>>(d, sr, sp, rows, inner8);
+    else row_copy8_kernel<S, D, 2><<<blocks, kThreads, 0, s>>>(d, sr, sp, rows, inner8);
+}
+template <typename S>
+void launch_rows_dst(const Gpu* g, void* dst, int dcode, const void* src, const CopySpec& sp, int64_t rows, int64_t inner8,
+                     cudaStream_t s) {
+    if (dcode == PARAS_SC_F32) launch_rows<S, float>(g, dst, src, sp, rows, inner8, s);
+    else if (dcode == PARAS_SC_BF16) launch_rows<S, __nv_bfloat16>(g, dst, src, sp, rows, inner8, s);
+    else launch_rows<S, __half>(g, dst, src, sp, rows, inner8, s);
+}
+
+// Picks a fast kernel for the common layouts of a copy; false = take the generic element-wise kernel.
+bool copy_fast_path(const Gpu* g, void* dst, int dcode, const void* src, int scode, const CopySpec& sp_in, int64_t n,
+                    cudaStream_t s) {
+    if (sp_in.ndim < 1 || n < 4096) return false;
+    // drop dimensions of size 1, merge neighbours that are contiguous on both sides
+    CopySpec sp{};
+    for (int d = 0; d < sp_in.ndim; ++d) {
+        if (sp_in.sizes[d] == 1) continue;
+        if (sp.ndim > 0 && sp.sstr[sp.ndim - 1] == sp_in.sstr[d] * sp_in.sizes[d] &&
+            sp.dstr[sp.ndim - 1] == sp_in.dstr[d] * sp_in.sizes[d]) {
+            sp.sizes[sp.ndim - 1] *= sp_in.sizes[d];
+            sp.sstr[sp.ndim - 1] = sp_in.sstr[d];
+            sp.dstr[sp.ndim - 1] = sp_in.dstr[d];
+        } else {
+            sp.sizes[sp.ndim] = sp_in.sizes[d];
+            sp.sstr[sp.ndim] = sp_in.sstr[d];
+            sp.dstr[sp.ndim] = sp_in.dstr[d];
+            ++sp.ndim;
+        }
+    }
+    if (sp.ndim < 1) return false;
+    const int L = sp.ndim - 1;
+    const int ss = code_size(scode), ds = code_size(dcode);
+    auto aligned = [&](const void* base, const int64_t* str, int es) {
+        if (reinterpret_cast<uintptr_t>(base) & 15u) return false;
+        for (int d = 0; d < L; ++d)
+            if ((str[d] * es) % 16) return false;
+        return true;
+    };
+    // rows of floating-point elements, unit stride on both sides
+    if (is_float16_32(scode) && is_float16_32(dcode) && sp.sstr[L] == 1 && sp.dstr[L] == 1 && sp.sizes[L] % 8 == 0 &&
+        aligned(src, sp.sstr, ss) && aligned(dst, sp.dstr, ds)) {
+        int64_t inner = sp.sizes[L], rows = n / inner;
+        if (sp.ndim == 1) {   // one long contiguous run: cut it into rows of 2048 elements (or fewer that divide it)
+            int64_t chunk = 2048;
+            while (chunk > 8 && inner % chunk) chunk /= 2;
+            sp.ndim = 2;
+            sp.sizes[0] = inner / chunk; sp.sstr[0] = chunk; sp.dstr[0] = chunk;
+            sp.sizes[1] = chunk; sp.sstr[1] = 1; sp.dstr[1] = 1;
+            rows = inner / chunk;
+            inner = chunk;
+        }
+        if (scode == PARAS_SC_F32) launch_rows_dst<float>(g, dst, dcode, src, sp, rows, inner / 8, s);
+        else if (scode == PARAS_SC_BF16) launch_rows_dst<__nv_bfloat16>(g, dst, dcode, src, sp, rows, inner / 8, s);
+        else launch_rows_dst<__half>(g, dst, dcode, src, sp, rows, inner / 8, s);
+        return true;
+    }
+    // the last two dimensions change places, same element size (2 or 4 bytes)
+    if (sp.ndim >= 2 && scode == dcode && (ss == 2 || ss == 4) && sp.dstr[L] == 1 && sp.sstr[L - 1] == 1 &&
+        sp.sstr[L] >= sp.sizes[L - 1] && sp.dstr[L - 1] >= sp.sizes[L]) {
+        const int64_t R = sp.sizes[L - 1], C = sp.sizes[L];
+        int64_t batch = 1;
+        for (int d = 0; d < L - 1; ++d) batch *= sp.sizes[d];
+        if (batch > 65535 || (C + 31) / 32 > 65535) return false;
+        dim3 grid(unsigned((R + 31) / 32), unsigned((C + 31) / 32), unsigned(batch));
+        if (ss == 2)
+            transpose_tile_kernel<uint16_t><<<grid, 256, 0, s>>>(static_cast<uint16_t*>(dst), static_cast<const uint16_t*>(src), sp,
+                                                               R, C, sp.sstr[L], sp.dstr[L - 1]);
+        else
+            transpose_tile_kernel<uint32_t><<<grid, 256, 0, s>>>(static_cast<uint32_t*>(dst), static_cast<const uint32_t*>(src), sp,
+                                                               R, C, sp.sstr[L], sp.dstr[L - 1]);
+        return true;
+    }
+    return false;
 }
 
 }  // namespace
@@ -476,10 +676,18 @@ int paras_b200_rotate_half(int gpu, const void* x, void* out, int64_t rows, int6
     if (n == 0) return PARAS_OK;
     if (!x || !out) return fail(PARAS_E_INVALID, "paras rotate_half: null pointer");
     cudaStream_t s = pb::pick_stream(g, stream);
-    const int blocks = pb::grid_for(g, n, pb::kThreads);
+    const int64_t per = 16 / int64_t(pb::dtype_size(dtype));
+    const bool vec = (D / 2) % per == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out)) & 15u) == 0;
+    const int blocks = pb::grid_for(g, vec ? n / per : n, pb::kThreads, 16);
 #define PB_ROT(T)                                                                   \
-    pb::rotate_half_kernel<T><<<blocks, pb::kThreads, 0, s>>>(                       \
-        static_cast<const T*>(x), static_cast<T*>(out), n, D, backward)
+    do {                                                                            \
+        if (vec)                                                                    \
+            pb::rotate_half_vec_kernel<T><<<blocks, pb::kThreads, 0, s>>>(           \
+                static_cast<const T*>(x), static_cast<T*>(out), n / per, int(D / 2 / per), backward); \
+        else                                                                        \
+            pb::rotate_half_kernel<T><<<blocks, pb::kThreads, 0, s>>>(               \
+                static_cast<const T*>(x), static_cast<T*>(out), n, D, backward);    \
+    } while (0)
     switch (dtype) {
         case PARAS_F32: PB_ROT(float); break;
         case PARAS_BF16: PB_ROT(__nv_bfloat16); break;
@@ -514,6 +722,10 @@ int paras_b200_strided_copy(int gpu, void* dst, int dst_code, const int64_t* dst
     }
     if (n == 0) return PARAS_OK;
     if (!dst || !src) return fail(PARAS_E_INVALID, "paras copy: null pointer");
+    if (pb::copy_fast_path(g, dst, dst_code, src, src_code, sp, n, pb::pick_stream(g, stream))) {
+        PB_LAUNCH_CHECK("copy fast path");
+        return PARAS_OK;
+    }
     const int blocks = pb::grid_for(g, n, pb::kThreads, 16);
     pb::strided_copy_kernel<<<blocks, pb::kThreads, 0, pb::pick_stream(g, stream)>>>(
         dst, dst_code, src, src_code, sp, n);

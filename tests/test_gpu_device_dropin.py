@@ -352,3 +352,41 @@ def test_memory_limit_makes_allocation_fail_like_a_full_device():
     out = torch.nn.functional.scaled_dot_product_attention(q, q, q, is_causal=True)
     ref = torch.nn.functional.scaled_dot_product_attention(q.cpu(), q.cpu(), q.cpu(), is_causal=True)
     assert torch.allclose(out.cpu(), ref, atol=1e-4, rtol=1e-4)
+
+
+def test_copies_casts_and_transposes_match_cpu_for_every_layout():
+    # the copy kernels behind .contiguous() / .to(dtype) / copy_: rows with a contiguous last dimension,
+    # transposes of the last two dimensions, general permutations and slices, every element type
+    import itertools
+    g = torch.Generator().manual_seed(0)
+
+    def same(name, fn):
+        want = fn(lambda t: t)
+        got = fn(lambda t: t.to("paras:1")).cpu()
+        assert got.shape == want.shape and got.dtype == want.dtype and torch.equal(got, want), name
+
+    for dt in (torch.bfloat16, torch.float16, torch.float32, torch.int32, torch.int16, torch.float64):
+        x = (torch.randn(3, 40, 8, 64, generator=g) * 50).to(dt)
+        same(f"transpose(1,2) {dt}", lambda dev: dev(x).transpose(1, 2).contiguous())
+        same(f"transpose(-1,-2) {dt}", lambda dev: dev(x).transpose(-1, -2).contiguous())
+        same(f"permute {dt}", lambda dev: dev(x).permute(3, 0, 2, 1).contiguous())
+        same(f"slice {dt}", lambda dev: dev(x)[:, 3:37, :, 8:56].contiguous())
+        same(f"clone {dt}", lambda dev: dev(x).clone())
+        y = (torch.randn(333, 517, generator=g) * 9).to(dt)
+        same(f"t() {dt}", lambda dev: dev(y).t().contiguous())
+        same(f"t() of a slice {dt}", lambda dev: dev(y)[5:300, 7:500].t().contiguous())
+    for a, b in itertools.permutations((torch.bfloat16, torch.float16, torch.float32), 2):
+        x = (torch.randn(5, 33, 128, generator=g) * 3).to(a)
+        same(f"cast {a} -> {b}", lambda dev: dev(x).to(b))
+        same(f"cast of a view {a} -> {b}", lambda dev: dev(x).transpose(0, 1).to(b))
+        z = torch.randn(1000003, generator=g).to(a)
+        same(f"cast, odd length {a} -> {b}", lambda dev: dev(z).to(b))
+        z2 = torch.randn(8 * 4097, generator=g).to(a)
+        same(f"cast, 8 x 4097 {a} -> {b}", lambda dev: dev(z2).to(b))
+    dst = torch.zeros(4, 64, 16, 128).bfloat16()
+    src = torch.randn(4, 16, 64, 128, generator=g).bfloat16()
+    d1 = dst.clone()
+    d1.transpose(1, 2).copy_(src)
+    d2 = dst.clone().to("paras:1")
+    d2.transpose(1, 2).copy_(src.to("paras:1"))
+    assert torch.equal(d1, d2.cpu())
