@@ -477,6 +477,14 @@ def run_ours(args):
         gbs = nbytes / (t * 1e-3) / 1e9
         extra[f"sdpa_decode_B{db}_kv32768"] = {"ms": t, "gbs": gbs, "frac_of_hbm_peak": gbs / peaks["hbm_gbs"],
                                             "bytes": nbytes, "kernel": abi.sdpa_last_kernel()}
+        # the same step over caches of different lengths: a bool key-padding mask [B,1,1,kv]
+        padm = torch.ones(db, 1, 1, 32768, dtype=torch.bool, device=dev)
+        padm[:, :, :, 30000:] = False
+        t = loop_ms(lambda: abi.sdpa_fwd(qd, kd, vd, out=od, mask=padm, workspace=ws if ws_bytes else None), s3, 3)
+        gbs = nbytes / (t * 1e-3) / 1e9
+        extra[f"sdpa_decode_padding_mask_B{db}_kv32768"] = {"ms": t, "gbs": gbs, "frac_of_hbm_peak": gbs / peaks["hbm_gbs"],
+                                                         "kernel": abi.sdpa_last_kernel()}
+        del padm
         del qd, kd, vd, od, ws
     if want("block"):
         # config 5, one GPU's share (B=64 over 8 GPUs -> 8 batch elements here): RMSNorm -> causal GQA

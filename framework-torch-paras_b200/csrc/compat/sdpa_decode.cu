@@ -55,6 +55,12 @@ struct DecParams {
     float* o_part;
     float2* ml_part;
     int* status;
+    // explicit attn_mask [B, Hq, Lq, Lk] (element strides, 0 = broadcast): 1 bool, 2 additive in the
+    // tensors' dtype, 3 additive fp32; additive values join the unscaled scores divided by the scale
+    const void* mask;
+    int mask_kind;
+    int64_t ms[4];
+    float inv_scale;
 };
 
 __device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t (&r)[4]) {
@@ -84,7 +90,7 @@ __device__ __forceinline__ uint32_t swz(int row, int c16) {
     return uint32_t(row * 128 + ((c16 ^ (row & 7)) << 4));
 }
 
-template <bool BF16>
+template <bool BF16, bool MASK>
 __global__ void __launch_bounds__(kThreads, 1)
 sdpa_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                    const DecParams p) {
@@ -168,14 +174,23 @@ sdpa_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
             lim[half] = p.Lk - 1;
             if (p.causal && r < p.rows) lim[half] = min(lim[half], r / p.group);  // top-left aligned
         }
+        int64_t mrow[2] = {0, 0};   // element offset of each row's mask entries for key 0
+        if (MASK) {
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                const int r = min(r0 + 8 * half, p.rows - 1);
+                mrow[half] = int64_t(b) * p.ms[0] + int64_t(hk * p.group + r % p.group) * p.ms[1] + int64_t(r / p.group) * p.ms[2];
+            }
+        }
         bool ok = true;
         for (int i = 0; i < ntiles; ++i) {
             const int s = i % kStages;
+            const int krow0 = warp * 16;  // this warp's 16 keys inside the tile
+            const int key_base = (t0 + i) * TK + krow0 + cpair;
             ok = mbar_wait(full(s), (i / kStages) & 1, abort_flag);
             if (!ok) break;
             const uint32_t kbase = smem_base + s * kStageBytes;
             const uint32_t vbase = kbase + kTileBytes;
-            const int krow0 = warp * 16;  // this warp's 16 keys inside the tile
 
             // ---- S = Q K^T for 16 keys: two n-tiles of 8 keys ----
             float acc_s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
@@ -193,7 +208,33 @@ sdpa_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
                 }
             }
             // ---- mask, online softmax ----
-            const int key_base = (t0 + i) * TK + krow0 + cpair;
+            // what the mask adds to this thread's four keys of each of its two rows (one set of loads when the
+            // rows share a mask row, as with a key-padding mask)
+            float madd[2][2][2];
+            if (MASK) {
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    if (half == 1 && mrow[1] == mrow[0]) {
+#pragma unroll
+                        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                            for (int e = 0; e < 2; ++e) madd[1][nt][e] = madd[0][nt][e];
+                        continue;
+                    }
+#pragma unroll
+                    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                        for (int e = 0; e < 2; ++e) {
+                            const int key = min(key_base + nt * 8 + e, p.Lk - 1);
+                            const int64_t mo = mrow[half] + int64_t(key) * p.ms[3];
+                            float a;
+                            if (p.mask_kind == 1) a = __ldg(static_cast<const unsigned char*>(p.mask) + mo) ? 0.f : -INFINITY;
+                            else if (p.mask_kind == 2) a = from16<BF16>(__ldg(static_cast<const uint16_t*>(p.mask) + mo)) * p.inv_scale;
+                            else a = __ldg(static_cast<const float*>(p.mask) + mo) * p.inv_scale;
+                            madd[half][nt][e] = a;
+                        }
+                }
+            }
             float p_[2][4];
             float alpha[2];
 #pragma unroll
@@ -206,6 +247,7 @@ sdpa_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
                         const int key = key_base + nt * 8 + e;
                         float v = acc_s[nt][2 * half + e];
                         if (key > lim[half]) v = -INFINITY;
+                        else if (MASK) v += madd[half][nt][e];   // -inf for a masked-out key
                         acc_s[nt][2 * half + e] = v;
                         mx = fmaxf(mx, v);
                     }
@@ -345,7 +387,7 @@ bool sdpa_decode_supported(const Gpu* g, const paras_sdpa_args& a, const char** 
     if (g->cc_major < 9) { *why = "GPU has no TMA"; return false; }
     if (a.dtype != PARAS_BF16 && a.dtype != PARAS_F16) { *why = "dtype is not 16-bit"; return false; }
     if (a.D != HD) { *why = "head dim is not 128"; return false; }
-    if (a.mask) { *why = "explicit attn_mask"; return false; }
+    if (a.mask && (a.mask_kind < 1 || a.mask_kind > 3)) { *why = "unknown mask kind"; return false; }
     if (a.Hkv < 1 || a.Lq < 1 || int64_t(a.Lq) * (a.Hq / a.Hkv) > kMaxRows) {
         *why = "more than 16 query rows per kv head";
         return false;
@@ -409,14 +451,19 @@ int sdpa_decode_launch(Gpu* g, const paras_sdpa_args& a, float scale, const Spli
     p.o_part = ws.o_part;
     p.ml_part = ws.ml_part;
     p.status = g->status_dev;
+    p.mask = a.mask;
+    p.mask_kind = a.mask ? a.mask_kind : 0;
+    for (int i = 0; i < 4; ++i) p.ms[i] = a.mask_strides[i];
+    p.inv_scale = 1.0f / scale;
     dim3 grid(ws.splits, a.Hkv, a.B);
-    if (a.dtype == PARAS_BF16) {
-        PB_CUDA(cudaFuncSetAttribute(sdpa_decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLaunch));
-        sdpa_decode_kernel<true><<<grid, kThreads, kSmemLaunch, s>>>(mk, mv, p);
-    } else {
-        PB_CUDA(cudaFuncSetAttribute(sdpa_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLaunch));
-        sdpa_decode_kernel<false><<<grid, kThreads, kSmemLaunch, s>>>(mk, mv, p);
-    }
+    auto go = [&](auto kernel) -> int {
+        PB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLaunch));
+        kernel<<<grid, kThreads, kSmemLaunch, s>>>(mk, mv, p);
+        return PARAS_OK;
+    };
+    if (a.dtype == PARAS_BF16) st = a.mask ? go(sdpa_decode_kernel<true, true>) : go(sdpa_decode_kernel<true, false>);
+    else st = a.mask ? go(sdpa_decode_kernel<false, true>) : go(sdpa_decode_kernel<false, false>);
+    if (st != PARAS_OK) return st;
     PB_LAUNCH_CHECK("sdpa_decode_kernel");
     if (ws.splits > 1) return sdpa_combine_launch(g, a, ws, s);
     return PARAS_OK;

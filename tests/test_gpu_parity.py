@@ -441,3 +441,36 @@ def test_backward_ops_and_rotate_half_against_oracle():
         r = torch.randn(5, 64, generator=g).to(dtype)
         assert torch.equal(abi.rotate_half(r.to(DEV)).cpu(), O.rotate_half(r))
         assert torch.equal(abi.rotate_half(r.to(DEV), backward=True).cpu(), O.rotate_half_backward(r))
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("kind", ["padding", "per_row_bool", "additive", "additive_f32"])
+def test_decode_kernel_with_explicit_masks(kind, dtype):
+    # batched decoding over caches of different lengths: one or a few query positions, a long cache and a mask;
+    # the streaming decode kernel takes these (not the 256-row tensor-core tiles)
+    B, Hq, Hkv, Lq, Lk = 3, 8, 2, 2, 1500
+    q, k, v = _qkv(B, Hq, Hkv, Lq, Lk, 128, dtype, seed=61)
+    g = torch.Generator().manual_seed(62)
+    if kind == "padding":
+        mask = torch.zeros(B, 1, 1, Lk, dtype=torch.bool)
+        for b, n in enumerate((1500, 777, 1)):
+            mask[b, :, :, :n] = True
+    elif kind == "per_row_bool":
+        mask = torch.rand(B, Hq, Lq, Lk, generator=g) > 0.5
+        mask[0, 3, 1] = False          # a row without any key: NaN, as in the reference
+        mask[..., 0] |= True
+        mask[0, 3, 1] = False
+    elif kind == "additive":
+        mask = (torch.randn(Lq, Lk, generator=g) * 2).to(dtype)
+    else:
+        mask = torch.randn(B, 1, Lq, Lk, generator=g) * 2
+        mask[:, :, :, 900:1000] = float("-inf")
+    got = abi.sdpa_fwd(q.to(DEV), k.to(DEV), v.to(DEV), mask=mask.to(DEV), flags=abi.SDPA_REF_SCALE)
+    assert abi.sdpa_last_kernel() == "decode_mma"
+    if mask.dtype == torch.bool:
+        tol_check(got, O.sdpa(q, k, v, attn_mask=mask, enable_gqa=True), f"masked decode {kind} {dtype}")
+    else:
+        sc = float(torch.tensor(1 / math.sqrt(128)).to(dtype))
+        s = (q.double() @ k.double().repeat_interleave(Hq // Hkv, 1).transpose(-1, -2)) * sc + mask.double()
+        want = torch.softmax(s, -1) @ v.double().repeat_interleave(Hq // Hkv, 1)
+        assert (got.cpu().double() - want).abs().max().item() <= 2e-2, f"masked decode {kind} {dtype}"
