@@ -30,7 +30,6 @@ namespace {
 
 using namespace tc;
 
-constexpr int HD = 128;
 constexpr int TK = 64;                       // keys per tile
 constexpr int kStages = 6;
 constexpr int kHalfBytes = 64 * 2 * TK;      // one 64-wide half of the head dim: 64 keys x 128 B
@@ -90,7 +89,8 @@ __device__ __forceinline__ uint32_t swz(int row, int c16) {
     return uint32_t(row * 128 + ((c16 ^ (row & 7)) << 4));
 }
 
-template <bool BF16, bool MASK>
+// HD = 128, or 64: the same tile layout with only the first 64-wide half of every K / V tile loaded and used.
+template <bool BF16, bool MASK, int HD>
 __global__ void __launch_bounds__(kThreads, 1)
 sdpa_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                    const DecParams p) {
@@ -135,13 +135,13 @@ sdpa_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
             for (int i = 0; i < ntiles; ++i) {
                 const int s = i % kStages;
                 if (!mbar_wait(empty(s), ((i / kStages) & 1) ^ 1u, abort_flag)) break;
-                mbar_arrive_expect_tx(full(s), kStageBytes);
+                mbar_arrive_expect_tx(full(s), 2 * (HD / 64) * kHalfBytes);
                 const uint32_t dst = smem_base + s * kStageBytes;
                 const int key0 = (t0 + i) * TK;
                 tma_load_4d(dst, &map_k, full(s), 0, key0, hk, b);
-                tma_load_4d(dst + kHalfBytes, &map_k, full(s), 64, key0, hk, b);
+                if (HD > 64) tma_load_4d(dst + kHalfBytes, &map_k, full(s), 64, key0, hk, b);
                 tma_load_4d(dst + kTileBytes, &map_v, full(s), 0, key0, hk, b);
-                tma_load_4d(dst + kTileBytes + kHalfBytes, &map_v, full(s), 64, key0, hk, b);
+                if (HD > 64) tma_load_4d(dst + kTileBytes + kHalfBytes, &map_v, full(s), 64, key0, hk, b);
             }
         }
     } else {
@@ -368,13 +368,13 @@ sdpa_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
     }
 }
 
-int make_kv_map(CUtensorMap* map, const void* base, int dtype, int B, int H, int L, const int64_t* st) {
-    return make_tensor_map_bhld(map, base, dtype, B, H, L, HD, st, TK);
+int make_kv_map(CUtensorMap* map, const void* base, int dtype, int B, int H, int L, int D, const int64_t* st) {
+    return make_tensor_map_bhld(map, base, dtype, B, H, L, D, st, TK);
 }
 
-bool kv_strides_ok(const void* base, const int64_t* st, int B, int H, int L) {
+bool kv_strides_ok(const void* base, const int64_t* st, int B, int H, int L, int D) {
     if (reinterpret_cast<uintptr_t>(base) & 15u) return false;
-    if (L > 1 && (st[2] < HD || (st[2] * 2) % 16)) return false;
+    if (L > 1 && (st[2] < D || (st[2] * 2) % 16)) return false;
     if (H > 1 && (st[1] <= 0 || (st[1] * 2) % 16)) return false;
     if (B > 1 && (st[0] <= 0 || (st[0] * 2) % 16)) return false;
     return true;
@@ -386,7 +386,7 @@ bool sdpa_decode_supported(const Gpu* g, const paras_sdpa_args& a, const char** 
     *why = "";
     if (g->cc_major < 9) { *why = "GPU has no TMA"; return false; }
     if (a.dtype != PARAS_BF16 && a.dtype != PARAS_F16) { *why = "dtype is not 16-bit"; return false; }
-    if (a.D != HD) { *why = "head dim is not 128"; return false; }
+    if (a.D != 128 && a.D != 64) { *why = "head dim is neither 128 nor 64"; return false; }
     if (a.mask && (a.mask_kind < 1 || a.mask_kind > 3)) { *why = "unknown mask kind"; return false; }
     if (a.Hkv < 1 || a.Lq < 1 || int64_t(a.Lq) * (a.Hq / a.Hkv) > kMaxRows) {
         *why = "more than 16 query rows per kv head";
@@ -396,7 +396,7 @@ bool sdpa_decode_supported(const Gpu* g, const paras_sdpa_args& a, const char** 
     if (!(a.scale > 0.0) || !std::isfinite(a.scale)) { *why = "scale is not positive"; return false; }
     if (a.Hkv > 65535 || a.B > 65535) { *why = "batch or heads exceed the grid limit"; return false; }
     if (g->smem_optin < size_t(kSmemLaunch)) { *why = "not enough shared memory"; return false; }
-    if (!kv_strides_ok(a.k, a.k_strides, a.B, a.Hkv, a.Lk) || !kv_strides_ok(a.v, a.v_strides, a.B, a.Hkv, a.Lk)) {
+    if (!kv_strides_ok(a.k, a.k_strides, a.B, a.Hkv, a.Lk, a.D) || !kv_strides_ok(a.v, a.v_strides, a.B, a.Hkv, a.Lk, a.D)) {
         *why = "K/V pointers or strides are not 16-byte aligned";
         return false;
     }
@@ -434,8 +434,8 @@ int sdpa_decode_launch(Gpu* g, const paras_sdpa_args& a, float scale, const Spli
     int st = check_status_word(g);
     if (st != PARAS_OK) return st;
     CUtensorMap mk, mv;
-    if ((st = make_kv_map(&mk, a.k, a.dtype, a.B, a.Hkv, a.Lk, a.k_strides)) != PARAS_OK) return st;
-    if ((st = make_kv_map(&mv, a.v, a.dtype, a.B, a.Hkv, a.Lk, a.v_strides)) != PARAS_OK) return st;
+    if ((st = make_kv_map(&mk, a.k, a.dtype, a.B, a.Hkv, a.Lk, a.D, a.k_strides)) != PARAS_OK) return st;
+    if ((st = make_kv_map(&mv, a.v, a.dtype, a.B, a.Hkv, a.Lk, a.D, a.v_strides)) != PARAS_OK) return st;
     DecParams p{};
     p.q = a.q; p.out = a.out; p.lse = a.lse;
     p.B = a.B; p.Hq = a.Hq; p.Hkv = a.Hkv; p.Lq = a.Lq; p.Lk = a.Lk;
@@ -461,8 +461,13 @@ int sdpa_decode_launch(Gpu* g, const paras_sdpa_args& a, float scale, const Spli
         kernel<<<grid, kThreads, kSmemLaunch, s>>>(mk, mv, p);
         return PARAS_OK;
     };
-    if (a.dtype == PARAS_BF16) st = a.mask ? go(sdpa_decode_kernel<true, true>) : go(sdpa_decode_kernel<true, false>);
-    else st = a.mask ? go(sdpa_decode_kernel<false, true>) : go(sdpa_decode_kernel<false, false>);
+    if (a.D == 128) {
+        if (a.dtype == PARAS_BF16) st = a.mask ? go(sdpa_decode_kernel<true, true, 128>) : go(sdpa_decode_kernel<true, false, 128>);
+        else st = a.mask ? go(sdpa_decode_kernel<false, true, 128>) : go(sdpa_decode_kernel<false, false, 128>);
+    } else {
+        if (a.dtype == PARAS_BF16) st = a.mask ? go(sdpa_decode_kernel<true, true, 64>) : go(sdpa_decode_kernel<true, false, 64>);
+        else st = a.mask ? go(sdpa_decode_kernel<false, true, 64>) : go(sdpa_decode_kernel<false, false, 64>);
+    }
     if (st != PARAS_OK) return st;
     PB_LAUNCH_CHECK("sdpa_decode_kernel");
     if (ws.splits > 1) return sdpa_combine_launch(g, a, ws, s);

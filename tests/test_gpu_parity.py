@@ -114,6 +114,7 @@ SDPA_CASES = [
     (1, 2, 2, 130, 400, 128, True),     # causal with Lk > Lq: top-left alignment
     (1, 2, 2, 400, 130, 128, True),     # causal with Lk < Lq
     (2, 8, 2, 1, 700, 128, False),      # decode step, GQA
+    (2, 8, 2, 2, 900, 64, False),       # decode step with head dim 64 (the decode kernel's one-slab form)
     (1, 4, 4, 7, 260, 128, False),      # a few query rows
     (1, 2, 2, 129, 129, 64, True),      # D = 64
     (2, 4, 2, 640, 640, 64, True),      # D = 64 on the tensor-core kernel: GQA, several kv tiles
