@@ -22,6 +22,7 @@
 //
 // Every wait is bounded (tc_prims.cuh); a wait that runs out raises the CTA's abort flag, all
 // roles leave through the common exit, TMEM is freed and the GPU's status word is set.
+#include <algorithm>
 #include <cmath>
 
 #include "common.cuh"
@@ -65,7 +66,8 @@ constexpr int kSmemMisc = kSmemBars + kNumBars * 8;             // tmem base wor
 constexpr int kSmemTotal = kSmemMisc + 16;
 
 enum { kEpiNone = 0, kEpiBias = 1, kEpiSwiglu = 2, kEpiProb = 3, kEpiDs = 4,   // 3, 4: attention backward only
-       kEpiRowScale = 5 };   // C = (A B^T) * row_scale[row]: RMSNorm folded into the projection that follows it
+       kEpiRowScale = 5,     // C = (A B^T) * row_scale[row]: RMSNorm folded into the projection that follows it
+       kEpiPartial = 6 };    // split-K (internal): the fp32 accumulator itself, written through a 16-bit view of the buffer
 
 struct GemmParams {
     int M, N, K;          // N = output columns (for SwiGLU: F)
@@ -460,6 +462,35 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     tmem_wait_ld();
                     tmem_ld_fence32(reinterpret_cast<uint32_t(&)[32]>(o[0]));
                     tmem_ld_fence32(reinterpret_cast<uint32_t(&)[32]>(o[32]));
+                    if (EPI == kEpiPartial) {
+                        // 64 fp32 columns leave as two 128-byte-wide pieces; the tensor map sees each fp32 as two
+                        // 16-bit elements, so a piece is the usual 64-element box at twice the column index
+                        if (c + kEpiGroups >= kChunks) {
+                            tc_fence_before_sync();
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(bar(kBarAccEmpty + buf));
+                        }
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            const uint32_t stage = stage0 + (nstore & 1u) * kOutStage;
+                            if (lane == 0) tma_store_wait_read_but_last();
+                            __syncwarp();
+#pragma unroll
+                            for (int v = 0; v < 8; ++v)
+                                st_shared_v4(stage + lane * 128 + ((v ^ (lane & 7)) << 4),
+                                             make_uint4(o[32 * h + 4 * v], o[32 * h + 4 * v + 1], o[32 * h + 4 * v + 2],
+                                                        o[32 * h + 4 * v + 3]));
+                            fence_proxy_async_smem();
+                            __syncwarp();
+                            if (lane == 0) {
+                                if (row_w < p.M && t.n0 + 64 * c + 32 * h < p.N)
+                                    tma_store_3d(&map_c, stage, 2 * (t.n0 + 64 * c + 32 * h), row_w, t.b);
+                                tma_store_commit();
+                            }
+                            ++nstore;
+                        }
+                        continue;
+                    }
                     if (EPI == kEpiProb) {
                         // C = exp(acc * scale - stat[row]), zero where the key comes after the query
                         const float neg = -stat * 1.4426950408889634f;
@@ -552,6 +583,30 @@ bool aligned16(const void* ptr, int64_t ld) {
     return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0 && ld % 8 == 0 && ld > 0;
 }
 
+// Split-K: C[m, n] = round(sum over the K slices of partial[s][m, n] (+ bias[n])), four columns per thread.
+template <bool BF16>
+__global__ void __launch_bounds__(256)
+gemm_splitk_reduce_kernel(const float* __restrict__ partial, int splits, int64_t M, int64_t N, const void* __restrict__ bias,
+                          void* __restrict__ c, int64_t ldc) {
+    const int64_t n4 = N / 4, total = M * n4;
+    for (int64_t i = int64_t(blockIdx.x) * 256 + threadIdx.x; i < total; i += int64_t(gridDim.x) * 256) {
+        const int64_t m = i / n4, n = (i - m * n4) * 4;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int sidx = 0; sidx < splits; ++sidx) {
+            const float4 v = __ldcs(reinterpret_cast<const float4*>(partial + (int64_t(sidx) * M + m) * N + n));
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+        if (bias) {
+            const uint16_t* bp = static_cast<const uint16_t*>(bias) + n;
+            acc.x += from16<BF16>(bp[0]); acc.y += from16<BF16>(bp[1]); acc.z += from16<BF16>(bp[2]); acc.w += from16<BF16>(bp[3]);
+        }
+        uint2 o;
+        o.x = pack16<BF16>(acc.x, acc.y);
+        o.y = pack16<BF16>(acc.z, acc.w);
+        *reinterpret_cast<uint2*>(static_cast<uint16_t*>(c) + m * ldc + n) = o;
+    }
+}
+
 template <bool BF16, bool A_ROWS_OF_M, bool B_ROWS_OF_N, int EPI>
 int launch(Gpu* g, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mb2,
            const CUtensorMap& mc, const GemmParams& p, cudaStream_t s) {
@@ -614,6 +669,51 @@ int gemm_run(const paras_gemm_args* a, const GemmExtra* ex) {
     // N <= 128 (the [.., head dim] products of attention backward): half-width B tiles and MMAs
     const bool narrow = a->N <= BN / 2 && (epi == kEpiNone || epi == kEpiBias || epi == kEpiRowScale);
     const int n_per_tile = a->epilogue == kEpiSwiglu || narrow ? BN / 2 : BN;
+    // Few output tiles and a long K (the projections of a decode step: M = the batch): the K range is cut
+    // into slices that run as the batches of one launch, each writing its fp32 accumulator to scratch, and a
+    // small kernel sums the slices, adds the bias and rounds.  Without it 16 of the 148 SMs stream the weight.
+    if (!ex && !at && a->batch == 1 && (a->epilogue == kEpiNone || a->epilogue == kEpiBias) && a->N % 4 == 0) {
+        const int sms = g->sm_count > 0 ? g->sm_count : 148;
+        const int64_t tiles = ((a->M + BM - 1) / BM) * ((a->N + n_per_tile - 1) / n_per_tile);
+        int splits = int(std::min<int64_t>(std::min<int64_t>(16, sms / std::max<int64_t>(tiles, 1)), a->K / (4 * BK)));
+        while (splits > 1 && a->K % (int64_t(splits) * BK)) --splits;
+        if (splits > 1) {
+            const int64_t ks = a->K / splits;
+            cudaStream_t s = pick_stream(g, a->stream);
+            void* scratch = nullptr;
+            if ((st = paras_b200_malloc_async(a->gpu, size_t(splits) * size_t(a->M) * size_t(a->N) * sizeof(float), s, &scratch)) != PARAS_OK)
+                return st;
+            CUtensorMap ma, mb, mc;
+            st = make_tensor_map_3d(&ma, a->a, a->dtype, ks, a->M, splits, a->lda, ks, BK, BM);
+            if (st == PARAS_OK)
+                st = kn ? make_tensor_map_3d(&mb, a->b, a->dtype, a->N, ks, splits, a->ldb, ks * a->ldb, 64, BK)
+                        : make_tensor_map_3d(&mb, a->b, a->dtype, ks, a->N, splits, a->ldb, ks, BK, n_per_tile);
+            if (st == PARAS_OK)
+                st = make_tensor_map_3d(&mc, scratch, a->dtype, 2 * a->N, a->M, splits, 2 * a->N, 2 * a->M * a->N, 64, 32);
+            if (st == PARAS_OK) {
+                GemmParams p{};
+                p.M = int(a->M); p.N = int(a->N); p.K = int(ks); p.batch = splits;
+                p.tiles_m = int((a->M + BM - 1) / BM);
+                p.tiles_n = int((a->N + n_per_tile - 1) / n_per_tile);
+                p.tiles = p.tiles_m * p.tiles_n * splits;
+                p.k_iters = int(ks / BK);
+                p.narrow = narrow;
+                p.status = g->status_dev;
+                const bool bf = a->dtype == PARAS_BF16;
+                if (bf) st = kn ? launch<true, false, true, kEpiPartial>(g, ma, mb, mb, mc, p, s) : launch<true, false, false, kEpiPartial>(g, ma, mb, mb, mc, p, s);
+                else st = kn ? launch<false, false, true, kEpiPartial>(g, ma, mb, mb, mc, p, s) : launch<false, false, false, kEpiPartial>(g, ma, mb, mb, mc, p, s);
+                if (st == PARAS_OK) {
+                    const int blocks = int(std::min<int64_t>((a->M * (a->N / 4) + 255) / 256, int64_t(sms) * 8));
+                    const void* bias = a->epilogue == kEpiBias ? a->bias : nullptr;
+                    if (bf) gemm_splitk_reduce_kernel<true><<<blocks, 256, 0, s>>>(static_cast<const float*>(scratch), splits, a->M, a->N, bias, a->c, a->ldc);
+                    else gemm_splitk_reduce_kernel<false><<<blocks, 256, 0, s>>>(static_cast<const float*>(scratch), splits, a->M, a->N, bias, a->c, a->ldc);
+                    if (cudaGetLastError() != cudaSuccess) st = fail(PARAS_E_CUDA, "paras gemm: split-K reduce launch failed");
+                }
+            }
+            const int st2 = paras_b200_free_async(a->gpu, scratch, s);
+            return st != PARAS_OK ? st : st2;
+        }
+    }
     CUtensorMap ma, mb, mb2, mc;
     if (at) {
         if ((st = make_tensor_map_3d(&ma, a->a, a->dtype, a->M, a->K, a->batch, a->lda, a->stride_a, 64, BK)) != PARAS_OK) return st;

@@ -78,6 +78,30 @@ def test_batched_and_strided_operands():
     assert float(out[:, :8].abs().sum()) == 0.0 and float(out[:, 272:].abs().sum()) == 0.0
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("shape", [(64, 4096, 4096), (16, 1024, 2048), (1, 520, 1024), (512, 1032, 3584),
+                                   (130, 128, 4096), (8, 72, 8192), (200, 264, 1536)])
+def test_few_tiles_and_a_long_k_split_the_k_range(shape, dtype):
+    # The projections of a decode step (M = the batch): too few output tiles to fill the GPU, so the
+    # K range runs as slices whose fp32 partial sums a second kernel adds up.  Same tolerance: one
+    # rounding at the end, on either side; with K this long and outputs this few, a handful of results on
+    # the neighbouring 16-bit value already is more than 1 % of them, hence the lower exact share.
+    M, N, K = shape
+    a, w, b = rand((M, K), 1, dtype, 0.5), rand((N, K), 2, dtype, 0.5), rand((K, N), 3, dtype, 0.5)
+    bias = rand((N,), 4, dtype)
+    close16(abi.gemm(a.to(CUDA), w.to(CUDA)), O.linear(a, w), f"A W^T {shape}", exact_share=0.97)
+    close16(abi.gemm(a.to(CUDA), b.to(CUDA), b_layout=abi.GEMM_B_KN), O.mm(a, b), f"A B {shape}", exact_share=0.97)
+    close16(abi.gemm(a.to(CUDA), w.to(CUDA), bias=bias.to(CUDA)), O.linear(a, w, bias), f"bias {shape}", exact_share=0.97)
+    # into a slice of a wider matrix: the columns either side stay untouched
+    out = torch.zeros(M, N + 16, dtype=dtype, device=CUDA)
+    abi.gemm(a.to(CUDA), w.to(CUDA), out=out[:, 8:N + 8])
+    close16(out[:, 8:N + 8], O.linear(a, w), f"strided C {shape}", exact_share=0.97)
+    assert float(out[:, :8].abs().sum()) == 0.0 and float(out[:, N + 8:].abs().sum()) == 0.0
+    # the same call twice gives the same bits (slices are summed in a fixed order)
+    x, y = abi.gemm(a.to(CUDA), w.to(CUDA)), abi.gemm(a.to(CUDA), w.to(CUDA))
+    assert torch.equal(x, y)
+
+
 @pytest.mark.parametrize("shape", [(128, 256, 64), (304, 520, 136), (1000, 264, 392), (520, 128, 1000), (304, 64, 136)])
 def test_transposed_a_operand(shape):
     # A given as [K, M] (rows of M): C = A^T B, with B in either layout
