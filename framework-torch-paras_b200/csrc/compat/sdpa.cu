@@ -101,7 +101,7 @@ int paras_b200_sdpa_workspace_bytes(const paras_sdpa_args* a, size_t* bytes) {
     const int64_t rows = int64_t(a->B) * a->Hq * a->Lq;
     if (pb::sdpa_wants_weights(*a)) return PARAS_OK;   // the two-pass kernel needs no scratch
     switch (pb::choose(g, *a, &why)) {
-        case pb::Path::Tensor: break;
+        case pb::Path::Tensor: *bytes = pb::sdpa_tc_workspace_bytes(g, *a); break;
         case pb::Path::Decode:
             *bytes = pb::split_workspace_bytes(rows, a->D, pb::sdpa_decode_pick_splits(g, *a));
             break;

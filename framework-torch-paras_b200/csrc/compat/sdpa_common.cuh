@@ -56,6 +56,8 @@ struct RopeTables {
 };
 bool sdpa_tc_supported(const Gpu* g, const paras_sdpa_args& a, const char** why);
 int sdpa_tc_launch(Gpu* g, const paras_sdpa_args& a, float scale, cudaStream_t s, const RopeTables* rope = nullptr);
+// scratch of the split-key route (few query blocks, many keys); 0 when the route is not taken
+size_t sdpa_tc_workspace_bytes(const Gpu* g, const paras_sdpa_args& a);
 
 // Tensor-core split-KV decode kernel: 16-bit, D == 128, short Lq, no mask tensor.
 bool sdpa_decode_supported(const Gpu* g, const paras_sdpa_args& a, const char** why);

@@ -114,7 +114,15 @@ struct TcParams {
     int64_t rope_pos0;
     int nq;      // 256-row query blocks per (batch, head)
     int npair;   // ceil(nq / 2)
-    int units;   // B * Hq * npair
+    int units;   // B * Hq * npair * nsplit
+    // Split keys (few query blocks against a long key range): a unit covers kv tiles
+    // [split * split_tiles, (split + 1) * split_tiles) only, and writes its normalised partial
+    // output and its log-sum-exp to scratch rows split * lq_pad + row; a second kernel merges them.
+    int nsplit;         // 1 = off
+    int split_tiles;    // kv tiles per split
+    int split_units;    // units per split = B * Hq * npair
+    int lq_pad;         // nq * 256
+    int64_t lse_bh;     // lse elements per (batch, head): Lq, or nsplit * lq_pad
 };
 
 // One work item = one 256-row query block of one (batch, head).
@@ -123,6 +131,8 @@ struct Item {
     int start[2];  // first query row of each 128-row tile
     int ntile[2];  // kv tiles each query tile visits (0 = tile is past the end of the sequence)
     int n;         // max of the two
+    int kv0;       // first kv tile (0 unless the keys are split)
+    int orow;      // output row offset (split * lq_pad)
 };
 
 __device__ __forceinline__ int kv_tiles_for(const TcParams& p, int start) {
@@ -138,9 +148,16 @@ __device__ __forceinline__ int kv_tiles_for(const TcParams& p, int start) {
 // and the query blocks of one head (and the heads of one GQA group, which are adjacent
 // units) run at the same time, so their K/V tiles are L2 hits.
 // `seq` counts items of this CTA: unit = blockIdx.x + (seq/2)*gridDim.x, half = seq & 1.
+template <bool SPLIT>
 __device__ __forceinline__ bool get_item(const TcParams& p, int seq, Item* it) {
-    const int unit = int(blockIdx.x) + (seq >> 1) * int(gridDim.x);
+    int unit = int(blockIdx.x) + (seq >> 1) * int(gridDim.x);
     if (unit >= p.units) return false;
+    // the split is the slowest index: CTAs that run at the same time work on neighbouring heads of
+    // the same key range, so the heads of a GQA group still find their K/V tiles in L2
+    const int split = SPLIT ? unit / p.split_units : 0;
+    unit -= split * p.split_units;
+    it->kv0 = split * p.split_tiles;
+    it->orow = split * p.lq_pad;
     const int hb = unit / p.npair;
     const int pair = unit - hb * p.npair;
     const int hi = p.nq - 1 - pair;
@@ -153,6 +170,7 @@ __device__ __forceinline__ bool get_item(const TcParams& p, int seq, Item* it) {
     for (int t = 0; t < 2; ++t) {
         it->start[t] = qblk * (kTilesPerCta * BM) + t * BM;
         it->ntile[t] = dup ? 0 : kv_tiles_for(p, it->start[t]);
+        if (SPLIT) it->ntile[t] = min(max(it->ntile[t] - it->kv0, 0), p.split_tiles);
     }
     it->n = max(it->ntile[0], it->ntile[1]);
     return true;
@@ -168,7 +186,9 @@ __device__ __forceinline__ bool any_zero_byte(const uint4& w) {
 // MASK: an explicit attn_mask is applied (a separate instantiation: the unmasked kernel pays
 // nothing for it, not even registers).  ROPE: the query tile is rotated in shared memory, by the
 // softmax warps that own its rows, between its TMA load and the first QK^T (head dim 128).
-template <bool BF16, bool MASK, int HD, bool ROPE = false>
+// SPLIT: units cover a piece of the key range and write partial results (its own instantiation as
+// well: an index added on the softmax chain costs the unsplit kernel 2-3 %).
+template <bool BF16, bool MASK, int HD, bool ROPE = false, bool SPLIT = false>
 __global__ void __launch_bounds__(kThreads, 1)
 sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o,
@@ -240,9 +260,10 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                 return true;
             };
             Item it;
-            for (int seq = 0; ok && get_item(p, seq, &it); ++seq) {
+            for (int seq = 0; ok && get_item<SPLIT>(p, seq, &it); ++seq) {
                 if (it.n == 0) continue;
-                ok = load_entry(&map_k, 0, it.hk, it.b);  // K0 completes the previous item's last pair
+                const int kv0 = SPLIT ? it.kv0 : 0;
+                ok = load_entry(&map_k, kv0 * BN, it.hk, it.b);  // K0 completes the previous item's last pair
                 if (!ok) break;
 #pragma unroll
                 for (int t = 0; t < 2; ++t) {
@@ -259,7 +280,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                     }
                 }
                 for (int x = 1; ok && x < 2 * it.n; ++x)
-                    ok = load_entry((x & 1) ? &map_v : &map_k, (x >> 1) * BN, it.hk, it.b);
+                    ok = load_entry((x & 1) ? &map_v : &map_k, (kv0 + (x >> 1)) * BN, it.hk, it.b);
             }
             if (ok && r > 0) mbar_arrive(bar(kBarKVFull + ((r >> 1) & 1)));  // the last pair has no K
         }
@@ -296,7 +317,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             uint32_t qcnt[2] = {0, 0};   // items that used tile t (Q / O barriers)
             uint32_t pcnt[2] = {0, 0};   // softmax iterations of tile t so far (P barrier)
             Item it;
-            for (int seq = 0; ok && get_item(p, seq, &it); ++seq) {
+            for (int seq = 0; ok && get_item<SPLIT>(p, seq, &it); ++seq) {
                 if (it.n == 0) continue;
                 if (!have) ok = mbar_wait(bar(kBarKVFull + (G & 1)), (G >> 1) & 1, abort_flag, 3);
 #pragma unroll
@@ -364,7 +385,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         uint32_t scnt = 0;  // S tiles consumed so far
         uint32_t ocnt = 0;  // items finished so far
         Item it;
-        for (int seq = 0; ok && get_item(p, seq, &it); ++seq) {
+        for (int seq = 0; ok && get_item<SPLIT>(p, seq, &it); ++seq) {
             const int nt = it.ntile[t];
             if (nt == 0) continue;
             const int row_q = it.start[t] + wq * 32 + lane;
@@ -652,7 +673,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                     tmem_wait_ld();
 #pragma unroll
                     for (int c = 0; c < 4; ++c) tmem_ld_fence32(reinterpret_cast<uint32_t(&)[32]>(s[32 * c]));
-                    const int col0 = j * BN;
+                    const int col0 = SPLIT ? (it.kv0 + j) * BN : j * BN;
                     const bool need_mask = (p.causal && col0 + BN - 1 > it.start[t]) || (col0 + BN > p.Lk);
                     if (need_mask) {
                         const int limit = (p.causal ? min(row_q, p.Lk - 1) : p.Lk - 1) - col0;
@@ -758,13 +779,14 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                     fence_proxy_async_smem();
                     __syncwarp();
                     if (lane == 0 && row_w < p.Lq) {
-                        tma_store_4d(&map_o, o_stage, 64 * (c >> 1), row_w, it.h, it.b);
+                        tma_store_4d(&map_o, o_stage, 64 * (c >> 1), (SPLIT ? it.orow : 0) + row_w, it.h, it.b);
                         tma_store_commit();
                     }
                 }
             }
             if (p.lse && live)
-                p.lse[(int64_t(it.b) * p.Hq + it.h) * p.Lq + row_q] = m * p.scale + logf(l);
+                p.lse[SPLIT ? (int64_t(it.b) * p.Hq + it.h) * p.lse_bh + it.orow + row_q
+                            : (int64_t(it.b) * p.Hq + it.h) * p.Lq + row_q] = m * p.scale + logf(l);
         }
         if (lane == 0) tma_store_wait_read();  // shared memory stays valid until the last store has read it
     }
@@ -784,6 +806,61 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     }
 }
 
+// ---- merge of the split-key partial results ------------------------------------------------
+struct CombineParams {
+    const uint16_t* part_o;   // [B, Hq, nsplit * lq_pad, HD], each split's output normalised by its own sum
+    const float* part_lse;    // [B, Hq, nsplit * lq_pad], natural-log sum of exponentials per split
+    void* out;
+    float* lse;               // [B, Hq, Lq] or null
+    int B, Hq, Lq, Lk, causal, nsplit, split_tiles, lq_pad;
+    int64_t os[3];
+};
+
+// out[row] = sum_s w_s * part_o[s][row] / sum_s w_s,  w_s = exp(lse_s - max_s lse_s).  A thread owns 8
+// columns of a row.  Which splits hold a row follows from the schedule above (a 128-row query tile
+// visits the kv tiles below its causal limit), so scratch needs no initialisation.
+template <bool BF16, int HD>
+__global__ void __launch_bounds__(256) sdpa_tc_combine_kernel(const CombineParams c) {
+    constexpr int kPerRow = HD / 8;
+    const int64_t idx = int64_t(blockIdx.x) * 256 + threadIdx.x;
+    const int64_t row = idx / kPerRow;
+    const int ch = int(idx - row * kPerRow);
+    if (row >= int64_t(c.B) * c.Hq * c.Lq) return;
+    const int64_t bh = row / c.Lq;
+    const int r = int(row - bh * c.Lq);
+    const int tile0 = r & ~(BM - 1);
+    const int lim = c.causal ? min(c.Lk, min(c.Lq, tile0 + BM)) : c.Lk;
+    const int span = c.split_tiles * BN;
+    const int live = min(c.nsplit, (lim + span - 1) / span);
+    const float* pl = c.part_lse + bh * (int64_t(c.nsplit) * c.lq_pad) + r;
+    float mx = -INFINITY;
+    for (int sp = 0; sp < live; ++sp) mx = fmaxf(mx, __ldg(pl + int64_t(sp) * c.lq_pad));
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    float den = 0.f;
+    for (int sp = 0; sp < live; ++sp) {
+        const float w = expf(__ldg(pl + int64_t(sp) * c.lq_pad) - mx);
+        den += w;
+        const uint4 v = __ldg(reinterpret_cast<const uint4*>(
+            c.part_o + ((bh * c.nsplit + sp) * int64_t(c.lq_pad) + r) * HD + 8 * ch));
+        const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            acc[2 * i] = fmaf(w, from16<BF16>(uint16_t(u[i] & 0xffffu)), acc[2 * i]);
+            acc[2 * i + 1] = fmaf(w, from16<BF16>(uint16_t(u[i] >> 16)), acc[2 * i + 1]);
+        }
+    }
+    const float inv = 1.0f / den;
+    uint4 o;
+    o.x = pack16<BF16>(acc[0] * inv, acc[1] * inv);
+    o.y = pack16<BF16>(acc[2] * inv, acc[3] * inv);
+    o.z = pack16<BF16>(acc[4] * inv, acc[5] * inv);
+    o.w = pack16<BF16>(acc[6] * inv, acc[7] * inv);
+    const int b = int(bh / c.Hq), h = int(bh - int64_t(b) * c.Hq);
+    uint16_t* dst = static_cast<uint16_t*>(c.out) + b * c.os[0] + h * c.os[1] + r * c.os[2] + 8 * ch;
+    *reinterpret_cast<uint4*>(dst) = o;
+    if (c.lse && ch == 0) c.lse[row] = mx + logf(den);
+}
+
 // ---- host side -------------------------------------------------------------------------
 // [B, H, L, D] tensor with element strides st = {B, H, L}
 int make_map(CUtensorMap* map, const void* base, int dtype, int B, int H, int L, int D,
@@ -799,7 +876,37 @@ bool strides_ok(const void* base, const int64_t* st, int B, int H, int L, int D)
     return true;
 }
 
+// Few query blocks against many keys (a prompt chunk or a handful of new tokens over a long cache):
+// B * Hq * npair units cannot fill the GPU, so the key range is cut into `nsplit` pieces of
+// `split_tiles` kv tiles.  No mask tensor and no rotary prologue on this route.
+struct SplitPlan { int nsplit, split_tiles, lq_pad; size_t o_bytes, bytes; };
+
+SplitPlan split_plan(const Gpu* g, const paras_sdpa_args& a, bool rope) {
+    SplitPlan sp{1, 1 << 28, 0, 0, 0};
+    if (a.mask || rope || (a.D != 128 && a.D != 64)) return sp;
+    const int nq = (a.Lq + kTilesPerCta * BM - 1) / (kTilesPerCta * BM);
+    const int64_t units = int64_t(a.B) * a.Hq * ((nq + 1) / 2);
+    const int sms = g->sm_count > 0 ? g->sm_count : 148;
+    if (units * 2 > sms) return sp;
+    const int keys = a.causal ? std::min(a.Lk, a.Lq) : a.Lk;
+    const int kv = (keys + BN - 1) / BN;
+    const int want = int(std::min<int64_t>(std::min<int64_t>(sms / units, kv / 4), 32));
+    if (want < 2) return sp;
+    const int per = (kv + want - 1) / want;
+    const int n = (kv + per - 1) / per;
+    if (n < 2) return sp;
+    sp.nsplit = n;
+    sp.split_tiles = per;
+    sp.lq_pad = nq * kTilesPerCta * BM;
+    const size_t rows = size_t(a.B) * a.Hq * n * sp.lq_pad;
+    sp.o_bytes = (rows * a.D * 2 + 255) & ~size_t(255);
+    sp.bytes = sp.o_bytes + rows * sizeof(float);
+    return sp;
+}
+
 }  // namespace
+
+size_t sdpa_tc_workspace_bytes(const Gpu* g, const paras_sdpa_args& a) { return split_plan(g, a, false).bytes; }
 
 bool sdpa_tc_supported(const Gpu* g, const paras_sdpa_args& a, const char** why) {
     *why = "";
@@ -822,14 +929,49 @@ bool sdpa_tc_supported(const Gpu* g, const paras_sdpa_args& a, const char** why)
 int sdpa_tc_launch(Gpu* g, const paras_sdpa_args& a, float scale, cudaStream_t s, const RopeTables* rope) {
     int st = check_status_word(g);  // an earlier launch's failure is reported once, here
     if (st != PARAS_OK) return st;
+    const SplitPlan sp = split_plan(g, a, rope != nullptr);
+    void* scratch = nullptr;
+    bool own = false;
+    if (sp.nsplit > 1) {
+        if (a.workspace) {
+            if (a.workspace_bytes < sp.bytes)
+                return fail(PARAS_E_INVALID, "paras sdpa: workspace of %zu bytes is smaller than %zu", a.workspace_bytes, sp.bytes);
+            if (reinterpret_cast<uintptr_t>(a.workspace) & 15u)
+                return fail(PARAS_E_INVALID, "paras sdpa: workspace must be 16-byte aligned");
+            scratch = a.workspace;
+        } else {
+            if ((st = paras_b200_malloc_async(a.gpu, sp.bytes, s, &scratch)) != PARAS_OK) return st;
+            own = true;
+        }
+    }
+    auto release = [&](int status) {
+        if (!own) return status;
+        const int st2 = paras_b200_free_async(a.gpu, scratch, s);
+        return status != PARAS_OK ? status : st2;
+    };
     CUtensorMap mq, mk, mv, mo;
-    if ((st = make_map(&mq, a.q, a.dtype, a.B, a.Hq, a.Lq, a.D, a.q_strides)) != PARAS_OK) return st;
-    if ((st = make_map(&mk, a.k, a.dtype, a.B, a.Hkv, a.Lk, a.D, a.k_strides)) != PARAS_OK) return st;
-    if ((st = make_map(&mv, a.v, a.dtype, a.B, a.Hkv, a.Lk, a.D, a.v_strides)) != PARAS_OK) return st;
-    if ((st = make_map(&mo, a.out, a.dtype, a.B, a.Hq, a.Lq, a.D, a.o_strides, 32)) != PARAS_OK) return st;
+    if ((st = make_map(&mq, a.q, a.dtype, a.B, a.Hq, a.Lq, a.D, a.q_strides)) != PARAS_OK) return release(st);
+    if ((st = make_map(&mk, a.k, a.dtype, a.B, a.Hkv, a.Lk, a.D, a.k_strides)) != PARAS_OK) return release(st);
+    if ((st = make_map(&mv, a.v, a.dtype, a.B, a.Hkv, a.Lk, a.D, a.v_strides)) != PARAS_OK) return release(st);
+    if (sp.nsplit > 1) {
+        const int rows = sp.nsplit * sp.lq_pad;
+        const int64_t pst[3] = {int64_t(a.Hq) * rows * a.D, int64_t(rows) * a.D, a.D};
+        st = make_map(&mo, scratch, a.dtype, a.B, a.Hq, rows, a.D, pst, 32);
+    } else {
+        st = make_map(&mo, a.out, a.dtype, a.B, a.Hq, a.Lq, a.D, a.o_strides, 32);
+    }
+    if (st != PARAS_OK) return release(st);
     TcParams p{};
     p.out = a.out;
     p.lse = a.lse;
+    p.nsplit = sp.nsplit;
+    p.split_tiles = sp.split_tiles;
+    p.lq_pad = sp.lq_pad;
+    p.lse_bh = a.Lq;
+    if (sp.nsplit > 1) {
+        p.lse = reinterpret_cast<float*>(static_cast<uint8_t*>(scratch) + sp.o_bytes);
+        p.lse_bh = int64_t(sp.nsplit) * sp.lq_pad;
+    }
     p.B = a.B; p.Hq = a.Hq; p.Hkv = a.Hkv; p.Lq = a.Lq; p.Lk = a.Lk;
     for (int i = 0; i < 3; ++i) p.os[i] = a.o_strides[i];
     p.causal = a.causal;
@@ -848,8 +990,9 @@ int sdpa_tc_launch(Gpu* g, const paras_sdpa_args& a, float scale, cudaStream_t s
     }
     p.nq = (a.Lq + kTilesPerCta * BM - 1) / (kTilesPerCta * BM);
     p.npair = (p.nq + 1) / 2;
-    const int64_t units = int64_t(a.B) * a.Hq * p.npair;
-    if (units > INT32_MAX) return fail(PARAS_E_UNSUPPORTED, "paras sdpa: too many work units");
+    p.split_units = int(std::min<int64_t>(int64_t(a.B) * a.Hq * p.npair, INT32_MAX));
+    const int64_t units = int64_t(a.B) * a.Hq * p.npair * p.nsplit;
+    if (units > INT32_MAX) return release(fail(PARAS_E_UNSUPPORTED, "paras sdpa: too many work units"));
     p.units = int(units);
     const int sms = g->sm_count > 0 ? g->sm_count : 148;
     dim3 grid(unsigned(units < sms ? units : sms));  // persistent: one CTA per SM
@@ -859,7 +1002,10 @@ int sdpa_tc_launch(Gpu* g, const paras_sdpa_args& a, float scale, cudaStream_t s
         return PARAS_OK;
     };
     const bool bf = a.dtype == PARAS_BF16;
-    if (rope) {
+    if (sp.nsplit > 1) {
+        if (a.D == 128) st = bf ? launch(sdpa_tc_kernel<true, false, 128, false, true>) : launch(sdpa_tc_kernel<false, false, 128, false, true>);
+        else st = bf ? launch(sdpa_tc_kernel<true, false, 64, false, true>) : launch(sdpa_tc_kernel<false, false, 64, false, true>);
+    } else if (rope) {
         st = bf ? launch(sdpa_tc_kernel<true, false, 128, true>) : launch(sdpa_tc_kernel<false, false, 128, true>);
     } else if (a.D == 128) {
         if (p.mask_kind) st = bf ? launch(sdpa_tc_kernel<true, true, 128>) : launch(sdpa_tc_kernel<false, true, 128>);
@@ -868,9 +1014,29 @@ int sdpa_tc_launch(Gpu* g, const paras_sdpa_args& a, float scale, cudaStream_t s
         if (p.mask_kind) st = bf ? launch(sdpa_tc_kernel<true, true, 64>) : launch(sdpa_tc_kernel<false, true, 64>);
         else st = bf ? launch(sdpa_tc_kernel<true, false, 64>) : launch(sdpa_tc_kernel<false, false, 64>);
     }
-    if (st != PARAS_OK) return st;
-    PB_LAUNCH_CHECK("sdpa_tc_kernel");
-    return PARAS_OK;
+    if (st != PARAS_OK) return release(st);
+    if (cudaGetLastError() != cudaSuccess) return release(fail(PARAS_E_CUDA, "paras sdpa: sdpa_tc_kernel launch failed"));
+    if (sp.nsplit > 1) {
+        CombineParams c{};
+        c.part_o = static_cast<const uint16_t*>(scratch);
+        c.part_lse = p.lse;
+        c.out = a.out;
+        c.lse = a.lse;
+        c.B = a.B; c.Hq = a.Hq; c.Lq = a.Lq; c.Lk = a.Lk; c.causal = a.causal;
+        c.nsplit = sp.nsplit; c.split_tiles = sp.split_tiles; c.lq_pad = sp.lq_pad;
+        for (int i = 0; i < 3; ++i) c.os[i] = a.o_strides[i];
+        const int64_t threads = int64_t(a.B) * a.Hq * a.Lq * (a.D / 8);
+        const unsigned blocks = unsigned((threads + 255) / 256);
+        if (a.D == 128) {
+            if (bf) sdpa_tc_combine_kernel<true, 128><<<blocks, 256, 0, s>>>(c);
+            else sdpa_tc_combine_kernel<false, 128><<<blocks, 256, 0, s>>>(c);
+        } else {
+            if (bf) sdpa_tc_combine_kernel<true, 64><<<blocks, 256, 0, s>>>(c);
+            else sdpa_tc_combine_kernel<false, 64><<<blocks, 256, 0, s>>>(c);
+        }
+        if (cudaGetLastError() != cudaSuccess) return release(fail(PARAS_E_CUDA, "paras sdpa: combine launch failed"));
+    }
+    return release(PARAS_OK);
 }
 
 }  // namespace pb

@@ -234,6 +234,43 @@ def test_sdpa_simt_and_tensor_kernels_agree():
     assert (a.float() - b.float()).abs().max().item() <= 2e-2
 
 
+SPLIT_KEY_CASES = [
+    # B, Hq, Hkv, Lq,  Lk,   D,  causal: few query blocks against many keys on the tensor-core kernel
+    (1, 8, 2, 300, 5000, 128, False),     # a prompt chunk over a long cache, GQA, ragged both ways
+    (2, 4, 4, 64, 4096, 64, False),       # D = 64, one query tile
+    (1, 4, 4, 1500, 3000, 128, True),     # causal: later key ranges hold only the later query tiles
+    (1, 2, 1, 520, 2100, 128, False),     # three query blocks (the middle one has no partner)
+    (1, 3, 3, 17, 8200, 128, False),      # more rows than the decode kernel takes
+]
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("case", SPLIT_KEY_CASES)
+def test_split_keys_on_the_tensor_core_kernel(case, dtype):
+    # Too few (batch, head, query block) units to fill the GPU: the key range is cut into pieces that
+    # run as separate units, and a second kernel merges the partial outputs by their log-sum-exp.
+    B, Hq, Hkv, Lq, Lk, D, causal = case
+    q, k, v = _qkv(B, Hq, Hkv, Lq, Lk, D, dtype, seed=hash(case) % 10000)
+    want = O.sdpa(q, k, v, is_causal=causal, enable_gqa=Hq != Hkv)
+    qd, kd, vd = q.to(DEV), k.to(DEV), v.to(DEV)
+    got, lse = abi.sdpa_fwd(qd, kd, vd, causal=causal, return_lse=True, flags=abi.SDPA_REF_SCALE | abi.SDPA_FORCE_TENSOR)
+    assert abi.sdpa_last_kernel() == "tcgen05"
+    need = abi.sdpa_workspace_bytes(qd, kd, vd, causal=causal, flags=abi.SDPA_FORCE_TENSOR)
+    assert need > 0, "this shape was meant to take the split-key route"
+    tol_check(got, want, f"split keys {case} {dtype}")
+    sc = float(torch.tensor(1 / math.sqrt(D)).to(dtype))
+    kk = k.repeat_interleave(Hq // Hkv, 1)
+    s = (q.double() @ kk.double().transpose(-1, -2)) * sc
+    if causal:
+        s = s.masked_fill(~torch.ones(Lq, Lk, dtype=torch.bool).tril(), float("-inf"))
+    assert torch.allclose(lse.cpu().double(), torch.logsumexp(s, -1), atol=2e-3, rtol=2e-3)
+    # caller-owned scratch gives the same bits, and a scratch that is too small is refused
+    ws = torch.empty(need, dtype=torch.uint8, device=DEV)
+    assert torch.equal(abi.sdpa_fwd(qd, kd, vd, causal=causal, workspace=ws, flags=abi.SDPA_REF_SCALE | abi.SDPA_FORCE_TENSOR), got)
+    with pytest.raises(RuntimeError):
+        abi.sdpa_fwd(qd, kd, vd, causal=causal, workspace=ws[:need // 2], flags=abi.SDPA_REF_SCALE | abi.SDPA_FORCE_TENSOR)
+
+
 def test_sdpa_strided_inputs_and_lse():
     # [B, L, H, D] storage viewed as [B, H, L, D]: what a fused QKV projection produces
     g = torch.Generator().manual_seed(3)
