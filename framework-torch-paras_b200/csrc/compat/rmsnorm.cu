@@ -466,6 +466,154 @@ rmsnorm_bwd_rows_kernel(const T* __restrict__ go, const T* __restrict__ x, const
                 make_float4(dwacc[i * N + e], dwacc[i * N + e + 1], dwacc[i * N + e + 2], dwacc[i * N + e + 3]);
 }
 
+// The same with the rows arriving through a three-deep ring in shared memory (cp.async, 16 bytes per
+// copy, each thread copying exactly the vectors it reads back, so the ring needs no barrier): the loads
+// of the next two rows are in flight while a row is reduced and written.  The plain kernel above has a
+// CTA's loads outstanding only between its store and its reduction, about half the time, and
+// reaches 0.59 of the HBM peak at [16384, 4096]; bytes in flight are what it lacks.
+constexpr int kBwdStages = 3;
+
+// Registers a thread of the ring kernel needs, roughly: R rows of grad_out and x (V 16-byte vectors each),
+// V*N grad_weight sums, the weight, and addressing.  Decides, on both sides of the launch, how many
+// CTAs (one or two) share an SM.
+// (An estimate on the generous side: a second CTA that squeezes the kernel into spills costs more than it
+// brings: [16384, 4096] bf16 went from 0.074 to 0.161 ms under a bound of three CTAs.)
+constexpr int bwd_regs(int v, int n, int r) { return 12 * v * r + v * n + 4 * v + 40; }
+constexpr int bwd_ctas(int threads, int v, int n, int r) { return bwd_regs(v, n, r) * threads * 2 <= 65536 ? 2 : 1; }
+
+__device__ __forceinline__ void cp_async16(uint32_t dst_smem, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+template <typename T, int V, int THREADS, int R, bool TAIL>
+__global__ void __launch_bounds__(THREADS, bwd_ctas(THREADS, V, Vec16<T>::N, R))
+rmsnorm_bwd_rows_pipe_kernel(const T* __restrict__ go, const T* __restrict__ x, const T* __restrict__ w,
+                             const float* __restrict__ rstd, T* __restrict__ gx, float* __restrict__ dw_part,
+                             int64_t rows, int64_t H) {
+    // A step is R consecutive rows: their reductions run side by side and share one barrier, which is
+    // what a CTA's time per row mostly consists of once the loads are ahead.
+    constexpr int N = Vec16<T>::N;
+    extern __shared__ __align__(16) unsigned char ring_raw[];   // [stage][row of the step][go | x][THREADS * V] vectors
+    __shared__ float red[2][R][THREADS / 32];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t ring = static_cast<uint32_t>(__cvta_generic_to_shared(ring_raw));
+    constexpr uint32_t kHalf = THREADS * V * 16, kRow = 2 * kHalf, kStage = R * kRow;
+    const int64_t steps = (rows + R - 1) / R;
+    // V = ceil(vectors per row / THREADS): only a thread's last vector can lie past the end of the row, and
+    // only in the TAIL instantiation (its own: the checks cost the kernel that sits at the register limit 12 %)
+    const bool last_ok = !TAIL || int64_t(tid) + int64_t(THREADS) * (V - 1) < H / N;
+    Vec16<T> zero;
+#pragma unroll
+    for (int e = 0; e < N; ++e) zero.v[e] = from_f32<T>(0.f);
+    auto issue = [&](int64_t step, int stage) {
+        if (step < steps) {
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                const int64_t row = step * R + r;
+                if (row < rows) {
+                    const T* gr = go + row * H;
+                    const T* xr = x + row * H;
+#pragma unroll
+                    for (int i = 0; i < V; ++i) {
+                        if (i == V - 1 && !last_ok) break;
+                        const uint32_t off = (uint32_t(tid) + uint32_t(THREADS) * i) * 16;
+                        cp_async16(ring + stage * kStage + r * kRow + off, gr + (int64_t(tid) + int64_t(THREADS) * i) * N);
+                        cp_async16(ring + stage * kStage + r * kRow + kHalf + off, xr + (int64_t(tid) + int64_t(THREADS) * i) * N);
+                    }
+                }
+            }
+        }
+        cp_async_commit();   // an empty group past the last step keeps the group count uniform
+    };
+    Vec16<T> wv[V];
+#pragma unroll
+    for (int i = 0; i < V; ++i) wv[i] = (i < V - 1 || last_ok) ? ld16(w + (int64_t(tid) + int64_t(THREADS) * i) * N) : zero;
+    float dwacc[V * N];
+#pragma unroll
+    for (int i = 0; i < V * N; ++i) dwacc[i] = 0.f;
+    const float inv_h = 1.0f / float(H);
+#pragma unroll
+    for (int st = 0; st < kBwdStages - 1; ++st) issue(int64_t(blockIdx.x) + int64_t(st) * gridDim.x, st);
+    int flip = 0, stage = 0;
+    float rr_next[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) rr_next[r] = rstd[min(int64_t(blockIdx.x) * R + r, rows - 1)];
+    for (int64_t step = blockIdx.x; step < steps; step += gridDim.x, flip ^= 1) {
+        // the stage refilled here is the one this thread emptied in the previous iteration
+        issue(step + int64_t(kBwdStages - 1) * gridDim.x, stage == 0 ? kBwdStages - 1 : stage - 1);
+        float rr[R];
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            rr[r] = rr_next[r];   // a scalar miss of its own: asked for a step ahead
+            rr_next[r] = rstd[min((step + gridDim.x) * R + r, rows - 1)];
+        }
+        cp_async_wait<kBwdStages - 1>();
+        Vec16<T> gv[R][V], xv[R][V];
+#pragma unroll
+        for (int r = 0; r < R; ++r)
+#pragma unroll
+            for (int i = 0; i < V; ++i) {
+                const uint32_t off = (uint32_t(tid) + uint32_t(THREADS) * i) * 16;
+                gv[r][i] = *reinterpret_cast<const Vec16<T>*>(ring_raw + stage * kStage + r * kRow + off);
+                xv[r][i] = *reinterpret_cast<const Vec16<T>*>(ring_raw + stage * kStage + r * kRow + kHalf + off);
+                if (i == V - 1 && !last_ok) gv[r][i] = xv[r][i] = zero;   // nothing was copied there
+            }
+        stage = stage + 1 == kBwdStages ? 0 : stage + 1;
+        float dot[R];
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            dot[r] = 0.f;
+#pragma unroll
+            for (int i = 0; i < V; ++i)
+#pragma unroll
+                for (int e = 0; e < N; ++e)
+                    dot[r] = fmaf(to_f32<T>(gv[r][i].v[e]) * to_f32<T>(wv[i].v[e]), to_f32<T>(xv[r][i].v[e]), dot[r]);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+            for (int r = 0; r < R; ++r) dot[r] += __shfl_xor_sync(0xffffffffu, dot[r], o);
+        if (lane == 0) {
+#pragma unroll
+            for (int r = 0; r < R; ++r) red[flip][r][warp] = dot[r];
+        }
+        __syncthreads();          // (the buffer alternates: the next step's writes cannot overtake these reads)
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const int64_t row = step * R + r;
+            if (row >= rows) break;   // the same for every thread; rows past the end hold stale ring data
+            float d = 0.f;
+#pragma unroll
+            for (int i = 0; i < THREADS / 32; ++i) d += red[flip][r][i];
+            const float coef = rr[r] * rr[r] * rr[r] * inv_h * d;
+            T* out = gx + row * H;
+#pragma unroll
+            for (int i = 0; i < V; ++i) {
+                Vec16<T> o;
+#pragma unroll
+                for (int e = 0; e < N; ++e) {
+                    const float g = to_f32<T>(gv[r][i].v[e]), xe = to_f32<T>(xv[r][i].v[e]);
+                    o.v[e] = from_f32<T>(fmaf(g * to_f32<T>(wv[i].v[e]), rr[r], -coef * xe));
+                    dwacc[i * N + e] = fmaf(g * xe, rr[r], dwacc[i * N + e]);
+                }
+                if (i < V - 1 || last_ok) st16_stream(out + (int64_t(tid) + int64_t(THREADS) * i) * N, o);
+            }
+        }
+    }
+    cp_async_wait<0>();
+    float* part = dw_part + int64_t(blockIdx.x) * H;
+#pragma unroll
+    for (int i = 0; i < V; ++i)
+#pragma unroll
+        for (int e = 0; e < N; e += 4)
+            if (i < V - 1 || last_ok) *reinterpret_cast<float4*>(part + (int64_t(tid) + int64_t(THREADS) * i) * N + e) =
+                make_float4(dwacc[i * N + e], dwacc[i * N + e + 1], dwacc[i * N + e + 2], dwacc[i * N + e + 3]);
+}
+
 // grad_weight[j] = sum over the partial rows: 16 threads per column take every sixteenth partial.
 template <typename T>
 __global__ void __launch_bounds__(1024)
@@ -486,6 +634,44 @@ rmsnorm_bwd_dw_reduce_kernel(const float* __restrict__ dw_part, T* __restrict__ 
         for (int i = 0; i < 16; ++i) t += sh[i][cx];
         gw[col] = from_f32<T>(float(t));
     }
+}
+
+struct BwdRowsArgs {
+    const void *go, *x, *w;
+    const float* rstd;
+    void* gx;
+    float* part;
+    int64_t rows, H;
+    int parts;
+    bool pipe, tail;
+    int rstep;
+    size_t ring;
+    cudaStream_t s;
+};
+
+template <typename T, int V, int THREADS, int R, bool TAIL = false>
+void launch_bwd_pipe(const BwdRowsArgs& a) {
+    cudaFuncSetAttribute(rmsnorm_bwd_rows_pipe_kernel<T, V, THREADS, R, TAIL>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(a.ring));
+    rmsnorm_bwd_rows_pipe_kernel<T, V, THREADS, R, TAIL><<<a.parts, THREADS, a.ring, a.s>>>(
+        static_cast<const T*>(a.go), static_cast<const T*>(a.x), static_cast<const T*>(a.w), a.rstd, static_cast<T*>(a.gx),
+        a.part, a.rows, a.H);
+}
+
+template <typename T, int V, int THREADS>
+void launch_bwd_rows(const BwdRowsArgs& a) {
+    if (a.pipe) {
+        if (a.tail) return launch_bwd_pipe<T, V, THREADS, 1, true>(a);
+        if constexpr (V <= 2) {
+            if (a.rstep == 4) return launch_bwd_pipe<T, V, THREADS, 4>(a);
+        }
+        if constexpr (V <= 4) {
+            if (a.rstep == 2) return launch_bwd_pipe<T, V, THREADS, 2>(a);
+        }
+        return launch_bwd_pipe<T, V, THREADS, 1>(a);
+    }
+    rmsnorm_bwd_rows_kernel<T, V, THREADS><<<a.parts, THREADS, 0, a.s>>>(
+        static_cast<const T*>(a.go), static_cast<const T*>(a.x), static_cast<const T*>(a.w), a.rstd, static_cast<T*>(a.gx),
+        a.part, a.rows, a.H);
 }
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -632,28 +818,47 @@ int paras_b200_rmsnorm_bwd(int gpu, const void* grad_out, const void* x, const v
         const int64_t nvec = H * int64_t(pb::dtype_size(dtype)) / 16;
         const bool vec_ok = (H * int64_t(pb::dtype_size(dtype))) % 16 == 0 && pb::aligned16(grad_out) && pb::aligned16(x) &&
                             pb::aligned16(weight) && pb::aligned16(grad_x);
+        // CTA size by row length, so that a thread holds at most 4 (last resort 8) vectors of a row; the ring
+        // kernel takes rows that do not fill the last vector slot of every thread
         int threads = 0;
-        if (vec_ok && nvec % 128 == 0 && nvec / 128 <= 8) threads = 128;
-        else if (vec_ok && nvec % 256 == 0 && nvec / 256 <= 8) threads = 256;
+        if (vec_ok) threads = nvec <= 512 ? 128 : nvec <= 1024 ? 256 : nvec <= 4096 ? 512 : 0;
         if (threads) {
-            const int v = int(nvec / threads);
-            const int parts = int(std::min<int64_t>(rows, int64_t(sms) * (threads == 128 ? 4 : 2)));
+            const int v = int((nvec + threads - 1) / threads);
+            // The ring variant: three stages of 1, 2 or 4 rows (grad_out and x) in shared memory, one or two
+            // CTAs per SM as registers and shared memory allow.  Measured at [16384, 4096] bf16: 0.104 ms
+            // without the ring, 0.085 with four CTAs per SM and one row per step, 0.074-0.076 with two CTAs
+            // and two rows per step (fewer partial rows of grad_weight as well).
+            const int nper = int(16 / pb::dtype_size(dtype));
+            const size_t slot_bytes = size_t(threads) * v * 16;   // a row in the ring
+            int rstep = 0, pipe_ctas = 1;
+            const bool tail = nvec % threads != 0;
+            for (int r = tail ? 1 : 4; r >= 1 && !rstep; r >>= 1) {
+                if ((r == 4 && v > 2) || (r == 2 && v > 4)) continue;   // (not instantiated: too many registers)
+                if (pb::bwd_regs(v, nper, r) * threads > 65536) continue;
+                int ctas = pb::bwd_ctas(threads, v, nper, r);
+                const size_t per_cta = size_t(pb::kBwdStages) * 2 * slot_bytes * r;
+                while (ctas > 1 && per_cta * ctas > 200 * 1024) --ctas;
+                if (per_cta * ctas <= 200 * 1024) { rstep = r; pipe_ctas = ctas; }
+            }
+            const size_t ring = size_t(pb::kBwdStages) * 2 * slot_bytes * (rstep ? rstep : 1);
+            const bool pipe = rstep && rows >= int64_t(sms) * pipe_ctas * rstep;
+            if (pipe || nvec % threads == 0) {   // (the plain one-pass kernel wants full slots)
+            const int parts = int(std::min<int64_t>(rows, int64_t(sms) * (pipe ? pipe_ctas : threads == 128 ? 4 : threads == 256 ? 2 : 1)));
             void* scratch = nullptr;
             st = paras_b200_malloc_async(gpu, size_t(parts) * size_t(H) * sizeof(float), s, &scratch);
             if (st != PARAS_OK) return st;
             float* part = static_cast<float*>(scratch);
-#define PB_ROWS(T, V, TH)                                                                                        \
-    pb::rmsnorm_bwd_rows_kernel<T, V, TH><<<parts, TH, 0, s>>>(static_cast<const T*>(grad_out), static_cast<const T*>(x), \
-        static_cast<const T*>(weight), rstd, static_cast<T*>(grad_x), part, rows, H)
+            const pb::BwdRowsArgs ra{grad_out, x, weight, rstd, grad_x, part, rows, H, parts, pipe, tail, rstep, ring, s};
 #define PB_ROWS_V(T, TH)                                                                                         \
     switch (v) {                                                                                                 \
-        case 1: PB_ROWS(T, 1, TH); break; case 2: PB_ROWS(T, 2, TH); break; case 3: PB_ROWS(T, 3, TH); break;     \
-        case 4: PB_ROWS(T, 4, TH); break; case 5: PB_ROWS(T, 5, TH); break; case 6: PB_ROWS(T, 6, TH); break;     \
-        case 7: PB_ROWS(T, 7, TH); break; default: PB_ROWS(T, 8, TH); break;                                      \
+        case 1: pb::launch_bwd_rows<T, 1, TH>(ra); break; case 2: pb::launch_bwd_rows<T, 2, TH>(ra); break;       \
+        case 3: pb::launch_bwd_rows<T, 3, TH>(ra); break; case 4: pb::launch_bwd_rows<T, 4, TH>(ra); break;       \
+        case 5: pb::launch_bwd_rows<T, 5, TH>(ra); break; case 6: pb::launch_bwd_rows<T, 6, TH>(ra); break;       \
+        case 7: pb::launch_bwd_rows<T, 7, TH>(ra); break; default: pb::launch_bwd_rows<T, 8, TH>(ra); break;      \
     }
 #define PB_ROWS_T(T)                                                                                             \
     do {                                                                                                         \
-        if (threads == 128) { PB_ROWS_V(T, 128) } else { PB_ROWS_V(T, 256) }                                     \
+        if (threads == 128) { PB_ROWS_V(T, 128) } else if (threads == 256) { PB_ROWS_V(T, 256) } else { PB_ROWS_V(T, 512) } \
         pb::rmsnorm_bwd_dw_reduce_kernel<T><<<int((H + 63) / 64), 1024, 0, s>>>(part, static_cast<T*>(grad_weight), parts, H); \
     } while (0)
             switch (dtype) {
@@ -663,10 +868,10 @@ int paras_b200_rmsnorm_bwd(int gpu, const void* grad_out, const void* x, const v
             }
 #undef PB_ROWS_T
 #undef PB_ROWS_V
-#undef PB_ROWS
             st = cudaGetLastError() == cudaSuccess ? PARAS_OK : fail(PARAS_E_CUDA, "paras rms_norm_backward: kernel launch failed");
             const int st2 = paras_b200_free_async(gpu, scratch, s);
             return st != PARAS_OK ? st : st2;
+            }
         }
     }
     int64_t blocks = (rows + pb::kWarpsPerBlock - 1) / pb::kWarpsPerBlock;

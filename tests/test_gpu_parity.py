@@ -481,6 +481,38 @@ def test_backward_ops_and_rotate_half_against_oracle():
         assert torch.equal(abi.rotate_half(r.to(DEV), backward=True).cpu(), O.rotate_half_backward(r))
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32, torch.float16])
+@pytest.mark.parametrize("shape", [
+    (1300, 4096),    # ring in shared memory, two rows a step
+    (2500, 1024),    # four rows a step
+    (700, 7168),     # the last vector slot of some threads lies past the row
+    (650, 5120),
+    (333, 8192),     # 256 / 512 threads
+    (301, 16384),
+    (100, 4096),     # too few rows for the ring: the plain one-pass kernel
+    (1300, 4104),    # a row length that no CTA size divides
+    (41, 1000),      # rows that are not whole 16-byte vectors in fp16/bf16 ... the two-kernel route
+    (1187, 2048),    # an odd row count: the last step of some CTAs is half empty
+])
+def test_rmsnorm_backward_row_kernels_against_oracle(shape, dtype):
+    rows, H = shape
+    g = torch.Generator().manual_seed(rows + H)
+    x = torch.randn(rows, H, generator=g).to(dtype)
+    w = (1 + 0.1 * torch.randn(H, generator=g)).to(dtype)
+    go = torch.randn(rows, H, generator=g).to(dtype)
+    _, rstd = O.rms_norm_fused(x, w, 1e-6)
+    gx, gw = abi.rmsnorm_bwd(go.to(DEV), x.to(DEV), w.to(DEV), rstd.to(DEV))
+    gxo, gwo = O.rms_norm_fused_backward(go, x, w, rstd)
+    tol_check(gx, gxo, f"rms_norm_backward dx {shape}")
+    # grad_weight sums `rows` products per column: the oracle adds them in the tensors' order in fp32, the
+    # kernel per CTA in fp32 and across CTAs in double; both round once at the end
+    ref = (go.double() * x.double() * rstd.double()[:, None]).sum(0)
+    err = (gw.cpu().double() - ref).abs().max().item()
+    ulp = 2.0 ** -8 if dtype == torch.bfloat16 else (2.0 ** -11 if dtype == torch.float16 else 2.0 ** -20)
+    assert err <= ulp * max(1.0, ref.abs().max().item()) + 1e-3, f"dw {shape}: {err:.3e}"
+    assert (gw.cpu().double() - gwo.double()).abs().max().item() <= 2e-2 * max(1.0, gwo.abs().max().item())
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("kind", ["padding", "per_row_bool", "additive", "additive_f32"])
 def test_decode_kernel_with_explicit_masks(kind, dtype):
