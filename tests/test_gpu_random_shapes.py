@@ -80,3 +80,40 @@ def test_random_shapes_forward_and_backward(seed):
             rel = (got_g.cpu().double() - want_g).abs().max().item() / scale
             assert rel <= (2e-4 if dtype == torch.float32 else 2e-2), f"{tag}: {name} off by {rel:.3e} of its scale"
     assert {"tcgen05", "simt"} <= seen, seen
+
+
+@pytest.mark.parametrize("seed", [21, 22])
+def test_random_long_key_ranges(seed):
+    """Few query blocks against long key ranges, the shapes whose key range the tensor-core kernel cuts
+    into pieces: forward, the log-sum-exp the pieces are merged with, and the fused backward fed by it."""
+    rnd = random.Random(seed)
+    for it in range(16):
+        dtype = rnd.choice([torch.bfloat16, torch.float16])
+        D = rnd.choice([128, 128, 64])
+        Hkv = rnd.choice([1, 2])
+        Hq = Hkv * rnd.choice([1, 2, 4])
+        B = rnd.choice([1, 2])
+        Lq = rnd.choice([17, 64, 128, 200, 300, 520, 1100])
+        Lk = rnd.choice([1000, 1500, 2047, 2048, 3000, 4100])
+        causal = rnd.random() < 0.3
+        g = torch.Generator().manual_seed(seed * 1000 + it)
+        q = torch.randn(B, Hq, Lq, D, generator=g).to(dtype)
+        k = torch.randn(B, Hkv, Lk, D, generator=g).to(dtype)
+        v = torch.randn(B, Hkv, Lk, D, generator=g).to(dtype)
+        do = torch.randn(B, Hq, Lq, D, generator=g).to(dtype)
+        tag = f"seed {seed} case {it}: {dtype} B{B} Hq{Hq} Hkv{Hkv} Lq{Lq} Lk{Lk} D{D} causal={causal}"
+        qd, kd, vd = q.to(DEV), k.to(DEV), v.to(DEV)
+        o, lse = abi.sdpa_fwd(qd, kd, vd, causal=causal, return_lse=True, flags=abi.SDPA_FORCE_TENSOR)
+        q64, k64, v64 = (t.double().requires_grad_(True) for t in (q, k, v))
+        s = scores64(q64, k64, causal, None)
+        want = torch.softmax(s, -1) @ v64.repeat_interleave(Hq // Hkv, 1)
+        err = (o.cpu().double() - want.detach()).abs().max().item()
+        assert err <= 2e-2, f"{tag}: forward max-abs {err:.3e}"
+        lerr = (lse.cpu().double() - torch.logsumexp(s.detach(), -1)).abs().max().item()
+        assert lerr <= 2e-3, f"{tag}: lse off by {lerr:.3e}"
+        want.backward(do.double())
+        grads = abi.sdpa_bwd(do.to(DEV), qd, kd, vd, o, lse, causal=causal)
+        for got_g, want_g, name in zip(grads, (q64.grad, k64.grad, v64.grad), ("dq", "dk", "dv")):
+            scale = max(want_g.abs().max().item(), 1e-2)
+            rel = (got_g.cpu().double() - want_g).abs().max().item() / scale
+            assert rel <= 2e-2, f"{tag}: {name} off by {rel:.3e} of its scale"
