@@ -137,8 +137,9 @@ int paras_b200_sdpa_fwd(const paras_sdpa_args* a) {
         return fail(PARAS_E_UNSUPPORTED, "paras sdpa: tensor-core kernel unavailable: %s", why);
 
     if (path == pb::Path::Tensor) {
-        st = pb::sdpa_tc_launch(g, *a, scale, s);
-        if (st == PARAS_OK) pb::set_last_kernel("tcgen05");
+        const char* variant = "tcgen05";
+        st = pb::sdpa_tc_launch(g, *a, scale, s, nullptr, &variant);
+        if (st == PARAS_OK) pb::set_last_kernel(variant);
         return st;
     }
 

@@ -55,7 +55,10 @@ struct RopeTables {
     int64_t pos0;
 };
 bool sdpa_tc_supported(const Gpu* g, const paras_sdpa_args& a, const char** why);
-int sdpa_tc_launch(Gpu* g, const paras_sdpa_args& a, float scale, cudaStream_t s, const RopeTables* rope = nullptr);
+// `variant` (optional) receives the name of the route taken: "tcgen05", "tcgen05_split" (key range in pieces),
+// "tcgen05_packed" (the heads of a GQA group in one item), "tcgen05_packed_split", "tcgen05_rope"
+int sdpa_tc_launch(Gpu* g, const paras_sdpa_args& a, float scale, cudaStream_t s, const RopeTables* rope = nullptr,
+                   const char** variant = nullptr);
 // scratch of the split-key route (few query blocks, many keys); 0 when the route is not taken
 size_t sdpa_tc_workspace_bytes(const Gpu* g, const paras_sdpa_args& a);
 

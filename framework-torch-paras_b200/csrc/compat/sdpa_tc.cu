@@ -123,6 +123,10 @@ struct TcParams {
     int split_units;    // units per split = B * Hq * npair
     int lq_pad;         // nq * 256
     int64_t lse_bh;     // lse elements per (batch, head): Lq, or nsplit * lq_pad
+    // Packed GQA groups (PACK): an item is one (batch, kv head); its 256 rows are the group's query heads,
+    // 2^pack_shift rows each (Lq <= 2^pack_shift), so a few query positions of 2, 4 or 8 heads fill both
+    // tiles against one pass over K/V.  Units are (split, batch, kv head); lq_pad = 2^pack_shift.
+    int pack_shift;
 };
 
 // One work item = one 256-row query block of one (batch, head).
@@ -148,8 +152,27 @@ __device__ __forceinline__ int kv_tiles_for(const TcParams& p, int start) {
 // and the query blocks of one head (and the heads of one GQA group, which are adjacent
 // units) run at the same time, so their K/V tiles are L2 hits.
 // `seq` counts items of this CTA: unit = blockIdx.x + (seq/2)*gridDim.x, half = seq & 1.
-template <bool SPLIT>
+template <bool SPLIT, bool PACK>
 __device__ __forceinline__ bool get_item(const TcParams& p, int seq, Item* it) {
+    if (PACK) {
+        int unit = int(blockIdx.x) + seq * int(gridDim.x);
+        if (unit >= p.units) return false;
+        const int split = SPLIT ? unit / p.split_units : 0;
+        unit -= split * p.split_units;
+        it->kv0 = split * p.split_tiles;
+        it->orow = split * p.lq_pad;
+        it->b = unit / p.Hkv;
+        it->hk = unit - it->b * p.Hkv;
+        it->h = it->hk * (p.Hq / p.Hkv);   // first head of the group
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+            it->start[t] = 0;              // every row of the item is a query position below 2^pack_shift
+            it->ntile[t] = kv_tiles_for(p, 0);
+            if (SPLIT) it->ntile[t] = min(max(it->ntile[t] - it->kv0, 0), p.split_tiles);
+        }
+        it->n = it->ntile[0];
+        return true;
+    }
     int unit = int(blockIdx.x) + (seq >> 1) * int(gridDim.x);
     if (unit >= p.units) return false;
     // the split is the slowest index: CTAs that run at the same time work on neighbouring heads of
@@ -188,7 +211,7 @@ __device__ __forceinline__ bool any_zero_byte(const uint4& w) {
 // softmax warps that own its rows, between its TMA load and the first QK^T (head dim 128).
 // SPLIT: units cover a piece of the key range and write partial results (its own instantiation as
 // well: an index added on the softmax chain costs the unsplit kernel 2-3 %).
-template <bool BF16, bool MASK, int HD, bool ROPE = false, bool SPLIT = false>
+template <bool BF16, bool MASK, int HD, bool ROPE = false, bool SPLIT = false, bool PACK = false>
 __global__ void __launch_bounds__(kThreads, 1)
 sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o,
@@ -260,7 +283,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                 return true;
             };
             Item it;
-            for (int seq = 0; ok && get_item<SPLIT>(p, seq, &it); ++seq) {
+            for (int seq = 0; ok && get_item<SPLIT, PACK>(p, seq, &it); ++seq) {
                 if (it.n == 0) continue;
                 const int kv0 = SPLIT ? it.kv0 : 0;
                 ok = load_entry(&map_k, kv0 * BN, it.hk, it.b);  // K0 completes the previous item's last pair
@@ -276,7 +299,8 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                         const uint32_t dst = smem_base + kSmemQ + t * kTileBytes;
 #pragma unroll
                         for (int c = 0; c < kChunks; ++c)
-                            tma_load_4d(dst + c * kChunkBytes, &map_q, bar(kBarQFull + t), 64 * c, it.start[t], it.h, it.b);
+                            tma_load_4d(dst + c * kChunkBytes, &map_q, bar(kBarQFull + t), 64 * c, it.start[t],
+                                        PACK ? it.h + (t << (7 - p.pack_shift)) : it.h, it.b);   // (PACK: a box of several heads)
                     }
                 }
                 for (int x = 1; ok && x < 2 * it.n; ++x)
@@ -317,7 +341,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             uint32_t qcnt[2] = {0, 0};   // items that used tile t (Q / O barriers)
             uint32_t pcnt[2] = {0, 0};   // softmax iterations of tile t so far (P barrier)
             Item it;
-            for (int seq = 0; ok && get_item<SPLIT>(p, seq, &it); ++seq) {
+            for (int seq = 0; ok && get_item<SPLIT, PACK>(p, seq, &it); ++seq) {
                 if (it.n == 0) continue;
                 if (!have) ok = mbar_wait(bar(kBarKVFull + (G & 1)), (G >> 1) & 1, abort_flag, 3);
 #pragma unroll
@@ -385,10 +409,12 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         uint32_t scnt = 0;  // S tiles consumed so far
         uint32_t ocnt = 0;  // items finished so far
         Item it;
-        for (int seq = 0; ok && get_item<SPLIT>(p, seq, &it); ++seq) {
+        for (int seq = 0; ok && get_item<SPLIT, PACK>(p, seq, &it); ++seq) {
             const int nt = it.ntile[t];
             if (nt == 0) continue;
-            const int row_q = it.start[t] + wq * 32 + lane;
+            // PACK: row r of the tile is query position r mod 2^pack_shift of head r >> pack_shift of the group
+            const int row_q = PACK ? ((wq * 32 + lane) & ((1 << p.pack_shift) - 1)) : it.start[t] + wq * 32 + lane;
+            const int head_q = PACK ? it.h + ((t * BM + wq * 32) >> p.pack_shift) : it.h;   // (a warp's 32 rows: one head)
             if (ROPE) {
                 // this lane's row of the freshly landed Q tile, rotated in place: 16-byte unit u of row r
                 // sits at u ^ (r & 7) in each 64-column slab; columns d and d + 64 share the offset
@@ -755,7 +781,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             // stores would touch 32 cache lines per instruction.  Two halves of 64 columns share
             // the warp's 4 KB staging buffer (128-byte swizzle: 16-byte chunk c of row r sits at
             // chunk c ^ (r & 7)); rows past the end of the sequence are clipped by the tensor map.
-            const int row_w = it.start[t] + wq * 32;
+            const int row_w = PACK ? ((wq * 32) & ((1 << p.pack_shift) - 1)) : it.start[t] + wq * 32;
 #pragma unroll 1
             for (int c = 0; c < HD / 32; ++c) {
                 uint32_t o[32];
@@ -779,14 +805,14 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                     fence_proxy_async_smem();
                     __syncwarp();
                     if (lane == 0 && row_w < p.Lq) {
-                        tma_store_4d(&map_o, o_stage, 64 * (c >> 1), (SPLIT ? it.orow : 0) + row_w, it.h, it.b);
+                        tma_store_4d(&map_o, o_stage, 64 * (c >> 1), (SPLIT ? it.orow : 0) + row_w, head_q, it.b);
                         tma_store_commit();
                     }
                 }
             }
             if (p.lse && live)
-                p.lse[SPLIT ? (int64_t(it.b) * p.Hq + it.h) * p.lse_bh + it.orow + row_q
-                            : (int64_t(it.b) * p.Hq + it.h) * p.Lq + row_q] = m * p.scale + logf(l);
+                p.lse[SPLIT ? (int64_t(it.b) * p.Hq + head_q) * p.lse_bh + it.orow + row_q
+                            : (int64_t(it.b) * p.Hq + head_q) * p.Lq + row_q] = m * p.scale + logf(l);
         }
         if (lane == 0) tma_store_wait_read();  // shared memory stays valid until the last store has read it
     }
@@ -864,8 +890,8 @@ __global__ void __launch_bounds__(256) sdpa_tc_combine_kernel(const CombineParam
 // ---- host side -------------------------------------------------------------------------
 // [B, H, L, D] tensor with element strides st = {B, H, L}
 int make_map(CUtensorMap* map, const void* base, int dtype, int B, int H, int L, int D,
-             const int64_t* st, int box_rows = BN) {
-    return make_tensor_map_bhld(map, base, dtype, B, H, L, D, st, box_rows);
+             const int64_t* st, int box_rows = BN, int box_heads = 1) {
+    return make_tensor_map_bhld(map, base, dtype, B, H, L, D, st, box_rows, box_heads);
 }
 
 bool strides_ok(const void* base, const int64_t* st, int B, int H, int L, int D) {
@@ -879,13 +905,20 @@ bool strides_ok(const void* base, const int64_t* st, int B, int H, int L, int D)
 // Few query blocks against many keys (a prompt chunk or a handful of new tokens over a long cache):
 // B * Hq * npair units cannot fill the GPU, so the key range is cut into `nsplit` pieces of
 // `split_tiles` kv tiles.  No mask tensor and no rotary prologue on this route.
-struct SplitPlan { int nsplit, split_tiles, lq_pad; size_t o_bytes, bytes; };
+//
+// Packed groups: with 2, 4 or 8 query heads per kv head and at most 256 / group query positions, the
+// group's heads share one item (2^pack_shift rows each), so both tiles are full of live rows and K/V is
+// read once per group instead of once per head.
+struct SplitPlan { int nsplit, split_tiles, lq_pad, pack_shift; size_t o_bytes, bytes; };
 
 SplitPlan split_plan(const Gpu* g, const paras_sdpa_args& a, bool rope) {
-    SplitPlan sp{1, 1 << 28, 0, 0, 0};
+    SplitPlan sp{1, 1 << 28, 0, 0, 0, 0};
     if (a.mask || rope || (a.D != 128 && a.D != 64)) return sp;
+    const int group = a.Hkv > 0 && a.Hq % a.Hkv == 0 ? a.Hq / a.Hkv : 1;
+    if ((group == 2 || group == 4 || group == 8) && a.Lq * group <= kTilesPerCta * BM)
+        sp.pack_shift = group == 2 ? 7 : group == 4 ? 6 : 5;
     const int nq = (a.Lq + kTilesPerCta * BM - 1) / (kTilesPerCta * BM);
-    const int64_t units = int64_t(a.B) * a.Hq * ((nq + 1) / 2);
+    const int64_t units = sp.pack_shift ? int64_t(a.B) * a.Hkv : int64_t(a.B) * a.Hq * ((nq + 1) / 2);
     const int sms = g->sm_count > 0 ? g->sm_count : 148;
     if (units * 2 > sms) return sp;
     const int keys = a.causal ? std::min(a.Lk, a.Lq) : a.Lk;
@@ -897,7 +930,7 @@ SplitPlan split_plan(const Gpu* g, const paras_sdpa_args& a, bool rope) {
     if (n < 2) return sp;
     sp.nsplit = n;
     sp.split_tiles = per;
-    sp.lq_pad = nq * kTilesPerCta * BM;
+    sp.lq_pad = sp.pack_shift ? 1 << sp.pack_shift : nq * kTilesPerCta * BM;
     const size_t rows = size_t(a.B) * a.Hq * n * sp.lq_pad;
     sp.o_bytes = (rows * a.D * 2 + 255) & ~size_t(255);
     sp.bytes = sp.o_bytes + rows * sizeof(float);
@@ -926,10 +959,14 @@ bool sdpa_tc_supported(const Gpu* g, const paras_sdpa_args& a, const char** why)
     return true;
 }
 
-int sdpa_tc_launch(Gpu* g, const paras_sdpa_args& a, float scale, cudaStream_t s, const RopeTables* rope) {
+int sdpa_tc_launch(Gpu* g, const paras_sdpa_args& a, float scale, cudaStream_t s, const RopeTables* rope,
+                   const char** variant) {
     int st = check_status_word(g);  // an earlier launch's failure is reported once, here
     if (st != PARAS_OK) return st;
     const SplitPlan sp = split_plan(g, a, rope != nullptr);
+    if (variant)
+        *variant = rope ? "tcgen05_rope" : sp.pack_shift ? (sp.nsplit > 1 ? "tcgen05_packed_split" : "tcgen05_packed")
+                                                         : (sp.nsplit > 1 ? "tcgen05_split" : "tcgen05");
     void* scratch = nullptr;
     bool own = false;
     if (sp.nsplit > 1) {
@@ -950,7 +987,9 @@ int sdpa_tc_launch(Gpu* g, const paras_sdpa_args& a, float scale, cudaStream_t s
         return status != PARAS_OK ? status : st2;
     };
     CUtensorMap mq, mk, mv, mo;
-    if ((st = make_map(&mq, a.q, a.dtype, a.B, a.Hq, a.Lq, a.D, a.q_strides)) != PARAS_OK) return release(st);
+    if (sp.pack_shift) st = make_map(&mq, a.q, a.dtype, a.B, a.Hq, a.Lq, a.D, a.q_strides, 1 << sp.pack_shift, BM >> sp.pack_shift);
+    else st = make_map(&mq, a.q, a.dtype, a.B, a.Hq, a.Lq, a.D, a.q_strides);
+    if (st != PARAS_OK) return release(st);
     if ((st = make_map(&mk, a.k, a.dtype, a.B, a.Hkv, a.Lk, a.D, a.k_strides)) != PARAS_OK) return release(st);
     if ((st = make_map(&mv, a.v, a.dtype, a.B, a.Hkv, a.Lk, a.D, a.v_strides)) != PARAS_OK) return release(st);
     if (sp.nsplit > 1) {
@@ -967,6 +1006,7 @@ int sdpa_tc_launch(Gpu* g, const paras_sdpa_args& a, float scale, cudaStream_t s
     p.nsplit = sp.nsplit;
     p.split_tiles = sp.split_tiles;
     p.lq_pad = sp.lq_pad;
+    p.pack_shift = sp.pack_shift;
     p.lse_bh = a.Lq;
     if (sp.nsplit > 1) {
         p.lse = reinterpret_cast<float*>(static_cast<uint8_t*>(scratch) + sp.o_bytes);
@@ -990,8 +1030,9 @@ int sdpa_tc_launch(Gpu* g, const paras_sdpa_args& a, float scale, cudaStream_t s
     }
     p.nq = (a.Lq + kTilesPerCta * BM - 1) / (kTilesPerCta * BM);
     p.npair = (p.nq + 1) / 2;
-    p.split_units = int(std::min<int64_t>(int64_t(a.B) * a.Hq * p.npair, INT32_MAX));
-    const int64_t units = int64_t(a.B) * a.Hq * p.npair * p.nsplit;
+    const int64_t per_split = sp.pack_shift ? int64_t(a.B) * a.Hkv : int64_t(a.B) * a.Hq * p.npair;
+    p.split_units = int(std::min<int64_t>(per_split, INT32_MAX));
+    const int64_t units = per_split * p.nsplit;
     if (units > INT32_MAX) return release(fail(PARAS_E_UNSUPPORTED, "paras sdpa: too many work units"));
     p.units = int(units);
     const int sms = g->sm_count > 0 ? g->sm_count : 148;
@@ -1002,7 +1043,13 @@ int sdpa_tc_launch(Gpu* g, const paras_sdpa_args& a, float scale, cudaStream_t s
         return PARAS_OK;
     };
     const bool bf = a.dtype == PARAS_BF16;
-    if (sp.nsplit > 1) {
+    if (sp.pack_shift && sp.nsplit > 1) {
+        if (a.D == 128) st = bf ? launch(sdpa_tc_kernel<true, false, 128, false, true, true>) : launch(sdpa_tc_kernel<false, false, 128, false, true, true>);
+        else st = bf ? launch(sdpa_tc_kernel<true, false, 64, false, true, true>) : launch(sdpa_tc_kernel<false, false, 64, false, true, true>);
+    } else if (sp.pack_shift) {
+        if (a.D == 128) st = bf ? launch(sdpa_tc_kernel<true, false, 128, false, false, true>) : launch(sdpa_tc_kernel<false, false, 128, false, false, true>);
+        else st = bf ? launch(sdpa_tc_kernel<true, false, 64, false, false, true>) : launch(sdpa_tc_kernel<false, false, 64, false, false, true>);
+    } else if (sp.nsplit > 1) {
         if (a.D == 128) st = bf ? launch(sdpa_tc_kernel<true, false, 128, false, true>) : launch(sdpa_tc_kernel<false, false, 128, false, true>);
         else st = bf ? launch(sdpa_tc_kernel<true, false, 64, false, true>) : launch(sdpa_tc_kernel<false, false, 64, false, true>);
     } else if (rope) {

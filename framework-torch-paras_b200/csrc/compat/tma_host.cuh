@@ -60,7 +60,7 @@ inline int make_tensor_map_3d(CUtensorMap* map, const void* base, int dtype, int
 // contiguous inner dim: box {64, box_rows, 1, 1}, 128-byte swizzle, rows outside the tensor read
 // as zero and are not written.
 inline int make_tensor_map_bhld(CUtensorMap* map, const void* base, int dtype, int B, int H, int L,
-                                int inner, const int64_t* st, int box_rows) {
+                                int inner, const int64_t* st, int box_rows, int box_heads = 1) {
     TensorMapEncodeFn fn = tensor_map_encode_fn();
     if (!fn) return fail(PARAS_E_CUDA, "paras_b200: cuTensorMapEncodeTiled is unavailable");
     const cuuint64_t dims[4] = {cuuint64_t(inner), cuuint64_t(L), cuuint64_t(H), cuuint64_t(B)};
@@ -69,7 +69,7 @@ inline int make_tensor_map_bhld(CUtensorMap* map, const void* base, int dtype, i
     const int64_t sh = H > 1 ? st[1] : sl * L;
     const int64_t sb = B > 1 ? st[0] : sh * H;
     const cuuint64_t strides[3] = {cuuint64_t(sl) * 2, cuuint64_t(sh) * 2, cuuint64_t(sb) * 2};
-    const cuuint32_t box[4] = {64, cuuint32_t(box_rows), 1, 1};
+    const cuuint32_t box[4] = {64, cuuint32_t(box_rows), cuuint32_t(box_heads), 1};
     const cuuint32_t estr[4] = {1, 1, 1, 1};
     const CUresult r = fn(map, dtype == PARAS_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
                                                   : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,

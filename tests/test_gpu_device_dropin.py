@@ -113,7 +113,7 @@ def test_sdpa_bf16_llama_shape_hits_the_tensor_core_kernel():
     k = torch.randn(1, 2, 512, 128, generator=g).bfloat16()
     v = torch.randn(1, 2, 512, 128, generator=g).bfloat16()
     out = F.scaled_dot_product_attention(q.to(DEV), k.to(DEV), v.to(DEV), is_causal=True, enable_gqa=True)
-    assert torch_paras._C.sdpa_last_kernel() == "tcgen05"
+    assert torch_paras._C.sdpa_last_kernel().startswith("tcgen05")
     want = O.sdpa(q, k, v, is_causal=True, enable_gqa=True)
     assert out.dtype == torch.bfloat16 and out.shape == want.shape
     assert (out.cpu().double() - want.double()).abs().max().item() <= 2e-2

@@ -35,7 +35,7 @@ def test_config2_llama_causal_sdpa_full_size():
     # bf16 B=8 Hq=Hkv=32 S=2048 D=128
     q, k, v = gen((8, 32, 2048, 128), 1), gen((8, 32, 2048, 128), 2), gen((8, 32, 2048, 128), 3)
     out = abi.sdpa_fwd(q, k, v, causal=True, flags=abi.SDPA_REF_SCALE)
-    assert abi.sdpa_last_kernel() == "tcgen05"
+    assert abi.sdpa_last_kernel().startswith("tcgen05")
     # oracle on ten whole (batch, head) units spread over the persistent grid's schedule (a unit =
     # all 16 query blocks of the head, so every pairing of long and short blocks is covered)
     for b, h in ((0, 0), (0, 31), (1, 5), (2, 17), (3, 30), (4, 9), (5, 26), (6, 13), (7, 1), (7, 31)):
@@ -62,7 +62,7 @@ def test_config3_gqa_causal_sdpa_long_sequence_slice():
     # bf16 Hq=64 Hkv=8 S=8192 D=128; one batch element (the config's B=4 repeats it)
     q, k, v = gen((1, 64, 8192, 128), 6), gen((1, 8, 8192, 128), 7), gen((1, 8, 8192, 128), 8)
     out = abi.sdpa_fwd(q, k, v, causal=True, flags=abi.SDPA_REF_SCALE)
-    assert abi.sdpa_last_kernel() == "tcgen05"
+    assert abi.sdpa_last_kernel().startswith("tcgen05")
     # GQA: query head 13 must read kv head 13 // 8 = 1, head 63 kv head 7.  Whole heads against the
     # oracle, all 8192 rows: rows >= 4096 walk 33-64 key tiles, over which the softmax reference of
     # a row has moved many times.
@@ -140,7 +140,7 @@ def test_config5_decoder_block_share_of_one_gpu():
     y1 = abi.rmsnorm_fwd(x, w, 1e-6, mode=abi.ROUND_PER_OP)
     q, k, v = gen((1, 32, S, 128), 32), gen((1, 8, S, 128), 33), gen((1, 8, S, 128), 34)
     att = abi.sdpa_fwd(q, k, v, causal=True, flags=abi.SDPA_REF_SCALE)
-    assert abi.sdpa_last_kernel() == "tcgen05"
+    assert abi.sdpa_last_kernel().startswith("tcgen05")
     y2 = abi.rmsnorm_fwd(att.transpose(1, 2).reshape(S, 4096).contiguous(), w, 1e-6, mode=abi.ROUND_PER_OP)
     gate, up = gen((S, 14336), 35), gen((S, 14336), 36)
     act = abi.swiglu_fwd(gate, up)
