@@ -464,6 +464,21 @@ def run_ours(args):
             res[key] = {"ms": t, "tflops": tf, "frac_of_bf16_peak": tf / peaks["bf16_tflops"], "kernel": abi.sdpa_last_kernel()}
         del q6, k6, v6, o6
         extra["sdpa_variants_B8_H32_S2048"] = res
+        # few query positions against a long key range (a prompt chunk, or the tokens a speculative step
+        # verifies): too few (batch, head, query block) units to fill the GPU, so the key range runs in
+        # pieces; with GQA the heads of a group share one pass over K/V.  HBM floor = K + V once per kv head.
+        res = {}
+        for key, (b_, lq_, lk_) in (("chunk_B1_Lq512_Lk32768", (1, 512, 32768)), ("verify_B8_Lq64_Lk16384", (8, 64, 16384)),
+                                    ("verify_B8_Lq16_Lk16384", (8, 16, 16384))):
+            qs_, ks_, vs_ = gen((b_, 32, lq_, 128), 47), gen((b_, 8, lk_, 128), 48), gen((b_, 8, lk_, 128), 49)
+            os_ = torch.empty_like(qs_)
+            t = loop_ms(lambda: abi.sdpa_fwd(qs_, ks_, vs_, out=os_, flags=abi.SDPA_FORCE_TENSOR), esteps)
+            tf = sdpa_flops(b_, 32, lq_, lk_, 128, False) / (t * 1e-3) / 1e12
+            gbs = (ks_.numel() + vs_.numel() + 2 * qs_.numel()) * 2 / (t * 1e-3) / 1e9
+            res[key] = {"ms": t, "tflops": tf, "frac_of_bf16_peak": tf / peaks["bf16_tflops"], "gbs": gbs,
+                        "frac_of_hbm_peak": gbs / peaks["hbm_gbs"], "kernel": abi.sdpa_last_kernel()}
+            del qs_, ks_, vs_, os_
+        extra["sdpa_short_queries_Hq32_Hkv8_D128"] = res
 
     if want("decode"):
         # config 4 decode: bytes = K + V (once per kv head) + q + o

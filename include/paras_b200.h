@@ -174,8 +174,12 @@ typedef struct paras_sdpa_args {
 
 int paras_b200_sdpa_fwd(const paras_sdpa_args* args);
 int paras_b200_sdpa_workspace_bytes(const paras_sdpa_args* args, size_t* bytes);
-/* Name of the kernel the last successful paras_b200_sdpa_fwd call of this thread used
- * ("tcgen05", "simt", "decode_mma", ...); for tests and logs. */
+/* Name of the kernel the last successful paras_b200_sdpa_fwd call of this thread used; for tests and
+ * logs.  "tcgen05" (tensor-core tiles), "tcgen05_split" (few query blocks against a long key range: the
+ * key range runs in pieces that a second kernel merges; scratch from `workspace` or the pool, size from
+ * paras_b200_sdpa_workspace_bytes), "tcgen05_packed" / "tcgen05_packed_split" (2, 4 or 8 query heads per
+ * kv head and at most 256 / that many query positions: the group's heads share one pass over K/V),
+ * "tcgen05_rope", "decode_mma", "simt", "simt_splitkv", "simt_splitkv_static", "weights". */
 const char* paras_b200_sdpa_last_kernel(void);
 
 /* Attention with the rotary position embedding applied to q and k first:
