@@ -614,24 +614,25 @@ rmsnorm_bwd_rows_pipe_kernel(const T* __restrict__ go, const T* __restrict__ x, 
                 make_float4(dwacc[i * N + e], dwacc[i * N + e + 1], dwacc[i * N + e + 2], dwacc[i * N + e + 3]);
 }
 
-// grad_weight[j] = sum over the partial rows: 16 threads per column take every sixteenth partial.
+// grad_weight[j] = sum over the partial rows: 32 threads per column take every thirty-second partial
+// (H / 32 CTAs: at H = 4096 that is 128 of them, and a thread's chain of loads is 5-10 long).
 template <typename T>
 __global__ void __launch_bounds__(1024)
 rmsnorm_bwd_dw_reduce_kernel(const float* __restrict__ dw_part, T* __restrict__ gw, int parts, int64_t H) {
-    __shared__ double sh[16][64];
-    const int cx = threadIdx.x & 63, py = threadIdx.x >> 6;
-    const int64_t col = int64_t(blockIdx.x) * 64 + cx;
+    __shared__ double sh[32][33];
+    const int cx = threadIdx.x & 31, py = threadIdx.x >> 5;
+    const int64_t col = int64_t(blockIdx.x) * 32 + cx;
     double acc = 0.0;
     if (col < H) {
 #pragma unroll 4
-        for (int pi = py; pi < parts; pi += 16) acc += double(__ldcs(dw_part + int64_t(pi) * H + col));
+        for (int pi = py; pi < parts; pi += 32) acc += double(__ldcs(dw_part + int64_t(pi) * H + col));
     }
     sh[py][cx] = acc;
     __syncthreads();
     if (py == 0 && col < H) {
         double t = 0.0;
 #pragma unroll
-        for (int i = 0; i < 16; ++i) t += sh[i][cx];
+        for (int i = 0; i < 32; ++i) t += sh[i][cx];
         gw[col] = from_f32<T>(float(t));
     }
 }
@@ -859,7 +860,7 @@ int paras_b200_rmsnorm_bwd(int gpu, const void* grad_out, const void* x, const v
 #define PB_ROWS_T(T)                                                                                             \
     do {                                                                                                         \
         if (threads == 128) { PB_ROWS_V(T, 128) } else if (threads == 256) { PB_ROWS_V(T, 256) } else { PB_ROWS_V(T, 512) } \
-        pb::rmsnorm_bwd_dw_reduce_kernel<T><<<int((H + 63) / 64), 1024, 0, s>>>(part, static_cast<T*>(grad_weight), parts, H); \
+        pb::rmsnorm_bwd_dw_reduce_kernel<T><<<int((H + 31) / 32), 1024, 0, s>>>(part, static_cast<T*>(grad_weight), parts, H); \
     } while (0)
             switch (dtype) {
                 case PARAS_F32: PB_ROWS_T(float); break;
