@@ -23,6 +23,10 @@ struct GemmExtra {
                             // only when every reader of C skips the same parts (k_skip does)
 };
 
+// The CTA-pair kernel (gemm_tc2.cu): 256 x 256 tiles on two CTAs of a cluster, for the large projections.
+bool gemm_tc2_eligible(const Gpu* g, const paras_gemm_args* a);
+int gemm_tc2_run(Gpu* g, const paras_gemm_args* a, cudaStream_t s);
+
 // paras_b200_gemm with `ex` (may be null); A must be [M, K] rows for epilogues 3 and 4.
 int gemm_run(const paras_gemm_args* a, const GemmExtra* ex);
 

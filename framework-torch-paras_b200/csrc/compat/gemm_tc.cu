@@ -669,6 +669,9 @@ int gemm_run(const paras_gemm_args* a, const GemmExtra* ex) {
     // N <= 128 (the [.., head dim] products of attention backward): half-width B tiles and MMAs
     const bool narrow = a->N <= BN / 2 && (epi == kEpiNone || epi == kEpiBias || epi == kEpiRowScale);
     const int n_per_tile = a->epilogue == kEpiSwiglu || narrow ? BN / 2 : BN;
+    // Large projections run on CTA pairs (PARAS_GEMM_PAIR=0 keeps them on this file's kernel, for comparison)
+    static const bool pair_off = getenv("PARAS_GEMM_PAIR") && getenv("PARAS_GEMM_PAIR")[0] == '0';
+    if (!ex && !pair_off && gemm_tc2_eligible(g, a)) return gemm_tc2_run(g, a, pick_stream(g, a->stream));
     // Few output tiles and a long K (the projections of a decode step: M = the batch): the K range is cut
     // into slices that run as the batches of one launch, each writing its fp32 accumulator to scratch, and a
     // small kernel sums the slices, adds the bias and rounds.  Without it 16 of the 148 SMs stream the weight.

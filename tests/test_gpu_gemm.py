@@ -102,6 +102,43 @@ def test_few_tiles_and_a_long_k_split_the_k_range(shape, dtype):
     assert torch.equal(x, y)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("shape", [(2304, 2304, 520), (2400, 2056, 264), (5000, 1032, 256), (1290, 4360, 1096)])
+def test_large_projections_on_cta_pairs(shape, dtype):
+    # At least half a wave of 256 x 256 tiles: the kernel that computes a tile on two CTAs of a cluster.
+    # Ragged M, N and K against the same host GEMM, with and without bias, and the same call on the
+    # single-CTA kernel must give the same bits (both accumulate a tile's K range in one fp32 chain).
+    M, N, K = shape
+    a, w = rand((M, K), 1, dtype, 0.5), rand((N, K), 2, dtype, 0.5)
+    bias = rand((N,), 4, dtype)
+    ad, wd = a.to(CUDA), w.to(CUDA)
+    got = abi.gemm(ad, wd)
+    close16(got, O.linear(a, w), f"pair A W^T {shape}")
+    close16(abi.gemm(ad, wd, bias=bias.to(CUDA)), O.linear(a, w, bias), f"pair bias {shape}")
+    out = torch.zeros(M, N + 16, dtype=dtype, device=CUDA)
+    abi.gemm(ad, wd, out=out[:, 8:N + 8])
+    assert torch.equal(out[:, 8:N + 8], got)
+    assert float(out[:, :8].abs().sum()) == 0.0 and float(out[:, N + 8:].abs().sum()) == 0.0
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_swiglu_and_row_scale_epilogues_on_cta_pairs(dtype):
+    M, Fd, K = 1300, 1704, 512
+    x, wg, wu = rand((M, K), 1, dtype), rand((Fd, K), 2, dtype, 0.05), rand((Fd, K), 3, dtype, 0.05)
+    got = abi.gemm(x.to(CUDA), wg.to(CUDA), up_weight=wu.to(CUDA))
+    close16(got, O.swiglu_linear(x, wg, wu), "pair swiglu epilogue", exact_share=0.97)
+    M, N, K = 2304, 2304, 512
+    x = rand((M, K), 11, dtype, 1.5)
+    wn = (1 + 0.1 * torch.randn(K, generator=torch.Generator().manual_seed(12))).to(dtype)
+    w = rand((N, K), 13, dtype, 0.05)
+    y, _ = O.rms_norm_fused(x, wn, 1e-6)
+    want = O.linear(y, w).double()
+    got = abi.rms_norm_linear(x.to(CUDA), wn.to(CUDA), w.to(CUDA), 1e-6).cpu().double()
+    ulp = 2.0 ** -7 if dtype == torch.bfloat16 else 2.0 ** -10
+    err = (got - want).abs()
+    assert (err <= 2 * ulp * want.abs() + 2e-2 * want.abs().max().item()).all(), f"worst {err.max().item():.3e}"
+
+
 @pytest.mark.parametrize("shape", [(128, 256, 64), (304, 520, 136), (1000, 264, 392), (520, 128, 1000), (304, 64, 136)])
 def test_transposed_a_operand(shape):
     # A given as [K, M] (rows of M): C = A^T B, with B in either layout
