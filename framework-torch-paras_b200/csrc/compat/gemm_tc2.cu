@@ -1,4 +1,4 @@
-// The projection GEMM on CTA pairs: C[M, N] = A[M, K] * B[N, K]^T with 256 x 256 output tiles, each
+// The projection GEMM on CTA pairs: C[M, N] = A[M, K] * B[N, K]^T (either operand also transposed, batched) with 256 x 256 output tiles, each
 // computed by two CTAs of a cluster (`tcgen05.mma.cta_group::2`, M = 256).  The call sites are the same as
 // gemm_tc.cu's: aten::linear / addmm / mm of the reference (csrc/ops/vision_ops.cpp:248-309, 388-423) and
 // the gate/up projection with SwiGLU (csrc/ops/rms_swiglu_ops.cpp:77-104).
@@ -61,22 +61,26 @@ enum { kEpiNone = 0, kEpiBias = 1, kEpiSwiglu = 2, kEpiRowScale = 5 };
 
 struct Params {
     int M, N, K;
-    int tiles_m, tiles_n, tiles;   // tiles of 256 rows x (256 | 128 with SwiGLU) columns
+    int batch;
+    int tiles_m, tiles_n, tiles;   // per batch: tiles of 256 rows x (256 | 128 with SwiGLU) columns; tiles = all batches
     int k_iters;
     const void* bias;
     const float* row_scale;
     int* status;
 };
 
-struct Tile { int m0, n0; };
+struct Tile { int b, m0, n0; };
 
 __device__ __forceinline__ Tile get_tile(const Params& p, int id, int n_per_tile) {
+    const int per_batch = p.tiles_m * p.tiles_n;
+    Tile t;
+    t.b = id / per_batch;
+    id -= t.b * per_batch;
     const int in_group = kGroupM * p.tiles_n;
     const int group = id / in_group;
     const int first_m = group * kGroupM;
     const int gm = min(p.tiles_m - first_m, kGroupM);
     const int q = id - group * in_group;
-    Tile t;
     t.m0 = (first_m + q % gm) * (2 * BMC);
     t.n0 = (q / gm) * n_per_tile;
     return t;
@@ -134,7 +138,10 @@ __device__ __forceinline__ void tma2_load_3d(uint32_t dst_smem, const CUtensorMa
         : "memory");
 }
 
-template <bool BF16, int EPI>
+// A_KM: A is given as [K, M] rows (the transposed operand of a weight gradient); B_KN: B as [K, N] rows
+// (mm / bmm, and the input gradient of a linear layer).  Such an operand lands in shared memory as
+// 64-column slabs of 64 K-rows and is read through MN-major descriptors, as in gemm_tc.cu.
+template <bool BF16, bool A_KM, bool B_KN, int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                 const __grid_constant__ CUtensorMap map_b2, const __grid_constant__ CUtensorMap map_c,
@@ -200,8 +207,20 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     const uint32_t full = map_to_cta(bar(kBarFull + st), 0);
                     for (int j = 0; j < n; ++j) {
                         const uint32_t a_dst = smem_base + st * kStageBytes + j * kStepBytes;
-                        tma2_load_3d(a_dst, &map_a, full, (kk + j) * BK, a_row, 0);
-                        tma2_load_3d(a_dst + kABytes, mb, full, (kk + j) * BK, b_row, 0);
+                        const int k0 = (kk + j) * BK;
+                        if (A_KM) {
+#pragma unroll
+                            for (int i = 0; i < BMC / 64; ++i) tma2_load_3d(a_dst + i * (BK * 128), &map_a, full, a_row + 64 * i, k0, t.b);
+                        } else {
+                            tma2_load_3d(a_dst, &map_a, full, k0, a_row, t.b);
+                        }
+                        if (B_KN) {
+#pragma unroll
+                            for (int i = 0; i < BN / 2 / 64; ++i)
+                                tma2_load_3d(a_dst + kABytes + i * (BK * 128), mb, full, b_row + 64 * i, k0, t.b);
+                        } else {
+                            tma2_load_3d(a_dst + kABytes, mb, full, k0, b_row, t.b);
+                        }
                     }
                     if (++st == kStages) { st = 0; phase ^= 1u; }
                 }
@@ -210,7 +229,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     } else if (warp == kMmaWarp) {
         // ------------------------------ MMA issuer (first CTA of the pair) --------------------
         if (leader && lane == 0) {
-            constexpr uint32_t idesc = instr_desc_f16(BF16 ? 1 : 0, 2 * BMC, BN, false, false);
+            constexpr uint32_t idesc = instr_desc_f16(BF16 ? 1 : 0, 2 * BMC, BN, A_KM, B_KN);
             bool ok = true;
             int st = 0, local = 0;
             uint32_t phase = 0;
@@ -230,9 +249,13 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                         const uint32_t a_addr = smem_base + st * kStageBytes + j * kStepBytes;
                         const uint32_t b_addr = a_addr + kABytes;
 #pragma unroll
-                        for (int ks = 0; ks < BK / 16; ++ks)
-                            mma2_ss(d_tm, smem_desc_sw128(a_addr + ks * 32, 16, 1024), smem_desc_sw128(b_addr + ks * 32, 16, 1024),
-                                    idesc, (kk || j || ks) ? 1u : 0u);
+                        for (int ks = 0; ks < BK / 16; ++ks) {
+                            const uint64_t a_desc = A_KM ? smem_desc_sw128(a_addr + ks * 16 * 128, BK * 128, 1024)
+                                                         : smem_desc_sw128(a_addr + ks * 32, 16, 1024);
+                            const uint64_t b_desc = B_KN ? smem_desc_sw128(b_addr + ks * 16 * 128, BK * 128, 1024)
+                                                         : smem_desc_sw128(b_addr + ks * 32, 16, 1024);
+                            mma2_ss(d_tm, a_desc, b_desc, idesc, (kk || j || ks) ? 1u : 0u);
+                        }
                     }
                     // the stage is free in both CTAs once these MMAs have read it
                     tc_commit2(bar(kBarEmpty + st));
@@ -260,7 +283,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             const int row_w = t.m0 + int(rank) * BMC + wq * 32;
             constexpr int kChunks = kNPerTile / 64;
             float stat = 0.f;
-            if (EPI == kEpiRowScale) stat = __ldg(p.row_scale + min(row_w + lane, p.M - 1));
+            if (EPI == kEpiRowScale) stat = __ldg(p.row_scale + int64_t(t.b) * p.M + min(row_w + lane, p.M - 1));
             ok = mbar_wait<32>(bar(kBarAccFull + buf), (local >> 1) & 1, abort_flag, 3);
             if (!ok) break;
             tc_fence_after_sync();
@@ -328,7 +351,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0) {
-                    if (row_w < p.M && t.n0 + 64 * c < p.N) tma_store_3d(&map_c, stage, t.n0 + 64 * c, row_w, 0);
+                    if (row_w < p.M && t.n0 + 64 * c < p.N) tma_store_3d(&map_c, stage, t.n0 + 64 * c, row_w, t.b);
                     tma_store_commit();
                 }
                 ++nstore;
@@ -354,10 +377,10 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     }
 }
 
-template <bool BF16, int EPI>
+template <bool BF16, bool A_KM, bool B_KN, int EPI>
 int launch2(Gpu* g, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mb2, const CUtensorMap& mc,
             const Params& p, cudaStream_t s) {
-    auto kernel = gemm_tc2_kernel<BF16, EPI>;
+    auto kernel = gemm_tc2_kernel<BF16, A_KM, B_KN, EPI>;
     PB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal));
     const int sms = g->sm_count > 0 ? g->sm_count : 148;
     const int pairs = std::min(p.tiles, sms / 2);
@@ -368,36 +391,42 @@ int launch2(Gpu* g, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensor
 
 }  // namespace
 
-// Shapes the pair kernel takes: A as [M, K] rows, B as [N, K] rows, one batch, epilogue none / bias /
-// row scale / SwiGLU, at least half a wave of 256 x 256 tiles (the single-CTA kernel would fill the same
+// Shapes the pair kernel takes: either operand in either layout, any batch count, epilogue none / bias /
+// row scale / SwiGLU (the epilogues as in gemm_tc.cu: A as [M, K] rows; SwiGLU two [F, K] weights), at least half a wave of 256 x 256 tiles (the single-CTA kernel would fill the same
 // share of the GPU with its 128-row tiles; below that it splits K instead).  A 256 x 128 tile variant for
 // outputs whose last round of tiles is mostly empty was measured and dropped: its MMAs run at two thirds
 // of the wide tile's rate ([4096]^3: 1019 against 1440 TFLOP/s), more than the fuller round returns.
 bool gemm_tc2_eligible(const Gpu* g, const paras_gemm_args* a) {
-    if (a->a_layout != PARAS_GEMM_A_MK || a->b_layout != PARAS_GEMM_B_NK || a->batch != 1) return false;
     if (a->epilogue != kEpiNone && a->epilogue != kEpiBias && a->epilogue != kEpiRowScale && a->epilogue != kEpiSwiglu)
         return false;
+    if (a->a_layout == PARAS_GEMM_A_KM && a->epilogue != kEpiNone) return false;
+    if (a->b_layout == PARAS_GEMM_B_KN && a->epilogue == kEpiSwiglu) return false;
     const int sms = g->sm_count > 0 ? g->sm_count : 148;
     const int n_per_tile = a->epilogue == kEpiSwiglu ? BN / 2 : BN;
-    const int64_t tiles = ((a->M + 2 * BMC - 1) / (2 * BMC)) * ((a->N + n_per_tile - 1) / n_per_tile);
+    const int64_t tiles = ((a->M + 2 * BMC - 1) / (2 * BMC)) * ((a->N + n_per_tile - 1) / n_per_tile) * a->batch;
     return tiles >= sms / 4 && a->K >= 4 * BK && a->N > BN / 2;
 }
 
 int gemm_tc2_run(Gpu* g, const paras_gemm_args* a, cudaStream_t s) {
     int st;
     CUtensorMap ma, mb, mb2, mc;
-    if ((st = make_tensor_map_3d(&ma, a->a, a->dtype, a->K, a->M, 1, a->lda, a->stride_a, BK, BMC)) != PARAS_OK) return st;
-    if ((st = make_tensor_map_3d(&mb, a->b, a->dtype, a->K, a->N, 1, a->ldb, a->stride_b, BK, BN / 2)) != PARAS_OK) return st;
+    const bool at = a->a_layout == PARAS_GEMM_A_KM, kn = a->b_layout == PARAS_GEMM_B_KN;
+    st = at ? make_tensor_map_3d(&ma, a->a, a->dtype, a->M, a->K, a->batch, a->lda, a->stride_a, 64, BK)
+            : make_tensor_map_3d(&ma, a->a, a->dtype, a->K, a->M, a->batch, a->lda, a->stride_a, BK, BMC);
+    if (st != PARAS_OK) return st;
+    st = kn ? make_tensor_map_3d(&mb, a->b, a->dtype, a->N, a->K, a->batch, a->ldb, a->stride_b, 64, BK)
+            : make_tensor_map_3d(&mb, a->b, a->dtype, a->K, a->N, a->batch, a->ldb, a->stride_b, BK, BN / 2);
+    if (st != PARAS_OK) return st;
     mb2 = mb;
     if (a->epilogue == kEpiSwiglu &&
-        (st = make_tensor_map_3d(&mb2, a->b2, a->dtype, a->K, a->N, 1, a->ldb, a->stride_b, BK, BN / 2)) != PARAS_OK) return st;
-    if ((st = make_tensor_map_3d(&mc, a->c, a->dtype, a->N, a->M, 1, a->ldc, a->stride_c, 64, 32)) != PARAS_OK) return st;
+        (st = make_tensor_map_3d(&mb2, a->b2, a->dtype, a->K, a->N, a->batch, a->ldb, a->stride_b, BK, BN / 2)) != PARAS_OK) return st;
+    if ((st = make_tensor_map_3d(&mc, a->c, a->dtype, a->N, a->M, a->batch, a->ldc, a->stride_c, 64, 32)) != PARAS_OK) return st;
     const int n_per_tile = a->epilogue == kEpiSwiglu ? BN / 2 : BN;
     Params p{};
-    p.M = int(a->M); p.N = int(a->N); p.K = int(a->K);
+    p.M = int(a->M); p.N = int(a->N); p.K = int(a->K); p.batch = int(a->batch);
     p.tiles_m = int((a->M + 2 * BMC - 1) / (2 * BMC));
     p.tiles_n = int((a->N + n_per_tile - 1) / n_per_tile);
-    const int64_t tiles = int64_t(p.tiles_m) * p.tiles_n;
+    const int64_t tiles = int64_t(p.tiles_m) * p.tiles_n * p.batch;
     if (tiles > INT32_MAX) return fail(PARAS_E_UNSUPPORTED, "paras gemm: too many tiles");
     p.tiles = int(tiles);
     p.k_iters = int((a->K + BK - 1) / BK);
@@ -405,12 +434,22 @@ int gemm_tc2_run(Gpu* g, const paras_gemm_args* a, cudaStream_t s) {
     p.row_scale = a->row_scale;
     p.status = g->status_dev;
     const bool bf = a->dtype == PARAS_BF16;
-    switch (a->epilogue) {
-        case kEpiBias: return bf ? launch2<true, kEpiBias>(g, ma, mb, mb2, mc, p, s) : launch2<false, kEpiBias>(g, ma, mb, mb2, mc, p, s);
-        case kEpiSwiglu: return bf ? launch2<true, kEpiSwiglu>(g, ma, mb, mb2, mc, p, s) : launch2<false, kEpiSwiglu>(g, ma, mb, mb2, mc, p, s);
-        case kEpiRowScale: return bf ? launch2<true, kEpiRowScale>(g, ma, mb, mb2, mc, p, s) : launch2<false, kEpiRowScale>(g, ma, mb, mb2, mc, p, s);
-        default: return bf ? launch2<true, kEpiNone>(g, ma, mb, mb2, mc, p, s) : launch2<false, kEpiNone>(g, ma, mb, mb2, mc, p, s);
+#define PB_GO(AT, KN, E) (bf ? launch2<true, AT, KN, E>(g, ma, mb, mb2, mc, p, s) : launch2<false, AT, KN, E>(g, ma, mb, mb2, mc, p, s))
+    if (at) return kn ? PB_GO(true, true, kEpiNone) : PB_GO(true, false, kEpiNone);
+    if (kn) {
+        switch (a->epilogue) {
+            case kEpiBias: return PB_GO(false, true, kEpiBias);
+            case kEpiRowScale: return PB_GO(false, true, kEpiRowScale);
+            default: return PB_GO(false, true, kEpiNone);
+        }
     }
+    switch (a->epilogue) {
+        case kEpiBias: return PB_GO(false, false, kEpiBias);
+        case kEpiSwiglu: return PB_GO(false, false, kEpiSwiglu);
+        case kEpiRowScale: return PB_GO(false, false, kEpiRowScale);
+        default: return PB_GO(false, false, kEpiNone);
+    }
+#undef PB_GO
 }
 
 }  // namespace pb

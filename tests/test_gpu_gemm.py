@@ -121,6 +121,24 @@ def test_large_projections_on_cta_pairs(shape, dtype):
     assert float(out[:, :8].abs().sum()) == 0.0 and float(out[:, N + 8:].abs().sum()) == 0.0
 
 
+@pytest.mark.parametrize("shape", [(2304, 2304, 520), (1296, 4360, 264)])
+def test_transposed_operands_and_batches_on_cta_pairs(shape):
+    # the gradients of a linear layer: dX = dY W (B as [K, N] rows), dW = dY^T X (A as [K, M] rows), and bmm
+    M, N, K = shape
+    dtype = torch.bfloat16
+    a, at, w, b = rand((M, K), 1, dtype, 0.5), rand((K, M), 5, dtype, 0.5), rand((N, K), 2, dtype, 0.5), rand((K, N), 3, dtype, 0.5)
+    bias = rand((N,), 4, dtype)
+    close16(abi.gemm(a.to(CUDA), b.to(CUDA), b_layout=abi.GEMM_B_KN), O.mm(a, b), f"pair A B {shape}")
+    close16(abi.gemm(a.to(CUDA), b.to(CUDA), b_layout=abi.GEMM_B_KN, bias=bias.to(CUDA)), O.linear(a, b.t().contiguous(), bias),
+            f"pair A B + bias {shape}")
+    close16(abi.gemm(at.to(CUDA), w.to(CUDA), a_transposed=True), O.mm(at.t(), w.t()), f"pair A^T W^T {shape}")
+    close16(abi.gemm(at.to(CUDA), b.to(CUDA), a_transposed=True, b_layout=abi.GEMM_B_KN), O.mm(at.t(), b), f"pair A^T B {shape}")
+    x3, y3 = rand((3, 1300, 520), 6, dtype, 0.5), rand((3, 520, 1800), 7, dtype, 0.5)
+    close16(abi.gemm(x3.to(CUDA), y3.to(CUDA), b_layout=abi.GEMM_B_KN), O.bmm(x3, y3), "pair bmm")
+    w3 = rand((3, 1800, 520), 8, dtype, 0.5)
+    close16(abi.gemm(x3.to(CUDA), w3.to(CUDA)), O.bmm(x3, w3.transpose(1, 2)), "pair batched A W^T")
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 def test_swiglu_and_row_scale_epilogues_on_cta_pairs(dtype):
     M, Fd, K = 1300, 1704, 512
