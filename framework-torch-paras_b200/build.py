@@ -26,7 +26,7 @@ PKG = os.path.join(HERE, "python", "torch_paras")
 OBJ = os.path.join(HERE, "build")
 
 CUDA_SOURCES = ["runtime.cu", "elementwise.cu", "rmsnorm.cu", "sdpa.cu", "sdpa_simt.cu",
-                "sdpa_tc.cu", "sdpa_decode.cu", "gemm_tc.cu", "gemm_tc2.cu", "sdpa_bwd.cu", "sdpa_bwd_tc.cu", "sdpa_bwd_general.cu", "sdpa_weights.cu", "selftest.cu"]
+                "sdpa_tc.cu", "sdpa_decode.cu", "gemm_tc.cu", "gemm_tc2.cu", "gemm_skinny.cu", "sdpa_bwd.cu", "sdpa_bwd_tc.cu", "sdpa_bwd_general.cu", "sdpa_weights.cu", "selftest.cu"]
 EXT_SOURCES = ["core/device_runtime.cpp", "ops/lifecycle_ops.cpp", "ops/attention_ops.cpp",
                "ops/norm_glu_ops.cpp", "ops/matmul_ops.cpp", "python/module.cpp"]
 

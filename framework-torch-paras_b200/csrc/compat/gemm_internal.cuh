@@ -27,6 +27,10 @@ struct GemmExtra {
 bool gemm_tc2_eligible(const Gpu* g, const paras_gemm_args* a);
 int gemm_tc2_run(Gpu* g, const paras_gemm_args* a, cudaStream_t s);
 
+// The decode-step kernel (gemm_skinny.cu): at most 128 rows of A against a weight that is read once.
+bool gemm_skinny_eligible(const Gpu* g, const paras_gemm_args* a);
+int gemm_skinny_run(Gpu* g, const paras_gemm_args* a, cudaStream_t s);
+
 // paras_b200_gemm with `ex` (may be null); A must be [M, K] rows for epilogues 3 and 4.
 int gemm_run(const paras_gemm_args* a, const GemmExtra* ex);
 

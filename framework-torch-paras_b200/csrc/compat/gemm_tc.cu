@@ -669,6 +669,9 @@ int gemm_run(const paras_gemm_args* a, const GemmExtra* ex) {
     // N <= 128 (the [.., head dim] products of attention backward): half-width B tiles and MMAs
     const bool narrow = a->N <= BN / 2 && (epi == kEpiNone || epi == kEpiBias || epi == kEpiRowScale);
     const int n_per_tile = a->epilogue == kEpiSwiglu || narrow ? BN / 2 : BN;
+    // A handful of rows against a weight: the weight-streaming kernel (PARAS_GEMM_SKINNY=0: this file's split-K)
+    static const bool skinny_off = getenv("PARAS_GEMM_SKINNY") && getenv("PARAS_GEMM_SKINNY")[0] == '0';
+    if (!ex && !skinny_off && gemm_skinny_eligible(g, a)) return gemm_skinny_run(g, a, pick_stream(g, a->stream));
     // Large projections run on CTA pairs (PARAS_GEMM_PAIR=0 keeps them on this file's kernel, for comparison)
     static const bool pair_off = getenv("PARAS_GEMM_PAIR") && getenv("PARAS_GEMM_PAIR")[0] == '0';
     if (!ex && !pair_off && gemm_tc2_eligible(g, a)) return gemm_tc2_run(g, a, pick_stream(g, a->stream));

@@ -121,6 +121,31 @@ def test_large_projections_on_cta_pairs(shape, dtype):
     assert float(out[:, :8].abs().sum()) == 0.0 and float(out[:, N + 8:].abs().sum()) == 0.0
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("shape", [(1, 4096, 4096), (7, 520, 1000), (16, 128, 256), (33, 6144, 4096), (64, 4096, 1096),
+                                   (100, 1032, 8192), (128, 2056, 4096), (48, 28672, 512), (5, 4096, 14336),
+                                   (130, 4096, 1024), (200, 19000, 264), (256, 6144, 4096)])
+def test_decode_step_projections_on_the_weight_streaming_kernel(shape, dtype):
+    # At most 128 rows against a weight: the weight rows sit on the MMA's M side, K is split inside a
+    # cluster and summed through distributed shared memory in a fixed order (the same bits every run).
+    M, N, K = shape
+    a, w = rand((M, K), 1, dtype, 0.5), rand((N, K), 2, dtype, 0.5)
+    bias = rand((N,), 4, dtype)
+    ad, wd = a.to(CUDA), w.to(CUDA)
+    got = abi.gemm(ad, wd)
+    close16(got, O.linear(a, w), f"skinny A W^T {shape}", exact_share=0.97)
+    close16(abi.gemm(ad, wd, bias=bias.to(CUDA)), O.linear(a, w, bias), f"skinny bias {shape}", exact_share=0.97)
+    assert torch.equal(abi.gemm(ad, wd), got)
+    out = torch.zeros(M, N + 16, dtype=dtype, device=CUDA)
+    abi.gemm(ad, wd, out=out[:, 8:N + 8])
+    assert torch.equal(out[:, 8:N + 8], got)
+    assert float(out[:, :8].abs().sum()) == 0.0 and float(out[:, N + 8:].abs().sum()) == 0.0
+    # rows that are slices of a wider activation matrix
+    wide = rand((M, K + 64), 9, dtype, 0.5)
+    close16(abi.gemm(wide.to(CUDA)[:, 32:K + 32], wd), O.linear(wide[:, 32:K + 32], w), f"skinny strided A {shape}",
+            exact_share=0.97)
+
+
 @pytest.mark.parametrize("shape", [(2304, 2304, 520), (1296, 4360, 264)])
 def test_transposed_operands_and_batches_on_cta_pairs(shape):
     # the gradients of a linear layer: dX = dY W (B as [K, N] rows), dW = dY^T X (A as [K, M] rows), and bmm
