@@ -83,9 +83,14 @@ __device__ __forceinline__ float4 ld_cluster_v4(uint32_t cluster_addr) {
     return v;
 }
 
-template <bool BF16>
+// SWIGLU: a block is 64 features; its weight tile is 64 gate-weight rows over 64 up-weight rows (two
+// loads), and the finishing step forms silu(gate) * up from the two halves of a token's partial sums,
+// each rounded to the tensors' dtype first as two separate projections would leave them
+// (the reference's paras::swiglu_linear, csrc/ops/rms_swiglu_ops.cpp:77-104).
+template <bool BF16, bool SWIGLU>
 __global__ void __launch_bounds__(kThreads, 1)
-gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const Params p) {
+gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_w2,
+                   const __grid_constant__ CUtensorMap map_x, const Params p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     const uint32_t smem_base = smem_u32(smem_raw);
     const uint32_t ring = smem_base + kSmemRing;
@@ -94,7 +99,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_raw + kSmemMisc + 4);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank(), split = cluster_nctarank();
-    const int n0 = int(blockIdx.x / split) * BW;
+    const int n0 = int(blockIdx.x / split) * (SWIGLU ? BW / 2 : BW);
     // this CTA's K steps: the k_iters are dealt out in consecutive, nearly equal ranges
     const int per = p.k_iters / int(split), extra = p.k_iters % int(split);
     const int k_begin = int(rank) * per + min(int(rank), extra);
@@ -119,6 +124,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     }
     if (warp == kLoadWarp && lane == 0) {
         tma_prefetch_desc(&map_w);
+        if (SWIGLU) tma_prefetch_desc(&map_w2);
         tma_prefetch_desc(&map_x);
     }
     tc_fence_before_sync();
@@ -138,6 +144,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 mbar_arrive_expect_tx(full, uint32_t(p.stage_bytes));
                 const uint32_t dst = ring + st * p.stage_bytes;
                 tma_load_3d(dst, &map_w, full, (k_begin + i) * BK, n0, 0);
+                if (SWIGLU) tma_load_3d(dst + kWBytes / 2, &map_w2, full, (k_begin + i) * BK, n0, 0);
                 tma_load_3d(dst + kWBytes, &map_x, full, (k_begin + i) * BK, 0, 0);
                 if (++st == p.stages) { st = 0; phase ^= 1u; }
             }
@@ -192,7 +199,48 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     // every CTA's partial tile is in its shared memory
     __syncthreads();
     cluster_sync_all();
-    if (warp < kEpiWarps) {
+    if (SWIGLU && warp < kEpiWarps) {
+        // half a warp per token: lane l of the half takes features 4l .. 4l+3, gate sums at [m][4l], up sums at [m][64 + 4l]
+        const int l16 = lane & 15, half = lane >> 4;
+        const int f = n0 + 4 * l16;
+        uint32_t peer[kMaxSplit];
+#pragma unroll
+        for (int s2 = 0; s2 < kMaxSplit; ++s2) peer[s2] = map_to_cta(ring + uint32_t(l16) * 16u, uint32_t(s2) < split ? uint32_t(s2) : rank);
+        const int mine = (p.M - int(rank) + int(split) - 1) / int(split);
+        for (int i0 = 2 * warp + half; i0 < mine; i0 += 2 * kEpiWarps) {
+            const int m = int(rank) + i0 * int(split);
+            float4 v[2][kMaxSplit];
+#pragma unroll
+            for (int u = 0; u < 2; ++u)
+#pragma unroll
+                for (int s2 = 0; s2 < kMaxSplit; ++s2)
+                    v[u][s2] = uint32_t(s2) < split ? ld_cluster_v4(peer[s2] + uint32_t(m) * (BW * 4u) + uint32_t(u) * (BW * 2u))
+                                                    : make_float4(0.f, 0.f, 0.f, 0.f);
+            float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+            for (int u = 0; u < 2; ++u)
+#pragma unroll
+                for (int s2 = 0; s2 < kMaxSplit; ++s2) {
+                    acc[u][0] += v[u][s2].x; acc[u][1] += v[u][s2].y; acc[u][2] += v[u][s2].z; acc[u][3] += v[u][s2].w;
+                }
+            float r[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float gg = round16<BF16>(acc[0][e]), uu = round16<BF16>(acc[1][e]);
+                r[e] = gg / (1.0f + __expf(-gg)) * uu;
+            }
+            uint16_t* dst = static_cast<uint16_t*>(p.c) + int64_t(m) * p.ldc + f;
+            const uint32_t lo = pack16<BF16>(r[0], r[1]), hi = pack16<BF16>(r[2], r[3]);
+            if (f + 3 < p.N && (reinterpret_cast<uintptr_t>(dst) & 7u) == 0) {
+                *reinterpret_cast<uint2*>(dst) = make_uint2(lo, hi);
+            } else {
+                if (f < p.N) dst[0] = uint16_t(lo & 0xffffu);
+                if (f + 1 < p.N) dst[1] = uint16_t(lo >> 16);
+                if (f + 2 < p.N) dst[2] = uint16_t(hi & 0xffffu);
+                if (f + 3 < p.N) dst[3] = uint16_t(hi >> 16);
+            }
+        }
+    } else if (warp < kEpiWarps) {
         // CTA `rank` finishes the tokens rank, rank + split, ...; a warp takes every fourth of them, a lane four
         // weight rows: 16-byte loads from each peer's tile, the loads of two tokens in flight before the first sum
         // (a remote load takes several hundred nanoseconds), an 8-byte store per lane = 256 contiguous bytes per warp.
@@ -254,8 +302,9 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 // X [M, K] rows with M <= 256, W [N, K] rows, one batch, no epilogue or a bias, K a multiple of 8 elements.
 bool gemm_skinny_eligible(const Gpu* g, const paras_gemm_args* a) {
     if (a->a_layout != PARAS_GEMM_A_MK || a->b_layout != PARAS_GEMM_B_NK || a->batch != 1) return false;
-    if (a->epilogue != 0 && a->epilogue != 1) return false;
+    if (a->epilogue != 0 && a->epilogue != 1 && a->epilogue != 2) return false;
     if (a->M > kMaxTokens || a->N < BW || a->K < 4 * BK) return false;
+    if (a->epilogue == 2) return a->M <= 128;   // SwiGLU: 64 features per block, usually more blocks than SMs
     // more than 128 tokens leave room for one CTA per SM only: with more weight-row blocks than SMs the
     // second round of CTAs costs more than the general kernel's wider tiles ([256, 28672, 4096]: 89 against 60 us)
     const int sms = g->sm_count > 0 ? g->sm_count : 148;
@@ -269,7 +318,9 @@ int gemm_skinny_run(Gpu* g, const paras_gemm_args* a, cudaStream_t s) {
     p.tokens = std::max(16, (p.M + 15) / 16 * 16);
     p.stage_bytes = kWBytes + p.tokens * 128;
     const int sms_all = g->sm_count > 0 ? g->sm_count : 148;
-    const int blocks_all = int((a->N + BW - 1) / BW);
+    const bool swiglu = a->epilogue == 2;
+    const int rows_per_block = swiglu ? BW / 2 : BW;   // output columns a block produces
+    const int blocks_all = int((a->N + rows_per_block - 1) / rows_per_block);
     // more weight-row blocks than SMs: half the ring, so that two CTAs share an SM and every block streams at once
     // (the partial tile of more than 128 tokens needs more than half the ring)
     const int ring_bytes = blocks_all > sms_all && p.tokens <= 128 ? kRingBytes / 2 : kRingBytes;
@@ -281,18 +332,22 @@ int gemm_skinny_run(Gpu* g, const paras_gemm_args* a, cudaStream_t s) {
     p.c = a->c;
     p.ldc = a->ldc;
     p.status = g->status_dev;
-    CUtensorMap mw, mx;
-    if ((st = make_tensor_map_3d(&mw, a->b, a->dtype, a->K, a->N, 1, a->ldb, a->stride_b, BK, BW)) != PARAS_OK) return st;
+    CUtensorMap mw, mw2, mx;
+    if ((st = make_tensor_map_3d(&mw, a->b, a->dtype, a->K, a->N, 1, a->ldb, a->stride_b, BK, rows_per_block)) != PARAS_OK) return st;
+    mw2 = mw;
+    if (swiglu && (st = make_tensor_map_3d(&mw2, a->b2, a->dtype, a->K, a->N, 1, a->ldb, a->stride_b, BK, rows_per_block)) != PARAS_OK) return st;
     if ((st = make_tensor_map_3d(&mx, a->a, a->dtype, a->K, a->M, 1, a->lda, a->stride_a, BK, p.tokens)) != PARAS_OK) return st;
-    const int blocks = int((a->N + BW - 1) / BW);
+    const int blocks = blocks_all;
     const bool bf = a->dtype == PARAS_BF16;
-    if (bf) PB_CUDA(cudaFuncSetAttribute(gemm_skinny_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_total));
-    else PB_CUDA(cudaFuncSetAttribute(gemm_skinny_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_total));
+    const void* kernel = swiglu ? (bf ? (const void*)gemm_skinny_kernel<true, true> : (const void*)gemm_skinny_kernel<false, true>)
+                                : (bf ? (const void*)gemm_skinny_kernel<true, false> : (const void*)gemm_skinny_kernel<false, false>);
+    PB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_total));
     // Split K so that as many SMs as possible stream weight at once, each CTA keeping at least 8 K steps.  How
     // many clusters of a size the GPU holds at a time depends on how its SMs group (a size that does not divide
     // a group leaves SMs out), so the driver is asked, once per size.
     constexpr int kGpuSlots = 64;
     static int fit[kGpuSlots][kMaxSplit + 1];   // clusters of size s resident at once; 0 = not asked yet
+    // (asked with the plain kernel: both instantiations use the same shared memory and one CTA per SM here)
     int split = 1, best = std::min(blocks, g->sm_count > 0 ? g->sm_count : 148);
     for (int sz = 2; sz <= kMaxSplit && sz <= p.k_iters / 8 && blocks <= sms_all; ++sz) {
         int& f = fit[a->gpu % kGpuSlots][sz];
@@ -307,8 +362,7 @@ int gemm_skinny_run(Gpu* g, const paras_gemm_args* a, cudaStream_t s) {
             q.attrs = &qa;
             q.numAttrs = 1;
             int n = 0;
-            const cudaError_t e = bf ? cudaOccupancyMaxActiveClusters(&n, gemm_skinny_kernel<true>, &q)
-                                     : cudaOccupancyMaxActiveClusters(&n, gemm_skinny_kernel<false>, &q);
+            const cudaError_t e = cudaOccupancyMaxActiveClusters(&n, kernel, &q);
             if (e != cudaSuccess) { cudaGetLastError(); n = -1; }
             f = n > 0 ? n : -1;
         }
@@ -327,8 +381,8 @@ int gemm_skinny_run(Gpu* g, const paras_gemm_args* a, cudaStream_t s) {
     attr.val.clusterDim.z = 1;
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
-    if (bf) PB_CUDA(cudaLaunchKernelEx(&cfg, gemm_skinny_kernel<true>, mw, mx, p));
-    else PB_CUDA(cudaLaunchKernelEx(&cfg, gemm_skinny_kernel<false>, mw, mx, p));
+    void* args[] = {(void*)&mw, (void*)&mw2, (void*)&mx, (void*)&p};
+    PB_CUDA(cudaLaunchKernelExC(&cfg, kernel, args));
     return PARAS_OK;
 }
 

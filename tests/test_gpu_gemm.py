@@ -146,6 +146,25 @@ def test_decode_step_projections_on_the_weight_streaming_kernel(shape, dtype):
             exact_share=0.97)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("shape", [(1, 1024, 512), (16, 14336, 4096), (64, 1704, 1000), (100, 2056, 1096), (128, 520, 264)])
+def test_decode_step_gate_up_projection_with_swiglu(shape, dtype):
+    # paras::swiglu_linear with a handful of rows: 64 gate-weight rows over 64 up-weight rows per block
+    M, Fd, K = shape
+    x, wg, wu = rand((M, K), 1, dtype), rand((Fd, K), 2, dtype, 0.05), rand((Fd, K), 3, dtype, 0.05)
+    got = abi.gemm(x.to(CUDA), wg.to(CUDA), up_weight=wu.to(CUDA))
+    want = O.swiglu_linear(x, wg, wu)
+    # Either projection may land on the neighbouring 16-bit value (K = 4096 terms summed in another order),
+    # which moves silu(g) * u by up to an ulp before its own rounding: two ulps of the result, not one.
+    g, w = got.cpu().double(), want.double()
+    ulp2 = 2.0 ** -6 if dtype == torch.bfloat16 else 2.0 ** -9
+    bad = (g - w).abs() > ulp2 * w.abs() + 2e-2
+    assert not bad.any(), f"skinny swiglu {shape}: {int(bad.sum())} elements off, worst {(g - w).abs().max():.3e}"
+    # (with K = 4096 each projection differs from the host GEMM's rounding in 1-1.5 % of its elements)
+    assert (got.cpu() == want).double().mean().item() >= 0.95
+    assert torch.equal(abi.gemm(x.to(CUDA), wg.to(CUDA), up_weight=wu.to(CUDA)), got)
+
+
 @pytest.mark.parametrize("shape", [(2304, 2304, 520), (1296, 4360, 264)])
 def test_transposed_operands_and_batches_on_cta_pairs(shape):
     # the gradients of a linear layer: dX = dY W (B as [K, N] rows), dW = dY^T X (A as [K, M] rows), and bmm
