@@ -53,6 +53,7 @@ struct Params {
     int k_iters;       // K steps of 64 in all
     int tmem_cols;
     const void* bias;
+    const float* row_scale;   // C[m, :] *= row_scale[m] (RMSNorm folded into the projection), or null
     void* c;
     int64_t ldc;
     int* status;
@@ -272,6 +273,10 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                     acc.x += v[u][s2].x; acc.y += v[u][s2].y; acc.z += v[u][s2].z; acc.w += v[u][s2].w;
                 }
                 if (m >= p.M) continue;
+                if (p.row_scale) {
+                    const float rs = __ldg(p.row_scale + m);
+                    acc.x *= rs; acc.y *= rs; acc.z *= rs; acc.w *= rs;
+                }
                 uint16_t* dst = static_cast<uint16_t*>(p.c) + int64_t(m) * p.ldc + n;
                 const uint32_t lo = pack16<BF16>(acc.x + bias[0], acc.y + bias[1]), hi = pack16<BF16>(acc.z + bias[2], acc.w + bias[3]);
                 if (n + 3 < p.N && (reinterpret_cast<uintptr_t>(dst) & 7u) == 0) {
@@ -299,10 +304,11 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 
 }  // namespace
 
-// X [M, K] rows with M <= 256, W [N, K] rows, one batch, no epilogue or a bias, K a multiple of 8 elements.
+// X [M, K] rows with M <= 256, W [N, K] rows, one batch; no epilogue, a bias, a scale per row of X, or
+// (M <= 128) the SwiGLU of two weights; K a multiple of 8 elements.
 bool gemm_skinny_eligible(const Gpu* g, const paras_gemm_args* a) {
     if (a->a_layout != PARAS_GEMM_A_MK || a->b_layout != PARAS_GEMM_B_NK || a->batch != 1) return false;
-    if (a->epilogue != 0 && a->epilogue != 1 && a->epilogue != 2) return false;
+    if (a->epilogue != 0 && a->epilogue != 1 && a->epilogue != 2 && a->epilogue != 5) return false;
     if (a->M > kMaxTokens || a->N < BW || a->K < 4 * BK) return false;
     if (a->epilogue == 2) return a->M <= 128;   // SwiGLU: 64 features per block, usually more blocks than SMs
     // more than 128 tokens leave room for one CTA per SM only: with more weight-row blocks than SMs the
@@ -329,6 +335,7 @@ int gemm_skinny_run(Gpu* g, const paras_gemm_args* a, cudaStream_t s) {
     p.k_iters = (p.K + BK - 1) / BK;
     p.tmem_cols = p.tokens <= 32 ? 32 : p.tokens <= 64 ? 64 : p.tokens <= 128 ? 128 : 256;
     p.bias = a->epilogue == 1 ? a->bias : nullptr;
+    p.row_scale = a->epilogue == 5 ? a->row_scale : nullptr;
     p.c = a->c;
     p.ldc = a->ldc;
     p.status = g->status_dev;

@@ -271,7 +271,8 @@ def test_linearity_at_projection_size():
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
-@pytest.mark.parametrize("shape", [(256, 512, 256), (300, 520, 1000), (1000, 128, 4096), (5, 264, 72)])
+@pytest.mark.parametrize("shape", [(256, 512, 256), (300, 520, 1000), (1000, 128, 4096), (5, 264, 72),
+                                   (16, 6144, 4096), (100, 1032, 520)])   # the last two: the decode-step kernel
 def test_rms_norm_folded_into_the_projection(shape, dtype):
     # linear(rms_norm(x, w), W) in one GEMM (row-scale epilogue) against the reference's two steps:
     # paras::rms_norm (fused_ops.cpp:43-88) rounded to 16 bits, then the host GEMM of linear
