@@ -500,6 +500,47 @@ def run_ours(args):
         extra[f"sdpa_decode_padding_mask_B{db}_kv32768"] = {"ms": t, "gbs": gbs, "frac_of_hbm_peak": gbs / peaks["hbm_gbs"],
                                                          "kernel": abi.sdpa_last_kernel()}
         del padm
+        # One decoder layer of that step (hidden 4096, Hq=32, Hkv=8, D=128, FFN 14336, batch db): RMSNorm folded
+        # into the QKV projection, decode attention, output projection, RMSNorm folded into the gate/up projection
+        # with SwiGLU, down projection.  Bytes = the layer's weights (436 MB) + its KV cache + activations; the
+        # launches queue behind a spin kernel so that the events see device time.
+        hid, ffn = 4096, 14336
+        xl = gen((db, hid), 70)
+        wn1 = gen((hid,), 71, mean=1.0, std=0.1)
+        w_qkv, w_o = gen((6144, hid), 72, std=0.02), gen((hid, hid), 73, std=0.02)
+        w_g, w_u, w_d = gen((ffn, hid), 74, std=0.02), gen((ffn, hid), 75, std=0.02), gen((hid, ffn), 76, std=0.02)
+        w_qkv_f = abi.scale_columns(w_qkv, wn1)
+        qkv = torch.empty((db, 6144), dtype=torch.bfloat16, device=dev)
+        att = torch.empty((db, 32, 1, 128), dtype=torch.bfloat16, device=dev)
+        h1, ff, h2 = (torch.empty((db, n_), dtype=torch.bfloat16, device=dev) for n_ in (hid, ffn, hid))
+
+        def layer():
+            abi.gemm(xl, w_qkv_f, row_scale=abi.rms_rstd(xl, 1e-6), out=qkv)
+            qv = qkv[:, :4096].view(db, 32, 1, 128)          # (the new token's k, v would be appended to the cache here)
+            abi.sdpa_fwd(qv, kd, vd, out=att, workspace=ws if ws_bytes else None)
+            abi.gemm(att.view(db, hid), w_o, out=h1)
+            abi.gemm(h1, w_g, up_weight=w_u, out=ff)          # (a second norm would fold into w_g, w_u like the first)
+            abi.gemm(ff, w_d, out=h2)
+
+        for _ in range(3):
+            layer()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda._sleep(int(4e7))
+        e0.record()
+        for _ in range(5):
+            layer()
+        e1.record()
+        torch.cuda.synchronize()
+        t_layer = e0.elapsed_time(e1) / 5
+        wbytes = (w_qkv.numel() + w_o.numel() + w_g.numel() + w_u.numel() + w_d.numel()) * 2
+        lbytes = wbytes + (kd.numel() + vd.numel()) * 2
+        extra[f"decode_layer_B{db}_kv32768"] = {
+            "ms": t_layer, "ms_attention_alone": extra[f"sdpa_decode_B{db}_kv32768"]["ms"], "weight_bytes": wbytes,
+            "gbs": lbytes / (t_layer * 1e-3) / 1e9, "frac_of_hbm_peak": lbytes / (t_layer * 1e-3) / 1e9 / peaks["hbm_gbs"],
+            "note": "rms_rstd + QKV projection (row-scale epilogue), decode attention, output projection, gate/up projection "
+                    "with SwiGLU, down projection: five weight-streaming GEMM launches around the attention kernel"}
+        del xl, wn1, w_qkv, w_o, w_g, w_u, w_d, w_qkv_f, qkv, att, h1, ff, h2
         del qd, kd, vd, od, ws
     if want("block"):
         # config 5, one GPU's share (B=64 over 8 GPUs -> 8 batch elements here): RMSNorm -> causal GQA
