@@ -182,11 +182,25 @@ sdpa_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
                 mrow[half] = int64_t(b) * p.ms[0] + int64_t(hk * p.group + r % p.group) * p.ms[1] + int64_t(r / p.group) * p.ms[2];
             }
         }
+        // A bool mask with contiguous keys whose two rows share a mask row (a key-padding mask): this thread's
+        // four bytes of a tile are two aligned 2-byte loads, asked for a tile ahead so that their latency runs
+        // under the tile before (after the MMAs, where the mask is needed, nothing else could hide it).
+        const bool mfast = MASK && p.mask_kind == 1 && p.ms[3] == 1 && mrow[0] == mrow[1] &&
+                           ((reinterpret_cast<uintptr_t>(p.mask) + size_t(mrow[0])) & 1u) == 0;
+        auto mask_pair = [&](int i) -> uint32_t {   // keys +0, +1 in the low half, +8, +9 in the high half
+            const int kb = (t0 + i) * TK + warp * 16 + cpair;
+            if (i >= ntiles || kb + 9 >= p.Lk) return 0u;
+            const unsigned char* mp = static_cast<const unsigned char*>(p.mask) + mrow[0] + kb;
+            return uint32_t(__ldg(reinterpret_cast<const uint16_t*>(mp))) | (uint32_t(__ldg(reinterpret_cast<const uint16_t*>(mp + 8))) << 16);
+        };
+        uint32_t mnext = mfast ? mask_pair(0) : 0u;
         bool ok = true;
         for (int i = 0; i < ntiles; ++i) {
             const int s = i % kStages;
             const int krow0 = warp * 16;  // this warp's 16 keys inside the tile
             const int key_base = (t0 + i) * TK + krow0 + cpair;
+            const uint32_t mcur = mnext;
+            if (mfast) mnext = mask_pair(i + 1);
             ok = mbar_wait(full(s), (i / kStages) & 1, abort_flag);
             if (!ok) break;
             const uint32_t kbase = smem_base + s * kStageBytes;
@@ -211,7 +225,13 @@ sdpa_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
             // what the mask adds to this thread's four keys of each of its two rows (one set of loads when the
             // rows share a mask row, as with a key-padding mask)
             float madd[2][2][2];
-            if (MASK) {
+            if (MASK && mfast && key_base + 9 < p.Lk) {
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                    for (int e = 0; e < 2; ++e)
+                        madd[0][nt][e] = madd[1][nt][e] = ((mcur >> (16 * nt + 8 * e)) & 0xffu) ? 0.f : -INFINITY;
+            } else if (MASK) {
 #pragma unroll
                 for (int half = 0; half < 2; ++half) {
                     if (half == 1 && mrow[1] == mrow[0]) {
