@@ -496,9 +496,11 @@ def run_ours(args):
         padm = torch.ones(db, 1, 1, 32768, dtype=torch.bool, device=dev)
         padm[:, :, :, 30000:] = False
         t = loop_ms(lambda: abi.sdpa_fwd(qd, kd, vd, out=od, mask=padm, workspace=ws if ws_bytes else None), s3, 3)
-        gbs = nbytes / (t * 1e-3) / 1e9
+        # the kernel stops at the last valid key of each batch element: only the 30000 valid keys count as bytes
+        vbytes = (kd.numel() + vd.numel()) * 2 * 30000 // 32768 + (qd.numel() + od.numel()) * 2
+        gbs = vbytes / (t * 1e-3) / 1e9
         extra[f"sdpa_decode_padding_mask_B{db}_kv32768"] = {"ms": t, "gbs": gbs, "frac_of_hbm_peak": gbs / peaks["hbm_gbs"],
-                                                         "kernel": abi.sdpa_last_kernel()}
+                                                         "bytes": vbytes, "valid_keys": 30000, "kernel": abi.sdpa_last_kernel()}
         del padm
         # One decoder layer of that step (hidden 4096, Hq=32, Hkv=8, D=128, FFN 14336, batch db): RMSNorm folded
         # into the QKV projection, decode attention, output projection, RMSNorm folded into the gate/up projection

@@ -103,10 +103,9 @@ sdpa_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int split = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
-    const int total_tiles = (p.Lk + TK - 1) / TK;
-    const int t0 = split * p.tiles_per_split;
-    const int t1 = min(total_tiles, t0 + p.tiles_per_split);
-    const int ntiles = max(0, t1 - t0);
+    int total_tiles = (p.Lk + TK - 1) / TK;
+    int tiles_per_split = p.tiles_per_split;
+    int* last_valid = reinterpret_cast<int*>(smem_gen + kSmemMisc + 4);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
@@ -114,10 +113,37 @@ sdpa_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
             mbar_init(empty(s), kConsumers);
         }
         *abort_flag = 0;
+        *last_valid = -1;
         mbar_fence_init();
         fence_proxy_async_smem();
     }
     __syncthreads();
+    // A bool mask that is one row of keys per batch element (caches of different lengths, padded to a common
+    // length): the keys after the last one that may be attended are never loaded.  The CTAs of a batch element
+    // find that key (a pass over the mask row, Lk bytes) and share the shorter range out among themselves.
+    if (MASK && p.mask_kind == 1 && p.ms[1] == 0 && p.ms[2] == 0 && p.ms[3] == 1) {
+        const unsigned char* row = static_cast<const unsigned char*>(p.mask) + int64_t(b) * p.ms[0];
+        int last = -1;
+        if ((reinterpret_cast<uintptr_t>(row) & 15u) == 0 && p.Lk % 16 == 0) {
+            for (int c = int(threadIdx.x); c < p.Lk / 16; c += kThreads) {
+                const uint4 w = __ldg(reinterpret_cast<const uint4*>(row) + c);
+                const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    if (ww[j]) last = 16 * c + 4 * j + (31 - __clz(int(ww[j]))) / 8;   // c grows: the later word wins
+            }
+        } else {
+            for (int k = int(threadIdx.x); k < p.Lk; k += kThreads)
+                if (row[k]) last = k;
+        }
+        if (last >= 0) atomicMax(last_valid, last);
+        __syncthreads();
+        total_tiles = (*last_valid + 1 + TK - 1) / TK;
+        tiles_per_split = (total_tiles + int(gridDim.x) - 1) / int(gridDim.x);
+    }
+    const int t0 = split * tiles_per_split;
+    const int t1 = min(total_tiles, t0 + tiles_per_split);
+    const int ntiles = max(0, t1 - t0);
 
     // per-thread softmax state for rows r0 = lane/4 and r0 + 8, and the O accumulators
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};

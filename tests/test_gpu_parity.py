@@ -548,6 +548,27 @@ def test_rmsnorm_backward_row_kernels_against_oracle(shape, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("offset", [0, 1])
+def test_decode_kernel_reads_no_keys_past_the_longest_valid_one(offset, dtype):
+    # caches of different lengths padded to one length: the kernel finds each batch element's last valid key
+    # from the [B,1,1,Lk] mask and shares only that range out among its CTAs; holes inside the range stay
+    # masked per key, a batch element without any key gives NaN as in the reference
+    B, Hq, Hkv, Lq, Lk = 5, 8, 2, 1, 4096
+    q, k, v = _qkv(B, Hq, Hkv, Lq, Lk, 128, dtype, seed=71)
+    full = torch.zeros(B, 1, 1, Lk + offset, dtype=torch.bool)
+    for b, n in enumerate((4096, 2049, 17, 0, 1000)):
+        full[b, :, :, offset:offset + n] = True
+    full[4, :, :, offset + 100:offset + 900] = False          # a hole
+    mask = full[:, :, :, offset:]                              # offset 1: the rows start on an odd address
+    want = O.sdpa(q, k, v, attn_mask=mask, enable_gqa=True)
+    got = abi.sdpa_fwd(q.to(DEV), k.to(DEV), v.to(DEV), mask=full.to(DEV)[:, :, :, offset:], flags=abi.SDPA_REF_SCALE).cpu()
+    assert abi.sdpa_last_kernel() == "decode_mma"
+    assert torch.equal(torch.isnan(got), torch.isnan(want)) and torch.isnan(want[3]).all() and not torch.isnan(want[0]).any()
+    fin = ~torch.isnan(want)
+    assert (got[fin].double() - want[fin].double()).abs().max().item() <= 2e-2
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("kind", ["padding", "per_row_bool", "additive", "additive_f32"])
 def test_decode_kernel_with_explicit_masks(kind, dtype):
     # batched decoding over caches of different lengths: one or a few query positions, a long cache and a mask;
