@@ -500,6 +500,11 @@ int sdpa_decode_launch(Gpu* g, const paras_sdpa_args& a, float scale, const Spli
     p.mask = a.mask;
     p.mask_kind = a.mask ? a.mask_kind : 0;
     for (int i = 0; i < 4; ++i) p.ms[i] = a.mask_strides[i];
+    // a dimension of extent 1 is never stepped along: its stride reads as 0, like a broadcast one
+    if (a.B == 1) p.ms[0] = 0;
+    if (a.Hq == 1) p.ms[1] = 0;
+    if (a.Lq == 1) p.ms[2] = 0;
+    if (a.Lk == 1) p.ms[3] = 1;
     p.inv_scale = 1.0f / scale;
     dim3 grid(ws.splits, a.Hkv, a.B);
     auto go = [&](auto kernel) -> int {
