@@ -501,6 +501,17 @@ def run_ours(args):
         gbs = vbytes / (t * 1e-3) / 1e9
         extra[f"sdpa_decode_padding_mask_B{db}_kv32768"] = {"ms": t, "gbs": gbs, "frac_of_hbm_peak": gbs / peaks["hbm_gbs"],
                                                          "bytes": vbytes, "valid_keys": 30000, "kernel": abi.sdpa_last_kernel()}
+        # caches of 1000 .. 32000 valid keys in one batch
+        lens = [1000 + (i * 499) % 31000 for i in range(db)]
+        for i, n_ in enumerate(lens):
+            padm[i, :, :, :n_] = True
+            padm[i, :, :, n_:] = False
+        t = loop_ms(lambda: abi.sdpa_fwd(qd, kd, vd, out=od, mask=padm, workspace=ws if ws_bytes else None), s3, 3)
+        vbytes = sum(lens) * 8 * 128 * 2 * 2 + (qd.numel() + od.numel()) * 2
+        gbs = vbytes / (t * 1e-3) / 1e9
+        extra[f"sdpa_decode_ragged_B{db}_kv1000_to_32000"] = {"ms": t, "gbs": gbs, "frac_of_hbm_peak": gbs / peaks["hbm_gbs"],
+                                                            "bytes": vbytes, "mean_valid_keys": sum(lens) / db,
+                                                            "kernel": abi.sdpa_last_kernel()}
         del padm
         # One decoder layer of that step (hidden 4096, Hq=32, Hkv=8, D=128, FFN 14336, batch db): RMSNorm folded
         # into the QKV projection, decode attention, output projection, RMSNorm folded into the gate/up projection

@@ -1022,6 +1022,10 @@ int sdpa_tc_launch(Gpu* g, const paras_sdpa_args& a, float scale, cudaStream_t s
     p.mask = a.mask;
     p.mask_kind = a.mask ? a.mask_kind : 0;
     for (int i = 0; i < 4; ++i) p.ms[i] = a.mask_strides[i];
+    // a dimension of extent 1 is never stepped along: its stride reads as 0, like a broadcast one
+    if (a.B == 1) p.ms[0] = 0;
+    if (a.Hq == 1) p.ms[1] = 0;
+    if (a.Lq == 1) p.ms[2] = 0;
     p.status = g->status_dev;
     if (rope) {
         if (a.D != 128 || p.mask_kind)
