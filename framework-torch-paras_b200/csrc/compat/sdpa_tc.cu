@@ -127,6 +127,13 @@ struct TcParams {
     // 2^pack_shift rows each (Lq <= 2^pack_shift), so a few query positions of 2, 4 or 8 heads fill both
     // tiles against one pass over K/V.  Units are (split, batch, kv head); lq_pad = 2^pack_shift.
     int pack_shift;
+    // A bool mask that is one row of keys per batch element (sequences padded to a common length), MASK
+    // kernels only: kv_len[b] = 1 + the last key of batch element b that may be attended (Lk when it has none:
+    // such rows end as NaN through the ordinary mask path), key_prefix[b] != 0 when every key before it may
+    // be.  An item visits the kv tiles below kv_len[b] only, and a prefix mask is applied as a sequence
+    // length (the tile on the boundary is cut like a ragged last tile) without reading the mask again.
+    const int* kv_len;
+    const int* key_prefix;
 };
 
 // One work item = one 256-row query block of one (batch, head).
@@ -137,11 +144,12 @@ struct Item {
     int n;         // max of the two
     int kv0;       // first kv tile (0 unless the keys are split)
     int orow;      // output row offset (split * lq_pad)
+    int lk;        // keys this item may see (MASK kernels with kv_len: the batch element's; else Lk)
 };
 
-__device__ __forceinline__ int kv_tiles_for(const TcParams& p, int start) {
+__device__ __forceinline__ int kv_tiles_for(const TcParams& p, int start, int lk) {
     if (start >= p.Lq) return 0;
-    int last = p.Lk;
+    int last = lk;
     if (p.causal) last = min(last, min(p.Lq, start + BM));  // keys 0..row
     return (last + BN - 1) / BN;
 }
@@ -152,8 +160,9 @@ __device__ __forceinline__ int kv_tiles_for(const TcParams& p, int start) {
 // and the query blocks of one head (and the heads of one GQA group, which are adjacent
 // units) run at the same time, so their K/V tiles are L2 hits.
 // `seq` counts items of this CTA: unit = blockIdx.x + (seq/2)*gridDim.x, half = seq & 1.
-template <bool SPLIT, bool PACK>
+template <bool SPLIT, bool PACK, bool MASK>
 __device__ __forceinline__ bool get_item(const TcParams& p, int seq, Item* it) {
+    it->lk = p.Lk;
     if (PACK) {
         int unit = int(blockIdx.x) + seq * int(gridDim.x);
         if (unit >= p.units) return false;
@@ -167,7 +176,7 @@ __device__ __forceinline__ bool get_item(const TcParams& p, int seq, Item* it) {
 #pragma unroll
         for (int t = 0; t < 2; ++t) {
             it->start[t] = 0;              // every row of the item is a query position below 2^pack_shift
-            it->ntile[t] = kv_tiles_for(p, 0);
+            it->ntile[t] = kv_tiles_for(p, 0, p.Lk);
             if (SPLIT) it->ntile[t] = min(max(it->ntile[t] - it->kv0, 0), p.split_tiles);
         }
         it->n = it->ntile[0];
@@ -189,10 +198,11 @@ __device__ __forceinline__ bool get_item(const TcParams& p, int seq, Item* it) {
     it->h = hb - it->b * p.Hq;
     it->hk = it->h / (p.Hq / p.Hkv);
     const bool dup = (seq & 1) && pair == hi;  // odd block count: the middle block has no partner
+    if (MASK && p.kv_len) it->lk = __ldg(p.kv_len + it->b);
 #pragma unroll
     for (int t = 0; t < 2; ++t) {
         it->start[t] = qblk * (kTilesPerCta * BM) + t * BM;
-        it->ntile[t] = dup ? 0 : kv_tiles_for(p, it->start[t]);
+        it->ntile[t] = dup ? 0 : kv_tiles_for(p, it->start[t], MASK ? it->lk : p.Lk);
         if (SPLIT) it->ntile[t] = min(max(it->ntile[t] - it->kv0, 0), p.split_tiles);
     }
     it->n = max(it->ntile[0], it->ntile[1]);
@@ -283,7 +293,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                 return true;
             };
             Item it;
-            for (int seq = 0; ok && get_item<SPLIT, PACK>(p, seq, &it); ++seq) {
+            for (int seq = 0; ok && get_item<SPLIT, PACK, MASK>(p, seq, &it); ++seq) {
                 if (it.n == 0) continue;
                 const int kv0 = SPLIT ? it.kv0 : 0;
                 ok = load_entry(&map_k, kv0 * BN, it.hk, it.b);  // K0 completes the previous item's last pair
@@ -341,7 +351,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             uint32_t qcnt[2] = {0, 0};   // items that used tile t (Q / O barriers)
             uint32_t pcnt[2] = {0, 0};   // softmax iterations of tile t so far (P barrier)
             Item it;
-            for (int seq = 0; ok && get_item<SPLIT, PACK>(p, seq, &it); ++seq) {
+            for (int seq = 0; ok && get_item<SPLIT, PACK, MASK>(p, seq, &it); ++seq) {
                 if (it.n == 0) continue;
                 if (!have) ok = mbar_wait(bar(kBarKVFull + (G & 1)), (G >> 1) & 1, abort_flag, 3);
 #pragma unroll
@@ -409,9 +419,11 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         uint32_t scnt = 0;  // S tiles consumed so far
         uint32_t ocnt = 0;  // items finished so far
         Item it;
-        for (int seq = 0; ok && get_item<SPLIT, PACK>(p, seq, &it); ++seq) {
+        for (int seq = 0; ok && get_item<SPLIT, PACK, MASK>(p, seq, &it); ++seq) {
             const int nt = it.ntile[t];
             if (nt == 0) continue;
+            const int lk_item = MASK ? it.lk : p.Lk;
+            const bool mask_off = MASK && p.key_prefix && __ldg(p.key_prefix + it.b) != 0;   // the length says it all
             // PACK: row r of the tile is query position r mod 2^pack_shift of head r >> pack_shift of the group
             const int row_q = PACK ? ((wq * 32 + lane) & ((1 << p.pack_shift) - 1)) : it.start[t] + wq * 32 + lane;
             const int head_q = PACK ? it.h + ((t * BM + wq * 32) >> p.pack_shift) : it.h;   // (a warp's 32 rows: one head)
@@ -640,7 +652,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                 if (MASK) {
                     // these warps are idle until S arrives: slice 0 of this step's mask goes to the staging
                     // buffer now, slice 1 stays in flight across the wait
-                    staged = mfast && (j + 1) * BN <= p.Lk;
+                    staged = mfast && !mask_off && (j + 1) * BN <= p.Lk;
                     if (staged) {
                         uint4 w0[8];
                         mask_ldg(j * BN, 0, w0);
@@ -648,7 +660,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                         mask_sts(w0);
                         __syncwarp();
                     }
-                    early = mbcast && (j + 1) * BN <= p.Lk;
+                    early = mbcast && !mask_off && (j + 1) * BN <= p.Lk;
                     if (early) {
 #pragma unroll
                         for (int v = 0; v < 8; ++v) mw[v] = __ldg(reinterpret_cast<const uint4*>(mask_bh + j * BN) + v);
@@ -700,14 +712,14 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 #pragma unroll
                     for (int c = 0; c < 4; ++c) tmem_ld_fence32(reinterpret_cast<uint32_t(&)[32]>(s[32 * c]));
                     const int col0 = SPLIT ? (it.kv0 + j) * BN : j * BN;
-                    const bool need_mask = (p.causal && col0 + BN - 1 > it.start[t]) || (col0 + BN > p.Lk);
+                    const bool need_mask = (p.causal && col0 + BN - 1 > it.start[t]) || (col0 + BN > lk_item);
                     if (need_mask) {
-                        const int limit = (p.causal ? min(row_q, p.Lk - 1) : p.Lk - 1) - col0;
+                        const int limit = (p.causal ? min(row_q, lk_item - 1) : lk_item - 1) - col0;
 #pragma unroll
                         for (int i = 0; i < BN; ++i)
                             if (i > limit) s[i] = 0xff800000u;  // -inf
                     }
-                    if (MASK) {
+                    if (MASK && !mask_off) {
                         if (staged && attempt == 0) {
                             mask_apply_staged(s, col0, mw);
                         } else if (early) {
@@ -829,6 +841,40 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         // so a broken launch costs every CTA one time limit in parallel, not one after another.
         *p.status = *abort_flag;
         __threadfence_system();
+    }
+}
+
+// ---- key-padding masks: the length each batch element's row stands for ---------------------------
+// One CTA per batch element over its Lk mask bytes: kv_len[b] = 1 + the last nonzero byte's index (Lk if
+// there is none), key_prefix[b] = 1 when every byte before it is nonzero too.
+__global__ void __launch_bounds__(256) key_mask_scan_kernel(const unsigned char* __restrict__ mask, int64_t bstride, int Lk,
+                                                            int* __restrict__ kv_len, int* __restrict__ key_prefix) {
+    __shared__ int s_last, s_count;
+    const unsigned char* row = mask + int64_t(blockIdx.x) * bstride;
+    if (threadIdx.x == 0) { s_last = -1; s_count = 0; }
+    __syncthreads();
+    int last = -1, count = 0;
+    if ((reinterpret_cast<uintptr_t>(row) & 15u) == 0 && Lk % 16 == 0) {
+        for (int c = int(threadIdx.x); c < Lk / 16; c += 256) {
+            const uint4 w = __ldg(reinterpret_cast<const uint4*>(row) + c);
+            const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    if ((ww[j] >> (8 * e)) & 0xffu) { last = 16 * c + 4 * j + e; ++count; }
+            }
+        }
+    } else {
+        for (int k = int(threadIdx.x); k < Lk; k += 256)
+            if (row[k]) { last = k; ++count; }
+    }
+    if (last >= 0) atomicMax(&s_last, last);
+    if (count) atomicAdd(&s_count, count);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        kv_len[blockIdx.x] = s_last < 0 ? Lk : s_last + 1;
+        key_prefix[blockIdx.x] = s_last >= 0 && s_count == s_last + 1;
     }
 }
 
@@ -981,7 +1027,12 @@ int sdpa_tc_launch(Gpu* g, const paras_sdpa_args& a, float scale, cudaStream_t s
             own = true;
         }
     }
+    void* lens = nullptr;   // kv_len and key_prefix of a key-padding mask
     auto release = [&](int status) {
+        if (lens) {
+            const int st3 = paras_b200_free_async(a.gpu, lens, s);
+            if (status == PARAS_OK) status = st3;
+        }
         if (!own) return status;
         const int st2 = paras_b200_free_async(a.gpu, scratch, s);
         return status != PARAS_OK ? status : st2;
@@ -1026,6 +1077,14 @@ int sdpa_tc_launch(Gpu* g, const paras_sdpa_args& a, float scale, cudaStream_t s
     if (a.B == 1) p.ms[0] = 0;
     if (a.Hq == 1) p.ms[1] = 0;
     if (a.Lq == 1) p.ms[2] = 0;
+    if (p.mask_kind == 1 && p.ms[1] == 0 && p.ms[2] == 0 && p.ms[3] == 1 && a.Lk > 1) {
+        if ((st = paras_b200_malloc_async(a.gpu, size_t(2 * a.B) * sizeof(int), s, &lens)) != PARAS_OK) return release(st);
+        int* li = static_cast<int*>(lens);
+        key_mask_scan_kernel<<<unsigned(a.B), 256, 0, s>>>(static_cast<const unsigned char*>(a.mask), p.ms[0], a.Lk, li, li + a.B);
+        if (cudaGetLastError() != cudaSuccess) return release(fail(PARAS_E_CUDA, "paras sdpa: mask scan launch failed"));
+        p.kv_len = li;
+        p.key_prefix = li + a.B;
+    }
     p.status = g->status_dev;
     if (rope) {
         if (a.D != 128 || p.mask_kind)

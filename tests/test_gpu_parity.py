@@ -549,6 +549,29 @@ def test_rmsnorm_backward_row_kernels_against_oracle(shape, dtype):
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("offset", [0, 1])
+@pytest.mark.parametrize("D", [128, 64])
+def test_key_padding_masks_on_the_tensor_core_kernel_act_as_sequence_lengths(D, offset, dtype):
+    # sequences of different lengths padded to one length, mask [B,1,1,Lk]: a scan finds each batch element's
+    # last valid key; its items visit no kv tile past it, and where the valid keys are a prefix the mask is
+    # not read again.  Holes stay masked per key; a batch element without any key gives NaN as the reference.
+    B, Hq, Hkv, Lq, Lk = 6, 4, 2, 300, 1024
+    q, k, v = _qkv(B, Hq, Hkv, Lq, Lk, D, dtype, seed=81)
+    full = torch.zeros(B, 1, 1, Lk + offset, dtype=torch.bool)
+    for b, n in enumerate((1024, 513, 17, 0, 700, 128)):
+        full[b, :, :, offset:offset + n] = True
+    full[4, :, :, offset + 100:offset + 400] = False          # a hole
+    mask = full[:, :, :, offset:]
+    want = O.sdpa(q, k, v, attn_mask=mask, enable_gqa=True)
+    got = abi.sdpa_fwd(q.to(DEV), k.to(DEV), v.to(DEV), mask=full.to(DEV)[:, :, :, offset:],
+                       flags=abi.SDPA_REF_SCALE | abi.SDPA_FORCE_TENSOR).cpu()
+    assert abi.sdpa_last_kernel() == "tcgen05"
+    assert torch.equal(torch.isnan(got), torch.isnan(want)) and torch.isnan(want[3]).all() and not torch.isnan(want[0]).any()
+    fin = ~torch.isnan(want)
+    assert (got[fin].double() - want[fin].double()).abs().max().item() <= 2e-2
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("offset", [0, 1])
 def test_decode_kernel_reads_no_keys_past_the_longest_valid_one(offset, dtype):
     # caches of different lengths padded to one length: the kernel finds each batch element's last valid key
     # from the [B,1,1,Lk] mask and shares only that range out among its CTAs; holes inside the range stay
