@@ -134,6 +134,11 @@ struct TcParams {
     // length (the tile on the boundary is cut like a ragged last tile) without reading the mask again.
     const int* kv_len;
     const int* key_prefix;
+    // A mask shared by every batch element and head ([Lq, Lk]) that turns out to be the causal mask written
+    // out (true / 0 where key <= query, false / -inf elsewhere): *mask_is_causal != 0, set by a scan kernel
+    // before the launch.  The MASK kernel then runs as the causal kernel does (no kv tile above the diagonal,
+    // the diagonal tile cut by position) and does not read the mask.
+    const int* mask_is_causal;
 };
 
 // One work item = one 256-row query block of one (batch, head).
@@ -147,10 +152,10 @@ struct Item {
     int lk;        // keys this item may see (MASK kernels with kv_len: the batch element's; else Lk)
 };
 
-__device__ __forceinline__ int kv_tiles_for(const TcParams& p, int start, int lk) {
+__device__ __forceinline__ int kv_tiles_for(const TcParams& p, int start, int lk, bool causal) {
     if (start >= p.Lq) return 0;
     int last = lk;
-    if (p.causal) last = min(last, min(p.Lq, start + BM));  // keys 0..row
+    if (causal) last = min(last, min(p.Lq, start + BM));  // keys 0..row
     return (last + BN - 1) / BN;
 }
 
@@ -176,7 +181,7 @@ __device__ __forceinline__ bool get_item(const TcParams& p, int seq, Item* it) {
 #pragma unroll
         for (int t = 0; t < 2; ++t) {
             it->start[t] = 0;              // every row of the item is a query position below 2^pack_shift
-            it->ntile[t] = kv_tiles_for(p, 0, p.Lk);
+            it->ntile[t] = kv_tiles_for(p, 0, p.Lk, p.causal != 0);
             if (SPLIT) it->ntile[t] = min(max(it->ntile[t] - it->kv0, 0), p.split_tiles);
         }
         it->n = it->ntile[0];
@@ -199,10 +204,11 @@ __device__ __forceinline__ bool get_item(const TcParams& p, int seq, Item* it) {
     it->hk = it->h / (p.Hq / p.Hkv);
     const bool dup = (seq & 1) && pair == hi;  // odd block count: the middle block has no partner
     if (MASK && p.kv_len) it->lk = __ldg(p.kv_len + it->b);
+    const bool causal = p.causal != 0 || (MASK && p.mask_is_causal && __ldg(p.mask_is_causal) != 0);
 #pragma unroll
     for (int t = 0; t < 2; ++t) {
         it->start[t] = qblk * (kTilesPerCta * BM) + t * BM;
-        it->ntile[t] = dup ? 0 : kv_tiles_for(p, it->start[t], MASK ? it->lk : p.Lk);
+        it->ntile[t] = dup ? 0 : kv_tiles_for(p, it->start[t], MASK ? it->lk : p.Lk, causal);
         if (SPLIT) it->ntile[t] = min(max(it->ntile[t] - it->kv0, 0), p.split_tiles);
     }
     it->n = max(it->ntile[0], it->ntile[1]);
@@ -423,7 +429,9 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             const int nt = it.ntile[t];
             if (nt == 0) continue;
             const int lk_item = MASK ? it.lk : p.Lk;
-            const bool mask_off = MASK && p.key_prefix && __ldg(p.key_prefix + it.b) != 0;   // the length says it all
+            const bool dyn_causal = MASK && p.mask_is_causal && __ldg(p.mask_is_causal) != 0;
+            const bool causal = p.causal != 0 || dyn_causal;
+            const bool mask_off = dyn_causal || (MASK && p.key_prefix && __ldg(p.key_prefix + it.b) != 0);   // position or length says it all
             // PACK: row r of the tile is query position r mod 2^pack_shift of head r >> pack_shift of the group
             const int row_q = PACK ? ((wq * 32 + lane) & ((1 << p.pack_shift) - 1)) : it.start[t] + wq * 32 + lane;
             const int head_q = PACK ? it.h + ((t * BM + wq * 32) >> p.pack_shift) : it.h;   // (a warp's 32 rows: one head)
@@ -712,9 +720,9 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 #pragma unroll
                     for (int c = 0; c < 4; ++c) tmem_ld_fence32(reinterpret_cast<uint32_t(&)[32]>(s[32 * c]));
                     const int col0 = SPLIT ? (it.kv0 + j) * BN : j * BN;
-                    const bool need_mask = (p.causal && col0 + BN - 1 > it.start[t]) || (col0 + BN > lk_item);
+                    const bool need_mask = (causal && col0 + BN - 1 > it.start[t]) || (col0 + BN > lk_item);
                     if (need_mask) {
-                        const int limit = (p.causal ? min(row_q, lk_item - 1) : lk_item - 1) - col0;
+                        const int limit = (causal ? min(row_q, lk_item - 1) : lk_item - 1) - col0;
 #pragma unroll
                         for (int i = 0; i < BN; ++i)
                             if (i > limit) s[i] = 0xff800000u;  // -inf
@@ -876,6 +884,28 @@ __global__ void __launch_bounds__(256) key_mask_scan_kernel(const unsigned char*
         kv_len[blockIdx.x] = s_last < 0 ? Lk : s_last + 1;
         key_prefix[blockIdx.x] = s_last >= 0 && s_count == s_last + 1;
     }
+}
+
+// Is a [Lq, Lk] mask the causal mask written out?  kind 1: bool, true exactly where key <= query; kinds 2, 3:
+// additive, 0 there and -inf elsewhere.  *flag is nonzero on entry; any element that does not fit clears it.
+__global__ void __launch_bounds__(256) causal_mask_check_kernel(const void* __restrict__ mask, int64_t row_stride, int Lq, int Lk,
+                                                               int kind, int bf16, int* __restrict__ flag) {
+    bool ok = true;
+    const int64_t total = int64_t(Lq) * Lk;
+    for (int64_t i = int64_t(blockIdx.x) * 256 + threadIdx.x; i < total && ok; i += int64_t(gridDim.x) * 256) {
+        const int r = int(i / Lk), c = int(i - int64_t(r) * Lk);
+        const bool seen = c <= r;
+        const int64_t off = int64_t(r) * row_stride + c;
+        if (kind == 1) {
+            ok = (static_cast<const unsigned char*>(mask)[off] != 0) == seen;
+        } else {
+            const float f = kind == 3 ? static_cast<const float*>(mask)[off]
+                                      : (bf16 ? from16<true>(static_cast<const uint16_t*>(mask)[off])
+                                              : from16<false>(static_cast<const uint16_t*>(mask)[off]));
+            ok = seen ? f == 0.f : f == -INFINITY;
+        }
+    }
+    if (!__syncthreads_and(ok) && threadIdx.x == 0) atomicAnd(flag, 0);
 }
 
 // ---- merge of the split-key partial results ------------------------------------------------
@@ -1084,6 +1114,17 @@ int sdpa_tc_launch(Gpu* g, const paras_sdpa_args& a, float scale, cudaStream_t s
         if (cudaGetLastError() != cudaSuccess) return release(fail(PARAS_E_CUDA, "paras sdpa: mask scan launch failed"));
         p.kv_len = li;
         p.key_prefix = li + a.B;
+    } else if (p.mask_kind && p.ms[0] == 0 && p.ms[1] == 0 && p.ms[3] == 1 && a.Lq > 1 && a.Lk > 1) {
+        // one [Lq, Lk] mask for every batch element and head: is it the causal mask written out?
+        if ((st = paras_b200_malloc_async(a.gpu, sizeof(int), s, &lens)) != PARAS_OK) return release(st);
+        int* flag = static_cast<int*>(lens);
+        if (cudaMemsetAsync(flag, 1, sizeof(int), s) != cudaSuccess) return release(fail(PARAS_E_CUDA, "paras sdpa: memset failed"));
+        const int64_t total = int64_t(a.Lq) * a.Lk;
+        const int sms_ = g->sm_count > 0 ? g->sm_count : 148;
+        const unsigned blocks = unsigned(std::min<int64_t>((total + 255) / 256, int64_t(sms_) * 8));
+        causal_mask_check_kernel<<<blocks, 256, 0, s>>>(a.mask, p.ms[2], a.Lq, a.Lk, p.mask_kind, a.dtype == PARAS_BF16 ? 1 : 0, flag);
+        if (cudaGetLastError() != cudaSuccess) return release(fail(PARAS_E_CUDA, "paras sdpa: mask check launch failed"));
+        p.mask_is_causal = flag;
     }
     p.status = g->status_dev;
     if (rope) {

@@ -548,6 +548,45 @@ def test_rmsnorm_backward_row_kernels_against_oracle(shape, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("kind", ["bool", "additive", "additive_f32", "bool_4d"])
+@pytest.mark.parametrize("shape", [(640, 640), (300, 456), (456, 300)])
+def test_a_causal_mask_written_out_runs_as_the_causal_kernel(shape, kind, dtype):
+    # attn_mask = the lower triangle as a tensor (bool, or 0 / -inf): a check kernel recognises it and the
+    # masked kernel then skips the tiles above the diagonal and never reads the mask; one entry off the
+    # pattern and the mask is applied as given.  Both against the oracle, and against is_causal=True.
+    Lq, Lk = shape
+    q, k, v = _qkv(2, 4, 2, Lq, Lk, 128, dtype, seed=91)
+    tri = torch.ones(Lq, Lk, dtype=torch.bool).tril()
+    def as_kind(t):
+        if kind == "bool":
+            return t
+        if kind == "bool_4d":
+            return t[None, None]
+        m = torch.zeros(Lq, Lk).masked_fill(~t, float("-inf"))
+        return m.to(dtype) if kind == "additive" else m
+    qd, kd, vd = q.to(DEV), k.to(DEV), v.to(DEV)
+    flags = abi.SDPA_REF_SCALE | abi.SDPA_FORCE_TENSOR
+    got = abi.sdpa_fwd(qd, kd, vd, mask=as_kind(tri).to(DEV), flags=flags)
+    assert abi.sdpa_last_kernel() == "tcgen05"
+    tol_check(got, O.sdpa(q, k, v, is_causal=True, enable_gqa=True), f"written-out causal {kind} {shape}")
+    assert torch.equal(got, abi.sdpa_fwd(qd, kd, vd, causal=True, flags=flags))
+    off = tri.clone()
+    off[Lq // 2, min(Lk - 1, Lq // 2 + 3)] = True        # one key above the diagonal is visible
+    off[Lq - 1, 0] = False                                # and one below it is not
+    got2 = abi.sdpa_fwd(qd, kd, vd, mask=as_kind(off).to(DEV), flags=flags)
+    if kind.startswith("bool"):
+        want2 = O.sdpa(q, k, v, attn_mask=off, enable_gqa=True)
+        tol_check(got2, want2, f"almost causal {kind} {shape}")
+    else:
+        sc = float(torch.tensor(1 / math.sqrt(128)).to(dtype))
+        s_ = (q.double() @ k.double().repeat_interleave(2, 1).transpose(-1, -2)) * sc
+        s_ = s_.masked_fill(~off, float("-inf"))
+        want2 = torch.softmax(s_, -1) @ v.double().repeat_interleave(2, 1)
+        assert (got2.cpu().double() - want2).abs().max().item() <= 2e-2
+    assert not torch.equal(got2, got)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("offset", [0, 1])
 @pytest.mark.parametrize("D", [128, 64])
 def test_key_padding_masks_on_the_tensor_core_kernel_act_as_sequence_lengths(D, offset, dtype):
