@@ -887,9 +887,12 @@ __global__ void __launch_bounds__(256) key_mask_scan_kernel(const unsigned char*
 }
 
 // Is a [Lq, Lk] mask the causal mask written out?  kind 1: bool, true exactly where key <= query; kinds 2, 3:
-// additive, 0 there and -inf elsewhere.  *flag is nonzero on entry; any element that does not fit clears it.
+// additive, 0 there and at most `masked_below` elsewhere (-inf, or the most negative finite value of the
+// dtype that some callers write instead: with a visible key at 0 in every row and the scale the launcher
+// checked, exp of such an entry is exactly 0, as for -inf).  *flag is nonzero on entry; any element that
+// does not fit clears it.
 __global__ void __launch_bounds__(256) causal_mask_check_kernel(const void* __restrict__ mask, int64_t row_stride, int Lq, int Lk,
-                                                               int kind, int bf16, int* __restrict__ flag) {
+                                                               int kind, int bf16, float masked_below, int* __restrict__ flag) {
     bool ok = true;
     const int64_t total = int64_t(Lq) * Lk;
     for (int64_t i = int64_t(blockIdx.x) * 256 + threadIdx.x; i < total && ok; i += int64_t(gridDim.x) * 256) {
@@ -902,7 +905,7 @@ __global__ void __launch_bounds__(256) causal_mask_check_kernel(const void* __re
             const float f = kind == 3 ? static_cast<const float*>(mask)[off]
                                       : (bf16 ? from16<true>(static_cast<const uint16_t*>(mask)[off])
                                               : from16<false>(static_cast<const uint16_t*>(mask)[off]));
-            ok = seen ? f == 0.f : f == -INFINITY;
+            ok = seen ? f == 0.f : f <= masked_below;
         }
     }
     if (!__syncthreads_and(ok) && threadIdx.x == 0) atomicAnd(flag, 0);
@@ -1122,7 +1125,10 @@ int sdpa_tc_launch(Gpu* g, const paras_sdpa_args& a, float scale, cudaStream_t s
         const int64_t total = int64_t(a.Lq) * a.Lk;
         const int sms_ = g->sm_count > 0 ? g->sm_count : 148;
         const unsigned blocks = unsigned(std::min<int64_t>((total + 255) / 256, int64_t(sms_) * 8));
-        causal_mask_check_kernel<<<blocks, 256, 0, s>>>(a.mask, p.ms[2], a.Lq, a.Lk, p.mask_kind, a.dtype == PARAS_BF16 ? 1 : 0, flag);
+        // -60000 (fp16's most negative values) times scale * log2(e) must be far below the -149 at which exp2 gives 0
+        const float masked_below = scale * 1.4426950408889634f * 60000.0f > 1000.0f ? -60000.0f : -INFINITY;
+        causal_mask_check_kernel<<<blocks, 256, 0, s>>>(a.mask, p.ms[2], a.Lq, a.Lk, p.mask_kind, a.dtype == PARAS_BF16 ? 1 : 0,
+                                                        masked_below, flag);
         if (cudaGetLastError() != cudaSuccess) return release(fail(PARAS_E_CUDA, "paras sdpa: mask check launch failed"));
         p.mask_is_causal = flag;
     }

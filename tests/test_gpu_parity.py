@@ -548,7 +548,7 @@ def test_rmsnorm_backward_row_kernels_against_oracle(shape, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
-@pytest.mark.parametrize("kind", ["bool", "additive", "additive_f32", "bool_4d"])
+@pytest.mark.parametrize("kind", ["bool", "additive", "additive_f32", "bool_4d", "additive_min"])
 @pytest.mark.parametrize("shape", [(640, 640), (300, 456), (456, 300)])
 def test_a_causal_mask_written_out_runs_as_the_causal_kernel(shape, kind, dtype):
     # attn_mask = the lower triangle as a tensor (bool, or 0 / -inf): a check kernel recognises it and the
@@ -562,6 +562,8 @@ def test_a_causal_mask_written_out_runs_as_the_causal_kernel(shape, kind, dtype)
             return t
         if kind == "bool_4d":
             return t[None, None]
+        if kind == "additive_min":     # the most negative finite value instead of -inf, as some callers write it
+            return torch.zeros(Lq, Lk, dtype=dtype).masked_fill(~t, torch.finfo(dtype).min)
         m = torch.zeros(Lq, Lk).masked_fill(~t, float("-inf"))
         return m.to(dtype) if kind == "additive" else m
     qd, kd, vd = q.to(DEV), k.to(DEV), v.to(DEV)
