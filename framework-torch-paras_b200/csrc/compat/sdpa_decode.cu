@@ -60,6 +60,7 @@ struct DecParams {
     int mask_kind;
     int64_t ms[4];
     float inv_scale;
+    float masked_below;   // an additive mask entry at or below this removes its key (-inf, or -60000 when the scale allows)
 };
 
 __device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t (&r)[4]) {
@@ -118,28 +119,56 @@ sdpa_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
         fence_proxy_async_smem();
     }
     __syncthreads();
-    // A bool mask that is one row of keys per batch element (caches of different lengths, padded to a common
-    // length): the keys after the last one that may be attended are never loaded.  The CTAs of a batch element
-    // find that key (a pass over the mask row, Lk bytes) and share the shorter range out among themselves.
-    if (MASK && p.mask_kind == 1 && p.ms[1] == 0 && p.ms[2] == 0 && p.ms[3] == 1) {
-        const unsigned char* row = static_cast<const unsigned char*>(p.mask) + int64_t(b) * p.ms[0];
-        int last = -1;
-        if ((reinterpret_cast<uintptr_t>(row) & 15u) == 0 && p.Lk % 16 == 0) {
+    // A mask that is one row of keys per batch element (caches of different lengths, padded to a common
+    // length), bool or additive with entries 0 / -inf: the keys after the last one that may be attended are
+    // never loaded.  The CTAs of a batch element find that key (a pass over the mask row) and share the shorter
+    // range out among themselves; when the valid keys form a prefix the mask is not read again at all.
+    // An additive row with any other value is a bias, not a padding mask, and is applied as given.
+    int last_key = p.Lk - 1;      // the last key that may be attended
+    bool mask_off = false;        // the key range says everything the mask says
+    if (MASK && p.ms[1] == 0 && p.ms[2] == 0 && p.ms[3] == 1) {
+        int* s_count = last_valid + 1;
+        int* s_other = last_valid + 2;
+        if (threadIdx.x == 0) { *s_count = 0; *s_other = 0; }
+        __syncthreads();
+        const int esz = p.mask_kind == 1 ? 1 : p.mask_kind == 2 ? 2 : 4;
+        const unsigned char* row = static_cast<const unsigned char*>(p.mask) + int64_t(b) * p.ms[0] * esz;
+        int last = -1, count = 0;
+        bool other = false;
+        auto take = [&](int k, bool valid, bool masked) {
+            if (valid) { last = k; ++count; }
+            else if (!masked) other = true;
+        };
+        if (p.mask_kind == 1 && (reinterpret_cast<uintptr_t>(row) & 15u) == 0 && p.Lk % 16 == 0) {
             for (int c = int(threadIdx.x); c < p.Lk / 16; c += kThreads) {
                 const uint4 w = __ldg(reinterpret_cast<const uint4*>(row) + c);
                 const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
                 for (int j = 0; j < 4; ++j)
-                    if (ww[j]) last = 16 * c + 4 * j + (31 - __clz(int(ww[j]))) / 8;   // c grows: the later word wins
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) take(16 * c + 4 * j + e, ((ww[j] >> (8 * e)) & 0xffu) != 0, true);
             }
         } else {
-            for (int k = int(threadIdx.x); k < p.Lk; k += kThreads)
-                if (row[k]) last = k;
+            for (int k = int(threadIdx.x); k < p.Lk; k += kThreads) {
+                if (p.mask_kind == 1) {
+                    take(k, row[k] != 0, true);
+                } else {
+                    const float f = p.mask_kind == 2 ? from16<BF16>(__ldg(reinterpret_cast<const uint16_t*>(row) + k))
+                                                     : __ldg(reinterpret_cast<const float*>(row) + k);
+                    take(k, f == 0.f, f <= p.masked_below);
+                }
+            }
         }
         if (last >= 0) atomicMax(last_valid, last);
+        if (count) atomicAdd(s_count, count);
+        if (other) atomicOr(s_other, 1);
         __syncthreads();
-        total_tiles = (*last_valid + 1 + TK - 1) / TK;
-        tiles_per_split = (total_tiles + int(gridDim.x) - 1) / int(gridDim.x);
+        if (*s_other == 0 && *last_valid >= 0) {
+            last_key = *last_valid;
+            mask_off = *s_count == last_key + 1;
+            total_tiles = (last_key + 1 + TK - 1) / TK;
+            tiles_per_split = (total_tiles + int(gridDim.x) - 1) / int(gridDim.x);
+        }
     }
     const int t0 = split * tiles_per_split;
     const int t1 = min(total_tiles, t0 + tiles_per_split);
@@ -197,7 +226,7 @@ sdpa_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
             const int r = r0 + 8 * half;
-            lim[half] = p.Lk - 1;
+            lim[half] = last_key;
             if (p.causal && r < p.rows) lim[half] = min(lim[half], r / p.group);  // top-left aligned
         }
         int64_t mrow[2] = {0, 0};   // element offset of each row's mask entries for key 0
@@ -219,14 +248,14 @@ sdpa_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
             const unsigned char* mp = static_cast<const unsigned char*>(p.mask) + mrow[0] + kb;
             return uint32_t(__ldg(reinterpret_cast<const uint16_t*>(mp))) | (uint32_t(__ldg(reinterpret_cast<const uint16_t*>(mp + 8))) << 16);
         };
-        uint32_t mnext = mfast ? mask_pair(0) : 0u;
+        uint32_t mnext = mfast && !mask_off ? mask_pair(0) : 0u;
         bool ok = true;
         for (int i = 0; i < ntiles; ++i) {
             const int s = i % kStages;
             const int krow0 = warp * 16;  // this warp's 16 keys inside the tile
             const int key_base = (t0 + i) * TK + krow0 + cpair;
             const uint32_t mcur = mnext;
-            if (mfast) mnext = mask_pair(i + 1);
+            if (mfast && !mask_off) mnext = mask_pair(i + 1);
             ok = mbar_wait(full(s), (i / kStages) & 1, abort_flag);
             if (!ok) break;
             const uint32_t kbase = smem_base + s * kStageBytes;
@@ -251,7 +280,12 @@ sdpa_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
             // what the mask adds to this thread's four keys of each of its two rows (one set of loads when the
             // rows share a mask row, as with a key-padding mask)
             float madd[2][2][2];
-            if (MASK && mfast && key_base + 9 < p.Lk) {
+            if (MASK && mask_off) {
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) madd[0][nt][e] = madd[1][nt][e] = 0.f;
+            } else if (MASK && mfast && key_base + 9 < p.Lk) {
 #pragma unroll
                 for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
@@ -506,6 +540,8 @@ int sdpa_decode_launch(Gpu* g, const paras_sdpa_args& a, float scale, const Spli
     if (a.Lq == 1) p.ms[2] = 0;
     if (a.Lk == 1) p.ms[3] = 1;
     p.inv_scale = 1.0f / scale;
+    // -60000 (fp16's most negative values) times scale * log2(e) must be far below the -149 at which exp2 gives 0
+    p.masked_below = scale * 1.4426950408889634f * 60000.0f > 1000.0f ? -60000.0f : -INFINITY;
     dim3 grid(ws.splits, a.Hkv, a.B);
     auto go = [&](auto kernel) -> int {
         PB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLaunch));

@@ -853,36 +853,53 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 }
 
 // ---- key-padding masks: the length each batch element's row stands for ---------------------------
-// One CTA per batch element over its Lk mask bytes: kv_len[b] = 1 + the last nonzero byte's index (Lk if
-// there is none), key_prefix[b] = 1 when every byte before it is nonzero too.
-__global__ void __launch_bounds__(256) key_mask_scan_kernel(const unsigned char* __restrict__ mask, int64_t bstride, int Lk,
-                                                            int* __restrict__ kv_len, int* __restrict__ key_prefix) {
-    __shared__ int s_last, s_count;
-    const unsigned char* row = mask + int64_t(blockIdx.x) * bstride;
-    if (threadIdx.x == 0) { s_last = -1; s_count = 0; }
+// One CTA per batch element over its Lk mask entries (bool: nonzero = valid; additive: 0 = valid, at most
+// `masked_below` = removed): kv_len[b] = 1 + the last valid key's index, key_prefix[b] = 1 when every key
+// before it is valid too.  A row without a valid key, or an additive row with any other value (a bias, not a
+// padding mask), gets kv_len = Lk and key_prefix = 0: the mask is then applied as given.
+__global__ void __launch_bounds__(256) key_mask_scan_kernel(const void* __restrict__ mask, int64_t bstride, int Lk, int kind, int bf16,
+                                                            float masked_below, int* __restrict__ kv_len,
+                                                            int* __restrict__ key_prefix) {
+    __shared__ int s_last, s_count, s_other;
+    if (threadIdx.x == 0) { s_last = -1; s_count = 0; s_other = 0; }
     __syncthreads();
     int last = -1, count = 0;
-    if ((reinterpret_cast<uintptr_t>(row) & 15u) == 0 && Lk % 16 == 0) {
-        for (int c = int(threadIdx.x); c < Lk / 16; c += 256) {
-            const uint4 w = __ldg(reinterpret_cast<const uint4*>(row) + c);
-            const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+    bool other = false;
+    if (kind == 1) {
+        const unsigned char* row = static_cast<const unsigned char*>(mask) + int64_t(blockIdx.x) * bstride;
+        if ((reinterpret_cast<uintptr_t>(row) & 15u) == 0 && Lk % 16 == 0) {
+            for (int c = int(threadIdx.x); c < Lk / 16; c += 256) {
+                const uint4 w = __ldg(reinterpret_cast<const uint4*>(row) + c);
+                const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
+                for (int j = 0; j < 4; ++j) {
 #pragma unroll
-                for (int e = 0; e < 4; ++e)
-                    if ((ww[j] >> (8 * e)) & 0xffu) { last = 16 * c + 4 * j + e; ++count; }
+                    for (int e = 0; e < 4; ++e)
+                        if ((ww[j] >> (8 * e)) & 0xffu) { last = 16 * c + 4 * j + e; ++count; }
+                }
             }
+        } else {
+            for (int k = int(threadIdx.x); k < Lk; k += 256)
+                if (row[k]) { last = k; ++count; }
         }
     } else {
-        for (int k = int(threadIdx.x); k < Lk; k += 256)
-            if (row[k]) { last = k; ++count; }
+        for (int k = int(threadIdx.x); k < Lk; k += 256) {
+            const int64_t off = int64_t(blockIdx.x) * bstride + k;
+            const float f = kind == 3 ? __ldg(static_cast<const float*>(mask) + off)
+                                      : (bf16 ? from16<true>(__ldg(static_cast<const uint16_t*>(mask) + off))
+                                              : from16<false>(__ldg(static_cast<const uint16_t*>(mask) + off)));
+            if (f == 0.f) { last = k; ++count; }
+            else if (!(f <= masked_below)) other = true;
+        }
     }
     if (last >= 0) atomicMax(&s_last, last);
     if (count) atomicAdd(&s_count, count);
+    if (other) atomicOr(&s_other, 1);
     __syncthreads();
     if (threadIdx.x == 0) {
-        kv_len[blockIdx.x] = s_last < 0 ? Lk : s_last + 1;
-        key_prefix[blockIdx.x] = s_last >= 0 && s_count == s_last + 1;
+        const bool usable = s_last >= 0 && s_other == 0;
+        kv_len[blockIdx.x] = usable ? s_last + 1 : Lk;
+        key_prefix[blockIdx.x] = usable && s_count == s_last + 1;
     }
 }
 
@@ -1110,10 +1127,13 @@ int sdpa_tc_launch(Gpu* g, const paras_sdpa_args& a, float scale, cudaStream_t s
     if (a.B == 1) p.ms[0] = 0;
     if (a.Hq == 1) p.ms[1] = 0;
     if (a.Lq == 1) p.ms[2] = 0;
-    if (p.mask_kind == 1 && p.ms[1] == 0 && p.ms[2] == 0 && p.ms[3] == 1 && a.Lk > 1) {
+    // -60000 (fp16's most negative values) times scale * log2(e) must be far below the -149 at which exp2 gives 0
+    const float masked_below = scale * 1.4426950408889634f * 60000.0f > 1000.0f ? -60000.0f : -INFINITY;
+    if (p.mask_kind && p.ms[1] == 0 && p.ms[2] == 0 && p.ms[3] == 1 && a.Lk > 1) {
         if ((st = paras_b200_malloc_async(a.gpu, size_t(2 * a.B) * sizeof(int), s, &lens)) != PARAS_OK) return release(st);
         int* li = static_cast<int*>(lens);
-        key_mask_scan_kernel<<<unsigned(a.B), 256, 0, s>>>(static_cast<const unsigned char*>(a.mask), p.ms[0], a.Lk, li, li + a.B);
+        key_mask_scan_kernel<<<unsigned(a.B), 256, 0, s>>>(a.mask, p.ms[0], a.Lk, p.mask_kind, a.dtype == PARAS_BF16 ? 1 : 0,
+                                                          masked_below, li, li + a.B);
         if (cudaGetLastError() != cudaSuccess) return release(fail(PARAS_E_CUDA, "paras sdpa: mask scan launch failed"));
         p.kv_len = li;
         p.key_prefix = li + a.B;
@@ -1125,8 +1145,6 @@ int sdpa_tc_launch(Gpu* g, const paras_sdpa_args& a, float scale, cudaStream_t s
         const int64_t total = int64_t(a.Lq) * a.Lk;
         const int sms_ = g->sm_count > 0 ? g->sm_count : 148;
         const unsigned blocks = unsigned(std::min<int64_t>((total + 255) / 256, int64_t(sms_) * 8));
-        // -60000 (fp16's most negative values) times scale * log2(e) must be far below the -149 at which exp2 gives 0
-        const float masked_below = scale * 1.4426950408889634f * 60000.0f > 1000.0f ? -60000.0f : -INFINITY;
         causal_mask_check_kernel<<<blocks, 256, 0, s>>>(a.mask, p.ms[2], a.Lq, a.Lk, p.mask_kind, a.dtype == PARAS_BF16 ? 1 : 0,
                                                         masked_below, flag);
         if (cudaGetLastError() != cudaSuccess) return release(fail(PARAS_E_CUDA, "paras sdpa: mask check launch failed"));

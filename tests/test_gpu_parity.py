@@ -589,47 +589,85 @@ def test_a_causal_mask_written_out_runs_as_the_causal_kernel(shape, kind, dtype)
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
-@pytest.mark.parametrize("offset", [0, 1])
+@pytest.mark.parametrize("kind", ["bool", "bool_odd_address", "additive", "additive_f32_min", "bias"])
 @pytest.mark.parametrize("D", [128, 64])
-def test_key_padding_masks_on_the_tensor_core_kernel_act_as_sequence_lengths(D, offset, dtype):
-    # sequences of different lengths padded to one length, mask [B,1,1,Lk]: a scan finds each batch element's
-    # last valid key; its items visit no kv tile past it, and where the valid keys are a prefix the mask is
-    # not read again.  Holes stay masked per key; a batch element without any key gives NaN as the reference.
+def test_key_padding_masks_on_the_tensor_core_kernel_act_as_sequence_lengths(D, kind, dtype):
+    # sequences of different lengths padded to one length, mask [B,1,1,Lk] (bool, additive 0 / -inf, or 0 / the
+    # most negative float): a scan finds each batch element's last valid key; its items visit no kv tile past
+    # it, and where the valid keys are a prefix the mask is not read again.  Holes stay masked per key; a batch
+    # element without any key gives NaN as the reference; an additive row of other values is a bias.
     B, Hq, Hkv, Lq, Lk = 6, 4, 2, 300, 1024
     q, k, v = _qkv(B, Hq, Hkv, Lq, Lk, D, dtype, seed=81)
+    offset = 1 if kind == "bool_odd_address" else 0
     full = torch.zeros(B, 1, 1, Lk + offset, dtype=torch.bool)
     for b, n in enumerate((1024, 513, 17, 0, 700, 128)):
         full[b, :, :, offset:offset + n] = True
     full[4, :, :, offset + 100:offset + 400] = False          # a hole
-    mask = full[:, :, :, offset:]
-    want = O.sdpa(q, k, v, attn_mask=mask, enable_gqa=True)
-    got = abi.sdpa_fwd(q.to(DEV), k.to(DEV), v.to(DEV), mask=full.to(DEV)[:, :, :, offset:],
+    vis = full[:, :, :, offset:]
+    if kind.startswith("bool"):
+        given = full
+    elif kind == "additive":
+        given = torch.zeros(full.shape).masked_fill(~full, float("-inf")).to(dtype)
+    elif kind == "additive_f32_min":
+        given = torch.zeros(full.shape).masked_fill(~full, torch.finfo(torch.float32).min)
+    else:
+        given = (torch.randn(full.shape, generator=torch.Generator().manual_seed(82)) * 2).to(dtype)
+    sc = float(torch.tensor(1 / math.sqrt(D)).to(dtype))
+    s_ = (q.double() @ k.double().repeat_interleave(Hq // Hkv, 1).transpose(-1, -2)) * sc
+    s_ = s_ + given[:, :, :, offset:].double() if kind == "bias" else s_.masked_fill(~vis, float("-inf"))
+    want = torch.softmax(s_, -1) @ v.double().repeat_interleave(Hq // Hkv, 1)
+    got = abi.sdpa_fwd(q.to(DEV), k.to(DEV), v.to(DEV), mask=given.to(DEV)[:, :, :, offset:],
                        flags=abi.SDPA_REF_SCALE | abi.SDPA_FORCE_TENSOR).cpu()
     assert abi.sdpa_last_kernel() == "tcgen05"
-    assert torch.equal(torch.isnan(got), torch.isnan(want)) and torch.isnan(want[3]).all() and not torch.isnan(want[0]).any()
-    fin = ~torch.isnan(want)
-    assert (got[fin].double() - want[fin].double()).abs().max().item() <= 2e-2
+    if kind.startswith("bool"):
+        ref = O.sdpa(q, k, v, attn_mask=vis, enable_gqa=True)
+        assert torch.equal(torch.isnan(got), torch.isnan(ref))
+    if kind in ("bool", "bool_odd_address", "additive"):
+        assert torch.isnan(got[3]).all()
+    fin = ~torch.isnan(want) & ~torch.isnan(got.double())
+    assert fin[[0, 1, 2, 4, 5]].all()
+    assert (got.double()[fin] - want[fin]).abs().max().item() <= 2e-2
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("offset", [0, 1])
-def test_decode_kernel_reads_no_keys_past_the_longest_valid_one(offset, dtype):
+@pytest.mark.parametrize("kind", ["bool", "additive", "additive_f32_min", "bias"])
+def test_decode_kernel_reads_no_keys_past_the_longest_valid_one(kind, offset, dtype):
     # caches of different lengths padded to one length: the kernel finds each batch element's last valid key
-    # from the [B,1,1,Lk] mask and shares only that range out among its CTAs; holes inside the range stay
-    # masked per key, a batch element without any key gives NaN as in the reference
+    # from the [B,1,1,Lk] mask (bool, or additive 0 / -inf, or 0 / the dtype's most negative value) and shares
+    # only that range out among its CTAs; holes inside the range stay masked per key, a batch element without
+    # any key gives NaN as in the reference; an additive row with other values ("bias") is applied as given
     B, Hq, Hkv, Lq, Lk = 5, 8, 2, 1, 4096
     q, k, v = _qkv(B, Hq, Hkv, Lq, Lk, 128, dtype, seed=71)
-    full = torch.zeros(B, 1, 1, Lk + offset, dtype=torch.bool)
+    full = torch.zeros(B, 1, 1, Lk + 2 * offset, dtype=torch.bool)
     for b, n in enumerate((4096, 2049, 17, 0, 1000)):
-        full[b, :, :, offset:offset + n] = True
-    full[4, :, :, offset + 100:offset + 900] = False          # a hole
-    mask = full[:, :, :, offset:]                              # offset 1: the rows start on an odd address
-    want = O.sdpa(q, k, v, attn_mask=mask, enable_gqa=True)
-    got = abi.sdpa_fwd(q.to(DEV), k.to(DEV), v.to(DEV), mask=full.to(DEV)[:, :, :, offset:], flags=abi.SDPA_REF_SCALE).cpu()
+        full[b, :, :, 2 * offset:2 * offset + n] = True
+    full[4, :, :, 2 * offset + 100:2 * offset + 900] = False          # a hole
+    vis = full[:, :, :, 2 * offset:]
+    if kind == "bool":
+        given, sl = full, slice(2 * offset, None)     # offset 1: the rows start two bytes off a 16-byte boundary
+    elif kind == "additive":
+        given, sl = torch.zeros(full.shape).masked_fill(~full, float("-inf")).to(dtype), slice(2 * offset, None)
+    elif kind == "additive_f32_min":
+        given, sl = torch.zeros(full.shape).masked_fill(~full, torch.finfo(torch.float32).min), slice(2 * offset, None)
+    else:
+        g = torch.Generator().manual_seed(72)
+        given, sl = (torch.randn(full.shape, generator=g) * 2).to(dtype), slice(2 * offset, None)
+    mask = given[:, :, :, sl]
+    sc = float(torch.tensor(1 / math.sqrt(128)).to(dtype))
+    s_ = (q.double() @ k.double().repeat_interleave(Hq // Hkv, 1).transpose(-1, -2)) * sc
+    s_ = s_ + mask.double() if kind == "bias" else s_.masked_fill(~vis, float("-inf"))
+    want = torch.softmax(s_, -1) @ v.double().repeat_interleave(Hq // Hkv, 1)
+    got = abi.sdpa_fwd(q.to(DEV), k.to(DEV), v.to(DEV), mask=given.to(DEV)[:, :, :, sl], flags=abi.SDPA_REF_SCALE).cpu()
     assert abi.sdpa_last_kernel() == "decode_mma"
-    assert torch.equal(torch.isnan(got), torch.isnan(want)) and torch.isnan(want[3]).all() and not torch.isnan(want[0]).any()
-    fin = ~torch.isnan(want)
-    assert (got[fin].double() - want[fin].double()).abs().max().item() <= 2e-2
+    if kind == "bool":
+        ref = O.sdpa(q, k, v, attn_mask=mask, enable_gqa=True)
+        assert torch.equal(torch.isnan(got), torch.isnan(ref))
+    if kind in ("bool", "additive"):
+        assert torch.isnan(got[3]).all()                 # no key at all: NaN, as in the reference
+    fin = ~torch.isnan(want) & ~torch.isnan(got.double())
+    assert fin[[0, 1, 2, 4]].all()
+    assert (got.double()[fin] - want[fin]).abs().max().item() <= 2e-2
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
