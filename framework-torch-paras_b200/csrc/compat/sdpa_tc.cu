@@ -139,6 +139,7 @@ struct TcParams {
     // before the launch.  The MASK kernel then runs as the causal kernel does (no kv tile above the diagonal,
     // the diagonal tile cut by position) and does not read the mask.
     const int* mask_is_causal;
+    int kv_len_if_causal;   // kv_len holds what the causal check found per batch element: valid only if *mask_is_causal
 };
 
 // One work item = one 256-row query block of one (batch, head).
@@ -203,8 +204,8 @@ __device__ __forceinline__ bool get_item(const TcParams& p, int seq, Item* it) {
     it->h = hb - it->b * p.Hq;
     it->hk = it->h / (p.Hq / p.Hkv);
     const bool dup = (seq & 1) && pair == hi;  // odd block count: the middle block has no partner
-    if (MASK && p.kv_len) it->lk = __ldg(p.kv_len + it->b);
     const bool causal = p.causal != 0 || (MASK && p.mask_is_causal && __ldg(p.mask_is_causal) != 0);
+    if (MASK && p.kv_len && (!p.kv_len_if_causal || causal)) it->lk = __ldg(p.kv_len + it->b);
 #pragma unroll
     for (int t = 0; t < 2; ++t) {
         it->start[t] = qblk * (kTilesPerCta * BM) + t * BM;
@@ -903,26 +904,77 @@ __global__ void __launch_bounds__(256) key_mask_scan_kernel(const void* __restri
     }
 }
 
-// Is a [Lq, Lk] mask the causal mask written out?  kind 1: bool, true exactly where key <= query; kinds 2, 3:
-// additive, 0 there and at most `masked_below` elsewhere (-inf, or the most negative finite value of the
-// dtype that some callers write instead: with a visible key at 0 in every row and the scale the launcher
-// checked, exp of such an entry is exactly 0, as for -inf).  *flag is nonzero on entry; any element that
-// does not fit clears it.
-__global__ void __launch_bounds__(256) causal_mask_check_kernel(const void* __restrict__ mask, int64_t row_stride, int Lq, int Lk,
-                                                               int kind, int bf16, float masked_below, int* __restrict__ flag) {
+// Is a mask the causal mask written out?  Entry (i, j) of batch element b must be visible exactly when
+// j <= i and j < len_b.  kind 1: bool, nonzero = visible; kinds 2, 3: additive, 0 = visible, at most
+// `masked_below` = removed (-inf, or the most negative finite value of the dtype that some callers write
+// instead: with key 0 visible in every row and the scale the launcher checked, exp of such an entry is exactly 0,
+// as for -inf); anything else is a bias and fails the check.
+//   kv_len == nullptr: one [Lq, Lk] mask for all batch elements, len = Lk (gridDim.y = 1).
+//   else: a [B, 1, Lq, Lk] mask over sequences padded on the right; every CTA of batch element b (blockIdx.y)
+//   takes len_b from the mask's last row, whose visible entries must be a prefix, and kv_len[b] = len_b.
+// *flag is nonzero on entry; any mismatch clears it.  A thread checks 16 consecutive entries of a row at a time
+// (16-byte loads when the rows allow).
+__global__ void __launch_bounds__(256) causal_check_kernel(const void* __restrict__ mask, int64_t batch_stride, int64_t row_stride,
+                                                          int Lq, int Lk, int kind, int bf16, float masked_below,
+                                                          int* __restrict__ kv_len, int* __restrict__ flag) {
+    __shared__ int s_last, s_count;
+    const int b = blockIdx.y;
+    const int esz = kind == 1 ? 1 : kind == 2 ? 2 : 4;
+    const unsigned char* base = static_cast<const unsigned char*>(mask) + int64_t(b) * batch_stride * esz;
     bool ok = true;
-    const int64_t total = int64_t(Lq) * Lk;
+    // visible / removed / neither for the entry at element offset `off` of this batch element
+    auto visible = [&](int64_t off) -> bool {
+        if (kind == 1) return base[off] != 0;
+        const float f = kind == 3 ? reinterpret_cast<const float*>(base)[off]
+                                  : (bf16 ? from16<true>(reinterpret_cast<const uint16_t*>(base)[off])
+                                          : from16<false>(reinterpret_cast<const uint16_t*>(base)[off]));
+        if (f == 0.f) return true;
+        if (!(f <= masked_below)) ok = false;
+        return false;
+    };
+    int len = Lk;
+    if (kv_len) {
+        if (threadIdx.x == 0) { s_last = -1; s_count = 0; }
+        __syncthreads();
+        int last = -1, count = 0;
+        for (int j = int(threadIdx.x); j < Lk; j += 256)
+            if (visible(int64_t(Lq - 1) * row_stride + j)) { last = j; ++count; }
+        if (last >= 0) atomicMax(&s_last, last);
+        if (count) atomicAdd(&s_count, count);
+        __syncthreads();
+        len = s_last + 1;
+        if (len < 1 || s_count != len) ok = false;
+        if (blockIdx.x == 0 && threadIdx.x == 0) kv_len[b] = len < 1 ? Lk : len;
+    }
+    const bool vec = (reinterpret_cast<uintptr_t>(base) & 15u) == 0 && (row_stride * esz) % 16 == 0 && Lk % 16 == 0;
+    const int spans = (Lk + 15) / 16;
+    const int64_t total = int64_t(Lq) * spans;
     for (int64_t i = int64_t(blockIdx.x) * 256 + threadIdx.x; i < total && ok; i += int64_t(gridDim.x) * 256) {
-        const int r = int(i / Lk), c = int(i - int64_t(r) * Lk);
-        const bool seen = c <= r;
-        const int64_t off = int64_t(r) * row_stride + c;
-        if (kind == 1) {
-            ok = (static_cast<const unsigned char*>(mask)[off] != 0) == seen;
+        const int r = int(i / spans), c0 = int(i - int64_t(r) * spans) * 16;
+        const int n = max(0, min(16, min(r + 1, len) - c0));   // the first n entries of the span are visible
+        const int64_t off = int64_t(r) * row_stride + c0;
+        if (vec && kind == 1) {
+            const uint4 w = __ldg(reinterpret_cast<const uint4*>(base + off));
+            const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+            for (int e = 0; e < 16; ++e) ok = ok && ((((ww[e >> 2] >> (8 * (e & 3))) & 0xffu) != 0) == (e < n));
+        } else if (vec && kind == 2) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const uint4 w = __ldg(reinterpret_cast<const uint4*>(base + (off + 8 * h) * 2));
+                const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    const uint16_t bits = uint16_t(ww[e >> 1] >> (16 * (e & 1)));
+                    const float f = bf16 ? from16<true>(bits) : from16<false>(bits);
+                    ok = ok && (8 * h + e < n ? f == 0.f : f <= masked_below);
+                }
+            }
         } else {
-            const float f = kind == 3 ? static_cast<const float*>(mask)[off]
-                                      : (bf16 ? from16<true>(static_cast<const uint16_t*>(mask)[off])
-                                              : from16<false>(static_cast<const uint16_t*>(mask)[off]));
-            ok = seen ? f == 0.f : f <= masked_below;
+            for (int e = 0; e < 16 && c0 + e < Lk; ++e) {
+                const bool v = visible(off + e);
+                ok = ok && v == (e < n);
+            }
         }
     }
     if (!__syncthreads_and(ok) && threadIdx.x == 0) atomicAnd(flag, 0);
@@ -1142,13 +1194,27 @@ int sdpa_tc_launch(Gpu* g, const paras_sdpa_args& a, float scale, cudaStream_t s
         if ((st = paras_b200_malloc_async(a.gpu, sizeof(int), s, &lens)) != PARAS_OK) return release(st);
         int* flag = static_cast<int*>(lens);
         if (cudaMemsetAsync(flag, 1, sizeof(int), s) != cudaSuccess) return release(fail(PARAS_E_CUDA, "paras sdpa: memset failed"));
-        const int64_t total = int64_t(a.Lq) * a.Lk;
+        const int64_t spans = int64_t(a.Lq) * ((a.Lk + 15) / 16);
         const int sms_ = g->sm_count > 0 ? g->sm_count : 148;
-        const unsigned blocks = unsigned(std::min<int64_t>((total + 255) / 256, int64_t(sms_) * 8));
-        causal_mask_check_kernel<<<blocks, 256, 0, s>>>(a.mask, p.ms[2], a.Lq, a.Lk, p.mask_kind, a.dtype == PARAS_BF16 ? 1 : 0,
-                                                        masked_below, flag);
+        const unsigned blocks = unsigned(std::min<int64_t>((spans + 255) / 256, int64_t(sms_) * 8));
+        causal_check_kernel<<<blocks, 256, 0, s>>>(a.mask, 0, p.ms[2], a.Lq, a.Lk, p.mask_kind, a.dtype == PARAS_BF16 ? 1 : 0,
+                                                   masked_below, nullptr, flag);
         if (cudaGetLastError() != cudaSuccess) return release(fail(PARAS_E_CUDA, "paras sdpa: mask check launch failed"));
         p.mask_is_causal = flag;
+    } else if (p.mask_kind && p.ms[0] != 0 && p.ms[1] == 0 && p.ms[2] != 0 && p.ms[3] == 1 && a.Lq > 1 && a.Lk > 1) {
+        // one [Lq, Lk] mask per batch element, shared by its heads: causal over right-padded sequences?
+        if ((st = paras_b200_malloc_async(a.gpu, size_t(a.B + 1) * sizeof(int), s, &lens)) != PARAS_OK) return release(st);
+        int* li = static_cast<int*>(lens);
+        if (cudaMemsetAsync(li + a.B, 1, sizeof(int), s) != cudaSuccess) return release(fail(PARAS_E_CUDA, "paras sdpa: memset failed"));
+        const int64_t spans = int64_t(a.Lq) * ((a.Lk + 15) / 16);
+        const int sms_ = g->sm_count > 0 ? g->sm_count : 148;
+        const unsigned chunks = unsigned(std::max<int64_t>(1, std::min<int64_t>((spans + 255) / 256, int64_t(sms_) * 8 / a.B)));
+        causal_check_kernel<<<dim3(chunks, unsigned(a.B)), 256, 0, s>>>(a.mask, p.ms[0], p.ms[2], a.Lq, a.Lk, p.mask_kind,
+                                                                      a.dtype == PARAS_BF16 ? 1 : 0, masked_below, li, li + a.B);
+        if (cudaGetLastError() != cudaSuccess) return release(fail(PARAS_E_CUDA, "paras sdpa: mask check launch failed"));
+        p.kv_len = li;
+        p.kv_len_if_causal = 1;
+        p.mask_is_causal = li + a.B;
     }
     p.status = g->status_dev;
     if (rope) {

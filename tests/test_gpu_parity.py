@@ -589,6 +589,45 @@ def test_a_causal_mask_written_out_runs_as_the_causal_kernel(shape, kind, dtype)
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("kind", ["bool", "additive_min", "additive_f32", "left_padded", "one_off"])
+@pytest.mark.parametrize("shape", [(640, 640), (300, 456)])
+def test_causal_masks_over_right_padded_sequences_run_as_causal_with_lengths(shape, kind, dtype):
+    # [B, 1, Lq, Lk] masks built as (key <= query) & (key < len_b): what callers pass for a padded batch when
+    # they cannot use is_causal.  A check kernel finds len_b and verifies every entry; the masked kernel then
+    # skips the tiles above the diagonal and past len_b and never reads the mask.  Left padding or one entry
+    # off the pattern and the mask is applied as given.
+    Lq, Lk = shape
+    B, Hq, Hkv, D = 4, 4, 2, 128
+    q, k, v = _qkv(B, Hq, Hkv, Lq, Lk, D, dtype, seed=95)
+    lens = (min(Lq, Lk), 300, 129, 1)
+    tri = torch.ones(Lq, Lk, dtype=torch.bool).tril()
+    vis = torch.stack([tri & (torch.arange(Lk)[None, :] < n) for n in lens])[:, None]        # [B,1,Lq,Lk]
+    if kind == "left_padded":
+        vis = torch.stack([tri & (torch.arange(Lk)[None, :] >= Lk // 4) for _ in lens])[:, None]
+        vis[..., 0] |= ~vis.any(-1)             # no empty rows
+    if kind == "one_off":
+        vis = vis.clone()
+        vis[1, 0, Lq // 2, 3] = False
+    if kind in ("bool", "left_padded", "one_off"):
+        given = vis
+    elif kind == "additive_min":
+        given = torch.zeros(vis.shape, dtype=dtype).masked_fill(~vis, torch.finfo(dtype).min)
+    else:
+        given = torch.zeros(vis.shape).masked_fill(~vis, float("-inf"))
+    sc = float(torch.tensor(1 / math.sqrt(D)).to(dtype))
+    s_ = (q.double() @ k.double().repeat_interleave(Hq // Hkv, 1).transpose(-1, -2)) * sc
+    want = torch.softmax(s_.masked_fill(~vis, float("-inf")), -1) @ v.double().repeat_interleave(Hq // Hkv, 1)
+    got = abi.sdpa_fwd(q.to(DEV), k.to(DEV), v.to(DEV), mask=given.to(DEV), flags=abi.SDPA_REF_SCALE | abi.SDPA_FORCE_TENSOR).cpu()
+    assert abi.sdpa_last_kernel() == "tcgen05"
+    assert not torch.isnan(got).any()
+    assert (got.double() - want).abs().max().item() <= 2e-2
+    if kind in ("bool", "additive_min", "additive_f32"):
+        # batch element 0 has no padding: its rows equal is_causal=True bit for bit
+        ref0 = abi.sdpa_fwd(q[:1].to(DEV), k[:1].to(DEV), v[:1].to(DEV), causal=True, flags=abi.SDPA_REF_SCALE | abi.SDPA_FORCE_TENSOR).cpu()
+        assert torch.equal(got[:1], ref0)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("kind", ["bool", "bool_odd_address", "additive", "additive_f32_min", "bias"])
 @pytest.mark.parametrize("D", [128, 64])
 def test_key_padding_masks_on_the_tensor_core_kernel_act_as_sequence_lengths(D, kind, dtype):
