@@ -112,6 +112,18 @@ int paras_b200_sdpa_workspace_bytes(const paras_sdpa_args* a, size_t* bytes) {
     return PARAS_OK;
 }
 
+int paras_b200_sdpa_mask_is_causal(int gpu, const void* mask, int mask_kind, int dtype, int64_t row_stride, int32_t Lq,
+                                   int32_t Lk, double scale, void* stream, int* result) {
+    if (!result) return fail(PARAS_E_INVALID, "paras sdpa: null output");
+    *result = 0;
+    if (dtype != PARAS_F32 && dtype != PARAS_BF16 && dtype != PARAS_F16)
+        return fail(PARAS_E_UNSUPPORTED, "paras sdpa: unsupported dtype %d", dtype);
+    int st;
+    Gpu* g = pb::use_gpu(gpu, &st);
+    if (!g) return st;
+    return pb::sdpa_mask_is_causal(g, gpu, mask, mask_kind, dtype, row_stride, Lq, Lk, float(scale), pb::pick_stream(g, stream), result);
+}
+
 int paras_b200_sdpa_fwd(const paras_sdpa_args* a) {
     pb::NvtxRange range("paras_b200_sdpa_fwd");
     int st = pb::validate(a);

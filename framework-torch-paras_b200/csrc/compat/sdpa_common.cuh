@@ -59,6 +59,8 @@ bool sdpa_tc_supported(const Gpu* g, const paras_sdpa_args& a, const char** why)
 // "tcgen05_packed" (the heads of a GQA group in one item), "tcgen05_packed_split", "tcgen05_rope"
 int sdpa_tc_launch(Gpu* g, const paras_sdpa_args& a, float scale, cudaStream_t s, const RopeTables* rope = nullptr,
                    const char** variant = nullptr);
+int sdpa_mask_is_causal(Gpu* g, int gpu, const void* mask, int mask_kind, int dtype, int64_t row_stride, int Lq, int Lk,
+                        float scale, cudaStream_t s, int* result);
 // scratch of the split-key route (few query blocks, many keys); 0 when the route is not taken
 size_t sdpa_tc_workspace_bytes(const Gpu* g, const paras_sdpa_args& a);
 

@@ -1089,6 +1089,35 @@ SplitPlan split_plan(const Gpu* g, const paras_sdpa_args& a, bool rope) {
 
 size_t sdpa_tc_workspace_bytes(const Gpu* g, const paras_sdpa_args& a) { return split_plan(g, a, false).bytes; }
 
+// The check of causal_check_kernel for one [Lq, Lk] mask, answered on the host (a copy back and a wait):
+// for callers that choose a route by it, as the operator layer does before it picks a backward.
+int sdpa_mask_is_causal(Gpu* g, int gpu, const void* mask, int mask_kind, int dtype, int64_t row_stride, int Lq, int Lk,
+                        float scale, cudaStream_t s, int* result) {
+    *result = 0;
+    if (!mask || mask_kind < 1 || mask_kind > 3 || Lq < 1 || Lk < 1) return PARAS_OK;
+    void* dev = nullptr;
+    int st = paras_b200_malloc_async(gpu, sizeof(int), s, &dev);
+    if (st != PARAS_OK) return st;
+    int* flag = static_cast<int*>(dev);
+    const float masked_below = scale * 1.4426950408889634f * 60000.0f > 1000.0f ? -60000.0f : -INFINITY;
+    const int64_t spans = int64_t(Lq) * ((Lk + 15) / 16);
+    const int sms = g->sm_count > 0 ? g->sm_count : 148;
+    const unsigned blocks = unsigned(std::min<int64_t>((spans + 255) / 256, int64_t(sms) * 8));
+    int host = 0;
+    cudaError_t e = cudaMemsetAsync(flag, 1, sizeof(int), s);
+    if (e == cudaSuccess) {
+        causal_check_kernel<<<blocks, 256, 0, s>>>(mask, 0, row_stride, Lq, Lk, mask_kind, dtype == PARAS_BF16 ? 1 : 0, masked_below,
+                                                   nullptr, flag);
+        e = cudaGetLastError();
+    }
+    if (e == cudaSuccess) e = cudaMemcpyAsync(&host, flag, sizeof(int), cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    const int st2 = paras_b200_free_async(gpu, dev, s);
+    if (e != cudaSuccess) return fail(PARAS_E_CUDA, "paras sdpa: mask check failed: %s", cudaGetErrorString(e));
+    *result = host != 0;
+    return st2;
+}
+
 bool sdpa_tc_supported(const Gpu* g, const paras_sdpa_args& a, const char** why) {
     *why = "";
     if (g->cc_major != 10) { *why = "GPU is not compute capability 10.x"; return false; }

@@ -430,9 +430,40 @@ struct SdpaGeneralFunction : public torch::autograd::Function<SdpaGeneralFunctio
     }
 };
 
+// Is `mask` one [Lq, Lk] mask for every batch element and head, and the causal mask written out?  Then the call
+// is the reference's is_causal=True (attention_ops.cpp:100-116 builds exactly that mask) and can take the fused
+// kernels, whose backward takes no mask tensor.  The answer needs a pass over the mask on the GPU and a wait for
+// it, so it is remembered for the tensor (storage, version, shape): a model hands the same mask to every layer.
+bool mask_is_causal(const Tensor& mask, const Tensor& query, int64_t Lq, int64_t Lk, double scale) {
+    if (mask.dim() < 2 || mask.size(-2) != Lq || mask.size(-1) != Lk || mask.stride(-1) != 1 || Lq < 2 || Lk < 2) return false;
+    for (int64_t d = 0; d + 2 < mask.dim(); ++d)
+        if (mask.size(d) != 1) return false;
+    int kind;
+    if (mask.scalar_type() == c10::kBool) kind = 1;
+    else if (mask.scalar_type() == query.scalar_type()) kind = 2;
+    else if (mask.scalar_type() == c10::kFloat) kind = 3;
+    else return false;
+    struct Seen { const void* ptr; uint32_t version; int64_t Lq, Lk, stride; int kind; double scale; bool result; };
+    static thread_local Seen seen{nullptr, 0, 0, 0, 0, 0, 0.0, false};
+    const void* ptr = mask.data_ptr();
+    const uint32_t version = mask._version();
+    if (seen.ptr == ptr && seen.version == version && seen.Lq == Lq && seen.Lk == Lk && seen.stride == mask.stride(-2) &&
+        seen.kind == kind && seen.scale == scale)
+        return seen.result;
+    Runtime& rt = Runtime::get();
+    c10::DeviceGuard guard(query.device());
+    int result = 0;
+    PARAS_ABI(paras_b200_sdpa_mask_is_causal(rt.gpu_of(query), ptr, kind, dtype_code(query.scalar_type()), mask.stride(-2),
+                                             int32_t(Lq), int32_t(Lk), scale, nullptr, &result));
+    seen = Seen{ptr, version, Lq, Lk, mask.stride(-2), kind, scale, result != 0};
+    return seen.result;
+}
+
 Tensor sdpa_autograd(const Tensor& query, const Tensor& key, const Tensor& value,
-                     const std::optional<Tensor>& attn_mask, double dropout_p, bool is_causal,
+                     const std::optional<Tensor>& attn_mask_in, double dropout_p, bool is_causal_in,
                      std::optional<double> scale, bool enable_gqa) {
+    std::optional<Tensor> attn_mask = attn_mask_in;
+    bool is_causal = is_causal_in;
     const bool needs_grad = at::GradMode::is_enabled() &&
                             (query.requires_grad() || key.requires_grad() || value.requires_grad());
     if (!needs_grad) {
@@ -440,13 +471,21 @@ Tensor sdpa_autograd(const Tensor& query, const Tensor& key, const Tensor& value
         return at::scaled_dot_product_attention(query, key, value, attn_mask, dropout_p, is_causal, scale,
                                                 enable_gqa);
     }
-    const bool has_mask = attn_mask.has_value() && attn_mask->defined();
+    bool has_mask = attn_mask.has_value() && attn_mask->defined();
     TORCH_CHECK(query.dim() >= 3 && key.dim() == query.dim() && value.dim() == query.dim(),
                 "paras sdpa: query, key and value must have the same rank (>= 3)");
     // the fused kernels: 16-bit, no mask tensor, no dropout, head dim 128 / 64 (or, on the composite of
     // GEMMs, 16-byte rows of both the head dim and the key length)
     const int64_t E = query.size(-1), Lk = key.size(-2);
     const bool half = query.scalar_type() == c10::kBFloat16 || query.scalar_type() == c10::kHalf;
+    // a causal mask passed as a tensor is is_causal=True
+    if (has_mask && !is_causal && dropout_p == 0.0 && half && (E == 128 || E == 64) && query.numel() > 0 && key.numel() > 0 &&
+        attn_mask->device() == query.device() &&
+        mask_is_causal(*attn_mask, query, query.size(-2), Lk, scale.has_value() ? *scale : 1.0 / std::sqrt(double(E)))) {
+        has_mask = false;
+        is_causal = true;
+        attn_mask = std::nullopt;
+    }
     const bool fused = !has_mask && dropout_p == 0.0 && half && E % 8 == 0 && (E == 128 || E == 64 || Lk % 8 == 0) &&
                        query.numel() > 0 && key.numel() > 0;
     if (!fused)

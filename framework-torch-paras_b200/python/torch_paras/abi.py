@@ -31,7 +31,7 @@ EXPORTS = [
     "paras_b200_memcpy_peer", "paras_b200_memset", "paras_b200_host_alloc", "paras_b200_host_free",
     "paras_b200_host_is_pinned",
     "paras_b200_strided_copy", "paras_b200_fill", "paras_b200_sdpa_fwd",
-    "paras_b200_sdpa_workspace_bytes", "paras_b200_sdpa_last_kernel", "paras_b200_rmsnorm_fwd",
+    "paras_b200_sdpa_workspace_bytes", "paras_b200_sdpa_mask_is_causal", "paras_b200_sdpa_last_kernel", "paras_b200_rmsnorm_fwd",
     "paras_b200_sdpa_fwd_static_scratch", "paras_b200_sdpa_static_scratch_bytes",
     "paras_b200_rmsnorm_bwd", "paras_b200_swiglu_fwd", "paras_b200_swiglu_bwd",
     "paras_b200_rotate_half", "paras_b200_gemm", "paras_b200_sdpa_fwd_host", "paras_b200_sdpa_bwd",
@@ -441,6 +441,18 @@ def sdpa_workspace_bytes(q, k, v, *, causal=False, flags=0) -> int:
     n = C.c_size_t(0)
     check(lib().paras_b200_sdpa_workspace_bytes(C.byref(a), C.byref(n)))
     return int(n.value)
+
+
+def sdpa_mask_is_causal(mask, dtype, scale=None, head_dim=128) -> bool:
+    """Whether a 2-D [Lq, Lk] mask (bool, `dtype`, or fp32) is the causal mask written out; waits for the GPU."""
+    assert mask.dim() == 2 and mask.stride(1) == 1
+    kind = 1 if mask.dtype == torch.bool else (2 if mask.dtype == dtype else 3)
+    res = C.c_int(0)
+    check(lib().paras_b200_sdpa_mask_is_causal(_gpu_of(mask), C.c_void_p(mask.data_ptr()), kind, _DT[dtype],
+                                               C.c_int64(mask.stride(0)), mask.shape[0], mask.shape[1],
+                                               C.c_double(scale if scale is not None else head_dim ** -0.5),
+                                               C.c_void_p(_stream_of(mask, None)), C.byref(res)))
+    return bool(res.value)
 
 
 def sdpa_split_layout(rows: int, D: int, splits: int):

@@ -174,6 +174,13 @@ typedef struct paras_sdpa_args {
 
 int paras_b200_sdpa_fwd(const paras_sdpa_args* args);
 int paras_b200_sdpa_workspace_bytes(const paras_sdpa_args* args, size_t* bytes);
+/* Is the [Lq, Lk] mask (mask_kind as in paras_sdpa_args, `dtype` the tensors' dtype, rows `row_stride` elements
+ * apart) the causal mask written out -- visible exactly where key <= query, i.e. what the reference builds from
+ * is_causal (attention_ops.cpp:100-116) -- so that the call may be made with causal = 1 and no mask?  Looks at
+ * the mask on the device and WAITS for the answer (*result = 1 or 0): for callers that pick a route by it, such
+ * as a backward that takes no mask tensor.  paras_b200_sdpa_fwd itself recognises such masks without waiting. */
+int paras_b200_sdpa_mask_is_causal(int gpu, const void* mask, int mask_kind, int dtype, int64_t row_stride, int32_t Lq,
+                                   int32_t Lk, double scale, void* stream, int* result);
 /* Name of the kernel the last successful paras_b200_sdpa_fwd call of this thread used; for tests and
  * logs.  "tcgen05" (tensor-core tiles), "tcgen05_split" (few query blocks against a long key range: the
  * key range runs in pieces that a second kernel merges; scratch from `workspace` or the pool, size from

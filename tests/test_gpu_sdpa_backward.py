@@ -140,6 +140,53 @@ def test_autograd_wrapper_on_the_device():
     assert dk_.grad.shape == k.shape and dq_.grad.dtype == torch.bfloat16
 
 
+@pytest.mark.parametrize("kind", ["bool", "additive", "additive_4d_min"])
+def test_a_causal_mask_passed_as_a_tensor_trains_through_the_fused_kernels(kind):
+    # F.scaled_dot_product_attention(q, k, v, attn_mask=<the lower triangle>) with requires_grad: the operator
+    # layer asks the GPU whether the mask is the causal mask and, if so, runs the call as is_causal=True:
+    # output and gradients equal that call's bit for bit.  A mask one entry off takes the general route
+    # and still matches float64.
+    g = torch.Generator().manual_seed(53)
+    q = torch.randn(2, 4, 320, 128, generator=g).bfloat16()
+    k = torch.randn(2, 2, 320, 128, generator=g).bfloat16()
+    v = torch.randn(2, 2, 320, 128, generator=g).bfloat16()
+    dout = torch.randn(2, 4, 320, 128, generator=g).bfloat16()
+    tri = torch.ones(320, 320, dtype=torch.bool).tril()
+
+    def as_kind(t):
+        if kind == "bool":
+            return t
+        if kind == "additive":
+            return torch.zeros(320, 320).masked_fill(~t, float("-inf")).bfloat16()
+        return torch.zeros(1, 1, 320, 320, dtype=torch.bfloat16).masked_fill(~t, torch.finfo(torch.bfloat16).min)
+
+    def run(**kw):
+        qd, kd, vd = (t.to(DEV).requires_grad_(True) for t in (q, k, v))
+        out = F.scaled_dot_product_attention(qd, kd, vd, enable_gqa=True, **kw)
+        out.backward(dout.to(DEV))
+        return out.detach().cpu(), qd.grad.cpu(), kd.grad.cpu(), vd.grad.cpu()
+
+    ref = run(is_causal=True)
+    mask_dev = as_kind(tri).to(DEV)
+    for _ in range(2):                       # the second call answers from the remembered check
+        got = run(attn_mask=mask_dev)
+        for a_, b_ in zip(got, ref):
+            assert torch.equal(a_, b_)
+    off = tri.clone()
+    off[200, 250] = True
+    got = run(attn_mask=as_kind(off).to(DEV))
+    assert not torch.equal(got[0], ref[0])
+    q64, k64, v64 = (t.double().requires_grad_(True) for t in (q, k, v))
+    s_ = (q64 @ k64.repeat_interleave(2, 1).transpose(-1, -2)) / math.sqrt(128)
+    want = torch.softmax(s_.masked_fill(~off, float("-inf")), -1) @ v64.repeat_interleave(2, 1)
+    want.backward(dout.double())
+    assert (got[0].double() - want.detach()).abs().max().item() <= 2e-2
+    for got_g, want_g in zip(got[1:], (q64.grad, k64.grad, v64.grad)):
+        assert (got_g.double() - want_g).abs().max().item() <= 2e-2 * max(want_g.abs().max().item(), 1e-2)
+    # the check itself, through the C ABI
+    assert abi.sdpa_mask_is_causal(tri.to(CUDA), torch.bfloat16) and not abi.sdpa_mask_is_causal(off.to(CUDA), torch.bfloat16)
+
+
 def test_unsupported_operands_raise():
     q = torch.randn(1, 2, 64, 128, device=CUDA)
     with pytest.raises(RuntimeError):
