@@ -443,20 +443,24 @@ bool mask_is_causal(const Tensor& mask, const Tensor& query, int64_t Lq, int64_t
     else if (mask.scalar_type() == query.scalar_type()) kind = 2;
     else if (mask.scalar_type() == c10::kFloat) kind = 3;
     else return false;
-    struct Seen { const void* ptr; uint32_t version; int64_t Lq, Lk, stride; int kind; double scale; bool result; };
-    static thread_local Seen seen{nullptr, 0, 0, 0, 0, 0, 0.0, false};
+    // The remembered mask is held, so that its memory cannot be handed to another tensor while the answer is
+    // kept; a write to it moves its version.  (Heap-allocated and never destroyed: a tensor of this device
+    // must not be released during static destruction, after the runtime.)
+    struct Seen { Tensor held; const void* ptr; uint32_t version; int64_t Lq, Lk, stride; int kind; double scale; bool result; };
+    static thread_local Seen& seen = *new Seen{Tensor(), nullptr, 0, 0, 0, 0, 0, 0.0, false};
     const void* ptr = mask.data_ptr();
-    const uint32_t version = mask._version();
-    if (seen.ptr == ptr && seen.version == version && seen.Lq == Lq && seen.Lk == Lk && seen.stride == mask.stride(-2) &&
-        seen.kind == kind && seen.scale == scale)
+    const bool tracked = !mask.is_inference();     // an inference tensor has no version counter: ask every time
+    const uint32_t version = tracked ? mask._version() : 0;
+    if (tracked && seen.held.defined() && seen.ptr == ptr && seen.version == version && seen.Lq == Lq && seen.Lk == Lk &&
+        seen.stride == mask.stride(-2) && seen.kind == kind && seen.scale == scale)
         return seen.result;
     Runtime& rt = Runtime::get();
     c10::DeviceGuard guard(query.device());
     int result = 0;
     PARAS_ABI(paras_b200_sdpa_mask_is_causal(rt.gpu_of(query), ptr, kind, dtype_code(query.scalar_type()), mask.stride(-2),
                                              int32_t(Lq), int32_t(Lk), scale, nullptr, &result));
-    seen = Seen{ptr, version, Lq, Lk, mask.stride(-2), kind, scale, result != 0};
-    return seen.result;
+    if (tracked) seen = Seen{mask, ptr, version, Lq, Lk, mask.stride(-2), kind, scale, result != 0};
+    return result != 0;
 }
 
 Tensor sdpa_autograd(const Tensor& query, const Tensor& key, const Tensor& value,

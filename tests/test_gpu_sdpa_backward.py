@@ -183,6 +183,18 @@ def test_a_causal_mask_passed_as_a_tensor_trains_through_the_fused_kernels(kind)
     assert (got[0].double() - want.detach()).abs().max().item() <= 2e-2
     for got_g, want_g in zip(got[1:], (q64.grad, k64.grad, v64.grad)):
         assert (got_g.double() - want_g).abs().max().item() <= 2e-2 * max(want_g.abs().max().item(), 1e-2)
+    # the remembered answer follows the tensor, not the address: writing into the mask, or a new mask of the same
+    # shape (which the allocator may place where an old one was), is looked at again
+    m2 = as_kind(tri).to(DEV)
+    assert torch.equal(run(attn_mask=m2)[0], ref[0])
+    if kind == "bool":
+        m2[200, 250] = True
+    else:
+        m2[..., 200, 250] = 0
+    assert not torch.equal(run(attn_mask=m2)[0], ref[0])
+    del m2
+    m3 = as_kind(off).to(DEV)
+    assert not torch.equal(run(attn_mask=m3)[0], ref[0])
     # the check itself, through the C ABI
     assert abi.sdpa_mask_is_causal(tri.to(CUDA), torch.bfloat16) and not abi.sdpa_mask_is_causal(off.to(CUDA), torch.bfloat16)
 
