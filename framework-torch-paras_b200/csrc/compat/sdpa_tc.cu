@@ -140,6 +140,11 @@ struct TcParams {
     // the diagonal tile cut by position) and does not read the mask.
     const int* mask_is_causal;
     int kv_len_if_causal;   // kv_len holds what the causal check found per batch element: valid only if *mask_is_causal
+    // Two launches for one call, of which the device picks one: this launch returns at once unless
+    // (*gate != 0) == (gate_want != 0).  (A mask that may be the causal mask: the causal kernel runs if it is,
+    // the masked kernel if it is not.)
+    const int* gate;
+    int gate_want;
 };
 
 // One work item = one 256-row query block of one (batch, head).
@@ -243,6 +248,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     constexpr int kChunks = HD / 64;                 // 64-element slabs of the head dim
     constexpr uint32_t kLoadBytes = kChunks * kChunkBytes;   // bytes one Q / K / V tile brings in
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (p.gate && (__ldg(p.gate) != 0) != (p.gate_want != 0)) return;   // the other launch of the pair does this call
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < kNumBars; ++i) {
@@ -1159,6 +1165,7 @@ int sdpa_tc_launch(Gpu* g, const paras_sdpa_args& a, float scale, cudaStream_t s
         }
     }
     void* lens = nullptr;   // kv_len and key_prefix of a key-padding mask
+    bool gate_pair = false;  // launch the causal kernel and the masked kernel, the device picks by the mask check
     auto release = [&](int status) {
         if (lens) {
             const int st3 = paras_b200_free_async(a.gpu, lens, s);
@@ -1230,6 +1237,7 @@ int sdpa_tc_launch(Gpu* g, const paras_sdpa_args& a, float scale, cudaStream_t s
                                                    masked_below, nullptr, flag);
         if (cudaGetLastError() != cudaSuccess) return release(fail(PARAS_E_CUDA, "paras sdpa: mask check launch failed"));
         p.mask_is_causal = flag;
+        gate_pair = a.D == 128 || a.D == 64;
     } else if (p.mask_kind && p.ms[0] != 0 && p.ms[1] == 0 && p.ms[2] != 0 && p.ms[3] == 1 && a.Lq > 1 && a.Lk > 1) {
         // one [Lq, Lk] mask per batch element, shared by its heads: causal over right-padded sequences?
         if ((st = paras_b200_malloc_async(a.gpu, size_t(a.B + 1) * sizeof(int), s, &lens)) != PARAS_OK) return release(st);
@@ -1277,12 +1285,27 @@ int sdpa_tc_launch(Gpu* g, const paras_sdpa_args& a, float scale, cudaStream_t s
         else st = bf ? launch(sdpa_tc_kernel<true, false, 64, false, true>) : launch(sdpa_tc_kernel<false, false, 64, false, true>);
     } else if (rope) {
         st = bf ? launch(sdpa_tc_kernel<true, false, 128, true>) : launch(sdpa_tc_kernel<false, false, 128, true>);
-    } else if (a.D == 128) {
-        if (p.mask_kind) st = bf ? launch(sdpa_tc_kernel<true, true, 128>) : launch(sdpa_tc_kernel<false, true, 128>);
-        else st = bf ? launch(sdpa_tc_kernel<true, false, 128>) : launch(sdpa_tc_kernel<false, false, 128>);
     } else {
-        if (p.mask_kind) st = bf ? launch(sdpa_tc_kernel<true, true, 64>) : launch(sdpa_tc_kernel<false, true, 64>);
-        else st = bf ? launch(sdpa_tc_kernel<true, false, 64>) : launch(sdpa_tc_kernel<false, false, 64>);
+        if (p.mask_kind && gate_pair) {
+            // The mask may be the causal mask: the causal kernel is launched for that case (it is a tenth faster
+            // than the masked kernel running without its mask) and returns at once otherwise; the masked kernel
+            // that follows does the opposite.
+            const TcParams keep = p;
+            p.mask = nullptr; p.mask_kind = 0; p.causal = 1;
+            p.gate = keep.mask_is_causal; p.gate_want = 1; p.mask_is_causal = nullptr;
+            if (a.D == 128) st = bf ? launch(sdpa_tc_kernel<true, false, 128>) : launch(sdpa_tc_kernel<false, false, 128>);
+            else st = bf ? launch(sdpa_tc_kernel<true, false, 64>) : launch(sdpa_tc_kernel<false, false, 64>);
+            p = keep;
+            p.gate = keep.mask_is_causal; p.gate_want = 0; p.mask_is_causal = nullptr;
+            if (st != PARAS_OK) return release(st);
+        }
+        if (a.D == 128) {
+            if (p.mask_kind) st = bf ? launch(sdpa_tc_kernel<true, true, 128>) : launch(sdpa_tc_kernel<false, true, 128>);
+            else st = bf ? launch(sdpa_tc_kernel<true, false, 128>) : launch(sdpa_tc_kernel<false, false, 128>);
+        } else {
+            if (p.mask_kind) st = bf ? launch(sdpa_tc_kernel<true, true, 64>) : launch(sdpa_tc_kernel<false, true, 64>);
+            else st = bf ? launch(sdpa_tc_kernel<true, false, 64>) : launch(sdpa_tc_kernel<false, false, 64>);
+        }
     }
     if (st != PARAS_OK) return release(st);
     if (cudaGetLastError() != cudaSuccess) return release(fail(PARAS_E_CUDA, "paras sdpa: sdpa_tc_kernel launch failed"));
