@@ -233,7 +233,9 @@ __device__ __forceinline__ bool any_zero_byte(const uint4& w) {
 // softmax warps that own its rows, between its TMA load and the first QK^T (head dim 128).
 // SPLIT: units cover a piece of the key range and write partial results (its own instantiation as
 // well: an index added on the softmax chain costs the unsplit kernel 2-3 %).
-template <bool BF16, bool MASK, int HD, bool ROPE = false, bool SPLIT = false, bool PACK = false>
+// LENS: the kernel without mask code, but with a key count per batch element (p.kv_len): what a mask that
+// turned out to be lengths, or the causal mask over padded sequences, runs on.
+template <bool BF16, bool MASK, int HD, bool ROPE = false, bool SPLIT = false, bool PACK = false, bool LENS = false>
 __global__ void __launch_bounds__(kThreads, 1)
 sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o,
@@ -306,7 +308,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                 return true;
             };
             Item it;
-            for (int seq = 0; ok && get_item<SPLIT, PACK, MASK>(p, seq, &it); ++seq) {
+            for (int seq = 0; ok && get_item<SPLIT, PACK, MASK || LENS>(p, seq, &it); ++seq) {
                 if (it.n == 0) continue;
                 const int kv0 = SPLIT ? it.kv0 : 0;
                 ok = load_entry(&map_k, kv0 * BN, it.hk, it.b);  // K0 completes the previous item's last pair
@@ -364,7 +366,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             uint32_t qcnt[2] = {0, 0};   // items that used tile t (Q / O barriers)
             uint32_t pcnt[2] = {0, 0};   // softmax iterations of tile t so far (P barrier)
             Item it;
-            for (int seq = 0; ok && get_item<SPLIT, PACK, MASK>(p, seq, &it); ++seq) {
+            for (int seq = 0; ok && get_item<SPLIT, PACK, MASK || LENS>(p, seq, &it); ++seq) {
                 if (it.n == 0) continue;
                 if (!have) ok = mbar_wait(bar(kBarKVFull + (G & 1)), (G >> 1) & 1, abort_flag, 3);
 #pragma unroll
@@ -432,10 +434,10 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         uint32_t scnt = 0;  // S tiles consumed so far
         uint32_t ocnt = 0;  // items finished so far
         Item it;
-        for (int seq = 0; ok && get_item<SPLIT, PACK, MASK>(p, seq, &it); ++seq) {
+        for (int seq = 0; ok && get_item<SPLIT, PACK, MASK || LENS>(p, seq, &it); ++seq) {
             const int nt = it.ntile[t];
             if (nt == 0) continue;
-            const int lk_item = MASK ? it.lk : p.Lk;
+            const int lk_item = (MASK || LENS) ? it.lk : p.Lk;
             const bool dyn_causal = MASK && p.mask_is_causal && __ldg(p.mask_is_causal) != 0;
             const bool causal = p.causal != 0 || dyn_causal;
             const bool mask_off = dyn_causal || (MASK && p.key_prefix && __ldg(p.key_prefix + it.b) != 0);   // position or length says it all
@@ -866,7 +868,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 // padding mask), gets kv_len = Lk and key_prefix = 0: the mask is then applied as given.
 __global__ void __launch_bounds__(256) key_mask_scan_kernel(const void* __restrict__ mask, int64_t bstride, int Lk, int kind, int bf16,
                                                             float masked_below, int* __restrict__ kv_len,
-                                                            int* __restrict__ key_prefix) {
+                                                            int* __restrict__ key_prefix, int* __restrict__ all_prefix) {
     __shared__ int s_last, s_count, s_other;
     if (threadIdx.x == 0) { s_last = -1; s_count = 0; s_other = 0; }
     __syncthreads();
@@ -907,6 +909,7 @@ __global__ void __launch_bounds__(256) key_mask_scan_kernel(const void* __restri
         const bool usable = s_last >= 0 && s_other == 0;
         kv_len[blockIdx.x] = usable ? s_last + 1 : Lk;
         key_prefix[blockIdx.x] = usable && s_count == s_last + 1;
+        if (!(usable && s_count == s_last + 1)) atomicAnd(all_prefix, 0);   // (nonzero on entry)
     }
 }
 
@@ -1166,6 +1169,8 @@ int sdpa_tc_launch(Gpu* g, const paras_sdpa_args& a, float scale, cudaStream_t s
     }
     void* lens = nullptr;   // kv_len and key_prefix of a key-padding mask
     bool gate_pair = false;  // launch the causal kernel and the masked kernel, the device picks by the mask check
+    const int* lens_gate = nullptr;   // likewise with the LENS kernel first (key counts per batch element), gated on this flag
+    bool lens_causal = false;
     auto release = [&](int status) {
         if (lens) {
             const int st3 = paras_b200_free_async(a.gpu, lens, s);
@@ -1218,10 +1223,12 @@ int sdpa_tc_launch(Gpu* g, const paras_sdpa_args& a, float scale, cudaStream_t s
     // -60000 (fp16's most negative values) times scale * log2(e) must be far below the -149 at which exp2 gives 0
     const float masked_below = scale * 1.4426950408889634f * 60000.0f > 1000.0f ? -60000.0f : -INFINITY;
     if (p.mask_kind && p.ms[1] == 0 && p.ms[2] == 0 && p.ms[3] == 1 && a.Lk > 1) {
-        if ((st = paras_b200_malloc_async(a.gpu, size_t(2 * a.B) * sizeof(int), s, &lens)) != PARAS_OK) return release(st);
+        if ((st = paras_b200_malloc_async(a.gpu, size_t(2 * a.B + 1) * sizeof(int), s, &lens)) != PARAS_OK) return release(st);
         int* li = static_cast<int*>(lens);
+        if (cudaMemsetAsync(li + 2 * a.B, 1, sizeof(int), s) != cudaSuccess) return release(fail(PARAS_E_CUDA, "paras sdpa: memset failed"));
         key_mask_scan_kernel<<<unsigned(a.B), 256, 0, s>>>(a.mask, p.ms[0], a.Lk, p.mask_kind, a.dtype == PARAS_BF16 ? 1 : 0,
-                                                          masked_below, li, li + a.B);
+                                                          masked_below, li, li + a.B, li + 2 * a.B);
+        lens_gate = li + 2 * a.B;   // every batch element's valid keys are a prefix: the kernel without mask code does
         if (cudaGetLastError() != cudaSuccess) return release(fail(PARAS_E_CUDA, "paras sdpa: mask scan launch failed"));
         p.kv_len = li;
         p.key_prefix = li + a.B;
@@ -1252,6 +1259,8 @@ int sdpa_tc_launch(Gpu* g, const paras_sdpa_args& a, float scale, cudaStream_t s
         p.kv_len = li;
         p.kv_len_if_causal = 1;
         p.mask_is_causal = li + a.B;
+        lens_gate = li + a.B;
+        lens_causal = true;
     }
     p.status = g->status_dev;
     if (rope) {
@@ -1286,7 +1295,17 @@ int sdpa_tc_launch(Gpu* g, const paras_sdpa_args& a, float scale, cudaStream_t s
     } else if (rope) {
         st = bf ? launch(sdpa_tc_kernel<true, false, 128, true>) : launch(sdpa_tc_kernel<false, false, 128, true>);
     } else {
-        if (p.mask_kind && gate_pair) {
+        if (p.mask_kind && lens_gate) {
+            const TcParams keep = p;
+            p.mask = nullptr; p.mask_kind = 0; p.causal = lens_causal ? 1 : 0;
+            p.key_prefix = nullptr; p.mask_is_causal = nullptr; p.kv_len_if_causal = 0;
+            p.gate = lens_gate; p.gate_want = 1;
+            if (a.D == 128) st = bf ? launch(sdpa_tc_kernel<true, false, 128, false, false, false, true>) : launch(sdpa_tc_kernel<false, false, 128, false, false, false, true>);
+            else st = bf ? launch(sdpa_tc_kernel<true, false, 64, false, false, false, true>) : launch(sdpa_tc_kernel<false, false, 64, false, false, false, true>);
+            p = keep;
+            p.gate = lens_gate; p.gate_want = 0;
+            if (st != PARAS_OK) return release(st);
+        } else if (p.mask_kind && gate_pair) {
             // The mask may be the causal mask: the causal kernel is launched for that case (it is a tenth faster
             // than the masked kernel running without its mask) and returns at once otherwise; the masked kernel
             // that follows does the opposite.
