@@ -39,7 +39,7 @@ def test_random_shapes_forward_and_backward(seed):
         Lq = rnd.choice([1, 2, 7, 64, 127, 128, 129, 200, 256, 300, 511, 640])
         Lk = rnd.choice([1, 5, 63, 64, 65, 128, 130, 255, 256, 257, 400, 700, 1000])
         causal = rnd.random() < 0.4
-        kind = None if causal else rnd.choice([None, None, "bool", "add", "addf32", "pad"])
+        kind = None if causal else rnd.choice([None, None, "bool", "add", "addf32", "pad", "tril", "trilpad"])
         g = torch.Generator().manual_seed(seed * 1000 + it)
         q = torch.randn(B, Hq, Lq, D, generator=g).to(dtype)
         k = torch.randn(B, Hkv, Lk, D, generator=g).to(dtype)
@@ -57,6 +57,13 @@ def test_random_shapes_forward_and_backward(seed):
             mask = torch.ones(B, 1, 1, Lk, dtype=torch.bool)
             mask[:, :, :, Lk - Lk // 3:] = False
             mask[..., 0] = True
+        elif kind == "tril":          # the causal mask written out, bool or additive
+            tri = torch.ones(Lq, Lk, dtype=torch.bool).tril()
+            mask = tri if rnd.random() < 0.5 else torch.zeros(Lq, Lk).masked_fill(~tri, float("-inf")).to(dtype)
+        elif kind == "trilpad":       # causal over sequences padded on the right
+            tri = torch.ones(Lq, Lk, dtype=torch.bool).tril()
+            lens = [max(1, Lk - b * (Lk // 3)) for b in range(B)]
+            mask = torch.stack([tri & (torch.arange(Lk)[None, :] < n) for n in lens])[:, None]
         tag = f"seed {seed} case {it}: {dtype} B{B} Hq{Hq} Hkv{Hkv} Lq{Lq} Lk{Lk} D{D} causal={causal} mask={kind}"
         dm = None if mask is None else mask.to(DEV)
         qd, kd, vd = q.to(DEV), k.to(DEV), v.to(DEV)
