@@ -37,6 +37,17 @@
 // over the row off the chain  S ready -> P ready -> next S  that bounds the kernel.  A tile
 // whose sums say that P may overflow is redone against its true max before P is stored.
 //
+// Instantiations beside the plain and the masked kernel (each pays only for what it uses; an index added to the
+// softmax chain at run time costs the plain kernel 2-3 %):
+//   ROPE   the query tile is rotated in shared memory before its first MMA (rotary embedding)
+//   SPLIT  few query blocks against a long key range: units take pieces of the key range, sdpa_tc_combine_kernel
+//          merges the partial outputs by their log-sum-exp
+//   PACK   the query heads of a GQA group share an item when group x Lq <= 256 (rows = (head, position))
+//   LENS   a key count per batch element (what a key-padding mask, or the causal mask over right-padded
+//          sequences, turns into after key_mask_scan_kernel / causal_check_kernel have looked at it)
+// and a gate (TcParams::gate) by which one of two launches made for the same call returns at once: the device,
+// not the host, knows what the mask check found.
+//
 // Every wait is bounded (tc_prims.cuh); a wait that runs out raises the CTA's abort flag,
 // all roles fall through to the common exit, TMEM is freed and the GPU's status word is set to
 // a mask of the waits that were pending (bits: 0-1 Q buffer free, 2 ring slot free, 3 K/V
